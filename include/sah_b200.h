@@ -1,0 +1,250 @@
+/*
+ * sah_b200.h -- C ABI of the B200 (sm_100a) sparse-decode attention library.
+ *
+ * Every entry point is `extern "C"`, takes plain device pointers, extents and
+ * element strides, launches its kernels on the CUDA stream passed as the last
+ * argument (a `cudaStream_t` carried as `void*`), never synchronises the host
+ * and never allocates.  The return value is an `sah_status`; on a non-zero
+ * status nothing has been launched and `sah_last_error()` describes why.
+ *
+ * Shared conventions
+ *   rows        one mask row per (batch b, query head h, query position q):
+ *               row = (b * Hq + h) * Sq + q.
+ *   bits        the active set of a mask: uint32 [rows][W], bit (j & 31) of
+ *               word (j >> 5) is key column j.  W >= ceil(S / 32); bits at
+ *               columns >= S are zero.
+ *   ptr/wpre    CSR companion of `bits`: ptr int64 [rows + 1] is the exclusive
+ *               scan of the per-row popcounts; wpre int32 [rows][W] is the
+ *               exclusive popcount scan of the words inside one row.  The
+ *               k-th set bit of a row (ascending column order) owns
+ *               data[ptr[row] + k].
+ *   data        per active entry weight in the mask dtype (the reference's
+ *               Mask.data); NULL means every active entry has weight 1.
+ *   dtype       SAH_F32 or SAH_BF16: element type of Q/K/V, of the additive
+ *               attention bias and of mask weights.
+ *   strides     counted in elements; the head dimension is always contiguous.
+ *   GQA         query head h reads KV head h / (Hq / Hkv).
+ *
+ * Reference citations name files of skylight-org/sparse-attention-hub by
+ * their path inside that project.
+ */
+#ifndef SAH_B200_H
+#define SAH_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  SAH_OK = 0,
+  SAH_ERR_INVALID = 1,     /* bad argument (null pointer, extent, alignment) */
+  SAH_ERR_UNSUPPORTED = 2, /* legal in the reference, not built here        */
+  SAH_ERR_CUDA = 3,        /* the CUDA runtime refused a launch             */
+  SAH_ERR_WORKSPACE = 4    /* caller-provided workspace too small           */
+} sah_status;
+
+typedef enum { SAH_F32 = 0, SAH_BF16 = 1 } sah_dtype;
+
+typedef enum {
+  SAH_ACT_RELU = 0,
+  SAH_ACT_SILU = 1,
+  SAH_ACT_GELU = 2,
+  SAH_ACT_TANH = 3
+} sah_activation;
+
+/* Library identity and the message of the last non-zero status returned on
+ * the calling thread. */
+const char* sah_version(void);
+const char* sah_last_error(void);
+
+/* ------------------------------------------------------------------------ *
+ * Mask container kernels
+ * ------------------------------------------------------------------------ */
+
+/* Set (value = 1) or clear (value = 0) a per-row column band: row (b,h,q)
+ * touches columns [lo_base + q * lo_qstep, hi_base + q * hi_qstep) clipped
+ * to [0, S).
+ *   SinkMasker  : lo = 0, hi = sink, steps 0, value 1
+ *                 (maskers/fixed/implementations/basic_fixed.py:354-363).
+ *   LocalMasker : band lo = S-Sq-W+1+q, hi = S-Sq+1+q, value 1, followed by a
+ *                 clear of [S-Sq+1+q, S) (basic_fixed.py:48-67).
+ * Valid only for masks whose weights are all 1 (data == NULL). */
+int sah_mask_fill_band(uint32_t* bits, int64_t rows, int Sq, int64_t S, int64_t W,
+                       int64_t lo_base, int64_t lo_qstep, int64_t hi_base,
+                       int64_t hi_qstep, int value, void* stream);
+
+/* ptr[rows+1] and (optionally, may be NULL) wpre[rows][W] from bits.
+ * Replaces the nonzero/count_nonzero/cumsum chain of Mask.get_index_mask
+ * (utils/mask.py:553-573). */
+int sah_mask_rowscan(const uint32_t* bits, int64_t rows, int64_t W, int32_t* wpre,
+                     int64_t* ptr, void* stream);
+
+/* Flat int64 indices (row * S + column, ascending) of every set bit, laid out
+ * by ptr/wpre: the `indices` array of utils/mask.py:233-270. */
+int sah_mask_bits_to_indices(const uint32_t* bits, const int32_t* wpre,
+                             const int64_t* ptr, int64_t rows, int64_t S, int64_t W,
+                             int64_t* indices, void* stream);
+
+/* Dense [rows][S] weights in `dtype` from bits (+ data): Mask.get_dense_mask
+ * (utils/mask.py:577-611). */
+int sah_mask_bits_to_dense(const uint32_t* bits, const void* data, const int32_t* wpre,
+                           const int64_t* ptr, int dtype, int64_t rows, int64_t S,
+                           int64_t W, void* dense, void* stream);
+
+/* bits from a dense [rows][S] weight tensor (non-zero = active):
+ * Mask.create_mask_from_dense_mask (utils/mask.py:272-299). */
+int sah_mask_dense_to_bits(const void* dense, int dtype, int64_t rows, int64_t S,
+                           int64_t W, uint32_t* bits, void* stream);
+
+/* data[ptr[row] + k] = dense[row][column of k-th set bit]. */
+int sah_mask_dense_gather_data(const void* dense, int dtype, const uint32_t* bits,
+                               const int32_t* wpre, const int64_t* ptr, int64_t rows,
+                               int64_t S, int64_t W, void* data, void* stream);
+
+/* Sampled-set merge, the `clamp(previous + sampled, 0, 1)` of
+ * Mask.merge_mask_dense (utils/mask.py:875-877) when the previous mask has
+ * unit weights: out_bits = prev | samp;  an entry already in prev keeps
+ * weight 1, an entry only in samp gets row_weight[row] (weights in `dtype`,
+ * rounded as the reference rounds them).  Writes out_bits, then the caller
+ * runs sah_mask_rowscan on out_bits and sah_mask_sample_data to fill data. */
+int sah_mask_or(const uint32_t* a, const uint32_t* b, int64_t words, uint32_t* out,
+                void* stream);
+int sah_mask_sample_data(const uint32_t* prev_bits, const uint32_t* out_bits,
+                         const int32_t* wpre, const int64_t* ptr, const void* row_weight,
+                         const void* dense_weight, int dtype, int64_t rows, int64_t S,
+                         int64_t W, void* data, void* stream);
+
+/* Scatter a ragged list of sampled columns into a bitmap.  sample j belongs
+ * to the row r with sptr[r] <= j < sptr[r+1] (sptr int64 [rows+1], device);
+ * cols int64 [n].  Duplicates collapse, as the dense conversion of the
+ * reference does (utils/mask.py:604-608).  `bits` must be zeroed by the
+ * caller (or hold a mask to OR into). */
+int sah_mask_scatter_samples(const int64_t* cols, const int64_t* sptr, int64_t rows,
+                             int64_t n_max, int64_t S, int64_t W, uint32_t* bits,
+                             void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * HashAttention top-k  (maskers/fixed/implementations/hashattention_top_k.py)
+ * ------------------------------------------------------------------------ */
+
+/* Sign-bit signatures of an MLP, packed one uint32 per vector
+ * (_get_signatures :203-238, _apply_single_layer :240-253).
+ *   x       [B][H_in][n][D] with strides (xs_b, xs_h, xs_n), vectors
+ *           n_begin .. n_end-1 are encoded
+ *   codes   uint32 [B][H_out][n_total]; head h_out uses weight set h_out and
+ *           reads input head h_out / (H_out / H_in) (keys are hashed per
+ *           query head, :354-359)
+ *   layers  n_layers <= 4; weights[l] is [H_out][dims[l]][dims[l+1]],
+ *           bias[l] is [H_out][dims[l+1]], both contiguous in `dtype`;
+ *           dims[0] = D, dims[n_layers] = bits <= 32
+ *   act     activation between layers; for SAH_BF16 `act_table` is a device
+ *           table uint16[65536] mapping the bf16 bit pattern of x to the bf16
+ *           bit pattern of act(x) (every bf16 rounding of the reference chain
+ *           is reproduced: product sums are accumulated in fp32 in ascending
+ *           input-channel order and rounded to bf16 after the sum, after the
+ *           bias add and after the activation).
+ * bit e of a code is 1 when output e is > 0 (the reference's sign() == +1). */
+int sah_hash_encode(const void* x, int dtype, int64_t xs_b, int64_t xs_h, int64_t xs_n,
+                    int B, int H_in, int H_out, int64_t n_begin, int64_t n_end,
+                    int64_t n_total, int n_layers, const int* dims,
+                    const void* const* weights, const void* const* bias, int act,
+                    const uint16_t* act_table, uint32_t* codes, void* stream);
+
+/* Top-k over Hamming scores with lowest-index tie-break
+ * (_compute_hashattention_score :343-371 followed by
+ * TopKMasker._get_topk_indices_from_inactive_positions,
+ * maskers/fixed/base.py:74-85).  score(j) = nbits - 2 * popcount(q ^ k_j)
+ * (+ bias[b][.][q][j], added and rounded in `dtype`, when bias != NULL).
+ * Only columns whose prev bit is clear compete; out_bits = prev | winners.
+ * kcodes uint32 [B][Hq][kc_stride] (first S of each row used), qcodes uint32
+ * [B][Hq][Sq].  out_bits may alias prev_bits. */
+int sah_hash_topk(const uint32_t* kcodes, int64_t kc_stride, const uint32_t* qcodes, int nbits,
+                  const void* bias, int dtype, int64_t bias_s_b, int64_t bias_s_h,
+                  int64_t bias_s_q, int B, int Hq, int Sq, int64_t S, int64_t W,
+                  const uint32_t* prev_bits, int64_t k, uint32_t* out_bits, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * Oracle top-k  (maskers/fixed/implementations/oracle_top_k.py:48-125)
+ * ------------------------------------------------------------------------ */
+
+/* scores[row][j] = q_row . k_j in `dtype` (unscaled, :70), plus the additive
+ * bias.  The dot product is accumulated in fp32 in a fixed order (eight
+ * interleaved partial sums over ascending 8-element chunks, then a fixed
+ * pairwise tree) and rounded once to `dtype`; the bias add is rounded again,
+ * as the reference's tensor ops do.  scores is [rows][S] in `dtype`. */
+int sah_qk_scores(const void* q, const void* k, int dtype, int64_t qs_b, int64_t qs_h,
+                  int64_t qs_q, int64_t ks_b, int64_t ks_h, int64_t ks_s, int B, int Hq,
+                  int Hkv, int Sq, int64_t S, int D, const void* bias, int64_t bias_s_b,
+                  int64_t bias_s_h, int64_t bias_s_q, void* scores, void* stream);
+
+/* Generic top-k of a [rows][S] score tensor in `dtype` over the columns whose
+ * prev bit is clear, in the column window [col_begin, col_end), ties to the
+ * lowest column; out_bits = prev | winners (maskers/fixed/base.py:74-85).
+ * out_bits may alias prev_bits. */
+int sah_topk_select(const void* scores, int dtype, int64_t rows, int64_t S, int64_t W,
+                    int64_t col_begin, int64_t col_end, const uint32_t* prev_bits,
+                    int64_t k, uint32_t* out_bits, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * Masked attention  (utils/mask_attention_utils.py:187-240, :406-491)
+ * ------------------------------------------------------------------------ */
+
+/* Work-list sizes for one call of sah_attn_plan / sah_masked_attention.
+ * group = (b, kv head, block of q positions); a group owns
+ * rows_per_group = (Hq/Hkv) * q_block mask rows (<= 16). */
+typedef struct {
+  int32_t groups;          /* B * Hkv * ceil(Sq / q_block)                  */
+  int32_t q_block;         /* query positions per group                     */
+  int32_t rows_per_group;  /* (Hq / Hkv) * q_block                          */
+  int32_t nsplit;          /* CTAs cooperating on one group                 */
+  int64_t ucols_bytes;     /* int32  [groups][S]                            */
+  int64_t umemb_bytes;     /* uint16 [groups][S]                            */
+  int64_t uw_bytes;        /* float  [groups][S][rows_per_group] (if data)  */
+  int64_t ucount_bytes;    /* int32  [groups] + chunk counters              */
+  int64_t partial_bytes;   /* float  [groups][nsplit][rows_per_group][D+2]  */
+} sah_attn_sizes;
+
+int sah_attn_query_sizes(int B, int Hq, int Hkv, int Sq, int64_t S, int D, int has_data,
+                         int sm_count, sah_attn_sizes* out);
+
+/* Union list of one group: the ascending columns selected by any of its
+ * rows (ucols), which rows selected each (umemb, bit i = i-th row of the
+ * group), and -- when data != NULL -- the inverse weights
+ * 1 / (data + 1e-6) evaluated in `dtype` exactly as Mask.apply_inv_mask_dense
+ * does (utils/mask.py:718-740), zero for non-members (uw). */
+int sah_attn_plan(const uint32_t* bits, const void* data, const int32_t* wpre,
+                  const int64_t* ptr, int dtype, int B, int Hq, int Hkv, int Sq, int64_t S,
+                  int64_t W, const sah_attn_sizes* sizes, int32_t* ucols, uint16_t* umemb,
+                  float* uw, int32_t* ucount, void* stream);
+
+/* out[b][q][h][:] = sum_j e_j w_j v_j / (sum_j e_j w_j [+ exp(sink_h)]),
+ * e_j = exp(scaling * q.k_j + bias_j), over the planned union list; fp32
+ * math, online softmax, every KV row fetched once per group and shared by
+ * the group's query heads.  out is [B][Sq][Hq][D] contiguous in `dtype`
+ * (utils/mask_attention_utils.py:479-481).  sinks: optional float [Hq]
+ * (apply_sink_bias :357-402).  lse_out: optional float [rows][2] = (running
+ * max, denominator) of each row, for cross-device merging. */
+int sah_masked_attention(const void* q, const void* k, const void* v, int dtype,
+                         int64_t qs_b, int64_t qs_h, int64_t qs_q, int64_t ks_b,
+                         int64_t ks_h, int64_t ks_s, int64_t vs_b, int64_t vs_h,
+                         int64_t vs_s, int B, int Hq, int Hkv, int Sq, int64_t S, int D,
+                         float scaling, const void* bias, int64_t bias_s_b,
+                         int64_t bias_s_h, int64_t bias_s_q, const float* sinks,
+                         const sah_attn_sizes* sizes, const int32_t* ucols,
+                         const uint16_t* umemb, const float* uw, const int32_t* ucount,
+                         float* partial, void* out, float* acc_out, float* lse_out,
+                         void* stream);
+
+/* Merge n_parts partial results (unnormalised fp32 accumulators acc
+ * [n_parts][rows][D] with lse [n_parts][rows][2]) into out [B][Sq][Hq][D]:
+ * the associative combine of sequence-sharded softmax partials. */
+int sah_attn_merge_parts(const float* acc, const float* lse, int n_parts, int B, int Hq,
+                         int Sq, int D, const float* sinks, int dtype, void* out,
+                         void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SAH_B200_H */

@@ -1,0 +1,717 @@
+// Masked attention over a bitmap Mask (utils/mask_attention_utils.py:406-491):
+//   sah_attn_query_sizes   work-list geometry for one call
+//   sah_attn_plan          per KV group: ascending union of the selected columns,
+//                          which rows selected each, inverse weights
+//   sah_masked_attention   gather of the selected K/V rows through a cp.async
+//                          pipeline, weighted online softmax in fp32, every row
+//                          fetched once per group and shared by its query heads
+//   sah_attn_merge_parts   associative merge of sequence-sharded partials
+#include "sah_common.cuh"
+
+#define AT_THREADS 128
+#define AT_STAGES 3
+#define AT_MAXR 16
+#define PLAN_CHUNK_WORDS 32  // one warp scans 32 bitmap words = 1024 columns
+
+// ---------------------------------------------------------------------------
+// geometry
+// ---------------------------------------------------------------------------
+extern "C" int sah_attn_query_sizes(int B, int Hq, int Hkv, int Sq, int64_t S, int D,
+                                    int has_data, int sm_count, sah_attn_sizes* out) {
+  SAH_REQUIRE(out != nullptr, "attn_query_sizes: out is null");
+  SAH_REQUIRE(B > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Sq > 0 && S > 0 && D > 0,
+              "attn_query_sizes: bad extents");
+  const int G = Hq / Hkv;
+  if (G > AT_MAXR)
+    return sah_fail(SAH_ERR_UNSUPPORTED, "attention: %d query heads per KV head (<= %d)", G,
+                    AT_MAXR);
+  // One register quad (4 mask rows) per group whenever the GQA ratio allows it.
+  int q_block = (G <= 4) ? (4 / G) : 1;
+  if (q_block > Sq) q_block = Sq;
+  const int nqb = (Sq + q_block - 1) / q_block;
+  const int64_t groups = (int64_t)B * Hkv * nqb;
+  SAH_REQUIRE(groups < (1ll << 30), "attn_query_sizes: too many groups");
+  if (sm_count <= 0) sm_count = 148;
+  int64_t target = (int64_t)sm_count * 4;
+  int64_t nsplit = (target + groups - 1) / groups;
+  int64_t max_split = (S + 255) / 256;  // at least 256 columns of range per CTA
+  if (nsplit > max_split) nsplit = max_split;
+  if (nsplit > 256) nsplit = 256;
+  if (nsplit < 1) nsplit = 1;
+  const int R = G * q_block;
+  const int64_t nchunks = (((S + 31) / 32) + PLAN_CHUNK_WORDS - 1) / PLAN_CHUNK_WORDS;
+  out->groups = (int32_t)groups;
+  out->q_block = q_block;
+  out->rows_per_group = R;
+  out->nsplit = (int32_t)nsplit;
+  out->ucols_bytes = groups * S * (int64_t)sizeof(int32_t);
+  out->umemb_bytes = groups * S * (int64_t)sizeof(uint16_t);
+  out->uw_bytes = has_data ? groups * S * R * (int64_t)sizeof(float) : 0;
+  out->ucount_bytes = (groups + groups * nchunks) * (int64_t)sizeof(int32_t);
+  out->partial_bytes = groups * nsplit * R * (int64_t)(D + 2) * (int64_t)sizeof(float);
+  return SAH_OK;
+}
+
+// ---------------------------------------------------------------------------
+// plan
+// ---------------------------------------------------------------------------
+struct PlanGeom {
+  int Hq, Hkv, Sq, G, q_block, nqb, R;
+  int64_t S, W, nchunks, groups;
+};
+
+// mask row of member r of group g, or -1 when the member's query is past Sq
+__device__ __forceinline__ int64_t plan_member_row(const PlanGeom& p, int64_t g, int r) {
+  int qb = (int)(g % p.nqb);
+  int64_t bk = g / p.nqb;
+  int kvh = (int)(bk % p.Hkv);
+  int64_t b = bk / p.Hkv;
+  int gi = r / p.q_block, qo = r - gi * p.q_block;
+  int qi = qb * p.q_block + qo;
+  if (qi >= p.Sq) return -1;
+  int h = kvh * p.G + gi;
+  return (b * p.Hq + h) * p.Sq + qi;
+}
+
+__global__ void attn_plan_count_kernel(const uint32_t* __restrict__ bits, PlanGeom p,
+                                       int32_t* __restrict__ chunkcnt) {
+  const int lane = threadIdx.x & 31;
+  const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t g = wid / p.nchunks, c = wid - g * p.nchunks;
+  if (g >= p.groups) return;  // surplus warps of the last block
+  const int64_t w = c * PLAN_CHUNK_WORDS + lane;
+  uint32_t u = 0u;
+  if (w < p.W) {
+    for (int r = 0; r < p.R; ++r) {
+      int64_t row = plan_member_row(p, g, r);
+      if (row >= 0) u |= bits[row * p.W + w];
+    }
+  }
+  int cnt = __popc(u);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+  if (lane == 0) chunkcnt[g * p.nchunks + c] = cnt;
+}
+
+template <typename T>
+__global__ void attn_plan_emit_kernel(const uint32_t* __restrict__ bits, const T* __restrict__ data,
+                                      const int32_t* __restrict__ wpre,
+                                      const int64_t* __restrict__ ptr, PlanGeom p,
+                                      const int32_t* __restrict__ chunkcnt,
+                                      int32_t* __restrict__ ucols, uint16_t* __restrict__ umemb,
+                                      float* __restrict__ uw, int32_t* __restrict__ ucount) {
+  const int lane = threadIdx.x & 31;
+  const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t g = wid / p.nchunks, c = wid - g * p.nchunks;
+  if (g >= p.groups) return;  // surplus warps of the last block
+  // columns selected in earlier chunks of this group
+  int base = 0;
+  for (int64_t cc = lane; cc < c; cc += 32) base += chunkcnt[g * p.nchunks + cc];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) base += __shfl_xor_sync(0xffffffffu, base, o);
+
+  const int64_t w = c * PLAN_CHUNK_WORDS + lane;
+  uint32_t words[AT_MAXR];
+  int64_t rows[AT_MAXR];
+  uint32_t u = 0u;
+#pragma unroll
+  for (int r = 0; r < AT_MAXR; ++r) {
+    words[r] = 0u;
+    rows[r] = -1;
+    if (r < p.R && w < p.W) {
+      rows[r] = plan_member_row(p, g, r);
+      if (rows[r] >= 0) words[r] = bits[rows[r] * p.W + w];
+    }
+    u |= words[r];
+  }
+  const int cnt = __popc(u);
+  int incl = cnt;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int n = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += n;
+  }
+  int64_t pos = (int64_t)g * p.S + base + incl - cnt;
+  uint32_t m = u;
+  while (m) {
+    const int b = __ffs(m) - 1;
+    m &= m - 1;
+    unsigned int memb = 0u;
+#pragma unroll
+    for (int r = 0; r < AT_MAXR; ++r) memb |= ((words[r] >> b) & 1u) << r;
+    ucols[pos] = (int32_t)(w * 32 + b);
+    umemb[pos] = (uint16_t)memb;
+    if (uw != nullptr) {
+#pragma unroll
+      for (int r = 0; r < AT_MAXR; ++r) {
+        if (r < p.R) {
+          float wv = 0.f;
+          if ((memb >> r) & 1u) {
+            int64_t dp = ptr[rows[r]] + wpre[rows[r] * p.W + w] +
+                         __popc(words[r] & ((1u << b) - 1u));
+            wv = sah_inv_weight<T>(sah_to_float<T>(data[dp]));
+          }
+          uw[pos * p.R + r] = wv;
+        }
+      }
+    }
+    ++pos;
+  }
+  if (c == p.nchunks - 1) {
+    int total = __shfl_sync(0xffffffffu, incl, 31);
+    if (lane == 0) ucount[g] = base + total;
+  }
+}
+
+extern "C" int sah_attn_plan(const uint32_t* bits, const void* data, const int32_t* wpre,
+                             const int64_t* ptr, int dtype, int B, int Hq, int Hkv, int Sq,
+                             int64_t S, int64_t W, const sah_attn_sizes* sizes, int32_t* ucols,
+                             uint16_t* umemb, float* uw, int32_t* ucount, void* stream) {
+  SAH_REQUIRE(bits && sizes && ucols && umemb && ucount, "attn_plan: null pointer");
+  SAH_REQUIRE(data == nullptr || (wpre && ptr && uw), "attn_plan: data needs wpre, ptr and uw");
+  SAH_REQUIRE(W * 32 >= S, "attn_plan: W too small");
+  PlanGeom p;
+  p.Hq = Hq; p.Hkv = Hkv; p.Sq = Sq; p.G = Hq / Hkv;
+  p.q_block = sizes->q_block;
+  p.nqb = (Sq + p.q_block - 1) / p.q_block;
+  p.R = sizes->rows_per_group;
+  p.S = S; p.W = W;
+  p.nchunks = (W + PLAN_CHUNK_WORDS - 1) / PLAN_CHUNK_WORDS;
+  const int64_t groups = sizes->groups;
+  p.groups = groups;
+  SAH_REQUIRE(groups == (int64_t)B * Hkv * p.nqb && p.R == p.G * p.q_block && p.R <= AT_MAXR,
+              "attn_plan: sizes do not match the extents");
+  int32_t* chunkcnt = ucount + groups;
+  const int64_t warps = groups * p.nchunks;
+  const int threads = 256;
+  const int64_t blocks = sah_ceil_div(warps * 32, threads);
+  cudaStream_t st = (cudaStream_t)stream;
+  attn_plan_count_kernel<<<(unsigned)blocks, threads, 0, st>>>(bits, p, chunkcnt);
+  SAH_LAUNCH_CHECK("attn_plan_count");
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    attn_plan_emit_kernel<T><<<(unsigned)blocks, threads, 0, st>>>(
+        bits, (const T*)data, wpre, ptr, p, chunkcnt, ucols, umemb, data ? uw : nullptr, ucount);
+  });
+  SAH_LAUNCH_CHECK("attn_plan_emit");
+  return SAH_OK;
+}
+
+// ---------------------------------------------------------------------------
+// attention
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void at_cp_async16(void* smem_dst, const void* gmem_src) {
+  unsigned int d = (unsigned int)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gmem_src));
+}
+__device__ __forceinline__ void at_cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void at_cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+struct AttnArgs {
+  const void *q, *k, *v;
+  int64_t qs_b, qs_h, qs_q, ks_b, ks_h, ks_s, vs_b, vs_h, vs_s;
+  int Hq, Hkv, Sq, G, q_block, nqb, R, nsplit;
+  int64_t S;
+  float scaling;
+  const void* bias;
+  int64_t bias_s_b, bias_s_h, bias_s_q;
+  const int32_t* ucols;
+  const uint16_t* umemb;
+  const float* uw;
+  const int32_t* ucount;
+  float* partial;
+};
+
+// Shared-memory rows are stored in 16-byte chunks; chunk c of tile row i sits
+// at chunk slot (c ^ (i & 7)), which spreads the rows of a quarter warp over
+// all banks for both the row-wise (QK) and the column-wise (PV) reads.
+template <typename T, int D>
+struct AttnCfg {
+  static constexpr int ROWB = D * (int)sizeof(T);        // bytes per K or V row
+  static constexpr int CPR = ROWB / 16;                  // 16-byte chunks per row
+  static constexpr int EPC = 16 / (int)sizeof(T);        // elements per chunk
+  static constexpr int TILE = (sizeof(T) == 2) ? 64 : 32;  // keys per pipeline stage
+  static constexpr int PARTS = AT_THREADS / TILE;        // threads sharing one key in QK
+  static constexpr int CPP = CPR / PARTS;                // chunks per part
+  static constexpr int KPL = TILE / 32;                  // keys per lane in the softmax phase
+  static constexpr int DPL = D / 32;                     // output dims per lane in PV
+  static constexpr int STAGE_BYTES = 2 * TILE * ROWB;    // K tile + V tile
+};
+
+template <typename T, int D, int NQUAD>
+__global__ void __launch_bounds__(AT_THREADS)
+masked_attention_kernel(AttnArgs a) {
+  using C = AttnCfg<T, D>;
+  constexpr int RP = NQUAD * 4;  // padded row count
+  extern __shared__ __align__(128) unsigned char at_smem[];
+  unsigned char* stage_base = at_smem;
+  float* q_sm = reinterpret_cast<float*>(at_smem + AT_STAGES * C::STAGE_BYTES);  // [RP][D]
+  float* s_part = q_sm + RP * D;                       // [PARTS][TILE][RP]
+  float* p_sm = s_part + C::PARTS * C::TILE * RP;      // [TILE][RP]
+  float* m_sm = p_sm + C::TILE * RP;                   // [RP]
+  float* l_sm = m_sm + RP;                             // [RP]
+  float* alpha_sm = l_sm + RP;                         // [RP]
+  int* cols_sm = reinterpret_cast<int*>(alpha_sm + RP);  // [STAGES][TILE]
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int split = blockIdx.x;
+  const int64_t g = blockIdx.y;
+  const int qb = (int)(g % a.nqb);
+  const int64_t bk = g / a.nqb;
+  const int kvh = (int)(bk % a.Hkv);
+  const int64_t b = bk / a.Hkv;
+
+  const T* kbase = reinterpret_cast<const T*>(a.k) + b * a.ks_b + kvh * a.ks_h;
+  const T* vbase = reinterpret_cast<const T*>(a.v) + b * a.vs_b + kvh * a.vs_h;
+  const int32_t* gcols = a.ucols + g * a.S;
+  const uint16_t* gmemb = a.umemb + g * a.S;
+  const float* guw = a.uw ? a.uw + g * a.S * a.R : nullptr;
+
+  // this CTA's slice of the group's union list
+  const int U = a.ucount[g];
+  int per = (U + a.nsplit - 1) / a.nsplit;
+  per = ((per + C::TILE - 1) / C::TILE) * C::TILE;
+  int start = split * per;
+  if (start > U) start = U;
+  int end = start + per;
+  if (end > U) end = U;
+  const int ntiles = (end - start + C::TILE - 1) / C::TILE;
+
+  // stage queries (fp32), reset softmax state
+  for (int idx = tid; idx < RP * D; idx += AT_THREADS) {
+    int r = idx / D, d = idx - r * D;
+    float val = 0.f;
+    if (r < a.R) {
+      int gi = r / a.q_block, qo = r - gi * a.q_block;
+      int qi = qb * a.q_block + qo;
+      if (qi < a.Sq) {
+        int h = kvh * a.G + gi;
+        val = sah_to_float<T>(
+            reinterpret_cast<const T*>(a.q)[b * a.qs_b + (int64_t)h * a.qs_h + qi * a.qs_q + d]);
+      }
+    }
+    q_sm[idx] = val;
+  }
+  if (tid < RP) {
+    m_sm[tid] = -INFINITY;
+    l_sm[tid] = 0.f;
+    alpha_sm[tid] = 1.f;
+  }
+
+  float acc[NQUAD][4][C::DPL];
+#pragma unroll
+  for (int qd = 0; qd < NQUAD; ++qd)
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int e = 0; e < C::DPL; ++e) acc[qd][r][e] = 0.f;
+
+  auto issue = [&](int t) {
+    const int st = t % AT_STAGES;
+    unsigned char* kst = stage_base + st * C::STAGE_BYTES;
+    unsigned char* vst = kst + C::TILE * C::ROWB;
+    const int t0 = start + t * C::TILE;
+    for (int idx = tid; idx < C::TILE * C::CPR; idx += AT_THREADS) {
+      const int i = idx / C::CPR, c = idx - i * C::CPR;
+      const int u = t0 + i;
+      if (u < end) {
+        const int64_t col = gcols[u];
+        const int slot = (c ^ (i & 7)) * 16;
+        at_cp_async16(kst + i * C::ROWB + slot,
+                      reinterpret_cast<const unsigned char*>(kbase + col * a.ks_s) + c * 16);
+        at_cp_async16(vst + i * C::ROWB + slot,
+                      reinterpret_cast<const unsigned char*>(vbase + col * a.vs_s) + c * 16);
+      }
+    }
+    if (tid < C::TILE) cols_sm[st * C::TILE + tid] = (t0 + tid < end) ? gcols[t0 + tid] : -1;
+  };
+
+#pragma unroll
+  for (int s = 0; s < AT_STAGES - 1; ++s) {
+    if (s < ntiles) issue(s);
+    at_cp_async_commit();
+  }
+
+  for (int t = 0; t < ntiles; ++t) {
+    if (t + AT_STAGES - 1 < ntiles) issue(t + AT_STAGES - 1);
+    at_cp_async_commit();
+    at_cp_async_wait<AT_STAGES - 1>();
+    __syncthreads();
+
+    const int st = t % AT_STAGES;
+    const unsigned char* kst = stage_base + st * C::STAGE_BYTES;
+    const unsigned char* vst = kst + C::TILE * C::ROWB;
+    const int t0 = start + t * C::TILE;
+    const int nvalid = (end - t0 < C::TILE) ? (end - t0) : C::TILE;
+
+    // ---- phase A: partial dot products, thread = (key, part of D) ----
+    {
+      const int i = tid % C::TILE, part = tid / C::TILE;
+      float sp[RP];
+#pragma unroll
+      for (int r = 0; r < RP; ++r) sp[r] = 0.f;
+      if (i < nvalid) {
+#pragma unroll
+        for (int cc = 0; cc < C::CPP; ++cc) {
+          const int c = part * C::CPP + cc;
+          float kf[C::EPC];
+          const unsigned char* src = kst + i * C::ROWB + ((c ^ (i & 7)) * 16);
+          if (sizeof(T) == 2) {
+            uint4 raw = *reinterpret_cast<const uint4*>(src);
+            float tmp[8];
+            sah_unpack8(raw, tmp);
+#pragma unroll
+            for (int e = 0; e < C::EPC; ++e) kf[e] = tmp[e];
+          } else {
+            float4 raw = *reinterpret_cast<const float4*>(src);
+            kf[0] = raw.x; kf[1] = raw.y; kf[2] = raw.z; kf[3] = raw.w;
+          }
+#pragma unroll
+          for (int r = 0; r < RP; ++r) {
+            const float* qp = q_sm + r * D + c * C::EPC;
+#pragma unroll
+            for (int e = 0; e < C::EPC; e += 4) {
+              const float4 qv = *reinterpret_cast<const float4*>(qp + e);
+              sp[r] = fmaf(qv.x, kf[e + 0], sp[r]);
+              sp[r] = fmaf(qv.y, kf[e + 1], sp[r]);
+              sp[r] = fmaf(qv.z, kf[e + 2], sp[r]);
+              sp[r] = fmaf(qv.w, kf[e + 3], sp[r]);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < RP; ++r) s_part[(part * C::TILE + i) * RP + r] = sp[r];
+    }
+    __syncthreads();
+
+    // ---- phase B: logits, running max, weights; warp w owns rows w, w+4, ... ----
+    for (int r = warp; r < RP; r += AT_THREADS / 32) {
+      float sv[C::KPL], wv[C::KPL];
+      float tmax = -INFINITY;
+      const bool row_ok = r < a.R;
+      int h = 0, qi = 0;
+      if (row_ok) {
+        int gi = r / a.q_block, qo = r - gi * a.q_block;
+        qi = qb * a.q_block + qo;
+        h = kvh * a.G + gi;
+      }
+#pragma unroll
+      for (int kk = 0; kk < C::KPL; ++kk) {
+        const int i = lane + kk * 32;
+        sv[kk] = -INFINITY;
+        wv[kk] = 0.f;
+        if (row_ok && i < nvalid) {
+          const int u = t0 + i;
+          const unsigned int memb = gmemb[u];
+          if ((memb >> r) & 1u) {
+            float s = 0.f;
+#pragma unroll
+            for (int pp = 0; pp < C::PARTS; ++pp) s += s_part[(pp * C::TILE + i) * RP + r];
+            s *= a.scaling;
+            if (a.bias != nullptr) {
+              const int64_t col = cols_sm[st * C::TILE + i];
+              s += sah_to_float<T>(reinterpret_cast<const T*>(
+                  a.bias)[b * a.bias_s_b + h * a.bias_s_h + qi * a.bias_s_q + col]);
+            }
+            sv[kk] = s;
+            wv[kk] = guw ? guw[(int64_t)u * a.R + r] : 1.f;
+            tmax = fmaxf(tmax, s);
+          }
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+      const float m_old = m_sm[r];
+      const float m_new = fmaxf(m_old, tmax);
+      float psum = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < C::KPL; ++kk) {
+        const int i = lane + kk * 32;
+        float pv = 0.f;
+        if (sv[kk] != -INFINITY) pv = expf(sv[kk] - m_new) * wv[kk];
+        p_sm[i * RP + r] = pv;
+        psum += pv;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
+      if (lane == 0) {
+        const float alpha = (m_new == -INFINITY) ? 1.f : expf(m_old - m_new);
+        alpha_sm[r] = alpha;
+        l_sm[r] = l_sm[r] * alpha + psum;
+        m_sm[r] = m_new;
+      }
+    }
+    __syncthreads();
+
+    // ---- phase C: acc = acc * alpha + p . V; thread = (dims of lane, keys of warp) ----
+    {
+#pragma unroll
+      for (int qd = 0; qd < NQUAD; ++qd)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const float al = alpha_sm[qd * 4 + r];
+#pragma unroll
+          for (int e = 0; e < C::DPL; ++e) acc[qd][r][e] *= al;
+        }
+      const int d0 = lane * C::DPL;                 // first output dim of this lane
+      const int c = (d0 * (int)sizeof(T)) / 16;     // chunk holding it
+      const int off = (d0 * (int)sizeof(T)) % 16;   // byte offset inside the chunk
+      for (int i = warp; i < nvalid; i += AT_THREADS / 32) {
+        const unsigned char* src = vst + i * C::ROWB + ((c ^ (i & 7)) * 16) + off;
+        float vf[C::DPL];
+        if (sizeof(T) == 2) {
+          if (C::DPL == 4) {
+            uint2 raw = *reinterpret_cast<const uint2*>(src);
+            vf[0] = __uint_as_float(raw.x << 16);
+            vf[1] = __uint_as_float(raw.x & 0xffff0000u);
+            vf[2] = __uint_as_float(raw.y << 16);
+            vf[3] = __uint_as_float(raw.y & 0xffff0000u);
+          } else {
+            unsigned int raw = *reinterpret_cast<const unsigned int*>(src);
+            vf[0] = __uint_as_float(raw << 16);
+            vf[1] = __uint_as_float(raw & 0xffff0000u);
+          }
+        } else {
+          if (C::DPL == 4) {
+            float4 raw = *reinterpret_cast<const float4*>(src);
+            vf[0] = raw.x; vf[1] = raw.y; vf[2] = raw.z; vf[3] = raw.w;
+          } else {
+            float2 raw = *reinterpret_cast<const float2*>(src);
+            vf[0] = raw.x; vf[1] = raw.y;
+          }
+        }
+#pragma unroll
+        for (int qd = 0; qd < NQUAD; ++qd) {
+          const float4 pv = *reinterpret_cast<const float4*>(p_sm + i * RP + qd * 4);
+#pragma unroll
+          for (int e = 0; e < C::DPL; ++e) {
+            acc[qd][0][e] = fmaf(pv.x, vf[e], acc[qd][0][e]);
+            acc[qd][1][e] = fmaf(pv.y, vf[e], acc[qd][1][e]);
+            acc[qd][2][e] = fmaf(pv.z, vf[e], acc[qd][2][e]);
+            acc[qd][3][e] = fmaf(pv.w, vf[e], acc[qd][3][e]);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  at_cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- combine the four warps' accumulators and write the partial ----
+  float* red = reinterpret_cast<float*>(stage_base);  // [4][RP][D]
+#pragma unroll
+  for (int qd = 0; qd < NQUAD; ++qd)
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int e = 0; e < C::DPL; ++e)
+        red[(warp * RP + qd * 4 + r) * D + lane * C::DPL + e] = acc[qd][r][e];
+  __syncthreads();
+  float* pout = a.partial + ((int64_t)g * a.nsplit + split) * a.R * (D + 2);
+  for (int idx = tid; idx < a.R * D; idx += AT_THREADS) {
+    const int r = idx / D, d = idx - r * D;
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < AT_THREADS / 32; ++w) s += red[(w * RP + r) * D + d];
+    pout[r * (D + 2) + d] = s;
+  }
+  if (tid < a.R) {
+    pout[tid * (D + 2) + D] = m_sm[tid];
+    pout[tid * (D + 2) + D + 1] = l_sm[tid];
+  }
+}
+
+// Merge the nsplit partials of every row; one CTA of D threads per (group, row).
+template <typename T>
+__global__ void attn_merge_splits_kernel(const float* __restrict__ partial, int nsplit, int R,
+                                         int D, int Hq, int Hkv, int Sq, int G, int q_block,
+                                         int nqb, const float* __restrict__ sinks,
+                                         T* __restrict__ out, float* __restrict__ acc_out,
+                                         float* __restrict__ lse_out) {
+  const int64_t g = blockIdx.x / R;
+  const int r = (int)(blockIdx.x % R);
+  const int qb = (int)(g % nqb);
+  const int64_t bk = g / nqb;
+  const int kvh = (int)(bk % Hkv);
+  const int64_t b = bk / Hkv;
+  const int gi = r / q_block, qo = r - gi * q_block;
+  const int qi = qb * q_block + qo;
+  if (qi >= Sq) return;
+  const int h = kvh * G + gi;
+  const float* p0 = partial + ((int64_t)g * nsplit) * R * (D + 2) + (int64_t)r * (D + 2);
+  const int64_t pstride = (int64_t)R * (D + 2);
+  float M = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, p0[s * pstride + D]);
+  float L = 0.f;
+  for (int s = 0; s < nsplit; ++s) {
+    float ms = p0[s * pstride + D];
+    if (ms != -INFINITY) L += p0[s * pstride + D + 1] * expf(ms - M);
+  }
+  const int64_t row = (b * Hq + h) * Sq + qi;
+  float Mx = M, sink_term = 0.f;
+  if (sinks != nullptr) {
+    const float sk = sinks[h];
+    Mx = fmaxf(M, sk);
+    sink_term = expf(sk - Mx);
+  }
+  const float resc = (M == -INFINITY) ? 0.f : expf(M - Mx);
+  const float den = L * resc + sink_term;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float accv = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      float ms = p0[s * pstride + D];
+      if (ms != -INFINITY) accv += p0[s * pstride + d] * expf(ms - M);
+    }
+    if (acc_out != nullptr) acc_out[row * D + d] = accv;
+    out[((b * Sq + qi) * Hq + h) * D + d] = sah_from_float<T>(accv * resc / den);
+  }
+  if (lse_out != nullptr && threadIdx.x == 0) {
+    lse_out[row * 2 + 0] = M;
+    lse_out[row * 2 + 1] = L;
+  }
+}
+
+template <typename T, int D>
+static int launch_attention(const AttnArgs& a, int groups, cudaStream_t st) {
+  using C = AttnCfg<T, D>;
+  const int nquad = (a.R + 3) / 4;
+  const int RP = nquad * 4;
+  size_t smem = (size_t)AT_STAGES * C::STAGE_BYTES +
+                sizeof(float) * ((size_t)RP * D + (size_t)C::PARTS * C::TILE * RP +
+                                 (size_t)C::TILE * RP + 3 * RP) +
+                sizeof(int) * AT_STAGES * C::TILE;
+  size_t red = sizeof(float) * 4 * RP * D;
+  if (red > (size_t)AT_STAGES * C::STAGE_BYTES)
+    return sah_fail(SAH_ERR_UNSUPPORTED, "attention: reduction buffer does not fit");
+  dim3 grid((unsigned)a.nsplit, (unsigned)groups);
+#define SAH_AT_LAUNCH(NQ)                                                                        \
+  {                                                                                              \
+    cudaError_t e = cudaFuncSetAttribute(masked_attention_kernel<T, D, NQ>,                      \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "attention attr: %s", cudaGetErrorString(e)); \
+    masked_attention_kernel<T, D, NQ><<<grid, AT_THREADS, smem, st>>>(a);                         \
+  }
+  switch (nquad) {
+    case 1: SAH_AT_LAUNCH(1) break;
+    case 2: SAH_AT_LAUNCH(2) break;
+    case 3: SAH_AT_LAUNCH(3) break;
+    default: SAH_AT_LAUNCH(4) break;
+  }
+#undef SAH_AT_LAUNCH
+  return SAH_OK;
+}
+
+extern "C" int sah_masked_attention(const void* q, const void* k, const void* v, int dtype,
+                                    int64_t qs_b, int64_t qs_h, int64_t qs_q, int64_t ks_b,
+                                    int64_t ks_h, int64_t ks_s, int64_t vs_b, int64_t vs_h,
+                                    int64_t vs_s, int B, int Hq, int Hkv, int Sq, int64_t S, int D,
+                                    float scaling, const void* bias, int64_t bias_s_b,
+                                    int64_t bias_s_h, int64_t bias_s_q, const float* sinks,
+                                    const sah_attn_sizes* sizes, const int32_t* ucols,
+                                    const uint16_t* umemb, const float* uw, const int32_t* ucount,
+                                    float* partial, void* out, float* acc_out, float* lse_out,
+                                    void* stream) {
+  SAH_REQUIRE(q && k && v && sizes && ucols && umemb && ucount && partial && out,
+              "masked_attention: null pointer");
+  SAH_REQUIRE(B > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Sq > 0 && S > 0,
+              "masked_attention: bad extents");
+  if (D != 64 && D != 128)
+    return sah_fail(SAH_ERR_UNSUPPORTED, "masked_attention: head dim %d (64 or 128 supported)", D);
+  const int64_t esz = (dtype == SAH_BF16) ? 2 : 4;
+  SAH_REQUIRE((ks_s * esz) % 16 == 0 && (ks_h * esz) % 16 == 0 && (ks_b * esz) % 16 == 0 &&
+                  (vs_s * esz) % 16 == 0 && (vs_h * esz) % 16 == 0 && (vs_b * esz) % 16 == 0 &&
+                  (uintptr_t)k % 16 == 0 && (uintptr_t)v % 16 == 0,
+              "masked_attention: K and V rows must be 16-byte aligned");
+  AttnArgs a;
+  a.q = q; a.k = k; a.v = v;
+  a.qs_b = qs_b; a.qs_h = qs_h; a.qs_q = qs_q;
+  a.ks_b = ks_b; a.ks_h = ks_h; a.ks_s = ks_s;
+  a.vs_b = vs_b; a.vs_h = vs_h; a.vs_s = vs_s;
+  a.Hq = Hq; a.Hkv = Hkv; a.Sq = Sq; a.G = Hq / Hkv;
+  a.q_block = sizes->q_block;
+  a.nqb = (Sq + a.q_block - 1) / a.q_block;
+  a.R = sizes->rows_per_group;
+  a.nsplit = sizes->nsplit;
+  a.S = S; a.scaling = scaling;
+  a.bias = bias; a.bias_s_b = bias_s_b; a.bias_s_h = bias_s_h; a.bias_s_q = bias_s_q;
+  a.ucols = ucols; a.umemb = umemb; a.uw = uw; a.ucount = ucount; a.partial = partial;
+  const int groups = sizes->groups;
+  SAH_REQUIRE((int64_t)groups == (int64_t)B * Hkv * a.nqb && a.R == a.G * a.q_block &&
+                  a.R <= AT_MAXR && a.nsplit >= 1,
+              "masked_attention: sizes do not match the extents");
+  cudaStream_t st = (cudaStream_t)stream;
+  int rc = SAH_OK;
+  if (dtype == SAH_BF16) {
+    rc = (D == 128) ? launch_attention<__nv_bfloat16, 128>(a, groups, st)
+                    : launch_attention<__nv_bfloat16, 64>(a, groups, st);
+  } else if (dtype == SAH_F32) {
+    rc = (D == 128) ? launch_attention<float, 128>(a, groups, st)
+                    : launch_attention<float, 64>(a, groups, st);
+  } else {
+    return sah_fail(SAH_ERR_INVALID, "masked_attention: unknown dtype %d", dtype);
+  }
+  if (rc != SAH_OK) return rc;
+  SAH_LAUNCH_CHECK("masked_attention");
+  const int mthreads = D;
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    attn_merge_splits_kernel<T><<<(unsigned)(groups * a.R), mthreads, 0, st>>>(
+        partial, a.nsplit, a.R, D, Hq, Hkv, Sq, a.G, a.q_block, a.nqb, sinks, (T*)out, acc_out,
+        lse_out);
+  });
+  SAH_LAUNCH_CHECK("attn_merge_splits");
+  return SAH_OK;
+}
+
+// Merge partial results computed on different sequence shards.
+template <typename T>
+__global__ void attn_merge_parts_kernel(const float* __restrict__ acc, const float* __restrict__ lse,
+                                        int n_parts, int64_t rows, int Hq, int Sq, int D,
+                                        const float* __restrict__ sinks, T* __restrict__ out) {
+  const int64_t row = blockIdx.x;
+  const int qi = (int)(row % Sq);
+  const int64_t bh = row / Sq;
+  const int h = (int)(bh % Hq);
+  const int64_t b = bh / Hq;
+  float M = -INFINITY;
+  for (int p = 0; p < n_parts; ++p) M = fmaxf(M, lse[((int64_t)p * rows + row) * 2]);
+  float L = 0.f;
+  for (int p = 0; p < n_parts; ++p) {
+    float mp = lse[((int64_t)p * rows + row) * 2];
+    if (mp != -INFINITY) L += lse[((int64_t)p * rows + row) * 2 + 1] * expf(mp - M);
+  }
+  float Mx = M, sink_term = 0.f;
+  if (sinks != nullptr) {
+    const float sk = sinks[h];
+    Mx = fmaxf(M, sk);
+    sink_term = expf(sk - Mx);
+  }
+  const float resc = (M == -INFINITY) ? 0.f : expf(M - Mx);
+  const float den = L * resc + sink_term;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float a = 0.f;
+    for (int p = 0; p < n_parts; ++p) {
+      float mp = lse[((int64_t)p * rows + row) * 2];
+      if (mp != -INFINITY) a += acc[((int64_t)p * rows + row) * D + d] * expf(mp - M);
+    }
+    out[((b * Sq + qi) * Hq + h) * D + d] = sah_from_float<T>(a * resc / den);
+  }
+}
+
+extern "C" int sah_attn_merge_parts(const float* acc, const float* lse, int n_parts, int B,
+                                    int Hq, int Sq, int D, const float* sinks, int dtype,
+                                    void* out, void* stream) {
+  SAH_REQUIRE(acc && lse && out, "attn_merge_parts: null pointer");
+  SAH_REQUIRE(n_parts > 0 && B > 0 && Hq > 0 && Sq > 0 && D > 0, "attn_merge_parts: bad extents");
+  const int64_t rows = (int64_t)B * Hq * Sq;
+  int threads = D < 32 ? 32 : (D > 256 ? 256 : D);
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    attn_merge_parts_kernel<T><<<(unsigned)rows, threads, 0, (cudaStream_t)stream>>>(
+        acc, lse, n_parts, rows, Hq, Sq, D, sinks, (T*)out);
+  });
+  SAH_LAUNCH_CHECK("attn_merge_parts");
+  return SAH_OK;
+}

@@ -1,0 +1,142 @@
+// Shared helpers of the sm_100a kernels: status plumbing, dtype access,
+// bf16 rounding and order-preserving float keys.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "sah_b200.h"
+
+int sah_fail(int status, const char* fmt, ...);
+
+#define SAH_REQUIRE(cond, ...)                                  \
+  do {                                                          \
+    if (!(cond)) return sah_fail(SAH_ERR_INVALID, __VA_ARGS__); \
+  } while (0)
+
+#define SAH_LAUNCH_CHECK(name)                                                     \
+  do {                                                                             \
+    cudaError_t e__ = cudaGetLastError();                                          \
+    if (e__ != cudaSuccess)                                                        \
+      return sah_fail(SAH_ERR_CUDA, "%s: %s", name, cudaGetErrorString(e__));      \
+  } while (0)
+
+static inline int64_t sah_ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// ---- element access -------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ float sah_to_float(T v);
+template <>
+__device__ __forceinline__ float sah_to_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float sah_to_float<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+
+template <typename T>
+__device__ __forceinline__ T sah_from_float(float v);
+template <>
+__device__ __forceinline__ float sah_from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 sah_from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+// Round a float to the value grid of T (identity for float).
+template <typename T>
+__device__ __forceinline__ float sah_round_to(float v) {
+  return sah_to_float<T>(sah_from_float<T>(v));
+}
+
+__device__ __forceinline__ float sah_bf16_bits_to_float(uint32_t b16) {
+  return __uint_as_float(b16 << 16);
+}
+__device__ __forceinline__ uint32_t sah_float_to_bf16_bits(float v) {
+  return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+
+// Order-preserving map float -> uint32 (larger float => larger key).
+__device__ __forceinline__ uint32_t sah_float_key(float f) {
+  uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// Inverse mask weight 1 / (m + 1e-6), each op rounded to the mask dtype.
+template <typename T>
+__device__ __forceinline__ float sah_inv_weight(float m) {
+  float s = sah_round_to<T>(__fadd_rn(m, 1e-6f));
+  return sah_round_to<T>(__fdiv_rn(1.0f, s));
+}
+
+// Unpack 8 consecutive elements (16 B for bf16, 32 B for fp32) to floats.
+__device__ __forceinline__ void sah_unpack8(const uint4& v, float* f) {
+  f[0] = __uint_as_float(v.x << 16);
+  f[1] = __uint_as_float(v.x & 0xffff0000u);
+  f[2] = __uint_as_float(v.y << 16);
+  f[3] = __uint_as_float(v.y & 0xffff0000u);
+  f[4] = __uint_as_float(v.z << 16);
+  f[5] = __uint_as_float(v.z & 0xffff0000u);
+  f[6] = __uint_as_float(v.w << 16);
+  f[7] = __uint_as_float(v.w & 0xffff0000u);
+}
+
+template <typename T>
+__device__ __forceinline__ void sah_load8(const T* p, float* f);
+template <>
+__device__ __forceinline__ void sah_load8<__nv_bfloat16>(const __nv_bfloat16* p, float* f) {
+  uint4 v = *reinterpret_cast<const uint4*>(p);
+  sah_unpack8(v, f);
+}
+template <>
+__device__ __forceinline__ void sah_load8<float>(const float* p, float* f) {
+  float4 a = *reinterpret_cast<const float4*>(p);
+  float4 b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+  f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
+// Exclusive scan across the CTA; `total` receives the CTA-wide sum.  `scratch`
+// holds 33 values.  Ends with a barrier, so scratch may be reused right away.
+template <typename V>
+__device__ __forceinline__ V sah_block_excl_scan(V c, V* scratch, V* total) {
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  V incl = c;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    V n = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += n;
+  }
+  if (lane == 31) scratch[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    V s = (lane < nwarp) ? scratch[lane] : (V)0;
+    V si = s;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      V n = __shfl_up_sync(0xffffffffu, si, o);
+      if (lane >= o) si += n;
+    }
+    scratch[lane] = si - s;           // exclusive offset of each warp
+    if (lane == 31) scratch[32] = si; // CTA total
+  }
+  __syncthreads();
+  V res = scratch[warp] + incl - c;
+  *total = scratch[32];
+  __syncthreads();
+  return res;
+}
+
+#define SAH_DISPATCH_DTYPE(dtype, T, ...)                              \
+  do {                                                                 \
+    if ((dtype) == SAH_F32) {                                          \
+      using T = float;                                                 \
+      __VA_ARGS__                                                      \
+    } else if ((dtype) == SAH_BF16) {                                  \
+      using T = __nv_bfloat16;                                         \
+      __VA_ARGS__                                                      \
+    } else {                                                           \
+      return sah_fail(SAH_ERR_INVALID, "unknown dtype %d", (int)(dtype)); \
+    }                                                                  \
+  } while (0)

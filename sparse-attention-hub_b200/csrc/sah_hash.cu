@@ -1,0 +1,298 @@
+// HashAttention kernels (maskers/fixed/implementations/hashattention_top_k.py):
+//   sah_hash_encode  per-head MLP -> sign bits -> one uint32 per vector
+//   sah_hash_topk    Hamming-score top-k with lowest-column tie-break
+#include "sah_common.cuh"
+#include "sah_select.cuh"
+
+// ---------------------------------------------------------------------------
+// Encode.  One CTA hashes a tile of TK vectors of one (batch, output head).
+// Activations live in shared memory as fp32 [channel][vector]; one layer is a
+// register-tiled product where each thread owns KT vectors x 4 outputs and
+// walks the input channels in ascending order with a single fp32 accumulator
+// per output, which fixes the summation order the CPU restatement follows.
+// ---------------------------------------------------------------------------
+#define HE_TK 64        // vectors per CTA
+#define HE_THREADS 256
+#define HE_MAXD 128     // widest layer
+
+struct HashEncodeArgs {
+  const void* x;
+  int64_t xs_b, xs_h, xs_n;
+  int H_in, H_out;
+  int64_t n_begin, n_end, n_total;
+  int n_layers;
+  int dims[5];
+  const void* weights[4];
+  const void* bias[4];
+  int act;
+  const uint16_t* act_table;
+  uint32_t* codes;
+};
+
+template <typename T>
+__device__ __forceinline__ float he_activate(float v, int act, const uint16_t* table);
+
+template <>
+__device__ __forceinline__ float he_activate<__nv_bfloat16>(float v, int act,
+                                                            const uint16_t* table) {
+  // v is a bf16 value; the table maps bf16 bit patterns to bf16 bit patterns.
+  uint32_t b = __float_as_uint(v) >> 16;
+  return __uint_as_float(((uint32_t)table[b]) << 16);
+}
+
+template <>
+__device__ __forceinline__ float he_activate<float>(float v, int act, const uint16_t*) {
+  switch (act) {
+    case SAH_ACT_RELU: return fmaxf(v, 0.f);
+    case SAH_ACT_SILU: return v / (1.f + expf(-v));
+    case SAH_ACT_GELU: return 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));
+    default: return tanhf(v);
+  }
+}
+
+template <typename T, int KT>
+__device__ __forceinline__ void he_layer(const float* __restrict__ a_in, float* __restrict__ a_out,
+                                         const float* __restrict__ w_sm,
+                                         const T* __restrict__ bias_h, int din, int dout,
+                                         bool last, int act, const uint16_t* act_table,
+                                         unsigned int* codes_sm) {
+  const int nkg = HE_TK / KT;  // vector groups
+  const int tk = threadIdx.x % nkg, to = threadIdx.x / nkg;
+  float acc[KT][4];
+#pragma unroll
+  for (int i = 0; i < KT; ++i)
+#pragma unroll
+    for (int o = 0; o < 4; ++o) acc[i][o] = 0.f;
+
+  for (int d = 0; d < din; ++d) {
+    float a[KT];
+    const float* ap = a_in + d * HE_TK + tk * KT;
+#pragma unroll
+    for (int i = 0; i < KT; ++i) a[i] = ap[i];
+    const float4 w = *reinterpret_cast<const float4*>(w_sm + d * dout + to * 4);
+#pragma unroll
+    for (int i = 0; i < KT; ++i) {
+      acc[i][0] = fmaf(a[i], w.x, acc[i][0]);
+      acc[i][1] = fmaf(a[i], w.y, acc[i][1]);
+      acc[i][2] = fmaf(a[i], w.z, acc[i][2]);
+      acc[i][3] = fmaf(a[i], w.w, acc[i][3]);
+    }
+  }
+
+  float b[4];
+#pragma unroll
+  for (int o = 0; o < 4; ++o) b[o] = sah_to_float<T>(bias_h[to * 4 + o]);
+
+#pragma unroll
+  for (int i = 0; i < KT; ++i) {
+    unsigned int nib = 0u;
+#pragma unroll
+    for (int o = 0; o < 4; ++o) {
+      float v = sah_round_to<T>(acc[i][o]);        // einsum output in dtype
+      v = sah_round_to<T>(__fadd_rn(v, b[o]));     // + bias, rounded
+      if (!last) {
+        v = he_activate<T>(v, act, act_table);
+        a_out[(to * 4 + o) * HE_TK + tk * KT + i] = v;
+      } else {
+        nib |= (v > 0.f ? 1u : 0u) << o;
+      }
+    }
+    if (last && nib) atomicOr(&codes_sm[tk * KT + i], nib << (to * 4));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(HE_THREADS)
+hash_encode_kernel(HashEncodeArgs p) {
+  extern __shared__ __align__(16) unsigned char he_smem[];
+  float* act0 = reinterpret_cast<float*>(he_smem);
+  float* act1 = act0 + HE_MAXD * HE_TK;
+  float* w_sm = act1 + HE_MAXD * HE_TK;
+  __shared__ unsigned int codes_sm[HE_TK];
+
+  const int64_t tile = blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int h_in = h / (p.H_out / p.H_in);
+  const int64_t n0 = p.n_begin + tile * HE_TK;
+  const int D = p.dims[0];
+  const T* xb = reinterpret_cast<const T*>(p.x) + b * p.xs_b + h_in * p.xs_h;
+
+  // Stage the input tile transposed: act0[d][i].
+  const int chunks = D / 8;
+  for (int idx = threadIdx.x; idx < HE_TK * chunks; idx += HE_THREADS) {
+    int i = idx % HE_TK, c = idx / HE_TK;
+    int64_t n = n0 + i;
+    float f[8];
+    if (n < p.n_end) {
+      sah_load8<T>(xb + n * p.xs_n + c * 8, f);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = 0.f;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) act0[(c * 8 + e) * HE_TK + i] = f[e];
+  }
+  if (threadIdx.x < HE_TK) codes_sm[threadIdx.x] = 0u;
+
+  float* a_in = act0;
+  float* a_out = act1;
+  for (int l = 0; l < p.n_layers; ++l) {
+    const int din = p.dims[l], dout = p.dims[l + 1];
+    __syncthreads();  // previous layer done with w_sm / a_out complete
+    const T* wl = reinterpret_cast<const T*>(p.weights[l]) + (int64_t)h * din * dout;
+    for (int idx = threadIdx.x; idx < din * dout; idx += HE_THREADS)
+      w_sm[idx] = sah_to_float<T>(wl[idx]);
+    __syncthreads();
+    const T* bl = reinterpret_cast<const T*>(p.bias[l]) + (int64_t)h * dout;
+    const bool last = (l == p.n_layers - 1);
+    switch (dout) {
+      case 128: he_layer<T, 8>(a_in, a_out, w_sm, bl, din, dout, last, p.act, p.act_table, codes_sm); break;
+      case 64:  he_layer<T, 4>(a_in, a_out, w_sm, bl, din, dout, last, p.act, p.act_table, codes_sm); break;
+      case 32:  he_layer<T, 2>(a_in, a_out, w_sm, bl, din, dout, last, p.act, p.act_table, codes_sm); break;
+      default:  he_layer<T, 1>(a_in, a_out, w_sm, bl, din, dout, last, p.act, p.act_table, codes_sm); break;
+    }
+    float* t = a_in; a_in = a_out; a_out = t;
+  }
+  __syncthreads();
+  if (threadIdx.x < HE_TK) {
+    int64_t n = n0 + threadIdx.x;
+    if (n < p.n_end)
+      p.codes[((int64_t)b * p.H_out + h) * p.n_total + n] = codes_sm[threadIdx.x];
+  }
+}
+
+extern "C" int sah_hash_encode(const void* x, int dtype, int64_t xs_b, int64_t xs_h,
+                               int64_t xs_n, int B, int H_in, int H_out, int64_t n_begin,
+                               int64_t n_end, int64_t n_total, int n_layers, const int* dims,
+                               const void* const* weights, const void* const* bias, int act,
+                               const uint16_t* act_table, uint32_t* codes, void* stream) {
+  SAH_REQUIRE(x && dims && weights && bias && codes, "hash_encode: null pointer");
+  SAH_REQUIRE(B > 0 && H_in > 0 && H_out > 0 && H_out % H_in == 0, "hash_encode: bad heads");
+  SAH_REQUIRE(0 <= n_begin && n_begin <= n_end && n_end <= n_total, "hash_encode: bad range");
+  if (n_layers < 1 || n_layers > 4)
+    return sah_fail(SAH_ERR_UNSUPPORTED, "hash_encode: %d layers (1..4 supported)", n_layers);
+  for (int l = 0; l <= n_layers; ++l) {
+    int d = dims[l];
+    bool ok = (l == 0) ? (d % 8 == 0 && d >= 8 && d <= HE_MAXD)
+                       : (d == 16 || d == 32 || d == 64 || d == 128);
+    if (!ok)
+      return sah_fail(SAH_ERR_UNSUPPORTED,
+                      "hash_encode: layer width %d at position %d (input: multiple of 8 up to "
+                      "128; outputs: 16, 32, 64 or 128)", d, l);
+  }
+  if (dims[n_layers] > 32)
+    return sah_fail(SAH_ERR_UNSUPPORTED, "hash_encode: %d signature bits (<= 32 supported)",
+                    dims[n_layers]);
+  SAH_REQUIRE(act >= SAH_ACT_RELU && act <= SAH_ACT_TANH, "hash_encode: bad activation");
+  SAH_REQUIRE(dtype != SAH_BF16 || n_layers == 1 || act_table != nullptr,
+              "hash_encode: bf16 needs the activation table");
+  SAH_REQUIRE(xs_n % 8 == 0 && xs_h % 8 == 0 && xs_b % 8 == 0 &&
+                  ((uintptr_t)x % 16 == 0),
+              "hash_encode: x rows must be 16-byte aligned");
+  if (n_begin == n_end) return SAH_OK;
+
+  HashEncodeArgs p;
+  p.x = x; p.xs_b = xs_b; p.xs_h = xs_h; p.xs_n = xs_n;
+  p.H_in = H_in; p.H_out = H_out;
+  p.n_begin = n_begin; p.n_end = n_end; p.n_total = n_total;
+  p.n_layers = n_layers;
+  for (int l = 0; l < 5; ++l) p.dims[l] = (l <= n_layers) ? dims[l] : 0;
+  for (int l = 0; l < 4; ++l) {
+    p.weights[l] = (l < n_layers) ? weights[l] : nullptr;
+    p.bias[l] = (l < n_layers) ? bias[l] : nullptr;
+    if (l < n_layers) SAH_REQUIRE(p.weights[l] && p.bias[l], "hash_encode: null layer %d", l);
+  }
+  p.act = act; p.act_table = act_table; p.codes = codes;
+
+  const size_t smem = (size_t)(2 * HE_MAXD * HE_TK + HE_MAXD * HE_MAXD) * sizeof(float);
+  dim3 grid((unsigned)sah_ceil_div(n_end - n_begin, HE_TK), (unsigned)H_out, (unsigned)B);
+  cudaStream_t st = (cudaStream_t)stream;
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    cudaError_t e = cudaFuncSetAttribute(hash_encode_kernel<T>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "hash_encode attr: %s", cudaGetErrorString(e));
+    hash_encode_kernel<T><<<grid, HE_THREADS, smem, st>>>(p);
+  });
+  SAH_LAUNCH_CHECK("hash_encode");
+  return SAH_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Top-k over Hamming scores.
+// ---------------------------------------------------------------------------
+struct HashKeyPlain {
+  const uint32_t* kc;
+  uint32_t qc;
+  int nbits;
+  __device__ __forceinline__ unsigned int operator()(int64_t j) const {
+    return (unsigned int)(nbits - __popc(kc[j] ^ qc));  // matching bits: monotone in the score
+  }
+};
+
+template <typename T, int KEYBITS>
+struct HashKeyBiased {
+  const uint32_t* kc;
+  uint32_t qc;
+  int nbits;
+  const T* bias;
+  __device__ __forceinline__ unsigned int operator()(int64_t j) const {
+    float s = (float)(nbits - 2 * __popc(kc[j] ^ qc));
+    float f = sah_round_to<T>(__fadd_rn(s, sah_to_float<T>(bias[j]))) + 0.0f;
+    unsigned int key = sah_float_key(f);
+    return KEYBITS == 16 ? (key >> 16) : key;
+  }
+};
+
+template <typename T, int KEYBITS, bool BIASED>
+__global__ void __launch_bounds__(SAH_SELECT_THREADS)
+hash_topk_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
+                 const uint32_t* __restrict__ qcodes, int nbits, const T* __restrict__ bias, int64_t bias_s_b, int64_t bias_s_h,
+                 int64_t bias_s_q, int Hq, int Sq, int64_t S, int64_t W,
+                 const uint32_t* __restrict__ prev_bits, int64_t k,
+                 uint32_t* __restrict__ out_bits) {
+  __shared__ SahSelectSmem sm;
+  const int64_t row = blockIdx.x;
+  const int q = (int)(row % Sq);
+  const int64_t bh = row / Sq;
+  const int h = (int)(bh % Hq);
+  const int64_t b = bh / Hq;
+  const uint32_t* kc = kcodes + bh * kc_stride;
+  const uint32_t qc = qcodes[row];
+  if (BIASED) {
+    HashKeyBiased<T, KEYBITS> kf{kc, qc, nbits, bias + b * bias_s_b + h * bias_s_h + q * bias_s_q};
+    sah_select_row<KEYBITS>(kf, prev_bits + row * W, out_bits + row * W, S, W, 0, S, k, sm);
+  } else {
+    HashKeyPlain kf{kc, qc, nbits};
+    sah_select_row<8>(kf, prev_bits + row * W, out_bits + row * W, S, W, 0, S, k, sm);
+  }
+}
+
+extern "C" int sah_hash_topk(const uint32_t* kcodes, int64_t kc_stride, const uint32_t* qcodes,
+                             int nbits,
+                             const void* bias, int dtype, int64_t bias_s_b, int64_t bias_s_h,
+                             int64_t bias_s_q, int B, int Hq, int Sq, int64_t S, int64_t W,
+                             const uint32_t* prev_bits, int64_t k, uint32_t* out_bits,
+                             void* stream) {
+  SAH_REQUIRE(kcodes && qcodes && prev_bits && out_bits, "hash_topk: null pointer");
+  SAH_REQUIRE(nbits > 0 && nbits <= 32, "hash_topk: nbits must be 1..32");
+  SAH_REQUIRE(kc_stride >= S, "hash_topk: kc_stride shorter than S");
+  SAH_REQUIRE(B > 0 && Hq > 0 && Sq > 0 && S > 0 && W * 32 >= S, "hash_topk: bad extents");
+  const int64_t rows = (int64_t)B * Hq * Sq;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (bias == nullptr) {
+    hash_topk_kernel<float, 8, false><<<(unsigned)rows, SAH_SELECT_THREADS, 0, st>>>(
+        kcodes, kc_stride, qcodes, nbits, nullptr, 0, 0, 0, Hq, Sq, S, W, prev_bits, k, out_bits);
+  } else if (dtype == SAH_BF16) {
+    hash_topk_kernel<__nv_bfloat16, 16, true><<<(unsigned)rows, SAH_SELECT_THREADS, 0, st>>>(
+        kcodes, kc_stride, qcodes, nbits, (const __nv_bfloat16*)bias, bias_s_b, bias_s_h, bias_s_q, Hq, Sq,
+        S, W, prev_bits, k, out_bits);
+  } else if (dtype == SAH_F32) {
+    hash_topk_kernel<float, 32, true><<<(unsigned)rows, SAH_SELECT_THREADS, 0, st>>>(
+        kcodes, kc_stride, qcodes, nbits, (const float*)bias, bias_s_b, bias_s_h, bias_s_q, Hq, Sq, S, W,
+        prev_bits, k, out_bits);
+  } else {
+    return sah_fail(SAH_ERR_INVALID, "hash_topk: unknown dtype %d", dtype);
+  }
+  SAH_LAUNCH_CHECK("hash_topk");
+  return SAH_OK;
+}

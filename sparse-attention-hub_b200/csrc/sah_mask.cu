@@ -1,0 +1,362 @@
+// Mask container kernels: the active set of a Mask lives on the device as a
+// bitmap (uint32 [rows][W]); these kernels edit it, scan it into the CSR
+// companion arrays (ptr / wpre) and convert between the bitmap form and the
+// reference's dense and indices/ptr/data forms (utils/mask.py).
+#include <stdarg.h>
+#include <string.h>
+
+#include "sah_common.cuh"
+
+// ---- status plumbing --------------------------------------------------------
+static thread_local char g_sah_err[512] = "";
+
+int sah_fail(int status, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_sah_err, sizeof(g_sah_err), fmt, ap);
+  va_end(ap);
+  return status;
+}
+
+extern "C" const char* sah_last_error(void) { return g_sah_err; }
+extern "C" const char* sah_version(void) { return "sah_b200 0.1 (sm_100a)"; }
+
+// ---- band fill --------------------------------------------------------------
+__global__ void mask_fill_band_kernel(uint32_t* __restrict__ bits, int64_t rows, int Sq,
+                                      int64_t S, int64_t W, int64_t w_begin, int64_t w_count,
+                                      int64_t lo_base, int64_t lo_qstep, int64_t hi_base,
+                                      int64_t hi_qstep, int value) {
+  int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= rows * w_count) return;
+  int64_t row = t / w_count;
+  int64_t w = w_begin + (t - row * w_count);
+  int64_t q = row % Sq;
+  int64_t lo = lo_base + q * lo_qstep;
+  int64_t hi = hi_base + q * hi_qstep;
+  if (lo < 0) lo = 0;
+  if (hi > S) hi = S;
+  int64_t c0 = w * 32, c1 = c0 + 32;
+  if (hi <= c0 || lo >= c1 || lo >= hi) return;
+  int64_t a = lo > c0 ? lo - c0 : 0;        // first bit in word
+  int64_t b = hi < c1 ? hi - c0 : 32;       // one past last bit
+  uint32_t m = (b >= 32 ? 0xffffffffu : ((1u << b) - 1u)) & ~((1u << a) - 1u);
+  uint32_t* p = bits + row * W + w;
+  if (value) *p |= m; else *p &= ~m;
+}
+
+extern "C" int sah_mask_fill_band(uint32_t* bits, int64_t rows, int Sq, int64_t S, int64_t W,
+                                  int64_t lo_base, int64_t lo_qstep, int64_t hi_base,
+                                  int64_t hi_qstep, int value, void* stream) {
+  SAH_REQUIRE(bits != nullptr, "fill_band: bits is null");
+  SAH_REQUIRE(rows >= 0 && Sq > 0 && S > 0 && W * 32 >= S, "fill_band: bad extents");
+  if (rows == 0) return SAH_OK;
+  // Column hull over all query positions bounds the words any row touches.
+  int64_t lo0 = lo_base, lo1 = lo_base + (Sq - 1) * lo_qstep;
+  int64_t hi0 = hi_base, hi1 = hi_base + (Sq - 1) * hi_qstep;
+  int64_t lo = lo0 < lo1 ? lo0 : lo1, hi = hi0 > hi1 ? hi0 : hi1;
+  if (lo < 0) lo = 0;
+  if (hi > S) hi = S;
+  if (hi <= lo) return SAH_OK;
+  int64_t w_begin = lo / 32, w_end = (hi + 31) / 32;
+  int64_t w_count = w_end - w_begin;
+  int64_t total = rows * w_count;
+  int threads = 256;
+  int64_t blocks = sah_ceil_div(total, threads);
+  mask_fill_band_kernel<<<(unsigned)blocks, threads, 0, (cudaStream_t)stream>>>(
+      bits, rows, Sq, S, W, w_begin, w_count, lo_base, lo_qstep, hi_base, hi_qstep, value);
+  SAH_LAUNCH_CHECK("mask_fill_band");
+  return SAH_OK;
+}
+
+// ---- row scan: wpre (per word exclusive popcount) and ptr --------------------
+// One CTA per row; the running base carries across blockDim-word chunks.
+__global__ void mask_rowscan_kernel(const uint32_t* __restrict__ bits, int64_t W,
+                                    int32_t* __restrict__ wpre, int64_t* __restrict__ rowcnt) {
+  __shared__ int scratch[33];
+  int64_t row = blockIdx.x;
+  const uint32_t* b = bits + row * W;
+  int base = 0;
+  for (int64_t w0 = 0; w0 < W; w0 += blockDim.x) {
+    int64_t w = w0 + threadIdx.x;
+    int c = (w < W) ? __popc(b[w]) : 0;
+    int total;
+    int ex = sah_block_excl_scan<int>(c, scratch, &total);
+    if (w < W && wpre != nullptr) wpre[row * W + w] = base + ex;
+    base += total;
+  }
+  if (threadIdx.x == 0) rowcnt[row] = base;
+}
+
+// Exclusive scan of rowcnt[rows] into ptr[rows+1] (single CTA, looped).
+__global__ void mask_ptrscan_kernel(const int64_t* rowcnt, int64_t rows, int64_t* ptr) {
+  __shared__ long long scratch[33];
+  long long base = 0;
+  for (int64_t r0 = 0; r0 < rows; r0 += blockDim.x) {
+    int64_t r = r0 + threadIdx.x;
+    long long c = (r < rows) ? rowcnt[r] : 0;
+    long long total;
+    long long ex = sah_block_excl_scan<long long>(c, scratch, &total);
+    if (r < rows) ptr[r] = base + ex;
+    base += total;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) ptr[rows] = base;
+}
+
+extern "C" int sah_mask_rowscan(const uint32_t* bits, int64_t rows, int64_t W, int32_t* wpre,
+                                int64_t* ptr, void* stream) {
+  SAH_REQUIRE(bits != nullptr && ptr != nullptr, "rowscan: null pointer");
+  SAH_REQUIRE(rows >= 0 && W > 0, "rowscan: bad extents");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (rows > 0) {
+    // Row counts are staged in ptr[1 .. rows]; the scan kernel reads them
+    // from there before overwriting (it walks forward, one chunk at a time,
+    // and every chunk is read completely before any of it is written).
+    mask_rowscan_kernel<<<(unsigned)rows, 1024, 0, st>>>(bits, W, wpre, ptr + 1);
+    SAH_LAUNCH_CHECK("mask_rowscan");
+  }
+  // In-place: chunk r0 reads ptr[1 + r] for r in the chunk, then writes ptr[r]
+  // for the same r; ptr[1 + last r of chunk] is read by the next chunk, so the
+  // write of ptr[r] (r <= last) never clobbers an unread count.
+  mask_ptrscan_kernel<<<1, 1024, 0, st>>>(ptr + 1, rows, ptr);
+  SAH_LAUNCH_CHECK("mask_ptrscan");
+  return SAH_OK;
+}
+
+// ---- bits -> flat indices ----------------------------------------------------
+__global__ void mask_bits_to_indices_kernel(const uint32_t* __restrict__ bits,
+                                            const int32_t* __restrict__ wpre,
+                                            const int64_t* __restrict__ ptr, int64_t rows,
+                                            int64_t S, int64_t W, int64_t* __restrict__ idx) {
+  int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= rows * W) return;
+  int64_t row = t / W, w = t - row * W;
+  uint32_t m = bits[t];
+  if (!m) return;
+  int64_t o = ptr[row] + wpre[t];
+  int64_t base = row * S + w * 32;
+  while (m) {
+    int b = __ffs(m) - 1;
+    idx[o++] = base + b;
+    m &= m - 1;
+  }
+}
+
+extern "C" int sah_mask_bits_to_indices(const uint32_t* bits, const int32_t* wpre,
+                                        const int64_t* ptr, int64_t rows, int64_t S, int64_t W,
+                                        int64_t* indices, void* stream) {
+  SAH_REQUIRE(bits && wpre && ptr, "bits_to_indices: null pointer");
+  if (rows == 0) return SAH_OK;
+  SAH_REQUIRE(indices != nullptr, "bits_to_indices: indices is null");
+  int64_t total = rows * W;
+  mask_bits_to_indices_kernel<<<(unsigned)sah_ceil_div(total, 256), 256, 0,
+                                (cudaStream_t)stream>>>(bits, wpre, ptr, rows, S, W, indices);
+  SAH_LAUNCH_CHECK("mask_bits_to_indices");
+  return SAH_OK;
+}
+
+// ---- bits (+data) -> dense ----------------------------------------------------
+template <typename T>
+__global__ void mask_bits_to_dense_kernel(const uint32_t* __restrict__ bits,
+                                          const T* __restrict__ data,
+                                          const int32_t* __restrict__ wpre,
+                                          const int64_t* __restrict__ ptr, int64_t rows,
+                                          int64_t S, int64_t W, T* __restrict__ dense) {
+  int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= rows * S) return;
+  int64_t row = t / S, j = t - row * S;
+  int64_t wi = row * W + (j >> 5);
+  uint32_t m = bits[wi];
+  int b = (int)(j & 31);
+  float v = 0.f;
+  if ((m >> b) & 1u) {
+    if (data == nullptr) {
+      v = 1.f;
+    } else {
+      int64_t pos = ptr[row] + wpre[wi] + __popc(m & ((1u << b) - 1u));
+      v = sah_to_float<T>(data[pos]);
+    }
+  }
+  dense[t] = sah_from_float<T>(v);
+}
+
+extern "C" int sah_mask_bits_to_dense(const uint32_t* bits, const void* data,
+                                      const int32_t* wpre, const int64_t* ptr, int dtype,
+                                      int64_t rows, int64_t S, int64_t W, void* dense,
+                                      void* stream) {
+  SAH_REQUIRE(bits && dense, "bits_to_dense: null pointer");
+  SAH_REQUIRE(data == nullptr || (wpre && ptr), "bits_to_dense: data needs wpre and ptr");
+  if (rows == 0) return SAH_OK;
+  int64_t total = rows * S;
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    mask_bits_to_dense_kernel<T><<<(unsigned)sah_ceil_div(total, 256), 256, 0,
+                                   (cudaStream_t)stream>>>(bits, (const T*)data, wpre, ptr,
+                                                           rows, S, W, (T*)dense);
+  });
+  SAH_LAUNCH_CHECK("mask_bits_to_dense");
+  return SAH_OK;
+}
+
+// ---- dense -> bits -------------------------------------------------------------
+template <typename T>
+__global__ void mask_dense_to_bits_kernel(const T* __restrict__ dense, int64_t rows, int64_t S,
+                                          int64_t W, uint32_t* __restrict__ bits) {
+  int64_t gw = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;  // one warp per word
+  int lane = threadIdx.x & 31;
+  if (gw >= rows * W) return;
+  int64_t row = gw / W, w = gw - row * W;
+  int64_t j = w * 32 + lane;
+  bool on = false;
+  if (j < S) on = sah_to_float<T>(dense[row * S + j]) != 0.f;
+  uint32_t m = __ballot_sync(0xffffffffu, on);
+  if (lane == 0) bits[gw] = m;
+}
+
+extern "C" int sah_mask_dense_to_bits(const void* dense, int dtype, int64_t rows, int64_t S,
+                                      int64_t W, uint32_t* bits, void* stream) {
+  SAH_REQUIRE(dense && bits, "dense_to_bits: null pointer");
+  SAH_REQUIRE(W * 32 >= S, "dense_to_bits: W too small");
+  if (rows == 0) return SAH_OK;
+  int64_t threads_total = rows * W * 32;
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    mask_dense_to_bits_kernel<T><<<(unsigned)sah_ceil_div(threads_total, 256), 256, 0,
+                                   (cudaStream_t)stream>>>((const T*)dense, rows, S, W, bits);
+  });
+  SAH_LAUNCH_CHECK("mask_dense_to_bits");
+  return SAH_OK;
+}
+
+// ---- dense -> data (CSR order) ---------------------------------------------------
+template <typename T>
+__global__ void mask_dense_gather_data_kernel(const T* __restrict__ dense,
+                                              const uint32_t* __restrict__ bits,
+                                              const int32_t* __restrict__ wpre,
+                                              const int64_t* __restrict__ ptr, int64_t rows,
+                                              int64_t S, int64_t W, T* __restrict__ data) {
+  int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= rows * S) return;
+  int64_t row = t / S, j = t - row * S;
+  int64_t wi = row * W + (j >> 5);
+  uint32_t m = bits[wi];
+  int b = (int)(j & 31);
+  if ((m >> b) & 1u) {
+    int64_t pos = ptr[row] + wpre[wi] + __popc(m & ((1u << b) - 1u));
+    data[pos] = dense[t];
+  }
+}
+
+extern "C" int sah_mask_dense_gather_data(const void* dense, int dtype, const uint32_t* bits,
+                                          const int32_t* wpre, const int64_t* ptr,
+                                          int64_t rows, int64_t S, int64_t W, void* data,
+                                          void* stream) {
+  SAH_REQUIRE(dense && bits && wpre && ptr, "dense_gather_data: null pointer");
+  if (rows == 0) return SAH_OK;
+  int64_t total = rows * S;
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    mask_dense_gather_data_kernel<T><<<(unsigned)sah_ceil_div(total, 256), 256, 0,
+                                       (cudaStream_t)stream>>>((const T*)dense, bits, wpre,
+                                                               ptr, rows, S, W, (T*)data);
+  });
+  SAH_LAUNCH_CHECK("mask_dense_gather_data");
+  return SAH_OK;
+}
+
+// ---- bitmap OR ---------------------------------------------------------------------
+__global__ void mask_or_kernel(const uint32_t* __restrict__ a, const uint32_t* __restrict__ b,
+                               int64_t words, uint32_t* __restrict__ out) {
+  int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t < words) out[t] = a[t] | b[t];
+}
+
+extern "C" int sah_mask_or(const uint32_t* a, const uint32_t* b, int64_t words, uint32_t* out,
+                           void* stream) {
+  SAH_REQUIRE(a && b && out, "mask_or: null pointer");
+  if (words == 0) return SAH_OK;
+  mask_or_kernel<<<(unsigned)sah_ceil_div(words, 256), 256, 0, (cudaStream_t)stream>>>(
+      a, b, words, out);
+  SAH_LAUNCH_CHECK("mask_or");
+  return SAH_OK;
+}
+
+// ---- weights of a sampled merge --------------------------------------------------------
+// data of out_bits = prev | samp where prev has unit weights: entries of prev
+// keep 1, new entries take the per-row weight (or the per-key dense weight).
+template <typename T>
+__global__ void mask_sample_data_kernel(const uint32_t* __restrict__ prev,
+                                        const uint32_t* __restrict__ outb,
+                                        const int32_t* __restrict__ wpre,
+                                        const int64_t* __restrict__ ptr,
+                                        const T* __restrict__ row_weight,
+                                        const T* __restrict__ dense_weight, int64_t rows,
+                                        int64_t S, int64_t W, T* __restrict__ data) {
+  int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= rows * W) return;
+  int64_t row = t / W, w = t - row * W;
+  uint32_t m = outb[t];
+  if (!m) return;
+  uint32_t p = prev ? prev[t] : 0u;
+  int64_t o = ptr[row] + wpre[t];
+  while (m) {
+    int b = __ffs(m) - 1;
+    T v;
+    if ((p >> b) & 1u) {
+      v = sah_from_float<T>(1.f);
+    } else if (dense_weight) {
+      v = dense_weight[row * S + w * 32 + b];
+    } else {
+      v = row_weight[row];
+    }
+    data[o++] = v;
+    m &= m - 1;
+  }
+}
+
+extern "C" int sah_mask_sample_data(const uint32_t* prev_bits, const uint32_t* out_bits,
+                                    const int32_t* wpre, const int64_t* ptr,
+                                    const void* row_weight, const void* dense_weight,
+                                    int dtype, int64_t rows, int64_t S, int64_t W, void* data,
+                                    void* stream) {
+  SAH_REQUIRE(out_bits && wpre && ptr, "sample_data: null pointer");
+  SAH_REQUIRE(row_weight || dense_weight, "sample_data: no weight source");
+  if (rows == 0) return SAH_OK;
+  SAH_REQUIRE(data != nullptr, "sample_data: data is null");
+  int64_t total = rows * W;
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    mask_sample_data_kernel<T><<<(unsigned)sah_ceil_div(total, 256), 256, 0,
+                                 (cudaStream_t)stream>>>(prev_bits, out_bits, wpre, ptr,
+                                                         (const T*)row_weight,
+                                                         (const T*)dense_weight, rows, S, W,
+                                                         (T*)data);
+  });
+  SAH_LAUNCH_CHECK("mask_sample_data");
+  return SAH_OK;
+}
+
+// ---- ragged sample list -> bitmap ----------------------------------------------------------
+__global__ void mask_scatter_samples_kernel(const int64_t* __restrict__ cols,
+                                            const int64_t* __restrict__ sptr, int64_t rows,
+                                            int64_t n_max, int64_t S, int64_t W,
+                                            uint32_t* __restrict__ bits) {
+  int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= n_max || j >= sptr[rows]) return;
+  // row = last r with sptr[r] <= j
+  int64_t lo = 0, hi = rows;  // invariant: sptr[lo] <= j < sptr[hi]
+  while (hi - lo > 1) {
+    int64_t mid = (lo + hi) >> 1;
+    if (sptr[mid] <= j) lo = mid; else hi = mid;
+  }
+  int64_t c = cols[j];
+  if (c < 0 || c >= S) return;
+  atomicOr(bits + lo * W + (c >> 5), 1u << (c & 31));
+}
+
+extern "C" int sah_mask_scatter_samples(const int64_t* cols, const int64_t* sptr, int64_t rows,
+                                        int64_t n_max, int64_t S, int64_t W, uint32_t* bits,
+                                        void* stream) {
+  SAH_REQUIRE(cols && sptr && bits, "scatter_samples: null pointer");
+  if (rows == 0 || n_max == 0) return SAH_OK;
+  mask_scatter_samples_kernel<<<(unsigned)sah_ceil_div(n_max, 256), 256, 0,
+                                (cudaStream_t)stream>>>(cols, sptr, rows, n_max, S, W, bits);
+  SAH_LAUNCH_CHECK("mask_scatter_samples");
+  return SAH_OK;
+}

@@ -1,0 +1,199 @@
+"""Thin Python wrappers around the C ABI, shared by the native maskers.
+
+Each wrapper validates devices, allocates outputs with torch (device memory
+and streams are torch's; all arithmetic is the library's) and launches on the
+current CUDA stream of the tensors' device.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import _native
+from .utils.mask import Mask, NativeBits, words_per_row
+
+
+def _rows(shape: Sequence[int]) -> int:
+    return int(np.prod(shape[:-1]))
+
+
+def bias_args(attention_mask: Optional[torch.Tensor], dtype: torch.dtype, n_keys: int):
+    """(keep-alive tensor, pointer, stride_b, stride_h, stride_q) for an additive bias."""
+    from .utils.mask_attention_utils import _bias_args
+
+    return _bias_args(attention_mask, dtype, n_keys)
+
+
+def unit_weight_bits(previous_mask: Mask) -> Optional[NativeBits]:
+    """Bitmap of `previous_mask` when all of its weights are 1, else None.
+
+    Native maskers edit such bitmaps directly; a mask with other weights goes
+    through its dense form instead.
+    """
+    if previous_mask.is_full:
+        return None
+    nb = previous_mask.native_bits()
+    return nb if nb.data is None else None
+
+
+def fresh_native(nb: NativeBits) -> NativeBits:
+    """Same bitmap storage, CSR companions dropped (call after editing the bits)."""
+    return NativeBits(nb.bits, nb.rows, nb.n_cols, data=None)
+
+
+def fill_band(nb: NativeBits, seq_len_queries: int, lo_base: int, lo_qstep: int, hi_base: int,
+              hi_qstep: int, value: int) -> None:
+    lib = _native.load()
+    dev = nb.bits.device
+    _native.check(
+        lib.sah_mask_fill_band(nb.bits.data_ptr(), nb.rows, seq_len_queries, nb.n_cols, nb.words,
+                               lo_base, lo_qstep, hi_base, hi_qstep, value, _native.stream_of(dev)),
+        "sah_mask_fill_band")
+    nb.ptr = None  # the CSR companions describe the old bits
+    nb.wpre = None
+
+
+def bits_andnot(a: NativeBits, b: NativeBits) -> NativeBits:
+    """a & ~b as a new bitmap (bookkeeping for the index-returning helper)."""
+    return NativeBits(torch.bitwise_and(a.bits, torch.bitwise_not(b.bits)), a.rows, a.n_cols)
+
+
+def topk_select(scores: torch.Tensor, previous_mask: Mask, k: int, col_begin: int = 0,
+                col_end: Optional[int] = None, out: Optional[NativeBits] = None) -> NativeBits:
+    """previous | top-k of `scores` over inactive columns in [col_begin, col_end)."""
+    _native.require_cuda(scores, "scores")
+    lib = _native.load()
+    S = scores.shape[-1]
+    rows = _rows(scores.shape)
+    prev = previous_mask.native_bits()
+    dst = out if out is not None else NativeBits(torch.empty_like(prev.bits), rows, S)
+    sc = scores.contiguous()
+    _native.check(
+        lib.sah_topk_select(sc.data_ptr(), _native.dtype_code(sc.dtype), rows, S, prev.words,
+                            col_begin, S if col_end is None else col_end, prev.bits.data_ptr(),
+                            k, dst.bits.data_ptr(), _native.stream_of(sc.device)),
+        "sah_topk_select")
+    return dst
+
+
+def qk_scores(queries: torch.Tensor, keys: torch.Tensor,
+              attention_mask: Optional[torch.Tensor]) -> torch.Tensor:
+    """Unscaled q.k in the input dtype (+ additive bias), `[B, Hq, Sq, S]`."""
+    _native.require_cuda(queries, "queries")
+    _native.require_cuda(keys, "keys")
+    lib = _native.load()
+    B, Hq, Sq, D = queries.shape
+    Hkv, S = keys.shape[1], keys.shape[2]
+    q = queries if queries.stride(-1) == 1 else queries.contiguous()
+    k = keys if keys.stride(-1) == 1 else keys.contiguous()
+    scores = torch.empty((B, Hq, Sq, S), dtype=q.dtype, device=q.device)
+    keep, bptr, bsb, bsh, bsq = bias_args(attention_mask, q.dtype, S)
+    _native.check(
+        lib.sah_qk_scores(q.data_ptr(), k.data_ptr(), _native.dtype_code(q.dtype), q.stride(0),
+                          q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2), B, Hq,
+                          Hkv, Sq, S, D, bptr, bsb, bsh, bsq, scores.data_ptr(),
+                          _native.stream_of(q.device)),
+        "sah_qk_scores")
+    del keep
+    return scores
+
+
+# ---- HashAttention ------------------------------------------------------------
+_ACT_TABLES: dict = {}
+
+
+def _bf16_bits_to_f64(bits: np.ndarray) -> np.ndarray:
+    return (bits.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+
+
+def _f64_to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even to bfloat16 (through float32, as a bf16 kernel does)."""
+    f = x.astype(np.float32)
+    u = f.view(np.uint32).astype(np.uint64)
+    rounded = (u + 0x7FFF + ((u >> 16) & 1)) >> 16
+    out = rounded.astype(np.uint32) & 0xFFFF
+    nan = np.isnan(f)
+    out[nan] = 0x7FC0
+    return out.astype(np.uint16)
+
+
+def activation_table(name: str, device: torch.device) -> torch.Tensor:
+    """uint16[65536]: bf16 bit pattern of x -> bf16 bit pattern of act(x).
+
+    The activation is evaluated in float64 and rounded once to bfloat16, which
+    is the value a float32 evaluation rounds to for every input except rare
+    double-rounding cases.
+    """
+    key = (name, str(device))
+    if key in _ACT_TABLES:
+        return _ACT_TABLES[key]
+    if name not in _native.ACTIVATIONS:
+        raise ValueError(f"Unsupported activation function: {name}")
+    bits = np.arange(65536, dtype=np.uint32)
+    x = _bf16_bits_to_f64(bits)
+    with np.errstate(over="ignore", invalid="ignore"):
+        if name == "relu":
+            y = np.maximum(x, 0.0)
+        elif name == "silu":
+            y = x / (1.0 + np.exp(-x))
+        elif name == "gelu":
+            from math import erf, sqrt
+            y = 0.5 * x * (1.0 + np.vectorize(erf)(x / sqrt(2.0)))
+        else:
+            y = np.tanh(x)
+    table = _f64_to_bf16_bits(np.where(np.isnan(x), x, y))
+    t = torch.from_numpy(table.view(np.int16).copy()).to(device)
+    _ACT_TABLES[key] = t
+    return t
+
+
+def hash_encode(x: torch.Tensor, n_heads_out: int, weights: List[torch.Tensor],
+                biases: List[torch.Tensor], activation: str, codes: torch.Tensor,
+                n_begin: int, n_end: int) -> None:
+    """Pack sign(MLP(x[:, :, n_begin:n_end])) into `codes[:, :, n_begin:n_end]` (int32 words)."""
+    _native.require_cuda(x, "hash input")
+    lib = _native.load()
+    B, H_in, _, D = x.shape
+    xs = x if x.stride(-1) == 1 else x.contiguous()
+    n_layers = len(weights)
+    dims = [D] + [int(w.shape[-1]) for w in weights]
+    for l, w in enumerate(weights):
+        if tuple(w.shape) != (n_heads_out, dims[l], dims[l + 1]) or not w.is_contiguous():
+            raise ValueError(f"hash weight {l} must be contiguous [H, {dims[l]}, {dims[l + 1]}]")
+        if w.dtype != x.dtype or biases[l].dtype != x.dtype:
+            raise ValueError("hash weights must be in the dtype of the hashed tensor")
+    c_dims = (ctypes.c_int * len(dims))(*dims)
+    c_w = (ctypes.c_void_p * n_layers)(*[w.data_ptr() for w in weights])
+    c_b = (ctypes.c_void_p * n_layers)(*[b.data_ptr() for b in biases])
+    table = activation_table(activation, x.device) if x.dtype == torch.bfloat16 else None
+    _native.check(
+        lib.sah_hash_encode(xs.data_ptr(), _native.dtype_code(x.dtype), xs.stride(0), xs.stride(1),
+                            xs.stride(2), B, H_in, n_heads_out, n_begin, n_end, codes.shape[-1],
+                            n_layers, c_dims, c_w, c_b, _native.ACTIVATIONS[activation],
+                            _native.ptr(table), codes.data_ptr(), _native.stream_of(x.device)),
+        "sah_hash_encode")
+
+
+def hash_topk(kcodes: torch.Tensor, n_keys: int, qcodes: torch.Tensor, nbits: int,
+              attention_mask: Optional[torch.Tensor], dtype: torch.dtype, previous_mask: Mask,
+              k: int, shape: Tuple[int, int, int, int]) -> NativeBits:
+    """previous | top-k Hamming matches; kcodes `[B, Hq, capacity]` with `n_keys` valid."""
+    lib = _native.load()
+    B, Hq, Sq, S = shape
+    if kcodes.shape[-1] < S or not kcodes.is_contiguous():
+        raise ValueError("key codes must be contiguous [B, Hq, capacity >= S]")
+    prev = previous_mask.native_bits()
+    dst = NativeBits(torch.empty_like(prev.bits), prev.rows, S)
+    keep, bptr, bsb, bsh, bsq = bias_args(attention_mask, dtype, S)
+    _native.check(
+        lib.sah_hash_topk(kcodes.data_ptr(), kcodes.shape[-1], qcodes.data_ptr(), nbits, bptr,
+                          _native.dtype_code(dtype), bsb, bsh, bsq, B, Hq, Sq, S, prev.words,
+                          prev.bits.data_ptr(), k, dst.bits.data_ptr(),
+                          _native.stream_of(kcodes.device)),
+        "sah_hash_topk")
+    del keep
+    return dst

@@ -1,0 +1,28 @@
+"""Fixed-pattern maskers."""
+
+from .base import (
+    FixedMasker,
+    FixedMaskerConfig,
+    TopKMasker,
+    TopKMaskerConfig,
+    TopPMasker,
+    TopPMaskerConfig,
+)
+from .implementations import (
+    CausalMasker,
+    HashAttentionTopKMasker,
+    HashAttentionTopKMaskerConfig,
+    LocalMasker,
+    LocalMaskerConfig,
+    OracleTopK,
+    OracleTopKConfig,
+    SinkMasker,
+    SinkMaskerConfig,
+)
+
+__all__ = [
+    "FixedMasker", "TopKMasker", "TopPMasker", "FixedMaskerConfig", "TopKMaskerConfig",
+    "TopPMaskerConfig", "LocalMasker", "CausalMasker", "SinkMasker", "OracleTopK",
+    "HashAttentionTopKMasker", "LocalMaskerConfig", "SinkMaskerConfig", "OracleTopKConfig",
+    "HashAttentionTopKMaskerConfig",
+]

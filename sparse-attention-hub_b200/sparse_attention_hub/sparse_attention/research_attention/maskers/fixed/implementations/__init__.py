@@ -1,0 +1,16 @@
+"""Native fixed maskers."""
+
+from .basic_fixed import (
+    CausalMasker,
+    LocalMasker,
+    LocalMaskerConfig,
+    SinkMasker,
+    SinkMaskerConfig,
+)
+from .hashattention_top_k import HashAttentionTopKMasker, HashAttentionTopKMaskerConfig
+from .oracle_top_k import OracleTopK, OracleTopKConfig
+
+__all__ = [
+    "LocalMasker", "CausalMasker", "SinkMasker", "OracleTopK", "HashAttentionTopKMasker",
+    "LocalMaskerConfig", "SinkMaskerConfig", "OracleTopKConfig", "HashAttentionTopKMaskerConfig",
+]

@@ -1,0 +1,153 @@
+"""Seeded synthetic decode workloads: Q/K/V and masker parameters.
+
+The reference measures this path on random tensors only
+(profile/profile_research_attention.py:68-127).  These generators produce the
+shapes and value distributions of the benchmark configurations from a seed,
+with numpy's Philox generator so that every machine gets identical values.
+All arrays are float32; `to_dtype` rounds them to the compute dtype.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Tuple
+
+import numpy as np
+
+
+def _rng(seed: int, stream: int) -> np.random.Generator:
+    return np.random.Generator(np.random.Philox(key=[seed, stream]))
+
+
+def _normalise(x: np.ndarray) -> np.ndarray:
+    return x / np.maximum(np.linalg.norm(x, axis=-1, keepdims=True), 1e-12)
+
+
+@dataclass
+class DecodeWorkload:
+    """One decode step of one layer."""
+
+    name: str
+    dtype: str                      # "f32" or "bf16"
+    q: np.ndarray                   # [B, Hq, Sq, D]
+    k: np.ndarray                   # [B, Hkv, S, D]
+    v: np.ndarray                   # [B, Hkv, S, D]
+    scaling: float
+    stack: List[Tuple[str, Dict[str, Any]]] = field(default_factory=list)
+
+    @property
+    def shape(self) -> Tuple[int, int, int, int, int, int]:
+        B, Hq, Sq, D = self.q.shape
+        return B, Hq, self.k.shape[1], Sq, self.k.shape[2], D
+
+
+def qkv_iid_outliers(seed: int, B: int, Hq: int, Hkv: int, S: int, D: int, Sq: int = 1,
+                     n_outlier: int = 4, outlier_scale: float = 8.0):
+    """N(0,1) everywhere; `n_outlier` fixed key channels scaled up."""
+    q = _rng(seed, 0).standard_normal((B, Hq, Sq, D), dtype=np.float32)
+    k = _rng(seed, 1).standard_normal((B, Hkv, S, D), dtype=np.float32)
+    v = _rng(seed, 2).standard_normal((B, Hkv, S, D), dtype=np.float32)
+    chans = _rng(seed, 3).choice(D, size=n_outlier, replace=False)
+    k[..., chans] *= np.float32(outlier_scale)
+    return q, k, v
+
+
+def qkv_planted(seed: int, B: int, Hq: int, Hkv: int, S: int, D: int, Sq: int = 1,
+                frac: float = 0.01, cosine: float = 0.6):
+    """K, V ~ N(0,1); per KV group a direction u; `frac` of the group's keys are
+    turned to cosine `cosine` with u; the group's queries point along u (plus a
+    little per-head noise), so attention is peaked on the planted keys."""
+    G = Hq // Hkv
+    k = _rng(seed, 1).standard_normal((B, Hkv, S, D), dtype=np.float32)
+    v = _rng(seed, 2).standard_normal((B, Hkv, S, D), dtype=np.float32)
+    u = _normalise(_rng(seed, 4).standard_normal((B, Hkv, 1, D), dtype=np.float32))
+    n_plant = max(1, int(frac * S))
+    pick = _rng(seed, 5)
+    for b in range(B):
+        for h in range(Hkv):
+            idx = pick.choice(S, size=n_plant, replace=False)
+            rows = k[b, h, idx]
+            norms = np.linalg.norm(rows, axis=-1, keepdims=True)
+            uu = u[b, h]
+            perp = _normalise(rows - (rows @ uu.T) * uu)
+            k[b, h, idx] = norms * (cosine * uu + np.sqrt(1.0 - cosine * cosine) * perp)
+    noise = _rng(seed, 6).standard_normal((B, Hkv, G, Sq, D), dtype=np.float32)
+    qd = _normalise(u[:, :, None, :, :] + 0.3 * _normalise(noise))
+    q = (np.sqrt(D) * qd).reshape(B, Hq, Sq, D).astype(np.float32)
+    return q, k, v
+
+
+def qkv_clustered(seed: int, B: int, Hq: int, Hkv: int, S: int, D: int, Sq: int = 1,
+                  n_clusters: int = 64, sigma: float = 0.3):
+    """Keys and values drawn around `n_clusters` unit-variance Gaussian centres."""
+    centres_k = _rng(seed, 7).standard_normal((B, Hkv, n_clusters, D), dtype=np.float32)
+    centres_v = _rng(seed, 8).standard_normal((B, Hkv, n_clusters, D), dtype=np.float32)
+    assign = _rng(seed, 9).integers(0, n_clusters, size=(B, Hkv, S))
+    bi = np.arange(B)[:, None, None]
+    hi = np.arange(Hkv)[None, :, None]
+    k = centres_k[bi, hi, assign] + sigma * _rng(seed, 1).standard_normal((B, Hkv, S, D), dtype=np.float32)
+    v = centres_v[bi, hi, assign] + sigma * _rng(seed, 2).standard_normal((B, Hkv, S, D), dtype=np.float32)
+    q = _rng(seed, 0).standard_normal((B, Hq, Sq, D), dtype=np.float32)
+    return q, k.astype(np.float32), v.astype(np.float32)
+
+
+def hat_weights(seed: int, n_heads: int, head_dim: int, hidden: int, bits: int,
+                n_layers: int = 3) -> Dict[str, List[np.ndarray]]:
+    """Random-init hash MLPs, query and key sides separate: weights N(0, 1/fan_in)
+    as `[heads, in, out]`, zero biases `[heads, out]`."""
+    dims = [head_dim] + [hidden] * (n_layers - 1) + [bits]
+    out: Dict[str, List[np.ndarray]] = {"query_matrix": [], "query_bias": [],
+                                        "key_matrix": [], "key_bias": []}
+    for side, base in (("query", 20), ("key", 40)):
+        for l in range(n_layers):
+            w = _rng(seed, base + l).standard_normal((n_heads, dims[l], dims[l + 1]), dtype=np.float32)
+            out[f"{side}_matrix"].append((w / np.sqrt(dims[l])).astype(np.float32))
+            out[f"{side}_bias"].append(np.zeros((n_heads, dims[l + 1]), np.float32))
+    return out
+
+
+def to_dtype(x: np.ndarray, dtype: str) -> np.ndarray:
+    """Round float32 values to the compute dtype's grid (still stored as float32)."""
+    if dtype == "f32":
+        return np.asarray(x, np.float32)
+    f = np.ascontiguousarray(x, dtype=np.float32)
+    u = f.view(np.uint32).astype(np.uint64)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint32) << 16
+    return r.view(np.float32).reshape(f.shape)
+
+
+# ---------------------------------------------------------------------------
+# The benchmark configurations (full size by default; `scale` shrinks S and B
+# for parity tests).
+# ---------------------------------------------------------------------------
+def sink_local_fp32(seed: int = 0, B: int = 1, Hq: int = 32, Hkv: int = 8, S: int = 4096,
+                    D: int = 128, sink: int = 128, window: int = 256, Sq: int = 1) -> DecodeWorkload:
+    q, k, v = qkv_iid_outliers(seed, B, Hq, Hkv, S, D, Sq)
+    return DecodeWorkload("sink_local_fp32", "f32", q, k, v, 1.0 / np.sqrt(D),
+                          [("sink", {"sink_size": sink}), ("local", {"window_size": window})])
+
+
+def hashattention_bf16(seed: int = 0, B: int = 8, Hq: int = 32, Hkv: int = 8, S: int = 32768,
+                       D: int = 128, sink: int = 128, window: int = 512, heavy=0.05,
+                       bits: int = 32, hidden: int = 128, layers: int = 3,
+                       activation: str = "silu", Sq: int = 1) -> DecodeWorkload:
+    q, k, v = qkv_planted(seed, B, Hq, Hkv, S, D, Sq)
+    w = {n: [to_dtype(a, "bf16") for a in arrs]
+         for n, arrs in hat_weights(seed, Hq, D, hidden, bits, layers).items()}
+    return DecodeWorkload(
+        "hashattention_bf16", "bf16", to_dtype(q, "bf16"), to_dtype(k, "bf16"), to_dtype(v, "bf16"),
+        1.0 / np.sqrt(D),
+        [("sink", {"sink_size": sink}), ("local", {"window_size": window}),
+         ("hash_topk", {"heavy_size": heavy, "bits": bits, "hidden": hidden, "layers": layers,
+                        "activation": activation, "weights": w})])
+
+
+def oracle_topk(seed: int = 0, dtype: str = "bf16", B: int = 4, Hq: int = 32, Hkv: int = 8,
+                S: int = 65536, D: int = 128, sink: int = 128, window: int = 512, heavy=0.02,
+                Sq: int = 1) -> DecodeWorkload:
+    q, k, v = qkv_clustered(seed, B, Hq, Hkv, S, D, Sq)
+    return DecodeWorkload(
+        "oracle_topk_" + dtype, dtype, to_dtype(q, dtype), to_dtype(k, dtype), to_dtype(v, dtype),
+        1.0 / np.sqrt(D),
+        [("sink", {"sink_size": sink}), ("local", {"window_size": window}),
+         ("oracle_topk", {"heavy_size": heavy})])
