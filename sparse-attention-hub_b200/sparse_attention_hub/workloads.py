@@ -151,3 +151,51 @@ def oracle_topk(seed: int = 0, dtype: str = "bf16", B: int = 4, Hq: int = 32, Hk
         1.0 / np.sqrt(D),
         [("sink", {"sink_size": sink}), ("local", {"window_size": window}),
          ("oracle_topk", {"heavy_size": heavy})])
+
+
+# ---------------------------------------------------------------------------
+# Turning a workload into device tensors and masker configs
+# ---------------------------------------------------------------------------
+def torch_dtype(dtype: str):
+    import torch
+
+    return {"f32": torch.float32, "bf16": torch.bfloat16}[dtype]
+
+
+def to_torch(x: np.ndarray, dtype: str, device):
+    import torch
+
+    return torch.from_numpy(np.ascontiguousarray(x, dtype=np.float32)).to(device=device, dtype=torch_dtype(dtype))
+
+
+def masker_configs(stack: List[Tuple[str, Dict[str, Any]]], dtype: str, device="cpu") -> list:
+    """Config dataclasses of `sparse_attention_hub` for a stack description."""
+    from .sparse_attention.research_attention.maskers import fixed
+
+    out = []
+    for kind, prm in stack:
+        if kind == "sink":
+            out.append(fixed.SinkMaskerConfig(sink_size=prm["sink_size"]))
+        elif kind == "local":
+            out.append(fixed.LocalMaskerConfig(window_size=prm["window_size"]))
+        elif kind == "oracle_topk":
+            out.append(fixed.OracleTopKConfig(heavy_size=prm["heavy_size"]))
+        elif kind == "hash_topk":
+            w = {0: {name: [to_torch(a, dtype, device) for a in arrs]
+                     for name, arrs in prm["weights"].items()}}
+            out.append(fixed.HashAttentionTopKMaskerConfig(
+                heavy_size=prm["heavy_size"], hat_bits=prm["bits"], hat_mlp_layers=prm["layers"],
+                hat_mlp_hidden_size=prm["hidden"], hat_mlp_activation=prm["activation"],
+                hat_weights=w))
+        else:
+            from . import workloads_extra
+
+            out.append(workloads_extra.masker_config(kind, prm, dtype, device))
+    return out
+
+
+def research_attention(stack, dtype: str, device="cpu"):
+    from .sparse_attention.research_attention import ResearchAttention, ResearchAttentionConfig
+
+    return ResearchAttention.create_from_config(
+        ResearchAttentionConfig(masker_configs=masker_configs(stack, dtype, device)))
