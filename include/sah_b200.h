@@ -59,6 +59,20 @@ typedef enum {
 const char* sah_version(void);
 const char* sah_last_error(void);
 
+/* Number of kernels this library has launched in the process so far. */
+long long sah_launch_count(void);
+
+/* Optional per-kernel device timing, off by default.  While enabled, the
+ * kernels named by a slot are bracketed by CUDA events on the launching
+ * stream (0 gather attention, 1 hash top-k, 2 hash encode, 3 q.k scores,
+ * 4 generic top-k, 5 attention plan, 6 split merge).  sah_profile_read waits
+ * for the recorded events of one slot, returns their summed duration and
+ * count, and forgets them.  This mirrors what the reference's timing harness
+ * does around whole calls with torch.cuda.synchronize
+ * (profile/profile_research_attention.py:294-330), at kernel granularity. */
+int sah_profile_enable(int on);
+int sah_profile_read(int slot, float* total_ms, int* launches);
+
 /* ------------------------------------------------------------------------ *
  * Mask container kernels
  * ------------------------------------------------------------------------ */

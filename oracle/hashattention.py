@@ -74,6 +74,24 @@ def mlp_outputs(x, mats, biases, act: str, dtype: str) -> np.ndarray:
     return h
 
 
+def signatures_blas(x, mats, biases, act: str, dtype: str) -> np.ndarray:
+    """Same MLP with float32 BLAS products (summation order left to the BLAS, as in the
+    reference).  Used only to set up timing runs at sizes where the ordered loop of
+    `mlp_outputs` is too slow; parity checks use `signatures`."""
+    h = np.asarray(x, np.float32)
+    for l, (W, b) in enumerate(zip(mats, biases)):
+        Wf = np.asarray(W, np.float32)
+        y = np.empty(h.shape[:-1] + (Wf.shape[-1],), np.float32)
+        for hh in range(Wf.shape[0]):
+            y[:, hh] = h[:, hh] @ Wf[hh]
+        y = round_to(y, dtype)
+        y = round_to(y + np.asarray(b, np.float32)[None, :, None, :], dtype)
+        if l < len(mats) - 1:
+            y = _activate(y, act, dtype)
+        h = y
+    return pack_signs(h)
+
+
 def pack_signs(y: np.ndarray) -> np.ndarray:
     """bit e = 1 where output e > 0 (sign == +1); uint32 per vector."""
     bits = (y > 0).astype(np.uint32)

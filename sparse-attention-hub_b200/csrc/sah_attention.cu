@@ -186,6 +186,7 @@ extern "C" int sah_attn_plan(const uint32_t* bits, const void* data, const int32
   const int threads = 256;
   const int64_t blocks = sah_ceil_div(warps * 32, threads);
   cudaStream_t st = (cudaStream_t)stream;
+  sah_prof_begin(SAH_PROF_ATTN_PLAN, (cudaStream_t)stream);
   attn_plan_count_kernel<<<(unsigned)blocks, threads, 0, st>>>(bits, p, chunkcnt);
   SAH_LAUNCH_CHECK("attn_plan_count");
   SAH_DISPATCH_DTYPE(dtype, T, {
@@ -193,6 +194,7 @@ extern "C" int sah_attn_plan(const uint32_t* bits, const void* data, const int32
         bits, (const T*)data, wpre, ptr, p, chunkcnt, ucols, umemb, data ? uw : nullptr, ucount);
   });
   SAH_LAUNCH_CHECK("attn_plan_emit");
+  sah_prof_end(SAH_PROF_ATTN_PLAN, (cudaStream_t)stream);
   return SAH_OK;
 }
 
@@ -644,6 +646,7 @@ extern "C" int sah_masked_attention(const void* q, const void* k, const void* v,
                   a.R <= AT_MAXR && a.nsplit >= 1,
               "masked_attention: sizes do not match the extents");
   cudaStream_t st = (cudaStream_t)stream;
+  sah_prof_begin(SAH_PROF_ATTENTION, (cudaStream_t)stream);
   int rc = SAH_OK;
   if (dtype == SAH_BF16) {
     rc = (D == 128) ? launch_attention<__nv_bfloat16, 128>(a, groups, st)
@@ -656,6 +659,8 @@ extern "C" int sah_masked_attention(const void* q, const void* k, const void* v,
   }
   if (rc != SAH_OK) return rc;
   SAH_LAUNCH_CHECK("masked_attention");
+  sah_prof_end(SAH_PROF_ATTENTION, (cudaStream_t)stream);
+  sah_prof_begin(SAH_PROF_ATTN_MERGE, (cudaStream_t)stream);
   const int mthreads = D;
   SAH_DISPATCH_DTYPE(dtype, T, {
     attn_merge_splits_kernel<T><<<(unsigned)(groups * a.R), mthreads, 0, st>>>(
@@ -663,6 +668,7 @@ extern "C" int sah_masked_attention(const void* q, const void* k, const void* v,
         lse_out);
   });
   SAH_LAUNCH_CHECK("attn_merge_splits");
+  sah_prof_end(SAH_PROF_ATTN_MERGE, (cudaStream_t)stream);
   return SAH_OK;
 }
 

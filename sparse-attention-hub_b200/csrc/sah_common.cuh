@@ -140,3 +140,29 @@ __device__ __forceinline__ V sah_block_excl_scan(V c, V* scratch, V* total) {
       return sah_fail(SAH_ERR_INVALID, "unknown dtype %d", (int)(dtype)); \
     }                                                                  \
   } while (0)
+
+// ---- launch accounting and optional per-kernel event timing -------------------
+// Slots name the kernels whose device time a caller may want in isolation.
+enum SahProfSlot {
+  SAH_PROF_ATTENTION = 0,
+  SAH_PROF_HASH_TOPK = 1,
+  SAH_PROF_HASH_ENCODE = 2,
+  SAH_PROF_QK_SCORES = 3,
+  SAH_PROF_TOPK_SELECT = 4,
+  SAH_PROF_ATTN_PLAN = 5,
+  SAH_PROF_ATTN_MERGE = 6,
+  SAH_PROF_OTHER = 7,
+  SAH_PROF_SLOTS = 16
+};
+void sah_prof_begin(int slot, cudaStream_t st);
+void sah_prof_end(int slot, cudaStream_t st);
+void sah_count_launch();
+
+#undef SAH_LAUNCH_CHECK
+#define SAH_LAUNCH_CHECK(name)                                                     \
+  do {                                                                             \
+    sah_count_launch();                                                            \
+    cudaError_t e__ = cudaGetLastError();                                          \
+    if (e__ != cudaSuccess)                                                        \
+      return sah_fail(SAH_ERR_CUDA, "%s: %s", name, cudaGetErrorString(e__));      \
+  } while (0)

@@ -207,6 +207,7 @@ extern "C" int sah_hash_encode(const void* x, int dtype, int64_t xs_b, int64_t x
   const size_t smem = (size_t)(2 * HE_MAXD * HE_TK + HE_MAXD * HE_MAXD) * sizeof(float);
   dim3 grid((unsigned)sah_ceil_div(n_end - n_begin, HE_TK), (unsigned)H_out, (unsigned)B);
   cudaStream_t st = (cudaStream_t)stream;
+  sah_prof_begin(SAH_PROF_HASH_ENCODE, (cudaStream_t)stream);
   SAH_DISPATCH_DTYPE(dtype, T, {
     cudaError_t e = cudaFuncSetAttribute(hash_encode_kernel<T>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -214,6 +215,7 @@ extern "C" int sah_hash_encode(const void* x, int dtype, int64_t xs_b, int64_t x
     hash_encode_kernel<T><<<grid, HE_THREADS, smem, st>>>(p);
   });
   SAH_LAUNCH_CHECK("hash_encode");
+  sah_prof_end(SAH_PROF_HASH_ENCODE, (cudaStream_t)stream);
   return SAH_OK;
 }
 
@@ -279,6 +281,7 @@ extern "C" int sah_hash_topk(const uint32_t* kcodes, int64_t kc_stride, const ui
   SAH_REQUIRE(B > 0 && Hq > 0 && Sq > 0 && S > 0 && W * 32 >= S, "hash_topk: bad extents");
   const int64_t rows = (int64_t)B * Hq * Sq;
   cudaStream_t st = (cudaStream_t)stream;
+  sah_prof_begin(SAH_PROF_HASH_TOPK, (cudaStream_t)stream);
   if (bias == nullptr) {
     hash_topk_kernel<float, 8, false><<<(unsigned)rows, SAH_SELECT_THREADS, 0, st>>>(
         kcodes, kc_stride, qcodes, nbits, nullptr, 0, 0, 0, Hq, Sq, S, W, prev_bits, k, out_bits);
@@ -294,5 +297,6 @@ extern "C" int sah_hash_topk(const uint32_t* kcodes, int64_t kc_stride, const ui
     return sah_fail(SAH_ERR_INVALID, "hash_topk: unknown dtype %d", dtype);
   }
   SAH_LAUNCH_CHECK("hash_topk");
+  sah_prof_end(SAH_PROF_HASH_TOPK, (cudaStream_t)stream);
   return SAH_OK;
 }

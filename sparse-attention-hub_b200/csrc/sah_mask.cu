@@ -21,6 +21,63 @@ int sah_fail(int status, const char* fmt, ...) {
 extern "C" const char* sah_last_error(void) { return g_sah_err; }
 extern "C" const char* sah_version(void) { return "sah_b200 0.1 (sm_100a)"; }
 
+// ---- launch accounting / per-kernel timing ---------------------------------------
+#include <atomic>
+#include <mutex>
+#include <vector>
+
+static std::atomic<long long> g_launches{0};
+static std::atomic<int> g_prof_on{0};
+static std::mutex g_prof_mu;
+struct ProfPair { cudaEvent_t a, b; };
+static std::vector<ProfPair> g_prof_events[SAH_PROF_SLOTS];
+static thread_local cudaEvent_t g_prof_open[SAH_PROF_SLOTS];
+
+void sah_count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+void sah_prof_begin(int slot, cudaStream_t st) {
+  if (!g_prof_on.load(std::memory_order_relaxed)) return;
+  cudaEvent_t e;
+  if (cudaEventCreate(&e) != cudaSuccess) return;
+  cudaEventRecord(e, st);
+  g_prof_open[slot] = e;
+}
+
+void sah_prof_end(int slot, cudaStream_t st) {
+  if (!g_prof_on.load(std::memory_order_relaxed) || g_prof_open[slot] == nullptr) return;
+  cudaEvent_t e;
+  if (cudaEventCreate(&e) != cudaSuccess) return;
+  cudaEventRecord(e, st);
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  g_prof_events[slot].push_back({g_prof_open[slot], e});
+  g_prof_open[slot] = nullptr;
+}
+
+extern "C" long long sah_launch_count(void) { return g_launches.load(); }
+
+extern "C" int sah_profile_enable(int on) {
+  g_prof_on.store(on ? 1 : 0);
+  return SAH_OK;
+}
+
+extern "C" int sah_profile_read(int slot, float* total_ms, int* launches) {
+  SAH_REQUIRE(slot >= 0 && slot < SAH_PROF_SLOTS && total_ms && launches, "profile_read: bad argument");
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  float sum = 0.f;
+  int n = 0;
+  for (auto& pr : g_prof_events[slot]) {
+    cudaEventSynchronize(pr.b);
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, pr.a, pr.b) == cudaSuccess) { sum += ms; ++n; }
+    cudaEventDestroy(pr.a);
+    cudaEventDestroy(pr.b);
+  }
+  g_prof_events[slot].clear();
+  *total_ms = sum;
+  *launches = n;
+  return SAH_OK;
+}
+
 // ---- band fill --------------------------------------------------------------
 __global__ void mask_fill_band_kernel(uint32_t* __restrict__ bits, int64_t rows, int Sq,
                                       int64_t S, int64_t W, int64_t w_begin, int64_t w_count,

@@ -110,6 +110,7 @@ extern "C" int sah_qk_scores(const void* q, const void* k, int dtype, int64_t qs
     return sah_fail(SAH_ERR_UNSUPPORTED, "qk_scores: %d query rows per KV head do not fit", R);
   dim3 grid((unsigned)sah_ceil_div(S, QK_THREADS), (unsigned)Hkv, (unsigned)B);
   cudaStream_t st = (cudaStream_t)stream;
+  sah_prof_begin(SAH_PROF_QK_SCORES, (cudaStream_t)stream);
   SAH_DISPATCH_DTYPE(dtype, T, {
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(qk_scores_kernel<T>,
@@ -121,6 +122,7 @@ extern "C" int sah_qk_scores(const void* q, const void* k, int dtype, int64_t qs
         (const T*)bias, bias_s_b, bias_s_h, bias_s_q, (T*)scores);
   });
   SAH_LAUNCH_CHECK("qk_scores");
+  sah_prof_end(SAH_PROF_QK_SCORES, (cudaStream_t)stream);
   return SAH_OK;
 }
 
@@ -155,6 +157,7 @@ extern "C" int sah_topk_select(const void* scores, int dtype, int64_t rows, int6
   SAH_REQUIRE(rows >= 0 && S > 0 && W * 32 >= S, "topk_select: bad extents");
   if (rows == 0) return SAH_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  sah_prof_begin(SAH_PROF_TOPK_SELECT, (cudaStream_t)stream);
   if (dtype == SAH_BF16) {
     topk_select_kernel<__nv_bfloat16, 16><<<(unsigned)rows, SAH_SELECT_THREADS, 0, st>>>(
         (const __nv_bfloat16*)scores, S, W, col_begin, col_end, prev_bits, k, out_bits);
@@ -165,5 +168,6 @@ extern "C" int sah_topk_select(const void* scores, int dtype, int64_t rows, int6
     return sah_fail(SAH_ERR_INVALID, "topk_select: unknown dtype %d", dtype);
   }
   SAH_LAUNCH_CHECK("topk_select");
+  sah_prof_end(SAH_PROF_TOPK_SELECT, (cudaStream_t)stream);
   return SAH_OK;
 }

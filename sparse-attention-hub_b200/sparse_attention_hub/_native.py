@@ -82,9 +82,14 @@ _SIGNATURES = {
                              _L, _I, c_float, _P, _L, _L, _L, _P, POINTER(AttnSizes), _P, _P, _P,
                              _P, _P, _P, _P, _P, _P],
     "sah_attn_merge_parts": [_P, _P, _I, _I, _I, _I, _I, _P, _I, _P, _P],
+    "sah_profile_enable": [_I],
+    "sah_profile_read": [_I, POINTER(c_float), POINTER(c_int)],
 }
 
-EXPORTED_SYMBOLS = sorted(list(_SIGNATURES) + ["sah_version", "sah_last_error"])
+PROFILE_SLOTS = {"attention": 0, "hash_topk": 1, "hash_encode": 2, "qk_scores": 3,
+                 "topk_select": 4, "attn_plan": 5, "attn_merge": 6}
+
+EXPORTED_SYMBOLS = sorted(list(_SIGNATURES) + ["sah_version", "sah_last_error", "sah_launch_count"])
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -109,8 +114,27 @@ def load() -> ctypes.CDLL:
         fn.restype = c_int
     lib.sah_version.restype = c_char_p
     lib.sah_last_error.restype = c_char_p
+    lib.sah_launch_count.restype = ctypes.c_longlong
+    lib.sah_launch_count.argtypes = []
     _lib = lib
     return lib
+
+
+def launch_count() -> int:
+    """Kernels launched by the library in this process so far."""
+    return int(load().sah_launch_count())
+
+
+def profile_enable(on: bool) -> None:
+    check(load().sah_profile_enable(int(on)), "sah_profile_enable")
+
+
+def profile_read(slot: str):
+    """(total milliseconds, launches) recorded for a kernel slot since the last read."""
+    ms, n = c_float(0.0), c_int(0)
+    check(load().sah_profile_read(PROFILE_SLOTS[slot], ctypes.byref(ms), ctypes.byref(n)),
+          "sah_profile_read")
+    return float(ms.value), int(n.value)
 
 
 def check(status: int, what: str) -> None:

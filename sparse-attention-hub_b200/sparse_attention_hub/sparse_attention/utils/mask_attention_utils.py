@@ -152,9 +152,19 @@ def native_masked_attention(
             _native.ptr(acc), _native.ptr(lse), st),
         "sah_masked_attention")
     del keep
+    _last_plan["ucount"] = ws["ucount"][: sizes.groups]
     if return_partials:
         return out, acc, lse
     return out
+
+
+_last_plan: Dict[str, Optional[torch.Tensor]] = {"ucount": None}
+
+
+def last_union_counts() -> Optional[torch.Tensor]:
+    """int32 [groups]: distinct K/V rows the most recent attention call gathered per KV group
+    (valid once the launching stream has run; used for bandwidth accounting)."""
+    return _last_plan["ucount"]
 
 
 def merge_attention_partials(acc: torch.Tensor, lse: torch.Tensor, batch: int, heads: int,
