@@ -32,14 +32,18 @@ extern "C" int sah_attn_query_sizes(int B, int Hq, int Hkv, int Sq, int64_t S, i
   const int64_t groups = (int64_t)B * Hkv * nqb;
   SAH_REQUIRE(groups < (1ll << 30), "attn_query_sizes: too many groups");
   if (sm_count <= 0) sm_count = 148;
-  int64_t target = (int64_t)sm_count * 4;
-  int64_t nsplit = (target + groups - 1) / groups;
+  // Two resident CTAs per SM; the split count is rounded down so that the grid
+  // fills whole waves of 2 * sm_count CTAs instead of spilling into a short tail.
+  const int64_t slots = (int64_t)sm_count * 2;
+  int64_t waves = (groups + slots - 1) / slots;
+  if (waves < 2) waves = 2;
+  int64_t nsplit = (waves * slots) / groups;
   int64_t max_split = (S + 255) / 256;  // at least 256 columns of range per CTA
   if (nsplit > max_split) nsplit = max_split;
   if (nsplit > 256) nsplit = 256;
   if (nsplit < 1) nsplit = 1;
   const int R = G * q_block;
-  const int64_t nchunks = (((S + 31) / 32) + PLAN_CHUNK_WORDS - 1) / PLAN_CHUNK_WORDS;
+  const int64_t nchunks = (((S + 31) / 32 + 3) / 4 * 4 + PLAN_CHUNK_WORDS - 1) / PLAN_CHUNK_WORDS;
   out->groups = (int32_t)groups;
   out->q_block = q_block;
   out->rows_per_group = R;
@@ -47,7 +51,8 @@ extern "C" int sah_attn_query_sizes(int B, int Hq, int Hkv, int Sq, int64_t S, i
   out->ucols_bytes = groups * S * (int64_t)sizeof(int32_t);
   out->umemb_bytes = groups * S * (int64_t)sizeof(uint16_t);
   out->uw_bytes = has_data ? groups * S * R * (int64_t)sizeof(float) : 0;
-  out->ucount_bytes = (groups + groups * nchunks) * (int64_t)sizeof(int32_t);
+  // [groups] union counts, [groups][nchunks] chunk counts, [groups] merge tickets
+  out->ucount_bytes = (2 * groups + groups * nchunks) * (int64_t)sizeof(int32_t);
   out->partial_bytes = groups * nsplit * R * (int64_t)(D + 2) * (int64_t)sizeof(float);
   return SAH_OK;
 }
@@ -91,6 +96,62 @@ __global__ void attn_plan_count_kernel(const uint32_t* __restrict__ bits, PlanGe
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
   if (lane == 0) chunkcnt[g * p.nchunks + c] = cnt;
+}
+
+// Short rows (W <= 1024 words, i.e. up to 32768 keys): one CTA per group, one
+// bitmap word per thread, a single ordered block scan places every word's
+// entries; no second kernel and no chunk counters.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+attn_plan_fused_kernel(const uint32_t* __restrict__ bits, const T* __restrict__ data,
+                       const int32_t* __restrict__ wpre, const int64_t* __restrict__ ptr,
+                       PlanGeom p, int32_t* __restrict__ ucols, uint16_t* __restrict__ umemb,
+                       float* __restrict__ uw, int32_t* __restrict__ ucount) {
+  __shared__ int scan[33];
+  const int64_t g = blockIdx.x;
+  const int64_t w = threadIdx.x;
+  uint32_t words[AT_MAXR];
+  int64_t rows[AT_MAXR];
+  uint32_t u = 0u;
+#pragma unroll
+  for (int r = 0; r < AT_MAXR; ++r) {
+    words[r] = 0u;
+    rows[r] = -1;
+    if (r < p.R && w < p.W) {
+      rows[r] = plan_member_row(p, g, r);
+      if (rows[r] >= 0) words[r] = bits[rows[r] * p.W + w];
+    }
+    u |= words[r];
+  }
+  int total;
+  const int before = sah_block_excl_scan<int>(__popc(u), scan, &total);
+  int64_t pos = (int64_t)g * p.S + before;
+  uint32_t m = u;
+  while (m) {
+    const int b = __ffs(m) - 1;
+    m &= m - 1;
+    unsigned int memb = 0u;
+#pragma unroll
+    for (int r = 0; r < AT_MAXR; ++r) memb |= ((words[r] >> b) & 1u) << r;
+    ucols[pos] = (int32_t)(w * 32 + b);
+    umemb[pos] = (uint16_t)memb;
+    if (uw != nullptr) {
+#pragma unroll
+      for (int r = 0; r < AT_MAXR; ++r) {
+        if (r < p.R) {
+          float wv = 0.f;
+          if ((memb >> r) & 1u) {
+            int64_t dp = ptr[rows[r]] + wpre[rows[r] * p.W + w] +
+                         __popc(words[r] & ((1u << b) - 1u));
+            wv = sah_inv_weight<T>(sah_to_float<T>(data[dp]));
+          }
+          uw[pos * p.R + r] = wv;
+        }
+      }
+    }
+    ++pos;
+  }
+  if (threadIdx.x == 0) ucount[g] = total;
 }
 
 template <typename T>
@@ -187,6 +248,15 @@ extern "C" int sah_attn_plan(const uint32_t* bits, const void* data, const int32
   const int64_t blocks = sah_ceil_div(warps * 32, threads);
   cudaStream_t st = (cudaStream_t)stream;
   sah_prof_begin(SAH_PROF_ATTN_PLAN, (cudaStream_t)stream);
+  if (W <= 1024) {
+    SAH_DISPATCH_DTYPE(dtype, T, {
+      attn_plan_fused_kernel<T><<<(unsigned)groups, 1024, 0, st>>>(
+          bits, (const T*)data, wpre, ptr, p, ucols, umemb, data ? uw : nullptr, ucount);
+    });
+    SAH_LAUNCH_CHECK("attn_plan_fused");
+    sah_prof_end(SAH_PROF_ATTN_PLAN, (cudaStream_t)stream);
+    return SAH_OK;
+  }
   attn_plan_count_kernel<<<(unsigned)blocks, threads, 0, st>>>(bits, p, chunkcnt);
   SAH_LAUNCH_CHECK("attn_plan_count");
   SAH_DISPATCH_DTYPE(dtype, T, {
@@ -241,6 +311,8 @@ struct AttnCfg {
   static constexpr int DPL = D / 32;                     // output dims per lane in PV
   static constexpr int STAGE_BYTES = 2 * TILE * ROWB;    // K tile + V tile
 };
+
+#include "sah_attention_mma.cuh"
 
 template <typename T, int D, int NQUAD>
 __global__ void __launch_bounds__(AT_THREADS)
@@ -649,24 +721,26 @@ extern "C" int sah_masked_attention(const void* q, const void* k, const void* v,
   sah_prof_begin(SAH_PROF_ATTENTION, (cudaStream_t)stream);
   int rc = SAH_OK;
   if (dtype == SAH_BF16) {
-    rc = (D == 128) ? launch_attention<__nv_bfloat16, 128>(a, groups, st)
-                    : launch_attention<__nv_bfloat16, 64>(a, groups, st);
-  } else if (dtype == SAH_F32) {
-    rc = (D == 128) ? launch_attention<float, 128>(a, groups, st)
-                    : launch_attention<float, 64>(a, groups, st);
-  } else {
-    return sah_fail(SAH_ERR_INVALID, "masked_attention: unknown dtype %d", dtype);
+    // tensor-core path; the split merge is fused into the kernel (ticket per group)
+    const int64_t nchunks = (((S + 31) / 32 + 3) / 4 * 4 + PLAN_CHUNK_WORDS - 1) / PLAN_CHUNK_WORDS;
+    int* tickets = const_cast<int*>(ucount) + groups + (int64_t)groups * nchunks;
+    rc = (D == 128) ? launch_attention_mma<128>(a, groups, tickets, sinks, out, acc_out, lse_out, st)
+                    : launch_attention_mma<64>(a, groups, tickets, sinks, out, acc_out, lse_out, st);
+    if (rc != SAH_OK) return rc;
+    SAH_LAUNCH_CHECK("masked_attention_mma");
+    sah_prof_end(SAH_PROF_ATTENTION, (cudaStream_t)stream);
+    return SAH_OK;
   }
+  if (dtype != SAH_F32) return sah_fail(SAH_ERR_INVALID, "masked_attention: unknown dtype %d", dtype);
+  rc = (D == 128) ? launch_attention<float, 128>(a, groups, st)
+                  : launch_attention<float, 64>(a, groups, st);
   if (rc != SAH_OK) return rc;
   SAH_LAUNCH_CHECK("masked_attention");
   sah_prof_end(SAH_PROF_ATTENTION, (cudaStream_t)stream);
   sah_prof_begin(SAH_PROF_ATTN_MERGE, (cudaStream_t)stream);
-  const int mthreads = D;
-  SAH_DISPATCH_DTYPE(dtype, T, {
-    attn_merge_splits_kernel<T><<<(unsigned)(groups * a.R), mthreads, 0, st>>>(
-        partial, a.nsplit, a.R, D, Hq, Hkv, Sq, a.G, a.q_block, a.nqb, sinks, (T*)out, acc_out,
-        lse_out);
-  });
+  attn_merge_splits_kernel<float><<<(unsigned)(groups * a.R), D, 0, st>>>(
+      partial, a.nsplit, a.R, D, Hq, Hkv, Sq, a.G, a.q_block, a.nqb, sinks, (float*)out, acc_out,
+      lse_out);
   SAH_LAUNCH_CHECK("attn_merge_splits");
   sah_prof_end(SAH_PROF_ATTN_MERGE, (cudaStream_t)stream);
   return SAH_OK;

@@ -161,6 +161,61 @@ hash_encode_kernel(HashEncodeArgs p) {
   }
 }
 
+// Few vectors per head (a decode step hashes one query and at most a few new
+// keys): one CTA per vector, thread e owns output e of the current layer and
+// walks the input channels in the same ascending order as the tiled kernel, so
+// both produce identical bits.  Weight reads are coalesced across outputs.
+#define HE_SMALL_MAX 16
+
+__device__ __forceinline__ void he_cp_async16(void* smem_dst, const void* gmem_src) {
+  unsigned int d = (unsigned int)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gmem_src));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(HE_MAXD)
+hash_encode_small_kernel(HashEncodeArgs p) {
+  extern __shared__ __align__(16) unsigned char hes_smem[];  // one layer's weights of head h
+  T* w_sm = reinterpret_cast<T*>(hes_smem);
+  __shared__ float xa[HE_MAXD];
+  __shared__ float xb[HE_MAXD];
+  const int64_t n = p.n_begin + blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int h_in = h / (p.H_out / p.H_in);
+  const int e = threadIdx.x;
+  const T* xr = reinterpret_cast<const T*>(p.x) + b * p.xs_b + h_in * p.xs_h + n * p.xs_n;
+  if (e < p.dims[0]) xa[e] = sah_to_float<T>(xr[e]);
+  float* a_in = xa;
+  float* a_out = xb;
+  unsigned int code = 0u;
+  for (int l = 0; l < p.n_layers; ++l) {
+    const int din = p.dims[l], dout = p.dims[l + 1];
+    const bool last = (l == p.n_layers - 1);
+    __syncthreads();  // previous layer finished with w_sm and wrote a_in
+    // the whole layer matrix in flight at once: the step is latency bound
+    const unsigned char* src = reinterpret_cast<const unsigned char*>(
+        reinterpret_cast<const T*>(p.weights[l]) + (int64_t)h * din * dout);
+    const int n16 = din * dout * (int)sizeof(T) / 16;
+    for (int i = threadIdx.x; i < n16; i += HE_MAXD) he_cp_async16(hes_smem + i * 16, src + i * 16);
+    asm volatile("cp.async.commit_group;\n" ::);
+    asm volatile("cp.async.wait_group 0;\n" ::);
+    __syncthreads();
+    float v = 0.f;
+    if (e < dout) {
+      float acc = 0.f;
+#pragma unroll 8
+      for (int d = 0; d < din; ++d) acc = fmaf(a_in[d], sah_to_float<T>(w_sm[d * dout + e]), acc);
+      v = sah_round_to<T>(acc);
+      v = sah_round_to<T>(__fadd_rn(
+          v, sah_to_float<T>(reinterpret_cast<const T*>(p.bias[l])[(int64_t)h * dout + e])));
+      if (!last) a_out[e] = he_activate<T>(v, p.act, p.act_table);
+    }
+    if (last && threadIdx.x < 32) code = __ballot_sync(0xffffffffu, e < dout && v > 0.f);
+    float* t = a_in; a_in = a_out; a_out = t;
+  }
+  if (threadIdx.x == 0) p.codes[((int64_t)b * p.H_out + h) * p.n_total + n] = code;
+}
+
 extern "C" int sah_hash_encode(const void* x, int dtype, int64_t xs_b, int64_t xs_h,
                                int64_t xs_n, int B, int H_in, int H_out, int64_t n_begin,
                                int64_t n_end, int64_t n_total, int n_layers, const int* dims,
@@ -204,9 +259,28 @@ extern "C" int sah_hash_encode(const void* x, int dtype, int64_t xs_b, int64_t x
   }
   p.act = act; p.act_table = act_table; p.codes = codes;
 
+  cudaStream_t st = (cudaStream_t)stream;
+  if (n_end - n_begin <= HE_SMALL_MAX) {
+    // decode-time shapes (queries, appended keys): one CTA per vector
+    sah_prof_begin(SAH_PROF_HASH_ENCODE, st);
+    dim3 sgrid((unsigned)(n_end - n_begin), (unsigned)H_out, (unsigned)B);
+    SAH_DISPATCH_DTYPE(dtype, T, {
+      const int wbytes = HE_MAXD * HE_MAXD * (int)sizeof(T);
+      if (wbytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(hash_encode_small_kernel<T>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, wbytes);
+        if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "hash_encode attr: %s", cudaGetErrorString(e));
+      }
+      for (int l = 0; l < n_layers; ++l)
+        SAH_REQUIRE(((uintptr_t)weights[l] % 16) == 0, "hash_encode: weights must be 16-byte aligned");
+      hash_encode_small_kernel<T><<<sgrid, HE_MAXD, wbytes, st>>>(p);
+    });
+    SAH_LAUNCH_CHECK("hash_encode_small");
+    sah_prof_end(SAH_PROF_HASH_ENCODE, st);
+    return SAH_OK;
+  }
   const size_t smem = (size_t)(2 * HE_MAXD * HE_TK + HE_MAXD * HE_MAXD) * sizeof(float);
   dim3 grid((unsigned)sah_ceil_div(n_end - n_begin, HE_TK), (unsigned)H_out, (unsigned)B);
-  cudaStream_t st = (cudaStream_t)stream;
   sah_prof_begin(SAH_PROF_HASH_ENCODE, (cudaStream_t)stream);
   SAH_DISPATCH_DTYPE(dtype, T, {
     cudaError_t e = cudaFuncSetAttribute(hash_encode_kernel<T>,
@@ -269,6 +343,137 @@ hash_topk_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
   }
 }
 
+// Counting select for the unbiased case: a score takes at most nbits + 1
+// values, so the k-th best score and the number of ties to take at it follow
+// from one histogram.  Each thread owns one bitmap word, i.e. 32 consecutive
+// keys (128 contiguous bytes of codes, read with 16-byte loads, all of them in
+// flight before the first use).  Pass 1 histograms the inactive keys (per-warp
+// shared-memory bins); pass 2 re-reads the codes (cache resident) and emits
+// the word: keys above the threshold, plus ties in column order through one
+// ordered block scan.
+#define HT_BINS 40  // >= nbits + 1, padded
+
+__device__ __forceinline__ void ht_load_codes(const uint32_t* __restrict__ kc, int64_t w, int64_t S,
+                                              bool aligned, uint32_t* codes) {
+  const int64_t c0 = w * 32;
+  if (aligned && c0 + 32 <= S) {
+    const uint4* p = reinterpret_cast<const uint4*>(kc + c0);
+    uint4 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = p[i];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      codes[4 * i + 0] = v[i].x; codes[4 * i + 1] = v[i].y;
+      codes[4 * i + 2] = v[i].z; codes[4 * i + 3] = v[i].w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) codes[i] = (c0 + i < S) ? kc[c0 + i] : 0u;
+  }
+}
+
+__global__ void __launch_bounds__(1024)
+hash_topk_fast_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
+                      const uint32_t* __restrict__ qcodes, int nbits, int Sq, int64_t S, int64_t W,
+                      const uint32_t* __restrict__ prev_bits, int64_t k,
+                      uint32_t* __restrict__ out_bits) {
+  __shared__ unsigned int hist[32][HT_BINS];
+  __shared__ long long scan[33];
+  __shared__ int thr_sm;
+  __shared__ long long need_sm;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t row = blockIdx.x;
+  const uint32_t* kc = kcodes + (row / Sq) * kc_stride;  // codes are shared by a head's queries
+  const uint32_t qc = qcodes[row];
+  const uint32_t* prev_row = prev_bits + row * W;
+  uint32_t* out_row = out_bits + row * W;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(kc) & 15) == 0);
+
+  for (int i = tid; i < 32 * HT_BINS; i += 1024) (&hist[0][0])[i] = 0u;
+  __syncthreads();
+
+  // ---- pass 1: histogram of matching-bit counts over inactive keys ----
+  for (int64_t w = tid; w < W; w += 1024) {
+    uint32_t codes[32];
+    ht_load_codes(kc, w, S, aligned, codes);
+    const uint32_t pw = prev_row[w];
+    const int64_t c0 = w * 32;
+    uint32_t valid = ~pw;
+    if (c0 + 32 > S) valid &= (c0 >= S) ? 0u : ((1u << (S - c0)) - 1u);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if ((valid >> i) & 1u) atomicAdd(&hist[warp][nbits - __popc(codes[i] ^ qc)], 1u);
+    }
+  }
+  __syncthreads();
+  if (warp == 0) {
+    // lane b owns bin b (b = 0..31); bin 32 (all bits match) is handled aside
+    unsigned int mine = 0u, top = 0u;
+    for (int w2 = 0; w2 < 32; ++w2) {
+      mine += hist[w2][lane];
+      top += hist[w2][32];
+    }
+    unsigned int incl = mine;  // suffix sum over lanes: keys with bin >= lane (bins <= 31)
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      unsigned int n = __shfl_down_sync(0xffffffffu, incl, o);
+      if (lane + o < 32) incl += n;
+    }
+    const long long ge = (long long)incl + top;   // keys scoring >= this lane's bin
+    const long long total = __shfl_sync(0xffffffffu, (long long)incl, 0) + top;
+    int thr;
+    long long need;
+    if (k <= 0) {
+      thr = 64; need = 0;                 // nothing qualifies
+    } else if (total <= k) {
+      thr = -1; need = 0;                 // every candidate qualifies
+    } else if ((long long)top >= k) {
+      thr = 32; need = k;
+    } else {
+      const unsigned int ok = __ballot_sync(0xffffffffu, ge >= k);
+      thr = 31 - __clz(ok);               // highest bin whose ">=" count reaches k
+      const long long ge_thr = __shfl_sync(0xffffffffu, ge, thr);
+      const long long mine_thr = __shfl_sync(0xffffffffu, (long long)mine, thr);
+      need = k - (ge_thr - mine_thr);     // ties to take at the threshold
+    }
+    if (lane == 0) { thr_sm = thr; need_sm = need; }
+  }
+  __syncthreads();
+  const int thr = thr_sm;
+  const long long need = need_sm;
+
+  // ---- pass 2: emit ----
+  long long base = 0;
+  for (int64_t w0 = 0; w0 < W; w0 += 1024) {
+    const int64_t w = w0 + tid;
+    uint32_t gt = 0u, eq = 0u, pw = 0u;
+    if (w < W) {
+      uint32_t codes[32];
+      ht_load_codes(kc, w, S, aligned, codes);
+      pw = prev_row[w];
+      const int64_t c0 = w * 32;
+      uint32_t valid = ~pw;
+      if (c0 + 32 > S) valid &= (c0 >= S) ? 0u : ((1u << (S - c0)) - 1u);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int sc = nbits - __popc(codes[i] ^ qc);
+        gt |= (sc > thr ? 1u : 0u) << i;
+        eq |= (sc == thr ? 1u : 0u) << i;
+      }
+      gt &= valid;
+      eq &= valid;
+    }
+    long long total_eq;
+    const long long before = sah_block_excl_scan<long long>((long long)__popc(eq), scan, &total_eq);
+    if (w < W) {
+      const long long quota = need - (base + before);
+      const int take = quota > 32 ? 32 : (quota < 0 ? 0 : (int)quota);
+      out_row[w] = pw | gt | sah_lowest_bits(eq, take);
+    }
+    base += total_eq;
+  }
+}
+
 extern "C" int sah_hash_topk(const uint32_t* kcodes, int64_t kc_stride, const uint32_t* qcodes,
                              int nbits,
                              const void* bias, int dtype, int64_t bias_s_b, int64_t bias_s_h,
@@ -283,8 +488,8 @@ extern "C" int sah_hash_topk(const uint32_t* kcodes, int64_t kc_stride, const ui
   cudaStream_t st = (cudaStream_t)stream;
   sah_prof_begin(SAH_PROF_HASH_TOPK, (cudaStream_t)stream);
   if (bias == nullptr) {
-    hash_topk_kernel<float, 8, false><<<(unsigned)rows, SAH_SELECT_THREADS, 0, st>>>(
-        kcodes, kc_stride, qcodes, nbits, nullptr, 0, 0, 0, Hq, Sq, S, W, prev_bits, k, out_bits);
+    hash_topk_fast_kernel<<<(unsigned)rows, 1024, 0, st>>>(kcodes, kc_stride, qcodes, nbits, Sq, S,
+                                                          W, prev_bits, k, out_bits);
   } else if (dtype == SAH_BF16) {
     hash_topk_kernel<__nv_bfloat16, 16, true><<<(unsigned)rows, SAH_SELECT_THREADS, 0, st>>>(
         kcodes, kc_stride, qcodes, nbits, (const __nv_bfloat16*)bias, bias_s_b, bias_s_h, bias_s_q, Hq, Sq,

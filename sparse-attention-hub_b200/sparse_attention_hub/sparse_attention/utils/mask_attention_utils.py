@@ -64,7 +64,8 @@ def _workspace(device: torch.device, sizes: _native.AttnSizes, key: Tuple) -> Di
             "umemb": torch.empty(max(1, sizes.umemb_bytes // 2), dtype=torch.int16, device=device),
             "uw": (torch.empty(sizes.uw_bytes // 4, dtype=torch.float32, device=device)
                    if sizes.uw_bytes > 0 else None),
-            "ucount": torch.empty(max(1, sizes.ucount_bytes // 4), dtype=torch.int32, device=device),
+            # zero-filled once: it ends with the merge tickets, which the kernel keeps at zero
+            "ucount": torch.zeros(max(1, sizes.ucount_bytes // 4), dtype=torch.int32, device=device),
             "partial": torch.empty(max(1, sizes.partial_bytes // 4), dtype=torch.float32,
                                    device=device),
         }
