@@ -52,7 +52,8 @@ extern "C" int sah_attn_query_sizes(int B, int Hq, int Hkv, int Sq, int64_t S, i
   out->umemb_bytes = groups * S * (int64_t)sizeof(uint16_t);
   out->uw_bytes = has_data ? groups * S * R * (int64_t)sizeof(float) : 0;
   // [groups] union counts, [groups][nchunks] chunk counts, [groups] merge tickets
-  out->ucount_bytes = (2 * groups + groups * nchunks) * (int64_t)sizeof(int32_t);
+  // and one error word (non-zero after a bounded device-side wait ran out)
+  out->ucount_bytes = (2 * groups + groups * nchunks + 4) * (int64_t)sizeof(int32_t);
   out->partial_bytes = groups * nsplit * R * (int64_t)(D + 2) * (int64_t)sizeof(float);
   return SAH_OK;
 }
@@ -101,7 +102,7 @@ __global__ void attn_plan_count_kernel(const uint32_t* __restrict__ bits, PlanGe
 // Short rows (W <= 1024 words, i.e. up to 32768 keys): one CTA per group, one
 // bitmap word per thread, a single ordered block scan places every word's
 // entries; no second kernel and no chunk counters.
-template <typename T>
+template <typename T, int RMAX>
 __global__ void __launch_bounds__(1024)
 attn_plan_fused_kernel(const uint32_t* __restrict__ bits, const T* __restrict__ data,
                        const int32_t* __restrict__ wpre, const int64_t* __restrict__ ptr,
@@ -110,11 +111,11 @@ attn_plan_fused_kernel(const uint32_t* __restrict__ bits, const T* __restrict__ 
   __shared__ int scan[33];
   const int64_t g = blockIdx.x;
   const int64_t w = threadIdx.x;
-  uint32_t words[AT_MAXR];
-  int64_t rows[AT_MAXR];
+  uint32_t words[RMAX];
+  int64_t rows[RMAX];
   uint32_t u = 0u;
 #pragma unroll
-  for (int r = 0; r < AT_MAXR; ++r) {
+  for (int r = 0; r < RMAX; ++r) {
     words[r] = 0u;
     rows[r] = -1;
     if (r < p.R && w < p.W) {
@@ -132,12 +133,12 @@ attn_plan_fused_kernel(const uint32_t* __restrict__ bits, const T* __restrict__ 
     m &= m - 1;
     unsigned int memb = 0u;
 #pragma unroll
-    for (int r = 0; r < AT_MAXR; ++r) memb |= ((words[r] >> b) & 1u) << r;
+    for (int r = 0; r < RMAX; ++r) memb |= ((words[r] >> b) & 1u) << r;
     ucols[pos] = (int32_t)(w * 32 + b);
     umemb[pos] = (uint16_t)memb;
     if (uw != nullptr) {
 #pragma unroll
-      for (int r = 0; r < AT_MAXR; ++r) {
+      for (int r = 0; r < RMAX; ++r) {
         if (r < p.R) {
           float wv = 0.f;
           if ((memb >> r) & 1u) {
@@ -250,8 +251,12 @@ extern "C" int sah_attn_plan(const uint32_t* bits, const void* data, const int32
   sah_prof_begin(SAH_PROF_ATTN_PLAN, (cudaStream_t)stream);
   if (W <= 1024) {
     SAH_DISPATCH_DTYPE(dtype, T, {
-      attn_plan_fused_kernel<T><<<(unsigned)groups, 1024, 0, st>>>(
-          bits, (const T*)data, wpre, ptr, p, ucols, umemb, data ? uw : nullptr, ucount);
+      if (p.R <= 4)
+        attn_plan_fused_kernel<T, 4><<<(unsigned)groups, 1024, 0, st>>>(
+            bits, (const T*)data, wpre, ptr, p, ucols, umemb, data ? uw : nullptr, ucount);
+      else
+        attn_plan_fused_kernel<T, AT_MAXR><<<(unsigned)groups, 1024, 0, st>>>(
+            bits, (const T*)data, wpre, ptr, p, ucols, umemb, data ? uw : nullptr, ucount);
     });
     SAH_LAUNCH_CHECK("attn_plan_fused");
     sah_prof_end(SAH_PROF_ATTN_PLAN, (cudaStream_t)stream);
@@ -312,7 +317,7 @@ struct AttnCfg {
   static constexpr int STAGE_BYTES = 2 * TILE * ROWB;    // K tile + V tile
 };
 
-#include "sah_attention_mma.cuh"
+#include "sah_attention_tc.cuh"
 
 template <typename T, int D, int NQUAD>
 __global__ void __launch_bounds__(AT_THREADS)
@@ -724,8 +729,10 @@ extern "C" int sah_masked_attention(const void* q, const void* k, const void* v,
     // tensor-core path; the split merge is fused into the kernel (ticket per group)
     const int64_t nchunks = (((S + 31) / 32 + 3) / 4 * 4 + PLAN_CHUNK_WORDS - 1) / PLAN_CHUNK_WORDS;
     int* tickets = const_cast<int*>(ucount) + groups + (int64_t)groups * nchunks;
-    rc = (D == 128) ? launch_attention_mma<128>(a, groups, tickets, sinks, out, acc_out, lse_out, st)
-                    : launch_attention_mma<64>(a, groups, tickets, sinks, out, acc_out, lse_out, st);
+    int* errflag = tickets + groups;  // set when a bounded wait inside the kernel ran out
+    rc = (D == 128)
+             ? launch_attention_mma<128>(a, groups, tickets, errflag, sinks, out, acc_out, lse_out, st)
+             : launch_attention_mma<64>(a, groups, tickets, errflag, sinks, out, acc_out, lse_out, st);
     if (rc != SAH_OK) return rc;
     SAH_LAUNCH_CHECK("masked_attention_mma");
     sah_prof_end(SAH_PROF_ATTENTION, (cudaStream_t)stream);

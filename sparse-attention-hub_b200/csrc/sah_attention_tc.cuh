@@ -1,0 +1,636 @@
+// bf16 gather attention on the tensor cores.
+//
+// Every warp runs its own pipeline with no CTA-wide barrier in the main loop:
+// it takes 16-key tiles of the group's union list (tiles are dealt round-robin
+// to the warps of the CTAs that share the group) and gathers the 16 K rows and
+// 16 V rows with bulk asynchronous copies (cp.async.bulk, one whole-row copy
+// issued by one lane each, completion counted on an mbarrier) into a private
+// ring in shared memory.  Rows are padded by 16 bytes so that the 8 rows of an
+// ldmatrix tile fall into different banks.  Per tile:
+//     S[rows x 16 keys] = Q . K^T          mma.m16n8k16, Q fragments in registers
+//     P = exp(S * scaling + bias - m) * w  online softmax in the C fragment
+//     O[rows x D]      += P . V            mma.m16n8k16, V fragments via ldmatrix.trans
+// "rows" are the mask rows of one KV group (query heads x query block, zero
+// padded to 16, or to 8 when HALF), so each gathered K/V row is read once for
+// all of them.  At the end the warps of a CTA merge their (m, l, O) in shared
+// memory, the CTA writes its partial, and the last CTA of a group (atomic
+// ticket) merges the group's partials and writes the output.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out sets the error
+// word, the warp stops consuming tiles, and the kernel still goes through its
+// merge and ticket protocol so that no other CTA is left waiting.
+#pragma once
+
+#ifndef ATM_WARPS
+#define ATM_WARPS 4
+#endif
+#ifndef ATM_STAGES
+#define ATM_STAGES 3
+#endif
+#ifndef ATM_BULK
+#define ATM_BULK 0  // 1: one cp.async.bulk per row + mbarrier; 0: 16-byte cp.async per lane
+#endif
+#ifndef ATM_PF_DIST
+#define ATM_PF_DIST 0  // tiles of L2 prefetch distance beyond the shared-memory ring
+#endif
+#define ATM_THREADS (ATM_WARPS * 32)
+#define ATM_TILE 16
+#define ATM_SPIN_LIMIT (1 << 22)
+
+__device__ __forceinline__ void atm_ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                                uint32_t& r3, uint32_t saddr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(saddr));
+}
+__device__ __forceinline__ void atm_ldmatrix_x2(uint32_t& r0, uint32_t& r1, uint32_t saddr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n"
+               : "=r"(r0), "=r"(r1)
+               : "r"(saddr));
+}
+__device__ __forceinline__ void atm_ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                                      uint32_t& r3, uint32_t saddr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(saddr));
+}
+// D(16x8) += A(16x16) . B(16x8), all four accumulator registers live.
+__device__ __forceinline__ void atm_mma_full(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// Same product when rows 8..15 of A are zero: only the two registers of rows 0..7
+// are carried; the other half reads constant zeros and its result is dropped.
+__device__ __forceinline__ void atm_mma_half(float& c0, float& c1, uint32_t a0, uint32_t a2,
+                                             uint32_t b0, uint32_t b1) {
+  float j0, j1;
+  const uint32_t z = 0u;
+  const float zf = 0.f;
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%10,%11};\n"
+      : "+f"(c0), "+f"(c1), "=f"(j0), "=f"(j1)
+      : "r"(a0), "r"(z), "r"(a2), "r"(z), "r"(b0), "r"(b1), "f"(zf), "f"(zf));
+}
+__device__ __forceinline__ uint32_t atm_pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// ---- mbarrier / bulk copy ----------------------------------------------------
+__device__ __forceinline__ void atm_mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void atm_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool atm_mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0u;
+}
+// Bounded wait: false when the phase did not complete within the spin limit.
+__device__ __forceinline__ bool atm_mbar_wait(uint32_t bar, uint32_t parity) {
+  for (int i = 0; i < ATM_SPIN_LIMIT; ++i) {
+    if (atm_mbar_test(bar, parity)) return true;
+    if (i > 64) __nanosleep(40);
+  }
+  return false;
+}
+__device__ __forceinline__ void atm_bulk_g2s(uint32_t dst, const void* src, uint32_t bytes,
+                                             uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::
+          "r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void atm_cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
+
+__device__ __forceinline__ void atm_prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p));
+}
+
+template <int D>
+struct AtmCfg {
+  static constexpr int ROWB = D * 2;                        // bytes of one bf16 row
+  static constexpr int RSTR = ROWB + 16;                    // padded row stride in shared memory
+  static constexpr int KSTEPS = D / 16;                     // k-steps of Q.K^T
+  static constexpr int NT = D / 8;                          // n-tiles of the output
+  static constexpr int TILE_BYTES = ATM_TILE * RSTR;        // one K (or V) tile
+  static constexpr int STAGE_BYTES = 2 * TILE_BYTES;        // K tile + V tile
+  static constexpr int WARP_BYTES = ATM_STAGES * STAGE_BYTES;
+  static constexpr int Q_BYTES = 16 * RSTR;
+  static constexpr int RS = D + 8;                          // fp32 row stride of the reduction scratch
+  static constexpr int RED_BYTES = 16 * RS * 4 + 16 * 2 * 4;
+  static constexpr int META_BYTES = ATM_WARPS * ATM_STAGES * 16 * 8;
+  static constexpr int BAR_BYTES = ATM_WARPS * ATM_STAGES * 8;
+  static constexpr int SMEM = ATM_WARPS * WARP_BYTES + Q_BYTES + META_BYTES + BAR_BYTES;
+};
+
+template <int D, bool HALF>
+__global__ void __launch_bounds__(ATM_THREADS, 2)
+masked_attention_mma_kernel(AttnArgs a, int* __restrict__ tickets, int* __restrict__ errflag,
+                            const float* __restrict__ sinks, __nv_bfloat16* __restrict__ out,
+                            float* __restrict__ acc_out, float* __restrict__ lse_out) {
+  using C = AtmCfg<D>;
+  constexpr int NR = HALF ? 1 : 2;  // row halves a thread owns in the C fragment
+  extern __shared__ __align__(128) unsigned char atm_smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  unsigned char* ring = atm_smem + warp * C::WARP_BYTES;
+  unsigned char* q_sm = atm_smem + ATM_WARPS * C::WARP_BYTES;
+  int2* meta_sm = reinterpret_cast<int2*>(q_sm + C::Q_BYTES) + warp * ATM_STAGES * 16;  // (col, memb)
+  unsigned char* bar_base = q_sm + C::Q_BYTES + C::META_BYTES + warp * ATM_STAGES * 8;
+  const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
+  const uint32_t bar_s = (uint32_t)__cvta_generic_to_shared(bar_base);
+  __shared__ int is_last_sm;
+
+  const int split = blockIdx.x;
+  const int64_t g = blockIdx.y;
+  const int qb = (int)(g % a.nqb);
+  const int64_t bk = g / a.nqb;
+  const int kvh = (int)(bk % a.Hkv);
+  const int64_t b = bk / a.Hkv;
+  const __nv_bfloat16* kbase = reinterpret_cast<const __nv_bfloat16*>(a.k) + b * a.ks_b + kvh * a.ks_h;
+  const __nv_bfloat16* vbase = reinterpret_cast<const __nv_bfloat16*>(a.v) + b * a.vs_b + kvh * a.vs_h;
+  const int32_t* gcols = a.ucols + g * a.S;
+  const uint16_t* gmemb = a.umemb + g * a.S;
+  const float* guw = a.uw ? a.uw + g * a.S * a.R : nullptr;
+
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < ATM_STAGES; ++s) atm_mbar_init(bar_s + s * 8, 1);
+  }
+  // ---- stage Q (zero padded to 16 rows) ----
+  for (int idx = tid; idx < 16 * (C::ROWB / 16); idx += ATM_THREADS) {
+    const int r = idx / (C::ROWB / 16), c = idx - r * (C::ROWB / 16);
+    uint4 val = make_uint4(0u, 0u, 0u, 0u);
+    if (r < a.R) {
+      const int gi = r / a.q_block, qo = r - gi * a.q_block;
+      const int qi = qb * a.q_block + qo;
+      if (qi < a.Sq) {
+        const int h = kvh * a.G + gi;
+        val = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.q) +
+                                              b * a.qs_b + (int64_t)h * a.qs_h + qi * a.qs_q + c * 8);
+      }
+    }
+    *reinterpret_cast<uint4*>(q_sm + r * C::RSTR + c * 16) = val;
+  }
+  asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  __syncthreads();
+
+  // Q fragments.  Full: [ks][0..3] = (rows 0-7, k lo), (rows 8-15, k lo), (rows 0-7, k hi),
+  // (rows 8-15, k hi).  HALF: [ks][0..1] = (rows 0-7, k lo), (rows 0-7, k hi).
+  uint32_t qf[C::KSTEPS][HALF ? 2 : 4];
+  {
+    const uint32_t q_s = (uint32_t)__cvta_generic_to_shared(q_sm);
+    const int mi = lane >> 3, rr = lane & 7;
+#pragma unroll
+    for (int ks = 0; ks < C::KSTEPS; ++ks) {
+      if constexpr (HALF) {
+        const int c = 2 * ks + (mi & 1);  // lanes 0-7: k lo, lanes 8-15: k hi
+        atm_ldmatrix_x2(qf[ks][0], qf[ks][1], q_s + rr * C::RSTR + c * 16);
+      } else {
+        const int row = (mi & 1) * 8 + rr;
+        const int c = 2 * ks + (mi >> 1);
+        atm_ldmatrix_x4(qf[ks][0], qf[ks][1], qf[ks][HALF ? 0 : 2], qf[ks][HALF ? 1 : 3],
+                        q_s + row * C::RSTR + c * 16);
+      }
+    }
+  }
+
+  // ---- this warp's tiles ----
+  const int U = a.ucount[g];
+  const int total_tiles = (U + ATM_TILE - 1) / ATM_TILE;
+  const int lanes_total = a.nsplit * ATM_WARPS;   // warps sharing the group
+  const int my_first = split * ATM_WARPS + warp;  // tile t of this warp = my_first + t * lanes_total
+  const int my_tiles =
+      (total_tiles > my_first) ? (total_tiles - my_first + lanes_total - 1) / lanes_total : 0;
+
+  // rows this thread owns in the C fragment, and their bias rows
+  const int r0 = lane >> 2, r1 = r0 + 8;
+  const __nv_bfloat16* bias_row[2] = {nullptr, nullptr};
+  if (a.bias != nullptr) {
+    const __nv_bfloat16* bb = reinterpret_cast<const __nv_bfloat16*>(a.bias) + b * a.bias_s_b;
+#pragma unroll
+    for (int rs = 0; rs < NR; ++rs) {
+      const int r = rs ? r1 : r0;
+      const int gi = r / a.q_block, qo = r - gi * a.q_block;
+      const int qi = qb * a.q_block + qo;
+      if (r < a.R && qi < a.Sq) bias_row[rs] = bb + (kvh * a.G + gi) * a.bias_s_h + qi * a.bias_s_q;
+    }
+  }
+
+  float o[C::NT][2 * NR];
+#pragma unroll
+  for (int nt = 0; nt < C::NT; ++nt)
+#pragma unroll
+    for (int e = 0; e < 2 * NR; ++e) o[nt][e] = 0.f;
+  float m_run[NR], l_run[NR];
+#pragma unroll
+  for (int rs = 0; rs < NR; ++rs) { m_run[rs] = -INFINITY; l_run[rs] = 0.f; }
+
+  // Column / membership of the next tile to issue are fetched one tile early so
+  // that their latency hides behind the tile being computed.
+  int pre_col = -1;
+  unsigned int pre_memb = 0u;
+  auto prefetch_meta = [&](int t) {
+    pre_col = -1;
+    pre_memb = 0u;
+    if (t < my_tiles) {
+      const int u = (my_first + t * lanes_total) * ATM_TILE + lane;
+      if (lane < ATM_TILE && u < U) {
+        pre_col = gcols[u];
+        pre_memb = gmemb[u];
+      }
+    }
+  };
+  prefetch_meta(0);
+
+  // The shared-memory ring bounds the bytes a warp can have in flight; rows of
+  // tiles further ahead are pulled into L2 with prefetches (lane l: row l & 15 of
+  // K for l < 16, of V otherwise), so that the ring's copies find them there.
+  const unsigned char* pf_base = reinterpret_cast<const unsigned char*>(lane < 16 ? kbase : vbase);
+  const int64_t pf_stride = (lane < 16 ? a.ks_s : a.vs_s) * 2;
+  auto l2_prefetch_tile = [&](int tt) {
+    if (tt < my_tiles) {
+      const int u = (my_first + tt * lanes_total) * ATM_TILE + (lane & 15);
+      if (u < U) {
+        const unsigned char* p = pf_base + (int64_t)gcols[u] * pf_stride;
+#pragma unroll
+        for (int off = 0; off < C::ROWB; off += 128) atm_prefetch_l2(p + off);
+      }
+    }
+  };
+#pragma unroll 1
+  for (int tt = ATM_STAGES - 1; tt < ATM_STAGES - 1 + ATM_PF_DIST; ++tt) l2_prefetch_tile(tt);
+
+#if ATM_BULK
+  // lane l copies row (l & 15) of K (l < 16) or of V (l >= 16)
+  const int my_row = lane & 15;
+  const uint32_t my_dst = (lane < 16 ? 0u : (uint32_t)C::TILE_BYTES) + my_row * C::RSTR;
+  const __nv_bfloat16* my_base = lane < 16 ? kbase : vbase;
+  const int64_t my_stride = lane < 16 ? a.ks_s : a.vs_s;
+
+  auto issue = [&](int t) {
+    const int st = t % ATM_STAGES;
+    const int col = pre_col;
+    const unsigned int memb = pre_memb;
+    prefetch_meta(t + 1);
+    if (lane < ATM_TILE) meta_sm[st * 16 + lane] = make_int2(col, (int)memb);
+    const int rc = __shfl_sync(0xffffffffu, col, my_row);
+    const uint32_t valid = __ballot_sync(0xffffffffu, rc >= 0);
+    const uint32_t bar = bar_s + st * 8;
+    if (lane == 0) atm_mbar_expect_tx(bar, (uint32_t)__popc(valid) * C::ROWB);
+    const uint32_t dst = ring_s + st * C::STAGE_BYTES + my_dst;
+    if (rc >= 0) {
+      atm_bulk_g2s(dst, my_base + (int64_t)rc * my_stride, C::ROWB, bar);
+    } else {
+      // unused rows must not feed NaNs into the tensor cores
+      unsigned char* p = ring + st * C::STAGE_BYTES + my_dst;
+#pragma unroll
+      for (int c = 0; c < C::ROWB / 16; ++c)
+        *reinterpret_cast<uint4*>(p + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+  };
+#else
+  // 16-byte asynchronous copies: CPR lanes cover one row, so a warp instruction
+  // moves 32 / CPR whole rows; destination offsets are compile-time constants
+  // plus a per-lane base.
+  constexpr int CPR = C::ROWB / 16;        // chunks per row
+  constexpr int RPS = 32 / CPR;            // rows per warp instruction
+  const int my_chunk = lane % CPR, my_sub = lane / CPR;
+  const uint32_t my_dst = my_sub * C::RSTR + my_chunk * 16;
+  const unsigned char* k_bytes = reinterpret_cast<const unsigned char*>(kbase) + my_chunk * 16;
+  const unsigned char* v_bytes = reinterpret_cast<const unsigned char*>(vbase) + my_chunk * 16;
+  const int64_t ks_bytes = a.ks_s * 2, vs_bytes = a.vs_s * 2;
+
+  auto issue = [&](int t) {
+    const int st = t % ATM_STAGES;
+    const int col = pre_col;
+    const unsigned int memb = pre_memb;
+    prefetch_meta(t + 1);
+    if (lane < ATM_TILE) meta_sm[st * 16 + lane] = make_int2(col, (int)memb);
+    const uint32_t dst0 = ring_s + st * C::STAGE_BYTES + my_dst;
+#pragma unroll
+    for (int it = 0; it < ATM_TILE / RPS; ++it) {
+      const int rc = __shfl_sync(0xffffffffu, col, it * RPS + my_sub);
+      const uint32_t dst = dst0 + it * RPS * C::RSTR;
+      if (rc >= 0) {
+        atm_cp_async16(dst, k_bytes + rc * ks_bytes);
+        atm_cp_async16(dst + C::TILE_BYTES, v_bytes + rc * vs_bytes);
+      } else {
+        // unused rows must not feed NaNs into the tensor cores
+        unsigned char* p = ring + st * C::STAGE_BYTES + my_dst + it * RPS * C::RSTR;
+        *reinterpret_cast<uint4*>(p) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(p + C::TILE_BYTES) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+  };
+#endif
+
+#pragma unroll
+  for (int s = 0; s < ATM_STAGES - 1; ++s) {
+    if (s < my_tiles) issue(s);
+#if !ATM_BULK
+    asm volatile("cp.async.commit_group;\n" ::);
+#endif
+  }
+
+  bool alive = true;
+  int t = 0;
+  for (; t < my_tiles; ++t) {
+    if (t + ATM_STAGES - 1 < my_tiles) issue(t + ATM_STAGES - 1);
+    l2_prefetch_tile(t + ATM_STAGES - 1 + ATM_PF_DIST);
+    const int st = t % ATM_STAGES;
+#if ATM_BULK
+    if (!atm_mbar_wait(bar_s + st * 8, (uint32_t)((t / ATM_STAGES) & 1))) {
+      alive = false;
+      break;
+    }
+#else
+    asm volatile("cp.async.commit_group;\n" ::);
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(ATM_STAGES - 1));
+    __syncwarp();
+#endif
+    const uint32_t kst = ring_s + st * C::STAGE_BYTES;
+    const uint32_t vst = kst + C::TILE_BYTES;
+    const int u0 = (my_first + t * lanes_total) * ATM_TILE;
+
+    // ---- S = Q . K^T ----
+    float s[2][2 * NR];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 2 * NR; ++e) s[nt][e] = 0.f;
+    {
+      const int mi = lane >> 3, rr = lane & 7;
+      const uint32_t kaddr = kst + ((mi >> 1) * 8 + rr) * C::RSTR + (mi & 1) * 16;
+#pragma unroll
+      for (int ks = 0; ks < C::KSTEPS; ++ks) {
+        uint32_t b0, b1, b2, b3;
+        atm_ldmatrix_x4(b0, b1, b2, b3, kaddr + ks * 32);
+        if constexpr (HALF) {
+          atm_mma_half(s[0][0], s[0][1], qf[ks][0], qf[ks][1], b0, b1);
+          atm_mma_half(s[1][0], s[1][1], qf[ks][0], qf[ks][1], b2, b3);
+        } else {
+          atm_mma_full(s[0], qf[ks], b0, b1);
+          atm_mma_full(s[1], qf[ks], b2, b3);
+        }
+      }
+    }
+
+    // ---- online softmax in the C fragment ----
+    // element (nt, e): row half rs = e >> 1, key j = nt * 8 + 2 * (lane & 3) + (e & 1)
+    float wts[2][2 * NR];
+    float tmax[NR];
+#pragma unroll
+    for (int rs = 0; rs < NR; ++rs) tmax[rs] = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2 * NR; ++e) {
+        const int j = nt * 8 + 2 * (lane & 3) + (e & 1);
+        const int rs = e >> 1;
+        const int r = rs ? r1 : r0;
+        const int2 cm = meta_sm[st * 16 + j];
+        float sv = -INFINITY, wv = 0.f;
+        if (cm.x >= 0 && ((cm.y >> r) & 1)) {
+          sv = s[nt][e] * a.scaling;
+          if (bias_row[rs] != nullptr) sv += __bfloat162float(bias_row[rs][cm.x]);
+          wv = guw ? guw[(int64_t)(u0 + j) * a.R + r] : 1.f;
+        }
+        s[nt][e] = sv;
+        wts[nt][e] = wv;
+        tmax[rs] = fmaxf(tmax[rs], sv);
+      }
+    }
+    float alpha[NR];
+#pragma unroll
+    for (int rs = 0; rs < NR; ++rs) {
+      tmax[rs] = fmaxf(tmax[rs], __shfl_xor_sync(0xffffffffu, tmax[rs], 1));
+      tmax[rs] = fmaxf(tmax[rs], __shfl_xor_sync(0xffffffffu, tmax[rs], 2));
+      const float m_new = fmaxf(m_run[rs], tmax[rs]);
+      alpha[rs] = (m_new == m_run[rs]) ? 1.f : __expf(m_run[rs] - m_new);
+      m_run[rs] = m_new;
+    }
+    float psum[NR];
+#pragma unroll
+    for (int rs = 0; rs < NR; ++rs) psum[rs] = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2 * NR; ++e) {
+        const int rs = e >> 1;
+        float pv = 0.f;
+        if (s[nt][e] != -INFINITY) pv = __expf(s[nt][e] - m_run[rs]) * wts[nt][e];
+        s[nt][e] = pv;  // s now holds P
+        psum[rs] += pv;
+      }
+    }
+    bool rescale = false;
+#pragma unroll
+    for (int rs = 0; rs < NR; ++rs) {
+      psum[rs] += __shfl_xor_sync(0xffffffffu, psum[rs], 1);
+      psum[rs] += __shfl_xor_sync(0xffffffffu, psum[rs], 2);
+      l_run[rs] = l_run[rs] * alpha[rs] + psum[rs];
+      rescale |= (alpha[rs] != 1.f);
+    }
+    if (__any_sync(0xffffffffu, rescale)) {  // the running maximum moved for some row
+#pragma unroll
+      for (int nt = 0; nt < C::NT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2 * NR; ++e) o[nt][e] *= alpha[e >> 1];
+    }
+
+    // ---- O += P . V ----
+    uint32_t pa[4];
+    pa[0] = atm_pack_bf16(s[0][0], s[0][1]);
+    pa[2] = atm_pack_bf16(s[1][0], s[1][1]);
+    pa[1] = HALF ? 0u : atm_pack_bf16(s[0][2 * NR - 2], s[0][2 * NR - 1]);
+    pa[3] = HALF ? 0u : atm_pack_bf16(s[1][2 * NR - 2], s[1][2 * NR - 1]);
+    {
+      const int mi = lane >> 3, rr = lane & 7;
+      const uint32_t vaddr = vst + ((mi & 1) * 8 + rr) * C::RSTR + (mi >> 1) * 16;
+#pragma unroll
+      for (int np = 0; np < C::NT / 2; ++np) {
+        uint32_t b0, b1, b2, b3;
+        atm_ldmatrix_x4_trans(b0, b1, b2, b3, vaddr + np * 32);
+        if constexpr (HALF) {
+          atm_mma_half(o[2 * np][0], o[2 * np][1], pa[0], pa[2], b0, b1);
+          atm_mma_half(o[2 * np + 1][0], o[2 * np + 1][1], pa[0], pa[2], b2, b3);
+        } else {
+          atm_mma_full(o[2 * np], pa, b0, b1);
+          atm_mma_full(o[2 * np + 1], pa, b2, b3);
+        }
+      }
+    }
+    __syncwarp();  // all lanes done with this stage before it is refilled
+  }
+#if !ATM_BULK
+  asm volatile("cp.async.wait_group 0;\n" ::);
+#endif
+  if (!alive) {
+    if (lane == 0) atomicExch(errflag, 1);
+    // give the copies still in flight a bounded chance to land before the ring is reused
+    for (int tt = t; tt < my_tiles && tt < t + ATM_STAGES; ++tt)
+      atm_mbar_wait(bar_s + (tt % ATM_STAGES) * 8, (uint32_t)((tt / ATM_STAGES) & 1));
+  }
+  __syncthreads();
+
+  // ---- merge the warps of this CTA (ring reused as fp32 scratch) ----
+  constexpr int RS = C::RS;
+  float* red_o = reinterpret_cast<float*>(ring);  // [16][RS]
+  float* red_ml = red_o + 16 * RS;                // [16][2]
+#pragma unroll
+  for (int nt = 0; nt < C::NT; ++nt) {
+    const int d = nt * 8 + 2 * (lane & 3);
+    *reinterpret_cast<float2*>(red_o + r0 * RS + d) = make_float2(o[nt][0], o[nt][1]);
+    if constexpr (!HALF)
+      *reinterpret_cast<float2*>(red_o + r1 * RS + d) =
+          make_float2(o[nt][2 * NR - 2], o[nt][2 * NR - 1]);
+  }
+  if ((lane & 3) == 0) {
+    red_ml[r0 * 2] = m_run[0];
+    red_ml[r0 * 2 + 1] = l_run[0];
+    if constexpr (!HALF) {
+      red_ml[r1 * 2] = m_run[NR - 1];
+      red_ml[r1 * 2 + 1] = l_run[NR - 1];
+    }
+  }
+  __syncthreads();
+  float* pout = a.partial + ((int64_t)g * a.nsplit + split) * a.R * (D + 2);
+  for (int idx = tid; idx < a.R * D; idx += ATM_THREADS) {
+    const int r = idx / D, d = idx - r * D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < ATM_WARPS; ++w)
+      M = fmaxf(M, reinterpret_cast<const float*>(atm_smem + w * C::WARP_BYTES)[16 * RS + r * 2]);
+    float acc = 0.f, L = 0.f;
+#pragma unroll
+    for (int w = 0; w < ATM_WARPS; ++w) {
+      const float* wo = reinterpret_cast<const float*>(atm_smem + w * C::WARP_BYTES);
+      const float mw = wo[16 * RS + r * 2];
+      if (mw != -INFINITY) {
+        const float sc = __expf(mw - M);
+        acc += wo[r * RS + d] * sc;
+        L += wo[16 * RS + r * 2 + 1] * sc;
+      }
+    }
+    pout[r * (D + 2) + d] = acc;
+    if (d == 0) {
+      pout[r * (D + 2) + D] = M;
+      pout[r * (D + 2) + D + 1] = L;
+    }
+  }
+
+  // ---- last CTA of the group merges the group's partials ----
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int old = atomicAdd(&tickets[g], 1);
+    const int last = (old == a.nsplit - 1);
+    if (last) tickets[g] = 0;  // ready for the next call
+    is_last_sm = last;
+  }
+  __syncthreads();
+  if (!is_last_sm) return;
+  __threadfence();
+  const float* p0 = a.partial + (int64_t)g * a.nsplit * a.R * (D + 2);
+  const int64_t pstride = (int64_t)a.R * (D + 2);
+  // phase 1: one warp per row finds the row maximum, the per-split rescale
+  // factors and the denominator (ring memory reused as scratch)
+  float* sc_sm = reinterpret_cast<float*>(atm_smem);  // [R][nsplit]
+  float* ml_sm = sc_sm + 16 * a.nsplit;               // [R][2]
+  for (int r = warp; r < a.R; r += ATM_WARPS) {
+    const float* pr = p0 + (int64_t)r * (D + 2);
+    float mloc = -INFINITY;
+    for (int s2 = lane; s2 < a.nsplit; s2 += 32) mloc = fmaxf(mloc, __ldcg(pr + s2 * pstride + D));
+#pragma unroll
+    for (int of = 16; of > 0; of >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, of));
+    float lsum = 0.f;
+    for (int s2 = lane; s2 < a.nsplit; s2 += 32) {
+      const float ms = __ldcg(pr + s2 * pstride + D);
+      const float sc = (ms == -INFINITY) ? 0.f : __expf(ms - mloc);
+      sc_sm[r * a.nsplit + s2] = sc;
+      lsum += __ldcg(pr + s2 * pstride + D + 1) * sc;
+    }
+#pragma unroll
+    for (int of = 16; of > 0; of >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, of);
+    if (lane == 0) {
+      ml_sm[r * 2] = mloc;
+      ml_sm[r * 2 + 1] = lsum;
+    }
+  }
+  __syncthreads();
+  // phase 2: every (row, dim) sums its column over the splits; the loads are independent
+  for (int idx = tid; idx < a.R * D; idx += ATM_THREADS) {
+    const int r = idx / D, d = idx - r * D;
+    const int gi = r / a.q_block, qo = r - gi * a.q_block;
+    const int qi = qb * a.q_block + qo;
+    if (qi >= a.Sq) continue;
+    const int h = kvh * a.G + gi;
+    const float* pr = p0 + (int64_t)r * (D + 2) + d;
+    const float* sc = sc_sm + r * a.nsplit;
+    float accv = 0.f;
+#pragma unroll 8
+    for (int s2 = 0; s2 < a.nsplit; ++s2) accv = fmaf(__ldcg(pr + s2 * pstride), sc[s2], accv);
+    const float M = ml_sm[r * 2], L = ml_sm[r * 2 + 1];
+    float Mx = M, sink_term = 0.f;
+    if (sinks != nullptr) {
+      const float sk = sinks[h];
+      Mx = fmaxf(M, sk);
+      sink_term = __expf(sk - Mx);
+    }
+    const float resc = (M == -INFINITY) ? 0.f : __expf(M - Mx);
+    const float den = L * resc + sink_term;
+    const int64_t row = (b * a.Hq + h) * a.Sq + qi;
+    if (acc_out != nullptr) acc_out[row * D + d] = accv;
+    out[((b * a.Sq + qi) * a.Hq + h) * D + d] = __float2bfloat16_rn(accv * resc / den);
+    if (lse_out != nullptr && d == 0) {
+      lse_out[row * 2 + 0] = M;
+      lse_out[row * 2 + 1] = L;
+    }
+  }
+}
+
+template <int D>
+static int launch_attention_mma(const AttnArgs& a, int groups, int* tickets, int* errflag,
+                                const float* sinks, void* out, float* acc_out, float* lse_out,
+                                cudaStream_t st) {
+  using C = AtmCfg<D>;
+  static_assert(C::RED_BYTES <= C::WARP_BYTES, "reduction scratch must fit the ring");
+  const int smem = C::SMEM;
+  if ((size_t)16 * a.nsplit * 4 + 128 > (size_t)ATM_WARPS * C::WARP_BYTES)
+    return sah_fail(SAH_ERR_UNSUPPORTED, "attention: %d splits do not fit the merge scratch", a.nsplit);
+  dim3 grid((unsigned)a.nsplit, (unsigned)groups);
+  cudaError_t e;
+  if (a.R <= 8) {
+    e = cudaFuncSetAttribute(masked_attention_mma_kernel<D, true>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "attention attr: %s", cudaGetErrorString(e));
+    masked_attention_mma_kernel<D, true><<<grid, ATM_THREADS, smem, st>>>(
+        a, tickets, errflag, sinks, (__nv_bfloat16*)out, acc_out, lse_out);
+  } else {
+    e = cudaFuncSetAttribute(masked_attention_mma_kernel<D, false>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "attention attr: %s", cudaGetErrorString(e));
+    masked_attention_mma_kernel<D, false><<<grid, ATM_THREADS, smem, st>>>(
+        a, tickets, errflag, sinks, (__nv_bfloat16*)out, acc_out, lse_out);
+  }
+  return SAH_OK;
+}

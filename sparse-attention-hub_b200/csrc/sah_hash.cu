@@ -389,10 +389,18 @@ hash_topk_fast_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
   uint32_t* out_row = out_bits + row * W;
   const bool aligned = ((reinterpret_cast<uintptr_t>(kc) & 15) == 0);
 
+  // Scores below `floor_sm` are left out of the histogram; a floor above zero is
+  // only a shortcut (retried at zero when fewer than k keys clear it).
+  __shared__ int floor_sm;
+  __shared__ int retry_sm;
+  if (tid == 0) floor_sm = 0;
+
+  for (int attempt = 0; attempt < 2; ++attempt) {
   for (int i = tid; i < 32 * HT_BINS; i += 1024) (&hist[0][0])[i] = 0u;
   __syncthreads();
+  const int floor_bin = floor_sm;
 
-  // ---- pass 1: histogram of matching-bit counts over inactive keys ----
+  // ---- pass 1: histogram of matching-bit counts >= floor over inactive keys ----
   for (int64_t w = tid; w < W; w += 1024) {
     uint32_t codes[32];
     ht_load_codes(kc, w, S, aligned, codes);
@@ -402,7 +410,8 @@ hash_topk_fast_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
     if (c0 + 32 > S) valid &= (c0 >= S) ? 0u : ((1u << (S - c0)) - 1u);
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
-      if ((valid >> i) & 1u) atomicAdd(&hist[warp][nbits - __popc(codes[i] ^ qc)], 1u);
+      const int sc = nbits - __popc(codes[i] ^ qc);
+      if (sc >= floor_bin && ((valid >> i) & 1u)) atomicAdd(&hist[warp][sc], 1u);
     }
   }
   __syncthreads();
@@ -423,9 +432,12 @@ hash_topk_fast_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
     const long long total = __shfl_sync(0xffffffffu, (long long)incl, 0) + top;
     int thr;
     long long need;
+    int retry = 0;
     if (k <= 0) {
       thr = 64; need = 0;                 // nothing qualifies
-    } else if (total <= k) {
+    } else if (total < k && floor_bin > 0) {
+      thr = 64; need = 0; retry = 1;      // the floor was too high for this row
+    } else if (total <= k && floor_bin == 0) {
       thr = -1; need = 0;                 // every candidate qualifies
     } else if ((long long)top >= k) {
       thr = 32; need = k;
@@ -436,9 +448,16 @@ hash_topk_fast_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
       const long long mine_thr = __shfl_sync(0xffffffffu, (long long)mine, thr);
       need = k - (ge_thr - mine_thr);     // ties to take at the threshold
     }
-    if (lane == 0) { thr_sm = thr; need_sm = need; }
+    if (lane == 0) {
+      thr_sm = thr;
+      need_sm = need;
+      retry_sm = retry;
+      if (retry) floor_sm = 0;
+    }
   }
   __syncthreads();
+  if (!retry_sm) break;
+  }  // attempt
   const int thr = thr_sm;
   const long long need = need_sm;
 

@@ -256,3 +256,41 @@ def test_partials_merge_equals_single_pass():
         lses.append(lse)
     got = merge_attention_partials(torch.stack(accs), torch.stack(lses), 1, 8, 1, torch.float32)
     _close(got.cpu().numpy(), want.cpu().numpy(), "f32")
+
+
+def test_hash_topk_degenerate_score_distributions():
+    """Rows whose scores are nothing like a binomial: all equal, two levels, all maximal."""
+    S, k = 5000, 300
+    shape = (1, 4, 1, S)
+    rng = np.random.default_rng(9)
+    q = np.array([[[0x0F0F0F0F], [0xFFFFFFFF], [0x12345678], [0]]], np.uint32)
+    kc = np.empty((1, 4, S), np.uint32)
+    kc[0, 0] = ~q[0, 0, 0]                      # every key scores 0 matching bits
+    kc[0, 1] = q[0, 1, 0]                       # every key matches all 32 bits
+    kc[0, 2] = np.where(rng.random(S) < 0.01, q[0, 2, 0], ~q[0, 2, 0])  # 1 % perfect, rest zero
+    kc[0, 3] = rng.integers(0, 2 ** 32, S, dtype=np.uint64).astype(np.uint32)
+    tk = torch.from_numpy(kc.view(np.int32)).to(DEV)
+    tq = torch.from_numpy(q.view(np.int32)).to(DEV)
+    prev = Mask.create_empty_mask(shape, torch.bfloat16, torch.device(DEV))
+    sel = _native_ops.hash_topk(tk, S, tq, 32, None, torch.bfloat16, prev, k, shape)
+    got = Mask._from_native(shape, torch.bfloat16, sel).get_dense_mask().float().cpu().numpy() != 0
+    from oracle import hashattention as oh, topk as ot
+    scores = oh.scores(q, kc, 32, "bf16")
+    want = ot.topk_inactive(scores, np.zeros(shape, bool), k)
+    np.testing.assert_array_equal(got, want)
+
+
+def test_attention_with_sixteen_rows_per_group():
+    """GQA ratio 16: every row of the 16-row tensor-core tile is a real query head."""
+    wl = workloads.sink_local_fp32(seed=44, B=1, Hq=16, Hkv=1, S=1500, D=128, sink=8, window=40)
+    rng = np.random.default_rng(11)
+    for dtype in ("bf16", "f32"):
+        q, k, v = (workloads.to_dtype(a, dtype) for a in (wl.q, wl.k, wl.v))
+        dense = (rng.random((1, 16, 1, 1500)) < 0.2).astype(np.float32)
+        dense[..., :8] = 1.0
+        tq, tk, tv = (workloads.to_torch(a, dtype, DEV) for a in (q, k, v))
+        m = Mask.create_mask_from_dense_mask(dense.shape, workloads.to_torch(dense, dtype, DEV),
+                                             workloads.torch_dtype(dtype))
+        out = native_masked_attention(tq, tk, tv, None, None, float(wl.scaling), m)
+        ref = o_attention.masked_attention(q, k, v, dense, wl.scaling, dtype)
+        _close(out.float().cpu().numpy(), ref, dtype)
