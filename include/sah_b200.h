@@ -258,6 +258,40 @@ int sah_attn_merge_parts(const float* acc, const float* lse, int n_parts, int B,
                          int Sq, int D, const float* sinks, int dtype, void* out,
                          void* stream);
 
+/* Masked attention that brings its own scratch: plan + gather attention for a
+ * unit-weight bitmap mask, with the union lists, counters and split partials
+ * held in a device array that is part of the library image.
+ *
+ * This entry point has no counterpart in the reference.  It exists for callers
+ * that have no way to hand the library scratch memory: a host whose device
+ * memory was partitioned once at start-up by another runtime, or one that must
+ * not allocate from the CUDA driver after initialisation because an allocation
+ * stalls every stream of the process.  Such a caller still passes the inputs
+ * (bits, Q, K, V, optional bias and sinks) and the output buffer; it passes no
+ * workspace and nothing is allocated, by this call or by anything it calls.
+ *
+ * Limits: B * Hkv * ceil(Sq / q_block) * S <= 2^20 union-list slots (for
+ * example 8 KV groups of 131072 keys, or 32 groups of 32768 keys), at most
+ * 2^16 counters and 2^21 fp32 words of split partials; larger problems are
+ * rejected with SAH_ERR_WORKSPACE and a message that states the three sizes.
+ * The array is 14.25 MiB and stays resident on every GPU that loads the
+ * library until the process exits.
+ *
+ * The first call on a device looks up the array's device address (once per
+ * device, with that device current); make that first call outside any stream
+ * capture.  All calls on a device share the one array, which keeps the
+ * contents of the previous call: each call re-zeroes the counters it needs on
+ * `stream` before use, but two calls whose kernels overlap on the GPU (two
+ * streams, two host threads) race on it and must be serialised by the caller.
+ * The mask must have unit weights (the data == NULL case of sah_attn_plan). */
+int sah_masked_attention_static(const uint32_t* bits, const void* q, const void* k, const void* v,
+                                int dtype, int64_t qs_b, int64_t qs_h, int64_t qs_q,
+                                int64_t ks_b, int64_t ks_h, int64_t ks_s, int64_t vs_b,
+                                int64_t vs_h, int64_t vs_s, int B, int Hq, int Hkv, int Sq,
+                                int64_t S, int64_t W, int D, float scaling, const void* bias,
+                                int64_t bias_s_b, int64_t bias_s_h, int64_t bias_s_q,
+                                const float* sinks, int sm_count, void* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -6,6 +6,8 @@
 //                          pipeline, weighted online softmax in fp32, every row
 //                          fetched once per group and shared by its query heads
 //   sah_attn_merge_parts   associative merge of sequence-sharded partials
+#include <mutex>
+
 #include "sah_common.cuh"
 
 #define AT_THREADS 128
@@ -801,4 +803,97 @@ extern "C" int sah_attn_merge_parts(const float* acc, const float* lse, int n_pa
   });
   SAH_LAUNCH_CHECK("attn_merge_parts");
   return SAH_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Masked attention with library-owned scratch (no allocation by anybody).
+//
+// Some hosts of this library cannot hand it scratch memory: an embedding whose
+// device memory is carved up once at start-up by another runtime, or a caller
+// that runs under a "no allocation after initialisation" rule (allocating from
+// the CUDA driver mid-run stalls every stream of the process), has nowhere to
+// get the work lists and partial buffers that plan + gather attention need.
+// This entry point keeps them in one statically sized device array that is
+// part of the library image, so nothing is allocated at any time -- at the
+// price of a fixed upper bound on the problem size and of one copy of the
+// array per GPU that loads the library.
+// ---------------------------------------------------------------------------
+#define SAH_STATIC_MAX_ENTRIES (1ll << 20)   // groups * S union-list slots
+#define SAH_STATIC_MAX_COUNTERS (1ll << 16)  // int32 counters (counts, chunk counts, tickets)
+#define SAH_STATIC_MAX_PARTIAL (1ll << 21)   // fp32 words of split partials
+
+#define SAH_STATIC_OFF_UCOLS 0ll
+#define SAH_STATIC_OFF_UMEMB (SAH_STATIC_OFF_UCOLS + SAH_STATIC_MAX_ENTRIES * 4)
+#define SAH_STATIC_OFF_COUNT (SAH_STATIC_OFF_UMEMB + SAH_STATIC_MAX_ENTRIES * 2)
+#define SAH_STATIC_OFF_PARTIAL (SAH_STATIC_OFF_COUNT + SAH_STATIC_MAX_COUNTERS * 4)
+#define SAH_STATIC_BYTES (SAH_STATIC_OFF_PARTIAL + SAH_STATIC_MAX_PARTIAL * 4)
+
+// 14.25 MiB of device memory on every GPU that loads this library, until exit.
+static __device__ __align__(256) unsigned char g_sah_static_scratch[SAH_STATIC_BYTES];
+
+#define SAH_STATIC_MAX_DEVICES 64
+static std::mutex g_static_mu;
+static unsigned char* g_static_ptr[SAH_STATIC_MAX_DEVICES] = {nullptr};
+
+// Device address of the scratch array on the current device.  In host code the
+// array's name is only a handle, not an address a kernel could use; the address
+// is asked for once per device, with that device current, and remembered.
+static int sah_static_scratch_ptr(unsigned char** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "static scratch: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= SAH_STATIC_MAX_DEVICES)
+    return sah_fail(SAH_ERR_UNSUPPORTED, "static scratch: device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (g_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_sah_static_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return sah_fail(SAH_ERR_CUDA, "static scratch: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    g_static_ptr[dev] = static_cast<unsigned char*>(p);
+  }
+  *out = g_static_ptr[dev];
+  return SAH_OK;
+}
+
+extern "C" int sah_masked_attention_static(
+    const uint32_t* bits, const void* q, const void* k, const void* v, int dtype, int64_t qs_b,
+    int64_t qs_h, int64_t qs_q, int64_t ks_b, int64_t ks_h, int64_t ks_s, int64_t vs_b,
+    int64_t vs_h, int64_t vs_s, int B, int Hq, int Hkv, int Sq, int64_t S, int64_t W, int D,
+    float scaling, const void* bias, int64_t bias_s_b, int64_t bias_s_h, int64_t bias_s_q,
+    const float* sinks, int sm_count, void* out, void* stream) {
+  SAH_REQUIRE(bits && q && k && v && out, "masked_attention_static: null pointer");
+  sah_attn_sizes sizes;
+  int rc = sah_attn_query_sizes(B, Hq, Hkv, Sq, S, D, /*has_data=*/0, sm_count, &sizes);
+  if (rc != SAH_OK) return rc;
+  const long long entries = (long long)sizes.groups * S;
+  const long long counters = sizes.ucount_bytes / 4;
+  const long long partial_words = sizes.partial_bytes / 4;
+  if (entries > SAH_STATIC_MAX_ENTRIES || counters > SAH_STATIC_MAX_COUNTERS ||
+      partial_words > SAH_STATIC_MAX_PARTIAL)
+    return sah_fail(SAH_ERR_WORKSPACE,
+                    "masked_attention_static: problem needs %lld list slots, %lld counters and %lld "
+                    "partial words; the built-in scratch holds %lld, %lld and %lld "
+                    "(use sah_attn_plan + sah_masked_attention with caller memory instead)",
+                    entries, counters, partial_words, (long long)SAH_STATIC_MAX_ENTRIES,
+                    (long long)SAH_STATIC_MAX_COUNTERS, (long long)SAH_STATIC_MAX_PARTIAL);
+  unsigned char* base = nullptr;
+  rc = sah_static_scratch_ptr(&base);
+  if (rc != SAH_OK) return rc;
+  int32_t* ucols = reinterpret_cast<int32_t*>(base + SAH_STATIC_OFF_UCOLS);
+  uint16_t* umemb = reinterpret_cast<uint16_t*>(base + SAH_STATIC_OFF_UMEMB);
+  int32_t* ucount = reinterpret_cast<int32_t*>(base + SAH_STATIC_OFF_COUNT);
+  float* partial = reinterpret_cast<float*>(base + SAH_STATIC_OFF_PARTIAL);
+  // The array keeps whatever the previous call left; the counters (union counts,
+  // merge tickets, error word) are the part that has to start from zero.
+  cudaError_t e = cudaMemsetAsync(ucount, 0, (size_t)sizes.ucount_bytes, (cudaStream_t)stream);
+  if (e != cudaSuccess)
+    return sah_fail(SAH_ERR_CUDA, "masked_attention_static: memset: %s", cudaGetErrorString(e));
+  rc = sah_attn_plan(bits, nullptr, nullptr, nullptr, dtype, B, Hq, Hkv, Sq, S, W, &sizes, ucols,
+                     umemb, nullptr, ucount, stream);
+  if (rc != SAH_OK) return rc;
+  return sah_masked_attention(q, k, v, dtype, qs_b, qs_h, qs_q, ks_b, ks_h, ks_s, vs_b, vs_h, vs_s,
+                              B, Hq, Hkv, Sq, S, D, scaling, bias, bias_s_b, bias_s_h, bias_s_q,
+                              sinks, &sizes, ucols, umemb, nullptr, ucount, partial, out, nullptr,
+                              nullptr, stream);
 }
