@@ -202,6 +202,53 @@ int sah_topk_select(const void* scores, int dtype, int64_t rows, int64_t S, int6
                     int64_t k, uint32_t* out_bits, void* stream);
 
 /* ------------------------------------------------------------------------ *
+ * PQCache  (maskers/fixed/implementations/pq_top_k.py, utils/pq_utils.py)
+ * ------------------------------------------------------------------------ */
+
+/* A "group" is one (batch, KV head, sub-vector): group = (b*Hkv + kvh)*n_sub + sub.
+ * centroids (k-means state) are float32 [groups][n_cent][sub_d]; codes are bytes
+ * [B][Hkv][cap][n_sub] (code of key j sits at row j - init_offset). */
+
+/* Nearest centroid of the sub-vectors of keys [key_begin, key_end): the assignment
+ * step of kmeans_batched (pq_utils.py:246-255, :353) and the quantisation of
+ * appended keys (pq_top_k.py:388-404).  Distance = sum over ascending dims of
+ * (x - c)^2 in fp32; the first minimum wins.  With dtype_math != 0 every
+ * operation is rounded to `dtype`, which is how the reference quantises appended
+ * keys against its stored dtype centroids. */
+int sah_pq_assign(const void* x, int dtype, int64_t xs_b, int64_t xs_h, int64_t xs_s, int B,
+                  int Hkv, int64_t key_begin, int64_t key_end, int64_t init_offset, int n_sub,
+                  int sub_d, int n_cent, const float* centroids, uint8_t* codes, int64_t cap,
+                  int dtype_math, void* stream);
+
+/* Per-cluster sums (float64 [groups][n_cent][sub_d]) and counts (int32
+ * [groups][n_cent]) of the current assignment; both must be zeroed by the caller
+ * (pq_utils.py:360-381 computes the same through one-hot masks). */
+int sah_pq_accumulate(const void* x, int dtype, int64_t xs_b, int64_t xs_h, int64_t xs_s, int B,
+                      int Hkv, int64_t n_keys, int64_t init_offset, int n_sub, int sub_d,
+                      int n_cent, const uint8_t* codes, int64_t cap, double* sums, int* counts,
+                      void* stream);
+
+/* New centres = fp32(sum) / fp32(count); an empty cluster takes the key at
+ * reseed[group][cluster] (int64 key index inside the clustered region, drawn by
+ * the caller: pq_utils.py:384-396); shift2[group] = (sum of centre moves)^2, the
+ * value kmeans_batched compares with its tolerance (:399-423). */
+int sah_pq_update(const void* x, int dtype, int64_t xs_b, int64_t xs_h, int64_t xs_s, int B,
+                  int Hkv, int64_t init_offset, int n_sub, int sub_d, int n_cent,
+                  const double* sums, const int* counts, const int64_t* reseed, float* centroids,
+                  float* shift2, void* stream);
+
+/* scores[row][init_offset + j] = sum over sub-vectors of lut[sub][code(j, sub)],
+ * lut[sub][c] = q_sub . centroid (rounded to `dtype`), the sum taken in fp32 in
+ * ascending sub-vector order and rounded once (_compute_pq_scores,
+ * pq_top_k.py:406-490).  centroids here are in `dtype`:
+ * [B][Hkv][n_sub][n_cent][sub_d].  Columns outside the clustered region are not
+ * written.  scores is [rows][S] in `dtype`. */
+int sah_pq_scores(const void* q, int dtype, int64_t qs_b, int64_t qs_h, int64_t qs_q,
+                  const void* centroids, const uint8_t* codes, int64_t cap, int B, int Hq, int Hkv,
+                  int Sq, int64_t n_keys, int64_t init_offset, int64_t S, int n_sub, int sub_d,
+                  int n_cent, void* scores, void* stream);
+
+/* ------------------------------------------------------------------------ *
  * Masked attention  (utils/mask_attention_utils.py:187-240, :406-491)
  * ------------------------------------------------------------------------ */
 

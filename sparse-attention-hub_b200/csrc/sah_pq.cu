@@ -1,0 +1,297 @@
+// PQCache kernels (maskers/fixed/implementations/pq_top_k.py and utils/pq_utils.py):
+//   sah_pq_assign         nearest centroid of every key sub-vector (k-means assignment
+//                         step, pq_utils.py:246-255 + :353; new-key quantisation,
+//                         pq_top_k.py:388-404)
+//   sah_pq_accumulate     per-cluster sums and counts of one Lloyd iteration
+//   sah_pq_update         new centres, empty-cluster reseeding and centre shift
+//                         (pq_utils.py:360-423)
+//   sah_pq_scores         query-centroid lookup tables and the code stream
+//                         (pq_top_k.py:406-490)
+//
+// A "group" is one (batch, KV head, sub-vector): groups = B * Hkv * n_sub,
+// group id = (b * Hkv + kvh) * n_sub + sub.  Codes are bytes laid out
+// [B][Hkv][capacity][n_sub], i.e. the n_sub codes of one key are contiguous, so the
+// scoring stream reads one 16-byte word per key for n_sub = 16.
+#include "sah_common.cuh"
+
+#define PQ_MAX_SUBD 16
+#define PQ_TILE 256
+
+// Squared distance in the fixed order the CPU restatement follows: dimensions
+// ascending, (x - c) * (x - c) rounded, then added.
+__device__ __forceinline__ float pq_dist(const float* x, const float* c, int sub_d) {
+  float d = 0.f;
+  for (int j = 0; j < sub_d; ++j) {
+    const float t = __fsub_rn(x[j], c[j]);
+    d = __fadd_rn(d, __fmul_rn(t, t));
+  }
+  return d;
+}
+
+// The same distance with every operation rounded to the key dtype: what the
+// reference's quantisation of appended keys computes, since there both the keys and
+// the stored centroids are dtype tensors (pq_top_k.py:388-404).
+template <typename T>
+__device__ __forceinline__ float pq_dist_dtype(const float* x, const float* c, int sub_d) {
+  float d = 0.f;
+  for (int j = 0; j < sub_d; ++j) {
+    const float t = sah_round_to<T>(__fsub_rn(x[j], c[j]));
+    d = __fadd_rn(d, sah_round_to<T>(__fmul_rn(t, t)));
+  }
+  return sah_round_to<T>(d);
+}
+
+template <typename T, bool DTYPE_MATH>
+__global__ void __launch_bounds__(PQ_TILE)
+pq_assign_kernel(const T* __restrict__ x, int64_t xs_b, int64_t xs_h, int64_t xs_s, int Hkv,
+                 int64_t key_begin, int64_t key_end, int64_t init_offset, int n_sub, int sub_d,
+                 int n_cent, const float* __restrict__ centroids, uint8_t* __restrict__ codes,
+                 int64_t cap) {
+  extern __shared__ float pq_cent_sm[];  // [n_cent][sub_d]
+  const int sub = blockIdx.y;
+  const int64_t bk = blockIdx.z;
+  const int kvh = (int)(bk % Hkv);
+  const int64_t b = bk / Hkv;
+  const int64_t grp = bk * n_sub + sub;
+  for (int i = threadIdx.x; i < n_cent * sub_d; i += PQ_TILE)
+    pq_cent_sm[i] = centroids[grp * n_cent * sub_d + i];
+  __syncthreads();
+  const int64_t j = key_begin + (int64_t)blockIdx.x * PQ_TILE + threadIdx.x;
+  if (j >= key_end) return;
+  const T* xr = x + b * xs_b + kvh * xs_h + j * xs_s + sub * sub_d;
+  float xv[PQ_MAX_SUBD];
+  for (int d = 0; d < sub_d; ++d) xv[d] = sah_to_float<T>(xr[d]);
+  float best = INFINITY;
+  int arg = 0;
+  for (int c = 0; c < n_cent; ++c) {
+    const float dist = DTYPE_MATH ? pq_dist_dtype<T>(xv, pq_cent_sm + c * sub_d, sub_d)
+                                  : pq_dist(xv, pq_cent_sm + c * sub_d, sub_d);
+    if (dist < best) { best = dist; arg = c; }  // first minimum wins, as argmin does
+  }
+  codes[(bk * cap + (j - init_offset)) * n_sub + sub] = (uint8_t)arg;
+}
+
+extern "C" int sah_pq_assign(const void* x, int dtype, int64_t xs_b, int64_t xs_h, int64_t xs_s,
+                             int B, int Hkv, int64_t key_begin, int64_t key_end,
+                             int64_t init_offset, int n_sub, int sub_d, int n_cent,
+                             const float* centroids, uint8_t* codes, int64_t cap, int dtype_math,
+                             void* stream) {
+  SAH_REQUIRE(x && centroids && codes, "pq_assign: null pointer");
+  SAH_REQUIRE(B > 0 && Hkv > 0 && n_sub > 0 && sub_d > 0 && n_cent > 0, "pq_assign: bad extents");
+  SAH_REQUIRE(init_offset <= key_begin && key_begin <= key_end && key_end - init_offset <= cap,
+              "pq_assign: bad key range");
+  if (sub_d > PQ_MAX_SUBD || n_cent > 256)
+    return sah_fail(SAH_ERR_UNSUPPORTED, "pq_assign: sub-vector dim %d (<= %d) / %d centroids (<= 256)",
+                    sub_d, PQ_MAX_SUBD, n_cent);
+  if (key_begin == key_end) return SAH_OK;
+  dim3 grid((unsigned)sah_ceil_div(key_end - key_begin, PQ_TILE), (unsigned)n_sub,
+            (unsigned)((int64_t)B * Hkv));
+  const size_t smem = (size_t)n_cent * sub_d * sizeof(float);
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    if (dtype_math)
+      pq_assign_kernel<T, true><<<grid, PQ_TILE, smem, (cudaStream_t)stream>>>(
+          (const T*)x, xs_b, xs_h, xs_s, Hkv, key_begin, key_end, init_offset, n_sub, sub_d, n_cent,
+          centroids, codes, cap);
+    else
+      pq_assign_kernel<T, false><<<grid, PQ_TILE, smem, (cudaStream_t)stream>>>(
+          (const T*)x, xs_b, xs_h, xs_s, Hkv, key_begin, key_end, init_offset, n_sub, sub_d, n_cent,
+          centroids, codes, cap);
+  });
+  SAH_LAUNCH_CHECK("pq_assign");
+  return SAH_OK;
+}
+
+// Cluster sums in fp64 (so that the summation order does not reach the fp32
+// result) and counts; shared-memory accumulation per CTA, then global atomics.
+template <typename T>
+__global__ void __launch_bounds__(PQ_TILE)
+pq_accumulate_kernel(const T* __restrict__ x, int64_t xs_b, int64_t xs_h, int64_t xs_s, int Hkv,
+                     int64_t n_keys, int64_t init_offset, int n_sub, int sub_d, int n_cent,
+                     const uint8_t* __restrict__ codes, int64_t cap, double* __restrict__ sums,
+                     int* __restrict__ counts) {
+  extern __shared__ double pq_sum_sm[];  // [n_cent][sub_d] then int [n_cent]
+  int* cnt_sm = reinterpret_cast<int*>(pq_sum_sm + n_cent * sub_d);
+  const int sub = blockIdx.y;
+  const int64_t bk = blockIdx.z;
+  const int kvh = (int)(bk % Hkv);
+  const int64_t b = bk / Hkv;
+  const int64_t grp = bk * n_sub + sub;
+  for (int i = threadIdx.x; i < n_cent * sub_d; i += PQ_TILE) pq_sum_sm[i] = 0.0;
+  for (int i = threadIdx.x; i < n_cent; i += PQ_TILE) cnt_sm[i] = 0;
+  __syncthreads();
+  // each CTA walks a strip of keys so that the global atomics stay few
+  const int64_t strip = (n_keys + gridDim.x - 1) / gridDim.x;
+  const int64_t j0 = (int64_t)blockIdx.x * strip;
+  const int64_t j1 = j0 + strip < n_keys ? j0 + strip : n_keys;
+  for (int64_t j = j0 + threadIdx.x; j < j1; j += PQ_TILE) {
+    const int c = codes[(bk * cap + j) * n_sub + sub];
+    const T* xr = x + b * xs_b + kvh * xs_h + (j + init_offset) * xs_s + sub * sub_d;
+    for (int d = 0; d < sub_d; ++d) atomicAdd(&pq_sum_sm[c * sub_d + d], (double)sah_to_float<T>(xr[d]));
+    atomicAdd(&cnt_sm[c], 1);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_cent * sub_d; i += PQ_TILE)
+    if (pq_sum_sm[i] != 0.0) atomicAdd(&sums[grp * n_cent * sub_d + i], pq_sum_sm[i]);
+  for (int i = threadIdx.x; i < n_cent; i += PQ_TILE)
+    if (cnt_sm[i]) atomicAdd(&counts[grp * n_cent + i], cnt_sm[i]);
+}
+
+extern "C" int sah_pq_accumulate(const void* x, int dtype, int64_t xs_b, int64_t xs_h, int64_t xs_s,
+                                 int B, int Hkv, int64_t n_keys, int64_t init_offset, int n_sub,
+                                 int sub_d, int n_cent, const uint8_t* codes, int64_t cap,
+                                 double* sums, int* counts, void* stream) {
+  SAH_REQUIRE(x && codes && sums && counts, "pq_accumulate: null pointer");
+  SAH_REQUIRE(B > 0 && Hkv > 0 && n_sub > 0 && sub_d > 0 && n_cent > 0 && n_keys >= 0,
+              "pq_accumulate: bad extents");
+  if (n_keys == 0) return SAH_OK;
+  int strips = (int)sah_ceil_div(n_keys, 4096);
+  if (strips > 64) strips = 64;
+  dim3 grid((unsigned)strips, (unsigned)n_sub, (unsigned)((int64_t)B * Hkv));
+  const size_t smem = (size_t)n_cent * sub_d * sizeof(double) + (size_t)n_cent * sizeof(int);
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    pq_accumulate_kernel<T><<<grid, PQ_TILE, smem, (cudaStream_t)stream>>>(
+        (const T*)x, xs_b, xs_h, xs_s, Hkv, n_keys, init_offset, n_sub, sub_d, n_cent, codes, cap,
+        sums, counts);
+  });
+  SAH_LAUNCH_CHECK("pq_accumulate");
+  return SAH_OK;
+}
+
+// new centre = fp32(sum) / fp32(count); an empty cluster takes the key sub-vector at
+// reseed[group][cluster] (pq_utils.py:384-396); shift2[group] = (sum over clusters of
+// the centre's Euclidean move)^2, the quantity compared with the tolerance (:399-423).
+template <typename T>
+__global__ void pq_update_kernel(const T* __restrict__ x, int64_t xs_b, int64_t xs_h, int64_t xs_s,
+                                 int Hkv, int64_t init_offset, int n_sub, int sub_d, int n_cent,
+                                 const double* __restrict__ sums, const int* __restrict__ counts,
+                                 const int64_t* __restrict__ reseed, float* __restrict__ centroids,
+                                 float* __restrict__ shift2) {
+  __shared__ float scratch[33];
+  const int64_t grp = blockIdx.x;
+  const int sub = (int)(grp % n_sub);
+  const int64_t bk = grp / n_sub;
+  const int kvh = (int)(bk % Hkv);
+  const int64_t b = bk / Hkv;
+  float move = 0.f;
+  const int c = threadIdx.x;
+  if (c < n_cent) {
+    const int cnt = counts[grp * n_cent + c];
+    float d2 = 0.f;
+    for (int d = 0; d < sub_d; ++d) {
+      float nv;
+      if (cnt > 0) {
+        nv = __fdiv_rn((float)sums[(grp * n_cent + c) * sub_d + d], (float)cnt);
+      } else {
+        const int64_t j = reseed[grp * n_cent + c];
+        nv = sah_to_float<T>(x[b * xs_b + kvh * xs_h + (j + init_offset) * xs_s + sub * sub_d + d]);
+      }
+      float* cp = centroids + (grp * n_cent + c) * sub_d + d;
+      const float t = __fsub_rn(nv, *cp);
+      d2 = __fadd_rn(d2, __fmul_rn(t, t));
+      *cp = nv;
+    }
+    move = sqrtf(d2);
+  }
+  float total;
+  sah_block_excl_scan<float>(move, scratch, &total);
+  if (threadIdx.x == 0) shift2[grp] = total * total;
+}
+
+extern "C" int sah_pq_update(const void* x, int dtype, int64_t xs_b, int64_t xs_h, int64_t xs_s,
+                             int B, int Hkv, int64_t init_offset, int n_sub, int sub_d, int n_cent,
+                             const double* sums, const int* counts, const int64_t* reseed,
+                             float* centroids, float* shift2, void* stream) {
+  SAH_REQUIRE(x && sums && counts && reseed && centroids && shift2, "pq_update: null pointer");
+  SAH_REQUIRE(n_cent > 0 && n_cent <= 256, "pq_update: 1..256 centroids");
+  const int64_t groups = (int64_t)B * Hkv * n_sub;
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    pq_update_kernel<T><<<(unsigned)groups, 256, 0, (cudaStream_t)stream>>>(
+        (const T*)x, xs_b, xs_h, xs_s, Hkv, init_offset, n_sub, sub_d, n_cent, sums, counts, reseed,
+        centroids, shift2);
+  });
+  SAH_LAUNCH_CHECK("pq_update");
+  return SAH_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Scores.  Per CTA: the lookup tables of up to PQ_ROWS mask rows of one KV group
+// (lut[r][sub][c] = q_sub . centroid, fma over ascending dims, rounded to the
+// dtype), then one thread per key sums its n_sub table entries in ascending
+// sub-vector order in fp32 and rounds once (the reference sums a dtype tensor
+// with an fp32 accumulator, pq_top_k.py:481-488).
+// ---------------------------------------------------------------------------
+#define PQ_ROWS 4
+
+template <typename T>
+__global__ void __launch_bounds__(PQ_TILE)
+pq_scores_kernel(const T* __restrict__ q, int64_t qs_b, int64_t qs_h, int64_t qs_q,
+                 const T* __restrict__ centroids, const uint8_t* __restrict__ codes, int64_t cap,
+                 int Hq, int Hkv, int Sq, int64_t n_keys, int64_t init_offset, int64_t S, int n_sub,
+                 int sub_d, int n_cent, T* __restrict__ scores) {
+  extern __shared__ float pq_lut_sm[];  // [PQ_ROWS][n_sub][n_cent]
+  const int G = Hq / Hkv;
+  const int R = G * Sq;  // rows sharing this KV head: r = g * Sq + qi
+  const int64_t bk = blockIdx.z;
+  const int kvh = (int)(bk % Hkv);
+  const int64_t b = bk / Hkv;
+  const int r_base = blockIdx.y * PQ_ROWS;
+  const int lut_row = n_sub * n_cent;
+  for (int idx = threadIdx.x; idx < PQ_ROWS * lut_row; idx += PQ_TILE) {
+    const int rr = idx / lut_row, rem = idx - rr * lut_row;
+    const int sub = rem / n_cent, c = rem - sub * n_cent;
+    const int r = r_base + rr;
+    float v = 0.f;
+    if (r < R) {
+      const int g = r / Sq, qi = r - g * Sq;
+      const T* qp = q + b * qs_b + (int64_t)(kvh * G + g) * qs_h + qi * qs_q + sub * sub_d;
+      const T* cp = centroids + ((bk * n_sub + sub) * n_cent + c) * sub_d;
+      float acc = 0.f;
+      for (int d = 0; d < sub_d; ++d) acc = fmaf(sah_to_float<T>(qp[d]), sah_to_float<T>(cp[d]), acc);
+      v = sah_round_to<T>(acc);
+    }
+    pq_lut_sm[idx] = v;
+  }
+  __syncthreads();
+  const int64_t j = (int64_t)blockIdx.x * PQ_TILE + threadIdx.x;
+  if (j >= n_keys) return;
+  const uint8_t* cj = codes + (bk * cap + j) * n_sub;
+  for (int rr = 0; rr < PQ_ROWS; ++rr) {
+    const int r = r_base + rr;
+    if (r >= R) break;
+    float s = 0.f;
+    for (int sub = 0; sub < n_sub; ++sub)
+      s = __fadd_rn(s, pq_lut_sm[rr * lut_row + sub * n_cent + cj[sub]]);
+    const int g = r / Sq, qi = r - g * Sq;
+    const int64_t row = (b * Hq + kvh * G + g) * Sq + qi;
+    scores[row * S + init_offset + j] = sah_from_float<T>(s);
+  }
+}
+
+extern "C" int sah_pq_scores(const void* q, int dtype, int64_t qs_b, int64_t qs_h, int64_t qs_q,
+                             const void* centroids, const uint8_t* codes, int64_t cap, int B, int Hq,
+                             int Hkv, int Sq, int64_t n_keys, int64_t init_offset, int64_t S,
+                             int n_sub, int sub_d, int n_cent, void* scores, void* stream) {
+  SAH_REQUIRE(q && centroids && codes && scores, "pq_scores: null pointer");
+  SAH_REQUIRE(B > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Sq > 0, "pq_scores: bad heads");
+  SAH_REQUIRE(n_keys >= 0 && init_offset >= 0 && init_offset + n_keys <= S && n_keys <= cap,
+              "pq_scores: bad key range");
+  if (n_keys == 0) return SAH_OK;
+  const int R = (Hq / Hkv) * Sq;
+  const size_t smem = (size_t)PQ_ROWS * n_sub * n_cent * sizeof(float);
+  if (smem > 200 * 1024)
+    return sah_fail(SAH_ERR_UNSUPPORTED, "pq_scores: %d x %d lookup table does not fit", n_sub, n_cent);
+  dim3 grid((unsigned)sah_ceil_div(n_keys, PQ_TILE), (unsigned)sah_ceil_div(R, PQ_ROWS),
+            (unsigned)((int64_t)B * Hkv));
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(pq_scores_kernel<T>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "pq_scores attr: %s", cudaGetErrorString(e));
+    }
+    pq_scores_kernel<T><<<grid, PQ_TILE, smem, (cudaStream_t)stream>>>(
+        (const T*)q, qs_b, qs_h, qs_q, (const T*)centroids, codes, cap, Hq, Hkv, Sq, n_keys,
+        init_offset, S, n_sub, sub_d, n_cent, (T*)scores);
+  });
+  SAH_LAUNCH_CHECK("pq_scores");
+  return SAH_OK;
+}

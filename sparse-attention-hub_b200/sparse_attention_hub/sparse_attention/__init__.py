@@ -12,6 +12,8 @@ from .research_attention.maskers.fixed import (
     LocalMaskerConfig,
     OracleTopK,
     OracleTopKConfig,
+    PQCache,
+    PQCacheConfig,
     SinkMasker,
     SinkMaskerConfig,
     TopKMasker,
@@ -26,5 +28,5 @@ __all__ = [
     "ResearchMasker", "SamplingMasker", "FixedMasker", "TopKMasker", "TopKMaskerConfig",
     "TopPMasker", "LocalMasker", "LocalMaskerConfig", "CausalMasker", "SinkMasker",
     "SinkMaskerConfig", "OracleTopK", "OracleTopKConfig", "HashAttentionTopKMasker",
-    "HashAttentionTopKMaskerConfig", "Mask",
+    "HashAttentionTopKMaskerConfig", "PQCache", "PQCacheConfig", "Mask",
 ]

@@ -16,6 +16,8 @@ from .implementations import (
     LocalMaskerConfig,
     OracleTopK,
     OracleTopKConfig,
+    PQCache,
+    PQCacheConfig,
     SinkMasker,
     SinkMaskerConfig,
 )
@@ -24,5 +26,5 @@ __all__ = [
     "FixedMasker", "TopKMasker", "TopPMasker", "FixedMaskerConfig", "TopKMaskerConfig",
     "TopPMaskerConfig", "LocalMasker", "CausalMasker", "SinkMasker", "OracleTopK",
     "HashAttentionTopKMasker", "LocalMaskerConfig", "SinkMaskerConfig", "OracleTopKConfig",
-    "HashAttentionTopKMaskerConfig",
+    "HashAttentionTopKMaskerConfig", "PQCache", "PQCacheConfig",
 ]

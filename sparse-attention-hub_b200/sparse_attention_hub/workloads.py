@@ -153,6 +153,26 @@ def oracle_topk(seed: int = 0, dtype: str = "bf16", B: int = 4, Hq: int = 32, Hk
          ("oracle_topk", {"heavy_size": heavy})])
 
 
+def pqcache(seed: int = 0, dtype: str = "bf16", B: int = 1, Hq: int = 32, Hkv: int = 8,
+            S: int = 131072, D: int = 128, sink: int = 64, window: int = 256, heavy=2048,
+            group_factor: int = 16, bits: int = 8, kmeans_iter: int = 10, Sq: int = 1,
+            n_clusters: int = 256) -> DecodeWorkload:
+    """Keys from a mixture of Gaussian clusters; Sink + Local + PQCache top-k."""
+    q, k, v = qkv_clustered(seed, B, Hq, Hkv, S, D, Sq, n_clusters=n_clusters)
+    return DecodeWorkload(
+        "pqcache_" + dtype, dtype, to_dtype(q, dtype), to_dtype(k, dtype), to_dtype(v, dtype),
+        1.0 / np.sqrt(D),
+        [("sink", {"sink_size": sink}), ("local", {"window_size": window}),
+         ("pq_topk", {"heavy_size": heavy, "pq_group_factor": group_factor, "pq_bits": bits,
+                      "kmeans_iter": kmeans_iter, "init_offset": sink, "metric": "euclidean"})])
+
+
+def pq_init_indices(seed: int, groups: int, n_keys: int, n_cent: int) -> np.ndarray:
+    """Seeded k-means initialisation: per group the first `n_cent` entries of a permutation."""
+    rng = _rng(seed, 60)
+    return np.stack([rng.permutation(n_keys)[:n_cent] for _ in range(groups)]).astype(np.int64)
+
+
 # ---------------------------------------------------------------------------
 # Turning a workload into device tensors and masker configs
 # ---------------------------------------------------------------------------
@@ -187,10 +207,13 @@ def masker_configs(stack: List[Tuple[str, Dict[str, Any]]], dtype: str, device="
                 heavy_size=prm["heavy_size"], hat_bits=prm["bits"], hat_mlp_layers=prm["layers"],
                 hat_mlp_hidden_size=prm["hidden"], hat_mlp_activation=prm["activation"],
                 hat_weights=w))
+        elif kind == "pq_topk":
+            out.append(fixed.PQCacheConfig(
+                heavy_size=prm["heavy_size"], pq_group_factor=prm["pq_group_factor"],
+                pq_bits=prm["pq_bits"], kmeans_iter=prm["kmeans_iter"],
+                init_offset=prm["init_offset"], metric=prm["metric"]))
         else:
-            from . import workloads_extra
-
-            out.append(workloads_extra.masker_config(kind, prm, dtype, device))
+            raise ValueError(f"unknown masker kind {kind}")
     return out
 
 
