@@ -202,6 +202,43 @@ int sah_topk_select(const void* scores, int dtype, int64_t rows, int64_t S, int6
                     int64_t k, uint32_t* out_bits, void* stream);
 
 /* ------------------------------------------------------------------------ *
+ * Adaptive sampling  (maskers/sampling/implementations/adaptive_sampling.py)
+ * ------------------------------------------------------------------------ */
+
+/* Per-row sample budget and sampling probability of the (epsilon, delta) masker
+ * (add_mask :304-407): exp weights of the scaled scores in `dtype`
+ * (_compute_exp_attention_scores :183-197), static denominator over the previous
+ * mask under its inverse weights (apply_inv_mask_sum), base sample of `nb` draws
+ * in [start, end) -> unbiased standard deviation and denominator estimate
+ * (_get_std_estimate_using_base_sample :237-280), budget
+ * clamp((ppf * std * n / max(eps * den, 1e-8))^2, 1, n) truncated, then clamped to
+ * [nb, n] (_compute_adaptive_budget :282-302, :394), probability budget / n.
+ * Every tensor operation of the reference is one rounding to `dtype`; sums run in
+ * a fixed order (1024 strided partial sums, then xor trees over lanes and warps).
+ *   scores      [rows][S] unscaled q.k in `dtype` (sah_qk_scores without bias)
+ *   prev_bits   NULL when the previous mask is empty or full (plain sum)
+ *   base_draws  optional int64 [rows][nb] columns; NULL: Philox4x32-10 of
+ *               (seed, row * nb + i) mapped to start + floor(u * n / 2^32)
+ *   exp_table   uint16[65536] bf16 exp table (SAH_BF16 only)
+ *   budget      int64 [rows];  prob `dtype` [rows];  stats optional float [rows][4]
+ *               (static denominator, std, estimated denominator, squared ratio) */
+int sah_adaptive_budget(const void* scores, int dtype, float scaling, const void* bias,
+                        int64_t bias_s_b, int64_t bias_s_h, int64_t bias_s_q,
+                        const uint32_t* prev_bits, const void* prev_data, const int32_t* wpre,
+                        const int64_t* ptr, int B, int Hq, int Sq, int64_t S, int64_t W,
+                        int64_t start, int64_t end, int64_t nb, uint64_t seed,
+                        const int64_t* base_draws, const uint16_t* exp_table, float delta_ppf,
+                        float epsilon, int64_t* budget, void* prob, float* stats, void* stream);
+
+/* Budgeted draws into a bitmap (create_sampling_mask_with_per_head_budget,
+ * utils/mask_attention_utils.py:105-184): sample j < sptr[rows] belongs to the row
+ * r with sptr[r] <= j < sptr[r+1] and is column pool[j], or, with pool == NULL,
+ * start + floor(philox(seed, j) * n / 2^32).  `bits` must be zeroed by the caller. */
+int sah_sample_scatter(const int64_t* sptr, int64_t rows, const int64_t* pool, uint64_t seed,
+                       int64_t start, int64_t n, int64_t S, int64_t W, int sm_count,
+                       uint32_t* bits, void* stream);
+
+/* ------------------------------------------------------------------------ *
  * PQCache  (maskers/fixed/implementations/pq_top_k.py, utils/pq_utils.py)
  * ------------------------------------------------------------------------ */
 

@@ -82,6 +82,9 @@ _SIGNATURES = {
                              _L, _I, c_float, _P, _L, _L, _L, _P, POINTER(AttnSizes), _P, _P, _P,
                              _P, _P, _P, _P, _P, _P],
     "sah_attn_merge_parts": [_P, _P, _I, _I, _I, _I, _I, _P, _I, _P, _P],
+    "sah_adaptive_budget": [_P, _I, c_float, _P, _L, _L, _L, _P, _P, _P, _P, _I, _I, _I, _L, _L, _L,
+                            _L, _L, ctypes.c_uint64, _P, _P, c_float, c_float, _P, _P, _P, _P],
+    "sah_sample_scatter": [_P, _L, _P, ctypes.c_uint64, _L, _L, _L, _L, _I, _P, _P],
     "sah_pq_assign": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _L, _I, _I, _I, _P, _P, _L, _I, _P],
     "sah_pq_accumulate": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _I, _I, _I, _P, _L, _P, _P, _P],
     "sah_pq_update": [_P, _I, _L, _L, _L, _I, _I, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P],

@@ -20,7 +20,13 @@ from .research_attention.maskers.fixed import (
     TopKMaskerConfig,
     TopPMasker,
 )
-from .research_attention.maskers.sampling import SamplingMasker
+from .research_attention.maskers.sampling import (
+    AdaptiveSamplingMasker,
+    AdaptiveSamplingMaskerConfig,
+    RandomSamplingMasker,
+    RandomSamplingMaskerConfig,
+    SamplingMasker,
+)
 from .utils import Mask
 
 __all__ = [
@@ -28,5 +34,6 @@ __all__ = [
     "ResearchMasker", "SamplingMasker", "FixedMasker", "TopKMasker", "TopKMaskerConfig",
     "TopPMasker", "LocalMasker", "LocalMaskerConfig", "CausalMasker", "SinkMasker",
     "SinkMaskerConfig", "OracleTopK", "OracleTopKConfig", "HashAttentionTopKMasker",
-    "HashAttentionTopKMaskerConfig", "PQCache", "PQCacheConfig", "Mask",
+    "HashAttentionTopKMaskerConfig", "PQCache", "PQCacheConfig", "RandomSamplingMasker",
+    "RandomSamplingMaskerConfig", "AdaptiveSamplingMasker", "AdaptiveSamplingMaskerConfig", "Mask",
 ]

@@ -197,3 +197,91 @@ def hash_topk(kcodes: torch.Tensor, n_keys: int, qcodes: torch.Tensor, nbits: in
         "sah_hash_topk")
     del keep
     return dst
+
+
+# ---- sampled sets ---------------------------------------------------------------
+def merge_sampled(previous_mask: Mask, cols: torch.Tensor, sptr: torch.Tensor,
+                  row_weight: torch.Tensor) -> Mask:
+    """`clamp(previous + sampled, 0, 1)` (Mask.merge_mask_dense) for a ragged sample list.
+
+    `cols` int64 [n] are key columns, sample j belongs to the row r with
+    sptr[r] <= j < sptr[r+1]; every sampled position carries `row_weight[row]`
+    (mask dtype).  Duplicates collapse to one entry; a position already active in the
+    previous (unit-weight) mask keeps weight 1.  No host synchronisation: the weight
+    array is sized for the worst case and the CSR pointers stay on the device.
+    """
+    _native.require_cuda(cols, "sampled columns")
+    lib = _native.load()
+    shape = tuple(previous_mask.shape)
+    S = shape[-1]
+    rows = _rows(shape)
+    dev = cols.device
+    st = _native.stream_of(dev)
+    dtype = previous_mask.dtype
+    prev = unit_weight_bits(previous_mask)
+    words = words_per_row(S)
+    samp = torch.zeros((rows, words), dtype=torch.int32, device=dev)
+    cols = cols.contiguous()
+    sptr = sptr.to(torch.int64).contiguous()
+    _native.check(lib.sah_mask_scatter_samples(cols.data_ptr(), sptr.data_ptr(), rows, cols.numel(), S,
+                                               words, samp.data_ptr(), st), "sah_mask_scatter_samples")
+    return merge_sampled_bits(previous_mask, samp, row_weight, cols.numel())
+
+
+def merge_sampled_bits(previous_mask: Mask, samp: torch.Tensor, row_weight: torch.Tensor,
+                       n_samples_bound: int) -> Mask:
+    """Second half of `merge_sampled`: the sampled set is already a bitmap `[rows, W]`."""
+    lib = _native.load()
+    shape = tuple(previous_mask.shape)
+    S = shape[-1]
+    rows = _rows(shape)
+    dev = samp.device
+    st = _native.stream_of(dev)
+    dtype = previous_mask.dtype
+    prev = unit_weight_bits(previous_mask)
+    words = samp.shape[-1]
+    if prev is None:
+        # weighted (or full) previous mask: the general dense merge
+        add = Mask._from_native(shape, dtype, _sampled_native(samp, None, rows, S, words, row_weight,
+                                                              dtype, n_samples_bound))
+        return previous_mask.merge_mask(add, inplace=False)
+    merged = torch.empty_like(samp)
+    _native.check(lib.sah_mask_or(prev.bits.data_ptr(), samp.data_ptr(), rows * words,
+                                  merged.data_ptr(), st), "sah_mask_or")
+    # the number of entries is only known on the device: size the weights for the worst case
+    nb = _sampled_native(merged, prev.bits, rows, S, words, row_weight, dtype, rows * S)
+    return Mask._from_native(shape, dtype, nb)
+
+
+_EXP_TABLES: dict = {}
+
+
+def exp_table(device: torch.device) -> torch.Tensor:
+    """uint16[65536]: bf16 bit pattern of x -> bf16 bit pattern of exp(x) (float64 evaluation,
+    rounded through float32), for kernels that reproduce a bf16 `torch.exp`."""
+    key = str(device)
+    if key not in _EXP_TABLES:
+        x = _bf16_bits_to_f64(np.arange(65536, dtype=np.uint32))
+        with np.errstate(over="ignore", invalid="ignore"):
+            y = np.exp(x)
+        table = _f64_to_bf16_bits(np.where(np.isnan(x), x, y))
+        _EXP_TABLES[key] = torch.from_numpy(table.view(np.int16).copy()).to(device)
+    return _EXP_TABLES[key]
+
+
+def _sampled_native(bits: torch.Tensor, prev_bits: Optional[torch.Tensor], rows: int, S: int,
+                    words: int, row_weight: torch.Tensor, dtype: torch.dtype,
+                    nnz_bound: int) -> NativeBits:
+    lib = _native.load()
+    dev = bits.device
+    st = _native.stream_of(dev)
+    nb = NativeBits(bits, rows, S)
+    nb.ensure_scan()
+    data = torch.empty(min(nnz_bound, rows * S), dtype=dtype, device=dev)
+    rw = row_weight.to(dtype).reshape(rows).contiguous()
+    _native.check(
+        lib.sah_mask_sample_data(_native.ptr(prev_bits), bits.data_ptr(), nb.wpre.data_ptr(),
+                                 nb.ptr.data_ptr(), rw.data_ptr(), None, _native.dtype_code(dtype),
+                                 rows, S, words, data.data_ptr(), st), "sah_mask_sample_data")
+    nb.data = data
+    return nb

@@ -58,11 +58,14 @@ class ResearchAttention(SparseAttention):
         """The masker loop alone: empty mask -> every masker in order."""
         shape = (queries.shape[0], queries.shape[1], queries.shape[2], keys.shape[2])
         mask = Mask.create_empty_mask(shape, dtype=queries.dtype, device=queries.device)
+        # Scratch shared by the maskers of this one call (e.g. the q.k score stream that both
+        # OracleTopK and adaptive sampling need); maskers that do not know the key ignore it.
+        call_cache: Dict[str, Any] = {}
         for masker in self.maskers:
             mask = masker.add_mask(keys=keys, queries=queries, values=values,
                                    attention_mask=attention_mask, scaling=scaling,
                                    dropout=dropout, sparse_meta_data=sparse_meta_data,
-                                   previous_mask=mask, **kwargs)
+                                   previous_mask=mask, _sah_call_cache=call_cache, **kwargs)
         return mask
 
     def custom_attention(self, module: Optional[nn.Module], queries: torch.Tensor,

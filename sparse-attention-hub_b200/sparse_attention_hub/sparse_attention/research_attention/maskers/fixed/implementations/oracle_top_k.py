@@ -45,12 +45,16 @@ class OracleTopK(TopKMasker):
         heavy = self._calculate_effective_heavy_size(dims.seq_len_keys)
         if self._should_use_full_attention(dims, heavy):
             return self._create_full_mask(dims, previous_mask.dtype, previous_mask.device)
-        return self.get_updated_mask(dims, heavy, keys, queries, attention_mask, previous_mask)
+        return self.get_updated_mask(dims, heavy, keys, queries, attention_mask, previous_mask,
+                                     call_cache=kwargs.get("_sah_call_cache"))
 
     def get_updated_mask(self, tensor_dims: AttentionTensorDimensions, effective_heavy_size: int,
                          keys: torch.Tensor, queries: torch.Tensor, attention_mask: torch.Tensor,
-                         previous_mask: Mask, mode: str = "native") -> Mask:
+                         previous_mask: Mask, mode: str = "native", call_cache=None) -> Mask:
         scores = self._compute_raw_attention_scores(keys, queries, attention_mask)
+        if call_cache is not None and attention_mask is None:
+            # later maskers of the same call (adaptive sampling) need the same q.k stream
+            call_cache["qk_scores"] = scores
         if _native_ops.unit_weight_bits(previous_mask) is None:
             # weighted previous mask: winners are written into its dense form
             merged = _native_ops.topk_select(scores, previous_mask, effective_heavy_size)

@@ -368,7 +368,7 @@ class Mask:
                                              idx.data_ptr(), _native.stream_of(dev)),
                 "sah_mask_bits_to_indices",
             )
-        data = nb.data if nb.data is not None else torch.ones(nnz, dtype=self.dtype, device=dev)
+        data = nb.data[:nnz] if nb.data is not None else torch.ones(nnz, dtype=self.dtype, device=dev)
         return idx, nb.ptr, data
 
     def native_bits(self) -> NativeBits:

@@ -153,6 +153,19 @@ def oracle_topk(seed: int = 0, dtype: str = "bf16", B: int = 4, Hq: int = 32, Hk
          ("oracle_topk", {"heavy_size": heavy})])
 
 
+def oracle_adaptive(seed: int = 0, dtype: str = "bf16", B: int = 4, Hq: int = 32, Hkv: int = 8,
+                    S: int = 65536, D: int = 128, sink: int = 128, window: int = 512, heavy=0.02,
+                    base_rate=0.05, epsilon: float = 0.05, delta: float = 0.05,
+                    Sq: int = 1) -> DecodeWorkload:
+    """Sink + Local + oracle top-k + adaptive (epsilon, delta) sampling over the rest."""
+    wl = oracle_topk(seed, dtype, B, Hq, Hkv, S, D, sink, window, heavy, Sq)
+    wl.name = "oracle_adaptive_" + dtype
+    wl.stack = wl.stack + [("adaptive_sampling", {
+        "base_rate_sampling": base_rate, "epsilon": epsilon, "delta": delta,
+        "init_offset": sink, "local_offset": window})]
+    return wl
+
+
 def pqcache(seed: int = 0, dtype: str = "bf16", B: int = 1, Hq: int = 32, Hkv: int = 8,
             S: int = 131072, D: int = 128, sink: int = 64, window: int = 256, heavy=2048,
             group_factor: int = 16, bits: int = 8, kmeans_iter: int = 10, Sq: int = 1,
@@ -212,6 +225,14 @@ def masker_configs(stack: List[Tuple[str, Dict[str, Any]]], dtype: str, device="
                 heavy_size=prm["heavy_size"], pq_group_factor=prm["pq_group_factor"],
                 pq_bits=prm["pq_bits"], kmeans_iter=prm["kmeans_iter"],
                 init_offset=prm["init_offset"], metric=prm["metric"]))
+        elif kind == "adaptive_sampling":
+            from .sparse_attention.research_attention.maskers import sampling
+            out.append(sampling.AdaptiveSamplingMaskerConfig(
+                base_rate_sampling=prm["base_rate_sampling"], epsilon=prm["epsilon"],
+                delta=prm["delta"], init_offset=prm["init_offset"], local_offset=prm["local_offset"]))
+        elif kind == "random_sampling":
+            from .sparse_attention.research_attention.maskers import sampling
+            out.append(sampling.RandomSamplingMaskerConfig(sampling_rate=prm["sampling_rate"]))
         else:
             raise ValueError(f"unknown masker kind {kind}")
     return out
