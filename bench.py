@@ -62,6 +62,14 @@ def make_workload(name: str, seed: int, small: bool = False):
         if small:
             return workloads.oracle_topk(seed=seed, B=1, S=8192)
         return workloads.oracle_topk(seed=seed)
+    if name == "oracle_adaptive":
+        if small:
+            return workloads.oracle_adaptive(seed=seed, B=1, S=8192)
+        return workloads.oracle_adaptive(seed=seed)
+    if name == "pqcache":
+        if small:
+            return workloads.pqcache(seed=seed, S=16384, heavy=512, kmeans_iter=3)
+        return workloads.pqcache(seed=seed)
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -160,6 +168,22 @@ def cpu_baseline(wl, name: str, steps: int, warmup: int, budget_s: float = 25.0)
             w = prm["weights"]
             meta["hash_kcodes"] = o_hash.signatures_blas(o_attn.repeat_kv(k, G), w["key_matrix"],
                                                          w["key_bias"], prm["activation"], wl.dtype)
+        if kind == "pq_topk":
+            # The decode step's cost does not depend on how good the codebook is: centres are
+            # the seeded initial keys (no Lloyd iteration), codes their nearest-centre assignment.
+            from oracle import pq as o_pq
+            from oracle.bf16 import round_to
+            from sparse_attention_hub import workloads as wls
+            off, n_sub, cent = prm["init_offset"], prm["pq_group_factor"], 2 ** prm["pq_bits"]
+            X = o_pq.split_keys(k, off, n_sub)
+            idx = wls.pq_init_indices(0, X.shape[0], X.shape[1], cent)
+            C = X[np.arange(X.shape[0])[:, None], idx]
+            codes = np.concatenate([o_pq.assign(X[g:g + 1], C[g:g + 1]) for g in range(X.shape[0])])
+            Hkv_, n_ = k.shape[1], X.shape[1]
+            meta["pq_centroids"] = round_to(C, wl.dtype).reshape(1, Hkv_, n_sub, cent, -1)
+            meta["pq_codes"] = codes.reshape(1, Hkv_, n_sub, n_).transpose(0, 1, 3, 2)
+        if kind == "adaptive_sampling":
+            meta["adaptive_seed"] = 0
     t_build = time.perf_counter() - t_build0
 
     def step():
@@ -315,6 +339,11 @@ def run_native(args) -> None:
         stage_bytes["hash_topk"] = B * Hq * S * 4
     if any(kind == "oracle_topk" for kind, _ in wl.stack):
         stage_bytes["qk_scores"] = B * Hkv * S * D * esz
+    for kind, prm in wl.stack:
+        if kind == "pq_topk":  # one byte per sub-vector code per key and KV head
+            stage_bytes["pq_scores"] = B * Hkv * (S - prm["init_offset"]) * prm["pq_group_factor"]
+        if kind == "adaptive_sampling":  # the q.k scores of every row, read once
+            stage_bytes["adaptive_budget"] = B * Hq * Sq * S * esz
     step_bytes = sum(stage_bytes.values())
 
     # e2e: host buffers in, host result out, incremental key append
@@ -379,6 +408,15 @@ def run_native(args) -> None:
         attn_avg_ms = attn_ms / max(attn_n, 1)
         achieved = attn_bytes / (attn_avg_ms * 1e-3) / 1e9 if attn_avg_ms > 0 else 0.0
         stage_times = {s: (ms / max(n, 1)) * 1e3 for s, (ms, n) in prof.items() if n > 0}
+        # DRAM traffic of one attention launch: ncu (dram__bytes_read.sum + dram__bytes_write.sum)
+        # measured 225 636 096 B for a launch of this workload whose algorithmic bytes were
+        # 219 225 088 B (profiles/sections_decode_kernels_hashattention.md); traffic grows with
+        # the rows gathered, so the launch timed here is scaled by that ratio.
+        traffic, traffic_src = None, None
+        if args.workload == "hashattention" and not args.small:
+            traffic = attn_bytes * (225636096.0 / 219225088.0)
+            traffic_src = ("ncu capture of one launch of this workload (read + write), scaled by "
+                           "algorithmic bytes of the timed launch")
         base = None
         if world == 1 and not args.no_cpu_baseline:
             base = cpu_baseline(wl, args.workload, steps=10, warmup=2)
@@ -415,7 +453,7 @@ def run_native(args) -> None:
                 "frac_of_nominal_8TBs": achieved / 8000.0,
                 "algorithmic_bytes_per_launch": attn_bytes,
                 "avg_launch_us": attn_avg_ms * 1e3, "launches_timed": attn_n,
-                "traffic": None,
+                "traffic": traffic, "traffic_source": traffic_src,
             },
             "e2e": {
                 "value": tokens / (e2e_total / args.steps), "unit": UNIT,
