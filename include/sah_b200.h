@@ -239,6 +239,80 @@ int sah_sample_scatter(const int64_t* sptr, int64_t rows, const int64_t* pool, u
                        uint32_t* bits, void* stream);
 
 /* ------------------------------------------------------------------------ *
+ * Merge of two weighted bitmap masks  (Mask.merge_mask_dense, utils/mask.py:809-891)
+ * ------------------------------------------------------------------------ */
+
+/* out = clamp(a + b, 0, 1) in the mask dtype; an entry is active when the sum is
+ * non-zero.  Each side is bits [rows][W] with an optional CSR weight array (data
+ * NULL = unit weights; with data, wpre and ptr of sah_mask_rowscan are needed).
+ * Pass 1 writes the result's bitmap; the caller runs sah_mask_rowscan on it; pass 2
+ * writes the result's weights in CSR order. */
+int sah_mask_merge_bits(const uint32_t* a_bits, const void* a_data, const int32_t* a_wpre,
+                        const int64_t* a_ptr, const uint32_t* b_bits, const void* b_data,
+                        const int32_t* b_wpre, const int64_t* b_ptr, int dtype, int64_t rows,
+                        int64_t W, uint32_t* out_bits, void* stream);
+int sah_mask_merge_data(const uint32_t* a_bits, const void* a_data, const int32_t* a_wpre,
+                        const int64_t* a_ptr, const uint32_t* b_bits, const void* b_data,
+                        const int32_t* b_wpre, const int64_t* b_ptr, int dtype, int64_t rows,
+                        int64_t W, const uint32_t* out_bits, const int32_t* out_wpre,
+                        const int64_t* out_ptr, void* out_data, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * MagicPig: SimHash sampling  (maskers/sampling/implementations/magic_pig.py)
+ * ------------------------------------------------------------------------ */
+
+/* Signatures are stored once per KV head (the reference hashes keys repeated over
+ * the query heads of a group with one projection per layer, magic_pig.py:564-565,
+ * :476-491), table-major: planes[(b*Hkv + h)*L + l][cap] holds the code of every
+ * key for table l (bit j of a code = sign bit of projection column l*K + j,
+ * :120-150); codes are uint8 for lsh_k <= 8 and uint16 for lsh_k <= 16 (larger
+ * lsh_k: SAH_ERR_UNSUPPORTED).  cap is a multiple of 32 keys; codes past the
+ * last key must be zero.  head_dim must be a multiple of 32, at most 256. */
+
+/* sums[(b*Hkv + h)*D + d] += sum over keys [s0, s1) in float64 (the key mean of
+ * _center_KQ, :152-183, is sums / S rounded to the dtype; the caller zeroes sums). */
+int sah_lsh_key_sums(const void* keys, int dtype, int64_t ks_b, int64_t ks_h, int64_t ks_s, int B,
+                     int Hkv, int64_t s0, int64_t s1, int D, double* sums, void* stream);
+
+/* norms[(b*Hkv + h)*cap + s] = |k_s - mean| rounded to the dtype, for s in [s0, s1);
+ * *max_norm_bits = max(*max_norm_bits, bits of the largest such norm): the global
+ * maximum key norm of _transform_for_mips (:348-353).  mean [B*Hkv][D] in the key
+ * dtype, or NULL when center=False. */
+int sah_lsh_key_stats(const void* keys, int dtype, int64_t ks_b, int64_t ks_h, int64_t ks_s, int B,
+                      int Hkv, int64_t s0, int64_t s1, int D, const void* mean, int64_t cap,
+                      float* norms, unsigned int* max_norm_bits, int sm_count, void* stream);
+
+/* Signatures of keys [s0, s1): centre, scale by the maximum norm, append
+ * sqrt(M^2 - |k|^2) / M (:332-372), project with proj [D+1][L*K] (key dtype), take
+ * sign bits (bit = projection > 0), pack per table. */
+int sah_lsh_key_sign(const void* keys, int dtype, int64_t ks_b, int64_t ks_h, int64_t ks_s, int B,
+                     int Hkv, int64_t s0, int64_t s1, int D, const void* mean, const float* norms,
+                     const unsigned int* max_norm_bits, const void* proj, int L, int K,
+                     int64_t cap, void* planes, void* stream);
+
+/* Per mask row (b, h, q): centred query normalised to unit length, its L codes
+ * (qcodes [rows][L], same code type as the planes) and the unit vector of the
+ * transformed query (qunit float [rows][D]; the appended column is zero). */
+int sah_lsh_query(const void* q, int dtype, int64_t qs_b, int64_t qs_h, int64_t qs_q, int B, int Hq,
+                  int Sq, int G, int D, const void* mean, const void* proj, int L, int K,
+                  void* qcodes, float* qunit, void* stream);
+
+/* out_bits[row][w]: keys whose code equals the query's in at least one table
+ * (_compute_matches_int64, :455-463).  Every word of every row is written. */
+int sah_lsh_match(const void* planes, int64_t cap, const void* qcodes, int B, int Hq, int Sq, int G,
+                  int L, int K, int64_t S, int64_t W, uint32_t* out_bits, void* stream);
+
+/* data[ptr[row] + i] = collision probability 1 - (1 - (1 - theta/pi)^K)^L of the
+ * i-th set bit of the row (:374-403), theta the angle between the transformed
+ * key and query, every operation rounded to the dtype.  bf16 needs `table`,
+ * uint16 [65536]: bits of the clamped cosine -> bits of the probability. */
+int sah_lsh_prob(const void* keys, int dtype, int64_t ks_b, int64_t ks_h, int64_t ks_s, int B,
+                 int Hq, int Sq, int G, int D, const void* mean, const float* norms, int64_t cap,
+                 const unsigned int* max_norm_bits, const float* qunit, const uint32_t* bits,
+                 const int32_t* wpre, const int64_t* ptr, int64_t W, int K, int L,
+                 const uint16_t* table, void* data, int sm_count, void* stream);
+
+/* ------------------------------------------------------------------------ *
  * PQCache  (maskers/fixed/implementations/pq_top_k.py, utils/pq_utils.py)
  * ------------------------------------------------------------------------ */
 

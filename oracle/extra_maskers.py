@@ -30,6 +30,9 @@ def apply(kind, prm, st, q, k, v, scaling, attention_mask, meta) -> None:
         full[..., off:off + n] = s
         sel = topk.topk_inactive(full, st.mask != 0, heavy, off, off + n)
         st.set(mask_ops.merge(st.mask, sel.astype(np.float32), st.dtype))
+    elif kind == "magicpig":
+        from . import magicpig
+        magicpig.apply(prm, st, q, k, meta)
     elif kind in ("random_sampling", "adaptive_sampling"):
         _apply_sampling(kind, prm, st, q, k, v, scaling, attention_mask, meta)
     else:

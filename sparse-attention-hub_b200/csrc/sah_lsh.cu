@@ -1,0 +1,566 @@
+// MagicPig: SimHash (LSH) sampling of keys (maskers/sampling/implementations/magic_pig.py).
+//
+//   sah_lsh_key_sums      per (batch, KV head, channel) sum of the keys in float64 (key mean, :152-183)
+//   sah_lsh_key_stats     norm of every centred key and the running maximum norm (:348-353)
+//   sah_lsh_key_sign      MIPS transform + random-hyperplane signatures of keys, packed per table (:332-372, :120-150)
+//   sah_lsh_query         centred, normalised query, its signatures and its unit vector (:152-183, :332-403)
+//   sah_lsh_match         keys that share at least one table code with the query (:455-463)
+//   sah_lsh_prob          collision probability of every matched key (:374-403)
+//
+// Signatures are stored table-major: plane l of (batch, KV head) holds the code of every key
+// for table l, one code per key (uint8 for lsh_k <= 8, uint16 for lsh_k <= 16), so that the
+// match kernel streams each plane with 16-byte loads.  The reference repeats keys over the
+// query heads of a group and uses one projection per layer, so the signatures of a group's
+// heads are identical and are stored once per KV head.
+//
+// Reductions over the head dimension use one fixed order ("lane order"): lane t of a warp
+// owns the D/32 consecutive channels starting at t*D/32 and sums them in ascending order,
+// then the 32 lane sums combine by xor shuffles 16, 8, 4, 2, 1.  Every tensor operation of
+// the reference is one rounding to the dtype here.
+#include "sah_common.cuh"
+
+#define LSH_MAX_PER_LANE 8  // D <= 256
+
+__device__ __forceinline__ float lsh_warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// ---------------------------------------------------------------------------------------
+// key sums
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void lsh_key_sums_kernel(const T* __restrict__ k, int64_t ks_b, int64_t ks_h,
+                                    int64_t ks_s, int Hkv, int64_t s0, int64_t s1, int D,
+                                    int64_t chunk, double* __restrict__ sums) {
+  const int64_t bh = blockIdx.y;
+  const int64_t b = bh / Hkv, h = bh % Hkv;
+  const int64_t lo = s0 + (int64_t)blockIdx.x * chunk;
+  const int64_t hi = lo + chunk < s1 ? lo + chunk : s1;
+  const T* base = k + b * ks_b + h * ks_h;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    double acc = 0.0;
+    for (int64_t s = lo; s < hi; ++s) acc += (double)sah_to_float<T>(base[s * ks_s + d]);
+    atomicAdd(&sums[bh * D + d], acc);
+  }
+}
+
+extern "C" int sah_lsh_key_sums(const void* keys, int dtype, int64_t ks_b, int64_t ks_h,
+                                int64_t ks_s, int B, int Hkv, int64_t s0, int64_t s1, int D,
+                                double* sums, void* stream) {
+  SAH_REQUIRE(keys && sums, "lsh_key_sums: null pointer");
+  SAH_REQUIRE(B > 0 && Hkv > 0 && D > 0 && s0 >= 0 && s1 >= s0, "lsh_key_sums: bad extents");
+  if (s1 == s0) return SAH_OK;
+  const int64_t chunk = 256;
+  dim3 grid((unsigned)((s1 - s0 + chunk - 1) / chunk), (unsigned)(B * Hkv));
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    lsh_key_sums_kernel<T><<<grid, 128, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const T*>(keys), ks_b, ks_h, ks_s, Hkv, s0, s1, D, chunk, sums);
+  });
+  SAH_LAUNCH_CHECK("lsh_key_sums");
+  return SAH_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// key statistics: norm of the centred key, running maximum
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void lsh_load_lane(const T* row, int per, int lane, float* x) {
+#pragma unroll
+  for (int t = 0; t < LSH_MAX_PER_LANE; ++t)
+    if (t < per) x[t] = sah_to_float<T>(row[lane * per + t]);
+}
+
+template <typename T>
+__global__ void lsh_key_stats_kernel(const T* __restrict__ k, int64_t ks_b, int64_t ks_h,
+                                     int64_t ks_s, int Hkv, int64_t s0, int64_t s1, int D,
+                                     const T* __restrict__ mean, int64_t cap,
+                                     float* __restrict__ norms, unsigned int* __restrict__ max_bits) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const int64_t bh = blockIdx.y;
+  const int64_t b = bh / Hkv, h = bh % Hkv;
+  const int per = D / 32;
+  float m[LSH_MAX_PER_LANE];
+  if (mean) lsh_load_lane<T>(mean + bh * D, per, lane, m);
+  float local_max = 0.f;
+  for (int64_t s = s0 + (int64_t)blockIdx.x * nwarp + warp; s < s1; s += (int64_t)gridDim.x * nwarp) {
+    float x[LSH_MAX_PER_LANE];
+    lsh_load_lane<T>(k + b * ks_b + h * ks_h + s * ks_s, per, lane, x);
+    float acc = 0.f;
+#pragma unroll
+    for (int t = 0; t < LSH_MAX_PER_LANE; ++t)
+      if (t < per) {
+        const float c = mean ? sah_round_to<T>(__fsub_rn(x[t], m[t])) : x[t];
+        acc = __fadd_rn(acc, __fmul_rn(c, c));
+      }
+    const float nk = sah_round_to<T>(sqrtf(lsh_warp_sum(acc)));
+    if (lane == 0) norms[bh * cap + s] = nk;
+    local_max = fmaxf(local_max, nk);
+  }
+  if (lane == 0 && local_max > 0.f) atomicMax(max_bits, __float_as_uint(local_max));
+}
+
+extern "C" int sah_lsh_key_stats(const void* keys, int dtype, int64_t ks_b, int64_t ks_h,
+                                 int64_t ks_s, int B, int Hkv, int64_t s0, int64_t s1, int D,
+                                 const void* mean, int64_t cap, float* norms,
+                                 unsigned int* max_norm_bits, int sm_count, void* stream) {
+  SAH_REQUIRE(keys && norms && max_norm_bits, "lsh_key_stats: null pointer");
+  SAH_REQUIRE(D % 32 == 0 && D <= 32 * LSH_MAX_PER_LANE, "lsh_key_stats: head_dim must be a multiple of 32, <= 256");
+  SAH_REQUIRE(s0 >= 0 && s1 >= s0 && s1 <= cap, "lsh_key_stats: bad key range");
+  if (s1 == s0) return SAH_OK;
+  if (sm_count <= 0) sm_count = 148;
+  int64_t gx = (s1 - s0 + 7) / 8;
+  const int64_t cap_x = ((int64_t)sm_count * 16 + (int64_t)B * Hkv - 1) / ((int64_t)B * Hkv);
+  if (gx > cap_x) gx = cap_x;
+  dim3 grid((unsigned)gx, (unsigned)(B * Hkv));
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    lsh_key_stats_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const T*>(keys), ks_b, ks_h, ks_s, Hkv, s0, s1, D,
+        reinterpret_cast<const T*>(mean), cap, norms, max_norm_bits);
+  });
+  SAH_LAUNCH_CHECK("lsh_key_stats");
+  return SAH_OK;
+}
+
+// augmentation column of the MIPS transform: sqrt(M^2 - |k|^2) / M, rounded per operation
+template <typename T>
+__device__ __forceinline__ float lsh_augment(float nk, float M) {
+  const float m2 = sah_round_to<T>(__fmul_rn(M, M));
+  const float n2 = sah_round_to<T>(__fmul_rn(nk, nk));
+  const float d = sah_round_to<T>(__fsub_rn(m2, n2));
+  return sah_round_to<T>(__fdiv_rn(sah_round_to<T>(sqrtf(d)), M));
+}
+
+// ---------------------------------------------------------------------------------------
+// key signatures
+// ---------------------------------------------------------------------------------------
+#define LSH_KT 64  // keys per CTA tile
+
+template <typename T, typename CodeT>
+__global__ void __launch_bounds__(256)
+lsh_key_sign_kernel(const T* __restrict__ k, int64_t ks_b, int64_t ks_h, int64_t ks_s, int Hkv,
+                    int64_t s0, int64_t s1, int D, const T* __restrict__ mean,
+                    const float* __restrict__ norms, const unsigned int* __restrict__ max_bits,
+                    const T* __restrict__ proj, int L, int K, int64_t cap,
+                    CodeT* __restrict__ planes) {
+  extern __shared__ __align__(16) unsigned char lsh_smem[];
+  const int nbits = L * K;
+  const int Dp = D + 1;
+  float* xt = reinterpret_cast<float*>(lsh_smem);                       // [Dp][LSH_KT] transformed keys
+  unsigned char* sb = lsh_smem + (size_t)Dp * LSH_KT * sizeof(float);   // [LSH_KT][nbits] sign bits
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t bh = blockIdx.y;
+  const int64_t b = bh / Hkv, h = bh % Hkv;
+  const int64_t t0 = s0 + (int64_t)blockIdx.x * LSH_KT;
+  const int per = D / 32;
+  const float M = __uint_as_float(*max_bits);
+
+  float m[LSH_MAX_PER_LANE];
+  if (mean) lsh_load_lane<T>(mean + bh * D, per, lane, m);
+  for (int kk = warp; kk < LSH_KT; kk += 8) {
+    const int64_t s = t0 + kk;
+    float x[LSH_MAX_PER_LANE];
+    if (s < s1) lsh_load_lane<T>(k + b * ks_b + h * ks_h + s * ks_s, per, lane, x);
+#pragma unroll
+    for (int t = 0; t < LSH_MAX_PER_LANE; ++t)
+      if (t < per) {
+        float v = 0.f;
+        if (s < s1) {
+          const float c = mean ? sah_round_to<T>(__fsub_rn(x[t], m[t])) : x[t];
+          v = sah_round_to<T>(__fdiv_rn(c, M));
+        }
+        xt[(lane * per + t) * LSH_KT + kk] = v;
+      }
+    if (lane == 0) xt[D * LSH_KT + kk] = s < s1 ? lsh_augment<T>(norms[bh * cap + s], M) : 0.f;
+  }
+  __syncthreads();
+
+  // one output column per thread, 8 keys at a time; single accumulator per (key, column),
+  // channels ascending (products of dtype values, added in float)
+  for (int o = threadIdx.x; o < nbits; o += 256) {
+    for (int k8 = 0; k8 < LSH_KT; k8 += 8) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int c = 0; c < Dp; ++c) {
+        const float p = sah_to_float<T>(proj[(int64_t)c * nbits + o]);
+        const float4 a = *reinterpret_cast<const float4*>(xt + c * LSH_KT + k8);
+        const float4 bq = *reinterpret_cast<const float4*>(xt + c * LSH_KT + k8 + 4);
+        acc[0] = __fadd_rn(acc[0], __fmul_rn(a.x, p));
+        acc[1] = __fadd_rn(acc[1], __fmul_rn(a.y, p));
+        acc[2] = __fadd_rn(acc[2], __fmul_rn(a.z, p));
+        acc[3] = __fadd_rn(acc[3], __fmul_rn(a.w, p));
+        acc[4] = __fadd_rn(acc[4], __fmul_rn(bq.x, p));
+        acc[5] = __fadd_rn(acc[5], __fmul_rn(bq.y, p));
+        acc[6] = __fadd_rn(acc[6], __fmul_rn(bq.z, p));
+        acc[7] = __fadd_rn(acc[7], __fmul_rn(bq.w, p));
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sb[(k8 + j) * nbits + o] = acc[j] > 0.f ? 1 : 0;
+    }
+  }
+  __syncthreads();
+  // pack: bit j of table l is column l*K + j (magic_pig.py:120-150)
+  for (int i = threadIdx.x; i < L * LSH_KT; i += 256) {
+    const int l = i / LSH_KT, kk = i % LSH_KT;
+    const int64_t s = t0 + kk;
+    if (s >= s1) continue;
+    unsigned int code = 0;
+    for (int j = 0; j < K; ++j) code |= (unsigned int)sb[kk * nbits + l * K + j] << j;
+    planes[(bh * L + l) * cap + s] = (CodeT)code;
+  }
+}
+
+extern "C" int sah_lsh_key_sign(const void* keys, int dtype, int64_t ks_b, int64_t ks_h,
+                                int64_t ks_s, int B, int Hkv, int64_t s0, int64_t s1, int D,
+                                const void* mean, const float* norms,
+                                const unsigned int* max_norm_bits, const void* proj, int L, int K,
+                                int64_t cap, void* planes, void* stream) {
+  SAH_REQUIRE(keys && norms && max_norm_bits && proj && planes, "lsh_key_sign: null pointer");
+  SAH_REQUIRE(D % 32 == 0 && D <= 32 * LSH_MAX_PER_LANE, "lsh_key_sign: head_dim must be a multiple of 32, <= 256");
+  SAH_REQUIRE(L > 0 && K > 0, "lsh_key_sign: bad table shape");
+  if (K > 16) return sah_fail(SAH_ERR_UNSUPPORTED, "lsh: lsh_k = %d > 16 bits per table is not built", K);
+  SAH_REQUIRE(s0 >= 0 && s1 >= s0 && s1 <= cap, "lsh_key_sign: bad key range");
+  if (s1 == s0) return SAH_OK;
+  const size_t smem = (size_t)(D + 1) * LSH_KT * sizeof(float) + (size_t)LSH_KT * L * K;
+  if (smem > 200 * 1024)
+    return sah_fail(SAH_ERR_UNSUPPORTED, "lsh_key_sign: %d x %d signature bits exceed shared memory", L, K);
+  dim3 grid((unsigned)((s1 - s0 + LSH_KT - 1) / LSH_KT), (unsigned)(B * Hkv));
+  cudaStream_t st = (cudaStream_t)stream;
+#define LSH_SIGN_LAUNCH(T, CodeT)                                                                  \
+  do {                                                                                             \
+    cudaError_t e = cudaFuncSetAttribute(lsh_key_sign_kernel<T, CodeT>,                            \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+    if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "lsh_key_sign attr: %s", cudaGetErrorString(e)); \
+    lsh_key_sign_kernel<T, CodeT><<<grid, 256, smem, st>>>(                                        \
+        reinterpret_cast<const T*>(keys), ks_b, ks_h, ks_s, Hkv, s0, s1, D,                        \
+        reinterpret_cast<const T*>(mean), norms, max_norm_bits, reinterpret_cast<const T*>(proj),  \
+        L, K, cap, reinterpret_cast<CodeT*>(planes));                                              \
+  } while (0)
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    if (K <= 8) LSH_SIGN_LAUNCH(T, uint8_t); else LSH_SIGN_LAUNCH(T, uint16_t);
+  });
+  SAH_LAUNCH_CHECK("lsh_key_sign");
+  return SAH_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// query: centre, normalise, signatures, unit vector
+// ---------------------------------------------------------------------------------------
+template <typename T, typename CodeT>
+__global__ void __launch_bounds__(256)
+lsh_query_kernel(const T* __restrict__ q, int64_t qs_b, int64_t qs_h, int64_t qs_q, int Hq, int Sq,
+                 int G, int D, const T* __restrict__ mean, const T* __restrict__ proj, int L, int K,
+                 CodeT* __restrict__ qcodes, float* __restrict__ qunit) {
+  extern __shared__ __align__(16) unsigned char lsh_smem[];
+  float* qn = reinterpret_cast<float*>(lsh_smem);                 // [D] normalised query
+  unsigned char* sb = lsh_smem + (size_t)D * sizeof(float);       // [L*K]
+  const int nbits = L * K;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t row = blockIdx.x;
+  const int qi = (int)(row % Sq);
+  const int64_t bh = row / Sq;
+  const int h = (int)(bh % Hq);
+  const int64_t b = bh / Hq;
+  const int per = D / 32;
+  if (warp == 0) {
+    float x[LSH_MAX_PER_LANE], m[LSH_MAX_PER_LANE], c[LSH_MAX_PER_LANE];
+    lsh_load_lane<T>(q + b * qs_b + h * qs_h + qi * qs_q, per, lane, x);
+    if (mean) lsh_load_lane<T>(mean + (b * (Hq / G) + h / G) * D, per, lane, m);
+    float acc = 0.f;
+#pragma unroll
+    for (int t = 0; t < LSH_MAX_PER_LANE; ++t)
+      if (t < per) {
+        c[t] = mean ? sah_round_to<T>(__fsub_rn(x[t], m[t])) : x[t];
+        acc = __fadd_rn(acc, __fmul_rn(c[t], c[t]));
+      }
+    // q / (|q| + 1e-8)
+    const float nq = sah_round_to<T>(sqrtf(lsh_warp_sum(acc)));
+    const float den = sah_round_to<T>(__fadd_rn(nq, 1e-8f));
+    acc = 0.f;
+#pragma unroll
+    for (int t = 0; t < LSH_MAX_PER_LANE; ++t)
+      if (t < per) {
+        c[t] = sah_round_to<T>(__fdiv_rn(c[t], den));
+        qn[lane * per + t] = c[t];
+        acc = __fadd_rn(acc, __fmul_rn(c[t], c[t]));
+      }
+    // unit vector of the transformed query (its extra column is zero): qn / (|qn| + 1e-8)
+    const float n2 = sah_round_to<T>(sqrtf(lsh_warp_sum(acc)));
+    const float den2 = sah_round_to<T>(__fadd_rn(n2, 1e-8f));
+#pragma unroll
+    for (int t = 0; t < LSH_MAX_PER_LANE; ++t)
+      if (t < per) qunit[row * D + lane * per + t] = sah_round_to<T>(__fdiv_rn(c[t], den2));
+  }
+  __syncthreads();
+  for (int o = threadIdx.x; o < nbits; o += 256) {
+    float acc = 0.f;
+    for (int c = 0; c < D; ++c)
+      acc = __fadd_rn(acc, __fmul_rn(qn[c], sah_to_float<T>(proj[(int64_t)c * nbits + o])));
+    acc = __fadd_rn(acc, __fmul_rn(0.f, sah_to_float<T>(proj[(int64_t)D * nbits + o])));
+    sb[o] = acc > 0.f ? 1 : 0;
+  }
+  __syncthreads();
+  for (int l = threadIdx.x; l < L; l += 256) {
+    unsigned int code = 0;
+    for (int j = 0; j < K; ++j) code |= (unsigned int)sb[l * K + j] << j;
+    qcodes[row * L + l] = (CodeT)code;
+  }
+}
+
+extern "C" int sah_lsh_query(const void* q, int dtype, int64_t qs_b, int64_t qs_h, int64_t qs_q,
+                             int B, int Hq, int Sq, int G, int D, const void* mean,
+                             const void* proj, int L, int K, void* qcodes, float* qunit,
+                             void* stream) {
+  SAH_REQUIRE(q && proj && qcodes && qunit, "lsh_query: null pointer");
+  SAH_REQUIRE(D % 32 == 0 && D <= 32 * LSH_MAX_PER_LANE, "lsh_query: head_dim must be a multiple of 32, <= 256");
+  SAH_REQUIRE(G > 0 && Hq % G == 0 && L > 0 && K > 0, "lsh_query: bad shape");
+  if (K > 16) return sah_fail(SAH_ERR_UNSUPPORTED, "lsh: lsh_k = %d > 16 bits per table is not built", K);
+  const size_t smem = (size_t)D * sizeof(float) + (size_t)L * K;
+  if (smem > 48 * 1024)
+    return sah_fail(SAH_ERR_UNSUPPORTED, "lsh_query: %d x %d signature bits exceed shared memory", L, K);
+  const int64_t rows = (int64_t)B * Hq * Sq;
+  cudaStream_t st = (cudaStream_t)stream;
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    if (K <= 8)
+      lsh_query_kernel<T, uint8_t><<<(unsigned)rows, 256, smem, st>>>(
+          reinterpret_cast<const T*>(q), qs_b, qs_h, qs_q, Hq, Sq, G, D,
+          reinterpret_cast<const T*>(mean), reinterpret_cast<const T*>(proj), L, K,
+          reinterpret_cast<uint8_t*>(qcodes), qunit);
+    else
+      lsh_query_kernel<T, uint16_t><<<(unsigned)rows, 256, smem, st>>>(
+          reinterpret_cast<const T*>(q), qs_b, qs_h, qs_q, Hq, Sq, G, D,
+          reinterpret_cast<const T*>(mean), reinterpret_cast<const T*>(proj), L, K,
+          reinterpret_cast<uint16_t*>(qcodes), qunit);
+  });
+  SAH_LAUNCH_CHECK("lsh_query");
+  return SAH_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// match: any table code equal
+// ---------------------------------------------------------------------------------------
+#define LSH_MR 4  // mask rows (query heads x query positions of a group) per pass
+
+// 4 byte flags (0xFF / 0x00) -> 4 bits, byte i -> bit i
+__device__ __forceinline__ unsigned int lsh_flags4(unsigned int w) {
+  return ((w & 0x01010101u) * 0x01020408u) >> 24;
+}
+// 2 halfword flags (0xFFFF / 0) -> 2 bits
+__device__ __forceinline__ unsigned int lsh_flags2(unsigned int w) {
+  return (w & 1u) | ((w >> 15) & 2u);
+}
+
+// Each thread owns 32 consecutive keys of one (batch, KV head): one bitmap word per mask row.
+template <typename CodeT>
+__global__ void __launch_bounds__(256)
+lsh_match_kernel(const CodeT* __restrict__ planes, int64_t cap, const CodeT* __restrict__ qcodes,
+                 int Hq, int Sq, int G, int L, int64_t S, int64_t W,
+                 uint32_t* __restrict__ out_bits) {
+  extern __shared__ __align__(16) unsigned char lsh_smem[];
+  CodeT* qs = reinterpret_cast<CodeT*>(lsh_smem);  // [R][L]
+  const int R = G * Sq;
+  const int64_t bh = blockIdx.y;           // b * Hkv + hkv
+  const int Hkv = Hq / G;
+  const int64_t b = bh / Hkv, hkv = bh % Hkv;
+  for (int i = threadIdx.x; i < R * L; i += blockDim.x) {
+    const int r = i / L, l = i % L;
+    const int g = r / Sq, qi = r % Sq;
+    qs[i] = qcodes[(((b * Hq) + hkv * G + g) * Sq + qi) * L + l];
+  }
+  __syncthreads();
+  const int64_t word = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (word * 32 >= S) return;
+  constexpr int PER16 = 16 / (int)sizeof(CodeT);  // codes per 16-byte load
+  constexpr int NV = 32 / PER16;                  // 16-byte loads per 32 keys
+  const CodeT* pbase = planes + bh * (int64_t)L * cap + word * 32;
+  for (int r0 = 0; r0 < R; r0 += LSH_MR) {
+    unsigned int acc[LSH_MR][NV * 4];
+#pragma unroll
+    for (int r = 0; r < LSH_MR; ++r)
+#pragma unroll
+      for (int i = 0; i < NV * 4; ++i) acc[r][i] = 0u;
+    for (int l = 0; l < L; ++l) {
+      uint4 v[NV];
+#pragma unroll
+      for (int i = 0; i < NV; ++i) v[i] = __ldg(reinterpret_cast<const uint4*>(pbase + (int64_t)l * cap) + i);
+#pragma unroll
+      for (int r = 0; r < LSH_MR; ++r) {
+        if (r0 + r < R) {
+          const unsigned int qc = (unsigned int)qs[(r0 + r) * L + l];
+          if (sizeof(CodeT) == 1) {
+            const unsigned int rep = qc * 0x01010101u;
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+              acc[r][i * 4 + 0] |= __vcmpeq4(v[i].x, rep);
+              acc[r][i * 4 + 1] |= __vcmpeq4(v[i].y, rep);
+              acc[r][i * 4 + 2] |= __vcmpeq4(v[i].z, rep);
+              acc[r][i * 4 + 3] |= __vcmpeq4(v[i].w, rep);
+            }
+          } else {
+            const unsigned int rep = qc * 0x00010001u;
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+              acc[r][i * 4 + 0] |= __vcmpeq2(v[i].x, rep);
+              acc[r][i * 4 + 1] |= __vcmpeq2(v[i].y, rep);
+              acc[r][i * 4 + 2] |= __vcmpeq2(v[i].z, rep);
+              acc[r][i * 4 + 3] |= __vcmpeq2(v[i].w, rep);
+            }
+          }
+        }
+      }
+    }
+    const int64_t left = S - word * 32;
+    const unsigned int valid = left >= 32 ? 0xffffffffu : ((1u << left) - 1u);
+#pragma unroll
+    for (int r = 0; r < LSH_MR; ++r) {
+      if (r0 + r < R) {
+        unsigned int bits = 0;
+        if (sizeof(CodeT) == 1) {
+#pragma unroll
+          for (int i = 0; i < NV * 4; ++i) bits |= lsh_flags4(acc[r][i]) << (4 * i);
+        } else {
+#pragma unroll
+          for (int i = 0; i < NV * 4; ++i) bits |= lsh_flags2(acc[r][i]) << (2 * i);
+        }
+        const int g = (r0 + r) / Sq, qi = (r0 + r) % Sq;
+        const int64_t row = ((b * Hq) + hkv * G + g) * Sq + qi;
+        out_bits[row * W + word] = bits & valid;
+      }
+    }
+  }
+}
+
+extern "C" int sah_lsh_match(const void* planes, int64_t cap, const void* qcodes, int B, int Hq,
+                             int Sq, int G, int L, int K, int64_t S, int64_t W, uint32_t* out_bits,
+                             void* stream) {
+  SAH_REQUIRE(planes && qcodes && out_bits, "lsh_match: null pointer");
+  SAH_REQUIRE(G > 0 && Hq % G == 0 && L > 0 && K > 0 && S > 0 && W * 32 >= S, "lsh_match: bad shape");
+  SAH_REQUIRE(cap % 32 == 0 && cap >= S, "lsh_match: plane capacity must be a multiple of 32 keys");
+  if (K > 16) return sah_fail(SAH_ERR_UNSUPPORTED, "lsh: lsh_k = %d > 16 bits per table is not built", K);
+  const int csz = K <= 8 ? 1 : 2;
+  const size_t smem = (size_t)G * Sq * L * csz;
+  if (smem > 48 * 1024) return sah_fail(SAH_ERR_UNSUPPORTED, "lsh_match: too many query rows per group");
+  const int64_t words = (S + 31) / 32;
+  dim3 grid((unsigned)((words + 255) / 256), (unsigned)(B * (Hq / G)));
+  cudaStream_t st = (cudaStream_t)stream;
+  if (csz == 1)
+    lsh_match_kernel<uint8_t><<<grid, 256, smem, st>>>(reinterpret_cast<const uint8_t*>(planes), cap,
+                                                       reinterpret_cast<const uint8_t*>(qcodes), Hq, Sq,
+                                                       G, L, S, W, out_bits);
+  else
+    lsh_match_kernel<uint16_t><<<grid, 256, smem, st>>>(reinterpret_cast<const uint16_t*>(planes), cap,
+                                                        reinterpret_cast<const uint16_t*>(qcodes), Hq,
+                                                        Sq, G, L, S, W, out_bits);
+  SAH_LAUNCH_CHECK("lsh_match");
+  return SAH_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// collision probability of matched keys
+// ---------------------------------------------------------------------------------------
+// 1 - (1 - (1 - acos(c) / pi)^K)^L with every operation rounded to the dtype (:374-403).
+// bf16 goes through a 65536-entry table of the whole chain; fp32 evaluates acos and pow in
+// double precision and rounds once, so that a CPU restatement reproduces the bits.
+template <typename T>
+__device__ __forceinline__ float lsh_collision_prob(float c, int K, int L, const uint16_t* table);
+template <>
+__device__ __forceinline__ float lsh_collision_prob<__nv_bfloat16>(float c, int, int,
+                                                                   const uint16_t* table) {
+  return __uint_as_float(((uint32_t)table[__float_as_uint(c) >> 16]) << 16);
+}
+template <>
+__device__ __forceinline__ float lsh_collision_prob<float>(float c, int K, int L, const uint16_t*) {
+  const float theta = (float)acos((double)c);
+  const float a = __fdiv_rn(theta, 3.14159274101257324f);
+  const float s = __fsub_rn(1.0f, a);
+  const float st = (float)pow((double)s, (double)K);
+  const float u = __fsub_rn(1.0f, st);
+  const float ul = (float)pow((double)u, (double)L);
+  return __fsub_rn(1.0f, ul);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+lsh_prob_kernel(const T* __restrict__ k, int64_t ks_b, int64_t ks_h, int64_t ks_s, int Hq, int Sq,
+                int G, int D, const T* __restrict__ mean, const float* __restrict__ norms,
+                int64_t cap, const unsigned int* __restrict__ max_bits,
+                const float* __restrict__ qunit, const uint32_t* __restrict__ bits,
+                const int32_t* __restrict__ wpre, const int64_t* __restrict__ ptr, int64_t W,
+                int K, int L, const uint16_t* __restrict__ table, T* __restrict__ data) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const int64_t row = blockIdx.x;
+  const int64_t bh = row / Sq;
+  const int h = (int)(bh % Hq);
+  const int64_t b = bh / Hq;
+  const int Hkv = Hq / G;
+  const int64_t kvh = b * Hkv + h / G;
+  const int per = D / 32;
+  const float M = __uint_as_float(*max_bits);
+  float m[LSH_MAX_PER_LANE], qu[LSH_MAX_PER_LANE];
+  if (mean) lsh_load_lane<T>(mean + kvh * D, per, lane, m);
+#pragma unroll
+  for (int t = 0; t < LSH_MAX_PER_LANE; ++t)
+    if (t < per) qu[t] = qunit[row * D + lane * per + t];
+  const T* kbase = k + b * ks_b + (h / G) * ks_h;
+  const int64_t base = ptr[row];
+  for (int64_t w = (int64_t)blockIdx.y * nwarp + warp; w < W; w += (int64_t)gridDim.y * nwarp) {
+    uint32_t word = bits[row * W + w];
+    int64_t pos = base + wpre[row * W + w];
+    while (word) {
+      const int bit = __ffs(word) - 1;
+      word &= word - 1;
+      const int64_t s = w * 32 + bit;
+      float x[LSH_MAX_PER_LANE];
+      lsh_load_lane<T>(kbase + s * ks_s, per, lane, x);
+      float acc = 0.f;
+#pragma unroll
+      for (int t = 0; t < LSH_MAX_PER_LANE; ++t)
+        if (t < per) {
+          const float c = mean ? sah_round_to<T>(__fsub_rn(x[t], m[t])) : x[t];
+          x[t] = sah_round_to<T>(__fdiv_rn(c, M));
+          acc = __fadd_rn(acc, __fmul_rn(x[t], x[t]));
+        }
+      const float aug = lsh_augment<T>(norms[kvh * cap + s], M);
+      // |transformed key|, then its unit vector dotted with the query's
+      const float n2 = __fadd_rn(lsh_warp_sum(acc), __fmul_rn(aug, aug));
+      const float den = sah_round_to<T>(__fadd_rn(sah_round_to<T>(sqrtf(n2)), 1e-8f));
+      acc = 0.f;
+#pragma unroll
+      for (int t = 0; t < LSH_MAX_PER_LANE; ++t)
+        if (t < per) acc = __fadd_rn(acc, __fmul_rn(qu[t], sah_round_to<T>(__fdiv_rn(x[t], den))));
+      float c = sah_round_to<T>(lsh_warp_sum(acc));
+      c = fminf(fmaxf(c, -1.0f), 1.0f);
+      if (lane == 0) data[pos] = sah_from_float<T>(lsh_collision_prob<T>(c, K, L, table));
+      ++pos;
+    }
+  }
+}
+
+extern "C" int sah_lsh_prob(const void* keys, int dtype, int64_t ks_b, int64_t ks_h, int64_t ks_s,
+                            int B, int Hq, int Sq, int G, int D, const void* mean,
+                            const float* norms, int64_t cap, const unsigned int* max_norm_bits,
+                            const float* qunit, const uint32_t* bits, const int32_t* wpre,
+                            const int64_t* ptr, int64_t W, int K, int L, const uint16_t* table,
+                            void* data, int sm_count, void* stream) {
+  SAH_REQUIRE(keys && norms && max_norm_bits && qunit && bits && wpre && ptr && data,
+              "lsh_prob: null pointer");
+  SAH_REQUIRE(D % 32 == 0 && D <= 32 * LSH_MAX_PER_LANE, "lsh_prob: head_dim must be a multiple of 32, <= 256");
+  SAH_REQUIRE(dtype != SAH_BF16 || table != nullptr, "lsh_prob: bf16 needs the probability table");
+  const int64_t rows = (int64_t)B * Hq * Sq;
+  if (sm_count <= 0) sm_count = 148;
+  int64_t gx = (W + 7) / 8;
+  const int64_t cap_x = ((int64_t)sm_count * 8 + rows - 1) / rows;
+  if (gx > cap_x) gx = cap_x;
+  if (gx < 1) gx = 1;
+  dim3 grid((unsigned)rows, (unsigned)gx);
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    lsh_prob_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const T*>(keys), ks_b, ks_h, ks_s, Hq, Sq, G, D,
+        reinterpret_cast<const T*>(mean), norms, cap, max_norm_bits, qunit, bits, wpre, ptr, W, K, L,
+        table, reinterpret_cast<T*>(data));
+  });
+  SAH_LAUNCH_CHECK("lsh_prob");
+  return SAH_OK;
+}

@@ -417,3 +417,109 @@ extern "C" int sah_mask_scatter_samples(const int64_t* cols, const int64_t* sptr
   SAH_LAUNCH_CHECK("mask_scatter_samples");
   return SAH_OK;
 }
+
+// ---- merge of two weighted bitmap masks -------------------------------------------------------
+// Mask.merge_mask_dense (utils/mask.py:875-877): clamp(a + b, 0, 1) in the mask dtype, an
+// entry being active when the result is non-zero.  A mask without a data array has unit
+// weights.  Two passes: the bitmap of the result, then (after a row scan of that bitmap) its
+// weights in CSR order.
+struct MergeSide {
+  const uint32_t* bits;
+  const void* data;      // null: unit weights
+  const int32_t* wpre;   // needed with data
+  const int64_t* ptr;    // needed with data
+};
+
+template <typename T>
+__device__ __forceinline__ float merge_side_weight(const MergeSide& s, int64_t row, int64_t t,
+                                                   uint32_t word, int bit) {
+  if (!((word >> bit) & 1u)) return 0.f;
+  if (s.data == nullptr) return 1.f;
+  const int64_t pos = s.ptr[row] + s.wpre[t] + __popc(word & ((1u << bit) - 1u));
+  return sah_to_float<T>(reinterpret_cast<const T*>(s.data)[pos]);
+}
+
+template <typename T>
+__device__ __forceinline__ float merge_weight(float a, float b) {
+  const float s = sah_round_to<T>(__fadd_rn(a, b));
+  return fminf(fmaxf(s, 0.f), 1.f);
+}
+
+template <typename T>
+__global__ void mask_merge_bits_kernel(MergeSide a, MergeSide b, int64_t rows, int64_t W,
+                                       uint32_t* __restrict__ out) {
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= rows * W) return;
+  const uint32_t wa = a.bits[t], wb = b.bits[t];
+  uint32_t m = wa | wb, keep = m;
+  if (a.data != nullptr || b.data != nullptr) {
+    const int64_t row = t / W;
+    while (m) {
+      const int bit = __ffs(m) - 1;
+      m &= m - 1;
+      const float w = merge_weight<T>(merge_side_weight<T>(a, row, t, wa, bit),
+                                      merge_side_weight<T>(b, row, t, wb, bit));
+      if (!(w != 0.f)) keep &= ~(1u << bit);
+    }
+  }
+  out[t] = keep;
+}
+
+template <typename T>
+__global__ void mask_merge_data_kernel(MergeSide a, MergeSide b, int64_t rows, int64_t W,
+                                       const uint32_t* __restrict__ outb,
+                                       const int32_t* __restrict__ out_wpre,
+                                       const int64_t* __restrict__ out_ptr, T* __restrict__ data) {
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= rows * W) return;
+  uint32_t m = outb[t];
+  if (!m) return;
+  const int64_t row = t / W;
+  const uint32_t wa = a.bits[t], wb = b.bits[t];
+  int64_t o = out_ptr[row] + out_wpre[t];
+  while (m) {
+    const int bit = __ffs(m) - 1;
+    m &= m - 1;
+    data[o++] = sah_from_float<T>(merge_weight<T>(merge_side_weight<T>(a, row, t, wa, bit),
+                                                  merge_side_weight<T>(b, row, t, wb, bit)));
+  }
+}
+
+static int merge_check(const uint32_t* bits, const void* data, const int32_t* wpre, const int64_t* ptr) {
+  return bits != nullptr && (data == nullptr || (wpre != nullptr && ptr != nullptr));
+}
+
+extern "C" int sah_mask_merge_bits(const uint32_t* a_bits, const void* a_data, const int32_t* a_wpre,
+                                   const int64_t* a_ptr, const uint32_t* b_bits, const void* b_data,
+                                   const int32_t* b_wpre, const int64_t* b_ptr, int dtype,
+                                   int64_t rows, int64_t W, uint32_t* out_bits, void* stream) {
+  SAH_REQUIRE(merge_check(a_bits, a_data, a_wpre, a_ptr) && merge_check(b_bits, b_data, b_wpre, b_ptr) && out_bits,
+              "mask_merge_bits: null pointer (data needs wpre and ptr)");
+  if (rows == 0 || W == 0) return SAH_OK;
+  MergeSide a{a_bits, a_data, a_wpre, a_ptr}, b{b_bits, b_data, b_wpre, b_ptr};
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    mask_merge_bits_kernel<T><<<(unsigned)sah_ceil_div(rows * W, 256), 256, 0, (cudaStream_t)stream>>>(
+        a, b, rows, W, out_bits);
+  });
+  SAH_LAUNCH_CHECK("mask_merge_bits");
+  return SAH_OK;
+}
+
+extern "C" int sah_mask_merge_data(const uint32_t* a_bits, const void* a_data, const int32_t* a_wpre,
+                                   const int64_t* a_ptr, const uint32_t* b_bits, const void* b_data,
+                                   const int32_t* b_wpre, const int64_t* b_ptr, int dtype,
+                                   int64_t rows, int64_t W, const uint32_t* out_bits,
+                                   const int32_t* out_wpre, const int64_t* out_ptr, void* out_data,
+                                   void* stream) {
+  SAH_REQUIRE(merge_check(a_bits, a_data, a_wpre, a_ptr) && merge_check(b_bits, b_data, b_wpre, b_ptr),
+              "mask_merge_data: null pointer (data needs wpre and ptr)");
+  SAH_REQUIRE(out_bits && out_wpre && out_ptr && out_data, "mask_merge_data: null output");
+  if (rows == 0 || W == 0) return SAH_OK;
+  MergeSide a{a_bits, a_data, a_wpre, a_ptr}, b{b_bits, b_data, b_wpre, b_ptr};
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    mask_merge_data_kernel<T><<<(unsigned)sah_ceil_div(rows * W, 256), 256, 0, (cudaStream_t)stream>>>(
+        a, b, rows, W, out_bits, out_wpre, out_ptr, reinterpret_cast<T*>(out_data));
+  });
+  SAH_LAUNCH_CHECK("mask_merge_data");
+  return SAH_OK;
+}

@@ -85,6 +85,15 @@ _SIGNATURES = {
     "sah_adaptive_budget": [_P, _I, c_float, _P, _L, _L, _L, _P, _P, _P, _P, _I, _I, _I, _L, _L, _L,
                             _L, _L, ctypes.c_uint64, _P, _P, c_float, c_float, _P, _P, _P, _P],
     "sah_sample_scatter": [_P, _L, _P, ctypes.c_uint64, _L, _L, _L, _L, _I, _P, _P],
+    "sah_mask_merge_bits": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _L, _P, _P],
+    "sah_mask_merge_data": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _L, _P, _P, _P, _P, _P],
+    "sah_lsh_key_sums": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _I, _P, _P],
+    "sah_lsh_key_stats": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _I, _P, _L, _P, _P, _I, _P],
+    "sah_lsh_key_sign": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _I, _P, _P, _P, _P, _I, _I, _L, _P, _P],
+    "sah_lsh_query": [_P, _I, _L, _L, _L, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P, _P, _P],
+    "sah_lsh_match": [_P, _L, _P, _I, _I, _I, _I, _I, _I, _L, _L, _P, _P],
+    "sah_lsh_prob": [_P, _I, _L, _L, _L, _I, _I, _I, _I, _I, _P, _P, _L, _P, _P, _P, _P, _P, _L,
+                     _I, _I, _P, _P, _I, _P],
     "sah_pq_assign": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _L, _I, _I, _I, _P, _P, _L, _I, _P],
     "sah_pq_accumulate": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _I, _I, _I, _P, _L, _P, _P, _P],
     "sah_pq_update": [_P, _I, _L, _L, _L, _I, _I, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P],

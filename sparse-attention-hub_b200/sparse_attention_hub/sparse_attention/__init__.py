@@ -23,6 +23,8 @@ from .research_attention.maskers.fixed import (
 from .research_attention.maskers.sampling import (
     AdaptiveSamplingMasker,
     AdaptiveSamplingMaskerConfig,
+    MagicPig,
+    MagicPigConfig,
     RandomSamplingMasker,
     RandomSamplingMaskerConfig,
     SamplingMasker,
@@ -35,5 +37,6 @@ __all__ = [
     "TopPMasker", "LocalMasker", "LocalMaskerConfig", "CausalMasker", "SinkMasker",
     "SinkMaskerConfig", "OracleTopK", "OracleTopKConfig", "HashAttentionTopKMasker",
     "HashAttentionTopKMaskerConfig", "PQCache", "PQCacheConfig", "RandomSamplingMasker",
-    "RandomSamplingMaskerConfig", "AdaptiveSamplingMasker", "AdaptiveSamplingMaskerConfig", "Mask",
+    "RandomSamplingMaskerConfig", "AdaptiveSamplingMasker", "AdaptiveSamplingMaskerConfig", "MagicPig",
+    "MagicPigConfig", "Mask",
 ]

@@ -285,3 +285,64 @@ def _sampled_native(bits: torch.Tensor, prev_bits: Optional[torch.Tensor], rows:
                                  rows, S, words, data.data_ptr(), st), "sah_mask_sample_data")
     nb.data = data
     return nb
+
+
+# ---- merge of two bitmap-form masks -------------------------------------------------
+def _side(nb: NativeBits):
+    if nb.data is not None:
+        nb.ensure_scan()
+        return (nb.bits.data_ptr(), nb.data.data_ptr(), nb.wpre.data_ptr(), nb.ptr.data_ptr())
+    return (nb.bits.data_ptr(), None, None, None)
+
+
+def merge_native(a: Mask, b: Mask) -> Mask:
+    """`clamp(a + b, 0, 1)` (Mask.merge_mask_dense, utils/mask.py:875-877) on the bitmap
+    forms of two masks that are neither full nor empty.  No dense tensor is built and
+    nothing is read back: the weight array is sized for the worst case."""
+    lib = _native.load()
+    an, bn = a.native_bits(), b.native_bits()
+    dev = an.bits.device
+    st = _native.stream_of(dev)
+    rows, S, W = an.rows, an.n_cols, an.words
+    code = _native.dtype_code(a.dtype)
+    out_bits = torch.empty_like(an.bits)
+    sa, sb = _side(an), _side(bn)
+    _native.check(lib.sah_mask_merge_bits(*sa, *sb, code, rows, W, out_bits.data_ptr(), st),
+                  "sah_mask_merge_bits")
+    nb = NativeBits(out_bits, rows, S)
+    if an.data is not None or bn.data is not None:
+        nb.ensure_scan()
+        bound = rows * S
+        if an.data is not None and bn.data is not None:
+            bound = min(bound, an.data.numel() + bn.data.numel())
+        data = torch.empty(bound, dtype=a.dtype, device=dev)
+        _native.check(
+            lib.sah_mask_merge_data(*sa, *sb, code, rows, W, out_bits.data_ptr(), nb.wpre.data_ptr(),
+                                    nb.ptr.data_ptr(), data.data_ptr(), st), "sah_mask_merge_data")
+        nb.data = data
+    return Mask._from_native(tuple(a.shape), a.dtype, nb)
+
+
+# ---- MagicPig ---------------------------------------------------------------------
+_LSH_TABLES: dict = {}
+
+
+def lsh_prob_table(device: torch.device, lsh_k: int, lsh_l: int) -> torch.Tensor:
+    """uint16[65536]: bf16 bits of a cosine -> bf16 bits of the collision probability
+    1 - (1 - (1 - acos(c)/pi)^K)^L with every operation rounded to bf16 as a bf16 tensor
+    program rounds it (magic_pig.py:389-403); float64 evaluation rounded through float32."""
+    key = (str(device), lsh_k, lsh_l)
+    if key not in _LSH_TABLES:
+        bf = lambda x: _bf16_bits_to_f64(_f64_to_bf16_bits(x))  # noqa: E731
+        with np.errstate(invalid="ignore", over="ignore"):
+            c = _bf16_bits_to_f64(np.arange(65536, dtype=np.uint32))
+            c = np.clip(c, -1.0, 1.0)  # NaN stays NaN
+            theta = bf(np.arccos(c))
+            a = bf((theta.astype(np.float32) / np.float32(np.pi)).astype(np.float64))
+            s = bf(1.0 - a)
+            st = bf(np.power(s, float(lsh_k)))
+            u = bf(1.0 - st)
+            ul = bf(np.power(u, float(lsh_l)))
+            table = _f64_to_bf16_bits(1.0 - ul)
+        _LSH_TABLES[key] = torch.from_numpy(table.view(np.int16).copy()).to(device)
+    return _LSH_TABLES[key]

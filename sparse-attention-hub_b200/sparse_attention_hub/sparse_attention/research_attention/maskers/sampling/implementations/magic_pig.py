@@ -1,0 +1,281 @@
+"""MagicPig: SimHash (LSH) sampling of keys with collision-probability weights.
+
+Reference: .../maskers/sampling/implementations/magic_pig.py (config :27-76,
+bit packing :120-150, centring :152-183, caches :185-330, MIPS transform
+:332-372, probabilities :374-403, matching :405-463, projections :465-508,
+add_mask :510-593).
+
+Keys and queries are centred by the per-head key mean, mapped to unit-norm
+vectors by the Neyshabur-Srebro transform (keys scaled by the largest key norm of
+the whole tensor and extended by sqrt(M^2 - |k|^2) / M, queries normalised and
+extended by 0), and hashed by `lsh_l` tables of `lsh_k` random hyperplanes.  A key
+is sampled when at least one of its table codes equals the query's; it then carries
+the probability of that event, 1 - (1 - (1 - theta/pi)^k)^l, as its weight.
+
+The reference materialises signatures as int64 `[B, Hq, S, L]` and probabilities for
+every key.  Here the signatures of a layer live in a `PackedLSHSignatures`
+(one code per table and key, table-major, once per KV head), a match kernel streams
+them, and probabilities are evaluated for matched keys only.
+
+`sparse_meta_data` keys are the reference's: `"projections"[layer]` (`[D+1, L*K]`,
+used as is when pre-populated), `"key_mean"[layer]` (`[B, Hq, 1, D]`, used as is when
+pre-populated) and `"key_signature"[layer]` (the packed handle; a reference-layout
+int64 tensor is converted on first use).
+"""
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, Literal, Optional, Tuple
+
+import torch
+
+from ..... import _native_ops
+from ....._native_ops import _native
+from .....utils.kv_utils import _get_num_key_value_groups
+from .....utils.mask import Mask, NativeBits, words_per_row
+from ...base import MaskerConfig, MaskerRegistry
+from ..base import SamplingMasker, SamplingMaskerConfig
+
+
+@dataclass
+class MagicPigConfig(SamplingMaskerConfig):
+    """lsh_l tables of lsh_k bits; `center` subtracts the key mean first; `packing` only
+    names the reference's signature storage ("int64" or "float32" give the same matches);
+    `seed` (+ layer index) seeds the projections."""
+
+    lsh_l: int
+    lsh_k: int
+    center: bool = True
+    packing: Literal["int64", "float32"] = "int64"
+    seed: Optional[int] = 42
+    search_space: Dict[str, Any] = field(default_factory=dict)
+
+    def __post_init__(self) -> None:
+        if self.lsh_l <= 0:
+            raise ValueError(f"lsh_l must be positive, got {self.lsh_l}")
+        if self.lsh_k <= 0:
+            raise ValueError(f"lsh_k must be positive, got {self.lsh_k}")
+        if self.packing not in ["int64", "float32"]:
+            raise ValueError(f"packing must be 'int64' or 'float32', got {self.packing}")
+        if self.packing == "int64" and self.lsh_k > 64:
+            raise ValueError(f"For 'int64' packing, lsh_k must be <= 64, but got {self.lsh_k}")
+        if self.seed is None:
+            raise ValueError("seed cannot be None")
+
+
+def _round_up(n: int, m: int) -> int:
+    return (n + m - 1) // m * m
+
+
+class PackedLSHSignatures:
+    """LSH state of one layer's keys.
+
+    planes   uint8 (lsh_k <= 8) or int16 `[B, Hkv, L, capacity]`: code of key s for table l
+    norms    float32 `[B, Hkv, capacity]`: norm of the centred key (rounded to the key dtype)
+    max_norm int32 `[1]`: float bits of the largest norm seen so far
+    length   number of valid keys
+    """
+
+    def __init__(self, planes: torch.Tensor, norms: torch.Tensor, max_norm: torch.Tensor,
+                 length: int, lsh_k: int) -> None:
+        self.planes, self.norms, self.max_norm, self.length, self.lsh_k = planes, norms, max_norm, length, lsh_k
+
+    @property
+    def capacity(self) -> int:
+        return self.planes.shape[-1]
+
+    @property
+    def shape(self) -> Tuple[int, ...]:
+        return (self.planes.shape[0], self.planes.shape[1], self.length, self.planes.shape[2])
+
+    @classmethod
+    def allocate(cls, B: int, Hkv: int, L: int, lsh_k: int, n_keys: int, device) -> "PackedLSHSignatures":
+        cap = _round_up(n_keys + max(256, n_keys // 8), 32)
+        code_dtype = torch.uint8 if lsh_k <= 8 else torch.int16
+        return cls(torch.zeros((B, Hkv, L, cap), dtype=code_dtype, device=device),
+                   torch.zeros((B, Hkv, cap), dtype=torch.float32, device=device),
+                   torch.zeros(1, dtype=torch.int32, device=device), 0, lsh_k)
+
+    def grown(self, n_keys: int) -> "PackedLSHSignatures":
+        if n_keys <= self.capacity:
+            return self
+        B, Hkv, L, _ = self.planes.shape
+        new = PackedLSHSignatures.allocate(B, Hkv, L, self.lsh_k, n_keys, self.planes.device)
+        new.planes[..., : self.length] = self.planes[..., : self.length]
+        new.norms[..., : self.length] = self.norms[..., : self.length]
+        new.max_norm.copy_(self.max_norm)
+        new.length = self.length
+        return new
+
+    def to_reference_layout(self, n_query_heads: int) -> torch.Tensor:
+        """int64 `[B, Hq, length, L]`, the tensor the reference caches (magic_pig.py:120-150)."""
+        G = n_query_heads // self.planes.shape[1]
+        codes = self.planes[..., : self.length].to(torch.int64)
+        if self.planes.dtype == torch.int16:
+            codes = codes & 0xFFFF
+        return codes.permute(0, 1, 3, 2).repeat_interleave(G, dim=1).contiguous()
+
+    @classmethod
+    def from_reference_layout(cls, sig: torch.Tensor, n_kv_heads: int, lsh_k: int) -> "PackedLSHSignatures":
+        """Adopt signatures cached by the reference (packed int64 `[B, Hq, S, L]`); the key
+        norms are filled by the caller."""
+        B, Hq, S, L = sig.shape
+        G = Hq // n_kv_heads
+        new = cls.allocate(B, n_kv_heads, L, lsh_k, S, sig.device)
+        new.planes[..., :S] = sig[:, ::G].permute(0, 1, 3, 2).to(new.planes.dtype)
+        return new
+
+
+@MaskerRegistry.register(MagicPigConfig)
+class MagicPig(SamplingMasker):
+    """LSH-sampled keys weighted by their collision probability."""
+
+    def __init__(self, config: MagicPigConfig) -> None:
+        super().__init__(config)
+        self.lsh_l = config.lsh_l
+        self.lsh_k = config.lsh_k
+        self.center = config.center
+        self.packing = config.packing
+        self.seed = config.seed
+
+    # ------------------------------------------------------------------ caches
+    def _validate_inputs(self, sparse_meta_data, kwargs: Dict[str, Any]) -> int:
+        if sparse_meta_data is None:
+            raise ValueError("sparse_meta_data cannot be None")
+        layer_idx = kwargs.get("layer_idx")
+        if layer_idx is None:
+            raise ValueError("layer_idx must be provided in kwargs")
+        return layer_idx
+
+    def _projection(self, meta: Dict[Any, Any], layer_idx: int, keys: torch.Tensor) -> torch.Tensor:
+        proj = meta.setdefault("projections", {}).get(layer_idx)
+        if proj is None:
+            generator = torch.Generator(device=keys.device)
+            generator.manual_seed(self.seed + layer_idx)
+            proj = torch.randn(keys.shape[-1] + 1, self.lsh_k * self.lsh_l, device=keys.device,
+                               dtype=keys.dtype, generator=generator)
+            meta["projections"][layer_idx] = proj
+        if proj.device != keys.device or proj.dtype != keys.dtype or not proj.is_contiguous():
+            proj = proj.to(device=keys.device, dtype=keys.dtype).contiguous()
+        return proj
+
+    def _key_mean(self, meta: Dict[Any, Any], layer_idx: int, keys: torch.Tensor, G: int,
+                  lib, st) -> Optional[torch.Tensor]:
+        """Compact `[B, Hkv, D]` key mean in the key dtype (None when center=False); the
+        reference-layout `[B, Hq, 1, D]` tensor is what sits in sparse_meta_data."""
+        cache = meta.setdefault("key_mean", {})
+        cache.setdefault(layer_idx, None)
+        if not self.center:
+            return None
+        B, Hkv, S, D = keys.shape
+        if cache[layer_idx] is None:
+            sums = torch.zeros((B, Hkv, D), dtype=torch.float64, device=keys.device)
+            _native.check(
+                lib.sah_lsh_key_sums(keys.data_ptr(), _native.dtype_code(keys.dtype), keys.stride(0),
+                                     keys.stride(1), keys.stride(2), B, Hkv, 0, S, D, sums.data_ptr(), st),
+                "sah_lsh_key_sums")
+            mean = (sums / S).to(torch.float32).to(keys.dtype)
+            cache[layer_idx] = mean.repeat_interleave(G, dim=1).unsqueeze(2)
+        full = cache[layer_idx]
+        compact = getattr(self, "_mean_compact", {}).get(layer_idx)
+        if compact is None or compact[0] is not full:
+            compact = (full, full[:, ::G, 0, :].to(device=keys.device, dtype=keys.dtype).contiguous())
+            if not hasattr(self, "_mean_compact"):
+                self._mean_compact = {}
+            self._mean_compact[layer_idx] = compact
+        return compact[1]
+
+    def _update_key_signatures(self, meta: Dict[Any, Any], layer_idx: int, keys: torch.Tensor,
+                               n_query_heads: int, mean: Optional[torch.Tensor], proj: torch.Tensor,
+                               lib, st) -> PackedLSHSignatures:
+        cache = meta.setdefault("key_signature", {})
+        handle = cache.get(layer_idx)
+        B, Hkv, S, D = keys.shape
+        code = _native.dtype_code(keys.dtype)
+        sms = _native.sm_count(keys.device)
+        kargs = (keys.data_ptr(), code, keys.stride(0), keys.stride(1), keys.stride(2), B, Hkv)
+
+        def stats(h: PackedLSHSignatures, s0: int, s1: int) -> None:
+            _native.check(lib.sah_lsh_key_stats(*kargs, s0, s1, D, _native.ptr(mean), h.capacity,
+                                                h.norms.data_ptr(), h.max_norm.data_ptr(), sms, st),
+                          "sah_lsh_key_stats")
+
+        if isinstance(handle, torch.Tensor):  # cached by the reference implementation
+            handle = PackedLSHSignatures.from_reference_layout(handle, Hkv, self.lsh_k)
+            n_cached = cache[layer_idx].shape[2]
+            if n_cached > S:
+                raise ValueError(f"Current number of keys ({S}) is less than cached number of keys ({n_cached})")
+            stats(handle, 0, n_cached)
+            handle.length = n_cached
+        if handle is None:
+            handle = PackedLSHSignatures.allocate(B, Hkv, self.lsh_l, self.lsh_k, S, keys.device)
+        if S < handle.length:
+            raise ValueError(
+                f"Current number of keys ({S}) is less than cached number of keys ({handle.length})")
+        if S > handle.length:
+            handle = handle.grown(S)
+            s0 = handle.length
+            stats(handle, s0, S)
+            _native.check(
+                lib.sah_lsh_key_sign(*kargs, s0, S, D, _native.ptr(mean), handle.norms.data_ptr(),
+                                     handle.max_norm.data_ptr(), proj.data_ptr(), self.lsh_l, self.lsh_k,
+                                     handle.capacity, handle.planes.data_ptr(), st), "sah_lsh_key_sign")
+            handle.length = S
+        cache[layer_idx] = handle
+        return handle
+
+    # ------------------------------------------------------------------ public
+    def add_mask(self, keys, queries, values, attention_mask, scaling, dropout,
+                 sparse_meta_data: Dict[Any, Any], previous_mask: Mask,
+                 **kwargs: Dict[str, Any]) -> Mask:
+        layer_idx = self._validate_inputs(sparse_meta_data, kwargs)
+        if previous_mask.is_full_mask():
+            return previous_mask
+        B, Hq, Sq, D = queries.shape
+        Hkv, S = keys.shape[1], keys.shape[2]
+        G = _get_num_key_value_groups(queries, keys)
+        _native.require_cuda(keys, "keys")
+        _native.require_cuda(queries, "queries")
+        lib = _native.load()
+        dev = keys.device
+        st = _native.stream_of(dev)
+        dtype = queries.dtype
+        code = _native.dtype_code(dtype)
+        k = keys if keys.stride(-1) == 1 else keys.contiguous()
+        q = queries if queries.stride(-1) == 1 else queries.contiguous()
+
+        mean = self._key_mean(sparse_meta_data, layer_idx, k, G, lib, st)
+        proj = self._projection(sparse_meta_data, layer_idx, k)
+        sig = self._update_key_signatures(sparse_meta_data, layer_idx, k, Hq, mean, proj, lib, st)
+
+        rows = B * Hq * Sq
+        W = words_per_row(S)
+        qcodes = torch.empty((rows, self.lsh_l), dtype=sig.planes.dtype, device=dev)
+        qunit = torch.empty((rows, D), dtype=torch.float32, device=dev)
+        _native.check(
+            lib.sah_lsh_query(q.data_ptr(), code, q.stride(0), q.stride(1), q.stride(2), B, Hq, Sq, G, D,
+                              _native.ptr(mean), proj.data_ptr(), self.lsh_l, self.lsh_k,
+                              qcodes.data_ptr(), qunit.data_ptr(), st), "sah_lsh_query")
+        bits = torch.zeros((rows, W), dtype=torch.int32, device=dev)
+        _native.check(
+            lib.sah_lsh_match(sig.planes.data_ptr(), sig.capacity, qcodes.data_ptr(), B, Hq, Sq, G,
+                              self.lsh_l, self.lsh_k, S, W, bits.data_ptr(), st), "sah_lsh_match")
+        nb = NativeBits(bits, rows, S)
+        nb.ensure_scan()
+        data = torch.empty(rows * S, dtype=dtype, device=dev)  # worst case; nothing is read back
+        table = _native_ops.lsh_prob_table(dev, self.lsh_k, self.lsh_l) if dtype == torch.bfloat16 else None
+        _native.check(
+            lib.sah_lsh_prob(k.data_ptr(), code, k.stride(0), k.stride(1), k.stride(2), B, Hq, Sq, G, D,
+                             _native.ptr(mean), sig.norms.data_ptr(), sig.capacity,
+                             sig.max_norm.data_ptr(), qunit.data_ptr(), bits.data_ptr(),
+                             nb.wpre.data_ptr(), nb.ptr.data_ptr(), W, self.lsh_k, self.lsh_l,
+                             _native.ptr(table), data.data_ptr(), _native.sm_count(dev), st),
+            "sah_lsh_prob")
+        nb.data = data
+        this_mask = Mask._from_native((B, Hq, Sq, S), previous_mask.dtype, nb)
+        return previous_mask.merge_mask(this_mask, inplace=False)
+
+    @classmethod
+    def create_from_config(cls, config: MaskerConfig) -> "MagicPig":
+        if not isinstance(config, MagicPigConfig):
+            raise ValueError(f"Invalid config type: {type(config)}")
+        return cls(config)

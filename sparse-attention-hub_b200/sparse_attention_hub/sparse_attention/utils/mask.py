@@ -497,6 +497,8 @@ class Mask:
             if index_form:
                 idx, ptr, data = src.get_index_mask()
                 return Mask.create_mask_from_indices(self.shape, idx, ptr, data, dtype=self.dtype)
+            if src._native is not None and src._dense is None and src.dtype == self.dtype:
+                return Mask._from_native(self.shape, self.dtype, src._native)  # bitmaps are not edited in place
             return Mask.create_mask_from_dense_mask(self.shape, src.get_dense_mask(),
                                                     dtype=self.dtype)
         return None
@@ -505,6 +507,16 @@ class Mask:
         done = self._merge_trivial(other_mask, inplace, index_form=False)
         if done is not None:
             return done
+        if (self._native is not None and other_mask._native is not None and self._dense is None
+                and other_mask._dense is None and self.dtype == other_mask.dtype):
+            # both sides live as device bitmaps: merge there, no dense tensor
+            from .._native_ops import merge_native
+
+            merged_mask = merge_native(self, other_mask)
+            if not inplace:
+                return merged_mask
+            self._become(merged_mask)
+            return self
         merged = torch.clamp(self.get_dense_mask() + other_mask.get_dense_mask(), 0.0, 1.0)
         if not inplace:
             return Mask.create_mask_from_dense_mask(self.shape, merged, dtype=self.dtype)

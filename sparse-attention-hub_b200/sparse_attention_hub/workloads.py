@@ -180,6 +180,21 @@ def pqcache(seed: int = 0, dtype: str = "bf16", B: int = 1, Hq: int = 32, Hkv: i
                       "kmeans_iter": kmeans_iter, "init_offset": sink, "metric": "euclidean"})])
 
 
+def magicpig(seed: int = 0, dtype: str = "bf16", B: int = 1, Hq: int = 32, Hkv: int = 8,
+             S: int = 1048576, D: int = 128, sink: int = 64, window: int = 256, lsh_l: int = 75,
+             lsh_k: int = 8, Sq: int = 1, n_clusters: int = 64) -> DecodeWorkload:
+    """Clustered keys; Sink + Local + MagicPig.  The hyperplanes are part of the workload
+    (`stack[-1][1]["projection"]`, `[D+1, lsh_l*lsh_k]` in the dtype) and are handed to every
+    implementation through `sparse_meta_data["projections"]`."""
+    q, k, v = qkv_clustered(seed, B, Hq, Hkv, S, D, Sq, n_clusters=n_clusters)
+    proj = to_dtype(_rng(seed, 70).standard_normal((D + 1, lsh_l * lsh_k)).astype(np.float32), dtype)
+    return DecodeWorkload(
+        "magicpig_" + dtype, dtype, to_dtype(q, dtype), to_dtype(k, dtype), to_dtype(v, dtype),
+        1.0 / np.sqrt(D),
+        [("sink", {"sink_size": sink}), ("local", {"window_size": window}),
+         ("magicpig", {"lsh_l": lsh_l, "lsh_k": lsh_k, "center": True, "projection": proj})])
+
+
 def pq_init_indices(seed: int, groups: int, n_keys: int, n_cent: int) -> np.ndarray:
     """Seeded k-means initialisation: per group the first `n_cent` entries of a permutation."""
     rng = _rng(seed, 60)
@@ -233,6 +248,10 @@ def masker_configs(stack: List[Tuple[str, Dict[str, Any]]], dtype: str, device="
         elif kind == "random_sampling":
             from .sparse_attention.research_attention.maskers import sampling
             out.append(sampling.RandomSamplingMaskerConfig(sampling_rate=prm["sampling_rate"]))
+        elif kind == "magicpig":
+            from .sparse_attention.research_attention.maskers import sampling
+            out.append(sampling.MagicPigConfig(lsh_l=prm["lsh_l"], lsh_k=prm["lsh_k"],
+                                               center=prm.get("center", True)))
         else:
             raise ValueError(f"unknown masker kind {kind}")
     return out

@@ -1,0 +1,185 @@
+"""MagicPig: numpy restatement vs the reference's fixtures (CPU), CUDA path vs both (GPU).
+
+Signature bits are signs of 129-term float sums; where a sum is within rounding of zero the
+reference's BLAS order and the restatement's fixed order can disagree, so key codes are
+compared as a mismatch count with a small bound, and everything downstream is checked on the
+reference's own codes, where the sampled index set must be the reference's exactly.  The
+weights are a chain of dtype-rounded operations on a 129-term dot product; they may differ
+from the reference by one rounding step of the dtype (bound below).  Between the restatement
+and the CUDA kernels, which share every order of operations, codes, index sets and weights
+are identical.
+"""
+
+import numpy as np
+import pytest
+
+from oracle import magicpig, mask_ops, stacks
+from sparse_attention_hub import workloads
+
+from conftest import load_golden
+
+CASES = {"magicpig_bf16": ("bf16", 61, 75, 8, 1024), "magicpig_f32": ("f32", 62, 12, 4, 512)}
+
+
+def _workload(name):
+    dtype, seed, L, K, S = CASES[name]
+    return workloads.magicpig(seed=seed, dtype=dtype, B=1, Hq=8, Hkv=2, S=S, D=128, sink=4, window=8,
+                              lsh_l=L, lsh_k=K, n_clusters=8)
+
+
+def _oracle(wl, meta):
+    meta = dict(meta)
+    meta["lsh_projection"] = wl.stack[-1][1]["projection"]
+    return stacks.run_stack(wl.stack, wl.q, wl.k, wl.v, wl.scaling, wl.dtype, meta=meta)
+
+
+def test_bit_packing_order():
+    # bit j of table l is column l*K + j (magic_pig.py:120-150)
+    signs = np.zeros((1, 8), bool)
+    signs[0, [0, 3, 5]] = True  # table 0: bits 0 and 3 -> 9; table 1: bit 1 -> 2
+    np.testing.assert_array_equal(magicpig.pack(signs, 2, 4), [[9, 2]])
+
+
+def test_probability_end_points():
+    for dtype in ("f32", "bf16"):
+        p = magicpig.collision_prob(np.array([1.0, -1.0, 0.0], np.float32), 4, 8, dtype)
+        assert p[0] == 1.0 and p[1] == 0.0
+        assert abs(p[2] - (1 - (1 - 0.5 ** 4) ** 8)) < 2e-2
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_codes_against_reference(name):
+    g = load_golden(name)
+    wl = _workload(name)
+    _, _, meta = _oracle(wl, {"lsh_key_mean": g["key_mean"]})
+    kdiff = np.mean(meta["lsh_key_codes"] != g["key_sig"])
+    qdiff = np.mean(meta["lsh_query_codes"] != g["query_sig"])
+    assert kdiff < 2e-3 and qdiff < 2e-2, (kdiff, qdiff)
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_mask_exact_on_reference_codes(name):
+    g = load_golden(name)
+    wl = _workload(name)
+    dtype = CASES[name][0]
+    state = {"codes": g["key_sig"].astype(np.int64), "norms": np.zeros((1, 2, 0), np.float32),
+             "M": np.float32(0)}
+    mask, out, _ = _oracle(wl, {"lsh_key_mean": g["key_mean"], "lsh_state": state,
+                                "lsh_query_codes_in": g["query_sig"]})
+    idx, ptr, data = mask_ops.to_csr(mask)
+    np.testing.assert_array_equal(ptr, g["ptr"])
+    np.testing.assert_array_equal(idx, g["idx"])
+    tol = 1.6e-2 if dtype == "bf16" else 1e-5
+    np.testing.assert_allclose(data, g["data"], rtol=tol, atol=tol * 1e-2)
+    assert np.mean(data != g["data"]) < (0.2 if dtype == "bf16" else 1.0)
+    np.testing.assert_allclose(out, g["out"], atol=2e-2 if dtype == "bf16" else 1e-4, rtol=2e-2)
+
+
+# ------------------------------------------------------------------ GPU: kernels vs restatement / reference
+def _native_stack(wl, meta, k=None, v=None):
+    import torch
+    from sparse_attention_hub.sparse_attention.utils.mask_attention_utils import get_masked_attention_output
+
+    dev = "cuda:0"
+    ra = workloads.research_attention(wl.stack, wl.dtype, dev)
+    q = workloads.to_torch(wl.q, wl.dtype, dev)
+    k = workloads.to_torch(wl.k if k is None else k, wl.dtype, dev)
+    v = workloads.to_torch(wl.v if v is None else v, wl.dtype, dev)
+    meta.setdefault("projections", {})[0] = workloads.to_torch(wl.stack[-1][1]["projection"], wl.dtype, dev)
+    mask = ra.build_mask(q, k, v, None, float(wl.scaling), 0.0, meta, layer_idx=0)
+    out = get_masked_attention_output(None, q, k, v, None, None, float(wl.scaling), 0.0, mask)
+    torch.cuda.synchronize()
+    idx, ptr, data = mask.get_index_mask()
+    return (idx.cpu().numpy(), ptr.cpu().numpy(), data.float().cpu().numpy()), out.float().cpu().numpy()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", list(CASES))
+def test_gpu_magicpig_matches_oracle_and_reference(name):
+    g = load_golden(name)
+    wl = _workload(name)
+    dtype = CASES[name][0]
+    meta: dict = {}
+    (idx, ptr, data), out = _native_stack(wl, meta)
+    ref_mask, ref_out, ometa = _oracle(wl, {})
+    # key mean, key codes
+    mean = meta["key_mean"][0][:, ::4, 0, :].float().cpu().numpy()
+    np.testing.assert_array_equal(mean, ometa["lsh_key_mean"])
+    np.testing.assert_array_equal(mean, g["key_mean"])
+    codes = meta["key_signature"][0].to_reference_layout(8)[:, ::4].cpu().numpy()
+    np.testing.assert_array_equal(codes, ometa["lsh_key_codes"])
+    ri, rp, rd = mask_ops.to_csr(ref_mask)
+    np.testing.assert_array_equal(ptr, rp)
+    np.testing.assert_array_equal(idx, ri)
+    np.testing.assert_array_equal(data, rd)
+    np.testing.assert_allclose(out, ref_out, atol=2e-2 if dtype == "bf16" else 1e-4, rtol=2e-2)
+    # the reference itself
+    np.testing.assert_array_equal(codes, g["key_sig"])
+    np.testing.assert_array_equal(ptr, g["ptr"])
+    np.testing.assert_array_equal(idx, g["idx"])
+    tol = 1.6e-2 if dtype == "bf16" else 1e-5
+    np.testing.assert_allclose(data, g["data"], rtol=tol, atol=tol * 1e-2)
+    np.testing.assert_allclose(out, g["out"], atol=2e-2 if dtype == "bf16" else 1e-4, rtol=2e-2)
+
+
+@pytest.mark.gpu
+def test_gpu_magicpig_adopts_reference_signature_cache():
+    """A signature tensor cached by the reference (int64 [B,Hq,S,L]) is used as it is."""
+    import torch
+
+    name = "magicpig_bf16"
+    g = load_golden(name)
+    wl = _workload(name)
+    sig = torch.from_numpy(np.repeat(g["key_sig"].astype(np.int64), 4, axis=1)).to("cuda:0")
+    meta = {"key_signature": {0: sig},
+            "key_mean": {0: workloads.to_torch(np.repeat(g["key_mean"], 4, axis=1)[:, :, None, :], "bf16", "cuda:0")}}
+    (idx, ptr, data), out = _native_stack(wl, meta)
+    np.testing.assert_array_equal(ptr, g["ptr"])
+    np.testing.assert_array_equal(idx, g["idx"])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,K,L,Sq", [("bf16", 8, 20, 1), ("f32", 10, 16, 2), ("bf16", 4, 6, 3)])
+def test_gpu_magicpig_appended_keys(dtype, K, L, Sq):
+    """Keys arriving after the first call are hashed with the maximum norm known then."""
+    wl = workloads.magicpig(seed=63, dtype=dtype, B=2, Hq=4, Hkv=2, S=700, D=64, sink=4, window=8,
+                            lsh_l=L, lsh_k=K, Sq=Sq, n_clusters=4)
+    wl.k[:, :, 690:] *= 1.5  # larger norms among the appended keys move the maximum
+    wl.k = workloads.to_dtype(wl.k, dtype)
+    meta: dict = {}
+    _native_stack(wl, meta, k=wl.k[:, :, :690], v=wl.v[:, :, :690])
+    (idx, ptr, data), out = _native_stack(wl, meta)
+    ometa = {"lsh_projection": wl.stack[-1][1]["projection"]}
+    stacks.run_stack(wl.stack, wl.q, wl.k[:, :, :690], wl.v[:, :, :690], wl.scaling, dtype, meta=ometa)
+    for key in ("lsh_key_codes", "lsh_query_codes", "lsh_match", "lsh_dense", "full", "empty"):
+        ometa.pop(key, None)
+    ref_mask, ref_out, ometa = stacks.run_stack(wl.stack, wl.q, wl.k, wl.v, wl.scaling, dtype, meta=ometa)
+    codes = meta["key_signature"][0].to_reference_layout(4)[:, ::2].cpu().numpy()
+    np.testing.assert_array_equal(codes, ometa["lsh_key_codes"])
+    ri, rp, rd = mask_ops.to_csr(ref_mask)
+    np.testing.assert_array_equal(ptr, rp)
+    np.testing.assert_array_equal(idx, ri)
+    np.testing.assert_array_equal(data, rd)
+    np.testing.assert_allclose(out, ref_out, atol=2e-2 if dtype == "bf16" else 1e-4, rtol=2e-2)
+
+
+@pytest.mark.gpu
+def test_gpu_merge_of_two_weighted_masks():
+    """clamp(a + b, 0, 1) on bitmaps equals the dense merge (utils/mask.py:875-877)."""
+    import torch
+    from sparse_attention_hub.sparse_attention.utils.mask import Mask
+
+    rng = np.random.default_rng(5)
+    shape = (2, 3, 2, 200)
+    for dtype in (torch.float32, torch.bfloat16):
+        a = torch.from_numpy((rng.random(shape) * (rng.random(shape) < 0.2)).astype(np.float32)).to("cuda:0", dtype)
+        b = torch.from_numpy((rng.random(shape) * (rng.random(shape) < 0.3)).astype(np.float32)).to("cuda:0", dtype)
+        ones = (torch.from_numpy(rng.random(shape) < 0.1).to("cuda:0")).to(dtype)
+        for x, y in ((a, b), (a, ones), (ones, b)):
+            ma = Mask.create_mask_from_dense_mask(shape, x, dtype)
+            mb = Mask.create_mask_from_dense_mask(shape, y, dtype)
+            na = Mask._from_native(shape, dtype, ma.native_bits())
+            nb = Mask._from_native(shape, dtype, mb.native_bits())
+            merged = na.merge_mask(nb, inplace=False)
+            want = torch.clamp(x + y, 0.0, 1.0)
+            assert torch.equal(merged.get_dense_mask(), want)
