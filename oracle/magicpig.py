@@ -29,10 +29,14 @@ def lane_sum(x: np.ndarray) -> np.ndarray:
     return acc[..., 0]
 
 
-def key_mean(k: np.ndarray, dtype: str) -> np.ndarray:
-    """keys.mean(dim=2) (:175-176): float64 sum / S, rounded through float32 to the dtype."""
+def key_mean(k: np.ndarray, dtype: str, shard=None) -> np.ndarray:
+    """keys.mean(dim=2) (:175-176): float64 sum / S, rounded through float32 to the dtype.
+    With a sequence shard the sum runs over all ranks and S is the whole length."""
     s = np.asarray(k, np.float64).sum(axis=2)
-    return round_to((s / k.shape[2]).astype(F), dtype)  # [B,Hkv,D]
+    n = k.shape[2]
+    if shard is not None:
+        s, n = shard.comm.all_reduce_sum(s), shard.total
+    return round_to((s / n).astype(F), dtype)  # [B,Hkv,D]
 
 
 def centred(x: np.ndarray, mean, dtype: str) -> np.ndarray:
@@ -113,8 +117,9 @@ def collision_prob(c: np.ndarray, K: int, L: int, dtype: str) -> np.ndarray:
     return (F(1) - ul).astype(F)
 
 
-def apply(prm, st, q, k, meta) -> None:
-    """One MagicPig.add_mask (:510-593) on the stack state."""
+def apply(prm, st, q, k, meta, shard=None) -> None:
+    """One MagicPig.add_mask (:510-593) on the stack state.  `shard` (begin, total, comm):
+    `k` is one rank's key range; the key mean and the maximum key norm are global."""
     dtype = st.dtype
     r = lambda v: round_to(np.asarray(v, F), dtype)  # noqa: E731
     B, Hq, Sq, D = q.shape
@@ -125,7 +130,7 @@ def apply(prm, st, q, k, meta) -> None:
     mean = None
     if prm.get("center", True):
         if meta.get("lsh_key_mean") is None:
-            meta["lsh_key_mean"] = key_mean(k, dtype)
+            meta["lsh_key_mean"] = key_mean(k, dtype, shard)
         mean = meta["lsh_key_mean"]
     # key state: norms of all keys seen, running maximum, codes computed with the maximum of
     # the call that first saw each key
@@ -140,6 +145,8 @@ def apply(prm, st, q, k, meta) -> None:
         c_new = centred(k[:, :, n0:], None if mean is None else mean[:, :, None, :], dtype)
         nk_new = norms(c_new, dtype)
         state["M"] = F(max(state["M"], nk_new.max()))
+        if shard is not None:
+            state["M"] = F(shard.comm.all_reduce_max(np.array([state["M"]], F))[0])
         codes_new = key_codes(k[:, :, n0:], mean, nk_new, state["M"], proj, L, K, dtype)
         state["codes"] = np.concatenate([state["codes"], codes_new], axis=2)
         state["norms"] = np.concatenate([state["norms"], nk_new], axis=2)

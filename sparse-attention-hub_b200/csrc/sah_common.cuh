@@ -152,6 +152,10 @@ enum SahProfSlot {
   SAH_PROF_ATTN_PLAN = 5,
   SAH_PROF_ATTN_MERGE = 6,
   SAH_PROF_OTHER = 7,
+  SAH_PROF_LSH_MATCH = 8,
+  SAH_PROF_LSH_PROB = 9,
+  SAH_PROF_PQ_SCORES = 10,
+  SAH_PROF_ADAPTIVE = 11,
   SAH_PROF_SLOTS = 16
 };
 void sah_prof_begin(int slot, cudaStream_t st);

@@ -524,3 +524,162 @@ extern "C" int sah_hash_topk(const uint32_t* kcodes, int64_t kc_stride, const ui
   sah_prof_end(SAH_PROF_HASH_TOPK, (cudaStream_t)stream);
   return SAH_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// Sequence-sharded Hamming top-k: the keys of a row are spread over `world` ranks (contiguous
+// ranges in rank order).  Each rank histograms its range (sah_hash_hist), the histograms of
+// all ranks are gathered by the caller, and every rank derives the same global threshold and
+// its own share of the ties at the threshold (sah_hash_shard_plan) -- ties go to the lowest
+// global column, that is to the lower ranks first -- and emits its part (sah_hash_emit).
+// The union over ranks is exactly the single-device selection.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+hash_hist_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
+                 const uint32_t* __restrict__ qcodes, int nbits, int Sq, int64_t S, int64_t W,
+                 const uint32_t* __restrict__ prev_bits, int32_t* __restrict__ hist_out) {
+  __shared__ unsigned int hist[32][HT_BINS];
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int64_t row = blockIdx.x;
+  const uint32_t* kc = kcodes + (row / Sq) * kc_stride;
+  const uint32_t qc = qcodes[row];
+  const uint32_t* prev_row = prev_bits + row * W;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(kc) & 15) == 0);
+  for (int i = tid; i < 32 * HT_BINS; i += 1024) (&hist[0][0])[i] = 0u;
+  __syncthreads();
+  for (int64_t w = tid; w < W; w += 1024) {
+    uint32_t codes[32];
+    ht_load_codes(kc, w, S, aligned, codes);
+    const int64_t c0 = w * 32;
+    uint32_t valid = ~prev_row[w];
+    if (c0 + 32 > S) valid &= (c0 >= S) ? 0u : ((1u << (S - c0)) - 1u);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const int sc = nbits - __popc(codes[i] ^ qc);
+      if ((valid >> i) & 1u) atomicAdd(&hist[warp][sc], 1u);
+    }
+  }
+  __syncthreads();
+  if (tid < 33) {
+    unsigned int s = 0;
+    for (int w2 = 0; w2 < 32; ++w2) s += hist[w2][tid];
+    hist_out[row * 33 + tid] = (int32_t)s;
+  }
+}
+
+extern "C" int sah_hash_hist(const uint32_t* kcodes, int64_t kc_stride, const uint32_t* qcodes,
+                             int nbits, int B, int Hq, int Sq, int64_t S, int64_t W,
+                             const uint32_t* prev_bits, int32_t* hist, void* stream) {
+  SAH_REQUIRE(kcodes && qcodes && prev_bits && hist, "hash_hist: null pointer");
+  SAH_REQUIRE(nbits > 0 && nbits <= 32, "hash_hist: nbits must be 1..32");
+  SAH_REQUIRE(kc_stride >= S && B > 0 && Hq > 0 && Sq > 0 && S > 0 && W * 32 >= S, "hash_hist: bad extents");
+  const int64_t rows = (int64_t)B * Hq * Sq;
+  hash_hist_kernel<<<(unsigned)rows, 1024, 0, (cudaStream_t)stream>>>(kcodes, kc_stride, qcodes, nbits, Sq,
+                                                                     S, W, prev_bits, hist);
+  SAH_LAUNCH_CHECK("hash_hist");
+  return SAH_OK;
+}
+
+// hist_all [world][rows][33]; one thread per row.  thr[row]: scores above it are taken whole
+// (-1: every candidate, 64: none); need[row]: ties at thr this rank takes.
+__global__ void hash_shard_plan_kernel(const int32_t* __restrict__ hist_all, int world, int rank,
+                                       int64_t rows, int64_t k, int32_t* __restrict__ thr_out,
+                                       int64_t* __restrict__ need_out) {
+  const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  long long ge = 0;  // candidates scoring >= bin, over all ranks
+  int thr = -1;
+  long long need = 0;
+  if (k <= 0) {
+    thr = 64;
+  } else {
+    for (int bin = 32; bin >= 0; --bin) {
+      long long here = 0, before_me = 0, mine = 0;
+      for (int g = 0; g < world; ++g) {
+        const long long c = hist_all[((int64_t)g * rows + row) * 33 + bin];
+        if (g < rank) before_me += c;
+        if (g == rank) mine = c;
+        here += c;
+      }
+      if (ge + here >= k) {  // the k-th best score is this bin
+        thr = bin;
+        const long long ties = k - ge;            // ties to take over all ranks
+        const long long left = ties - before_me;  // what lower ranks leave for this one
+        need = left <= 0 ? 0 : (left < mine ? left : mine);
+        break;
+      }
+      ge += here;
+    }
+  }
+  thr_out[row] = thr;
+  need_out[row] = need;
+}
+
+extern "C" int sah_hash_shard_plan(const int32_t* hist_all, int world, int rank, int64_t rows,
+                                   int64_t k, int32_t* thr, int64_t* need, void* stream) {
+  SAH_REQUIRE(hist_all && thr && need, "hash_shard_plan: null pointer");
+  SAH_REQUIRE(world > 0 && rank >= 0 && rank < world && rows > 0, "hash_shard_plan: bad extents");
+  hash_shard_plan_kernel<<<(unsigned)sah_ceil_div(rows, 128), 128, 0, (cudaStream_t)stream>>>(
+      hist_all, world, rank, rows, k, thr, need);
+  SAH_LAUNCH_CHECK("hash_shard_plan");
+  return SAH_OK;
+}
+
+__global__ void __launch_bounds__(1024)
+hash_emit_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
+                 const uint32_t* __restrict__ qcodes, int nbits, int Sq, int64_t S, int64_t W,
+                 const uint32_t* __restrict__ prev_bits, const int32_t* __restrict__ thr_in,
+                 const int64_t* __restrict__ need_in, uint32_t* __restrict__ out_bits) {
+  __shared__ long long scan[33];
+  const int tid = threadIdx.x;
+  const int64_t row = blockIdx.x;
+  const uint32_t* kc = kcodes + (row / Sq) * kc_stride;
+  const uint32_t qc = qcodes[row];
+  const uint32_t* prev_row = prev_bits + row * W;
+  uint32_t* out_row = out_bits + row * W;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(kc) & 15) == 0);
+  const int thr = thr_in[row];
+  const long long need = need_in[row];
+  long long base = 0;
+  for (int64_t w0 = 0; w0 < W; w0 += 1024) {
+    const int64_t w = w0 + tid;
+    uint32_t gt = 0u, eq = 0u, pw = 0u;
+    if (w < W) {
+      uint32_t codes[32];
+      ht_load_codes(kc, w, S, aligned, codes);
+      pw = prev_row[w];
+      const int64_t c0 = w * 32;
+      uint32_t valid = ~pw;
+      if (c0 + 32 > S) valid &= (c0 >= S) ? 0u : ((1u << (S - c0)) - 1u);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int sc = nbits - __popc(codes[i] ^ qc);
+        gt |= (sc > thr ? 1u : 0u) << i;
+        eq |= (sc == thr ? 1u : 0u) << i;
+      }
+      gt &= valid;
+      eq &= valid;
+    }
+    long long total_eq;
+    const long long before = sah_block_excl_scan<long long>((long long)__popc(eq), scan, &total_eq);
+    if (w < W) {
+      const long long quota = need - (base + before);
+      const int take = quota > 32 ? 32 : (quota < 0 ? 0 : (int)quota);
+      out_row[w] = pw | gt | sah_lowest_bits(eq, take);
+    }
+    base += total_eq;
+  }
+}
+
+extern "C" int sah_hash_emit(const uint32_t* kcodes, int64_t kc_stride, const uint32_t* qcodes,
+                             int nbits, int B, int Hq, int Sq, int64_t S, int64_t W,
+                             const uint32_t* prev_bits, const int32_t* thr, const int64_t* need,
+                             uint32_t* out_bits, void* stream) {
+  SAH_REQUIRE(kcodes && qcodes && prev_bits && thr && need && out_bits, "hash_emit: null pointer");
+  SAH_REQUIRE(nbits > 0 && nbits <= 32, "hash_emit: nbits must be 1..32");
+  SAH_REQUIRE(kc_stride >= S && B > 0 && Hq > 0 && Sq > 0 && S > 0 && W * 32 >= S, "hash_emit: bad extents");
+  const int64_t rows = (int64_t)B * Hq * Sq;
+  hash_emit_kernel<<<(unsigned)rows, 1024, 0, (cudaStream_t)stream>>>(kcodes, kc_stride, qcodes, nbits, Sq,
+                                                                     S, W, prev_bits, thr, need, out_bits);
+  SAH_LAUNCH_CHECK("hash_emit");
+  return SAH_OK;
+}

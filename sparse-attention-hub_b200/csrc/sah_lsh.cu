@@ -445,6 +445,7 @@ extern "C" int sah_lsh_match(const void* planes, int64_t cap, const void* qcodes
   const int64_t words = (S + 31) / 32;
   dim3 grid((unsigned)((words + 255) / 256), (unsigned)(B * (Hq / G)));
   cudaStream_t st = (cudaStream_t)stream;
+  sah_prof_begin(SAH_PROF_LSH_MATCH, st);
   if (csz == 1)
     lsh_match_kernel<uint8_t><<<grid, 256, smem, st>>>(reinterpret_cast<const uint8_t*>(planes), cap,
                                                        reinterpret_cast<const uint8_t*>(qcodes), Hq, Sq,
@@ -454,6 +455,7 @@ extern "C" int sah_lsh_match(const void* planes, int64_t cap, const void* qcodes
                                                         reinterpret_cast<const uint16_t*>(qcodes), Hq,
                                                         Sq, G, L, S, W, out_bits);
   SAH_LAUNCH_CHECK("lsh_match");
+  sah_prof_end(SAH_PROF_LSH_MATCH, st);
   return SAH_OK;
 }
 
@@ -481,6 +483,58 @@ __device__ __forceinline__ float lsh_collision_prob<float>(float c, int K, int L
   return __fsub_rn(1.0f, ul);
 }
 
+// x / M for a fixed divisor.  bf16: the quotient of two bf16 values rounded to bf16 depends on
+// the dividend only through its 7 mantissa bits (a power-of-two factor commutes with both
+// roundings), so a 128-entry table of bf16((1 + m/128) / M), built with true divisions,
+// replaces the division; dividends with a zero or all-ones exponent field take the division.
+// fp32: the IEEE division.
+template <typename T>
+struct LshDivM;
+template <>
+struct LshDivM<__nv_bfloat16> {
+  static __device__ __forceinline__ void build(float* tab, float M) {
+    for (int m = threadIdx.x; m < 128; m += blockDim.x)
+      tab[m] = sah_round_to<__nv_bfloat16>(__fdiv_rn(1.0f + (float)m * 0.0078125f, M));
+  }
+  static __device__ __forceinline__ float div(float c, float M, const float* tab) {
+    const uint32_t u = __float_as_uint(c);
+    const uint32_t e = (u >> 23) & 0xffu;
+    if (e == 0u || e == 255u) return sah_round_to<__nv_bfloat16>(__fdiv_rn(c, M));
+    const float r = __fmul_rn(__uint_as_float(u & 0xff800000u), tab[(u >> 16) & 0x7fu]);
+    // the product of a power of two and a bf16 value is exact unless it leaves the normal range
+    const uint32_t er = (__float_as_uint(r) >> 23) & 0xffu;
+    return (er == 0u || er == 255u) ? sah_round_to<__nv_bfloat16>(__fdiv_rn(c, M)) : r;
+  }
+};
+template <>
+struct LshDivM<float> {
+  static __device__ __forceinline__ void build(float*, float) {}
+  static __device__ __forceinline__ float div(float c, float M, const float*) { return __fdiv_rn(c, M); }
+};
+
+// x / den for a per-key divisor.  bf16: both operands are bf16 values; with y = RN(1 / den),
+// q = RN(x * y), r = x - q * den (exact in one fma), RN(q + r * y) rounded to bf16 equals the
+// IEEE quotient rounded to bf16 for every pair of bf16 significands (checked exhaustively on
+// the host, tests/test_magicpig.py); operands outside the normal range take the division.
+template <typename T>
+__device__ __forceinline__ float lsh_div_den(float x, float den, float rcp);
+template <>
+__device__ __forceinline__ float lsh_div_den<__nv_bfloat16>(float x, float den, float rcp) {
+  const float q = __fmul_rn(x, rcp);
+  const float r = __fmaf_rn(-q, den, x);
+  const float q2 = __fmaf_rn(r, rcp, q);
+  const uint32_t e = (__float_as_uint(q2) >> 23) & 0xffu;
+  if (e < 2u || e >= 254u) return sah_round_to<__nv_bfloat16>(__fdiv_rn(x, den));
+  return sah_round_to<__nv_bfloat16>(q2);
+}
+template <>
+__device__ __forceinline__ float lsh_div_den<float>(float x, float den, float) {
+  return __fdiv_rn(x, den);
+}
+
+// One CTA per (KV group, chunk of bitmap words); a warp takes a word, forms the union of the
+// group's rows for it, transforms each key of the union once (centre, scale, normalise) and
+// dots it with the unit query of every row that matched it.
 template <typename T>
 __global__ void __launch_bounds__(256)
 lsh_prob_kernel(const T* __restrict__ k, int64_t ks_b, int64_t ks_h, int64_t ks_s, int Hq, int Sq,
@@ -488,29 +542,37 @@ lsh_prob_kernel(const T* __restrict__ k, int64_t ks_b, int64_t ks_h, int64_t ks_
                 int64_t cap, const unsigned int* __restrict__ max_bits,
                 const float* __restrict__ qunit, const uint32_t* __restrict__ bits,
                 const int32_t* __restrict__ wpre, const int64_t* __restrict__ ptr, int64_t W,
-                int K, int L, const uint16_t* __restrict__ table, T* __restrict__ data) {
+                int K, int L, const uint16_t* __restrict__ table, int q_in_smem,
+                T* __restrict__ data) {
+  extern __shared__ __align__(16) unsigned char lsh_smem[];
+  float* tab = reinterpret_cast<float*>(lsh_smem);  // [128]
+  float* qs = tab + 128;                            // [R][D] when q_in_smem
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
-  const int64_t row = blockIdx.x;
-  const int64_t bh = row / Sq;
-  const int h = (int)(bh % Hq);
-  const int64_t b = bh / Hq;
   const int Hkv = Hq / G;
-  const int64_t kvh = b * Hkv + h / G;
+  const int64_t kvh = blockIdx.x;  // b * Hkv + hkv
+  const int64_t b = kvh / Hkv;
+  const int hkv = (int)(kvh % Hkv);
+  const int R = G * Sq;
   const int per = D / 32;
   const float M = __uint_as_float(*max_bits);
-  float m[LSH_MAX_PER_LANE], qu[LSH_MAX_PER_LANE];
+  const int64_t row0 = (b * Hq + (int64_t)hkv * G) * Sq;  // rows of a group are contiguous
+  LshDivM<T>::build(tab, M);
+  if (q_in_smem)
+    for (int i = threadIdx.x; i < R * D; i += blockDim.x) qs[i] = qunit[row0 * D + i];
+  __syncthreads();
+  const float* qsrc = q_in_smem ? qs : qunit + row0 * D;
+  float m[LSH_MAX_PER_LANE];
   if (mean) lsh_load_lane<T>(mean + kvh * D, per, lane, m);
-#pragma unroll
-  for (int t = 0; t < LSH_MAX_PER_LANE; ++t)
-    if (t < per) qu[t] = qunit[row * D + lane * per + t];
-  const T* kbase = k + b * ks_b + (h / G) * ks_h;
-  const int64_t base = ptr[row];
+  const T* kbase = k + b * ks_b + hkv * ks_h;
   for (int64_t w = (int64_t)blockIdx.y * nwarp + warp; w < W; w += (int64_t)gridDim.y * nwarp) {
-    uint32_t word = bits[row * W + w];
-    int64_t pos = base + wpre[row * W + w];
-    while (word) {
-      const int bit = __ffs(word) - 1;
-      word &= word - 1;
+    // union of the rows' words (lane r holds row r, r + 32, ...)
+    uint32_t uni = 0u;
+    for (int r = lane; r < R; r += 32) uni |= bits[(row0 + r) * W + w];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) uni |= __shfl_xor_sync(0xffffffffu, uni, o);
+    while (uni) {
+      const int bit = __ffs(uni) - 1;
+      uni &= uni - 1;
       const int64_t s = w * 32 + bit;
       float x[LSH_MAX_PER_LANE];
       lsh_load_lane<T>(kbase + s * ks_s, per, lane, x);
@@ -519,21 +581,32 @@ lsh_prob_kernel(const T* __restrict__ k, int64_t ks_b, int64_t ks_h, int64_t ks_
       for (int t = 0; t < LSH_MAX_PER_LANE; ++t)
         if (t < per) {
           const float c = mean ? sah_round_to<T>(__fsub_rn(x[t], m[t])) : x[t];
-          x[t] = sah_round_to<T>(__fdiv_rn(c, M));
+          x[t] = LshDivM<T>::div(c, M, tab);
           acc = __fadd_rn(acc, __fmul_rn(x[t], x[t]));
         }
       const float aug = lsh_augment<T>(norms[kvh * cap + s], M);
-      // |transformed key|, then its unit vector dotted with the query's
+      // |transformed key|, then its unit vector
       const float n2 = __fadd_rn(lsh_warp_sum(acc), __fmul_rn(aug, aug));
       const float den = sah_round_to<T>(__fadd_rn(sah_round_to<T>(sqrtf(n2)), 1e-8f));
-      acc = 0.f;
+      const float rcp = __frcp_rn(den);
 #pragma unroll
       for (int t = 0; t < LSH_MAX_PER_LANE; ++t)
-        if (t < per) acc = __fadd_rn(acc, __fmul_rn(qu[t], sah_round_to<T>(__fdiv_rn(x[t], den))));
-      float c = sah_round_to<T>(lsh_warp_sum(acc));
-      c = fminf(fmaxf(c, -1.0f), 1.0f);
-      if (lane == 0) data[pos] = sah_from_float<T>(lsh_collision_prob<T>(c, K, L, table));
-      ++pos;
+        if (t < per) x[t] = lsh_div_den<T>(x[t], den, rcp);
+      for (int r = 0; r < R; ++r) {
+        const uint32_t word = bits[(row0 + r) * W + w];  // warp-uniform, L1 resident
+        if (!((word >> bit) & 1u)) continue;
+        const float* qu = qsrc + r * D + lane * per;
+        acc = 0.f;
+#pragma unroll
+        for (int t = 0; t < LSH_MAX_PER_LANE; ++t)
+          if (t < per) acc = __fadd_rn(acc, __fmul_rn(qu[t], x[t]));
+        float c = sah_round_to<T>(lsh_warp_sum(acc));
+        c = fminf(fmaxf(c, -1.0f), 1.0f);
+        if (lane == 0) {
+          const int64_t pos = ptr[row0 + r] + wpre[(row0 + r) * W + w] + __popc(word & ((1u << bit) - 1u));
+          data[pos] = sah_from_float<T>(lsh_collision_prob<T>(c, K, L, table));
+        }
+      }
     }
   }
 }
@@ -547,20 +620,28 @@ extern "C" int sah_lsh_prob(const void* keys, int dtype, int64_t ks_b, int64_t k
   SAH_REQUIRE(keys && norms && max_norm_bits && qunit && bits && wpre && ptr && data,
               "lsh_prob: null pointer");
   SAH_REQUIRE(D % 32 == 0 && D <= 32 * LSH_MAX_PER_LANE, "lsh_prob: head_dim must be a multiple of 32, <= 256");
+  SAH_REQUIRE(G > 0 && Hq % G == 0, "lsh_prob: bad head grouping");
   SAH_REQUIRE(dtype != SAH_BF16 || table != nullptr, "lsh_prob: bf16 needs the probability table");
-  const int64_t rows = (int64_t)B * Hq * Sq;
+  const int64_t groups = (int64_t)B * (Hq / G);
+  const int R = G * Sq;
   if (sm_count <= 0) sm_count = 148;
-  int64_t gx = (W + 7) / 8;
-  const int64_t cap_x = ((int64_t)sm_count * 8 + rows - 1) / rows;
-  if (gx > cap_x) gx = cap_x;
-  if (gx < 1) gx = 1;
-  dim3 grid((unsigned)rows, (unsigned)gx);
+  int64_t gy = (W + 7) / 8;
+  const int64_t cap_y = ((int64_t)sm_count * 8 + groups - 1) / groups;
+  if (gy > cap_y) gy = cap_y;
+  if (gy < 1) gy = 1;
+  if (gy > 65535) gy = 65535;
+  size_t smem = 128 * sizeof(float);
+  const int q_in_smem = (size_t)R * D * sizeof(float) <= 40 * 1024;
+  if (q_in_smem) smem += (size_t)R * D * sizeof(float);
+  dim3 grid((unsigned)groups, (unsigned)gy);
+  sah_prof_begin(SAH_PROF_LSH_PROB, (cudaStream_t)stream);
   SAH_DISPATCH_DTYPE(dtype, T, {
-    lsh_prob_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>(
+    lsh_prob_kernel<T><<<grid, 256, smem, (cudaStream_t)stream>>>(
         reinterpret_cast<const T*>(keys), ks_b, ks_h, ks_s, Hq, Sq, G, D,
         reinterpret_cast<const T*>(mean), norms, cap, max_norm_bits, qunit, bits, wpre, ptr, W, K, L,
-        table, reinterpret_cast<T*>(data));
+        table, q_in_smem, reinterpret_cast<T*>(data));
   });
   SAH_LAUNCH_CHECK("lsh_prob");
+  sah_prof_end(SAH_PROF_LSH_PROB, (cudaStream_t)stream);
   return SAH_OK;
 }

@@ -282,6 +282,7 @@ extern "C" int sah_pq_scores(const void* q, int dtype, int64_t qs_b, int64_t qs_
     return sah_fail(SAH_ERR_UNSUPPORTED, "pq_scores: %d x %d lookup table does not fit", n_sub, n_cent);
   dim3 grid((unsigned)sah_ceil_div(n_keys, PQ_TILE), (unsigned)sah_ceil_div(R, PQ_ROWS),
             (unsigned)((int64_t)B * Hkv));
+  sah_prof_begin(SAH_PROF_PQ_SCORES, (cudaStream_t)stream);
   SAH_DISPATCH_DTYPE(dtype, T, {
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(pq_scores_kernel<T>,
@@ -293,5 +294,6 @@ extern "C" int sah_pq_scores(const void* q, int dtype, int64_t qs_b, int64_t qs_
         init_offset, S, n_sub, sub_d, n_cent, (T*)scores);
   });
   SAH_LAUNCH_CHECK("pq_scores");
+  sah_prof_end(SAH_PROF_PQ_SCORES, (cudaStream_t)stream);
   return SAH_OK;
 }

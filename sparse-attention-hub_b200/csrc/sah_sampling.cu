@@ -231,6 +231,7 @@ extern "C" int sah_adaptive_budget(const void* scores, int dtype, float scaling,
                     (long long)S);
   const int64_t rows = (int64_t)B * Hq * Sq;
   cudaStream_t st = (cudaStream_t)stream;
+  sah_prof_begin(SAH_PROF_ADAPTIVE, st);
   SAH_DISPATCH_DTYPE(dtype, T, {
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(adaptive_budget_kernel<T>,
@@ -240,6 +241,7 @@ extern "C" int sah_adaptive_budget(const void* scores, int dtype, float scaling,
     adaptive_budget_kernel<T><<<(unsigned)rows, 1024, smem, st>>>(a);
   });
   SAH_LAUNCH_CHECK("adaptive_budget");
+  sah_prof_end(SAH_PROF_ADAPTIVE, st);
   return SAH_OK;
 }
 

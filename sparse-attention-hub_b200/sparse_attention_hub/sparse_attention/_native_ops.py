@@ -199,6 +199,35 @@ def hash_topk(kcodes: torch.Tensor, n_keys: int, qcodes: torch.Tensor, nbits: in
     return dst
 
 
+def hash_topk_sharded(kcodes: torch.Tensor, qcodes: torch.Tensor, nbits: int, previous_mask: Mask,
+                      k: int, shape: Tuple[int, int, int, int], comm) -> NativeBits:
+    """`hash_topk` when the row's keys are spread over the ranks of `comm` (contiguous ranges in
+    rank order): local histogram, one all-gather of `rows x 33` counters, global threshold
+    with the ties served to the lowest columns first, local emit.  `k` counts keys of the
+    whole sequence; `shape[-1]` is the local key count."""
+    lib = _native.load()
+    B, Hq, Sq, S = shape
+    if kcodes.shape[-1] < S or not kcodes.is_contiguous():
+        raise ValueError("key codes must be contiguous [B, Hq, capacity >= S]")
+    dev = kcodes.device
+    st = _native.stream_of(dev)
+    prev = previous_mask.native_bits()
+    rows = prev.rows
+    hist = torch.empty((rows, 33), dtype=torch.int32, device=dev)
+    args = (kcodes.data_ptr(), kcodes.shape[-1], qcodes.data_ptr(), nbits, B, Hq, Sq, S, prev.words,
+            prev.bits.data_ptr())
+    _native.check(lib.sah_hash_hist(*args, hist.data_ptr(), st), "sah_hash_hist")
+    hist_all = comm.all_gather(hist)
+    thr = torch.empty(rows, dtype=torch.int32, device=dev)
+    need = torch.empty(rows, dtype=torch.int64, device=dev)
+    _native.check(lib.sah_hash_shard_plan(hist_all.data_ptr(), comm.world, comm.rank, rows, k,
+                                          thr.data_ptr(), need.data_ptr(), st), "sah_hash_shard_plan")
+    dst = NativeBits(torch.empty_like(prev.bits), rows, S)
+    _native.check(lib.sah_hash_emit(*args, thr.data_ptr(), need.data_ptr(), dst.bits.data_ptr(), st),
+                  "sah_hash_emit")
+    return dst
+
+
 # ---- sampled sets ---------------------------------------------------------------
 def merge_sampled(previous_mask: Mask, cols: torch.Tensor, sptr: torch.Tensor,
                   row_weight: torch.Tensor) -> Mask:

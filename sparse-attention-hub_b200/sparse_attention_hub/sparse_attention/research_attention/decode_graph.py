@@ -59,8 +59,13 @@ class DecodeStepGraph:
         torch.cuda.current_stream(queries.device).wait_stream(side)
         torch.cuda.synchronize(queries.device)
 
+        # The attention scratch is cached per (stream, shape): capture on the warm-up stream so
+        # that the capture finds it, and keep it alive for as long as the graph may replay.
+        from ..utils import mask_attention_utils
+
+        self._scratch = list(mask_attention_utils._workspace_cache.values())
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
+        with torch.cuda.graph(self.graph, stream=side):
             self.out = call()
 
     def replay(self, queries: Optional[torch.Tensor] = None) -> torch.Tensor:

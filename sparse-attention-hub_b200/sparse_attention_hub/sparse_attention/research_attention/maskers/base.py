@@ -91,6 +91,14 @@ class ResearchMasker(ABC):
         return Mask.create_from_row_wise_idx(shape=self._mask_shape(dims), row_wise_idx=indices,
                                              data=data, mask_type="dense", dtype=dtype)
 
+    def _refuse_sequence_shard(self, kwargs: Dict[str, Any]) -> None:
+        """Maskers whose selection needs the whole sequence (a global top-k, a global sample
+        budget) must not treat one rank's key range as all of it."""
+        if kwargs.get("sequence_shard") is not None:
+            raise NotImplementedError(
+                f"{type(self).__name__} does not run on a sequence shard; "
+                "Sink, Local, HashAttention top-k and MagicPig do")
+
     def _calculate_effective_size(self, size_param: Union[float, int], seq_len_keys: int) -> int:
         """A float is a fraction of the key length (truncated), an int is a count."""
         if isinstance(size_param, float):

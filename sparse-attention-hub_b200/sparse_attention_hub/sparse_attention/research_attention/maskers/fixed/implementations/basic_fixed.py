@@ -52,16 +52,23 @@ class LocalMasker(FixedMasker):
         if previous_mask.is_full_mask():
             return previous_mask
         dims = self._extract_tensor_dimensions(keys, queries)
-        window = self._calculate_effective_window_size(dims.seq_len_keys)
-        if self._should_use_full_attention(dims, window):
+        # With a sequence shard the keys at hand are columns [begin, begin + S) of `total`
+        # keys: sizes and the full-attention rule follow the whole sequence.
+        shard = kwargs.get("sequence_shard")
+        total = shard.total if shard is not None else dims.seq_len_keys
+        window = self._calculate_effective_window_size(total)
+        if total <= window + dims.seq_len_queries:
             return self._create_full_mask(dims, previous_mask.dtype, previous_mask.device)
-        return self.get_updated_mask(dims, window, keys, previous_mask)
+        return self.get_updated_mask(dims, window, keys, previous_mask,
+                                     key_offset=shard.begin if shard is not None else 0, total=total)
 
     def get_updated_mask(self, tensor_dims: AttentionTensorDimensions, effective_window_size: int,
-                         keys: torch.Tensor, previous_mask: Mask, mode: str = "native") -> Mask:
+                         keys: torch.Tensor, previous_mask: Mask, mode: str = "native",
+                         key_offset: int = 0, total: int = None) -> Mask:
         S, Sq = tensor_dims.seq_len_keys, tensor_dims.seq_len_queries
-        band_lo = S - Sq - effective_window_size + 1
-        band_hi = S - Sq + 1
+        total = S if total is None else total
+        band_lo = total - Sq - effective_window_size + 1 - key_offset
+        band_hi = total - Sq + 1 - key_offset
         nb = _native_ops.unit_weight_bits(previous_mask)
         if nb is not None:
             _native_ops.fill_band(nb, Sq, band_lo, 1, band_hi, 1, 1)
@@ -136,20 +143,25 @@ class SinkMasker(FixedMasker):
         if previous_mask.is_full_mask():
             return previous_mask
         dims = self._extract_tensor_dimensions(keys, queries)
-        sink = self._calculate_effective_sink_size(dims.seq_len_keys)
-        if self._should_use_full_attention(dims, sink):
+        shard = kwargs.get("sequence_shard")  # see LocalMasker.add_mask
+        total = shard.total if shard is not None else dims.seq_len_keys
+        sink = self._calculate_effective_sink_size(total)
+        if total <= sink:
             return self._create_full_mask(dims, previous_mask.dtype, previous_mask.device)
-        return self.get_updated_mask(dims, sink, keys, previous_mask)
+        return self.get_updated_mask(dims, sink, keys, previous_mask,
+                                     key_offset=shard.begin if shard is not None else 0)
 
     def get_updated_mask(self, tensor_dims: AttentionTensorDimensions, effective_sink_size: int,
-                         keys: torch.Tensor, previous_mask: Mask, mode: str = "native") -> Mask:
+                         keys: torch.Tensor, previous_mask: Mask, mode: str = "native",
+                         key_offset: int = 0) -> Mask:
         nb = _native_ops.unit_weight_bits(previous_mask)
+        hi = max(0, effective_sink_size - key_offset)
         if nb is not None:
-            _native_ops.fill_band(nb, tensor_dims.seq_len_queries, 0, 0, effective_sink_size, 0, 1)
+            _native_ops.fill_band(nb, tensor_dims.seq_len_queries, 0, 0, hi, 0, 1)
             return Mask._from_native(previous_mask.shape, previous_mask.dtype,
                                      _native_ops.fresh_native(nb))
         dense = previous_mask.get_dense_mask()
-        dense[..., :effective_sink_size] = 1.0
+        dense[..., :hi] = 1.0
         return Mask.create_mask_from_dense_mask(dense.shape, dense, previous_mask.dtype)
 
     def _calculate_effective_sink_size(self, seq_len_keys: int) -> int:

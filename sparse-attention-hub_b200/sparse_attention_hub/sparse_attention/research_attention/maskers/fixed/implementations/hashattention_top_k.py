@@ -87,8 +87,12 @@ class HashAttentionTopKMasker(TopKMasker):
         if previous_mask.is_full_mask():
             return previous_mask
         dims = self._extract_tensor_dimensions(keys, queries)
-        heavy = self._calculate_effective_heavy_size(dims.seq_len_keys)
-        if self._should_use_full_attention(dims, heavy):
+        # On a sequence shard the keys at hand are one rank's range: k and the full-attention
+        # rule follow the whole sequence, and the top-k is global (exact, same tie rule).
+        shard = kwargs.get("sequence_shard")
+        total = shard.total if shard is not None else dims.seq_len_keys
+        heavy = self._calculate_effective_heavy_size(total)
+        if total <= heavy:
             return self._create_full_mask(dims, previous_mask.dtype, previous_mask.device)
         if self.hat_mlp_activation not in ("relu", "silu", "gelu", "tanh"):
             raise ValueError(f"Unsupported activation function: {self.hat_mlp_activation}")
@@ -97,8 +101,15 @@ class HashAttentionTopKMasker(TopKMasker):
         key_sig = self._update_key_signatures(keys, queries.shape[1], sparse_meta_data, layer_idx)
         query_codes = self._encode(queries, queries.shape[1], layer_idx, "query")
         shape = self._mask_shape(dims)
-        merged = _native_ops.hash_topk(key_sig.codes, key_sig.length, query_codes, self.hat_bits,
-                                       attention_mask, queries.dtype, previous_mask, heavy, shape)
+        if shard is not None:
+            if attention_mask is not None:
+                raise NotImplementedError(
+                    "HashAttention top-k on a sequence shard takes no additive attention mask")
+            merged = _native_ops.hash_topk_sharded(key_sig.codes, query_codes, self.hat_bits,
+                                                   previous_mask, heavy, shape, shard.comm)
+        else:
+            merged = _native_ops.hash_topk(key_sig.codes, key_sig.length, query_codes, self.hat_bits,
+                                           attention_mask, queries.dtype, previous_mask, heavy, shape)
         if _native_ops.unit_weight_bits(previous_mask) is None:
             new_only = _native_ops.bits_andnot(merged, previous_mask.native_bits())
             add = Mask._from_native(shape, previous_mask.dtype, new_only)

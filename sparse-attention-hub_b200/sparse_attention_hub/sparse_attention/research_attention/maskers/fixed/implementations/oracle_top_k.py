@@ -39,6 +39,7 @@ class OracleTopK(TopKMasker):
     def add_mask(self, keys, queries, values, attention_mask, scaling, dropout,
                  sparse_meta_data: Dict[Any, Any], previous_mask: Mask,
                  **kwargs: Dict[str, Any]) -> Mask:
+        self._refuse_sequence_shard(kwargs)
         if previous_mask.is_full_mask():
             return previous_mask
         dims = self._extract_tensor_dimensions(keys, queries)

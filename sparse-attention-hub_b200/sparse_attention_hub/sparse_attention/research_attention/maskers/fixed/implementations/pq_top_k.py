@@ -103,6 +103,7 @@ class PQCache(TopKMasker):
     def add_mask(self, keys, queries, values, attention_mask, scaling, dropout,
                  sparse_meta_data: Dict[Any, Any], previous_mask: Mask,
                  **kwargs: Dict[str, Any]) -> Mask:
+        self._refuse_sequence_shard(kwargs)
         layer_idx = self._validate_inputs(sparse_meta_data, kwargs)
         if previous_mask.is_full_mask():
             return previous_mask

@@ -78,6 +78,8 @@ class PackedLSHSignatures:
     def __init__(self, planes: torch.Tensor, norms: torch.Tensor, max_norm: torch.Tensor,
                  length: int, lsh_k: int) -> None:
         self.planes, self.norms, self.max_norm, self.length, self.lsh_k = planes, norms, max_norm, length, lsh_k
+        # sequence-sharded use: total key count at which max_norm was last reduced over the shards
+        self.synced_total: Optional[int] = None
 
     @property
     def capacity(self) -> int:
@@ -104,6 +106,7 @@ class PackedLSHSignatures:
         new.norms[..., : self.length] = self.norms[..., : self.length]
         new.max_norm.copy_(self.max_norm)
         new.length = self.length
+        new.synced_total = self.synced_total
         return new
 
     def to_reference_layout(self, n_query_heads: int) -> torch.Tensor:
@@ -159,7 +162,7 @@ class MagicPig(SamplingMasker):
         return proj
 
     def _key_mean(self, meta: Dict[Any, Any], layer_idx: int, keys: torch.Tensor, G: int,
-                  lib, st) -> Optional[torch.Tensor]:
+                  lib, st, shard=None) -> Optional[torch.Tensor]:
         """Compact `[B, Hkv, D]` key mean in the key dtype (None when center=False); the
         reference-layout `[B, Hq, 1, D]` tensor is what sits in sparse_meta_data."""
         cache = meta.setdefault("key_mean", {})
@@ -173,6 +176,9 @@ class MagicPig(SamplingMasker):
                 lib.sah_lsh_key_sums(keys.data_ptr(), _native.dtype_code(keys.dtype), keys.stride(0),
                                      keys.stride(1), keys.stride(2), B, Hkv, 0, S, D, sums.data_ptr(), st),
                 "sah_lsh_key_sums")
+            if shard is not None:  # the mean is over the whole sequence
+                shard.comm.all_reduce_sum_(sums)
+                S = shard.total
             mean = (sums / S).to(torch.float32).to(keys.dtype)
             cache[layer_idx] = mean.repeat_interleave(G, dim=1).unsqueeze(2)
         full = cache[layer_idx]
@@ -186,7 +192,7 @@ class MagicPig(SamplingMasker):
 
     def _update_key_signatures(self, meta: Dict[Any, Any], layer_idx: int, keys: torch.Tensor,
                                n_query_heads: int, mean: Optional[torch.Tensor], proj: torch.Tensor,
-                               lib, st) -> PackedLSHSignatures:
+                               lib, st, shard=None) -> PackedLSHSignatures:
         cache = meta.setdefault("key_signature", {})
         handle = cache.get(layer_idx)
         B, Hkv, S, D = keys.shape
@@ -211,10 +217,18 @@ class MagicPig(SamplingMasker):
         if S < handle.length:
             raise ValueError(
                 f"Current number of keys ({S}) is less than cached number of keys ({handle.length})")
-        if S > handle.length:
+        # With a sequence shard the maximum key norm is over all shards: whenever the total
+        # length moved (any rank got new keys) every rank joins one 4-byte max-reduction.
+        resync = shard is not None and handle.synced_total != shard.total
+        if S > handle.length or resync:
             handle = handle.grown(S)
             s0 = handle.length
             stats(handle, s0, S)
+            if resync:
+                shard.comm.all_reduce_max_(handle.max_norm)
+                handle.synced_total = shard.total
+        if S > handle.length:
+            s0 = handle.length
             _native.check(
                 lib.sah_lsh_key_sign(*kargs, s0, S, D, _native.ptr(mean), handle.norms.data_ptr(),
                                      handle.max_norm.data_ptr(), proj.data_ptr(), self.lsh_l, self.lsh_k,
@@ -243,9 +257,10 @@ class MagicPig(SamplingMasker):
         k = keys if keys.stride(-1) == 1 else keys.contiguous()
         q = queries if queries.stride(-1) == 1 else queries.contiguous()
 
-        mean = self._key_mean(sparse_meta_data, layer_idx, k, G, lib, st)
+        shard = kwargs.get("sequence_shard")  # keys are columns [begin, begin + S) of `total`
+        mean = self._key_mean(sparse_meta_data, layer_idx, k, G, lib, st, shard)
         proj = self._projection(sparse_meta_data, layer_idx, k)
-        sig = self._update_key_signatures(sparse_meta_data, layer_idx, k, Hq, mean, proj, lib, st)
+        sig = self._update_key_signatures(sparse_meta_data, layer_idx, k, Hq, mean, proj, lib, st, shard)
 
         rows = B * Hq * Sq
         W = words_per_row(S)

@@ -47,6 +47,7 @@ class RandomSamplingMasker(SamplingMasker):
     def add_mask(self, keys, queries, values, attention_mask, scaling, dropout,
                  sparse_meta_data: Dict[Any, Any], previous_mask: Mask,
                  **kwargs: Dict[str, Any]) -> Mask:
+        self._refuse_sequence_shard(kwargs)
         if previous_mask.is_full_mask():
             return previous_mask
         B, H, Sq = queries.shape[0], queries.shape[1], queries.shape[2]

@@ -19,6 +19,7 @@ native path does not call them.
 from __future__ import annotations
 
 import ctypes
+import threading
 from typing import Any, Dict, Optional, Tuple, Union
 
 import torch
@@ -122,7 +123,9 @@ def native_masked_attention(
     _native.check(lib.sah_attn_query_sizes(B, Hq, Hkv, Sq, S, D, int(has_data),
                                            _native.sm_count(dev), ctypes.byref(sizes)),
                   "sah_attn_query_sizes")
-    ws = _workspace(dev, sizes, (dev.index, B, Hq, Hkv, Sq, S, D, has_data))
+    # scratch is reused across calls of one shape; calls that could overlap on the device
+    # (another stream, another host thread) get their own
+    ws = _workspace(dev, sizes, (dev.index, st, threading.get_ident(), B, Hq, Hkv, Sq, S, D, has_data))
     _native.check(
         lib.sah_attn_plan(nb.bits.data_ptr(), _native.ptr(nb.data), _native.ptr(nb.wpre),
                           _native.ptr(nb.ptr), code, B, Hq, Hkv, Sq, S, nb.words,
@@ -178,8 +181,11 @@ def merge_attention_partials(acc: torch.Tensor, lse: torch.Tensor, batch: int, h
     dev = acc.device
     out = torch.empty((batch, seq_len_queries, heads, D), dtype=dtype, device=dev)
     sink_t = None if sinks is None else sinks.to(device=dev, dtype=torch.float32).contiguous()
+    # named, so that the copies outlive the launch (a temporary would be freed, and its memory
+    # handed to the next allocation, as soon as its address had been read)
+    acc_c, lse_c = acc.contiguous(), lse.contiguous()
     _native.check(
-        lib.sah_attn_merge_parts(acc.contiguous().data_ptr(), lse.contiguous().data_ptr(), parts,
+        lib.sah_attn_merge_parts(acc_c.data_ptr(), lse_c.data_ptr(), parts,
                                  batch, heads, seq_len_queries, D, _native.ptr(sink_t),
                                  _native.dtype_code(dtype), out.data_ptr(), _native.stream_of(dev)),
         "sah_attn_merge_parts")

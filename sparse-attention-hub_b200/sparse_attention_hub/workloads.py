@@ -195,6 +195,35 @@ def magicpig(seed: int = 0, dtype: str = "bf16", B: int = 1, Hq: int = 32, Hkv: 
          ("magicpig", {"lsh_l": lsh_l, "lsh_k": lsh_k, "center": True, "projection": proj})])
 
 
+def clustered_kv_range(seed: int, B: int, Hkv: int, begin: int, end: int, D: int, device,
+                       dtype: str = "bf16", n_clusters: int = 64, sigma: float = 0.3,
+                       chunk: int = 32768):
+    """Keys and values [B, Hkv, end - begin, D] of a long clustered sequence, generated on
+    `device` in chunks of `chunk` keys, each chunk from its own seed: any key range gives the
+    same values whichever way the sequence is cut into ranges (sequence-sharded runs at
+    different GPU counts see one workload).  Cluster centres come from `seed` alone."""
+    import torch
+
+    tdt = torch_dtype(dtype)
+    g = torch.Generator(device=device)
+    g.manual_seed(seed * 1000003 + 17)
+    centres_k = torch.randn((B, Hkv, n_clusters, D), generator=g, device=device)
+    centres_v = torch.randn((B, Hkv, n_clusters, D), generator=g, device=device)
+    k = torch.empty((B, Hkv, end - begin, D), dtype=tdt, device=device)
+    v = torch.empty((B, Hkv, end - begin, D), dtype=tdt, device=device)
+    bi = torch.arange(B, device=device)[:, None, None]
+    hi = torch.arange(Hkv, device=device)[None, :, None]
+    for c in range(begin // chunk, (end + chunk - 1) // chunk):
+        g.manual_seed(seed * 1000003 + 1000 + c)
+        assign = torch.randint(0, n_clusters, (B, Hkv, chunk), generator=g, device=device)
+        kc = centres_k[bi, hi, assign] + sigma * torch.randn((B, Hkv, chunk, D), generator=g, device=device)
+        vc = centres_v[bi, hi, assign] + sigma * torch.randn((B, Hkv, chunk, D), generator=g, device=device)
+        lo, hi_ = max(begin, c * chunk), min(end, (c + 1) * chunk)
+        k[:, :, lo - begin:hi_ - begin] = kc[:, :, lo - c * chunk:hi_ - c * chunk].to(tdt)
+        v[:, :, lo - begin:hi_ - begin] = vc[:, :, lo - c * chunk:hi_ - c * chunk].to(tdt)
+    return k, v
+
+
 def pq_init_indices(seed: int, groups: int, n_keys: int, n_cent: int) -> np.ndarray:
     """Seeded k-means initialisation: per group the first `n_cent` entries of a permutation."""
     rng = _rng(seed, 60)

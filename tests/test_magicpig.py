@@ -183,3 +183,45 @@ def test_gpu_merge_of_two_weighted_masks():
             merged = na.merge_mask(nb, inplace=False)
             want = torch.clamp(x + y, 0.0, 1.0)
             assert torch.equal(merged.get_dense_mask(), want)
+
+
+# ------------------------------------------------------------------ CPU: arithmetic shortcuts of the kernels
+def _rn(x, bits):
+    """Round a positive Fraction to `bits` significant bits, ties to even (no range limits)."""
+    from fractions import Fraction
+    import math
+
+    if x == 0:
+        return Fraction(0)
+    e = math.floor(math.log2(x))
+    while Fraction(2) ** e > x:
+        e -= 1
+    while Fraction(2) ** (e + 1) <= x:
+        e += 1
+    scale = Fraction(2) ** (e - bits + 1)
+    n = x / scale
+    lo = n.numerator // n.denominator
+    rem = n - lo
+    if rem > Fraction(1, 2) or (rem == Fraction(1, 2) and lo % 2 == 1):
+        lo += 1
+    return lo * scale
+
+
+def test_reciprocal_division_of_bf16_values_is_exact():
+    """The probability kernel divides a bf16 value by a bf16 value as q = RN(x*y), r = x - q*d,
+    RN(q + r*y) with y = RN(1/d) in float32, then rounds to bf16.  For every pair of bf16
+    significands this equals the IEEE float32 quotient rounded to bf16 (signs and exponents
+    factor out of every step)."""
+    from fractions import Fraction
+
+    for d in range(128, 256):
+        y = _rn(Fraction(1, d), 24)
+        for x in range(128, 256):
+            q = _rn(x * y, 24)
+            r = x - q * d
+            assert abs(r) == _rn(abs(r), 24)  # the fma residual is exact
+            q2 = q + r * y
+            assert q2 > 0
+            got = _rn(_rn(q2, 24), 8)
+            want = _rn(_rn(Fraction(x, d), 24), 8)
+            assert got == want, (x, d)
