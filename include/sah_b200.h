@@ -201,6 +201,17 @@ int sah_topk_select(const void* scores, int dtype, int64_t rows, int64_t S, int6
                     int64_t col_begin, int64_t col_end, const uint32_t* prev_bits,
                     int64_t k, uint32_t* out_bits, void* stream);
 
+/* The same selection with every row spread over many CTAs (sah_topk_select gives
+ * a row to one CTA, which leaves most SMs idle when there are few, long rows).
+ * Needs a 16-byte aligned device workspace of sah_topk_select_ws_bytes(rows, W)
+ * bytes (SAH_ERR_WORKSPACE when smaller); rows <= 65535.  out_bits may alias
+ * prev_bits.  Same result as sah_topk_select, bit for bit. */
+int64_t sah_topk_select_ws_bytes(int64_t rows, int64_t W);
+int sah_topk_select_ws(const void* scores, int dtype, int64_t rows, int64_t S, int64_t W,
+                       int64_t col_begin, int64_t col_end, const uint32_t* prev_bits,
+                       int64_t k, uint32_t* out_bits, void* workspace,
+                       int64_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------------ *
  * Adaptive sampling  (maskers/sampling/implementations/adaptive_sampling.py)
  * ------------------------------------------------------------------------ */
@@ -372,11 +383,15 @@ int sah_pq_update(const void* x, int dtype, int64_t xs_b, int64_t xs_h, int64_t 
  * ascending sub-vector order and rounded once (_compute_pq_scores,
  * pq_top_k.py:406-490).  centroids here are in `dtype`:
  * [B][Hkv][n_sub][n_cent][sub_d].  Columns outside the clustered region are not
- * written.  scores is [rows][S] in `dtype`. */
+ * written.  scores is [rows][S] in `dtype`.  The tables are built once per call in
+ * `workspace` (16-byte aligned device memory of sah_pq_scores_ws_bytes(...) bytes;
+ * SAH_ERR_WORKSPACE when smaller) and streamed from shared memory. */
+int64_t sah_pq_scores_ws_bytes(int B, int Hq, int Hkv, int Sq, int n_sub, int n_cent);
 int sah_pq_scores(const void* q, int dtype, int64_t qs_b, int64_t qs_h, int64_t qs_q,
                   const void* centroids, const uint8_t* codes, int64_t cap, int B, int Hq, int Hkv,
                   int Sq, int64_t n_keys, int64_t init_offset, int64_t S, int n_sub, int sub_d,
-                  int n_cent, void* scores, void* stream);
+                  int n_cent, void* scores, void* workspace, int64_t workspace_bytes,
+                  void* stream);
 
 /* ------------------------------------------------------------------------ *
  * Masked attention  (utils/mask_attention_utils.py:187-240, :406-491)

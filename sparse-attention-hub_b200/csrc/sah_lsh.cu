@@ -65,11 +65,32 @@ extern "C" int sah_lsh_key_sums(const void* keys, int dtype, int64_t ks_b, int64
 // ---------------------------------------------------------------------------------------
 // key statistics: norm of the centred key, running maximum
 // ---------------------------------------------------------------------------------------
+// lane `lane` loads its `per` consecutive channels of a row (one vector load when the row
+// address allows it: rows of the usual 64 / 128 / 256 channels always do)
 template <typename T>
 __device__ __forceinline__ void lsh_load_lane(const T* row, int per, int lane, float* x) {
+  const T* p = row + lane * per;
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  if (sizeof(T) == 2 && per == 4 && (a & 7) == 0) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    x[0] = __uint_as_float(v.x << 16);
+    x[1] = __uint_as_float(v.x & 0xffff0000u);
+    x[2] = __uint_as_float(v.y << 16);
+    x[3] = __uint_as_float(v.y & 0xffff0000u);
+  } else if (sizeof(T) == 2 && per == 2 && (a & 3) == 0) {
+    const uint32_t v = *reinterpret_cast<const uint32_t*>(p);
+    x[0] = __uint_as_float(v << 16);
+    x[1] = __uint_as_float(v & 0xffff0000u);
+  } else if (sizeof(T) == 2 && per == 8 && (a & 15) == 0) {
+    sah_unpack8(*reinterpret_cast<const uint4*>(p), x);
+  } else if (sizeof(T) == 4 && per == 4 && (a & 15) == 0) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+  } else {
 #pragma unroll
-  for (int t = 0; t < LSH_MAX_PER_LANE; ++t)
-    if (t < per) x[t] = sah_to_float<T>(row[lane * per + t]);
+    for (int t = 0; t < LSH_MAX_PER_LANE; ++t)
+      if (t < per) x[t] = sah_to_float<T>(p[t]);
+  }
 }
 
 template <typename T>
@@ -566,16 +587,32 @@ lsh_prob_kernel(const T* __restrict__ k, int64_t ks_b, int64_t ks_h, int64_t ks_
   const T* kbase = k + b * ks_b + hkv * ks_h;
   for (int64_t w = (int64_t)blockIdx.y * nwarp + warp; w < W; w += (int64_t)gridDim.y * nwarp) {
     // union of the rows' words (lane r holds row r, r + 32, ...)
-    uint32_t uni = 0u;
-    for (int r = lane; r < R; r += 32) uni |= bits[(row0 + r) * W + w];
+    uint32_t uni = 0u, myword = 0u;
+    for (int r = lane; r < R; r += 32) {
+      const uint32_t wd = bits[(row0 + r) * W + w];
+      if (r < 32) myword = wd;
+      uni |= wd;
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) uni |= __shfl_xor_sync(0xffffffffu, uni, o);
+    if (!uni) continue;
+    // the next key's row is loaded while the current one is worked on
+    int nbit = __ffs(uni) - 1;
+    float xn[LSH_MAX_PER_LANE];
+    lsh_load_lane<T>(kbase + (w * 32 + nbit) * ks_s, per, lane, xn);
+    float nkn = norms[kvh * cap + w * 32 + nbit];
     while (uni) {
-      const int bit = __ffs(uni) - 1;
-      uni &= uni - 1;
-      const int64_t s = w * 32 + bit;
+      const int bit = nbit;
+      const float nk = nkn;
       float x[LSH_MAX_PER_LANE];
-      lsh_load_lane<T>(kbase + s * ks_s, per, lane, x);
+#pragma unroll
+      for (int t = 0; t < LSH_MAX_PER_LANE; ++t) x[t] = xn[t];
+      uni &= uni - 1;
+      if (uni) {
+        nbit = __ffs(uni) - 1;
+        lsh_load_lane<T>(kbase + (w * 32 + nbit) * ks_s, per, lane, xn);
+        nkn = norms[kvh * cap + w * 32 + nbit];
+      }
       float acc = 0.f;
 #pragma unroll
       for (int t = 0; t < LSH_MAX_PER_LANE; ++t)
@@ -584,7 +621,7 @@ lsh_prob_kernel(const T* __restrict__ k, int64_t ks_b, int64_t ks_h, int64_t ks_
           x[t] = LshDivM<T>::div(c, M, tab);
           acc = __fadd_rn(acc, __fmul_rn(x[t], x[t]));
         }
-      const float aug = lsh_augment<T>(norms[kvh * cap + s], M);
+      const float aug = lsh_augment<T>(nk, M);
       // |transformed key|, then its unit vector
       const float n2 = __fadd_rn(lsh_warp_sum(acc), __fmul_rn(aug, aug));
       const float den = sah_round_to<T>(__fadd_rn(sah_round_to<T>(sqrtf(n2)), 1e-8f));
@@ -593,7 +630,8 @@ lsh_prob_kernel(const T* __restrict__ k, int64_t ks_b, int64_t ks_h, int64_t ks_
       for (int t = 0; t < LSH_MAX_PER_LANE; ++t)
         if (t < per) x[t] = lsh_div_den<T>(x[t], den, rcp);
       for (int r = 0; r < R; ++r) {
-        const uint32_t word = bits[(row0 + r) * W + w];  // warp-uniform, L1 resident
+        // warp-uniform: the first 32 rows' words sit in the lanes, the rest are re-read (L1)
+        const uint32_t word = r < 32 ? __shfl_sync(0xffffffffu, myword, r) : bits[(row0 + r) * W + w];
         if (!((word >> bit) & 1u)) continue;
         const float* qu = qsrc + r * D + lane * per;
         acc = 0.f;

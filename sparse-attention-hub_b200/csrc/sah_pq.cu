@@ -221,79 +221,147 @@ extern "C" int sah_pq_update(const void* x, int dtype, int64_t xs_b, int64_t xs_
 // with an fp32 accumulator, pq_top_k.py:481-488).
 // ---------------------------------------------------------------------------
 #define PQ_ROWS 4
+#define PQ_KEYS_PER_THREAD 8
 
+// lut[(bk * rblocks + rblk)][sub][c][rr] = q_sub(row rblk*4 + rr) . centroid(sub, c), fma over
+// ascending dims, rounded to the dtype; rows past R hold 0.  One thread per (sub, c).
 template <typename T>
-__global__ void __launch_bounds__(PQ_TILE)
-pq_scores_kernel(const T* __restrict__ q, int64_t qs_b, int64_t qs_h, int64_t qs_q,
-                 const T* __restrict__ centroids, const uint8_t* __restrict__ codes, int64_t cap,
-                 int Hq, int Hkv, int Sq, int64_t n_keys, int64_t init_offset, int64_t S, int n_sub,
-                 int sub_d, int n_cent, T* __restrict__ scores) {
-  extern __shared__ float pq_lut_sm[];  // [PQ_ROWS][n_sub][n_cent]
+__global__ void __launch_bounds__(256)
+pq_lut_kernel(const T* __restrict__ q, int64_t qs_b, int64_t qs_h, int64_t qs_q,
+              const T* __restrict__ centroids, int Hq, int Hkv, int Sq, int n_sub, int sub_d,
+              int n_cent, float* __restrict__ lut) {
   const int G = Hq / Hkv;
-  const int R = G * Sq;  // rows sharing this KV head: r = g * Sq + qi
+  const int R = G * Sq;
   const int64_t bk = blockIdx.z;
   const int kvh = (int)(bk % Hkv);
   const int64_t b = bk / Hkv;
-  const int r_base = blockIdx.y * PQ_ROWS;
-  const int lut_row = n_sub * n_cent;
-  for (int idx = threadIdx.x; idx < PQ_ROWS * lut_row; idx += PQ_TILE) {
-    const int rr = idx / lut_row, rem = idx - rr * lut_row;
-    const int sub = rem / n_cent, c = rem - sub * n_cent;
-    const int r = r_base + rr;
+  const int rblk = blockIdx.y, rblocks = gridDim.y;
+  const int idx = blockIdx.x * 256 + threadIdx.x;  // sub * n_cent + c
+  if (idx >= n_sub * n_cent) return;
+  const int sub = idx / n_cent;
+  const T* cp = centroids + (bk * n_sub * (int64_t)n_cent + idx) * sub_d;
+  float out[PQ_ROWS];
+#pragma unroll
+  for (int rr = 0; rr < PQ_ROWS; ++rr) {
+    const int r = rblk * PQ_ROWS + rr;
     float v = 0.f;
     if (r < R) {
       const int g = r / Sq, qi = r - g * Sq;
       const T* qp = q + b * qs_b + (int64_t)(kvh * G + g) * qs_h + qi * qs_q + sub * sub_d;
-      const T* cp = centroids + ((bk * n_sub + sub) * n_cent + c) * sub_d;
       float acc = 0.f;
       for (int d = 0; d < sub_d; ++d) acc = fmaf(sah_to_float<T>(qp[d]), sah_to_float<T>(cp[d]), acc);
       v = sah_round_to<T>(acc);
     }
-    pq_lut_sm[idx] = v;
+    out[rr] = v;
   }
+  *reinterpret_cast<float4*>(lut + (((bk * rblocks + rblk) * (int64_t)n_sub * n_cent) + idx) * PQ_ROWS) =
+      make_float4(out[0], out[1], out[2], out[3]);
+}
+
+// One CTA: the table of one (KV group, block of 4 rows) in shared memory, 256 x
+// PQ_KEYS_PER_THREAD keys; a key's n_sub codes index float4 entries (one per row).
+template <typename T>
+__global__ void __launch_bounds__(PQ_TILE)
+pq_scores_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes, int64_t cap, int Hq,
+                 int Hkv, int Sq, int64_t n_keys, int64_t init_offset, int64_t S, int n_sub, int n_cent,
+                 T* __restrict__ scores) {
+  extern __shared__ __align__(16) float pq_lut_sm[];  // [n_sub][n_cent][PQ_ROWS]
+  const int G = Hq / Hkv;
+  const int R = G * Sq;
+  const int64_t bk = blockIdx.z;
+  const int kvh = (int)(bk % Hkv);
+  const int64_t b = bk / Hkv;
+  const int rblk = blockIdx.y, rblocks = gridDim.y;
+  const int entries = n_sub * n_cent;
+  const float4* src = reinterpret_cast<const float4*>(lut) + (bk * rblocks + rblk) * (int64_t)entries;
+  float4* dst = reinterpret_cast<float4*>(pq_lut_sm);
+  for (int i = threadIdx.x; i < entries; i += PQ_TILE) dst[i] = src[i];
   __syncthreads();
-  const int64_t j = (int64_t)blockIdx.x * PQ_TILE + threadIdx.x;
-  if (j >= n_keys) return;
-  const uint8_t* cj = codes + (bk * cap + j) * n_sub;
+  const bool vec = (n_sub == 16) && ((reinterpret_cast<uintptr_t>(codes) & 15) == 0);
+  int64_t rowoff[PQ_ROWS];
+#pragma unroll
   for (int rr = 0; rr < PQ_ROWS; ++rr) {
-    const int r = r_base + rr;
-    if (r >= R) break;
-    float s = 0.f;
-    for (int sub = 0; sub < n_sub; ++sub)
-      s = __fadd_rn(s, pq_lut_sm[rr * lut_row + sub * n_cent + cj[sub]]);
+    const int r = rblk * PQ_ROWS + rr;
     const int g = r / Sq, qi = r - g * Sq;
-    const int64_t row = (b * Hq + kvh * G + g) * Sq + qi;
-    scores[row * S + init_offset + j] = sah_from_float<T>(s);
+    rowoff[rr] = r < R ? ((b * Hq + kvh * G + g) * Sq + qi) * S + init_offset : -1;
   }
+  const int64_t j0 = (int64_t)blockIdx.x * PQ_TILE * PQ_KEYS_PER_THREAD;
+  for (int i = 0; i < PQ_KEYS_PER_THREAD; ++i) {
+    const int64_t j = j0 + (int64_t)i * PQ_TILE + threadIdx.x;
+    if (j >= n_keys) break;
+    const uint8_t* cj = codes + (bk * cap + j) * n_sub;
+    float s[PQ_ROWS] = {0.f, 0.f, 0.f, 0.f};
+    if (vec) {
+      const uint4 cv = *reinterpret_cast<const uint4*>(cj);
+      const uint32_t w[4] = {cv.x, cv.y, cv.z, cv.w};
+#pragma unroll
+      for (int sub = 0; sub < 16; ++sub) {
+        const uint32_t c = (w[sub >> 2] >> ((sub & 3) * 8)) & 255u;
+        const float4 e = dst[sub * n_cent + c];
+        s[0] = __fadd_rn(s[0], e.x); s[1] = __fadd_rn(s[1], e.y);
+        s[2] = __fadd_rn(s[2], e.z); s[3] = __fadd_rn(s[3], e.w);
+      }
+    } else {
+      for (int sub = 0; sub < n_sub; ++sub) {
+        const float4 e = dst[sub * n_cent + cj[sub]];
+        s[0] = __fadd_rn(s[0], e.x); s[1] = __fadd_rn(s[1], e.y);
+        s[2] = __fadd_rn(s[2], e.z); s[3] = __fadd_rn(s[3], e.w);
+      }
+    }
+#pragma unroll
+    for (int rr = 0; rr < PQ_ROWS; ++rr)
+      if (rowoff[rr] >= 0) scores[rowoff[rr] + j] = sah_from_float<T>(s[rr]);
+  }
+}
+
+extern "C" int64_t sah_pq_scores_ws_bytes(int B, int Hq, int Hkv, int Sq, int n_sub, int n_cent) {
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Sq <= 0 || n_sub <= 0 || n_cent <= 0) return 0;
+  const int64_t R = (int64_t)(Hq / Hkv) * Sq;
+  const int64_t rblocks = (R + PQ_ROWS - 1) / PQ_ROWS;
+  return (int64_t)B * Hkv * rblocks * n_sub * n_cent * PQ_ROWS * (int64_t)sizeof(float);
 }
 
 extern "C" int sah_pq_scores(const void* q, int dtype, int64_t qs_b, int64_t qs_h, int64_t qs_q,
                              const void* centroids, const uint8_t* codes, int64_t cap, int B, int Hq,
                              int Hkv, int Sq, int64_t n_keys, int64_t init_offset, int64_t S,
-                             int n_sub, int sub_d, int n_cent, void* scores, void* stream) {
-  SAH_REQUIRE(q && centroids && codes && scores, "pq_scores: null pointer");
+                             int n_sub, int sub_d, int n_cent, void* scores, void* workspace,
+                             int64_t workspace_bytes, void* stream) {
+  SAH_REQUIRE(q && centroids && codes && scores && workspace, "pq_scores: null pointer");
   SAH_REQUIRE(B > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Sq > 0, "pq_scores: bad heads");
   SAH_REQUIRE(n_keys >= 0 && init_offset >= 0 && init_offset + n_keys <= S && n_keys <= cap,
               "pq_scores: bad key range");
+  SAH_REQUIRE(n_cent <= 256, "pq_scores: codes are bytes, at most 256 centroids");
+  SAH_REQUIRE(((uintptr_t)workspace & 15) == 0, "pq_scores: workspace must be 16-byte aligned");
+  if (workspace_bytes < sah_pq_scores_ws_bytes(B, Hq, Hkv, Sq, n_sub, n_cent))
+    return sah_fail(SAH_ERR_WORKSPACE, "pq_scores: workspace of %lld bytes, need %lld",
+                    (long long)workspace_bytes,
+                    (long long)sah_pq_scores_ws_bytes(B, Hq, Hkv, Sq, n_sub, n_cent));
   if (n_keys == 0) return SAH_OK;
   const int R = (Hq / Hkv) * Sq;
+  const int rblocks = (R + PQ_ROWS - 1) / PQ_ROWS;
   const size_t smem = (size_t)PQ_ROWS * n_sub * n_cent * sizeof(float);
   if (smem > 200 * 1024)
     return sah_fail(SAH_ERR_UNSUPPORTED, "pq_scores: %d x %d lookup table does not fit", n_sub, n_cent);
-  dim3 grid((unsigned)sah_ceil_div(n_keys, PQ_TILE), (unsigned)sah_ceil_div(R, PQ_ROWS),
+  SAH_REQUIRE(rblocks <= 65535 && (int64_t)B * Hkv <= 65535, "pq_scores: too many rows per launch");
+  cudaStream_t st = (cudaStream_t)stream;
+  float* lut = reinterpret_cast<float*>(workspace);
+  sah_prof_begin(SAH_PROF_PQ_SCORES, st);
+  dim3 lgrid((unsigned)sah_ceil_div((int64_t)n_sub * n_cent, 256), (unsigned)rblocks, (unsigned)((int64_t)B * Hkv));
+  dim3 grid((unsigned)sah_ceil_div(n_keys, (int64_t)PQ_TILE * PQ_KEYS_PER_THREAD), (unsigned)rblocks,
             (unsigned)((int64_t)B * Hkv));
-  sah_prof_begin(SAH_PROF_PQ_SCORES, (cudaStream_t)stream);
   SAH_DISPATCH_DTYPE(dtype, T, {
+    pq_lut_kernel<T><<<lgrid, 256, 0, st>>>((const T*)q, qs_b, qs_h, qs_q, (const T*)centroids, Hq, Hkv,
+                                            Sq, n_sub, sub_d, n_cent, lut);
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(pq_scores_kernel<T>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "pq_scores attr: %s", cudaGetErrorString(e));
     }
-    pq_scores_kernel<T><<<grid, PQ_TILE, smem, (cudaStream_t)stream>>>(
-        (const T*)q, qs_b, qs_h, qs_q, (const T*)centroids, codes, cap, Hq, Hkv, Sq, n_keys,
-        init_offset, S, n_sub, sub_d, n_cent, (T*)scores);
+    pq_scores_kernel<T><<<grid, PQ_TILE, smem, st>>>(lut, codes, cap, Hq, Hkv, Sq, n_keys, init_offset, S,
+                                                     n_sub, n_cent, (T*)scores);
   });
+  sah_count_launch();
   SAH_LAUNCH_CHECK("pq_scores");
-  sah_prof_end(SAH_PROF_PQ_SCORES, (cudaStream_t)stream);
+  sah_prof_end(SAH_PROF_PQ_SCORES, st);
   return SAH_OK;
 }

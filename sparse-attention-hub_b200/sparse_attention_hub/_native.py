@@ -75,6 +75,8 @@ _SIGNATURES = {
     "sah_qk_scores": [_P, _P, _I, _L, _L, _L, _L, _L, _L, _I, _I, _I, _I, _L, _I, _P, _L, _L,
                       _L, _P, _P],
     "sah_topk_select": [_P, _I, _L, _L, _L, _L, _L, _P, _L, _P, _P],
+    "sah_topk_select_ws_bytes": [_L, _L],  # returns int64
+    "sah_topk_select_ws": [_P, _I, _L, _L, _L, _L, _L, _P, _L, _P, _P, _L, _P],
     "sah_attn_query_sizes": [_I, _I, _I, _I, _L, _I, _I, _I, POINTER(AttnSizes)],
     "sah_attn_plan": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _L, _L, POINTER(AttnSizes), _P, _P,
                       _P, _P, _P],
@@ -100,8 +102,9 @@ _SIGNATURES = {
     "sah_pq_assign": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _L, _I, _I, _I, _P, _P, _L, _I, _P],
     "sah_pq_accumulate": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _I, _I, _I, _P, _L, _P, _P, _P],
     "sah_pq_update": [_P, _I, _L, _L, _L, _I, _I, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P],
+    "sah_pq_scores_ws_bytes": [_I, _I, _I, _I, _I, _I],  # returns int64
     "sah_pq_scores": [_P, _I, _L, _L, _L, _P, _P, _L, _I, _I, _I, _I, _L, _L, _L, _I, _I, _I, _P,
-                      _P],
+                      _P, _L, _P],
     "sah_masked_attention_static": [_P, _P, _P, _P, _I, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _I,
                                     _I, _I, _L, _L, _I, c_float, _P, _L, _L, _L, _P, _I, _P, _P],
     "sah_profile_enable": [_I],
@@ -135,6 +138,8 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = c_int
+    lib.sah_topk_select_ws_bytes.restype = c_int64
+    lib.sah_pq_scores_ws_bytes.restype = c_int64
     lib.sah_version.restype = c_char_p
     lib.sah_last_error.restype = c_char_p
     lib.sah_launch_count.restype = ctypes.c_longlong

@@ -72,10 +72,20 @@ def topk_select(scores: torch.Tensor, previous_mask: Mask, k: int, col_begin: in
     prev = previous_mask.native_bits()
     dst = out if out is not None else NativeBits(torch.empty_like(prev.bits), rows, S)
     sc = scores.contiguous()
+    st = _native.stream_of(sc.device)
+    end = S if col_end is None else col_end
+    if rows <= 65535:
+        # rows are spread over many CTAs; the histograms live in a scratch buffer
+        nbytes = int(lib.sah_topk_select_ws_bytes(rows, prev.words))
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=sc.device)
+        _native.check(
+            lib.sah_topk_select_ws(sc.data_ptr(), _native.dtype_code(sc.dtype), rows, S, prev.words,
+                                   col_begin, end, prev.bits.data_ptr(), k, dst.bits.data_ptr(),
+                                   ws.data_ptr(), nbytes, st), "sah_topk_select_ws")
+        return dst
     _native.check(
         lib.sah_topk_select(sc.data_ptr(), _native.dtype_code(sc.dtype), rows, S, prev.words,
-                            col_begin, S if col_end is None else col_end, prev.bits.data_ptr(),
-                            k, dst.bits.data_ptr(), _native.stream_of(sc.device)),
+                            col_begin, end, prev.bits.data_ptr(), k, dst.bits.data_ptr(), st),
         "sah_topk_select")
     return dst
 

@@ -251,12 +251,14 @@ class PQCache(TopKMasker):
         q = queries if queries.stride(-1) == 1 else queries.contiguous()
         cent = centroids[..., :sub_d].to(q.dtype).contiguous()
         scores = torch.empty((B, Hq, Sq, S), dtype=q.dtype, device=q.device)
+        nbytes = int(lib.sah_pq_scores_ws_bytes(B, Hq, Hkv, Sq, n_sub, n_cent))
+        tables = torch.empty(nbytes, dtype=torch.uint8, device=q.device)  # the query-centroid tables
         _native.check(
             lib.sah_pq_scores(q.data_ptr(), _native.dtype_code(q.dtype), q.stride(0), q.stride(1),
                               q.stride(2), cent.data_ptr(), codebook.codes.data_ptr(),
                               codebook.codes.shape[2], B, Hq, Hkv, Sq, codebook.length,
                               self.init_offset, S, n_sub, sub_d, n_cent, scores.data_ptr(),
-                              _native.stream_of(q.device)), "sah_pq_scores")
+                              tables.data_ptr(), nbytes, _native.stream_of(q.device)), "sah_pq_scores")
         return scores
 
     @classmethod
