@@ -1,0 +1,58 @@
+"""The C ABI without a GPU: the shared library loads, exports every function that
+include/sah_b200.h declares, the ctypes table covers the same set, and entry points refuse
+bad arguments with a status and a message instead of launching anything."""
+
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+from sparse_attention_hub import _native
+
+HEADER = Path(__file__).resolve().parent.parent / "include" / "sah_b200.h"
+
+
+def _declared():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(sah_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_function():
+    lib = _native.load()
+    names = _declared()
+    assert len(names) > 40
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, missing
+
+
+def test_ctypes_table_matches_the_header():
+    assert sorted(_native.EXPORTED_SYMBOLS) == _declared()
+
+
+def test_version_and_launch_counter():
+    lib = _native.load()
+    assert lib.sah_version().decode().startswith("sah_b200")
+    assert _native.launch_count() >= 0
+
+
+def test_bad_arguments_return_a_status_and_a_message():
+    lib = _native.load()
+    # null pointers: nothing is launched, so this is safe without a device
+    assert lib.sah_mask_fill_band(None, 1, 1, 32, 1, 0, 0, 1, 0, 1, None) == 1
+    assert b"null" in lib.sah_last_error()
+    assert lib.sah_hash_topk(None, 0, None, 32, None, 1, 0, 0, 0, 1, 1, 1, 32, 1, None, 1, None, None) == 1
+    assert lib.sah_lsh_match(None, 32, None, 1, 4, 1, 4, 5, 4, 32, 1, None, None) == 1
+    with pytest.raises(_native.NativeLibraryError):
+        _native.check(1, "sah_lsh_match")
+    with pytest.raises(NotImplementedError):
+        _native.check(2, "anything")
+
+
+def test_workspace_size_queries():
+    lib = _native.load()
+    assert lib.sah_topk_select_ws_bytes(32, 4096) > 32 * 4096 // 256 * 1024
+    assert lib.sah_pq_scores_ws_bytes(1, 32, 8, 1, 16, 256) == 8 * 16 * 256 * 4 * 4
+    sizes = _native.AttnSizes()
+    assert lib.sah_attn_query_sizes(8, 32, 8, 1, 32768, 128, 0, 148, ctypes.byref(sizes)) == 0
+    assert sizes.groups == 64 and sizes.ucols_bytes > 0
