@@ -335,9 +335,20 @@ int sah_lsh_match(const void* planes, int64_t cap, const void* qcodes, int B, in
 /* data[ptr[row] + i] = collision probability 1 - (1 - (1 - theta/pi)^K)^L of the
  * i-th set bit of the row (:374-403), theta the angle between the transformed
  * key and query, every operation rounded to the dtype.  bf16 needs `table`,
- * uint16 [65536]: bits of the clamped cosine -> bits of the probability. */
+ * uint16 [65536]: bits of the clamped cosine -> bits of the probability.
+ * `dens` (optional, bf16 only): the cached norms of sah_lsh_key_den, which
+ * shorten the per-key work; they must be current for the keys and *max_norm_bits. */
+int sah_lsh_key_den(const void* keys, int dtype, int64_t ks_b, int64_t ks_h, int64_t ks_s, int B,
+                    int Hkv, int64_t s_new0, int64_t s1, int D, const void* mean,
+                    const float* norms, int64_t cap, const unsigned int* max_norm_bits,
+                    unsigned int* dens_max_bits, float* dens, int sm_count, void* stream);
+/* ^ dens[(b*Hkv + h)*cap + s] = |transformed key s| + 1e-8 (rounded per operation) for
+ * s in [s_new0, s1), or for every s in [0, s1) when *max_norm_bits differs from
+ * *dens_max_bits (the maximum the cached values were made with); then
+ * *dens_max_bits = *max_norm_bits.  Call after sah_lsh_key_stats whenever keys arrived. */
 int sah_lsh_prob(const void* keys, int dtype, int64_t ks_b, int64_t ks_h, int64_t ks_s, int B,
-                 int Hq, int Sq, int G, int D, const void* mean, const float* norms, int64_t cap,
+                 int Hq, int Sq, int G, int D, const void* mean, const float* norms,
+                 const float* dens, int64_t cap,
                  const unsigned int* max_norm_bits, const float* qunit, const uint32_t* bits,
                  const int32_t* wpre, const int64_t* ptr, int64_t W, int K, int L,
                  const uint16_t* table, void* data, int sm_count, void* stream);

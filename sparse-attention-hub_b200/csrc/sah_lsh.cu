@@ -649,12 +649,330 @@ lsh_prob_kernel(const T* __restrict__ k, int64_t ks_b, int64_t ks_h, int64_t ks_
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// Cached norm of the transformed key.  |[k_c / M, sqrt(M^2 - |k_c|^2) / M]| + 1e-8 depends on
+// the key, the key mean and the maximum norm M only, not on the query, so it is computed when
+// keys arrive (and again for every key if M moved) instead of at every decode step.
+// dens_max_bits holds the M the cached values were computed with.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+lsh_key_den_kernel(const T* __restrict__ k, int64_t ks_b, int64_t ks_h, int64_t ks_s, int Hkv,
+                   int64_t s_new0, int64_t s1, int D, const T* __restrict__ mean,
+                   const float* __restrict__ norms, int64_t cap,
+                   const unsigned int* __restrict__ max_bits,
+                   const unsigned int* __restrict__ dens_max_bits, float* __restrict__ dens) {
+  __shared__ float tab[128];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const int64_t bh = blockIdx.y;
+  const int64_t b = bh / Hkv, h = bh % Hkv;
+  const int per = D / 32;
+  const unsigned int mb = *max_bits;
+  const float M = __uint_as_float(mb);
+  const int64_t begin = (mb == *dens_max_bits) ? s_new0 : 0;  // M moved: every key again
+  if (begin >= s1) return;
+  LshDivM<T>::build(tab, M);
+  __syncthreads();
+  float m[LSH_MAX_PER_LANE];
+  if (mean) lsh_load_lane<T>(mean + bh * D, per, lane, m);
+  for (int64_t s = begin + (int64_t)blockIdx.x * nwarp + warp; s < s1; s += (int64_t)gridDim.x * nwarp) {
+    float x[LSH_MAX_PER_LANE];
+    lsh_load_lane<T>(k + b * ks_b + h * ks_h + s * ks_s, per, lane, x);
+    float acc = 0.f;
+#pragma unroll
+    for (int t = 0; t < LSH_MAX_PER_LANE; ++t)
+      if (t < per) {
+        const float c = mean ? sah_round_to<T>(__fsub_rn(x[t], m[t])) : x[t];
+        const float ks = LshDivM<T>::div(c, M, tab);
+        acc = __fadd_rn(acc, __fmul_rn(ks, ks));
+      }
+    const float aug = lsh_augment<T>(norms[bh * cap + s], M);
+    const float n2 = __fadd_rn(lsh_warp_sum(acc), __fmul_rn(aug, aug));
+    if (lane == 0) dens[bh * cap + s] = sah_round_to<T>(__fadd_rn(sah_round_to<T>(sqrtf(n2)), 1e-8f));
+  }
+}
+
+__global__ void lsh_den_commit_kernel(const unsigned int* max_bits, unsigned int* dens_max_bits) {
+  *dens_max_bits = *max_bits;
+}
+
+extern "C" int sah_lsh_key_den(const void* keys, int dtype, int64_t ks_b, int64_t ks_h, int64_t ks_s,
+                               int B, int Hkv, int64_t s_new0, int64_t s1, int D, const void* mean,
+                               const float* norms, int64_t cap, const unsigned int* max_norm_bits,
+                               unsigned int* dens_max_bits, float* dens, int sm_count, void* stream) {
+  SAH_REQUIRE(keys && norms && max_norm_bits && dens_max_bits && dens, "lsh_key_den: null pointer");
+  SAH_REQUIRE(D % 32 == 0 && D <= 32 * LSH_MAX_PER_LANE, "lsh_key_den: head_dim must be a multiple of 32, <= 256");
+  SAH_REQUIRE(s_new0 >= 0 && s_new0 <= s1 && s1 <= cap, "lsh_key_den: bad key range");
+  if (s1 == 0) return SAH_OK;
+  if (sm_count <= 0) sm_count = 148;
+  int64_t gx = (s1 + 7) / 8;
+  const int64_t cap_x = ((int64_t)sm_count * 8 + (int64_t)B * Hkv - 1) / ((int64_t)B * Hkv);
+  if (gx > cap_x) gx = cap_x;
+  dim3 grid((unsigned)gx, (unsigned)(B * Hkv));
+  cudaStream_t st = (cudaStream_t)stream;
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    lsh_key_den_kernel<T><<<grid, 256, 0, st>>>(reinterpret_cast<const T*>(keys), ks_b, ks_h, ks_s, Hkv,
+                                                s_new0, s1, D, reinterpret_cast<const T*>(mean), norms,
+                                                cap, max_norm_bits, dens_max_bits, dens);
+  });
+  SAH_LAUNCH_CHECK("lsh_key_den");
+  lsh_den_commit_kernel<<<1, 1, 0, st>>>(max_norm_bits, dens_max_bits);
+  SAH_LAUNCH_CHECK("lsh_den_commit");
+  return SAH_OK;
+}
+
+// bf16 with cached norms: the two divisions collapse into one table.  A centred key channel c
+// (a bf16 value) times 1 / M rounded to bf16, times 1 / den rounded to bf16, equals
+// 2^exponent(c) * U[den][mantissa(c)] with U = bf16(bf16((1 + m/128) / M) / den), because a
+// power-of-two factor commutes with both roundings while everything stays in the normal
+// range.  den is the norm of an (almost) unit vector: the 32 bf16 values from 0.9375 up
+// cover it; other dens, and channels whose exponent could leave the normal range, take the
+// two IEEE divisions.
+#define LSH_DEN_BASE 0x3F70u
+#define LSH_DEN_TABLES 32
+
+__global__ void __launch_bounds__(256)
+lsh_prob_fast_kernel(const __nv_bfloat16* __restrict__ k, int64_t ks_b, int64_t ks_h, int64_t ks_s,
+                     int Hq, int Sq, int G, int D, const __nv_bfloat16* __restrict__ mean,
+                     const float* __restrict__ dens, int64_t cap,
+                     const unsigned int* __restrict__ max_bits, const float* __restrict__ qunit,
+                     const uint32_t* __restrict__ bits, const int32_t* __restrict__ wpre,
+                     const int64_t* __restrict__ ptr, int64_t W, const uint16_t* __restrict__ table,
+                     int q_in_smem, __nv_bfloat16* __restrict__ data) {
+  typedef __nv_bfloat16 T;
+  extern __shared__ __align__(16) unsigned char lsh_smem[];
+  float* U = reinterpret_cast<float*>(lsh_smem);  // [LSH_DEN_TABLES][128]
+  float* qs = U + LSH_DEN_TABLES * 128;           // [R][D] when q_in_smem
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const int Hkv = Hq / G;
+  const int64_t kvh = blockIdx.x;
+  const int64_t b = kvh / Hkv;
+  const int hkv = (int)(kvh % Hkv);
+  const int R = G * Sq;
+  const int per = D / 32;
+  const unsigned int mbits = *max_bits;
+  const float M = __uint_as_float(mbits);
+  const int64_t row0 = (b * Hq + (int64_t)hkv * G) * Sq;
+  for (int i = threadIdx.x; i < LSH_DEN_TABLES * 128; i += blockDim.x) {
+    const int di = i >> 7, m = i & 127;
+    const float t = sah_round_to<T>(__fdiv_rn(1.0f + (float)m * 0.0078125f, M));
+    const float d = __uint_as_float((LSH_DEN_BASE + (unsigned)di) << 16);
+    U[i] = sah_round_to<T>(__fdiv_rn(t, d));
+  }
+  if (q_in_smem)
+    for (int i = threadIdx.x; i < R * D; i += blockDim.x) qs[i] = qunit[row0 * D + i];
+  __syncthreads();
+  // exponent fields of c for which c / M / den surely stays normal (den is within [0.9375, 1.12])
+  const int shift = 127 - (int)((mbits >> 23) & 0xffu);
+  const int elo = max(1, 4 - shift), ehi = min(254, 250 - shift);
+  const float* qsrc = q_in_smem ? qs : qunit + row0 * D;
+  float m[LSH_MAX_PER_LANE];
+  if (mean) lsh_load_lane<T>(mean + kvh * D, per, lane, m);
+  const T* kbase = k + b * ks_b + hkv * ks_h;
+  for (int64_t w = (int64_t)blockIdx.y * nwarp + warp; w < W; w += (int64_t)gridDim.y * nwarp) {
+    uint32_t uni = 0u, myword = 0u;
+    for (int r = lane; r < R; r += 32) {
+      const uint32_t wd = bits[(row0 + r) * W + w];
+      if (r < 32) myword = wd;
+      uni |= wd;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) uni |= __shfl_xor_sync(0xffffffffu, uni, o);
+    if (!uni) continue;
+    int nbit = __ffs(uni) - 1;
+    float xn[LSH_MAX_PER_LANE];
+    lsh_load_lane<T>(kbase + (w * 32 + nbit) * ks_s, per, lane, xn);
+    float dn = dens[kvh * cap + w * 32 + nbit];
+    while (uni) {
+      const int bit = nbit;
+      const float den = dn;
+      float x[LSH_MAX_PER_LANE];
+#pragma unroll
+      for (int t = 0; t < LSH_MAX_PER_LANE; ++t) x[t] = xn[t];
+      uni &= uni - 1;
+      if (uni) {
+        nbit = __ffs(uni) - 1;
+        lsh_load_lane<T>(kbase + (w * 32 + nbit) * ks_s, per, lane, xn);
+        dn = dens[kvh * cap + w * 32 + nbit];
+      }
+      const unsigned int di = (__float_as_uint(den) >> 16) - LSH_DEN_BASE;
+      const float* Ud = U + (di < LSH_DEN_TABLES ? di : 0u) * 128;
+#pragma unroll
+      for (int t = 0; t < LSH_MAX_PER_LANE; ++t)
+        if (t < per) {
+          const float c = mean ? sah_round_to<T>(__fsub_rn(x[t], m[t])) : x[t];
+          const uint32_t u = __float_as_uint(c);
+          const int e = (int)((u >> 23) & 0xffu);
+          if (di < LSH_DEN_TABLES && e >= elo && e <= ehi) {
+            x[t] = __fmul_rn(__uint_as_float(u & 0xff800000u), Ud[(u >> 16) & 0x7fu]);
+          } else {
+            const float ks = sah_round_to<T>(__fdiv_rn(c, M));
+            x[t] = sah_round_to<T>(__fdiv_rn(ks, den));
+          }
+        }
+      for (int r = 0; r < R; ++r) {
+        const uint32_t word = r < 32 ? __shfl_sync(0xffffffffu, myword, r) : bits[(row0 + r) * W + w];
+        if (!((word >> bit) & 1u)) continue;
+        const float* qu = qsrc + r * D + lane * per;
+        float acc = 0.f;
+#pragma unroll
+        for (int t = 0; t < LSH_MAX_PER_LANE; ++t)
+          if (t < per) acc = __fadd_rn(acc, __fmul_rn(qu[t], x[t]));
+        float c = sah_round_to<T>(lsh_warp_sum(acc));
+        c = fminf(fmaxf(c, -1.0f), 1.0f);
+        if (lane == 0) {
+          const int64_t pos = ptr[row0 + r] + wpre[(row0 + r) * W + w] + __popc(word & ((1u << bit) - 1u));
+          data[pos] = __ushort_as_bfloat16(table[__float_as_uint(c) >> 16]);
+        }
+      }
+    }
+  }
+}
+
+// The decode shape of the same kernel: at most 4 rows per KV group (GQA 4, one query), head
+// dim 32 * PER known at compile time, keys 8-byte aligned.  Row words, CSR bases and the unit
+// queries sit in registers / shared memory for a whole bitmap word; the rows' results are
+// written by lanes 0..3 side by side.
+template <int PER>
+__global__ void __launch_bounds__(256)
+lsh_prob_decode_kernel(const __nv_bfloat16* __restrict__ k, int64_t ks_b, int64_t ks_h, int64_t ks_s,
+                       int Hq, int Sq, int G, const __nv_bfloat16* __restrict__ mean,
+                       const float* __restrict__ dens, int64_t cap,
+                       const unsigned int* __restrict__ max_bits, const float* __restrict__ qunit,
+                       const uint32_t* __restrict__ bits, const int32_t* __restrict__ wpre,
+                       const int64_t* __restrict__ ptr, int64_t W, const uint16_t* __restrict__ table,
+                       __nv_bfloat16* __restrict__ data) {
+  typedef __nv_bfloat16 T;
+  constexpr int D = 32 * PER;
+  __shared__ float U[LSH_DEN_TABLES * 128];
+  __shared__ float qs[4 * D];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const int Hkv = Hq / G;
+  const int64_t kvh = blockIdx.x;
+  const int64_t b = kvh / Hkv;
+  const int hkv = (int)(kvh % Hkv);
+  const int R = G * Sq;  // <= 4
+  const unsigned int mbits = *max_bits;
+  const float M = __uint_as_float(mbits);
+  const int64_t row0 = (b * Hq + (int64_t)hkv * G) * Sq;
+  for (int i = threadIdx.x; i < LSH_DEN_TABLES * 128; i += blockDim.x) {
+    const int di = i >> 7, m = i & 127;
+    const float t = sah_round_to<T>(__fdiv_rn(1.0f + (float)m * 0.0078125f, M));
+    const float d = __uint_as_float((LSH_DEN_BASE + (unsigned)di) << 16);
+    U[i] = sah_round_to<T>(__fdiv_rn(t, d));
+  }
+  for (int i = threadIdx.x; i < 4 * D; i += blockDim.x) qs[i] = i < R * D ? qunit[row0 * D + i] : 0.f;
+  __syncthreads();
+  const int shift = 127 - (int)((mbits >> 23) & 0xffu);
+  const int elo = max(1, 4 - shift), ehi = min(254, 250 - shift);
+  float m[PER];
+#pragma unroll
+  for (int t = 0; t < PER; ++t) m[t] = mean ? __bfloat162float(mean[kvh * D + lane * PER + t]) : 0.f;
+  // this lane's slice of the (up to) four unit queries
+  float qu[4][PER];
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int t = 0; t < PER; ++t) qu[r][t] = qs[r * D + lane * PER + t];
+  const T* kbase = k + b * ks_b + hkv * ks_h;
+  const float* dbase = dens + kvh * cap;
+  for (int64_t w = (int64_t)blockIdx.y * nwarp + warp; w < W; w += (int64_t)gridDim.y * nwarp) {
+    // lane 8r (r < R): word of row r and the CSR position of its first bit; the reduction
+    // below leaves row r's cosine in lanes 8r .. 8r+7
+    uint32_t myword = 0u;
+    int64_t mypos = 0;
+    if ((lane & 7) == 0 && (lane >> 3) < R) {
+      const int r = lane >> 3;
+      myword = bits[(row0 + r) * W + w];
+      mypos = ptr[row0 + r] + wpre[(row0 + r) * W + w];
+    }
+    uint32_t uni = myword;
+#pragma unroll
+    for (int o = 16; o >= 8; o >>= 1) uni |= __shfl_xor_sync(0xffffffffu, uni, o);
+    uni = __shfl_sync(0xffffffffu, uni, 0);
+    if (!uni) continue;
+    // Keys are taken four at a time: their rows are requested together, so that a warp has
+    // four independent row loads in flight, then worked on one after the other.
+    while (uni) {
+      int kb[4];
+      float xs[4][PER], dn[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        kb[j] = uni ? __ffs(uni) - 1 : -1;
+        uni &= uni - 1;  // 0 stays 0
+        if (kb[j] >= 0) {
+          lsh_load_lane<T>(kbase + (w * 32 + kb[j]) * ks_s, PER, lane, xs[j]);
+          dn[j] = dbase[w * 32 + kb[j]];
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (kb[j] < 0) break;
+        const int bit = kb[j];
+        const float den = dn[j];
+        float x[PER];
+        const unsigned int di = (__float_as_uint(den) >> 16) - LSH_DEN_BASE;
+        const float* Ud = U + (di < LSH_DEN_TABLES ? di : 0u) * 128;
+        float cc[PER];
+        bool slow = di >= LSH_DEN_TABLES;
+#pragma unroll
+        for (int t = 0; t < PER; ++t) {
+          cc[t] = mean ? sah_round_to<T>(__fsub_rn(xs[j][t], m[t])) : xs[j][t];
+          const uint32_t u = __float_as_uint(cc[t]);
+          const unsigned int e = (u >> 23) & 0xffu;
+          slow |= (e - (unsigned)elo) > (unsigned)(ehi - elo);
+          x[t] = __fmul_rn(__uint_as_float(u & 0xff800000u), Ud[(u >> 16) & 0x7fu]);
+        }
+        if (__any_sync(0xffffffffu, slow)) {  // rare: zero channels, denormals, an unusual norm
+          if (slow) {
+#pragma unroll
+            for (int t = 0; t < PER; ++t) {
+              const unsigned int e = (__float_as_uint(cc[t]) >> 23) & 0xffu;
+              if (di >= LSH_DEN_TABLES || (e - (unsigned)elo) > (unsigned)(ehi - elo))
+                x[t] = sah_round_to<T>(__fdiv_rn(sah_round_to<T>(__fdiv_rn(cc[t], M)), den));
+            }
+          }
+        }
+        // Four dot products at once.  Each row's 32 lane partials combine in the fixed tree
+        // (xor 16, 8, 4, 2, 1); the first two levels also sort the rows onto lane groups, so
+        // six shuffles serve all four rows and every sum is associated exactly as in a
+        // per-row tree.
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+        for (int t = 0; t < PER; ++t) {
+          a0 = __fadd_rn(a0, __fmul_rn(qu[0][t], x[t]));
+          a1 = __fadd_rn(a1, __fmul_rn(qu[1][t], x[t]));
+          a2 = __fadd_rn(a2, __fmul_rn(qu[2][t], x[t]));
+          a3 = __fadd_rn(a3, __fmul_rn(qu[3][t], x[t]));
+        }
+        const bool hi16 = (lane & 16) != 0, hi8 = (lane & 8) != 0;
+        const float r0 = __shfl_xor_sync(0xffffffffu, hi16 ? a0 : a2, 16);
+        const float r1 = __shfl_xor_sync(0xffffffffu, hi16 ? a1 : a3, 16);
+        const float k0 = __fadd_rn(hi16 ? a2 : a0, r0);  // rows 0 / 2
+        const float k1 = __fadd_rn(hi16 ? a3 : a1, r1);  // rows 1 / 3
+        const float r2 = __shfl_xor_sync(0xffffffffu, hi8 ? k0 : k1, 8);
+        float cosv = __fadd_rn(hi8 ? k1 : k0, r2);       // row 2 * bit4 + bit3
+        cosv = __fadd_rn(cosv, __shfl_xor_sync(0xffffffffu, cosv, 4));
+        cosv = __fadd_rn(cosv, __shfl_xor_sync(0xffffffffu, cosv, 2));
+        cosv = __fadd_rn(cosv, __shfl_xor_sync(0xffffffffu, cosv, 1));
+        if ((myword >> bit) & 1u) {  // only lanes 8r hold a word
+          float c = sah_round_to<T>(cosv);
+          c = fminf(fmaxf(c, -1.0f), 1.0f);
+          data[mypos + __popc(myword & ((1u << bit) - 1u))] =
+              __ushort_as_bfloat16(table[__float_as_uint(c) >> 16]);
+        }
+      }
+    }
+  }
+}
+
 extern "C" int sah_lsh_prob(const void* keys, int dtype, int64_t ks_b, int64_t ks_h, int64_t ks_s,
                             int B, int Hq, int Sq, int G, int D, const void* mean,
-                            const float* norms, int64_t cap, const unsigned int* max_norm_bits,
-                            const float* qunit, const uint32_t* bits, const int32_t* wpre,
-                            const int64_t* ptr, int64_t W, int K, int L, const uint16_t* table,
-                            void* data, int sm_count, void* stream) {
+                            const float* norms, const float* dens, int64_t cap,
+                            const unsigned int* max_norm_bits, const float* qunit,
+                            const uint32_t* bits, const int32_t* wpre, const int64_t* ptr, int64_t W,
+                            int K, int L, const uint16_t* table, void* data, int sm_count,
+                            void* stream) {
   SAH_REQUIRE(keys && norms && max_norm_bits && qunit && bits && wpre && ptr && data,
               "lsh_prob: null pointer");
   SAH_REQUIRE(D % 32 == 0 && D <= 32 * LSH_MAX_PER_LANE, "lsh_prob: head_dim must be a multiple of 32, <= 256");
@@ -668,11 +986,36 @@ extern "C" int sah_lsh_prob(const void* keys, int dtype, int64_t ks_b, int64_t k
   if (gy > cap_y) gy = cap_y;
   if (gy < 1) gy = 1;
   if (gy > 65535) gy = 65535;
-  size_t smem = 128 * sizeof(float);
-  const int q_in_smem = (size_t)R * D * sizeof(float) <= 40 * 1024;
-  if (q_in_smem) smem += (size_t)R * D * sizeof(float);
+  const int q_in_smem = (size_t)R * D * sizeof(float) <= 24 * 1024;
   dim3 grid((unsigned)groups, (unsigned)gy);
   sah_prof_begin(SAH_PROF_LSH_PROB, (cudaStream_t)stream);
+  if (dtype == SAH_BF16 && dens != nullptr) {
+    // cached key norms (sah_lsh_key_den): one table lookup per channel
+    if (R <= 4 && (D == 64 || D == 128 || D == 256)) {
+#define LSH_DECODE_LAUNCH(PER)                                                                       \
+  lsh_prob_decode_kernel<PER><<<grid, 256, 0, (cudaStream_t)stream>>>(                               \
+      reinterpret_cast<const __nv_bfloat16*>(keys), ks_b, ks_h, ks_s, Hq, Sq, G,                     \
+      reinterpret_cast<const __nv_bfloat16*>(mean), dens, cap, max_norm_bits, qunit, bits, wpre, ptr, \
+      W, table, reinterpret_cast<__nv_bfloat16*>(data))
+      if (D == 64) LSH_DECODE_LAUNCH(2);
+      else if (D == 128) LSH_DECODE_LAUNCH(4);
+      else LSH_DECODE_LAUNCH(8);
+      SAH_LAUNCH_CHECK("lsh_prob");
+      sah_prof_end(SAH_PROF_LSH_PROB, (cudaStream_t)stream);
+      return SAH_OK;
+    }
+    size_t fsmem = (size_t)LSH_DEN_TABLES * 128 * sizeof(float);
+    if (q_in_smem) fsmem += (size_t)R * D * sizeof(float);
+    lsh_prob_fast_kernel<<<grid, 256, fsmem, (cudaStream_t)stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(keys), ks_b, ks_h, ks_s, Hq, Sq, G, D,
+        reinterpret_cast<const __nv_bfloat16*>(mean), dens, cap, max_norm_bits, qunit, bits, wpre, ptr,
+        W, table, q_in_smem, reinterpret_cast<__nv_bfloat16*>(data));
+    SAH_LAUNCH_CHECK("lsh_prob");
+    sah_prof_end(SAH_PROF_LSH_PROB, (cudaStream_t)stream);
+    return SAH_OK;
+  }
+  size_t smem = 128 * sizeof(float);
+  if (q_in_smem) smem += (size_t)R * D * sizeof(float);
   SAH_DISPATCH_DTYPE(dtype, T, {
     lsh_prob_kernel<T><<<grid, 256, smem, (cudaStream_t)stream>>>(
         reinterpret_cast<const T*>(keys), ks_b, ks_h, ks_s, Hq, Sq, G, D,

@@ -72,12 +72,16 @@ class PackedLSHSignatures:
     planes   uint8 (lsh_k <= 8) or int16 `[B, Hkv, L, capacity]`: code of key s for table l
     norms    float32 `[B, Hkv, capacity]`: norm of the centred key (rounded to the key dtype)
     max_norm int32 `[1]`: float bits of the largest norm seen so far
+    dens     float32 `[B, Hkv, capacity]`: norm of the transformed key + 1e-8 (a per-key constant
+             of the probability formula), valid for the maximum norm in `dens_max`
     length   number of valid keys
     """
 
     def __init__(self, planes: torch.Tensor, norms: torch.Tensor, max_norm: torch.Tensor,
                  length: int, lsh_k: int) -> None:
         self.planes, self.norms, self.max_norm, self.length, self.lsh_k = planes, norms, max_norm, length, lsh_k
+        self.dens = torch.zeros_like(norms)
+        self.dens_max = torch.zeros_like(max_norm)
         # sequence-sharded use: total key count at which max_norm was last reduced over the shards
         self.synced_total: Optional[int] = None
 
@@ -105,6 +109,8 @@ class PackedLSHSignatures:
         new.planes[..., : self.length] = self.planes[..., : self.length]
         new.norms[..., : self.length] = self.norms[..., : self.length]
         new.max_norm.copy_(self.max_norm)
+        new.dens[..., : self.length] = self.dens[..., : self.length]
+        new.dens_max.copy_(self.dens_max)
         new.length = self.length
         new.synced_total = self.synced_total
         return new
@@ -205,7 +211,8 @@ class MagicPig(SamplingMasker):
                                                 h.norms.data_ptr(), h.max_norm.data_ptr(), sms, st),
                           "sah_lsh_key_stats")
 
-        if isinstance(handle, torch.Tensor):  # cached by the reference implementation
+        adopted = isinstance(handle, torch.Tensor)
+        if adopted:  # cached by the reference implementation
             handle = PackedLSHSignatures.from_reference_layout(handle, Hkv, self.lsh_k)
             n_cached = cache[layer_idx].shape[2]
             if n_cached > S:
@@ -227,6 +234,7 @@ class MagicPig(SamplingMasker):
             if resync:
                 shard.comm.all_reduce_max_(handle.max_norm)
                 handle.synced_total = shard.total
+        s_new0 = handle.length
         if S > handle.length:
             s0 = handle.length
             _native.check(
@@ -234,6 +242,14 @@ class MagicPig(SamplingMasker):
                                      handle.max_norm.data_ptr(), proj.data_ptr(), self.lsh_l, self.lsh_k,
                                      handle.capacity, handle.planes.data_ptr(), st), "sah_lsh_key_sign")
             handle.length = S
+        if S > s_new0 or resync or adopted:
+            # per-key constants of the probability formula: the new keys, or every key when
+            # the maximum norm moved (the kernel compares it with the one it last used)
+            _native.check(
+                lib.sah_lsh_key_den(*kargs, 0 if adopted else s_new0, S, D, _native.ptr(mean),
+                                    handle.norms.data_ptr(), handle.capacity, handle.max_norm.data_ptr(),
+                                    handle.dens_max.data_ptr(), handle.dens.data_ptr(), sms, st),
+                "sah_lsh_key_den")
         cache[layer_idx] = handle
         return handle
 
@@ -280,7 +296,7 @@ class MagicPig(SamplingMasker):
         table = _native_ops.lsh_prob_table(dev, self.lsh_k, self.lsh_l) if dtype == torch.bfloat16 else None
         _native.check(
             lib.sah_lsh_prob(k.data_ptr(), code, k.stride(0), k.stride(1), k.stride(2), B, Hq, Sq, G, D,
-                             _native.ptr(mean), sig.norms.data_ptr(), sig.capacity,
+                             _native.ptr(mean), sig.norms.data_ptr(), sig.dens.data_ptr(), sig.capacity,
                              sig.max_norm.data_ptr(), qunit.data_ptr(), bits.data_ptr(),
                              nb.wpre.data_ptr(), nb.ptr.data_ptr(), W, self.lsh_k, self.lsh_l,
                              _native.ptr(table), data.data_ptr(), _native.sm_count(dev), st),
