@@ -834,7 +834,7 @@ lsh_prob_fast_kernel(const __nv_bfloat16* __restrict__ k, int64_t ks_b, int64_t 
 // queries sit in registers / shared memory for a whole bitmap word; the rows' results are
 // written by lanes 0..3 side by side.
 template <int PER>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 lsh_prob_decode_kernel(const __nv_bfloat16* __restrict__ k, int64_t ks_b, int64_t ks_h, int64_t ks_s,
                        int Hq, int Sq, int G, const __nv_bfloat16* __restrict__ mean,
                        const float* __restrict__ dens, int64_t cap,
