@@ -526,27 +526,34 @@ extern "C" int sah_hash_topk(const uint32_t* kcodes, int64_t kc_stride, const ui
 }
 
 // ---------------------------------------------------------------------------------------
-// Sequence-sharded Hamming top-k: the keys of a row are spread over `world` ranks (contiguous
-// ranges in rank order).  Each rank histograms its range (sah_hash_hist), the histograms of
-// all ranks are gathered by the caller, and every rank derives the same global threshold and
-// its own share of the ties at the threshold (sah_hash_shard_plan) -- ties go to the lowest
-// global column, that is to the lower ranks first -- and emits its part (sah_hash_emit).
-// The union over ranks is exactly the single-device selection.
+// Hamming top-k in pieces: a row's keys are cut into `parts` contiguous column ranges -- the
+// `chunks` chunks of each of `world` ranks, rank-major, so part index order is column order.
+// Every part is histogrammed by its own CTA (sah_hash_hist), all parts' histograms are put
+// side by side (across ranks by the caller's all-gather), every part derives the same
+// threshold and its own share of the ties at the threshold -- ties go to the lowest column,
+// that is to the lower parts first (sah_hash_shard_plan) -- and emits its range
+// (sah_hash_emit).  The union over parts is exactly the selection of hash_topk_fast_kernel.
+// With world = 1 this is the single-device path for few, long rows (sah_hash_topk_ws).
 // ---------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024)
+#define HP_THREADS 256
+
+__global__ void __launch_bounds__(HP_THREADS)
 hash_hist_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
                  const uint32_t* __restrict__ qcodes, int nbits, int Sq, int64_t S, int64_t W,
-                 const uint32_t* __restrict__ prev_bits, int32_t* __restrict__ hist_out) {
-  __shared__ unsigned int hist[32][HT_BINS];
+                 int64_t chunk_words, const uint32_t* __restrict__ prev_bits, int64_t rows,
+                 int32_t* __restrict__ hist_out) {
+  __shared__ unsigned int hist[HP_THREADS / 32][HT_BINS];
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int64_t row = blockIdx.x;
+  const int64_t row = blockIdx.x, chunk = blockIdx.y;
   const uint32_t* kc = kcodes + (row / Sq) * kc_stride;
   const uint32_t qc = qcodes[row];
   const uint32_t* prev_row = prev_bits + row * W;
   const bool aligned = ((reinterpret_cast<uintptr_t>(kc) & 15) == 0);
-  for (int i = tid; i < 32 * HT_BINS; i += 1024) (&hist[0][0])[i] = 0u;
+  for (int i = tid; i < (HP_THREADS / 32) * HT_BINS; i += HP_THREADS) (&hist[0][0])[i] = 0u;
   __syncthreads();
-  for (int64_t w = tid; w < W; w += 1024) {
+  const int64_t w_lo = chunk * chunk_words;
+  const int64_t w_hi = w_lo + chunk_words < W ? w_lo + chunk_words : W;
+  for (int64_t w = w_lo + tid; w < w_hi; w += HP_THREADS) {
     uint32_t codes[32];
     ht_load_codes(kc, w, S, aligned, codes);
     const int64_t c0 = w * 32;
@@ -561,32 +568,40 @@ hash_hist_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
   __syncthreads();
   if (tid < 33) {
     unsigned int s = 0;
-    for (int w2 = 0; w2 < 32; ++w2) s += hist[w2][tid];
-    hist_out[row * 33 + tid] = (int32_t)s;
+#pragma unroll
+    for (int w2 = 0; w2 < HP_THREADS / 32; ++w2) s += hist[w2][tid];
+    hist_out[(chunk * rows + row) * 33 + tid] = (int32_t)s;
   }
 }
 
 extern "C" int sah_hash_hist(const uint32_t* kcodes, int64_t kc_stride, const uint32_t* qcodes,
-                             int nbits, int B, int Hq, int Sq, int64_t S, int64_t W,
+                             int nbits, int B, int Hq, int Sq, int64_t S, int64_t W, int chunks,
                              const uint32_t* prev_bits, int32_t* hist, void* stream) {
   SAH_REQUIRE(kcodes && qcodes && prev_bits && hist, "hash_hist: null pointer");
   SAH_REQUIRE(nbits > 0 && nbits <= 32, "hash_hist: nbits must be 1..32");
   SAH_REQUIRE(kc_stride >= S && B > 0 && Hq > 0 && Sq > 0 && S > 0 && W * 32 >= S, "hash_hist: bad extents");
+  SAH_REQUIRE(chunks >= 1 && chunks <= 65535, "hash_hist: 1..65535 chunks");
   const int64_t rows = (int64_t)B * Hq * Sq;
-  hash_hist_kernel<<<(unsigned)rows, 1024, 0, (cudaStream_t)stream>>>(kcodes, kc_stride, qcodes, nbits, Sq,
-                                                                     S, W, prev_bits, hist);
+  const int64_t chunk_words = sah_ceil_div(W, chunks);
+  dim3 grid((unsigned)rows, (unsigned)chunks);
+  hash_hist_kernel<<<grid, HP_THREADS, 0, (cudaStream_t)stream>>>(kcodes, kc_stride, qcodes, nbits, Sq, S, W,
+                                                                chunk_words, prev_bits, rows, hist);
   SAH_LAUNCH_CHECK("hash_hist");
   return SAH_OK;
 }
 
-// hist_all [world][rows][33]; one thread per row.  thr[row]: scores above it are taken whole
-// (-1: every candidate, 64: none); need[row]: ties at thr this rank takes.
+// hist_all [world][chunks][rows][33]; one thread per (row, chunk of this rank).
+// thr: scores above it are taken whole (-1: every candidate, 64: none); need: ties at thr
+// this part takes.  Outputs are [chunks][rows].
 __global__ void hash_shard_plan_kernel(const int32_t* __restrict__ hist_all, int world, int rank,
-                                       int64_t rows, int64_t k, int32_t* __restrict__ thr_out,
-                                       int64_t* __restrict__ need_out) {
-  const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (row >= rows) return;
-  long long ge = 0;  // candidates scoring >= bin, over all ranks
+                                       int chunks, int64_t rows, int64_t k,
+                                       int32_t* __restrict__ thr_out, int64_t* __restrict__ need_out) {
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= rows * chunks) return;
+  const int64_t row = t % rows;
+  const int chunk = (int)(t / rows);
+  const int parts = world * chunks, me = rank * chunks + chunk;
+  long long ge = 0;  // candidates scoring >= bin, over all parts
   int thr = -1;
   long long need = 0;
   if (k <= 0) {
@@ -594,56 +609,61 @@ __global__ void hash_shard_plan_kernel(const int32_t* __restrict__ hist_all, int
   } else {
     for (int bin = 32; bin >= 0; --bin) {
       long long here = 0, before_me = 0, mine = 0;
-      for (int g = 0; g < world; ++g) {
+      for (int g = 0; g < parts; ++g) {
         const long long c = hist_all[((int64_t)g * rows + row) * 33 + bin];
-        if (g < rank) before_me += c;
-        if (g == rank) mine = c;
+        if (g < me) before_me += c;
+        if (g == me) mine = c;
         here += c;
       }
       if (ge + here >= k) {  // the k-th best score is this bin
         thr = bin;
-        const long long ties = k - ge;            // ties to take over all ranks
-        const long long left = ties - before_me;  // what lower ranks leave for this one
+        const long long ties = k - ge;            // ties to take over all parts
+        const long long left = ties - before_me;  // what lower parts leave for this one
         need = left <= 0 ? 0 : (left < mine ? left : mine);
         break;
       }
       ge += here;
     }
   }
-  thr_out[row] = thr;
-  need_out[row] = need;
+  thr_out[t] = thr;
+  need_out[t] = need;
 }
 
-extern "C" int sah_hash_shard_plan(const int32_t* hist_all, int world, int rank, int64_t rows,
-                                   int64_t k, int32_t* thr, int64_t* need, void* stream) {
+extern "C" int sah_hash_shard_plan(const int32_t* hist_all, int world, int rank, int chunks,
+                                   int64_t rows, int64_t k, int32_t* thr, int64_t* need,
+                                   void* stream) {
   SAH_REQUIRE(hist_all && thr && need, "hash_shard_plan: null pointer");
-  SAH_REQUIRE(world > 0 && rank >= 0 && rank < world && rows > 0, "hash_shard_plan: bad extents");
-  hash_shard_plan_kernel<<<(unsigned)sah_ceil_div(rows, 128), 128, 0, (cudaStream_t)stream>>>(
-      hist_all, world, rank, rows, k, thr, need);
+  SAH_REQUIRE(world > 0 && rank >= 0 && rank < world && rows > 0 && chunks >= 1,
+              "hash_shard_plan: bad extents");
+  hash_shard_plan_kernel<<<(unsigned)sah_ceil_div(rows * chunks, 128), 128, 0, (cudaStream_t)stream>>>(
+      hist_all, world, rank, chunks, rows, k, thr, need);
   SAH_LAUNCH_CHECK("hash_shard_plan");
   return SAH_OK;
 }
 
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(HP_THREADS)
 hash_emit_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
                  const uint32_t* __restrict__ qcodes, int nbits, int Sq, int64_t S, int64_t W,
-                 const uint32_t* __restrict__ prev_bits, const int32_t* __restrict__ thr_in,
-                 const int64_t* __restrict__ need_in, uint32_t* __restrict__ out_bits) {
+                 int64_t chunk_words, const uint32_t* __restrict__ prev_bits, int64_t rows,
+                 const int32_t* __restrict__ thr_in, const int64_t* __restrict__ need_in,
+                 uint32_t* __restrict__ out_bits) {
   __shared__ long long scan[33];
   const int tid = threadIdx.x;
-  const int64_t row = blockIdx.x;
+  const int64_t row = blockIdx.x, chunk = blockIdx.y;
   const uint32_t* kc = kcodes + (row / Sq) * kc_stride;
   const uint32_t qc = qcodes[row];
   const uint32_t* prev_row = prev_bits + row * W;
   uint32_t* out_row = out_bits + row * W;
   const bool aligned = ((reinterpret_cast<uintptr_t>(kc) & 15) == 0);
-  const int thr = thr_in[row];
-  const long long need = need_in[row];
+  const int thr = thr_in[chunk * rows + row];
+  const long long need = need_in[chunk * rows + row];
+  const int64_t w_lo = chunk * chunk_words;
+  const int64_t w_hi = w_lo + chunk_words < W ? w_lo + chunk_words : W;
   long long base = 0;
-  for (int64_t w0 = 0; w0 < W; w0 += 1024) {
+  for (int64_t w0 = w_lo; w0 < w_hi; w0 += HP_THREADS) {
     const int64_t w = w0 + tid;
     uint32_t gt = 0u, eq = 0u, pw = 0u;
-    if (w < W) {
+    if (w < w_hi) {
       uint32_t codes[32];
       ht_load_codes(kc, w, S, aligned, codes);
       pw = prev_row[w];
@@ -661,7 +681,7 @@ hash_emit_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
     }
     long long total_eq;
     const long long before = sah_block_excl_scan<long long>((long long)__popc(eq), scan, &total_eq);
-    if (w < W) {
+    if (w < w_hi) {
       const long long quota = need - (base + before);
       const int take = quota > 32 ? 32 : (quota < 0 ? 0 : (int)quota);
       out_row[w] = pw | gt | sah_lowest_bits(eq, take);
@@ -671,15 +691,67 @@ hash_emit_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
 }
 
 extern "C" int sah_hash_emit(const uint32_t* kcodes, int64_t kc_stride, const uint32_t* qcodes,
-                             int nbits, int B, int Hq, int Sq, int64_t S, int64_t W,
+                             int nbits, int B, int Hq, int Sq, int64_t S, int64_t W, int chunks,
                              const uint32_t* prev_bits, const int32_t* thr, const int64_t* need,
                              uint32_t* out_bits, void* stream) {
   SAH_REQUIRE(kcodes && qcodes && prev_bits && thr && need && out_bits, "hash_emit: null pointer");
   SAH_REQUIRE(nbits > 0 && nbits <= 32, "hash_emit: nbits must be 1..32");
   SAH_REQUIRE(kc_stride >= S && B > 0 && Hq > 0 && Sq > 0 && S > 0 && W * 32 >= S, "hash_emit: bad extents");
+  SAH_REQUIRE(chunks >= 1 && chunks <= 65535, "hash_emit: 1..65535 chunks");
   const int64_t rows = (int64_t)B * Hq * Sq;
-  hash_emit_kernel<<<(unsigned)rows, 1024, 0, (cudaStream_t)stream>>>(kcodes, kc_stride, qcodes, nbits, Sq,
-                                                                     S, W, prev_bits, thr, need, out_bits);
+  const int64_t chunk_words = sah_ceil_div(W, chunks);
+  dim3 grid((unsigned)rows, (unsigned)chunks);
+  hash_emit_kernel<<<grid, HP_THREADS, 0, (cudaStream_t)stream>>>(kcodes, kc_stride, qcodes, nbits, Sq, S, W,
+                                                                chunk_words, prev_bits, rows, thr, need,
+                                                                out_bits);
   SAH_LAUNCH_CHECK("hash_emit");
+  return SAH_OK;
+}
+
+// The single-device use of the three kernels above: rows cut into chunks so that the grid
+// fills the GPU whatever the row count.
+static int hash_ws_chunks(int64_t rows, int64_t W, int sm_count) {
+  if (sm_count <= 0) sm_count = 148;
+  int64_t chunks = sah_ceil_div((int64_t)sm_count * 8, rows);
+  const int64_t max_chunks = sah_ceil_div(W, HP_THREADS);  // at least one word per thread
+  if (chunks > max_chunks) chunks = max_chunks;
+  if (chunks < 1) chunks = 1;
+  if (chunks > 1024) chunks = 1024;
+  return (int)chunks;
+}
+
+extern "C" int64_t sah_hash_topk_ws_bytes(int64_t rows, int64_t W, int sm_count) {
+  if (rows <= 0 || W <= 0) return 0;
+  const int64_t chunks = hash_ws_chunks(rows, W, sm_count);
+  return rows * chunks * (33 * 4 + 4 + 8) + 64;
+}
+
+extern "C" int sah_hash_topk_ws(const uint32_t* kcodes, int64_t kc_stride, const uint32_t* qcodes,
+                                int nbits, int B, int Hq, int Sq, int64_t S, int64_t W,
+                                const uint32_t* prev_bits, int64_t k, uint32_t* out_bits,
+                                void* workspace, int64_t workspace_bytes, int sm_count, void* stream) {
+  SAH_REQUIRE(workspace != nullptr && ((uintptr_t)workspace & 15) == 0,
+              "hash_topk_ws: workspace must be a 16-byte aligned device pointer");
+  const int64_t rows = (int64_t)B * Hq * Sq;
+  SAH_REQUIRE(rows > 0 && rows <= 2147483647, "hash_topk_ws: bad row count");
+  if (workspace_bytes < sah_hash_topk_ws_bytes(rows, W, sm_count))
+    return sah_fail(SAH_ERR_WORKSPACE, "hash_topk_ws: workspace of %lld bytes, need %lld",
+                    (long long)workspace_bytes, (long long)sah_hash_topk_ws_bytes(rows, W, sm_count));
+  const int chunks = hash_ws_chunks(rows, W, sm_count);
+  unsigned char* p = reinterpret_cast<unsigned char*>(workspace);
+  int64_t* need = reinterpret_cast<int64_t*>(p);
+  p += rows * chunks * 8;
+  int32_t* hist = reinterpret_cast<int32_t*>(p);
+  p += rows * chunks * 33 * 4;
+  int32_t* thr = reinterpret_cast<int32_t*>(p);
+  sah_prof_begin(SAH_PROF_HASH_TOPK, (cudaStream_t)stream);
+  int rc = sah_hash_hist(kcodes, kc_stride, qcodes, nbits, B, Hq, Sq, S, W, chunks, prev_bits, hist, stream);
+  if (rc != SAH_OK) return rc;
+  rc = sah_hash_shard_plan(hist, 1, 0, chunks, rows, k, thr, need, stream);
+  if (rc != SAH_OK) return rc;
+  rc = sah_hash_emit(kcodes, kc_stride, qcodes, nbits, B, Hq, Sq, S, W, chunks, prev_bits, thr, need,
+                     out_bits, stream);
+  if (rc != SAH_OK) return rc;
+  sah_prof_end(SAH_PROF_HASH_TOPK, (cudaStream_t)stream);
   return SAH_OK;
 }

@@ -198,12 +198,25 @@ def hash_topk(kcodes: torch.Tensor, n_keys: int, qcodes: torch.Tensor, nbits: in
         raise ValueError("key codes must be contiguous [B, Hq, capacity >= S]")
     prev = previous_mask.native_bits()
     dst = NativeBits(torch.empty_like(prev.bits), prev.rows, S)
+    dev = kcodes.device
+    st = _native.stream_of(dev)
+    sms = _native.sm_count(dev)
+    if attention_mask is None and prev.rows < sms:
+        # fewer rows than SMs (long contexts, small batches): histogram / plan / emit with
+        # every row cut into chunks, so that the grid still fills the device; with more rows
+        # the one-CTA-per-row kernel below does the same in a single launch
+        nbytes = int(lib.sah_hash_topk_ws_bytes(prev.rows, prev.words, sms))
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        _native.check(
+            lib.sah_hash_topk_ws(kcodes.data_ptr(), kcodes.shape[-1], qcodes.data_ptr(), nbits, B, Hq, Sq,
+                                 S, prev.words, prev.bits.data_ptr(), k, dst.bits.data_ptr(),
+                                 ws.data_ptr(), nbytes, sms, st), "sah_hash_topk_ws")
+        return dst
     keep, bptr, bsb, bsh, bsq = bias_args(attention_mask, dtype, S)
     _native.check(
         lib.sah_hash_topk(kcodes.data_ptr(), kcodes.shape[-1], qcodes.data_ptr(), nbits, bptr,
                           _native.dtype_code(dtype), bsb, bsh, bsq, B, Hq, Sq, S, prev.words,
-                          prev.bits.data_ptr(), k, dst.bits.data_ptr(),
-                          _native.stream_of(kcodes.device)),
+                          prev.bits.data_ptr(), k, dst.bits.data_ptr(), st),
         "sah_hash_topk")
     del keep
     return dst
@@ -223,14 +236,18 @@ def hash_topk_sharded(kcodes: torch.Tensor, qcodes: torch.Tensor, nbits: int, pr
     st = _native.stream_of(dev)
     prev = previous_mask.native_bits()
     rows = prev.rows
-    hist = torch.empty((rows, 33), dtype=torch.int32, device=dev)
-    args = (kcodes.data_ptr(), kcodes.shape[-1], qcodes.data_ptr(), nbits, B, Hq, Sq, S, prev.words,
+    # every rank cuts its range into the same number of chunks (one CTA per row and chunk);
+    # the count depends on the row count only, so that all ranks agree on it
+    words = prev.words
+    chunks = max(1, min(-(-_native.sm_count(dev) * 8 // rows), 256))
+    hist = torch.empty((chunks, rows, 33), dtype=torch.int32, device=dev)
+    args = (kcodes.data_ptr(), kcodes.shape[-1], qcodes.data_ptr(), nbits, B, Hq, Sq, S, words, chunks,
             prev.bits.data_ptr())
     _native.check(lib.sah_hash_hist(*args, hist.data_ptr(), st), "sah_hash_hist")
-    hist_all = comm.all_gather(hist)
-    thr = torch.empty(rows, dtype=torch.int32, device=dev)
-    need = torch.empty(rows, dtype=torch.int64, device=dev)
-    _native.check(lib.sah_hash_shard_plan(hist_all.data_ptr(), comm.world, comm.rank, rows, k,
+    hist_all = comm.all_gather(hist)  # [world, chunks, rows, 33]
+    thr = torch.empty((chunks, rows), dtype=torch.int32, device=dev)
+    need = torch.empty((chunks, rows), dtype=torch.int64, device=dev)
+    _native.check(lib.sah_hash_shard_plan(hist_all.data_ptr(), comm.world, comm.rank, chunks, rows, k,
                                           thr.data_ptr(), need.data_ptr(), st), "sah_hash_shard_plan")
     dst = NativeBits(torch.empty_like(prev.bits), rows, S)
     _native.check(lib.sah_hash_emit(*args, thr.data_ptr(), need.data_ptr(), dst.bits.data_ptr(), st),
