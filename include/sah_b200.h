@@ -207,6 +207,33 @@ int sah_topk_select(const void* scores, int dtype, int64_t rows, int64_t S, int6
  * bytes (SAH_ERR_WORKSPACE when smaller); rows <= 65535.  out_bits may alias
  * prev_bits.  Same result as sah_topk_select, bit for bit. */
 int64_t sah_topk_select_ws_bytes(int64_t rows, int64_t W);
+/* The same selection step by step, for rows whose keys are spread over ranks
+ * (contiguous column ranges in rank order; every rank works on its own columns with
+ * its own workspace of sah_topk_select_ws_bytes bytes):
+ *   sah_topk_sel_begin(k)            reset the state (k counts keys of the whole row);
+ *   for shift = keybits-8, ..., 0    (keybits 16 for bf16, 32 for fp32):
+ *     sah_topk_sel_hist(shift)       digit histogram of this rank's candidates into the
+ *                                    uint32 [rows][256] array that starts
+ *                                    sah_topk_sel_hist_offset(rows, W) bytes into the
+ *                                    workspace; the caller sums it over the ranks in place;
+ *     sah_topk_sel_pick(shift, first = (shift == keybits-8), eq_total)
+ *                                    fix the digit; at shift 0, eq_total[row] (int64, may
+ *                                    be NULL) = this rank's keys equal to the threshold;
+ *   sah_topk_sel_emit(tie_offset)    tie_offset[row] (int64, may be NULL) = such keys on
+ *                                    lower ranks; out_bits = prev | above | first ties.
+ * With one rank and NULL eq_total / tie_offset this is sah_topk_select_ws. */
+int64_t sah_topk_sel_hist_offset(int64_t rows, int64_t W);
+int sah_topk_sel_begin(int64_t rows, int64_t W, int64_t k, void* workspace,
+                       int64_t workspace_bytes, void* stream);
+int sah_topk_sel_hist(const void* scores, int dtype, int64_t rows, int64_t S, int64_t W,
+                      int64_t col_begin, int64_t col_end, const uint32_t* prev_bits,
+                      void* workspace, int shift, void* stream);
+int sah_topk_sel_pick(int64_t rows, int64_t W, void* workspace, int shift, int first,
+                      int64_t* eq_total, void* stream);
+int sah_topk_sel_emit(const void* scores, int dtype, int64_t rows, int64_t S, int64_t W,
+                      int64_t col_begin, int64_t col_end, const uint32_t* prev_bits,
+                      void* workspace, const int64_t* tie_offset, uint32_t* out_bits,
+                      void* stream);
 int sah_topk_select_ws(const void* scores, int dtype, int64_t rows, int64_t S, int64_t W,
                        int64_t col_begin, int64_t col_end, const uint32_t* prev_bits,
                        int64_t k, uint32_t* out_bits, void* workspace,

@@ -132,6 +132,17 @@ def build_local_mask(stack, q, k_loc, dtype: str, shard: Shard, meta: Dict[str, 
             s = hashattention.scores(qc, kc, prm["bits"], dtype, None)
             sel = _global_topk_local_part(s, st.mask != 0, kk, shard)
             st.set(mask_ops.merge(st.mask, sel.astype(np.float32), dtype))
+        elif kind == "oracle_topk":
+            from . import qk
+            kk = mask_ops.effective_size(prm["heavy_size"], shard.total)
+            if shard.total <= kk:
+                st.full = True
+                continue
+            s = qk.qk_scores(q, k_loc, dtype, None)
+            sel = _global_topk_local_part(s, st.mask != 0, kk, shard)
+            out = st.mask.copy()
+            out[sel] = 1.0
+            st.set(out)
         elif kind == "magicpig":
             magicpig.apply(prm, st, q, k_loc, meta, shard)
         else:

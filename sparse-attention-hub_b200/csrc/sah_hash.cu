@@ -493,6 +493,127 @@ hash_topk_fast_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
   }
 }
 
+// The same selection with 512 threads per row and the scores kept in registers between the two
+// passes: thread t owns bitmap words t, t + 512, ... (WPT of them), its 32 scores per word
+// packed as bytes, so pass 2 neither reloads the codes nor recounts bits, and byte-wise SIMD
+// compares produce the "above" and "equal" masks.  Two CTAs fit on an SM, so 256 rows make one
+// balanced wave on 148 SMs where 1024-thread CTAs made two.
+#define HT2_THREADS 512
+
+__device__ __forceinline__ unsigned int ht_flags4(unsigned int w) {  // 4 byte flags -> 4 bits
+  return ((w & 0x01010101u) * 0x01020408u) >> 24;
+}
+
+template <int WPT>
+__global__ void __launch_bounds__(HT2_THREADS, 2)
+hash_topk_reg_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
+                     const uint32_t* __restrict__ qcodes, int nbits, int Sq, int64_t S, int64_t W,
+                     const uint32_t* __restrict__ prev_bits, int64_t k,
+                     uint32_t* __restrict__ out_bits) {
+  __shared__ unsigned int hist[HT2_THREADS / 32][HT_BINS];
+  __shared__ long long scan[33];
+  __shared__ int thr_sm;
+  __shared__ long long need_sm;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t row = blockIdx.x;
+  const uint32_t* kc = kcodes + (row / Sq) * kc_stride;
+  const uint32_t qc = qcodes[row];
+  const uint32_t* prev_row = prev_bits + row * W;
+  uint32_t* out_row = out_bits + row * W;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(kc) & 15) == 0);
+  for (int i = tid; i < (HT2_THREADS / 32) * HT_BINS; i += HT2_THREADS) (&hist[0][0])[i] = 0u;
+  __syncthreads();
+
+  uint32_t sc4[WPT][8];   // scores, four per register
+  uint32_t validm[WPT], prevw[WPT];
+#pragma unroll
+  for (int j = 0; j < WPT; ++j) {
+    const int64_t w = tid + (int64_t)j * HT2_THREADS;
+    validm[j] = 0u;
+    prevw[j] = 0u;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sc4[j][i] = 0u;
+    if (w < W) {
+      uint32_t codes[32];
+      ht_load_codes(kc, w, S, aligned, codes);
+      const uint32_t pw = prev_row[w];
+      const int64_t c0 = w * 32;
+      uint32_t valid = ~pw;
+      if (c0 + 32 > S) valid &= (c0 >= S) ? 0u : ((1u << (S - c0)) - 1u);
+      prevw[j] = pw;
+      validm[j] = valid;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const unsigned int sc = (unsigned int)(nbits - __popc(codes[i] ^ qc));
+        sc4[j][i >> 2] |= sc << ((i & 3) * 8);
+        if ((valid >> i) & 1u) atomicAdd(&hist[warp][sc], 1u);
+      }
+    }
+  }
+  __syncthreads();
+  if (warp == 0) {
+    // lane b owns bin b (b = 0..31); bin 32 (all bits match) is handled aside
+    unsigned int mine = 0u, top = 0u;
+    for (int w2 = 0; w2 < HT2_THREADS / 32; ++w2) {
+      mine += hist[w2][lane];
+      top += hist[w2][32];
+    }
+    unsigned int incl = mine;  // suffix sum over lanes: keys with bin >= lane (bins <= 31)
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      unsigned int n = __shfl_down_sync(0xffffffffu, incl, o);
+      if (lane + o < 32) incl += n;
+    }
+    const long long ge = (long long)incl + top;
+    const long long total = __shfl_sync(0xffffffffu, (long long)incl, 0) + top;
+    int thr;
+    long long need;
+    if (k <= 0) {
+      thr = 64; need = 0;                 // nothing qualifies
+    } else if (total <= k) {
+      thr = -1; need = 0;                 // every candidate qualifies
+    } else if ((long long)top >= k) {
+      thr = 32; need = k;
+    } else {
+      const unsigned int ok = __ballot_sync(0xffffffffu, ge >= k);
+      thr = 31 - __clz(ok);               // highest bin whose ">=" count reaches k
+      const long long ge_thr = __shfl_sync(0xffffffffu, ge, thr);
+      const long long mine_thr = __shfl_sync(0xffffffffu, (long long)mine, thr);
+      need = k - (ge_thr - mine_thr);     // ties to take at the threshold
+    }
+    if (lane == 0) {
+      thr_sm = thr;
+      need_sm = need;
+    }
+  }
+  __syncthreads();
+  const int thr = thr_sm;
+  const long long need = need_sm;
+  const unsigned int thr4 = (unsigned int)(thr & 0xff) * 0x01010101u;
+
+  long long base = 0;
+#pragma unroll
+  for (int j = 0; j < WPT; ++j) {
+    const int64_t w = tid + (int64_t)j * HT2_THREADS;
+    uint32_t gt = 0u, eq = 0u;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      gt |= ht_flags4(__vcmpgts4(sc4[j][i], thr4)) << (4 * i);
+      eq |= ht_flags4(__vcmpeq4(sc4[j][i], thr4)) << (4 * i);
+    }
+    gt &= validm[j];
+    eq &= validm[j];
+    long long total_eq;
+    const long long before = sah_block_excl_scan<long long>((long long)__popc(eq), scan, &total_eq);
+    if (w < W) {
+      const long long quota = need - (base + before);
+      const int take = quota > 32 ? 32 : (quota < 0 ? 0 : (int)quota);
+      out_row[w] = prevw[j] | gt | sah_lowest_bits(eq, take);
+    }
+    base += total_eq;
+  }
+}
+
 extern "C" int sah_hash_topk(const uint32_t* kcodes, int64_t kc_stride, const uint32_t* qcodes,
                              int nbits,
                              const void* bias, int dtype, int64_t bias_s_b, int64_t bias_s_h,
@@ -507,8 +628,19 @@ extern "C" int sah_hash_topk(const uint32_t* kcodes, int64_t kc_stride, const ui
   cudaStream_t st = (cudaStream_t)stream;
   sah_prof_begin(SAH_PROF_HASH_TOPK, (cudaStream_t)stream);
   if (bias == nullptr) {
-    hash_topk_fast_kernel<<<(unsigned)rows, 1024, 0, st>>>(kcodes, kc_stride, qcodes, nbits, Sq, S,
-                                                          W, prev_bits, k, out_bits);
+    const int64_t wpt = sah_ceil_div(W, HT2_THREADS);
+    if (wpt <= 1)
+      hash_topk_reg_kernel<1><<<(unsigned)rows, HT2_THREADS, 0, st>>>(kcodes, kc_stride, qcodes, nbits, Sq,
+                                                                     S, W, prev_bits, k, out_bits);
+    else if (wpt <= 2)
+      hash_topk_reg_kernel<2><<<(unsigned)rows, HT2_THREADS, 0, st>>>(kcodes, kc_stride, qcodes, nbits, Sq,
+                                                                     S, W, prev_bits, k, out_bits);
+    else if (wpt <= 4)
+      hash_topk_reg_kernel<4><<<(unsigned)rows, HT2_THREADS, 0, st>>>(kcodes, kc_stride, qcodes, nbits, Sq,
+                                                                     S, W, prev_bits, k, out_bits);
+    else
+      hash_topk_fast_kernel<<<(unsigned)rows, 1024, 0, st>>>(kcodes, kc_stride, qcodes, nbits, Sq, S,
+                                                            W, prev_bits, k, out_bits);
   } else if (dtype == SAH_BF16) {
     hash_topk_kernel<__nv_bfloat16, 16, true><<<(unsigned)rows, SAH_SELECT_THREADS, 0, st>>>(
         kcodes, kc_stride, qcodes, nbits, (const __nv_bfloat16*)bias, bias_s_b, bias_s_h, bias_s_q, Hq, Sq,

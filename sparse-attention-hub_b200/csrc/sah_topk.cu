@@ -359,7 +359,7 @@ sel_hist_kernel(const T* __restrict__ scores, int64_t S, int64_t W, int64_t col_
 __global__ void __launch_bounds__(256)
 sel_pick_kernel(SelState* __restrict__ state, unsigned int* __restrict__ hist, int shift, int first,
                 const unsigned int* __restrict__ chunk_hist, long long* __restrict__ chunk_before,
-                int64_t chunks) {
+                int64_t chunks, long long* __restrict__ eq_total_out) {
   __shared__ long long scan[33];
   __shared__ int bin_sm;
   const int tid = threadIdx.x;
@@ -369,6 +369,7 @@ sel_pick_kernel(SelState* __restrict__ state, unsigned int* __restrict__ hist, i
   const int bin = 255 - tid;
   const long long cnt = hist[row * 256 + bin];
   hist[row * 256 + bin] = 0u;  // ready for the next digit
+  if (eq_total_out != nullptr && tid == 0) eq_total_out[row] = 0;
   if (st.mode != 0) return;
   long long total;
   const long long above = sah_block_excl_scan<long long>(cnt, scan, &total);
@@ -398,6 +399,8 @@ sel_pick_kernel(SelState* __restrict__ state, unsigned int* __restrict__ hist, i
     if (c < chunks) chunk_before[row * chunks + c] = base + ex;
     base += tot;
   }
+  // keys equal to the threshold in this rank's range (ties are served to lower ranks first)
+  if (eq_total_out != nullptr && tid == 0) eq_total_out[row] = base;
 }
 
 template <typename T, int KEYBITS>
@@ -405,7 +408,7 @@ __global__ void __launch_bounds__(SEL_THREADS)
 sel_emit_kernel(const T* __restrict__ scores, int64_t S, int64_t W, int64_t col_begin, int64_t col_end,
                 const uint32_t* __restrict__ prev_bits, const SelState* __restrict__ state,
                 const long long* __restrict__ chunk_before, int64_t chunks, int vec,
-                uint32_t* __restrict__ out_bits) {
+                const long long* __restrict__ tie_offset, uint32_t* __restrict__ out_bits) {
   __shared__ long long scan[33];
   const int tid = threadIdx.x;
   const int64_t row = blockIdx.y, chunk = blockIdx.x;
@@ -432,7 +435,8 @@ sel_emit_kernel(const T* __restrict__ scores, int64_t S, int64_t W, int64_t col_
   long long total;
   const long long before = sah_block_excl_scan<long long>((long long)__popc(eq), scan, &total);
   if (w < W) {
-    const long long quota = st.need - (chunk_before[row * chunks + chunk] + before);
+    const long long lower = tie_offset != nullptr ? tie_offset[row] : 0;  // ties taken by lower ranks
+    const long long quota = st.need - (lower + chunk_before[row * chunks + chunk] + before);
     const int take = st.mode != 0 ? 0 : (quota > 32 ? 32 : (quota < 0 ? 0 : (int)quota));
     out_bits[row * W + w] = pw | gt | sah_lowest_bits(eq, take);
   }
@@ -443,35 +447,121 @@ extern "C" int64_t sah_topk_select_ws_bytes(int64_t rows, int64_t W) {
   return (int64_t)sel_ws_bytes(rows, (W + SEL_CHUNK_WORDS - 1) / SEL_CHUNK_WORDS);
 }
 
+// ---- the selection step by step (a multi-rank caller reduces the digit histogram between
+// sah_topk_sel_hist and sah_topk_sel_pick, and gathers the ranks' tie counts before the emit)
+extern "C" int64_t sah_topk_sel_hist_offset(int64_t rows, int64_t W) {
+  const int64_t chunks = (W + SEL_CHUNK_WORDS - 1) / SEL_CHUNK_WORDS;
+  return rows * chunks * 8 + rows * (int64_t)sizeof(SelState);
+}
+
+extern "C" int sah_topk_sel_begin(int64_t rows, int64_t W, int64_t k, void* workspace,
+                                  int64_t workspace_bytes, void* stream) {
+  SAH_REQUIRE(workspace != nullptr && ((uintptr_t)workspace % 16) == 0, "topk_sel_begin: bad workspace");
+  SAH_REQUIRE(rows > 0 && rows <= 65535 && W > 0, "topk_sel_begin: bad extents");
+  if (workspace_bytes < sah_topk_select_ws_bytes(rows, W))
+    return sah_fail(SAH_ERR_WORKSPACE, "topk_sel_begin: workspace of %lld bytes, need %lld",
+                    (long long)workspace_bytes, (long long)sah_topk_select_ws_bytes(rows, W));
+  const int64_t chunks = (W + SEL_CHUNK_WORDS - 1) / SEL_CHUNK_WORDS;
+  SelWorkspace o = sel_ws_carve(workspace, rows, chunks);
+  cudaStream_t st = (cudaStream_t)stream;
+  sel_init_kernel<<<(unsigned)sah_ceil_div(rows * 256, 256), 256, 0, st>>>(o.state, o.hist, rows, k);
+  SAH_LAUNCH_CHECK("topk_select init");
+  cudaMemsetAsync(o.chunk_before, 0, (size_t)rows * chunks * 8, st);
+  return SAH_OK;
+}
+
 template <typename T, int KEYBITS>
-static int sel_run(const T* scores, int64_t rows, int64_t S, int64_t W, int64_t col_begin, int64_t col_end,
-                   const uint32_t* prev_bits, int64_t k, uint32_t* out_bits, void* ws, cudaStream_t st) {
+static int sel_hist_step(const T* scores, int64_t rows, int64_t S, int64_t W, int64_t col_begin,
+                         int64_t col_end, const uint32_t* prev_bits, void* ws, int shift, cudaStream_t st) {
   const int64_t chunks = (W + SEL_CHUNK_WORDS - 1) / SEL_CHUNK_WORDS;
   SelWorkspace o = sel_ws_carve(ws, rows, chunks);
   const int vec = ((S * (int64_t)sizeof(T)) % 16 == 0 && ((uintptr_t)scores % 16) == 0) ? 1 : 0;
-  sel_init_kernel<<<(unsigned)sah_ceil_div(rows * 256, 256), 256, 0, st>>>(o.state, o.hist, rows, k);
-  SAH_LAUNCH_CHECK("topk_select init");
-  if (k > 0) {
-    cudaMemsetAsync(o.chunk_before, 0, (size_t)rows * chunks * 8, st);
-    dim3 grid((unsigned)chunks, (unsigned)rows);
-    for (int shift = KEYBITS - 8; shift >= 0; shift -= 8) {
-      const bool last = shift == 0;
-      sel_hist_kernel<T, KEYBITS><<<grid, SEL_THREADS, 0, st>>>(scores, S, W, col_begin, col_end, prev_bits,
-                                                                o.state, o.hist, last ? o.chunk_hist : nullptr,
-                                                                chunks, shift, vec);
-      SAH_LAUNCH_CHECK("topk_select hist");
-      sel_pick_kernel<<<(unsigned)rows, 256, 0, st>>>(o.state, o.hist, shift, shift == KEYBITS - 8 ? 1 : 0,
-                                                     last ? o.chunk_hist : nullptr, o.chunk_before, chunks);
-      SAH_LAUNCH_CHECK("topk_select pick");
-    }
-  } else {
-    cudaMemsetAsync(o.chunk_before, 0, (size_t)rows * chunks * 8, st);
-  }
   dim3 grid((unsigned)chunks, (unsigned)rows);
-  sel_emit_kernel<T, KEYBITS><<<grid, SEL_THREADS, 0, st>>>(scores, S, W, col_begin, col_end, prev_bits,
-                                                            o.state, o.chunk_before, chunks, vec, out_bits);
+  sel_hist_kernel<T, KEYBITS><<<grid, SEL_THREADS, 0, st>>>(scores, S, W, col_begin, col_end, prev_bits, o.state,
+                                                            o.hist, shift == 0 ? o.chunk_hist : nullptr, chunks,
+                                                            shift, vec);
+  SAH_LAUNCH_CHECK("topk_select hist");
+  return SAH_OK;
+}
+
+extern "C" int sah_topk_sel_hist(const void* scores, int dtype, int64_t rows, int64_t S, int64_t W,
+                                 int64_t col_begin, int64_t col_end, const uint32_t* prev_bits,
+                                 void* workspace, int shift, void* stream) {
+  SAH_REQUIRE(scores && prev_bits && workspace, "topk_sel_hist: null pointer");
+  SAH_REQUIRE(shift >= 0 && shift % 8 == 0, "topk_sel_hist: shift must be a multiple of 8");
+  if (col_begin < 0) col_begin = 0;
+  if (col_end > S) col_end = S;
+  if (dtype == SAH_BF16) {
+    SAH_REQUIRE(shift <= 8, "topk_sel_hist: bf16 keys have 16 bits");
+    return sel_hist_step<__nv_bfloat16, 16>((const __nv_bfloat16*)scores, rows, S, W, col_begin, col_end,
+                                            prev_bits, workspace, shift, (cudaStream_t)stream);
+  }
+  if (dtype == SAH_F32) {
+    SAH_REQUIRE(shift <= 24, "topk_sel_hist: fp32 keys have 32 bits");
+    return sel_hist_step<float, 32>((const float*)scores, rows, S, W, col_begin, col_end, prev_bits, workspace,
+                                    shift, (cudaStream_t)stream);
+  }
+  return sah_fail(SAH_ERR_INVALID, "topk_sel_hist: unknown dtype %d", dtype);
+}
+
+extern "C" int sah_topk_sel_pick(int64_t rows, int64_t W, void* workspace, int shift, int first,
+                                 int64_t* eq_total, void* stream) {
+  SAH_REQUIRE(workspace != nullptr && rows > 0, "topk_sel_pick: bad arguments");
+  const int64_t chunks = (W + SEL_CHUNK_WORDS - 1) / SEL_CHUNK_WORDS;
+  SelWorkspace o = sel_ws_carve(workspace, rows, chunks);
+  sel_pick_kernel<<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>(
+      o.state, o.hist, shift, first, shift == 0 ? o.chunk_hist : nullptr, o.chunk_before, chunks,
+      reinterpret_cast<long long*>(eq_total));
+  SAH_LAUNCH_CHECK("topk_select pick");
+  return SAH_OK;
+}
+
+template <typename T, int KEYBITS>
+static int sel_emit_step(const T* scores, int64_t rows, int64_t S, int64_t W, int64_t col_begin,
+                         int64_t col_end, const uint32_t* prev_bits, void* ws, const int64_t* tie_offset,
+                         uint32_t* out_bits, cudaStream_t st) {
+  const int64_t chunks = (W + SEL_CHUNK_WORDS - 1) / SEL_CHUNK_WORDS;
+  SelWorkspace o = sel_ws_carve(ws, rows, chunks);
+  const int vec = ((S * (int64_t)sizeof(T)) % 16 == 0 && ((uintptr_t)scores % 16) == 0) ? 1 : 0;
+  dim3 grid((unsigned)chunks, (unsigned)rows);
+  sel_emit_kernel<T, KEYBITS><<<grid, SEL_THREADS, 0, st>>>(scores, S, W, col_begin, col_end, prev_bits, o.state,
+                                                            o.chunk_before, chunks, vec,
+                                                            reinterpret_cast<const long long*>(tie_offset),
+                                                            out_bits);
   SAH_LAUNCH_CHECK("topk_select emit");
   return SAH_OK;
+}
+
+extern "C" int sah_topk_sel_emit(const void* scores, int dtype, int64_t rows, int64_t S, int64_t W,
+                                 int64_t col_begin, int64_t col_end, const uint32_t* prev_bits,
+                                 void* workspace, const int64_t* tie_offset, uint32_t* out_bits,
+                                 void* stream) {
+  SAH_REQUIRE(scores && prev_bits && workspace && out_bits, "topk_sel_emit: null pointer");
+  if (col_begin < 0) col_begin = 0;
+  if (col_end > S) col_end = S;
+  if (dtype == SAH_BF16)
+    return sel_emit_step<__nv_bfloat16, 16>((const __nv_bfloat16*)scores, rows, S, W, col_begin, col_end,
+                                            prev_bits, workspace, tie_offset, out_bits, (cudaStream_t)stream);
+  if (dtype == SAH_F32)
+    return sel_emit_step<float, 32>((const float*)scores, rows, S, W, col_begin, col_end, prev_bits, workspace,
+                                    tie_offset, out_bits, (cudaStream_t)stream);
+  return sah_fail(SAH_ERR_INVALID, "topk_sel_emit: unknown dtype %d", dtype);
+}
+
+template <typename T, int KEYBITS>
+static int sel_run(const T* scores, int64_t rows, int64_t S, int64_t W, int64_t col_begin, int64_t col_end,
+                   const uint32_t* prev_bits, int64_t k, uint32_t* out_bits, void* ws, cudaStream_t st) {
+  int rc = sah_topk_sel_begin(rows, W, k, ws, sah_topk_select_ws_bytes(rows, W), st);
+  if (rc != SAH_OK) return rc;
+  if (k > 0) {
+    for (int shift = KEYBITS - 8; shift >= 0; shift -= 8) {
+      rc = sel_hist_step<T, KEYBITS>(scores, rows, S, W, col_begin, col_end, prev_bits, ws, shift, st);
+      if (rc != SAH_OK) return rc;
+      rc = sah_topk_sel_pick(rows, W, ws, shift, shift == KEYBITS - 8 ? 1 : 0, nullptr, st);
+      if (rc != SAH_OK) return rc;
+    }
+  }
+  return sel_emit_step<T, KEYBITS>(scores, rows, S, W, col_begin, col_end, prev_bits, ws, nullptr, out_bits, st);
 }
 
 extern "C" int sah_topk_select_ws(const void* scores, int dtype, int64_t rows, int64_t S, int64_t W,

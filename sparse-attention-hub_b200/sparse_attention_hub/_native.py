@@ -76,6 +76,11 @@ _SIGNATURES = {
                       _L, _P, _P],
     "sah_topk_select": [_P, _I, _L, _L, _L, _L, _L, _P, _L, _P, _P],
     "sah_topk_select_ws_bytes": [_L, _L],  # returns int64
+    "sah_topk_sel_hist_offset": [_L, _L],  # returns int64
+    "sah_topk_sel_begin": [_L, _L, _L, _P, _L, _P],
+    "sah_topk_sel_hist": [_P, _I, _L, _L, _L, _L, _L, _P, _P, _I, _P],
+    "sah_topk_sel_pick": [_L, _L, _P, _I, _I, _P, _P],
+    "sah_topk_sel_emit": [_P, _I, _L, _L, _L, _L, _L, _P, _P, _P, _P, _P],
     "sah_topk_select_ws": [_P, _I, _L, _L, _L, _L, _L, _P, _L, _P, _P, _L, _P],
     "sah_attn_query_sizes": [_I, _I, _I, _I, _L, _I, _I, _I, POINTER(AttnSizes)],
     "sah_attn_plan": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _L, _L, POINTER(AttnSizes), _P, _P,
@@ -143,6 +148,7 @@ def load() -> ctypes.CDLL:
         fn.restype = c_int
     lib.sah_topk_select_ws_bytes.restype = c_int64
     lib.sah_pq_scores_ws_bytes.restype = c_int64
+    lib.sah_topk_sel_hist_offset.restype = c_int64
     lib.sah_hash_topk_ws_bytes.restype = c_int64
     lib.sah_version.restype = c_char_p
     lib.sah_last_error.restype = c_char_p

@@ -90,6 +90,52 @@ def topk_select(scores: torch.Tensor, previous_mask: Mask, k: int, col_begin: in
     return dst
 
 
+def topk_select_sharded(scores: torch.Tensor, previous_mask: Mask, k: int, comm, col_begin: int = 0,
+                        col_end: Optional[int] = None) -> NativeBits:
+    """`topk_select` when each row's keys are spread over the ranks of `comm` (contiguous ranges
+    in rank order, `scores` holding this rank's columns): per digit of the radix select the
+    ranks sum their 256-bin histograms, so all of them fix the same threshold; the count of
+    keys equal to it is gathered and lower ranks are served first, which keeps the
+    lowest-column tie rule.  `k` counts keys of the whole row.  Same result as the
+    single-device selection, bit for bit."""
+    _native.require_cuda(scores, "scores")
+    lib = _native.load()
+    S = scores.shape[-1]
+    rows = _rows(scores.shape)
+    if rows > 65535:
+        raise NotImplementedError("sequence-sharded top-k handles at most 65535 mask rows per call")
+    prev = previous_mask.native_bits()
+    dst = NativeBits(torch.empty_like(prev.bits), rows, S)
+    sc = scores.contiguous()
+    dev = sc.device
+    st = _native.stream_of(dev)
+    code = _native.dtype_code(sc.dtype)
+    end = S if col_end is None else col_end
+    words = prev.words
+    nbytes = int(lib.sah_topk_select_ws_bytes(rows, words))
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    off = int(lib.sah_topk_sel_hist_offset(rows, words))
+    hist = ws[off:off + rows * 1024].view(torch.int32)  # the digit histogram, summed in place
+    _native.check(lib.sah_topk_sel_begin(rows, words, k, ws.data_ptr(), nbytes, st), "sah_topk_sel_begin")
+    eq_total = torch.zeros(rows, dtype=torch.int64, device=dev)
+    shifts = (8, 0) if sc.dtype == torch.bfloat16 else (24, 16, 8, 0)
+    if k > 0:
+        for shift in shifts:
+            _native.check(lib.sah_topk_sel_hist(sc.data_ptr(), code, rows, S, words, col_begin, end,
+                                                prev.bits.data_ptr(), ws.data_ptr(), shift, st),
+                          "sah_topk_sel_hist")
+            comm.all_reduce_sum_(hist)
+            _native.check(lib.sah_topk_sel_pick(rows, words, ws.data_ptr(), shift, int(shift == shifts[0]),
+                                                eq_total.data_ptr() if shift == 0 else None, st),
+                          "sah_topk_sel_pick")
+    gathered = comm.all_gather(eq_total)  # [world, rows]
+    tie_offset = gathered[: comm.rank].sum(dim=0) if comm.rank > 0 else torch.zeros_like(eq_total)
+    _native.check(lib.sah_topk_sel_emit(sc.data_ptr(), code, rows, S, words, col_begin, end,
+                                        prev.bits.data_ptr(), ws.data_ptr(), tie_offset.data_ptr(),
+                                        dst.bits.data_ptr(), st), "sah_topk_sel_emit")
+    return dst
+
+
 def qk_scores(queries: torch.Tensor, keys: torch.Tensor,
               attention_mask: Optional[torch.Tensor]) -> torch.Tensor:
     """Unscaled q.k in the input dtype (+ additive bias), `[B, Hq, Sq, S]`."""

@@ -29,7 +29,9 @@ class DecodeStepGraph:
     def __init__(self, attention, queries: torch.Tensor, keys: torch.Tensor, values: torch.Tensor,
                  attention_mask: Optional[torch.Tensor], scaling: float,
                  sparse_meta_data: Dict[Any, Any], layer_idx: int = 0, warmup: int = 2,
-                 before_each_call: Optional[Callable[[], None]] = None, **kwargs: Any) -> None:
+                 before_each_call: Optional[Callable[[], None]] = None,
+                 host_query: Optional[torch.Tensor] = None, host_inputs=(),
+                 host_output: Optional[torch.Tensor] = None, **kwargs: Any) -> None:
         if not queries.is_cuda:
             raise RuntimeError("DecodeStepGraph needs CUDA tensors")
         self.attention = attention
@@ -40,13 +42,27 @@ class DecodeStepGraph:
         self.meta = sparse_meta_data
         self.kwargs = dict(kwargs, layer_idx=layer_idx)
         self._before = before_each_call
+        # Optional host side of the step, captured with it: the query is read from a pinned
+        # host tensor, `host_inputs` = [(device view, pinned host tensor), ...] are copied in
+        # first (e.g. the appended K/V rows), and the output is copied to a pinned host tensor.
+        # The caller rewrites the pinned tensors in place between replays.
+        self.host_query, self.host_inputs, self.host_output = host_query, list(host_inputs), host_output
+        for t in [host_query, host_output] + [h for _, h in self.host_inputs]:
+            if t is not None and not t.is_pinned():
+                raise RuntimeError("host tensors of a captured step must be pinned")
 
         def call() -> torch.Tensor:
             if self._before is not None:
                 self._before()
+            if self.host_query is not None:
+                self.queries.copy_(self.host_query, non_blocking=True)
+            for dst, src in self.host_inputs:
+                dst.copy_(src, non_blocking=True)
             out, _ = self.attention.custom_attention(
                 None, self.queries, self.keys, self.values, self.attention_mask, self.scaling, 0.0,
                 sparse_meta_data=self.meta, **self.kwargs)
+            if self.host_output is not None:
+                self.host_output.copy_(out, non_blocking=True)
             return out
 
         # Warm up on a side stream: fills the workspaces, tables and signature caches

@@ -97,7 +97,7 @@ class ResearchMasker(ABC):
         if kwargs.get("sequence_shard") is not None:
             raise NotImplementedError(
                 f"{type(self).__name__} does not run on a sequence shard; "
-                "Sink, Local, HashAttention top-k and MagicPig do")
+                "Sink, Local, OracleTopK, HashAttention top-k and MagicPig do")
 
     def _calculate_effective_size(self, size_param: Union[float, int], seq_len_keys: int) -> int:
         """A float is a fraction of the key length (truncated), an int is a count."""

@@ -39,13 +39,22 @@ class OracleTopK(TopKMasker):
     def add_mask(self, keys, queries, values, attention_mask, scaling, dropout,
                  sparse_meta_data: Dict[Any, Any], previous_mask: Mask,
                  **kwargs: Dict[str, Any]) -> Mask:
-        self._refuse_sequence_shard(kwargs)
         if previous_mask.is_full_mask():
             return previous_mask
         dims = self._extract_tensor_dimensions(keys, queries)
-        heavy = self._calculate_effective_heavy_size(dims.seq_len_keys)
-        if self._should_use_full_attention(dims, heavy):
+        # On a sequence shard the keys at hand are one rank's range: k and the full-attention
+        # rule follow the whole sequence, and the top-k is global (exact, same tie rule).
+        shard = kwargs.get("sequence_shard")
+        total = shard.total if shard is not None else dims.seq_len_keys
+        heavy = self._calculate_effective_heavy_size(total)
+        if total <= heavy:
             return self._create_full_mask(dims, previous_mask.dtype, previous_mask.device)
+        if shard is not None:
+            if _native_ops.unit_weight_bits(previous_mask) is None:
+                raise NotImplementedError("OracleTopK on a sequence shard needs a unit-weight previous mask")
+            scores = self._compute_raw_attention_scores(keys, queries, attention_mask)
+            merged = _native_ops.topk_select_sharded(scores, previous_mask, heavy, shard.comm)
+            return Mask._from_native(previous_mask.shape, previous_mask.dtype, merged)
         return self.get_updated_mask(dims, heavy, keys, queries, attention_mask, previous_mask,
                                      call_cache=kwargs.get("_sah_call_cache"))
 

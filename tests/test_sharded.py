@@ -34,6 +34,13 @@ def _hash_wl(S=1000, seed=72):
                                         heavy=0.05, hidden=32, layers=2)
 
 
+def _oracle_wl(dtype="bf16", S=1000, seed=74):
+    wl = workloads.oracle_topk(seed=seed, dtype=dtype, B=2, Hq=4, Hkv=2, S=S, D=64, sink=5, window=40, heavy=0.05)
+    # duplicate a block of keys so that equal scores straddle the shard boundaries
+    wl.k[:, :, 300:700] = wl.k[:, :, 100:500]
+    return wl
+
+
 def _oracle_meta(wl):
     last = wl.stack[-1]
     return {"lsh_projection": last[1]["projection"]} if last[0] == "magicpig" else {}
@@ -92,7 +99,7 @@ def _gloo_rank(rank: int, world: int, port: int, results) -> None:
         comm = o_sharded.TorchComm()
         ok = True
         for wl, dtype in ((_magicpig_wl("bf16"), "bf16"), (_magicpig_wl("f32", S=700, Sq=2), "f32"),
-                          (_hash_wl(), "bf16")):
+                          (_hash_wl(), "bf16"), (_oracle_wl("bf16"), "bf16")):
             S = wl.k.shape[2]
             b, e = o_sharded.plan_shards(S, world)[rank]
             ref_mask, ref_out, _ = stacks.run_stack(wl.stack, wl.q, wl.k, wl.v, wl.scaling, dtype,
@@ -179,12 +186,13 @@ def _proj_meta(wl):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("case", ["magicpig_bf16", "magicpig_f32_sq2", "hash_bf16"])
+@pytest.mark.parametrize("case", ["magicpig_bf16", "magicpig_f32_sq2", "hash_bf16", "oracle_bf16", "oracle_f32"])
 @pytest.mark.parametrize("world", [2, 4])
 def test_gpu_sharded_equals_unsharded(case, world):
     wl = {"magicpig_bf16": lambda: _magicpig_wl("bf16"),
           "magicpig_f32_sq2": lambda: _magicpig_wl("f32", S=700, Sq=2),
-          "hash_bf16": _hash_wl}[case]()
+          "hash_bf16": _hash_wl, "oracle_bf16": lambda: _oracle_wl("bf16"),
+          "oracle_f32": lambda: _oracle_wl("f32", S=900)}[case]()
     dtype = wl.dtype
     full_mask, full_out = _native_unsharded(wl, _proj_meta(wl)("cuda:0"))
     plan, results = _native_sharded(wl, world, _proj_meta(wl))
@@ -203,6 +211,6 @@ def test_gpu_sharded_equals_unsharded(case, world):
 
 @pytest.mark.gpu
 def test_gpu_unshardable_masker_refuses_a_shard():
-    wl = workloads.oracle_topk(seed=73, dtype="bf16", B=1, Hq=4, Hkv=2, S=512, D=64, sink=4, window=8)
+    wl = workloads.oracle_adaptive(seed=73, dtype="bf16", B=1, Hq=4, Hkv=2, S=512, D=64, sink=4, window=8)
     with pytest.raises(NotImplementedError):
         _native_sharded(wl, 2, lambda dev: {})
