@@ -115,14 +115,19 @@ attn_plan_fused_kernel(const uint32_t* __restrict__ bits, const T* __restrict__ 
   const int64_t w = threadIdx.x;
   uint32_t words[RMAX];
   int64_t rows[RMAX];
+  int64_t dbase[RMAX];  // CSR position of the first entry of this row's word
   uint32_t u = 0u;
 #pragma unroll
   for (int r = 0; r < RMAX; ++r) {
     words[r] = 0u;
     rows[r] = -1;
+    dbase[r] = 0;
     if (r < p.R && w < p.W) {
       rows[r] = plan_member_row(p, g, r);
-      if (rows[r] >= 0) words[r] = bits[rows[r] * p.W + w];
+      if (rows[r] >= 0) {
+        words[r] = bits[rows[r] * p.W + w];
+        if (uw != nullptr && words[r]) dbase[r] = ptr[rows[r]] + wpre[rows[r] * p.W + w];
+      }
     }
     u |= words[r];
   }
@@ -144,8 +149,7 @@ attn_plan_fused_kernel(const uint32_t* __restrict__ bits, const T* __restrict__ 
         if (r < p.R) {
           float wv = 0.f;
           if ((memb >> r) & 1u) {
-            int64_t dp = ptr[rows[r]] + wpre[rows[r] * p.W + w] +
-                         __popc(words[r] & ((1u << b) - 1u));
+            const int64_t dp = dbase[r] + __popc(words[r] & ((1u << b) - 1u));
             wv = sah_inv_weight<T>(sah_to_float<T>(data[dp]));
           }
           uw[pos * p.R + r] = wv;
@@ -177,14 +181,19 @@ __global__ void attn_plan_emit_kernel(const uint32_t* __restrict__ bits, const T
   const int64_t w = c * PLAN_CHUNK_WORDS + lane;
   uint32_t words[AT_MAXR];
   int64_t rows[AT_MAXR];
+  int64_t dbase[AT_MAXR];  // CSR position of the first entry of this row's word
   uint32_t u = 0u;
 #pragma unroll
   for (int r = 0; r < AT_MAXR; ++r) {
     words[r] = 0u;
     rows[r] = -1;
+    dbase[r] = 0;
     if (r < p.R && w < p.W) {
       rows[r] = plan_member_row(p, g, r);
-      if (rows[r] >= 0) words[r] = bits[rows[r] * p.W + w];
+      if (rows[r] >= 0) {
+        words[r] = bits[rows[r] * p.W + w];
+        if (uw != nullptr && words[r]) dbase[r] = ptr[rows[r]] + wpre[rows[r] * p.W + w];
+      }
     }
     u |= words[r];
   }
@@ -211,8 +220,7 @@ __global__ void attn_plan_emit_kernel(const uint32_t* __restrict__ bits, const T
         if (r < p.R) {
           float wv = 0.f;
           if ((memb >> r) & 1u) {
-            int64_t dp = ptr[rows[r]] + wpre[rows[r] * p.W + w] +
-                         __popc(words[r] & ((1u << b) - 1u));
+            const int64_t dp = dbase[r] + __popc(words[r] & ((1u << b) - 1u));
             wv = sah_inv_weight<T>(sah_to_float<T>(data[dp]));
           }
           uw[pos * p.R + r] = wv;

@@ -67,7 +67,7 @@ __device__ __forceinline__ uint32_t sah_float_key(float f) {
 template <typename T>
 __device__ __forceinline__ float sah_inv_weight(float m) {
   float s = sah_round_to<T>(__fadd_rn(m, 1e-6f));
-  return sah_round_to<T>(__fdiv_rn(1.0f, s));
+  return sah_round_to<T>(__frcp_rn(s));  // the correctly rounded reciprocal, as 1.0f / s is
 }
 
 // Unpack 8 consecutive elements (16 B for bf16, 32 B for fp32) to floats.
