@@ -175,8 +175,7 @@ __device__ __forceinline__ void he_cp_async16(void* smem_dst, const void* gmem_s
 template <typename T>
 __global__ void __launch_bounds__(HE_MAXD)
 hash_encode_small_kernel(HashEncodeArgs p) {
-  extern __shared__ __align__(16) unsigned char hes_smem[];  // one layer's weights of head h
-  T* w_sm = reinterpret_cast<T*>(hes_smem);
+  extern __shared__ __align__(16) unsigned char hes_smem[];  // every layer's weights of head h
   __shared__ float xa[HE_MAXD];
   __shared__ float xb[HE_MAXD];
   const int64_t n = p.n_begin + blockIdx.x;
@@ -188,23 +187,35 @@ hash_encode_small_kernel(HashEncodeArgs p) {
   float* a_in = xa;
   float* a_out = xb;
   unsigned int code = 0u;
+  // Every layer's matrix is requested up front, one cp.async group per layer, each into its
+  // own region: the step is latency bound, so later layers load while earlier ones compute.
+  const int layer_bytes = HE_MAXD * HE_MAXD * (int)sizeof(T);
   for (int l = 0; l < p.n_layers; ++l) {
     const int din = p.dims[l], dout = p.dims[l + 1];
-    const bool last = (l == p.n_layers - 1);
-    __syncthreads();  // previous layer finished with w_sm and wrote a_in
-    // the whole layer matrix in flight at once: the step is latency bound
     const unsigned char* src = reinterpret_cast<const unsigned char*>(
         reinterpret_cast<const T*>(p.weights[l]) + (int64_t)h * din * dout);
     const int n16 = din * dout * (int)sizeof(T) / 16;
-    for (int i = threadIdx.x; i < n16; i += HE_MAXD) he_cp_async16(hes_smem + i * 16, src + i * 16);
+    for (int i = threadIdx.x; i < n16; i += HE_MAXD)
+      he_cp_async16(hes_smem + l * layer_bytes + i * 16, src + i * 16);
     asm volatile("cp.async.commit_group;\n" ::);
-    asm volatile("cp.async.wait_group 0;\n" ::);
-    __syncthreads();
+  }
+  for (int l = 0; l < p.n_layers; ++l) {
+    const int din = p.dims[l], dout = p.dims[l + 1];
+    const bool last = (l == p.n_layers - 1);
+    const T* w_l = reinterpret_cast<const T*>(hes_smem + l * layer_bytes);
+    // groups complete in order: layer l is there once at most n_layers - 1 - l are pending
+    switch (p.n_layers - 1 - l) {
+      case 0: asm volatile("cp.async.wait_group 0;\n" ::); break;
+      case 1: asm volatile("cp.async.wait_group 1;\n" ::); break;
+      case 2: asm volatile("cp.async.wait_group 2;\n" ::); break;
+      default: asm volatile("cp.async.wait_group 3;\n" ::); break;
+    }
+    __syncthreads();  // everybody's copies of layer l have landed, and a_in is written
     float v = 0.f;
     if (e < dout) {
       float acc = 0.f;
 #pragma unroll 8
-      for (int d = 0; d < din; ++d) acc = fmaf(a_in[d], sah_to_float<T>(w_sm[d * dout + e]), acc);
+      for (int d = 0; d < din; ++d) acc = fmaf(a_in[d], sah_to_float<T>(w_l[d * dout + e]), acc);
       v = sah_round_to<T>(acc);
       v = sah_round_to<T>(__fadd_rn(
           v, sah_to_float<T>(reinterpret_cast<const T*>(p.bias[l])[(int64_t)h * dout + e])));
@@ -260,12 +271,13 @@ extern "C" int sah_hash_encode(const void* x, int dtype, int64_t xs_b, int64_t x
   p.act = act; p.act_table = act_table; p.codes = codes;
 
   cudaStream_t st = (cudaStream_t)stream;
-  if (n_end - n_begin <= HE_SMALL_MAX) {
+  const size_t small_bytes = (size_t)n_layers * HE_MAXD * HE_MAXD * (dtype == SAH_BF16 ? 2 : 4);
+  if (n_end - n_begin <= HE_SMALL_MAX && small_bytes <= 200 * 1024) {
     // decode-time shapes (queries, appended keys): one CTA per vector
     sah_prof_begin(SAH_PROF_HASH_ENCODE, st);
     dim3 sgrid((unsigned)(n_end - n_begin), (unsigned)H_out, (unsigned)B);
     SAH_DISPATCH_DTYPE(dtype, T, {
-      const int wbytes = HE_MAXD * HE_MAXD * (int)sizeof(T);
+      const int wbytes = n_layers * HE_MAXD * HE_MAXD * (int)sizeof(T);
       if (wbytes > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(hash_encode_small_kernel<T>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, wbytes);
