@@ -20,6 +20,29 @@
 #define QK_STAGES 1
 #define QK_TILES_PER_CTA 1
 
+// Two of those at once: sm_100 issues a pair of fp32 operations per instruction
+// (fma.rn.f32x2), each lane rounding exactly as the scalar fma; used for bf16 inputs, whose
+// products are exact in fp32.
+template <typename T>
+__device__ __forceinline__ void qk_mac2(float& c0, float& c1, float a0, float a1, float b0, float b1);
+template <>
+__device__ __forceinline__ void qk_mac2<__nv_bfloat16>(float& c0, float& c1, float a0, float a1,
+                                                       float b0, float b1) {
+  unsigned long long a, b, c;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(a0), "f"(a1));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(b) : "f"(b0), "f"(b1));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(c) : "f"(c0), "f"(c1));
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(c) : "l"(a), "l"(b));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(c0), "=f"(c1) : "l"(c));
+}
+template <>
+__device__ __forceinline__ void qk_mac2<float>(float& c0, float& c1, float a0, float a1, float b0,
+                                               float b1) {
+  // fp32 inputs: a rounded product, then a rounded sum (no fma), one lane at a time
+  c0 = __fadd_rn(c0, __fmul_rn(a0, b0));
+  c1 = __fadd_rn(c1, __fmul_rn(a1, b1));
+}
+
 template <typename T>
 __device__ __forceinline__ float qk_mac(float a, float b, float c);
 template <>
@@ -106,14 +129,10 @@ qk_scores_kernel(const T* __restrict__ q, const T* __restrict__ k, int64_t qs_b,
             if (FULL4 || r0 + r < R) {
               const float4 qa = *reinterpret_cast<const float4*>(q_sm + (r0 + r) * D + t * 8);
               const float4 qb = *reinterpret_cast<const float4*>(q_sm + (r0 + r) * D + t * 8 + 4);
-              acc[r][0] = qk_mac<T>(qa.x, kf[0], acc[r][0]);
-              acc[r][1] = qk_mac<T>(qa.y, kf[1], acc[r][1]);
-              acc[r][2] = qk_mac<T>(qa.z, kf[2], acc[r][2]);
-              acc[r][3] = qk_mac<T>(qa.w, kf[3], acc[r][3]);
-              acc[r][4] = qk_mac<T>(qb.x, kf[4], acc[r][4]);
-              acc[r][5] = qk_mac<T>(qb.y, kf[5], acc[r][5]);
-              acc[r][6] = qk_mac<T>(qb.z, kf[6], acc[r][6]);
-              acc[r][7] = qk_mac<T>(qb.w, kf[7], acc[r][7]);
+              qk_mac2<T>(acc[r][0], acc[r][1], qa.x, qa.y, kf[0], kf[1]);
+              qk_mac2<T>(acc[r][2], acc[r][3], qa.z, qa.w, kf[2], kf[3]);
+              qk_mac2<T>(acc[r][4], acc[r][5], qb.x, qb.y, kf[4], kf[5]);
+              qk_mac2<T>(acc[r][6], acc[r][7], qb.z, qb.w, kf[6], kf[7]);
             }
           }
         }
