@@ -756,9 +756,18 @@ def run_long_native(args) -> None:
         }
         if base is not None:
             line["cpu_baseline"] = {k_: base[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
+        import gc
+
         import torch.distributed as dist
+
+        # graphs that captured collectives must be gone before their communicator is
+        step = eager_step
+        graph = e2e_graph = None  # noqa: F841
+        gc.collect()
+        torch.cuda.synchronize()
+        dist.barrier()
         dist.destroy_process_group()
 
 

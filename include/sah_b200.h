@@ -281,25 +281,31 @@ int sah_sample_scatter(const int64_t* sptr, int64_t rows, const int64_t* pool, u
  * column order -- each worked on by its own CTA.
  *   sah_hash_hist        hist[chunk][row][33]: candidates (not in prev_bits) per score
  *                        0..32 in each of this rank's chunks (chunk c covers bitmap
- *                        words [c*ceil(W/chunks), (c+1)*ceil(W/chunks)));
+ *                        words [c*cw, (c+1)*cw), cw = ceil(W/chunks) rounded up to 32);
  *   (a multi-rank caller gathers all ranks' histograms: hist_all [world][chunks][rows][33])
  *   sah_hash_shard_plan  thr[chunk][row]: scores above it are taken whole (-1 every
  *                        candidate, 64 none); need[chunk][row]: ties at thr the part
  *                        takes, lower parts (lower columns) being served first;
  *   sah_hash_emit        out_bits = prev | {score > thr} | first need ties, per chunk.
  * The union over parts equals the selection of sah_hash_topk on the whole row.
- * sah_hash_topk_ws runs the three on one device (world = 1) with a chunk count that
- * fills the GPU for any row count; workspace: 16-byte aligned device memory of
- * sah_hash_topk_ws_bytes(rows, W, sm_count) bytes (SAH_ERR_WORKSPACE when smaller). */
+ * `scores` (optional, NULL to do without): 16-byte aligned device scratch of
+ * sah_hash_scores_bytes(rows, W) bytes in which sah_hash_hist leaves one byte per key (its
+ * score) and from which sah_hash_emit, given the same pointer and chunk count, reads them
+ * instead of re-reading the four-byte codes.
+ * sah_hash_topk_ws runs histogram and emit on one device (world = 1; every emit CTA plans
+ * for itself) with a chunk count that fills the GPU for any row count; workspace: 16-byte
+ * aligned device memory of sah_hash_topk_ws_bytes(rows, W, sm_count) bytes
+ * (SAH_ERR_WORKSPACE when smaller). */
+int64_t sah_hash_scores_bytes(int64_t rows, int64_t W);
 int sah_hash_hist(const uint32_t* kcodes, int64_t kc_stride, const uint32_t* qcodes, int nbits,
                   int B, int Hq, int Sq, int64_t S, int64_t W, int chunks,
-                  const uint32_t* prev_bits, int32_t* hist, void* stream);
+                  const uint32_t* prev_bits, int32_t* hist, void* scores, void* stream);
 int sah_hash_shard_plan(const int32_t* hist_all, int world, int rank, int chunks, int64_t rows,
                         int64_t k, int32_t* thr, int64_t* need, void* stream);
 int sah_hash_emit(const uint32_t* kcodes, int64_t kc_stride, const uint32_t* qcodes, int nbits,
                   int B, int Hq, int Sq, int64_t S, int64_t W, int chunks,
                   const uint32_t* prev_bits, const int32_t* thr, const int64_t* need,
-                  uint32_t* out_bits, void* stream);
+                  const void* scores, uint32_t* out_bits, void* stream);
 int64_t sah_hash_topk_ws_bytes(int64_t rows, int64_t W, int sm_count);
 int sah_hash_topk_ws(const uint32_t* kcodes, int64_t kc_stride, const uint32_t* qcodes, int nbits,
                      int B, int Hq, int Sq, int64_t S, int64_t W, const uint32_t* prev_bits,

@@ -199,7 +199,23 @@ hash_encode_small_kernel(HashEncodeArgs p) {
       he_cp_async16(hes_smem + l * layer_bytes + i * 16, src + i * 16);
     asm volatile("cp.async.commit_group;\n" ::);
   }
-  for (int l = 0; l < p.n_layers; ++l) {
+  // The step is a chain of dependent latencies; whatever does not depend on the activations is
+  // asked for now: every layer's bias, and (bf16) the activation table pulled towards L2, one
+  // 128-byte line per thread and a different eighth of the table per head.
+  float bias_r[4];
+#pragma unroll
+  for (int l = 0; l < 4; ++l)
+    bias_r[l] = (l < p.n_layers && e < p.dims[l + 1])
+                    ? sah_to_float<T>(reinterpret_cast<const T*>(p.bias[l])[(int64_t)h * p.dims[l + 1] + e])
+                    : 0.f;
+  if (sizeof(T) == 2 && p.act_table != nullptr && p.n_layers > 1) {
+    const unsigned char* line = reinterpret_cast<const unsigned char*>(p.act_table) +
+                                ((size_t)((h & 7) * HE_MAXD + e) << 7);
+    asm volatile("prefetch.global.L2 [%0];\n" ::"l"(line));
+  }
+#pragma unroll
+  for (int l = 0; l < 4; ++l) {
+    if (l >= p.n_layers) break;
     const int din = p.dims[l], dout = p.dims[l + 1];
     const bool last = (l == p.n_layers - 1);
     const T* w_l = reinterpret_cast<const T*>(hes_smem + l * layer_bytes);
@@ -217,8 +233,7 @@ hash_encode_small_kernel(HashEncodeArgs p) {
 #pragma unroll 8
       for (int d = 0; d < din; ++d) acc = fmaf(a_in[d], sah_to_float<T>(w_l[d * dout + e]), acc);
       v = sah_round_to<T>(acc);
-      v = sah_round_to<T>(__fadd_rn(
-          v, sah_to_float<T>(reinterpret_cast<const T*>(p.bias[l])[(int64_t)h * dout + e])));
+      v = sah_round_to<T>(__fadd_rn(v, bias_r[l]));
       if (!last) a_out[e] = he_activate<T>(v, p.act, p.act_table);
     }
     if (last && threadIdx.x < 32) code = __ballot_sync(0xffffffffu, e < dout && v > 0.f);
@@ -505,16 +520,193 @@ hash_topk_fast_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
   }
 }
 
-// The same selection with 512 threads per row and the scores kept in registers between the two
-// passes: thread t owns bitmap words t, t + 512, ... (WPT of them), its 32 scores per word
-// packed as bytes, so pass 2 neither reloads the codes nor recounts bits, and byte-wise SIMD
-// compares produce the "above" and "equal" masks.  Two CTAs fit on an SM, so 256 rows make one
-// balanced wave on 148 SMs where 1024-thread CTAs made two.
-#define HT2_THREADS 512
+// ---------------------------------------------------------------------------------------
+// Warp tiles.  A warp takes 32 consecutive bitmap words (1024 keys, 4 KB of codes) with eight
+// coalesced 16-byte loads per lane: lane L, slot j holds keys 128 j + 4 L .. + 3 of the tile,
+// which are bits 4 (L % 8) .. + 3 of the tile's word 4 j + L / 8 ("load order").  Bitmap words
+// are owned one per lane (lane W owns word W of the tile, "owner order"); eight shuffles move a
+// set of per-key flags from load order to owner order.
+// ---------------------------------------------------------------------------------------
+// Per-lane private counters: cnt[distance][lane] bytes of one warp (33 rows).  No two lanes
+// share a counter, so the histogram needs no atomics; a lane may count 255 keys between flushes.
+#define HT_CNT_BYTES (33 * 32)
 
-__device__ __forceinline__ unsigned int ht_flags4(unsigned int w) {  // 4 byte flags -> 4 bits
-  return ((w & 0x01010101u) * 0x01020408u) >> 24;
+__device__ __forceinline__ void ht_count1(unsigned char* cnt_lane, unsigned int dist, unsigned int inc) {
+  unsigned char* c = cnt_lane + dist * 32;
+  *c = (unsigned char)(*c + inc);
 }
+
+// Hamming distances of a tile's keys to the query code, four per register (d4[8]); the score
+// of a key is nbits - distance.  With COUNT the keys whose flag in `vflags` (load order, bit
+// 4 j + i) is set are counted into the lane's private counters on the way.
+template <bool COUNT>
+__device__ __forceinline__ void ht_tile_dist(const uint32_t* __restrict__ kc, int64_t c0, int64_t S,
+                                             bool aligned, uint32_t qc, int lane, uint32_t* d4,
+                                             unsigned char* cnt_lane = nullptr, uint32_t vflags = 0u,
+                                             bool all_valid = false) {
+  uint4 v[8];
+  if (aligned && c0 + 1024 <= S) {
+    const uint4* p = reinterpret_cast<const uint4*>(kc + c0) + lane;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = p[j * 32];
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int64_t c = c0 + 128 * j + 4 * lane;
+      v[j].x = (c + 0 < S) ? kc[c + 0] : 0u;
+      v[j].y = (c + 1 < S) ? kc[c + 1] : 0u;
+      v[j].z = (c + 2 < S) ? kc[c + 2] : 0u;
+      v[j].w = (c + 3 < S) ? kc[c + 3] : 0u;
+    }
+  }
+  if (COUNT && all_valid) {   // warp-uniform: no key of the tile is masked out
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const unsigned int a = __popc(v[j].x ^ qc), b = __popc(v[j].y ^ qc);
+      const unsigned int c = __popc(v[j].z ^ qc), d = __popc(v[j].w ^ qc);
+      ht_count1(cnt_lane, a, 1u);
+      ht_count1(cnt_lane, b, 1u);
+      ht_count1(cnt_lane, c, 1u);
+      ht_count1(cnt_lane, d, 1u);
+      d4[j] = a | (b << 8) | (c << 16) | (d << 24);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const unsigned int a = __popc(v[j].x ^ qc), b = __popc(v[j].y ^ qc);
+      const unsigned int c = __popc(v[j].z ^ qc), d = __popc(v[j].w ^ qc);
+      if (COUNT) {
+        ht_count1(cnt_lane, a, (vflags >> (4 * j + 0)) & 1u);
+        ht_count1(cnt_lane, b, (vflags >> (4 * j + 1)) & 1u);
+        ht_count1(cnt_lane, c, (vflags >> (4 * j + 2)) & 1u);
+        ht_count1(cnt_lane, d, (vflags >> (4 * j + 3)) & 1u);
+      }
+      d4[j] = a | (b << 8) | (c << 16) | (d << 24);
+    }
+  }
+}
+
+// Loads and counts a tile: `valid` is the owner-order candidate word of this lane.
+__device__ __forceinline__ void ht_tile_dist_count(const uint32_t* __restrict__ kc, int64_t c0, int64_t S,
+                                                   bool aligned, uint32_t qc, int lane, uint32_t valid,
+                                                   unsigned char* cnt_lane, uint32_t* d4);
+
+// Owner-order word -> load order: bit 4 j + i is the flag of this lane's key i of slot j.
+__device__ __forceinline__ uint32_t ht_tile_scatter(uint32_t owner_word, int lane) {
+  uint32_t out = 0u;
+  const int sh = 4 * (lane & 7);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t wv = __shfl_sync(0xffffffffu, owner_word, 4 * j + (lane >> 3));
+    out |= ((wv >> sh) & 0xFu) << (4 * j);
+  }
+  return out;
+}
+
+// Load-order flags (bit 4 j + i) -> the owner-order word of this lane.
+__device__ __forceinline__ uint32_t ht_tile_gather(uint32_t flags, int lane) {
+  uint32_t out = 0u;
+  const int src0 = 8 * (lane & 3), sh = 4 * (lane >> 2);
+#pragma unroll
+  for (int p = 0; p < 8; ++p) {
+    const uint32_t v = __shfl_sync(0xffffffffu, flags, src0 + p);
+    out |= ((v >> sh) & 0xFu) << (4 * p);
+  }
+  return out;
+}
+
+// bit 7 of every byte -> 4 bits
+__device__ __forceinline__ unsigned int ht_flags4(unsigned int w) {
+  return (((w >> 7) & 0x01010101u) * 0x01020408u) >> 24;
+}
+
+// "above" and "equal" flags (load order) of a tile's packed distances against a score threshold
+// thr in -1..64: score > thr is distance < nbits - thr.  Distances are 0..32, so plain 32-bit
+// adds act on the four bytes at once: byte + (128 - t) stays below bit 7 exactly when
+// distance < t, and (byte ^ t) + 127 stays below it exactly when distance == t; no byte carries
+// into its neighbour.
+__device__ __forceinline__ void ht_tile_compare(const uint32_t* d4, int nbits, int thr, uint32_t* gt,
+                                                uint32_t* eq) {
+  int t = nbits - thr;                    // -32 .. 33
+  if (t < 0) t = 0;                       // nothing is closer than 0
+  const unsigned int add_lt = (unsigned int)(128 - t) * 0x01010101u;
+  const unsigned int t_eq = ((thr >= 0 && thr <= nbits) ? (unsigned int)(nbits - thr) : 127u) * 0x01010101u;
+  uint32_t g = 0u, e = 0u;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    g |= ht_flags4(~(d4[j] + add_lt)) << (4 * j);
+    e |= ht_flags4(~((d4[j] ^ t_eq) + 0x7f7f7f7fu)) << (4 * j);
+  }
+  *gt = g;
+  *eq = e;
+}
+
+__device__ __forceinline__ void ht_tile_dist_count(const uint32_t* __restrict__ kc, int64_t c0, int64_t S,
+                                                   bool aligned, uint32_t qc, int lane, uint32_t valid,
+                                                   unsigned char* cnt_lane, uint32_t* d4) {
+  const bool all_valid = __all_sync(0xffffffffu, valid == 0xffffffffu);
+  const uint32_t vflags = all_valid ? 0xffffffffu : ht_tile_scatter(valid, lane);
+  ht_tile_dist<true>(kc, c0, S, aligned, qc, lane, d4, cnt_lane, vflags, all_valid);
+}
+
+// Adds a warp's private counters into hist[33] (shared, u32, indexed by score = nbits -
+// distance) and clears them.
+__device__ __forceinline__ void ht_cnt_flush(unsigned char* cnt_warp, unsigned int* hist, int nbits, int lane) {
+  __syncwarp();
+  uint32_t* row = reinterpret_cast<uint32_t*>(cnt_warp + lane * 32);   // distance = lane
+  unsigned int s = 0u;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int ii = (i + (lane >> 2)) & 7;  // 32 lanes on 32 banks
+    s += __vsadu4(row[ii], 0u);
+    row[ii] = 0u;
+  }
+  if (s && lane <= nbits) atomicAdd(&hist[nbits - lane], s);
+  if (lane < 8) {
+    uint32_t* top = reinterpret_cast<uint32_t*>(cnt_warp + 32 * 32);     // distance 32
+    const unsigned int t = __vsadu4(top[lane], 0u);
+    top[lane] = 0u;
+    if (t && nbits == 32) atomicAdd(&hist[0], t);
+  }
+  __syncwarp();
+}
+
+// Threshold and ties from a histogram hist[33] held in shared memory; called by one full warp.
+__device__ __forceinline__ void ht_pick(const unsigned int* hist, long long k, int lane, int* thr_out,
+                                        long long* need_out) {
+  const unsigned int mine = hist[lane], top = hist[32];
+  unsigned int incl = mine;  // suffix sum over lanes: keys with bin >= lane (bins <= 31)
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    unsigned int n = __shfl_down_sync(0xffffffffu, incl, o);
+    if (lane + o < 32) incl += n;
+  }
+  const long long ge = (long long)incl + top;
+  const long long total = __shfl_sync(0xffffffffu, (long long)incl, 0) + top;
+  int thr;
+  long long need;
+  if (k <= 0) {
+    thr = 64; need = 0;                 // nothing qualifies
+  } else if (total <= k) {
+    thr = -1; need = 0;                 // every candidate qualifies
+  } else if ((long long)top >= k) {
+    thr = 32; need = k;
+  } else {
+    const unsigned int ok = __ballot_sync(0xffffffffu, ge >= k);
+    thr = 31 - __clz(ok);               // highest bin whose ">=" count reaches k
+    const long long ge_thr = __shfl_sync(0xffffffffu, ge, thr);
+    const long long mine_thr = __shfl_sync(0xffffffffu, (long long)mine, thr);
+    need = k - (ge_thr - mine_thr);     // ties to take at the threshold
+  }
+  *thr_out = thr;
+  *need_out = need;
+}
+
+// The counting select with 512 threads per row and the scores kept in registers between the
+// two passes (rows of up to 512 * WPT words): warp v takes tiles v, v + 16, ...; pass 2 neither
+// reloads the codes nor recounts bits, byte-wise SIMD compares give the "above" and "equal"
+// flags.  Two CTAs fit on an SM, so 256 rows make one balanced wave on 148 SMs.
+#define HT2_THREADS 512
 
 template <int WPT>
 __global__ void __launch_bounds__(HT2_THREADS, 2)
@@ -522,8 +714,9 @@ hash_topk_reg_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
                      const uint32_t* __restrict__ qcodes, int nbits, int Sq, int64_t S, int64_t W,
                      const uint32_t* __restrict__ prev_bits, int64_t k,
                      uint32_t* __restrict__ out_bits) {
-  __shared__ unsigned int hist[HT2_THREADS / 32][HT_BINS];
-  __shared__ long long scan[33];
+  __shared__ __align__(16) unsigned char cnt[HT2_THREADS / 32][HT_CNT_BYTES];
+  __shared__ unsigned int hist[HT_BINS];
+  __shared__ int scan[33];
   __shared__ int thr_sm;
   __shared__ long long need_sm;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -533,66 +726,38 @@ hash_topk_reg_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
   const uint32_t* prev_row = prev_bits + row * W;
   uint32_t* out_row = out_bits + row * W;
   const bool aligned = ((reinterpret_cast<uintptr_t>(kc) & 15) == 0);
-  for (int i = tid; i < (HT2_THREADS / 32) * HT_BINS; i += HT2_THREADS) (&hist[0][0])[i] = 0u;
+  for (int i = tid; i < (HT2_THREADS / 32) * HT_CNT_BYTES / 4; i += HT2_THREADS)
+    reinterpret_cast<uint32_t*>(&cnt[0][0])[i] = 0u;
+  if (tid < HT_BINS) hist[tid] = 0u;
   __syncthreads();
 
-  uint32_t sc4[WPT][8];   // scores, four per register
+  uint32_t s4[WPT][8];   // packed distances of the tiles this warp owns
   uint32_t validm[WPT], prevw[WPT];
 #pragma unroll
   for (int j = 0; j < WPT; ++j) {
-    const int64_t w = tid + (int64_t)j * HT2_THREADS;
-    validm[j] = 0u;
-    prevw[j] = 0u;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) sc4[j][i] = 0u;
+    const int64_t w = tid + (int64_t)j * HT2_THREADS;   // the word this lane owns
+    const int64_t c0 = (w - lane) * 32;                 // first key of the warp's tile
+    uint32_t pw = 0u, valid = 0u;
     if (w < W) {
-      uint32_t codes[32];
-      ht_load_codes(kc, w, S, aligned, codes);
-      const uint32_t pw = prev_row[w];
-      const int64_t c0 = w * 32;
-      uint32_t valid = ~pw;
-      if (c0 + 32 > S) valid &= (c0 >= S) ? 0u : ((1u << (S - c0)) - 1u);
-      prevw[j] = pw;
-      validm[j] = valid;
+      pw = prev_row[w];
+      valid = ~pw;
+      if (w * 32 + 32 > S) valid &= (w * 32 >= S) ? 0u : ((1u << (S - w * 32)) - 1u);
+    }
+    prevw[j] = pw;
+    validm[j] = valid;
+    if (c0 < S) {  // warp-uniform
+      ht_tile_dist_count(kc, c0, S, aligned, qc, lane, valid, &cnt[warp][lane], s4[j]);
+    } else {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const unsigned int sc = (unsigned int)(nbits - __popc(codes[i] ^ qc));
-        sc4[j][i >> 2] |= sc << ((i & 3) * 8);
-        if ((valid >> i) & 1u) atomicAdd(&hist[warp][sc], 1u);
-      }
+      for (int i = 0; i < 8; ++i) s4[j][i] = 0u;
     }
   }
+  ht_cnt_flush(cnt[warp], hist, nbits, lane);
   __syncthreads();
   if (warp == 0) {
-    // lane b owns bin b (b = 0..31); bin 32 (all bits match) is handled aside
-    unsigned int mine = 0u, top = 0u;
-    for (int w2 = 0; w2 < HT2_THREADS / 32; ++w2) {
-      mine += hist[w2][lane];
-      top += hist[w2][32];
-    }
-    unsigned int incl = mine;  // suffix sum over lanes: keys with bin >= lane (bins <= 31)
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      unsigned int n = __shfl_down_sync(0xffffffffu, incl, o);
-      if (lane + o < 32) incl += n;
-    }
-    const long long ge = (long long)incl + top;
-    const long long total = __shfl_sync(0xffffffffu, (long long)incl, 0) + top;
     int thr;
     long long need;
-    if (k <= 0) {
-      thr = 64; need = 0;                 // nothing qualifies
-    } else if (total <= k) {
-      thr = -1; need = 0;                 // every candidate qualifies
-    } else if ((long long)top >= k) {
-      thr = 32; need = k;
-    } else {
-      const unsigned int ok = __ballot_sync(0xffffffffu, ge >= k);
-      thr = 31 - __clz(ok);               // highest bin whose ">=" count reaches k
-      const long long ge_thr = __shfl_sync(0xffffffffu, ge, thr);
-      const long long mine_thr = __shfl_sync(0xffffffffu, (long long)mine, thr);
-      need = k - (ge_thr - mine_thr);     // ties to take at the threshold
-    }
+    ht_pick(hist, k, lane, &thr, &need);
     if (lane == 0) {
       thr_sm = thr;
       need_sm = need;
@@ -600,26 +765,21 @@ hash_topk_reg_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
   }
   __syncthreads();
   const int thr = thr_sm;
-  const long long need = need_sm;
-  const unsigned int thr4 = (unsigned int)(thr & 0xff) * 0x01010101u;
+  const int need = (int)need_sm;   // at most 65536 keys in a row here
 
-  long long base = 0;
+  int base = 0;
 #pragma unroll
   for (int j = 0; j < WPT; ++j) {
     const int64_t w = tid + (int64_t)j * HT2_THREADS;
-    uint32_t gt = 0u, eq = 0u;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      gt |= ht_flags4(__vcmpgts4(sc4[j][i], thr4)) << (4 * i);
-      eq |= ht_flags4(__vcmpeq4(sc4[j][i], thr4)) << (4 * i);
-    }
-    gt &= validm[j];
-    eq &= validm[j];
-    long long total_eq;
-    const long long before = sah_block_excl_scan<long long>((long long)__popc(eq), scan, &total_eq);
+    uint32_t gl, el;
+    ht_tile_compare(s4[j], nbits, thr, &gl, &el);
+    const uint32_t gt = ht_tile_gather(gl, lane) & validm[j];
+    const uint32_t eq = ht_tile_gather(el, lane) & validm[j];
+    int total_eq;
+    const int before = sah_block_excl_scan<int>(__popc(eq), scan, &total_eq);
     if (w < W) {
-      const long long quota = need - (base + before);
-      const int take = quota > 32 ? 32 : (quota < 0 ? 0 : (int)quota);
+      const int quota = need - (base + before);
+      const int take = quota > 32 ? 32 : (quota < 0 ? 0 : quota);
       out_row[w] = prevw[j] | gt | sah_lowest_bits(eq, take);
     }
     base += total_eq;
@@ -681,96 +841,196 @@ extern "C" int sah_hash_topk(const uint32_t* kcodes, int64_t kc_stride, const ui
 // ---------------------------------------------------------------------------------------
 #define HP_THREADS 256
 
-__global__ void __launch_bounds__(HP_THREADS)
+// words per chunk: whole warp tiles (32 words), so that chunk borders are tile borders
+static inline int64_t hash_chunk_words(int64_t W, int chunks) {
+  return sah_ceil_div(sah_ceil_div(W, (int64_t)chunks), (int64_t)32) * 32;
+}
+
+// Packed distances of a tile in the scratch that carries them from the histogram pass to the emit
+// pass: 64 uint4 per tile, [half][lane], lane L holding slots 4 half .. 4 half + 3.
+__device__ __forceinline__ void ht_scores_store(uint4* __restrict__ tile, int lane, const uint32_t* s4) {
+  tile[lane] = make_uint4(s4[0], s4[1], s4[2], s4[3]);
+  tile[32 + lane] = make_uint4(s4[4], s4[5], s4[6], s4[7]);
+}
+__device__ __forceinline__ void ht_scores_load(const uint4* __restrict__ tile, int lane, uint32_t* s4) {
+  const uint4 a = tile[lane], b = tile[32 + lane];
+  s4[0] = a.x; s4[1] = a.y; s4[2] = a.z; s4[3] = a.w;
+  s4[4] = b.x; s4[5] = b.y; s4[6] = b.z; s4[7] = b.w;
+}
+
+__global__ void __launch_bounds__(HP_THREADS, 4)
 hash_hist_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
                  const uint32_t* __restrict__ qcodes, int nbits, int Sq, int64_t S, int64_t W,
                  int64_t chunk_words, const uint32_t* __restrict__ prev_bits, int64_t rows,
-                 int32_t* __restrict__ hist_out) {
-  __shared__ unsigned int hist[HP_THREADS / 32][HT_BINS];
-  const int tid = threadIdx.x, warp = tid >> 5;
+                 int32_t* __restrict__ hist_out, uint4* __restrict__ scores_out) {
+  __shared__ __align__(16) unsigned char cnt[HP_THREADS / 32][HT_CNT_BYTES];
+  __shared__ unsigned int hist[HT_BINS];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t row = blockIdx.x, chunk = blockIdx.y;
   const uint32_t* kc = kcodes + (row / Sq) * kc_stride;
   const uint32_t qc = qcodes[row];
   const uint32_t* prev_row = prev_bits + row * W;
   const bool aligned = ((reinterpret_cast<uintptr_t>(kc) & 15) == 0);
-  for (int i = tid; i < (HP_THREADS / 32) * HT_BINS; i += HP_THREADS) (&hist[0][0])[i] = 0u;
+  const int64_t row_tiles = (W + 31) >> 5;
+  for (int i = tid; i < (HP_THREADS / 32) * HT_CNT_BYTES / 4; i += HP_THREADS)
+    reinterpret_cast<uint32_t*>(&cnt[0][0])[i] = 0u;
+  if (tid < HT_BINS) hist[tid] = 0u;
   __syncthreads();
-  const int64_t w_lo = chunk * chunk_words;
+  const int64_t w_lo = chunk * chunk_words;   // chunk_words is a multiple of 32: whole tiles
   const int64_t w_hi = w_lo + chunk_words < W ? w_lo + chunk_words : W;
-  for (int64_t w = w_lo + tid; w < w_hi; w += HP_THREADS) {
-    uint32_t codes[32];
-    ht_load_codes(kc, w, S, aligned, codes);
-    const int64_t c0 = w * 32;
-    uint32_t valid = ~prev_row[w];
-    if (c0 + 32 > S) valid &= (c0 >= S) ? 0u : ((1u << (S - c0)) - 1u);
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const int sc = nbits - __popc(codes[i] ^ qc);
-      if ((valid >> i) & 1u) atomicAdd(&hist[warp][sc], 1u);
+  int pending = 0;
+  for (int64_t t0 = w_lo + 32 * warp; t0 < w_hi; t0 += HP_THREADS) {
+    if (t0 * 32 >= S) break;
+    const int64_t w = t0 + lane;
+    uint32_t valid = 0u;
+    if (w < w_hi) {
+      valid = ~prev_row[w];
+      if (w * 32 + 32 > S) valid &= (w * 32 >= S) ? 0u : ((1u << (S - w * 32)) - 1u);
+    }
+    uint32_t s4[8];
+    ht_tile_dist_count(kc, t0 * 32, S, aligned, qc, lane, valid, &cnt[warp][lane], s4);
+    if (scores_out != nullptr) ht_scores_store(scores_out + (row * row_tiles + (t0 >> 5)) * 64, lane, s4);
+    if (++pending == 7) {  // a lane's byte counters hold 255
+      ht_cnt_flush(cnt[warp], hist, nbits, lane);
+      pending = 0;
     }
   }
+  ht_cnt_flush(cnt[warp], hist, nbits, lane);
   __syncthreads();
-  if (tid < 33) {
-    unsigned int s = 0;
-#pragma unroll
-    for (int w2 = 0; w2 < HP_THREADS / 32; ++w2) s += hist[w2][tid];
-    hist_out[(chunk * rows + row) * 33 + tid] = (int32_t)s;
-  }
+  if (tid < 33) hist_out[(chunk * rows + row) * 33 + tid] = (int32_t)hist[tid];
 }
 
 extern "C" int sah_hash_hist(const uint32_t* kcodes, int64_t kc_stride, const uint32_t* qcodes,
                              int nbits, int B, int Hq, int Sq, int64_t S, int64_t W, int chunks,
-                             const uint32_t* prev_bits, int32_t* hist, void* stream) {
+                             const uint32_t* prev_bits, int32_t* hist, void* scores, void* stream) {
   SAH_REQUIRE(kcodes && qcodes && prev_bits && hist, "hash_hist: null pointer");
+  SAH_REQUIRE(((uintptr_t)scores & 15) == 0, "hash_hist: scores must be 16-byte aligned");
   SAH_REQUIRE(nbits > 0 && nbits <= 32, "hash_hist: nbits must be 1..32");
   SAH_REQUIRE(kc_stride >= S && B > 0 && Hq > 0 && Sq > 0 && S > 0 && W * 32 >= S, "hash_hist: bad extents");
   SAH_REQUIRE(chunks >= 1 && chunks <= 65535, "hash_hist: 1..65535 chunks");
   const int64_t rows = (int64_t)B * Hq * Sq;
-  const int64_t chunk_words = sah_ceil_div(W, chunks);
+  const int64_t chunk_words = hash_chunk_words(W, chunks);
   dim3 grid((unsigned)rows, (unsigned)chunks);
   hash_hist_kernel<<<grid, HP_THREADS, 0, (cudaStream_t)stream>>>(kcodes, kc_stride, qcodes, nbits, Sq, S, W,
-                                                                chunk_words, prev_bits, rows, hist);
+                                                                chunk_words, prev_bits, rows, hist,
+                                                                reinterpret_cast<uint4*>(scores));
   SAH_LAUNCH_CHECK("hash_hist");
   return SAH_OK;
 }
 
-// hist_all [world][chunks][rows][33]; one thread per (row, chunk of this rank).
-// thr: scores above it are taken whole (-1: every candidate, 64: none); need: ties at thr
-// this part takes.  Outputs are [chunks][rows].
-__global__ void hash_shard_plan_kernel(const int32_t* __restrict__ hist_all, int world, int rank,
-                                       int chunks, int64_t rows, int64_t k,
-                                       int32_t* __restrict__ thr_out, int64_t* __restrict__ need_out) {
-  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= rows * chunks) return;
-  const int64_t row = t % rows;
-  const int chunk = (int)(t / rows);
-  const int parts = world * chunks, me = rank * chunks + chunk;
-  long long ge = 0;  // candidates scoring >= bin, over all parts
+// Threshold and tie share of part `me` from the per-bin sums over all parts; one full warp,
+// lane L holding bin 31 - L (here / before_me / mine) and every lane the sums of bin 32.  A
+// prefix scan over the lanes walks the bins from the top.
+__device__ __forceinline__ void hash_plan_scan(long long here, long long before_me, long long mine,
+                                               long long here32, long long before32, long long mine32,
+                                               long long k, int lane, int* thr_out, long long* need_out) {
+  long long incl = here;   // candidates scoring >= this lane's bin, bin 32 aside
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const long long n = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += n;
+  }
+  incl += here32;
   int thr = -1;
   long long need = 0;
   if (k <= 0) {
     thr = 64;
+  } else if (here32 >= k) {  // the k-th best score is the top bin
+    thr = 32;
+    const long long left = k - before32;
+    need = left <= 0 ? 0 : (left < mine32 ? left : mine32);
   } else {
-    for (int bin = 32; bin >= 0; --bin) {
-      long long here = 0, before_me = 0, mine = 0;
-      for (int g = 0; g < parts; ++g) {
-        const long long c = hist_all[((int64_t)g * rows + row) * 33 + bin];
-        if (g < me) before_me += c;
-        if (g == me) mine = c;
-        here += c;
-      }
-      if (ge + here >= k) {  // the k-th best score is this bin
-        thr = bin;
-        const long long ties = k - ge;            // ties to take over all parts
-        const long long left = ties - before_me;  // what lower parts leave for this one
-        need = left <= 0 ? 0 : (left < mine ? left : mine);
-        break;
-      }
-      ge += here;
+    const unsigned int ok = __ballot_sync(0xffffffffu, incl >= k);
+    if (ok) {
+      const int src = __ffs(ok) - 1;            // first lane (highest bin) reaching k
+      const long long ties = k - (incl - here); // ties to take over all parts
+      const long long left = ties - before_me;  // what lower parts leave for this one
+      const long long nd = left <= 0 ? 0 : (left < mine ? left : mine);
+      thr = 31 - src;
+      need = __shfl_sync(0xffffffffu, nd, src);
     }
   }
-  thr_out[t] = thr;
-  need_out[t] = need;
+  *thr_out = thr;
+  *need_out = need;
+}
+
+// One warp per (row, chunk of this rank): lane L sums bin 31 - L over all parts, bin 32 is
+// summed by all lanes together.
+__device__ __forceinline__ void hash_plan_warp(const int32_t* __restrict__ hist_all, int parts, int me,
+                                               int64_t rows, int64_t row, long long k, int lane,
+                                               int* thr_out, long long* need_out) {
+  const int bin = 31 - lane;
+  long long here = 0, before_me = 0, mine = 0;
+  for (int g = 0; g < parts; ++g) {
+    const long long c = hist_all[((int64_t)g * rows + row) * 33 + bin];
+    here += c;
+    if (g < me) before_me += c;
+    if (g == me) mine = c;
+  }
+  long long here32 = 0, before32 = 0, mine32 = 0;
+  for (int g = lane; g < parts; g += 32) {
+    const long long c = hist_all[((int64_t)g * rows + row) * 33 + 32];
+    here32 += c;
+    if (g < me) before32 += c;
+    if (g == me) mine32 = c;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    here32 += __shfl_xor_sync(0xffffffffu, here32, o);
+    before32 += __shfl_xor_sync(0xffffffffu, before32, o);
+    mine32 += __shfl_xor_sync(0xffffffffu, mine32, o);
+  }
+  hash_plan_scan(here, before_me, mine, here32, before32, mine32, k, lane, thr_out, need_out);
+}
+
+// The same by a whole CTA: every thread fetches a few of the parts * 33 counters (all loads in
+// flight together), shared-memory sums, then warp 0 scans.  pl: [3][33] (all, before me, mine).
+__device__ __forceinline__ void hash_plan_cta(const int32_t* __restrict__ hist_all, int parts, int me,
+                                              int64_t rows, int64_t row, long long k,
+                                              unsigned long long (*pl)[33], int* thr_sm, long long* need_sm) {
+  const int tid = threadIdx.x, lane = tid & 31;
+  for (int i = tid; i < 3 * 33; i += blockDim.x) (&pl[0][0])[i] = 0ull;
+  __syncthreads();
+  for (int idx = tid; idx < parts * 33; idx += blockDim.x) {
+    const int g = idx / 33, bin = idx - g * 33;
+    const unsigned long long c = (unsigned long long)hist_all[((int64_t)g * rows + row) * 33 + bin];
+    if (c) {
+      atomicAdd(&pl[0][bin], c);
+      if (g < me) atomicAdd(&pl[1][bin], c);
+      if (g == me) pl[2][bin] = c;
+    }
+  }
+  __syncthreads();
+  if (tid < 32) {
+    int thr;
+    long long need;
+    hash_plan_scan((long long)pl[0][31 - lane], (long long)pl[1][31 - lane], (long long)pl[2][31 - lane],
+                   (long long)pl[0][32], (long long)pl[1][32], (long long)pl[2][32], k, lane, &thr, &need);
+    if (lane == 0) {
+      *thr_sm = thr;
+      *need_sm = need;
+    }
+  }
+  __syncthreads();
+}
+
+// hist_all [world][chunks][rows][33].  thr: scores above it are taken whole (-1: every
+// candidate, 64: none); need: ties at thr this part takes.  Outputs are [chunks][rows].
+__global__ void hash_shard_plan_kernel(const int32_t* __restrict__ hist_all, int world, int rank,
+                                       int chunks, int64_t rows, int64_t k,
+                                       int32_t* __restrict__ thr_out, int64_t* __restrict__ need_out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t t = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (t >= rows * chunks) return;   // warp-uniform
+  const int64_t row = t % rows;
+  const int chunk = (int)(t / rows);
+  int thr;
+  long long need;
+  hash_plan_warp(hist_all, world * chunks, rank * chunks + chunk, rows, row, k, lane, &thr, &need);
+  if (lane == 0) {
+    thr_out[t] = thr;
+    need_out[t] = need;
+  }
 }
 
 extern "C" int sah_hash_shard_plan(const int32_t* hist_all, int world, int rank, int chunks,
@@ -779,75 +1039,126 @@ extern "C" int sah_hash_shard_plan(const int32_t* hist_all, int world, int rank,
   SAH_REQUIRE(hist_all && thr && need, "hash_shard_plan: null pointer");
   SAH_REQUIRE(world > 0 && rank >= 0 && rank < world && rows > 0 && chunks >= 1,
               "hash_shard_plan: bad extents");
-  hash_shard_plan_kernel<<<(unsigned)sah_ceil_div(rows * chunks, 128), 128, 0, (cudaStream_t)stream>>>(
+  hash_shard_plan_kernel<<<(unsigned)sah_ceil_div(rows * chunks, 4), 128, 0, (cudaStream_t)stream>>>(
       hist_all, world, rank, chunks, rows, k, thr, need);
   SAH_LAUNCH_CHECK("hash_shard_plan");
   return SAH_OK;
 }
 
-__global__ void __launch_bounds__(HP_THREADS)
+// thr_in/need_in: the plan of sah_hash_shard_plan; when they are null the CTA derives its own
+// entry from hist_all (the single-device path, one launch less).  scores_in: the packed scores
+// left by the histogram pass, or null to recompute them from the codes.  A warp takes HE_TILES
+// consecutive tiles at a time, so the ordered count of ties needs one CTA barrier per
+// 8 * HE_TILES tiles.
+#define HE_TILES 4
+
+__global__ void __launch_bounds__(HP_THREADS, 4)
 hash_emit_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
                  const uint32_t* __restrict__ qcodes, int nbits, int Sq, int64_t S, int64_t W,
                  int64_t chunk_words, const uint32_t* __restrict__ prev_bits, int64_t rows,
                  const int32_t* __restrict__ thr_in, const int64_t* __restrict__ need_in,
-                 uint32_t* __restrict__ out_bits) {
-  __shared__ long long scan[33];
-  const int tid = threadIdx.x;
+                 const int32_t* __restrict__ hist_all, int chunks, int64_t k,
+                 const uint4* __restrict__ scores_in, uint32_t* __restrict__ out_bits) {
+  __shared__ int wsum[2][HP_THREADS / 32];
+  __shared__ unsigned long long pl[3][33];
+  __shared__ int thr_sm;
+  __shared__ long long need_sm;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t row = blockIdx.x, chunk = blockIdx.y;
   const uint32_t* kc = kcodes + (row / Sq) * kc_stride;
   const uint32_t qc = qcodes[row];
   const uint32_t* prev_row = prev_bits + row * W;
   uint32_t* out_row = out_bits + row * W;
   const bool aligned = ((reinterpret_cast<uintptr_t>(kc) & 15) == 0);
-  const int thr = thr_in[chunk * rows + row];
-  const long long need = need_in[chunk * rows + row];
+  const int64_t row_tiles = (W + 31) >> 5;
+  if (thr_in != nullptr) {
+    if (tid == 0) {
+      thr_sm = thr_in[chunk * rows + row];
+      need_sm = need_in[chunk * rows + row];
+    }
+    __syncthreads();
+  } else {
+    hash_plan_cta(hist_all, chunks, (int)chunk, rows, row, k, pl, &thr_sm, &need_sm);
+  }
+  const int thr = thr_sm;
+  const long long need = need_sm;
   const int64_t w_lo = chunk * chunk_words;
   const int64_t w_hi = w_lo + chunk_words < W ? w_lo + chunk_words : W;
   long long base = 0;
-  for (int64_t w0 = w_lo; w0 < w_hi; w0 += HP_THREADS) {
-    const int64_t w = w0 + tid;
-    uint32_t gt = 0u, eq = 0u, pw = 0u;
-    if (w < w_hi) {
-      uint32_t codes[32];
-      ht_load_codes(kc, w, S, aligned, codes);
-      pw = prev_row[w];
-      const int64_t c0 = w * 32;
-      uint32_t valid = ~pw;
-      if (c0 + 32 > S) valid &= (c0 >= S) ? 0u : ((1u << (S - c0)) - 1u);
+  int it = 0;
+  for (int64_t sb = w_lo; sb < w_hi; sb += HP_THREADS * HE_TILES, ++it) {
+    uint32_t gt[HE_TILES], eq[HE_TILES], pw[HE_TILES];
+    int excl[HE_TILES];
+    int run = 0;   // ties in this warp's earlier tiles of the block
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int sc = nbits - __popc(codes[i] ^ qc);
-        gt |= (sc > thr ? 1u : 0u) << i;
-        eq |= (sc == thr ? 1u : 0u) << i;
+    for (int t = 0; t < HE_TILES; ++t) {
+      const int64_t t0 = sb + (int64_t)(warp * HE_TILES + t) * 32;   // first word of the tile
+      const int64_t w = t0 + lane;
+      gt[t] = 0u; eq[t] = 0u; pw[t] = 0u;
+      if (t0 < w_hi) {   // warp-uniform
+        uint32_t valid = 0u;
+        if (w < w_hi) {
+          pw[t] = prev_row[w];
+          valid = ~pw[t];
+          if (w * 32 + 32 > S) valid &= (w * 32 >= S) ? 0u : ((1u << (S - w * 32)) - 1u);
+        }
+        if (t0 * 32 < S) {
+          uint32_t s4[8], gl, el;
+          if (scores_in != nullptr) ht_scores_load(scores_in + (row * row_tiles + (t0 >> 5)) * 64, lane, s4);
+          else ht_tile_dist<false>(kc, t0 * 32, S, aligned, qc, lane, s4);
+          ht_tile_compare(s4, nbits, thr, &gl, &el);
+          gt[t] = ht_tile_gather(gl, lane) & valid;
+          eq[t] = ht_tile_gather(el, lane) & valid;
+        }
       }
-      gt &= valid;
-      eq &= valid;
+      const int c = __popc(eq[t]);
+      int incl = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += n;
+      }
+      excl[t] = run + incl - c;
+      run += __shfl_sync(0xffffffffu, incl, 31);
     }
-    long long total_eq;
-    const long long before = sah_block_excl_scan<long long>((long long)__popc(eq), scan, &total_eq);
-    if (w < w_hi) {
-      const long long quota = need - (base + before);
-      const int take = quota > 32 ? 32 : (quota < 0 ? 0 : (int)quota);
-      out_row[w] = pw | gt | sah_lowest_bits(eq, take);
+    if (lane == 0) wsum[it & 1][warp] = run;
+    __syncthreads();
+    int before_warps = 0, total = 0;
+#pragma unroll
+    for (int v = 0; v < HP_THREADS / 32; ++v) {
+      const int x = wsum[it & 1][v];
+      total += x;
+      if (v < warp) before_warps += x;
     }
-    base += total_eq;
+#pragma unroll
+    for (int t = 0; t < HE_TILES; ++t) {
+      const int64_t w = sb + (int64_t)(warp * HE_TILES + t) * 32 + lane;
+      if (w < w_hi) {
+        const long long quota = need - (base + before_warps + excl[t]);
+        const int take = quota > 32 ? 32 : (quota < 0 ? 0 : (int)quota);
+        out_row[w] = pw[t] | gt[t] | sah_lowest_bits(eq[t], take);
+      }
+    }
+    base += total;
   }
 }
 
 extern "C" int sah_hash_emit(const uint32_t* kcodes, int64_t kc_stride, const uint32_t* qcodes,
                              int nbits, int B, int Hq, int Sq, int64_t S, int64_t W, int chunks,
                              const uint32_t* prev_bits, const int32_t* thr, const int64_t* need,
-                             uint32_t* out_bits, void* stream) {
+                             const void* scores, uint32_t* out_bits, void* stream) {
   SAH_REQUIRE(kcodes && qcodes && prev_bits && thr && need && out_bits, "hash_emit: null pointer");
+  SAH_REQUIRE(((uintptr_t)scores & 15) == 0, "hash_emit: scores must be 16-byte aligned");
   SAH_REQUIRE(nbits > 0 && nbits <= 32, "hash_emit: nbits must be 1..32");
   SAH_REQUIRE(kc_stride >= S && B > 0 && Hq > 0 && Sq > 0 && S > 0 && W * 32 >= S, "hash_emit: bad extents");
   SAH_REQUIRE(chunks >= 1 && chunks <= 65535, "hash_emit: 1..65535 chunks");
   const int64_t rows = (int64_t)B * Hq * Sq;
-  const int64_t chunk_words = sah_ceil_div(W, chunks);
+  const int64_t chunk_words = hash_chunk_words(W, chunks);
   dim3 grid((unsigned)rows, (unsigned)chunks);
   hash_emit_kernel<<<grid, HP_THREADS, 0, (cudaStream_t)stream>>>(kcodes, kc_stride, qcodes, nbits, Sq, S, W,
                                                                 chunk_words, prev_bits, rows, thr, need,
-                                                                out_bits);
+                                                                nullptr, chunks, 0,
+                                                                reinterpret_cast<const uint4*>(scores), out_bits);
   SAH_LAUNCH_CHECK("hash_emit");
   return SAH_OK;
 }
@@ -864,10 +1175,19 @@ static int hash_ws_chunks(int64_t rows, int64_t W, int sm_count) {
   return (int)chunks;
 }
 
+extern "C" int64_t sah_hash_scores_bytes(int64_t rows, int64_t W) {
+  if (rows <= 0 || W <= 0) return 0;
+  return rows * ((W + 31) / 32) * 1024;   // one byte per key, whole 1024-key tiles
+}
+
+static int64_t hash_ws_hist_bytes(int64_t rows, int64_t chunks) {
+  return (rows * chunks * 33 * 4 + 15) / 16 * 16;
+}
+
 extern "C" int64_t sah_hash_topk_ws_bytes(int64_t rows, int64_t W, int sm_count) {
   if (rows <= 0 || W <= 0) return 0;
   const int64_t chunks = hash_ws_chunks(rows, W, sm_count);
-  return rows * chunks * (33 * 4 + 4 + 8) + 64;
+  return hash_ws_hist_bytes(rows, chunks) + sah_hash_scores_bytes(rows, W);
 }
 
 extern "C" int sah_hash_topk_ws(const uint32_t* kcodes, int64_t kc_stride, const uint32_t* qcodes,
@@ -876,6 +1196,7 @@ extern "C" int sah_hash_topk_ws(const uint32_t* kcodes, int64_t kc_stride, const
                                 void* workspace, int64_t workspace_bytes, int sm_count, void* stream) {
   SAH_REQUIRE(workspace != nullptr && ((uintptr_t)workspace & 15) == 0,
               "hash_topk_ws: workspace must be a 16-byte aligned device pointer");
+  SAH_REQUIRE(kcodes && qcodes && prev_bits && out_bits, "hash_topk_ws: null pointer");
   const int64_t rows = (int64_t)B * Hq * Sq;
   SAH_REQUIRE(rows > 0 && rows <= 2147483647, "hash_topk_ws: bad row count");
   if (workspace_bytes < sah_hash_topk_ws_bytes(rows, W, sm_count))
@@ -883,19 +1204,20 @@ extern "C" int sah_hash_topk_ws(const uint32_t* kcodes, int64_t kc_stride, const
                     (long long)workspace_bytes, (long long)sah_hash_topk_ws_bytes(rows, W, sm_count));
   const int chunks = hash_ws_chunks(rows, W, sm_count);
   unsigned char* p = reinterpret_cast<unsigned char*>(workspace);
-  int64_t* need = reinterpret_cast<int64_t*>(p);
-  p += rows * chunks * 8;
   int32_t* hist = reinterpret_cast<int32_t*>(p);
-  p += rows * chunks * 33 * 4;
-  int32_t* thr = reinterpret_cast<int32_t*>(p);
+  void* scores = p + hash_ws_hist_bytes(rows, chunks);
   sah_prof_begin(SAH_PROF_HASH_TOPK, (cudaStream_t)stream);
-  int rc = sah_hash_hist(kcodes, kc_stride, qcodes, nbits, B, Hq, Sq, S, W, chunks, prev_bits, hist, stream);
+  int rc = sah_hash_hist(kcodes, kc_stride, qcodes, nbits, B, Hq, Sq, S, W, chunks, prev_bits, hist, scores,
+                         stream);
   if (rc != SAH_OK) return rc;
-  rc = sah_hash_shard_plan(hist, 1, 0, chunks, rows, k, thr, need, stream);
-  if (rc != SAH_OK) return rc;
-  rc = sah_hash_emit(kcodes, kc_stride, qcodes, nbits, B, Hq, Sq, S, W, chunks, prev_bits, thr, need,
-                     out_bits, stream);
-  if (rc != SAH_OK) return rc;
+  {
+    // every emit CTA derives its threshold and tie share from the chunk histograms itself
+    dim3 grid((unsigned)rows, (unsigned)chunks);
+    hash_emit_kernel<<<grid, HP_THREADS, 0, (cudaStream_t)stream>>>(
+        kcodes, kc_stride, qcodes, nbits, Sq, S, W, hash_chunk_words(W, chunks), prev_bits, rows, nullptr,
+        nullptr, hist, chunks, k, reinterpret_cast<const uint4*>(scores), out_bits);
+    SAH_LAUNCH_CHECK("hash_topk_ws emit");
+  }
   sah_prof_end(SAH_PROF_HASH_TOPK, (cudaStream_t)stream);
   return SAH_OK;
 }

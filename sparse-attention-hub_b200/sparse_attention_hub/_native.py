@@ -92,9 +92,10 @@ _SIGNATURES = {
     "sah_adaptive_budget": [_P, _I, c_float, _P, _L, _L, _L, _P, _P, _P, _P, _I, _I, _I, _L, _L, _L,
                             _L, _L, ctypes.c_uint64, _P, _P, c_float, c_float, _P, _P, _P, _P],
     "sah_sample_scatter": [_P, _L, _P, ctypes.c_uint64, _L, _L, _L, _L, _I, _P, _P],
-    "sah_hash_hist": [_P, _L, _P, _I, _I, _I, _I, _L, _L, _I, _P, _P, _P],
+    "sah_hash_hist": [_P, _L, _P, _I, _I, _I, _I, _L, _L, _I, _P, _P, _P, _P],
+    "sah_hash_scores_bytes": [_L, _L],  # returns int64
     "sah_hash_shard_plan": [_P, _I, _I, _I, _L, _L, _P, _P, _P],
-    "sah_hash_emit": [_P, _L, _P, _I, _I, _I, _I, _L, _L, _I, _P, _P, _P, _P, _P],
+    "sah_hash_emit": [_P, _L, _P, _I, _I, _I, _I, _L, _L, _I, _P, _P, _P, _P, _P, _P],
     "sah_hash_topk_ws_bytes": [_L, _L, _I],  # returns int64
     "sah_hash_topk_ws": [_P, _L, _P, _I, _I, _I, _I, _L, _L, _P, _L, _P, _P, _L, _I, _P],
     "sah_mask_merge_bits": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _L, _P, _P],
@@ -150,6 +151,7 @@ def load() -> ctypes.CDLL:
     lib.sah_pq_scores_ws_bytes.restype = c_int64
     lib.sah_topk_sel_hist_offset.restype = c_int64
     lib.sah_hash_topk_ws_bytes.restype = c_int64
+    lib.sah_hash_scores_bytes.restype = c_int64
     lib.sah_version.restype = c_char_p
     lib.sah_last_error.restype = c_char_p
     lib.sah_launch_count.restype = ctypes.c_longlong

@@ -247,10 +247,11 @@ def hash_topk(kcodes: torch.Tensor, n_keys: int, qcodes: torch.Tensor, nbits: in
     dev = kcodes.device
     st = _native.stream_of(dev)
     sms = _native.sm_count(dev)
-    if attention_mask is None and prev.rows < sms:
-        # fewer rows than SMs (long contexts, small batches): histogram / plan / emit with
-        # every row cut into chunks, so that the grid still fills the device; with more rows
-        # the one-CTA-per-row kernel below does the same in a single launch
+    if attention_mask is None and (prev.rows < sms or prev.words > 2048):
+        # fewer rows than SMs (long contexts, small batches), or rows too long for the
+        # register-resident kernel: histogram, then emit, with every row cut into chunks so
+        # that the grid fills the device; otherwise the one-CTA-per-row kernel below does the
+        # same in a single launch
         nbytes = int(lib.sah_hash_topk_ws_bytes(prev.rows, prev.words, sms))
         ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
         _native.check(
@@ -289,15 +290,17 @@ def hash_topk_sharded(kcodes: torch.Tensor, qcodes: torch.Tensor, nbits: int, pr
     hist = torch.empty((chunks, rows, 33), dtype=torch.int32, device=dev)
     args = (kcodes.data_ptr(), kcodes.shape[-1], qcodes.data_ptr(), nbits, B, Hq, Sq, S, words, chunks,
             prev.bits.data_ptr())
-    _native.check(lib.sah_hash_hist(*args, hist.data_ptr(), st), "sah_hash_hist")
+    # one byte per key carries the scores from the histogram pass to the emit pass
+    scores = torch.empty(int(lib.sah_hash_scores_bytes(rows, words)), dtype=torch.uint8, device=dev)
+    _native.check(lib.sah_hash_hist(*args, hist.data_ptr(), scores.data_ptr(), st), "sah_hash_hist")
     hist_all = comm.all_gather(hist)  # [world, chunks, rows, 33]
     thr = torch.empty((chunks, rows), dtype=torch.int32, device=dev)
     need = torch.empty((chunks, rows), dtype=torch.int64, device=dev)
     _native.check(lib.sah_hash_shard_plan(hist_all.data_ptr(), comm.world, comm.rank, chunks, rows, k,
                                           thr.data_ptr(), need.data_ptr(), st), "sah_hash_shard_plan")
     dst = NativeBits(torch.empty_like(prev.bits), rows, S)
-    _native.check(lib.sah_hash_emit(*args, thr.data_ptr(), need.data_ptr(), dst.bits.data_ptr(), st),
-                  "sah_hash_emit")
+    _native.check(lib.sah_hash_emit(*args, thr.data_ptr(), need.data_ptr(), scores.data_ptr(),
+                                    dst.bits.data_ptr(), st), "sah_hash_emit")
     return dst
 
 

@@ -280,6 +280,77 @@ def test_hash_topk_degenerate_score_distributions():
     np.testing.assert_array_equal(got, want)
 
 
+@pytest.mark.parametrize("S,cap,rows_h,k,nbits,path", [
+    (5000, 5003, 4, 300, 32, "row"),      # ragged tail, odd capacity: rows 1.. are not 16-byte aligned
+    (5000, 5003, 4, 300, 32, "chunks"),
+    (16384, 16384, 3, 512, 32, "row"),    # one word per thread
+    (40000, 40960, 2, 1000, 16, "row"),   # two / four words per thread, 16-bit codes
+    (40000, 40960, 2, 1000, 16, "chunks"),
+    (70001, 70016, 2, 4000, 32, "row"),   # longer than the register-resident kernel takes
+    (70001, 70016, 2, 4000, 32, "chunks"),
+    (300000, 300000, 1, 9000, 32, "chunks"),
+    (300000, 300000, 2, 9000, 32, "pieces"),  # two chunks per row: the byte counters flush several times
+    (300000, 300000, 2, 9000, 32, "pieces_scratch"),  # the same with the one-byte score scratch
+    (1500, 1500, 2, 0, 32, "row"),
+    (1500, 1500, 2, 5000, 32, "chunks"),  # k above the number of candidates
+])
+def test_hash_topk_kernel_variants(S, cap, rows_h, k, nbits, path):
+    """Every Hamming top-k kernel (one CTA per row: register-resident and streaming; chunked
+    rows with the plan fused into the emit pass) against the same selection rule, with a
+    previous mask in place and score ties cut in column order."""
+    from oracle import hashattention as oh, topk as ot
+    from sparse_attention_hub import _native
+    lib = _native.load()
+    rng = np.random.default_rng(S + k + nbits)
+    shape = (1, rows_h, 1, S)
+    mask_bits = np.uint64((1 << nbits) - 1)
+    kc = np.zeros((1, rows_h, cap), np.uint32)
+    kc[..., :S] = (rng.integers(0, 2 ** 32, (1, rows_h, S), dtype=np.uint64) & mask_bits).astype(np.uint32)
+    kc[0, 0, : S // 2] &= np.uint32(0xFF)   # a row with few distinct scores: long tie runs
+    q = (rng.integers(0, 2 ** 32, (1, rows_h, 1), dtype=np.uint64) & mask_bits).astype(np.uint32)
+    prev_np = np.zeros(shape, bool)
+    prev_np[..., :37] = True
+    prev_np[..., S - 70:] = True
+    prev_np[0, 0, 0, rng.integers(0, S, 200)] = True
+    prev = Mask.create_mask_from_dense_mask(shape, torch.from_numpy(prev_np).to(DEV).to(torch.bfloat16),
+                                            torch.bfloat16)
+    pb = prev.native_bits()
+    tk = torch.from_numpy(kc.view(np.int32)).to(DEV)
+    tq = torch.from_numpy(q.view(np.int32)).to(DEV)
+    out = torch.empty_like(pb.bits)
+    st = _native.stream_of(tk.device)
+    if path == "row":
+        _native.check(lib.sah_hash_topk(tk.data_ptr(), cap, tq.data_ptr(), nbits, None, _native.SAH_BF16, 0, 0, 0,
+                                        1, rows_h, 1, S, pb.words, pb.bits.data_ptr(), k, out.data_ptr(), st),
+                      "sah_hash_topk")
+    elif path in ("pieces", "pieces_scratch"):
+        chunks = 2
+        scratch = None
+        if path == "pieces_scratch":
+            scratch = torch.empty(int(lib.sah_hash_scores_bytes(pb.rows, pb.words)), dtype=torch.uint8, device=DEV)
+        sp = None if scratch is None else scratch.data_ptr()
+        hist = torch.empty((chunks, pb.rows, 33), dtype=torch.int32, device=DEV)
+        thr = torch.empty((chunks, pb.rows), dtype=torch.int32, device=DEV)
+        need = torch.empty((chunks, pb.rows), dtype=torch.int64, device=DEV)
+        args = (tk.data_ptr(), cap, tq.data_ptr(), nbits, 1, rows_h, 1, S, pb.words, chunks, pb.bits.data_ptr())
+        _native.check(lib.sah_hash_hist(*args, hist.data_ptr(), sp, st), "sah_hash_hist")
+        _native.check(lib.sah_hash_shard_plan(hist.data_ptr(), 1, 0, chunks, pb.rows, k, thr.data_ptr(),
+                                              need.data_ptr(), st), "sah_hash_shard_plan")
+        _native.check(lib.sah_hash_emit(*args, thr.data_ptr(), need.data_ptr(), sp, out.data_ptr(), st),
+                      "sah_hash_emit")
+    else:
+        sms = _native.sm_count(tk.device)
+        nbytes = int(lib.sah_hash_topk_ws_bytes(pb.rows, pb.words, sms))
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=DEV)
+        _native.check(lib.sah_hash_topk_ws(tk.data_ptr(), cap, tq.data_ptr(), nbits, 1, rows_h, 1, S, pb.words,
+                                           pb.bits.data_ptr(), k, out.data_ptr(), ws.data_ptr(), nbytes, sms,
+                                           st), "sah_hash_topk_ws")
+    got = Mask._from_native(shape, torch.bfloat16, type(pb)(out, pb.rows, S)).get_dense_mask().float().cpu().numpy() != 0
+    scores = oh.scores(q, kc[..., :S], nbits, "bf16")
+    want = ot.topk_inactive(scores, prev_np, k) | prev_np
+    np.testing.assert_array_equal(got, want)
+
+
 def test_attention_with_sixteen_rows_per_group():
     """GQA ratio 16: every row of the 16-row tensor-core tile is a real query head."""
     wl = workloads.sink_local_fp32(seed=44, B=1, Hq=16, Hkv=1, S=1500, D=128, sink=8, window=40)
