@@ -66,6 +66,10 @@ def make_workload(name: str, seed: int, small: bool = False):
         if small:
             return workloads.oracle_adaptive(seed=seed, B=1, S=8192)
         return workloads.oracle_adaptive(seed=seed)
+    if name == "oracle_topp":
+        if small:
+            return workloads.oracle_topp(seed=seed, B=1, S=8192)
+        return workloads.oracle_topp(seed=seed)
     if name == "pqcache":
         if small:
             return workloads.pqcache(seed=seed, S=16384, heavy=512, kmeans_iter=3)
@@ -337,13 +341,15 @@ def run_native(args) -> None:
     stage_bytes = {"attention": attn_bytes}
     if any(kind == "hash_topk" for kind, _ in wl.stack):
         stage_bytes["hash_topk"] = B * Hq * S * 4
-    if any(kind == "oracle_topk" for kind, _ in wl.stack):
+    if any(kind in ("oracle_topk", "oracle_topp") for kind, _ in wl.stack):
         stage_bytes["qk_scores"] = B * Hkv * S * D * esz
     for kind, prm in wl.stack:
         if kind == "pq_topk":  # one byte per sub-vector code per key and KV head
             stage_bytes["pq_scores"] = B * Hkv * (S - prm["init_offset"]) * prm["pq_group_factor"]
         if kind == "adaptive_sampling":  # the q.k scores of every row, read once
             stage_bytes["adaptive_budget"] = B * Hq * Sq * S * esz
+        if kind == "oracle_topp":        # the same for the top-p threshold
+            stage_bytes["topp_select"] = B * Hq * Sq * S * esz
     step_bytes = sum(stage_bytes.values())
 
     # e2e: host buffers in, host result out, incremental key append

@@ -276,6 +276,26 @@ int sah_sample_scatter(const int64_t* sptr, int64_t rows, const int64_t* pool, u
                        int64_t start, int64_t n, int64_t S, int64_t W, int sm_count,
                        uint32_t* bits, void* stream);
 
+/* ------------------------------------------------------------------------ *
+ * Oracle top-p  (maskers/fixed/implementations/oracle_top_p.py:85-169)
+ * ------------------------------------------------------------------------ */
+
+/* out_bits = {j : w_j >= t_row} (| prev_bits when or_prev != 0), where
+ * w = exp(scaling * scores + bias - rowmax) with the previously active positions at
+ * the lowest finite value (_compute_exp_attention_scores :85-106, every tensor
+ * operation one rounding to bf16) and t_row is the sorted weight at which the
+ * normalised cumulative sum first exceeds top_p, the search position clamped to the
+ * last element (_compute_top_p_thresholds :108-136).  The cumulative sum is the
+ * reference's on a CPU: one float32 accumulator over the weights in descending
+ * order, prefixes rounded to bf16.  dtype must be SAH_BF16 (SAH_ERR_UNSUPPORTED
+ * otherwise).
+ *   scores     [rows][S] unscaled q.k (sah_qk_scores without bias)
+ *   exp_table  uint16[65536]: bf16 bits of x -> bf16 bits of exp(x) */
+int sah_topp_select(const void* scores, int dtype, float scaling, const void* bias,
+                    int64_t bias_s_b, int64_t bias_s_h, int64_t bias_s_q, int B, int Hq, int Sq,
+                    int64_t S, int64_t W, const uint32_t* prev_bits, float top_p,
+                    const uint16_t* exp_table, int or_prev, uint32_t* out_bits, void* stream);
+
 /* sah_hash_topk in pieces (no additive bias): the keys of a row are cut into
  * world * chunks contiguous column ranges ("parts") -- `chunks` per rank, ranks in
  * column order -- each worked on by its own CTA.

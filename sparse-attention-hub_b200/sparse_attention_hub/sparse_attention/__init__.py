@@ -12,6 +12,8 @@ from .research_attention.maskers.fixed import (
     LocalMaskerConfig,
     OracleTopK,
     OracleTopKConfig,
+    OracleTopPMasker,
+    OracleTopPMaskerConfig,
     PQCache,
     PQCacheConfig,
     SinkMasker,
@@ -38,5 +40,5 @@ __all__ = [
     "SinkMaskerConfig", "OracleTopK", "OracleTopKConfig", "HashAttentionTopKMasker",
     "HashAttentionTopKMaskerConfig", "PQCache", "PQCacheConfig", "RandomSamplingMasker",
     "RandomSamplingMaskerConfig", "AdaptiveSamplingMasker", "AdaptiveSamplingMaskerConfig", "MagicPig",
-    "MagicPigConfig", "Mask",
+    "MagicPigConfig", "OracleTopPMasker", "OracleTopPMaskerConfig", "Mask",
 ]

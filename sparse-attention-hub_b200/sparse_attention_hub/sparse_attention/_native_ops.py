@@ -158,6 +158,26 @@ def qk_scores(queries: torch.Tensor, keys: torch.Tensor,
     return scores
 
 
+def topp_select(scores: torch.Tensor, attention_mask: Optional[torch.Tensor], scaling: float,
+                previous_mask: Mask, top_p: float, or_prev: bool) -> NativeBits:
+    """Keys whose exp weight reaches the row's top-p threshold (`| previous` when `or_prev`).
+
+    `scores` are the unscaled q.k of `qk_scores` without bias; bfloat16 only."""
+    lib = _native.load()
+    B, Hq, Sq, S = scores.shape
+    prev = previous_mask.native_bits()
+    dst = NativeBits(torch.empty_like(prev.bits), prev.rows, S)
+    keep, bptr, bsb, bsh, bsq = bias_args(attention_mask, scores.dtype, S)
+    table = exp_table(scores.device)
+    _native.check(
+        lib.sah_topp_select(scores.data_ptr(), _native.dtype_code(scores.dtype), float(scaling), bptr,
+                            bsb, bsh, bsq, B, Hq, Sq, S, prev.words, prev.bits.data_ptr(), float(top_p),
+                            table.data_ptr(), int(or_prev), dst.bits.data_ptr(),
+                            _native.stream_of(scores.device)), "sah_topp_select")
+    del keep
+    return dst
+
+
 # ---- HashAttention ------------------------------------------------------------
 _ACT_TABLES: dict = {}
 

@@ -16,6 +16,8 @@ from .implementations import (
     LocalMaskerConfig,
     OracleTopK,
     OracleTopKConfig,
+    OracleTopPMasker,
+    OracleTopPMaskerConfig,
     PQCache,
     PQCacheConfig,
     SinkMasker,
@@ -26,5 +28,5 @@ __all__ = [
     "FixedMasker", "TopKMasker", "TopPMasker", "FixedMaskerConfig", "TopKMaskerConfig",
     "TopPMaskerConfig", "LocalMasker", "CausalMasker", "SinkMasker", "OracleTopK",
     "HashAttentionTopKMasker", "LocalMaskerConfig", "SinkMaskerConfig", "OracleTopKConfig",
-    "HashAttentionTopKMaskerConfig", "PQCache", "PQCacheConfig",
+    "HashAttentionTopKMaskerConfig", "PQCache", "PQCacheConfig", "OracleTopPMasker", "OracleTopPMaskerConfig",
 ]

@@ -99,7 +99,7 @@ class TopPMaskerConfig(FixedMaskerConfig):
 
 
 class TopPMasker(FixedMasker):
-    """Abstract base of cumulative-mass maskers (no native implementation yet)."""
+    """Abstract base of cumulative-mass maskers."""
 
     def __init__(self, config: TopPMaskerConfig) -> None:
         super().__init__(config)

@@ -9,10 +9,11 @@ from .basic_fixed import (
 )
 from .hashattention_top_k import HashAttentionTopKMasker, HashAttentionTopKMaskerConfig
 from .oracle_top_k import OracleTopK, OracleTopKConfig
+from .oracle_top_p import OracleTopPMasker, OracleTopPMaskerConfig
 from .pq_top_k import PQCache, PQCacheConfig
 
 __all__ = [
     "LocalMasker", "CausalMasker", "SinkMasker", "OracleTopK", "HashAttentionTopKMasker",
     "LocalMaskerConfig", "SinkMaskerConfig", "OracleTopKConfig", "HashAttentionTopKMaskerConfig",
-    "PQCache", "PQCacheConfig",
+    "PQCache", "PQCacheConfig", "OracleTopPMasker", "OracleTopPMaskerConfig",
 ]

@@ -153,6 +153,16 @@ def oracle_topk(seed: int = 0, dtype: str = "bf16", B: int = 4, Hq: int = 32, Hk
          ("oracle_topk", {"heavy_size": heavy})])
 
 
+def oracle_topp(seed: int = 0, dtype: str = "bf16", B: int = 4, Hq: int = 32, Hkv: int = 8,
+                S: int = 65536, D: int = 128, sink: int = 128, window: int = 512, top_p: float = 0.9,
+                Sq: int = 1) -> DecodeWorkload:
+    """Sink + Local + oracle top-p on the clustered keys of `oracle_topk`."""
+    wl = oracle_topk(seed, dtype, B, Hq, Hkv, S, D, sink, window, 0.02, Sq)
+    wl.name = "oracle_topp_" + dtype
+    wl.stack = wl.stack[:2] + [("oracle_topp", {"top_p": top_p})]
+    return wl
+
+
 def oracle_adaptive(seed: int = 0, dtype: str = "bf16", B: int = 4, Hq: int = 32, Hkv: int = 8,
                     S: int = 65536, D: int = 128, sink: int = 128, window: int = 512, heavy=0.02,
                     base_rate=0.05, epsilon: float = 0.05, delta: float = 0.05,
@@ -257,6 +267,8 @@ def masker_configs(stack: List[Tuple[str, Dict[str, Any]]], dtype: str, device="
             out.append(fixed.LocalMaskerConfig(window_size=prm["window_size"]))
         elif kind == "oracle_topk":
             out.append(fixed.OracleTopKConfig(heavy_size=prm["heavy_size"]))
+        elif kind == "oracle_topp":
+            out.append(fixed.OracleTopPMaskerConfig(top_p=prm["top_p"]))
         elif kind == "hash_topk":
             w = {0: {name: [to_torch(a, dtype, device) for a in arrs]
                      for name, arrs in prm["weights"].items()}}
