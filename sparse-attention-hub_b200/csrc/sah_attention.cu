@@ -101,39 +101,57 @@ __global__ void attn_plan_count_kernel(const uint32_t* __restrict__ bits, PlanGe
   if (lane == 0) chunkcnt[g * p.nchunks + c] = cnt;
 }
 
-// Short rows (W <= 1024 words, i.e. up to 32768 keys): one CTA per group, one
-// bitmap word per thread, a single ordered block scan places every word's
-// entries; no second kernel and no chunk counters.
+// Short rows (W <= 1024 words, i.e. up to 32768 keys): PLAN_FUSED_THREADS bitmap words per CTA,
+// one per thread, up to four CTAs per group.  A CTA first counts the union bits of the words in
+// front of its own (a few loads per thread from a bitmap that is cache resident), then a single
+// ordered block scan places every word's entries; no second kernel and no chunk counters.
+#define PLAN_FUSED_THREADS 256
+
 template <typename T, int RMAX>
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(PLAN_FUSED_THREADS)
 attn_plan_fused_kernel(const uint32_t* __restrict__ bits, const T* __restrict__ data,
                        const int32_t* __restrict__ wpre, const int64_t* __restrict__ ptr,
                        PlanGeom p, int32_t* __restrict__ ucols, uint16_t* __restrict__ umemb,
                        float* __restrict__ uw, int32_t* __restrict__ ucount) {
   __shared__ int scan[33];
+  __shared__ int64_t rows_sm[RMAX];
   const int64_t g = blockIdx.x;
-  const int64_t w = threadIdx.x;
+  const int64_t w0 = (int64_t)blockIdx.y * PLAN_FUSED_THREADS;   // first word of this CTA
+  const int64_t w = w0 + threadIdx.x;
+  if (threadIdx.x < RMAX) rows_sm[threadIdx.x] = (threadIdx.x < p.R) ? plan_member_row(p, g, threadIdx.x) : -1;
+  __syncthreads();
   uint32_t words[RMAX];
   int64_t rows[RMAX];
   int64_t dbase[RMAX];  // CSR position of the first entry of this row's word
   uint32_t u = 0u;
+  int ahead = 0;        // union bits in this thread's share of the words before w0
+#pragma unroll
+  for (int r = 0; r < RMAX; ++r) rows[r] = rows_sm[r];
+  for (int64_t wa = threadIdx.x; wa < w0; wa += PLAN_FUSED_THREADS) {
+    uint32_t ua = 0u;
+#pragma unroll
+    for (int r = 0; r < RMAX; ++r)
+      if (rows[r] >= 0) ua |= bits[rows[r] * p.W + wa];
+    ahead += __popc(ua);
+  }
 #pragma unroll
   for (int r = 0; r < RMAX; ++r) {
     words[r] = 0u;
-    rows[r] = -1;
     dbase[r] = 0;
-    if (r < p.R && w < p.W) {
-      rows[r] = plan_member_row(p, g, r);
-      if (rows[r] >= 0) {
-        words[r] = bits[rows[r] * p.W + w];
-        if (uw != nullptr && words[r]) dbase[r] = ptr[rows[r]] + wpre[rows[r] * p.W + w];
-      }
+    if (w < p.W && rows[r] >= 0) {
+      words[r] = bits[rows[r] * p.W + w];
+      if (uw != nullptr && words[r]) dbase[r] = ptr[rows[r]] + wpre[rows[r] * p.W + w];
     }
     u |= words[r];
   }
+  int base = 0;
+  if (w0 > 0) {
+    int dummy = sah_block_excl_scan<int>(ahead, scan, &base);
+    (void)dummy;
+  }
   int total;
   const int before = sah_block_excl_scan<int>(__popc(u), scan, &total);
-  int64_t pos = (int64_t)g * p.S + before;
+  int64_t pos = (int64_t)g * p.S + base + before;
   uint32_t m = u;
   while (m) {
     const int b = __ffs(m) - 1;
@@ -158,7 +176,7 @@ attn_plan_fused_kernel(const uint32_t* __restrict__ bits, const T* __restrict__ 
     }
     ++pos;
   }
-  if (threadIdx.x == 0) ucount[g] = total;
+  if (threadIdx.x == 0 && blockIdx.y == gridDim.y - 1) ucount[g] = base + total;
 }
 
 template <typename T>
@@ -260,12 +278,13 @@ extern "C" int sah_attn_plan(const uint32_t* bits, const void* data, const int32
   cudaStream_t st = (cudaStream_t)stream;
   sah_prof_begin(SAH_PROF_ATTN_PLAN, (cudaStream_t)stream);
   if (W <= 1024) {
+    const dim3 fgrid((unsigned)groups, (unsigned)sah_ceil_div(W, PLAN_FUSED_THREADS));
     SAH_DISPATCH_DTYPE(dtype, T, {
       if (p.R <= 4)
-        attn_plan_fused_kernel<T, 4><<<(unsigned)groups, 1024, 0, st>>>(
+        attn_plan_fused_kernel<T, 4><<<fgrid, PLAN_FUSED_THREADS, 0, st>>>(
             bits, (const T*)data, wpre, ptr, p, ucols, umemb, data ? uw : nullptr, ucount);
       else
-        attn_plan_fused_kernel<T, AT_MAXR><<<(unsigned)groups, 1024, 0, st>>>(
+        attn_plan_fused_kernel<T, AT_MAXR><<<fgrid, PLAN_FUSED_THREADS, 0, st>>>(
             bits, (const T*)data, wpre, ptr, p, ucols, umemb, data ? uw : nullptr, ucount);
     });
     SAH_LAUNCH_CHECK("attn_plan_fused");
