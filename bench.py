@@ -418,12 +418,12 @@ def run_native(args) -> None:
         achieved = attn_bytes / (attn_avg_ms * 1e-3) / 1e9 if attn_avg_ms > 0 else 0.0
         stage_times = {s: (ms / max(n, 1)) * 1e3 for s, (ms, n) in prof.items() if n > 0}
         # DRAM traffic of one attention launch: ncu (dram__bytes_read.sum + dram__bytes_write.sum)
-        # measured 225 636 096 B for a launch of this workload whose algorithmic bytes were
+        # measured 225 719 552 B for a launch of this workload whose algorithmic bytes were
         # 219 225 088 B (profiles/sections_decode_kernels_hashattention.md); traffic grows with
         # the rows gathered, so the launch timed here is scaled by that ratio.
         traffic, traffic_src = None, None
         if args.workload == "hashattention" and not args.small:
-            traffic = attn_bytes * (225636096.0 / 219225088.0)
+            traffic = attn_bytes * (225719552.0 / 219225088.0)
             traffic_src = ("ncu capture of one launch of this workload (read + write), scaled by "
                            "algorithmic bytes of the timed launch")
         base = None
