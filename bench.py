@@ -70,6 +70,10 @@ def make_workload(name: str, seed: int, small: bool = False):
         if small:
             return workloads.oracle_topp(seed=seed, B=1, S=8192)
         return workloads.oracle_topp(seed=seed)
+    if name == "quest":
+        if small:
+            return workloads.quest(seed=seed, B=2, S=4096)
+        return workloads.quest(seed=seed)
     if name == "pqcache":
         if small:
             return workloads.pqcache(seed=seed, S=16384, heavy=512, kmeans_iter=3)
@@ -350,6 +354,8 @@ def run_native(args) -> None:
             stage_bytes["adaptive_budget"] = B * Hq * Sq * S * esz
         if kind == "oracle_topp":        # the same for the top-p threshold
             stage_bytes["topp_select"] = B * Hq * Sq * S * esz
+        if kind == "quest_topk":         # per-page minimum and maximum of every channel, per KV head
+            stage_bytes["quest_scores"] = B * Hkv * (-(-S // prm["page_size"])) * D * esz * 2
     step_bytes = sum(stage_bytes.values())
 
     # e2e: host buffers in, host result out, incremental key append

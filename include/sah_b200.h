@@ -296,6 +296,37 @@ int sah_topp_select(const void* scores, int dtype, float scaling, const void* bi
                     int64_t S, int64_t W, const uint32_t* prev_bits, float top_p,
                     const uint16_t* exp_table, int or_prev, uint32_t* out_bits, void* stream);
 
+/* ------------------------------------------------------------------------ *
+ * Quest page top-k  (maskers/fixed/implementations/quest_top_k.py:108-196,
+ * utils/quest_utils.py)
+ * ------------------------------------------------------------------------ */
+
+/* Per-page bounds (compute_page_min_max, quest_utils.py:10-50): pmin/pmax
+ * [B][Hkv][P_cap][D] in `dtype`, page p covering keys [p*page_size, min(S, (p+1)*page_size));
+ * pages page_begin .. ceil(S/page_size)-1 are (re)computed, so appended keys cost only the
+ * pages they touch.  Bounds are kept per KV head: the reference's repeat over the query
+ * heads of a group repeats them. */
+int sah_quest_page_minmax(const void* k, int dtype, int64_t ks_b, int64_t ks_h, int64_t ks_s, int B,
+                          int Hkv, int64_t S, int D, int page_size, int64_t page_begin,
+                          int64_t P_cap, void* pmin, void* pmax, void* stream);
+/* scores[row][p] = sum_j max(q_j * pmin_j, q_j * pmax_j) in `dtype` (quest_page_scores :53-67),
+ * every product rounded to `dtype`, the sum in the order of the reference's CPU row reduction
+ * (8-lane float32 vectors, four interleaved accumulators, lanes last).  With a bias (additive
+ * attention mask shared by the heads, bias_s_h == 0) a page without any key of bias >= 0
+ * scores the lowest finite value (pages_valid :115-137, quest_top_k.py:156-170).
+ * scores is [rows][ceil(S/page_size)].  D: multiple of 8, at most 512. */
+int sah_quest_scores(const void* q, int dtype, int64_t qs_b, int64_t qs_h, int64_t qs_q,
+                     const void* pmin, const void* pmax, int64_t P_cap, int B, int Hq, int Hkv,
+                     int Sq, int64_t S, int D, int page_size, const void* bias, int64_t bias_s_b,
+                     int64_t bias_s_h, int64_t bias_s_q, void* scores, void* stream);
+/* out_bits = (prev_bits | keys of the pages set in page_bits) & {bias >= 0}
+ * (pages_to_token_mask :70-93, maximum with the previous mask and the gate by the attention
+ * mask, quest_top_k.py:178-191).  page_bits uint32 [rows][Wp]; prev_bits and bias may be NULL. */
+int sah_quest_expand(const uint32_t* page_bits, int64_t Wp, const uint32_t* prev_bits,
+                     const void* bias, int dtype, int64_t bias_s_b, int64_t bias_s_h,
+                     int64_t bias_s_q, int B, int Hq, int Sq, int64_t S, int64_t W, int page_size,
+                     uint32_t* out_bits, void* stream);
+
 /* sah_hash_topk in pieces (no additive bias): the keys of a row are cut into
  * world * chunks contiguous column ranges ("parts") -- `chunks` per rank, ranks in
  * column order -- each worked on by its own CTA.

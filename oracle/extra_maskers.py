@@ -35,6 +35,9 @@ def apply(kind, prm, st, q, k, v, scaling, attention_mask, meta) -> None:
         magicpig.apply(prm, st, q, k, meta)
     elif kind in ("random_sampling", "adaptive_sampling"):
         _apply_sampling(kind, prm, st, q, k, v, scaling, attention_mask, meta)
+    elif kind == "quest_topk":
+        from . import quest
+        quest.apply(prm, st, q, k, attention_mask, meta)
     elif kind == "oracle_topp":
         from . import topp
         topp.apply(prm, st, q, k, scaling, attention_mask, meta)

@@ -157,6 +157,7 @@ enum SahProfSlot {
   SAH_PROF_PQ_SCORES = 10,
   SAH_PROF_ADAPTIVE = 11,
   SAH_PROF_TOPP = 12,
+  SAH_PROF_QUEST = 13,
   SAH_PROF_SLOTS = 16
 };
 void sah_prof_begin(int slot, cudaStream_t st);

@@ -16,6 +16,8 @@ from .research_attention.maskers.fixed import (
     OracleTopPMaskerConfig,
     PQCache,
     PQCacheConfig,
+    QuestTopKMasker,
+    QuestTopKMaskerConfig,
     SinkMasker,
     SinkMaskerConfig,
     TopKMasker,
@@ -40,5 +42,5 @@ __all__ = [
     "SinkMaskerConfig", "OracleTopK", "OracleTopKConfig", "HashAttentionTopKMasker",
     "HashAttentionTopKMaskerConfig", "PQCache", "PQCacheConfig", "RandomSamplingMasker",
     "RandomSamplingMaskerConfig", "AdaptiveSamplingMasker", "AdaptiveSamplingMaskerConfig", "MagicPig",
-    "MagicPigConfig", "OracleTopPMasker", "OracleTopPMaskerConfig", "Mask",
+    "MagicPigConfig", "OracleTopPMasker", "OracleTopPMaskerConfig", "QuestTopKMasker", "QuestTopKMaskerConfig", "Mask",
 ]

@@ -20,6 +20,8 @@ from .implementations import (
     OracleTopPMaskerConfig,
     PQCache,
     PQCacheConfig,
+    QuestTopKMasker,
+    QuestTopKMaskerConfig,
     SinkMasker,
     SinkMaskerConfig,
 )
@@ -28,5 +30,5 @@ __all__ = [
     "FixedMasker", "TopKMasker", "TopPMasker", "FixedMaskerConfig", "TopKMaskerConfig",
     "TopPMaskerConfig", "LocalMasker", "CausalMasker", "SinkMasker", "OracleTopK",
     "HashAttentionTopKMasker", "LocalMaskerConfig", "SinkMaskerConfig", "OracleTopKConfig",
-    "HashAttentionTopKMaskerConfig", "PQCache", "PQCacheConfig", "OracleTopPMasker", "OracleTopPMaskerConfig",
+    "HashAttentionTopKMaskerConfig", "PQCache", "PQCacheConfig", "OracleTopPMasker", "OracleTopPMaskerConfig", "QuestTopKMasker", "QuestTopKMaskerConfig",
 ]

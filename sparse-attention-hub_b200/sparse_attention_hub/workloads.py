@@ -163,6 +163,16 @@ def oracle_topp(seed: int = 0, dtype: str = "bf16", B: int = 4, Hq: int = 32, Hk
     return wl
 
 
+def quest(seed: int = 0, dtype: str = "bf16", B: int = 8, Hq: int = 32, Hkv: int = 8, S: int = 32768,
+          D: int = 128, sink: int = 128, window: int = 512, heavy=0.05, page_size: int = 64,
+          Sq: int = 1) -> DecodeWorkload:
+    """Sink + Local + Quest page top-k on clustered keys (the shape of the HashAttention workload)."""
+    wl = oracle_topk(seed, dtype, B, Hq, Hkv, S, D, sink, window, 0.02, Sq)
+    wl.name = "quest_" + dtype
+    wl.stack = wl.stack[:2] + [("quest_topk", {"heavy_size": heavy, "page_size": page_size})]
+    return wl
+
+
 def oracle_adaptive(seed: int = 0, dtype: str = "bf16", B: int = 4, Hq: int = 32, Hkv: int = 8,
                     S: int = 65536, D: int = 128, sink: int = 128, window: int = 512, heavy=0.02,
                     base_rate=0.05, epsilon: float = 0.05, delta: float = 0.05,
@@ -269,6 +279,9 @@ def masker_configs(stack: List[Tuple[str, Dict[str, Any]]], dtype: str, device="
             out.append(fixed.OracleTopKConfig(heavy_size=prm["heavy_size"]))
         elif kind == "oracle_topp":
             out.append(fixed.OracleTopPMaskerConfig(top_p=prm["top_p"]))
+        elif kind == "quest_topk":
+            out.append(fixed.QuestTopKMaskerConfig(heavy_size=prm["heavy_size"], page_size=prm["page_size"],
+                                                   label_bits=prm.get("label_bits", 16)))
         elif kind == "hash_topk":
             w = {0: {name: [to_torch(a, dtype, device) for a in arrs]
                      for name, arrs in prm["weights"].items()}}
