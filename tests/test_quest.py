@@ -72,7 +72,7 @@ def test_config_and_rules_cpu():
 
 
 # ------------------------------------------------------------------ GPU
-def _native_stack(wl, stack, am, meta):
+def _native_stack(wl, stack, am, meta, with_out=True):
     import torch
     from sparse_attention_hub.sparse_attention.utils.mask_attention_utils import get_masked_attention_output
 
@@ -81,10 +81,13 @@ def _native_stack(wl, stack, am, meta):
     q, k, v = (workloads.to_torch(a, wl.dtype, dev) for a in (wl.q, wl.k, wl.v))
     amt = None if am is None else workloads.to_torch(am, wl.dtype, dev)
     mask = ra.build_mask(q, k, v, amt, float(wl.scaling), 0.0, meta, layer_idx=0)
-    out = get_masked_attention_output(None, q, k, v, amt, None, float(wl.scaling), 0.0, mask)
+    out = None
+    if with_out:
+        out = get_masked_attention_output(None, q, k, v, amt, None, float(wl.scaling), 0.0, mask)
+        out = out.float().cpu().numpy()
     torch.cuda.synchronize()
     idx, ptr, data = mask.get_index_mask()
-    return (idx.cpu().numpy(), ptr.cpu().numpy(), data.float().cpu().numpy()), out.float().cpu().numpy()
+    return (idx.cpu().numpy(), ptr.cpu().numpy(), data.float().cpu().numpy()), out
 
 
 @pytest.mark.gpu
@@ -131,11 +134,13 @@ def test_gpu_page_scores_and_mask_against_restatement(dtype, S, D, page, heavy, 
                                        pmax.data_ptr(), P, 1, 8, 4, Sq, S, D, page, None, 0, 0, 0,
                                        sc.data_ptr(), st), "scores")
     np.testing.assert_array_equal(sc.float().cpu().numpy(), meta["quest_page_scores"])
-    got, out = _native_stack(wl, stack, None, {})
+    attend = D in (64, 128)     # the attention kernels take head dimensions 64 and 128
+    got, out = _native_stack(wl, stack, None, {}, with_out=attend)
     ri, rp, rd = mask_ops.to_csr(ref_mask)
     np.testing.assert_array_equal(got[0], ri)
     np.testing.assert_array_equal(got[1], rp)
-    np.testing.assert_allclose(out, ref_out, atol=1e-4 if dtype == "f32" else 2e-2, rtol=2e-2)
+    if attend:
+        np.testing.assert_allclose(out, ref_out, atol=1e-4 if dtype == "f32" else 2e-2, rtol=2e-2)
 
 
 @pytest.mark.gpu
@@ -150,7 +155,7 @@ def test_gpu_appended_keys_update_only_their_pages():
     ra = workloads.research_attention(stack, "bf16", dev)
     q, k, v = (workloads.to_torch(a, "bf16", dev) for a in (wl.q, wl.k, wl.v))
     meta: dict = {}
-    for n in (1000, 1001, 1037, 1500):     # growth inside a page, across pages, and past the capacity
+    for n in (600, 601, 640, 1500):        # growth inside a page, across pages, and past the capacity
         mask = ra.build_mask(q, k[:, :, :n], v[:, :, :n], None, float(wl.scaling), 0.0, meta, layer_idx=0)
         fresh = ra.build_mask(q, k[:, :, :n], v[:, :, :n], None, float(wl.scaling), 0.0, {}, layer_idx=0)
         assert meta["quest_pages"][0]["n_keys"] == n
