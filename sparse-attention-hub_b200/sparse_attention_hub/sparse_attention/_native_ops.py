@@ -63,8 +63,12 @@ def bits_andnot(a: NativeBits, b: NativeBits) -> NativeBits:
 
 
 def topk_select(scores: torch.Tensor, previous_mask: Mask, k: int, col_begin: int = 0,
-                col_end: Optional[int] = None, out: Optional[NativeBits] = None) -> NativeBits:
-    """previous | top-k of `scores` over inactive columns in [col_begin, col_end)."""
+                col_end: Optional[int] = None, out: Optional[NativeBits] = None,
+                per_row: bool = False) -> NativeBits:
+    """previous | top-k of `scores` over inactive columns in [col_begin, col_end).
+
+    `per_row`: one CTA per row in a single launch instead of rows spread over many CTAs with
+    histograms in a scratch buffer; the better choice for many short rows (page scores)."""
     _native.require_cuda(scores, "scores")
     lib = _native.load()
     S = scores.shape[-1]
@@ -74,7 +78,7 @@ def topk_select(scores: torch.Tensor, previous_mask: Mask, k: int, col_begin: in
     sc = scores.contiguous()
     st = _native.stream_of(sc.device)
     end = S if col_end is None else col_end
-    if rows <= 65535:
+    if rows <= 65535 and not per_row:
         # rows are spread over many CTAs; the histograms live in a scratch buffer
         nbytes = int(lib.sah_topk_select_ws_bytes(rows, prev.words))
         ws = torch.empty(nbytes, dtype=torch.uint8, device=sc.device)

@@ -138,7 +138,8 @@ class QuestTopKMasker(TopKMasker):
         if k_pages <= 0:
             k_pages = 1
         no_pages = Mask.create_empty_mask((B, Hq, Sq, P), previous_mask.dtype, dev)
-        picked = _native_ops.topk_select(scores, no_pages, k_pages)      # bitmap over pages
+        # bitmap over pages; rows of a few hundred to a few thousand page scores: one CTA each
+        picked = _native_ops.topk_select(scores, no_pages, k_pages, per_row=(P <= 8192))
         unit = _native_ops.unit_weight_bits(previous_mask)
         prev = previous_mask.native_bits()
         out = _native_ops.NativeBits(torch.empty_like(prev.bits), prev.rows, S)

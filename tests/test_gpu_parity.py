@@ -190,6 +190,28 @@ def test_topk_select_ties_and_short_rows():
     assert Mask._from_native((1, 3, 1, S), torch.float32, everything).get_density() == 1.0
 
 
+@pytest.mark.parametrize("dtype,S,rows_h,k", [("bf16", 512, 40, 25), ("f32", 700, 9, 60), ("bf16", 5000, 5, 333),
+                                              ("f32", 33, 3, 40)])
+def test_topk_select_one_cta_per_row_equals_chunked(dtype, S, rows_h, k):
+    """Both exact top-k paths give the same bitmap, previous mask and ties included."""
+    rng = np.random.default_rng(S + k)
+    x = rng.normal(size=(1, rows_h, 1, S)).astype(np.float32)
+    x[0, 0, 0, : S // 2] = np.round(x[0, 0, 0, : S // 2])       # many ties
+    sc = workloads.to_torch(workloads.to_dtype(x, dtype), dtype, DEV)
+    shape = (1, rows_h, 1, S)
+    prev_np = np.zeros(shape, np.float32)
+    prev_np[..., :5] = 1.0
+    tdt = torch.bfloat16 if dtype == "bf16" else torch.float32
+    prev = Mask.create_mask_from_dense_mask(shape, torch.from_numpy(prev_np).to(DEV).to(tdt), tdt)
+    a = _native_ops.topk_select(sc, prev, k)
+    b = _native_ops.topk_select(sc, prev, k, per_row=True)
+    assert torch.equal(a.bits, b.bits)
+    from oracle import topk as ot
+    want = ot.topk_inactive(sc.float().cpu().numpy(), prev_np != 0, k) | (prev_np != 0)
+    got = Mask._from_native(shape, tdt, b).get_dense_mask().float().cpu().numpy() != 0
+    np.testing.assert_array_equal(got, want)
+
+
 # ---------------------------------------------------------------------------
 def test_mask_conversions_round_trip():
     rng = np.random.default_rng(5)
