@@ -89,6 +89,13 @@ int sah_mask_fill_band(uint32_t* bits, int64_t rows, int Sq, int64_t S, int64_t 
                        int64_t lo_base, int64_t lo_qstep, int64_t hi_base,
                        int64_t hi_qstep, int value, void* stream);
 
+/* Several band edits in one pass over the bitmap: bands is a HOST array of n_bands (<= 6)
+ * quintuples (lo_base, lo_qstep, hi_base, hi_qstep, value), applied in order with the
+ * meaning of sah_mask_fill_band; with init_zero != 0 the bitmap's previous contents are
+ * ignored (it starts empty), so a fresh mask needs no separate clear. */
+int sah_mask_fill_bands(uint32_t* bits, int64_t rows, int Sq, int64_t S, int64_t W, int n_bands,
+                        const int64_t* bands, int init_zero, void* stream);
+
 /* ptr[rows+1] and (optionally, may be NULL) wpre[rows][W] from bits.
  * Replaces the nonzero/count_nonzero/cumsum chain of Mask.get_index_mask
  * (utils/mask.py:553-573). */

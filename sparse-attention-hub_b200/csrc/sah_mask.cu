@@ -125,6 +125,65 @@ extern "C" int sah_mask_fill_band(uint32_t* bits, int64_t rows, int Sq, int64_t 
   return SAH_OK;
 }
 
+// ---- several band fills in one pass ------------------------------------------
+// A stack of fixed-pattern maskers (sink, local window, ...) is a short list of band edits on a
+// bitmap that starts empty: one launch writes every word once, applying the bands in order.
+#define SAH_MAX_BANDS 6
+struct MaskBands {
+  int n;
+  int64_t lo_base[SAH_MAX_BANDS], lo_qstep[SAH_MAX_BANDS], hi_base[SAH_MAX_BANDS], hi_qstep[SAH_MAX_BANDS];
+  int value[SAH_MAX_BANDS];
+};
+
+__global__ void mask_fill_bands_kernel(uint32_t* __restrict__ bits, int64_t rows, int Sq, int64_t S,
+                                       int64_t W, MaskBands bands, int init_zero) {
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= rows * W) return;
+  const int64_t row = t / W;
+  const int64_t w = t - row * W;
+  const int64_t q = row % Sq;
+  const int64_t c0 = w * 32, c1 = c0 + 32;
+  uint32_t v = init_zero ? 0u : bits[t];
+#pragma unroll
+  for (int i = 0; i < SAH_MAX_BANDS; ++i) {
+    if (i >= bands.n) break;
+    int64_t lo = bands.lo_base[i] + q * bands.lo_qstep[i];
+    int64_t hi = bands.hi_base[i] + q * bands.hi_qstep[i];
+    if (lo < 0) lo = 0;
+    if (hi > S) hi = S;
+    if (hi <= c0 || lo >= c1 || lo >= hi) continue;
+    const int64_t a = lo > c0 ? lo - c0 : 0;        // first bit in word
+    const int64_t b = hi < c1 ? hi - c0 : 32;       // one past last bit
+    const uint32_t m = (b >= 32 ? 0xffffffffu : ((1u << b) - 1u)) & ~((1u << a) - 1u);
+    if (bands.value[i]) v |= m; else v &= ~m;
+  }
+  bits[t] = v;
+}
+
+extern "C" int sah_mask_fill_bands(uint32_t* bits, int64_t rows, int Sq, int64_t S, int64_t W,
+                                   int n_bands, const int64_t* bands, int init_zero, void* stream) {
+  SAH_REQUIRE(bits != nullptr, "fill_bands: bits is null");
+  SAH_REQUIRE(rows >= 0 && Sq > 0 && S > 0 && W * 32 >= S, "fill_bands: bad extents");
+  SAH_REQUIRE(n_bands >= 0 && n_bands <= SAH_MAX_BANDS && (n_bands == 0 || bands != nullptr),
+              "fill_bands: 0..%d bands", SAH_MAX_BANDS);
+  if (rows == 0 || (n_bands == 0 && !init_zero)) return SAH_OK;
+  MaskBands mb;
+  mb.n = n_bands;
+  for (int i = 0; i < SAH_MAX_BANDS; ++i) {
+    const bool on = i < n_bands;
+    mb.lo_base[i] = on ? bands[5 * i + 0] : 0;
+    mb.lo_qstep[i] = on ? bands[5 * i + 1] : 0;
+    mb.hi_base[i] = on ? bands[5 * i + 2] : 0;
+    mb.hi_qstep[i] = on ? bands[5 * i + 3] : 0;
+    mb.value[i] = on ? (int)bands[5 * i + 4] : 0;
+  }
+  const int64_t total = rows * W;
+  mask_fill_bands_kernel<<<(unsigned)sah_ceil_div(total, 256), 256, 0, (cudaStream_t)stream>>>(
+      bits, rows, Sq, S, W, mb, init_zero);
+  SAH_LAUNCH_CHECK("mask_fill_bands");
+  return SAH_OK;
+}
+
 // ---- row scan: wpre (per word exclusive popcount) and ptr --------------------
 // One CTA per row; the running base carries across blockDim-word chunks.
 __global__ void mask_rowscan_kernel(const uint32_t* __restrict__ bits, int64_t W,

@@ -61,6 +61,7 @@ _L = c_int64
 # name -> argument types (all functions return int status unless noted)
 _SIGNATURES = {
     "sah_mask_fill_band": [_P, _L, _I, _L, _L, _L, _L, _L, _L, _I, _P],
+    "sah_mask_fill_bands": [_P, _L, _I, _L, _L, _I, _P, _I, _P],
     "sah_mask_rowscan": [_P, _L, _L, _P, _P, _P],
     "sah_mask_bits_to_indices": [_P, _P, _P, _L, _L, _L, _P, _P],
     "sah_mask_bits_to_dense": [_P, _P, _P, _P, _I, _L, _L, _L, _P, _P],

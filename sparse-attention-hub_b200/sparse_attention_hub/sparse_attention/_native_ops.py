@@ -41,20 +41,14 @@ def unit_weight_bits(previous_mask: Mask) -> Optional[NativeBits]:
 
 
 def fresh_native(nb: NativeBits) -> NativeBits:
-    """Same bitmap storage, CSR companions dropped (call after editing the bits)."""
-    return NativeBits(nb.bits, nb.rows, nb.n_cols, data=None)
+    """Same bitmap storage (and pending band edits), CSR companions dropped."""
+    return nb.share()
 
 
 def fill_band(nb: NativeBits, seq_len_queries: int, lo_base: int, lo_qstep: int, hi_base: int,
               hi_qstep: int, value: int) -> None:
-    lib = _native.load()
-    dev = nb.bits.device
-    _native.check(
-        lib.sah_mask_fill_band(nb.bits.data_ptr(), nb.rows, seq_len_queries, nb.n_cols, nb.words,
-                               lo_base, lo_qstep, hi_base, hi_qstep, value, _native.stream_of(dev)),
-        "sah_mask_fill_band")
-    nb.ptr = None  # the CSR companions describe the old bits
-    nb.wpre = None
+    """Band edit of a unit-weight bitmap; applied with the next flush of its pending edits."""
+    nb.add_band(seq_len_queries, lo_base, lo_qstep, hi_base, hi_qstep, value)
 
 
 def bits_andnot(a: NativeBits, b: NativeBits) -> NativeBits:

@@ -40,13 +40,24 @@ def words_per_row(n_cols: int) -> int:
 
 
 class NativeBits:
-    """Device bitmap of a mask plus its lazily built CSR companions."""
+    """Device bitmap of a mask plus its lazily built CSR companions.
 
-    __slots__ = ("bits", "data", "ptr", "wpre", "rows", "n_cols", "words")
+    Band edits (sink, local window: `add_band`) and the clearing of a fresh bitmap are not
+    launched one by one: they are noted and applied by a single kernel when the words are first
+    needed (`bits`).  Objects made by `share()` see the same storage and the same notes.
+    """
+
+    __slots__ = ("_bits", "_lazy", "data", "ptr", "wpre", "rows", "n_cols", "words")
+
+    MAX_BANDS = 6
 
     def __init__(self, bits: torch.Tensor, rows: int, n_cols: int,
-                 data: Optional[torch.Tensor] = None) -> None:
-        self.bits = bits          # int32 tensor holding uint32 words, [rows, W]
+                 data: Optional[torch.Tensor] = None, zero_pending: bool = False) -> None:
+        self._bits = bits         # int32 tensor holding uint32 words, [rows, W]
+        # edits not yet applied to the storage: {"zero": the storage is uninitialised and stands
+        # for an empty bitmap, "sq": query rows per (batch, head), "bands": [(lo_base, lo_qstep,
+        # hi_base, hi_qstep, value), ...]}
+        self._lazy = {"zero": bool(zero_pending), "sq": 1, "bands": []}
         self.rows = rows
         self.n_cols = n_cols
         self.words = bits.shape[-1]
@@ -54,12 +65,69 @@ class NativeBits:
         self.ptr: Optional[torch.Tensor] = None
         self.wpre: Optional[torch.Tensor] = None
 
+    @classmethod
+    def empty(cls, rows: int, n_cols: int, device: torch.device) -> "NativeBits":
+        """An all-zero bitmap whose clearing is deferred to the first band flush."""
+        words = words_per_row(n_cols)
+        return cls(torch.empty((rows, words), dtype=torch.int32, device=device), rows, n_cols,
+                   zero_pending=True)
+
+    def share(self) -> "NativeBits":
+        """Same storage and pending edits, CSR companions dropped."""
+        other = NativeBits(self._bits, self.rows, self.n_cols)
+        other._lazy = self._lazy
+        return other
+
+    @property
+    def device(self) -> torch.device:
+        return self._bits.device
+
+    @property
+    def bits(self) -> torch.Tensor:
+        if self._lazy["zero"] or self._lazy["bands"]:
+            self.flush()
+        return self._bits
+
+    @bits.setter
+    def bits(self, value: torch.Tensor) -> None:
+        self._bits = value
+        self._lazy = {"zero": False, "sq": 1, "bands": []}
+
+    def add_band(self, seq_len_queries: int, lo_base: int, lo_qstep: int, hi_base: int,
+                 hi_qstep: int, value: int) -> None:
+        """Note a band edit (meaning of `sah_mask_fill_band`); valid for unit-weight masks."""
+        lazy = self._lazy
+        if lazy["bands"] and (lazy["sq"] != seq_len_queries or len(lazy["bands"]) >= self.MAX_BANDS):
+            self.flush()
+        lazy["sq"] = seq_len_queries
+        lazy["bands"].append((int(lo_base), int(lo_qstep), int(hi_base), int(hi_qstep), int(value)))
+        self.ptr = None   # the CSR companions describe the old bits
+        self.wpre = None
+
+    def flush(self) -> None:
+        """Apply the pending clear and band edits with one launch."""
+        lazy = self._lazy
+        bands = lazy["bands"]
+        if not lazy["zero"] and not bands:
+            return
+        import ctypes
+
+        lib = _native.load()
+        flat = [x for band in bands for x in band]
+        arr = (ctypes.c_int64 * max(len(flat), 1))(*flat)
+        _native.check(
+            lib.sah_mask_fill_bands(self._bits.data_ptr(), self.rows, lazy["sq"], self.n_cols, self.words,
+                                    len(bands), arr, int(lazy["zero"]),
+                                    _native.stream_of(self._bits.device)), "sah_mask_fill_bands")
+        lazy["zero"] = False
+        lazy["bands"] = []
+
     def ensure_scan(self) -> None:
         """Fill ptr (int64 [rows+1]) and wpre (int32 [rows, W])."""
         if self.ptr is not None:
             return
         lib = _native.load()
-        dev = self.bits.device
+        dev = self._bits.device
         self.ptr = torch.empty(self.rows + 1, dtype=torch.int64, device=dev)
         self.wpre = torch.empty((self.rows, self.words), dtype=torch.int32, device=dev)
         _native.check(
@@ -206,7 +274,7 @@ class Mask:
     @classmethod
     def _from_native(cls, shape, dtype, native: NativeBits) -> "Mask":
         """Dense-semantics mask whose payload is a device bitmap (native maskers)."""
-        m = cls(shape=shape, dtype=dtype, device=native.bits.device, is_empty=True)
+        m = cls(shape=shape, dtype=dtype, device=native.device, is_empty=True)
         m.is_empty = False
         m.from_dense_mask = True
         m._native = native
@@ -388,7 +456,7 @@ class Mask:
         lib = _native.load()
         st = _native.stream_of(dev)
         if self.is_empty:
-            return NativeBits(torch.zeros((rows, words), dtype=torch.int32, device=dev), rows, n)
+            return NativeBits.empty(rows, n, dev)
         if self.is_full:
             bits = torch.zeros((rows, words), dtype=torch.int32, device=dev)
             _native.check(lib.sah_mask_fill_band(bits.data_ptr(), rows, 1, n, words, 0, 0, n, 0, 1, st),
