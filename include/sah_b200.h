@@ -309,7 +309,8 @@ int sah_topp_select(const void* scores, int dtype, float scaling, const void* bi
  * ------------------------------------------------------------------------ */
 
 /* Per-page bounds (compute_page_min_max, quest_utils.py:10-50): pmin/pmax
- * [B][Hkv][P_cap][D] in `dtype`, page p covering keys [p*page_size, min(S, (p+1)*page_size));
+ * [B][Hkv][D/8][P_cap][8] in `dtype` (channel d of page p at chunk d/8, slot d%8; D a multiple
+ * of 8), page p covering keys [p*page_size, min(S, (p+1)*page_size));
  * pages page_begin .. ceil(S/page_size)-1 are (re)computed, so appended keys cost only the
  * pages they touch.  Bounds are kept per KV head: the reference's repeat over the query
  * heads of a group repeats them. */

@@ -3,7 +3,9 @@
 // q.k per page from them, top pages, pages expanded to keys.
 //
 // The page bounds are kept per KV head (the reference repeats the keys over the query heads of
-// a group first, which repeats the bounds).  The bound is a sum over the head dimension of
+// a group first, which repeats the bounds), as [B][Hkv][D/8][page capacity][8]: the scoring
+// kernel has one thread per page, and with eight channels of consecutive pages next to each
+// other its 16-byte loads are coalesced.  The bound is a sum over the head dimension of
 // dtype-rounded products; it is taken in the order of the reference's CPU row reduction so that
 // page scores, and with them the chosen pages, are the reference's bit for bit: float32
 // accumulation in vectors of 8 lanes (a bfloat16 load brings 16 elements and adds its two
@@ -29,7 +31,7 @@ __global__ void quest_minmax_kernel(const T* __restrict__ k, int64_t ks_b, int64
       lo = fminf(lo, x);
       hi = fmaxf(hi, x);
     }
-    const int64_t o = ((b * Hkv + h) * P_cap + page) * D + d;
+    const int64_t o = ((((b * Hkv + h) * (D / 8) + d / 8) * P_cap + page) << 3) + (d & 7);
     pmin[o] = sah_from_float<T>(lo);
     pmax[o] = sah_from_float<T>(hi);
   }
@@ -40,7 +42,8 @@ extern "C" int sah_quest_page_minmax(const void* k, int dtype, int64_t ks_b, int
                                      int64_t page_begin, int64_t P_cap, void* pmin, void* pmax,
                                      void* stream) {
   SAH_REQUIRE(k && pmin && pmax, "quest_page_minmax: null pointer");
-  SAH_REQUIRE(B > 0 && Hkv > 0 && S > 0 && D > 0 && page_size > 0, "quest_page_minmax: bad extents");
+  SAH_REQUIRE(B > 0 && Hkv > 0 && S > 0 && D > 0 && D % 8 == 0 && page_size > 0,
+              "quest_page_minmax: bad extents (the head dimension must be a multiple of 8)");
   const int64_t P = sah_ceil_div(S, page_size);
   SAH_REQUIRE(page_begin >= 0 && page_begin <= P && P <= P_cap, "quest_page_minmax: bad page range");
   SAH_REQUIRE(Hkv <= 65535 && B <= 65535, "quest_page_minmax: too many heads or batches");
@@ -83,8 +86,10 @@ quest_scores_kernel(const T* __restrict__ q, int64_t qs_b, int64_t qs_h, int64_t
   const int64_t P = (S + page_size - 1) / page_size;
   const int64_t page = (int64_t)blockIdx.x * QS_THREADS + threadIdx.x;
   if (page >= P) return;
-  const T* lo = pmin + ((b * Hkv + kvh) * P_cap + page) * D;
-  const T* hi = pmax + ((b * Hkv + kvh) * P_cap + page) * D;
+  // chunk c (channels 8c .. 8c+7) of this page: base + (c * P_cap + page) * 8
+  const T* lo = pmin + (b * Hkv + kvh) * (int64_t)D * P_cap + page * 8;
+  const T* hi = pmax + (b * Hkv + kvh) * (int64_t)D * P_cap + page * 8;
+  const int64_t cstride = P_cap * 8;
 
   constexpr int VEC = QuestVec<T>::N;
   const int nv = D / VEC;
@@ -101,8 +106,8 @@ quest_scores_kernel(const T* __restrict__ q, int64_t qs_b, int64_t qs_h, int64_t
 #pragma unroll
     for (int half = 0; half < VEC / 8; ++half) {
       const int j0 = v * VEC + half * 8;
-      sah_load8<T>(lo + j0, a);
-      sah_load8<T>(hi + j0, c);
+      sah_load8<T>(lo + (j0 >> 3) * cstride, a);
+      sah_load8<T>(hi + (j0 >> 3) * cstride, c);
 #pragma unroll
       for (int l = 0; l < 8; ++l) {
         const float qv = q_sm[j0 + l];
@@ -133,8 +138,9 @@ quest_scores_kernel(const T* __restrict__ q, int64_t qs_b, int64_t qs_h, int64_t
   float fin = 0.f;
   for (int j = nv * VEC; j < D; ++j) {   // elements past the last whole vector come first
     const float qv = q_sm[j];
-    const float m = fmaxf(sah_round_to<T>(__fmul_rn(qv, sah_to_float<T>(lo[j]))),
-                          sah_round_to<T>(__fmul_rn(qv, sah_to_float<T>(hi[j]))));
+    const int64_t o = (j >> 3) * cstride + (j & 7);
+    const float m = fmaxf(sah_round_to<T>(__fmul_rn(qv, sah_to_float<T>(lo[o]))),
+                          sah_round_to<T>(__fmul_rn(qv, sah_to_float<T>(hi[o]))));
     fin = __fadd_rn(fin, m);
   }
 #pragma unroll

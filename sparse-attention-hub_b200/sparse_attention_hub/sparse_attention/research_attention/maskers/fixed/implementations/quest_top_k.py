@@ -80,6 +80,8 @@ class QuestTopKMasker(TopKMasker):
         _native.require_cuda(keys, "keys")
         lib = _native.load()
         B, Hkv, S, D = keys.shape
+        if D % 8 != 0:
+            raise NotImplementedError(f"QuestTopKMasker: head dimension {D} (multiples of 8)")
         k = keys if keys.stride(-1) == 1 else keys.contiguous()
         ps = self.page_size
         P = -(-S // ps)
@@ -92,13 +94,14 @@ class QuestTopKMasker(TopKMasker):
             cap = max(P + P // 2, 16)
             state = {"shape": (B, Hkv, D), "dtype": k.dtype, "page_size": ps, "n_keys": 0, "cap": cap,
                      "device": k.device,
-                     "pmin": torch.empty((B, Hkv, cap, D), dtype=k.dtype, device=k.device),
-                     "pmax": torch.empty((B, Hkv, cap, D), dtype=k.dtype, device=k.device)}
+                     # [B, Hkv, D/8, page capacity, 8]: eight channels of consecutive pages adjoin
+                     "pmin": torch.empty((B, Hkv, D // 8, cap, 8), dtype=k.dtype, device=k.device),
+                     "pmax": torch.empty((B, Hkv, D // 8, cap, 8), dtype=k.dtype, device=k.device)}
         elif P > state["cap"]:
             cap = P + P // 2
             for name in ("pmin", "pmax"):
-                grown = torch.empty((B, Hkv, cap, D), dtype=k.dtype, device=k.device)
-                grown[:, :, : state["cap"]] = state[name]
+                grown = torch.empty((B, Hkv, D // 8, cap, 8), dtype=k.dtype, device=k.device)
+                grown[:, :, :, : state["cap"]] = state[name]
                 state[name] = grown
             state["cap"] = cap
         first = state["n_keys"] // ps   # the page the first new key falls into

@@ -120,15 +120,15 @@ def test_gpu_page_scores_and_mask_against_restatement(dtype, S, D, page, heavy, 
     dev = torch.device("cuda:0")
     q, k = (workloads.to_torch(a, dtype, dev) for a in (wl.q, wl.k))
     P = -(-S // page)
-    pmin = torch.empty((1, 4, P, D), dtype=q.dtype, device=dev)
+    pmin = torch.empty((1, 4, D // 8, P, 8), dtype=q.dtype, device=dev)   # [B, Hkv, D/8, pages, 8]
     pmax = torch.empty_like(pmin)
     st = _native.stream_of(dev)
     code = _native.dtype_code(q.dtype)
     _native.check(lib.sah_quest_page_minmax(k.data_ptr(), code, k.stride(0), k.stride(1), k.stride(2), 1, 4, S, D,
                                             page, 0, P, pmin.data_ptr(), pmax.data_ptr(), st), "minmax")
     lo, hi = quest.page_min_max(np.asarray(wl.k, np.float32), page)
-    np.testing.assert_array_equal(pmin.float().cpu().numpy(), lo)
-    np.testing.assert_array_equal(pmax.float().cpu().numpy(), hi)
+    np.testing.assert_array_equal(pmin.permute(0, 1, 3, 2, 4).reshape(1, 4, P, D).float().cpu().numpy(), lo)
+    np.testing.assert_array_equal(pmax.permute(0, 1, 3, 2, 4).reshape(1, 4, P, D).float().cpu().numpy(), hi)
     sc = torch.empty((1, 8, Sq, P), dtype=q.dtype, device=dev)
     _native.check(lib.sah_quest_scores(q.data_ptr(), code, q.stride(0), q.stride(1), q.stride(2), pmin.data_ptr(),
                                        pmax.data_ptr(), P, 1, 8, 4, Sq, S, D, page, None, 0, 0, 0,
