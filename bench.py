@@ -102,20 +102,30 @@ class ClockSampler:
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int) -> None:
+    def __init__(self, index: int, enabled: bool = True) -> None:
         self.index = index
+        self.enabled = enabled   # one sampler per job (rank 0) is enough
         self.proc = None
         self.lines: list = []
+        self.first = 0           # lines before the timed region started
         self.thread = None
 
     def __enter__(self):
+        if not self.enabled:
+            return self
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100", "-i", str(self.index)],
+                 "-lms", "25", "-i", str(self.index)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
+            # nvidia-smi needs a moment to enumerate the devices (seconds on an 8-GPU host):
+            # the timed region starts once it delivers samples
+            t0 = time.perf_counter()
+            while not self.lines and time.perf_counter() - t0 < 15.0:
+                time.sleep(0.02)
+            self.first = len(self.lines)
         except OSError:
             self.proc = None
         return self
@@ -126,12 +136,18 @@ class ClockSampler:
 
     def __exit__(self, *exc):
         if self.proc is not None:
-            time.sleep(0.15)
+            # the region may be shorter than the sampling period: keep the GPU busy state
+            # visible by waiting for at least one sample taken after it started
+            t0 = time.perf_counter()
+            while len(self.lines) < self.first + 2 and time.perf_counter() - t0 < 1.0:
+                time.sleep(0.02)
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=5)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
+            if len(self.lines) > self.first:
+                self.lines = self.lines[self.first:]
 
     def summary(self) -> dict:
         sm, mx, reasons = [], [], set()
@@ -318,7 +334,8 @@ def run_native(args) -> None:
     launches_per_step = _native.launch_count() - launches0
     torch.cuda.synchronize()
     barrier()
-    with ClockSampler(local_rank) as clocks:
+    with ClockSampler(local_rank, enabled=(rank == 0)) as clocks:
+        barrier()   # rank 0 may have waited for the sampler's first line
         per_step_ms = timed_loop(args.steps)
     barrier()
     launches = launches_per_step * args.steps
@@ -640,7 +657,8 @@ def run_long_native(args) -> None:
         for _ in range(3):
             step()
         barrier()
-    with ClockSampler(local_rank) as clocks:
+    with ClockSampler(local_rank, enabled=(rank == 0)) as clocks:
+        barrier()   # rank 0 may have waited for the sampler's first line
         per_step_ms = timed_loop(args.steps)
     barrier()
     total_ms = float(sum(per_step_ms))
