@@ -137,6 +137,14 @@ int sah_mask_sample_data(const uint32_t* prev_bits, const uint32_t* out_bits,
                          const void* dense_weight, int dtype, int64_t rows, int64_t S,
                          int64_t W, void* data, void* stream);
 
+/* data[entry] = 1 for every entry of `bits` whose column is also set in unit_bits
+ * (other entries keep their value): the clamp(previous + p, 0, 1) of
+ * Mask.merge_mask_dense (utils/mask.py:875-877) for a unit-weight previous mask and
+ * probabilities p <= 1 that were written for every entry of the joined set. */
+int sah_mask_unit_data(const uint32_t* bits, const uint32_t* unit_bits, const int32_t* wpre,
+                       const int64_t* ptr, int dtype, int64_t rows, int64_t W, void* data,
+                       void* stream);
+
 /* Scatter a ragged list of sampled columns into a bitmap.  sample j belongs
  * to the row r with sptr[r] <= j < sptr[r+1] (sptr int64 [rows+1], device);
  * cols int64 [n].  Duplicates collapse, as the dense conversion of the
@@ -425,15 +433,21 @@ int sah_lsh_key_sign(const void* keys, int dtype, int64_t ks_b, int64_t ks_h, in
 
 /* Per mask row (b, h, q): centred query normalised to unit length, its L codes
  * (qcodes [rows][L], same code type as the planes) and the unit vector of the
- * transformed query (qunit float [rows][D]; the appended column is zero). */
+ * transformed query (qunit float [rows][D]; the appended column is zero).
+ * Optional (NULL to skip): qhat [rows][D], the same unit vector in `dtype` (its values
+ * are representable, so nothing is lost), and qmu float [rows] = qunit . mean; both
+ * feed sah_masked_attention_lsh. */
 int sah_lsh_query(const void* q, int dtype, int64_t qs_b, int64_t qs_h, int64_t qs_q, int B, int Hq,
                   int Sq, int G, int D, const void* mean, const void* proj, int L, int K,
-                  void* qcodes, float* qunit, void* stream);
+                  void* qcodes, float* qunit, void* qhat, float* qmu, void* stream);
 
 /* out_bits[row][w]: keys whose code equals the query's in at least one table
- * (_compute_matches_int64, :455-463).  Every word of every row is written. */
+ * (_compute_matches_int64, :455-463), joined with prev_bits[row][w] when prev_bits is
+ * not NULL (the active set of the dense merge with the previous mask, :593).  Every
+ * word of every row is written. */
 int sah_lsh_match(const void* planes, int64_t cap, const void* qcodes, int B, int Hq, int Sq, int G,
-                  int L, int K, int64_t S, int64_t W, uint32_t* out_bits, void* stream);
+                  int L, int K, int64_t S, int64_t W, const uint32_t* prev_bits, uint32_t* out_bits,
+                  int sm_count, void* stream);
 
 /* data[ptr[row] + i] = collision probability 1 - (1 - (1 - theta/pi)^K)^L of the
  * i-th set bit of the row (:374-403), theta the angle between the transformed
@@ -521,11 +535,16 @@ typedef struct {
   int32_t nsplit;          /* CTAs cooperating on one group                 */
   int64_t ucols_bytes;     /* int32  [groups][S]                            */
   int64_t umemb_bytes;     /* uint16 [groups][S]                            */
-  int64_t uw_bytes;        /* float  [groups][S][rows_per_group] (if data)  */
+  int64_t uw_bytes;        /* float  [groups][S][rows_per_group] (has_data 1)
+                              or float [groups][S] (has_data 2)             */
   int64_t ucount_bytes;    /* int32  [groups] + chunk counters              */
   int64_t partial_bytes;   /* float  [groups][nsplit][rows_per_group][D+2]  */
 } sah_attn_sizes;
 
+/* has_data: 0 unit-weight mask, 1 mask with per-entry weights, 2 MagicPig mask whose
+ * weights the attention kernel evaluates (sah_attn_plan_lsh / sah_masked_attention_lsh).
+ * The counter block (ucount_bytes) ends with one merge ticket per group, which must be
+ * zero when an attention call starts (the kernel leaves them zero) and one error word. */
 int sah_attn_query_sizes(int B, int Hq, int Hkv, int Sq, int64_t S, int D, int has_data,
                          int sm_count, sah_attn_sizes* out);
 
@@ -538,6 +557,18 @@ int sah_attn_plan(const uint32_t* bits, const void* data, const int32_t* wpre,
                   const int64_t* ptr, int dtype, int B, int Hq, int Hkv, int Sq, int64_t S,
                   int64_t W, const sah_attn_sizes* sizes, int32_t* ucols, uint16_t* umemb,
                   float* uw, int32_t* ucount, void* stream);
+
+/* The same for a MagicPig mask whose weights sah_masked_attention_lsh evaluates itself
+ * (sizes queried with has_data = 2; at most 4 mask rows per KV group).  `bits` are the
+ * LSH matches (sah_lsh_match), `unit_bits` (may be NULL) what the previous maskers
+ * selected with weight 1 -- magic_pig.py:593 clamps those to 1; the active set is the
+ * union of the two.  umemb carries membership in its low byte and "weight is 1" flags in its high
+ * byte; uinv [groups][S] holds 1 / (M * dens[col]) per union entry, dens and
+ * max_norm_bits being those of sah_lsh_key_den (dens_cap = their row stride). */
+int sah_attn_plan_lsh(const uint32_t* bits, const uint32_t* unit_bits, const float* dens,
+                      int64_t dens_cap, const unsigned int* max_norm_bits, int B, int Hq, int Hkv,
+                      int Sq, int64_t S, int64_t W, const sah_attn_sizes* sizes, int32_t* ucols,
+                      uint16_t* umemb, float* uinv, int32_t* ucount, void* stream);
 
 /* out[b][q][h][:] = sum_j e_j w_j v_j / (sum_j e_j w_j [+ exp(sink_h)]),
  * e_j = exp(scaling * q.k_j + bias_j), over the planned union list; fp32
@@ -556,6 +587,29 @@ int sah_masked_attention(const void* q, const void* k, const void* v, int dtype,
                          const uint16_t* umemb, const float* uw, const int32_t* ucount,
                          float* partial, void* out, float* acc_out, float* lse_out,
                          void* stream);
+
+/* sah_masked_attention (bfloat16) over a union list made by sah_attn_plan_lsh, with the
+ * MagicPig sampling weights computed where the key row already is: the weight of a
+ * sampled key is 1 / (p + 1e-6) (Mask.apply_inv_mask_dense, utils/mask.py:718-740) with
+ * p = 1 - (1 - (1 - acos(c)/pi)^K)^L read from prob_table (uint16 [65536], bf16 bits of
+ * the clamped cosine -> bf16 bits of p, the chain of magic_pig.py:389-403) and
+ * c = (qhat . k - qmu) / (M * |transformed key|) evaluated in float32 and rounded once
+ * to bfloat16.  The reference rounds every step of that cosine to bfloat16
+ * (:332-372), so a weight can differ from the reference's by the effect of one bfloat16
+ * step of the cosine; the selected index set does not depend on the weights.
+ * qhat [rows][D] bfloat16 (16-byte aligned) and qmu [rows] come from sah_lsh_query.
+ * w_dump (optional): float [groups][S][rows_per_group], receives the weight used for
+ * every (union entry, member row) pair. */
+int sah_masked_attention_lsh(const void* q, const void* k, const void* v, int64_t qs_b,
+                             int64_t qs_h, int64_t qs_q, int64_t ks_b, int64_t ks_h, int64_t ks_s,
+                             int64_t vs_b, int64_t vs_h, int64_t vs_s, int B, int Hq, int Hkv,
+                             int Sq, int64_t S, int D, float scaling, const void* bias,
+                             int64_t bias_s_b, int64_t bias_s_h, int64_t bias_s_q,
+                             const float* sinks, const sah_attn_sizes* sizes, const int32_t* ucols,
+                             const uint16_t* umemb, const float* uinv, const int32_t* ucount,
+                             float* partial, const void* qhat, const float* qmu,
+                             const uint16_t* prob_table, void* out, float* acc_out, float* lse_out,
+                             float* w_dump, void* stream);
 
 /* Merge n_parts partial results (unnormalised fp32 accumulators acc
  * [n_parts][rows][D] with lse [n_parts][rows][2]) into out [B][Sq][Hq][D]:

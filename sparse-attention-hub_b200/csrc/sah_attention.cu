@@ -15,6 +15,13 @@
 #define AT_MAXR 16
 #define PLAN_CHUNK_WORDS 32  // one warp scans 32 bitmap words = 1024 columns
 
+// Chunk counters per group: a function of the key count alone, so that the plan, the
+// attention kernel and the size query agree on where the counters, the merge tickets and
+// the error word sit, whatever row stride W the caller's bitmap has.
+static inline int64_t plan_chunks(int64_t S) {
+  return (((S + 31) / 32 + 3) / 4 * 4 + PLAN_CHUNK_WORDS - 1) / PLAN_CHUNK_WORDS;
+}
+
 // ---------------------------------------------------------------------------
 // geometry
 // ---------------------------------------------------------------------------
@@ -45,14 +52,17 @@ extern "C" int sah_attn_query_sizes(int B, int Hq, int Hkv, int Sq, int64_t S, i
   if (nsplit > 256) nsplit = 256;
   if (nsplit < 1) nsplit = 1;
   const int R = G * q_block;
-  const int64_t nchunks = (((S + 31) / 32 + 3) / 4 * 4 + PLAN_CHUNK_WORDS - 1) / PLAN_CHUNK_WORDS;
+  const int64_t nchunks = plan_chunks(S);
   out->groups = (int32_t)groups;
   out->q_block = q_block;
   out->rows_per_group = R;
   out->nsplit = (int32_t)nsplit;
   out->ucols_bytes = groups * S * (int64_t)sizeof(int32_t);
   out->umemb_bytes = groups * S * (int64_t)sizeof(uint16_t);
-  out->uw_bytes = has_data ? groups * S * R * (int64_t)sizeof(float) : 0;
+  // has_data: 0 unit weights, 1 per-entry weights (uw [groups][S][R]), 2 MagicPig weights
+  // evaluated inside the attention kernel (one key constant per union entry, [groups][S])
+  out->uw_bytes = has_data == 1 ? groups * S * R * (int64_t)sizeof(float)
+                                : (has_data == 2 ? groups * S * (int64_t)sizeof(float) : 0);
   // [groups] union counts, [groups][nchunks] chunk counts, [groups] merge tickets
   // and one error word (non-zero after a bounded device-side wait ran out)
   out->ucount_bytes = (2 * groups + groups * nchunks + 4) * (int64_t)sizeof(int32_t);
@@ -66,7 +76,14 @@ extern "C" int sah_attn_query_sizes(int B, int Hq, int Hkv, int Sq, int64_t S, i
 struct PlanGeom {
   int Hq, Hkv, Sq, G, q_block, nqb, R;
   int64_t S, W, nchunks, groups;
+  int64_t Wv;          // words that hold columns < S (<= W)
+  uint32_t tail_mask;  // valid bits of word Wv - 1
 };
+
+// word w of a row with the bits of columns >= S dropped
+__device__ __forceinline__ uint32_t plan_word(const PlanGeom& p, uint32_t v, int64_t w) {
+  return w == p.Wv - 1 ? (v & p.tail_mask) : v;
+}
 
 // mask row of member r of group g, or -1 when the member's query is past Sq
 __device__ __forceinline__ int64_t plan_member_row(const PlanGeom& p, int64_t g, int r) {
@@ -81,7 +98,8 @@ __device__ __forceinline__ int64_t plan_member_row(const PlanGeom& p, int64_t g,
   return (b * p.Hq + h) * p.Sq + qi;
 }
 
-__global__ void attn_plan_count_kernel(const uint32_t* __restrict__ bits, PlanGeom p,
+__global__ void attn_plan_count_kernel(const uint32_t* __restrict__ bits,
+                                       const uint32_t* __restrict__ ubits, PlanGeom p,
                                        int32_t* __restrict__ chunkcnt) {
   const int lane = threadIdx.x & 31;
   const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -89,11 +107,15 @@ __global__ void attn_plan_count_kernel(const uint32_t* __restrict__ bits, PlanGe
   if (g >= p.groups) return;  // surplus warps of the last block
   const int64_t w = c * PLAN_CHUNK_WORDS + lane;
   uint32_t u = 0u;
-  if (w < p.W) {
+  if (w < p.Wv) {
     for (int r = 0; r < p.R; ++r) {
       int64_t row = plan_member_row(p, g, r);
-      if (row >= 0) u |= bits[row * p.W + w];
+      if (row >= 0) {
+        u |= bits[row * p.W + w];
+        if (ubits != nullptr) u |= ubits[row * p.W + w];  // a second set joined with the first
+      }
     }
+    u = plan_word(p, u, w);
   }
   int cnt = __popc(u);
 #pragma unroll
@@ -138,8 +160,10 @@ attn_plan_fused_kernel(const uint32_t* __restrict__ bits, const T* __restrict__ 
   for (int r = 0; r < RMAX; ++r) {
     words[r] = 0u;
     dbase[r] = 0;
-    if (w < p.W && rows[r] >= 0) {
-      words[r] = bits[rows[r] * p.W + w];
+    if (w < p.Wv && rows[r] >= 0) {
+      // wpre counts every set bit of the caller's words; bits past S are dropped after
+      // the CSR offsets were taken from the unmasked prefix (they can only sit last)
+      words[r] = plan_word(p, bits[rows[r] * p.W + w], w);
       if (uw != nullptr && words[r]) dbase[r] = ptr[rows[r]] + wpre[rows[r] * p.W + w];
     }
     u |= words[r];
@@ -206,10 +230,10 @@ __global__ void attn_plan_emit_kernel(const uint32_t* __restrict__ bits, const T
     words[r] = 0u;
     rows[r] = -1;
     dbase[r] = 0;
-    if (r < p.R && w < p.W) {
+    if (r < p.R && w < p.Wv) {
       rows[r] = plan_member_row(p, g, r);
       if (rows[r] >= 0) {
-        words[r] = bits[rows[r] * p.W + w];
+        words[r] = plan_word(p, bits[rows[r] * p.W + w], w);
         if (uw != nullptr && words[r]) dbase[r] = ptr[rows[r]] + wpre[rows[r] * p.W + w];
       }
     }
@@ -253,6 +277,30 @@ __global__ void attn_plan_emit_kernel(const uint32_t* __restrict__ bits, const T
   }
 }
 
+// Geometry shared by the plan entry points.  The chunk counters are laid out by the key
+// count (plan_chunks), not by the caller's row stride W, which may be padded further than
+// the library's own bitmaps are; words past the last key are never read and the bits of the
+// last word past S are ignored.
+static int plan_geometry(int B, int Hq, int Hkv, int Sq, int64_t S, int64_t W,
+                         const sah_attn_sizes* sizes, PlanGeom* out) {
+  PlanGeom p;
+  p.Hq = Hq; p.Hkv = Hkv; p.Sq = Sq; p.G = Hq / Hkv;
+  p.q_block = sizes->q_block;
+  p.nqb = (Sq + p.q_block - 1) / p.q_block;
+  p.R = sizes->rows_per_group;
+  p.S = S; p.W = W;
+  p.Wv = (S + 31) / 32;
+  p.tail_mask = (S % 32) ? ((1u << (S % 32)) - 1u) : 0xffffffffu;
+  p.nchunks = plan_chunks(S);
+  p.groups = sizes->groups;
+  SAH_REQUIRE(p.groups == (int64_t)B * Hkv * p.nqb && p.R == p.G * p.q_block && p.R <= AT_MAXR,
+              "attn_plan: sizes do not match the extents");
+  SAH_REQUIRE(sizes->ucount_bytes >= (2 * p.groups + p.groups * p.nchunks + 4) * (int64_t)sizeof(int32_t),
+              "attn_plan: sizes were not made by sah_attn_query_sizes for this key count");
+  *out = p;
+  return SAH_OK;
+}
+
 extern "C" int sah_attn_plan(const uint32_t* bits, const void* data, const int32_t* wpre,
                              const int64_t* ptr, int dtype, int B, int Hq, int Hkv, int Sq,
                              int64_t S, int64_t W, const sah_attn_sizes* sizes, int32_t* ucols,
@@ -261,24 +309,17 @@ extern "C" int sah_attn_plan(const uint32_t* bits, const void* data, const int32
   SAH_REQUIRE(data == nullptr || (wpre && ptr && uw), "attn_plan: data needs wpre, ptr and uw");
   SAH_REQUIRE(W * 32 >= S, "attn_plan: W too small");
   PlanGeom p;
-  p.Hq = Hq; p.Hkv = Hkv; p.Sq = Sq; p.G = Hq / Hkv;
-  p.q_block = sizes->q_block;
-  p.nqb = (Sq + p.q_block - 1) / p.q_block;
-  p.R = sizes->rows_per_group;
-  p.S = S; p.W = W;
-  p.nchunks = (W + PLAN_CHUNK_WORDS - 1) / PLAN_CHUNK_WORDS;
-  const int64_t groups = sizes->groups;
-  p.groups = groups;
-  SAH_REQUIRE(groups == (int64_t)B * Hkv * p.nqb && p.R == p.G * p.q_block && p.R <= AT_MAXR,
-              "attn_plan: sizes do not match the extents");
+  int rc0 = plan_geometry(B, Hq, Hkv, Sq, S, W, sizes, &p);
+  if (rc0 != SAH_OK) return rc0;
+  const int64_t groups = p.groups;
   int32_t* chunkcnt = ucount + groups;
   const int64_t warps = groups * p.nchunks;
   const int threads = 256;
   const int64_t blocks = sah_ceil_div(warps * 32, threads);
   cudaStream_t st = (cudaStream_t)stream;
   sah_prof_begin(SAH_PROF_ATTN_PLAN, (cudaStream_t)stream);
-  if (W <= 1024) {
-    const dim3 fgrid((unsigned)groups, (unsigned)sah_ceil_div(W, PLAN_FUSED_THREADS));
+  if (p.Wv <= 1024) {
+    const dim3 fgrid((unsigned)groups, (unsigned)sah_ceil_div(p.Wv, PLAN_FUSED_THREADS));
     SAH_DISPATCH_DTYPE(dtype, T, {
       if (p.R <= 4)
         attn_plan_fused_kernel<T, 4><<<fgrid, PLAN_FUSED_THREADS, 0, st>>>(
@@ -291,7 +332,7 @@ extern "C" int sah_attn_plan(const uint32_t* bits, const void* data, const int32
     sah_prof_end(SAH_PROF_ATTN_PLAN, (cudaStream_t)stream);
     return SAH_OK;
   }
-  attn_plan_count_kernel<<<(unsigned)blocks, threads, 0, st>>>(bits, p, chunkcnt);
+  attn_plan_count_kernel<<<(unsigned)blocks, threads, 0, st>>>(bits, nullptr, p, chunkcnt);
   SAH_LAUNCH_CHECK("attn_plan_count");
   SAH_DISPATCH_DTYPE(dtype, T, {
     attn_plan_emit_kernel<T><<<(unsigned)blocks, threads, 0, st>>>(
@@ -299,6 +340,103 @@ extern "C" int sah_attn_plan(const uint32_t* bits, const void* data, const int32
   });
   SAH_LAUNCH_CHECK("attn_plan_emit");
   sah_prof_end(SAH_PROF_ATTN_PLAN, (cudaStream_t)stream);
+  return SAH_OK;
+}
+
+// Union list for a MagicPig mask whose weights the attention kernel evaluates itself
+// (at most 4 mask rows per group).  `bits` are the LSH matches, `ubits` (may be NULL) the
+// unit-weight part of the mask; the active set is their union.  Per union
+// entry: the column, membership in the low byte and "weight is 1" flags in the high byte
+// of umemb, and the key's constant of the cosine, 1 / (M * |transformed key|).
+__global__ void attn_plan_emit_lsh_kernel(const uint32_t* __restrict__ bits,
+                                          const uint32_t* __restrict__ ubits,
+                                          const float* __restrict__ dens, int64_t dens_cap,
+                                          const unsigned int* __restrict__ max_bits, PlanGeom p,
+                                          const int32_t* __restrict__ chunkcnt,
+                                          int32_t* __restrict__ ucols, uint16_t* __restrict__ umemb,
+                                          float* __restrict__ uinv, int32_t* __restrict__ ucount) {
+  const int lane = threadIdx.x & 31;
+  const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t g = wid / p.nchunks, c = wid - g * p.nchunks;
+  if (g >= p.groups) return;  // surplus warps of the last block
+  int base = 0;
+  for (int64_t cc = lane; cc < c; cc += 32) base += chunkcnt[g * p.nchunks + cc];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) base += __shfl_xor_sync(0xffffffffu, base, o);
+
+  const int64_t w = c * PLAN_CHUNK_WORDS + lane;
+  uint32_t words[4], units[4];
+  uint32_t u = 0u;
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    words[r] = 0u;
+    units[r] = 0u;
+    if (r < p.R && w < p.Wv) {
+      const int64_t row = plan_member_row(p, g, r);
+      if (row >= 0) {
+        units[r] = ubits ? plan_word(p, ubits[row * p.W + w], w) : 0u;
+        words[r] = plan_word(p, bits[row * p.W + w], w) | units[r];
+      }
+    }
+    u |= words[r];
+  }
+  const int cnt = __popc(u);
+  int incl = cnt;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int n = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += n;
+  }
+  int64_t pos = (int64_t)g * p.S + base + incl - cnt;
+  const float M = __uint_as_float(*max_bits);
+  const float* gd = dens + (g / p.nqb) * dens_cap;  // (batch, KV head) of the group
+  uint32_t m = u;
+  while (m) {
+    const int b = __ffs(m) - 1;
+    m &= m - 1;
+    unsigned int memb = 0u;
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+      memb |= (((words[r] >> b) & 1u) << r) | (((units[r] >> b) & 1u) << (8 + r));
+    const int64_t col = w * 32 + b;
+    ucols[pos] = (int32_t)col;
+    umemb[pos] = (uint16_t)memb;
+    uinv[pos] = __frcp_rn(__fmul_rn(M, gd[col]));
+    ++pos;
+  }
+  if (c == p.nchunks - 1) {
+    int total = __shfl_sync(0xffffffffu, incl, 31);
+    if (lane == 0) ucount[g] = base + total;
+  }
+}
+
+extern "C" int sah_attn_plan_lsh(const uint32_t* bits, const uint32_t* unit_bits, const float* dens,
+                                 int64_t dens_cap, const unsigned int* max_norm_bits, int B, int Hq,
+                                 int Hkv, int Sq, int64_t S, int64_t W, const sah_attn_sizes* sizes,
+                                 int32_t* ucols, uint16_t* umemb, float* uinv, int32_t* ucount,
+                                 void* stream) {
+  SAH_REQUIRE(bits && dens && max_norm_bits && sizes && ucols && umemb && uinv && ucount,
+              "attn_plan_lsh: null pointer");
+  SAH_REQUIRE(W * 32 >= S && dens_cap >= S, "attn_plan_lsh: W or the key-constant stride too small");
+  PlanGeom p;
+  int rc0 = plan_geometry(B, Hq, Hkv, Sq, S, W, sizes, &p);
+  if (rc0 != SAH_OK) return rc0;
+  if (p.R > 4)
+    return sah_fail(SAH_ERR_UNSUPPORTED, "attn_plan_lsh: %d mask rows per KV group (<= 4)", p.R);
+  SAH_REQUIRE(sizes->uw_bytes >= p.groups * S * (int64_t)sizeof(float),
+              "attn_plan_lsh: sizes were not queried for in-kernel MagicPig weights");
+  int32_t* chunkcnt = ucount + p.groups;
+  const int64_t warps = p.groups * p.nchunks;
+  const int threads = 256;
+  const int64_t blocks = sah_ceil_div(warps * 32, threads);
+  cudaStream_t st = (cudaStream_t)stream;
+  sah_prof_begin(SAH_PROF_ATTN_PLAN, st);
+  attn_plan_count_kernel<<<(unsigned)blocks, threads, 0, st>>>(bits, unit_bits, p, chunkcnt);
+  SAH_LAUNCH_CHECK("attn_plan_count");
+  attn_plan_emit_lsh_kernel<<<(unsigned)blocks, threads, 0, st>>>(
+      bits, unit_bits, dens, dens_cap, max_norm_bits, p, chunkcnt, ucols, umemb, uinv, ucount);
+  SAH_LAUNCH_CHECK("attn_plan_emit_lsh");
+  sah_prof_end(SAH_PROF_ATTN_PLAN, st);
   return SAH_OK;
 }
 
@@ -328,6 +466,11 @@ struct AttnArgs {
   const float* uw;
   const int32_t* ucount;
   float* partial;
+  // MagicPig weights evaluated inside the bf16 kernel (uw then holds one constant per entry)
+  const __nv_bfloat16* qhat;  // [rows][D] centred unit queries
+  const float* qmu;           // [rows] qhat . key mean
+  const uint16_t* ptable;     // [65536] bf16 bits of the cosine -> bits of the probability
+  float* w_dump;              // optional [groups][S][R]: the weights used (tests)
 };
 
 // Shared-memory rows are stored in 16-byte chunks; chunk c of tile row i sits
@@ -713,16 +856,23 @@ static int launch_attention(const AttnArgs& a, int groups, cudaStream_t st) {
   return SAH_OK;
 }
 
-extern "C" int sah_masked_attention(const void* q, const void* k, const void* v, int dtype,
-                                    int64_t qs_b, int64_t qs_h, int64_t qs_q, int64_t ks_b,
-                                    int64_t ks_h, int64_t ks_s, int64_t vs_b, int64_t vs_h,
-                                    int64_t vs_s, int B, int Hq, int Hkv, int Sq, int64_t S, int D,
-                                    float scaling, const void* bias, int64_t bias_s_b,
-                                    int64_t bias_s_h, int64_t bias_s_q, const float* sinks,
-                                    const sah_attn_sizes* sizes, const int32_t* ucols,
-                                    const uint16_t* umemb, const float* uw, const int32_t* ucount,
-                                    float* partial, void* out, float* acc_out, float* lse_out,
-                                    void* stream) {
+struct AttnLsh {
+  const void* qhat;
+  const float* qmu;
+  const uint16_t* ptable;
+  float* w_dump;
+};
+
+static int masked_attention_impl(const void* q, const void* k, const void* v, int dtype,
+                                 int64_t qs_b, int64_t qs_h, int64_t qs_q, int64_t ks_b,
+                                 int64_t ks_h, int64_t ks_s, int64_t vs_b, int64_t vs_h,
+                                 int64_t vs_s, int B, int Hq, int Hkv, int Sq, int64_t S, int D,
+                                 float scaling, const void* bias, int64_t bias_s_b,
+                                 int64_t bias_s_h, int64_t bias_s_q, const float* sinks,
+                                 const sah_attn_sizes* sizes, const int32_t* ucols,
+                                 const uint16_t* umemb, const float* uw, const int32_t* ucount,
+                                 float* partial, void* out, float* acc_out, float* lse_out,
+                                 const AttnLsh* lsh, void* stream) {
   SAH_REQUIRE(q && k && v && sizes && ucols && umemb && ucount && partial && out,
               "masked_attention: null pointer");
   SAH_REQUIRE(B > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Sq > 0 && S > 0,
@@ -747,6 +897,10 @@ extern "C" int sah_masked_attention(const void* q, const void* k, const void* v,
   a.S = S; a.scaling = scaling;
   a.bias = bias; a.bias_s_b = bias_s_b; a.bias_s_h = bias_s_h; a.bias_s_q = bias_s_q;
   a.ucols = ucols; a.umemb = umemb; a.uw = uw; a.ucount = ucount; a.partial = partial;
+  a.qhat = lsh ? reinterpret_cast<const __nv_bfloat16*>(lsh->qhat) : nullptr;
+  a.qmu = lsh ? lsh->qmu : nullptr;
+  a.ptable = lsh ? lsh->ptable : nullptr;
+  a.w_dump = lsh ? lsh->w_dump : nullptr;
   const int groups = sizes->groups;
   SAH_REQUIRE((int64_t)groups == (int64_t)B * Hkv * a.nqb && a.R == a.G * a.q_block &&
                   a.R <= AT_MAXR && a.nsplit >= 1,
@@ -756,18 +910,18 @@ extern "C" int sah_masked_attention(const void* q, const void* k, const void* v,
   int rc = SAH_OK;
   if (dtype == SAH_BF16) {
     // tensor-core path; the split merge is fused into the kernel (ticket per group)
-    const int64_t nchunks = (((S + 31) / 32 + 3) / 4 * 4 + PLAN_CHUNK_WORDS - 1) / PLAN_CHUNK_WORDS;
-    int* tickets = const_cast<int*>(ucount) + groups + (int64_t)groups * nchunks;
-    int* errflag = tickets + groups;  // set when a bounded wait inside the kernel ran out
+    int* tickets = const_cast<int*>(ucount) + groups + (int64_t)groups * plan_chunks(S);
     rc = (D == 128)
-             ? launch_attention_mma<128>(a, groups, tickets, errflag, sinks, out, acc_out, lse_out, st)
-             : launch_attention_mma<64>(a, groups, tickets, errflag, sinks, out, acc_out, lse_out, st);
+             ? launch_attention_mma<128>(a, groups, tickets, sinks, out, acc_out, lse_out, lsh != nullptr, st)
+             : launch_attention_mma<64>(a, groups, tickets, sinks, out, acc_out, lse_out, lsh != nullptr, st);
     if (rc != SAH_OK) return rc;
     SAH_LAUNCH_CHECK("masked_attention_mma");
     sah_prof_end(SAH_PROF_ATTENTION, (cudaStream_t)stream);
     return SAH_OK;
   }
   if (dtype != SAH_F32) return sah_fail(SAH_ERR_INVALID, "masked_attention: unknown dtype %d", dtype);
+  if (lsh != nullptr)
+    return sah_fail(SAH_ERR_UNSUPPORTED, "masked_attention_lsh: bfloat16 only");
   rc = (D == 128) ? launch_attention<float, 128>(a, groups, st)
                   : launch_attention<float, 64>(a, groups, st);
   if (rc != SAH_OK) return rc;
@@ -780,6 +934,43 @@ extern "C" int sah_masked_attention(const void* q, const void* k, const void* v,
   SAH_LAUNCH_CHECK("attn_merge_splits");
   sah_prof_end(SAH_PROF_ATTN_MERGE, (cudaStream_t)stream);
   return SAH_OK;
+}
+
+extern "C" int sah_masked_attention(const void* q, const void* k, const void* v, int dtype,
+                                    int64_t qs_b, int64_t qs_h, int64_t qs_q, int64_t ks_b,
+                                    int64_t ks_h, int64_t ks_s, int64_t vs_b, int64_t vs_h,
+                                    int64_t vs_s, int B, int Hq, int Hkv, int Sq, int64_t S, int D,
+                                    float scaling, const void* bias, int64_t bias_s_b,
+                                    int64_t bias_s_h, int64_t bias_s_q, const float* sinks,
+                                    const sah_attn_sizes* sizes, const int32_t* ucols,
+                                    const uint16_t* umemb, const float* uw, const int32_t* ucount,
+                                    float* partial, void* out, float* acc_out, float* lse_out,
+                                    void* stream) {
+  return masked_attention_impl(q, k, v, dtype, qs_b, qs_h, qs_q, ks_b, ks_h, ks_s, vs_b, vs_h, vs_s,
+                               B, Hq, Hkv, Sq, S, D, scaling, bias, bias_s_b, bias_s_h, bias_s_q,
+                               sinks, sizes, ucols, umemb, uw, ucount, partial, out, acc_out,
+                               lse_out, nullptr, stream);
+}
+
+extern "C" int sah_masked_attention_lsh(const void* q, const void* k, const void* v, int64_t qs_b,
+                                        int64_t qs_h, int64_t qs_q, int64_t ks_b, int64_t ks_h,
+                                        int64_t ks_s, int64_t vs_b, int64_t vs_h, int64_t vs_s,
+                                        int B, int Hq, int Hkv, int Sq, int64_t S, int D,
+                                        float scaling, const void* bias, int64_t bias_s_b,
+                                        int64_t bias_s_h, int64_t bias_s_q, const float* sinks,
+                                        const sah_attn_sizes* sizes, const int32_t* ucols,
+                                        const uint16_t* umemb, const float* uinv,
+                                        const int32_t* ucount, float* partial, const void* qhat,
+                                        const float* qmu, const uint16_t* prob_table, void* out,
+                                        float* acc_out, float* lse_out, float* w_dump,
+                                        void* stream) {
+  SAH_REQUIRE(uinv && qhat && qmu && prob_table, "masked_attention_lsh: null pointer");
+  SAH_REQUIRE((uintptr_t)qhat % 16 == 0, "masked_attention_lsh: qhat must be 16-byte aligned");
+  AttnLsh lsh = {qhat, qmu, prob_table, w_dump};
+  return masked_attention_impl(q, k, v, SAH_BF16, qs_b, qs_h, qs_q, ks_b, ks_h, ks_s, vs_b, vs_h,
+                               vs_s, B, Hq, Hkv, Sq, S, D, scaling, bias, bias_s_b, bias_s_h,
+                               bias_s_q, sinks, sizes, ucols, umemb, uinv, ucount, partial, out,
+                               acc_out, lse_out, &lsh, stream);
 }
 
 // Merge partial results computed on different sequence shards.

@@ -3,10 +3,9 @@
 // Every warp runs its own pipeline with no CTA-wide barrier in the main loop:
 // it takes 16-key tiles of the group's union list (tiles are dealt round-robin
 // to the warps of the CTAs that share the group) and gathers the 16 K rows and
-// 16 V rows with bulk asynchronous copies (cp.async.bulk, one whole-row copy
-// issued by one lane each, completion counted on an mbarrier) into a private
-// ring in shared memory.  Rows are padded by 16 bytes so that the 8 rows of an
-// ldmatrix tile fall into different banks.  Per tile:
+// 16 V rows with 16-byte asynchronous copies into a private ring in shared
+// memory.  Rows are padded by 16 bytes so that the 8 rows of an ldmatrix tile
+// fall into different banks.  Per tile:
 //     S[rows x 16 keys] = Q . K^T          mma.m16n8k16, Q fragments in registers
 //     P = exp(S * scaling + bias - m) * w  online softmax in the C fragment
 //     O[rows x D]      += P . V            mma.m16n8k16, V fragments via ldmatrix.trans
@@ -16,9 +15,14 @@
 // memory, the CTA writes its partial, and the last CTA of a group (atomic
 // ticket) merges the group's partials and writes the output.
 //
-// Every wait on an mbarrier is bounded; a wait that runs out sets the error
-// word, the warp stops consuming tiles, and the kernel still goes through its
-// merge and ticket protocol so that no other CTA is left waiting.
+// LSHW (MagicPig weights evaluated in place; HALF tiles with at most 4 mask rows):
+// rows 4..7 of the Q tile, otherwise zero padding, hold the group's centred unit
+// queries, so the same mma that gives q.k also gives qhat.k.  The cosine between
+// the transformed key and query is (qhat.k - qhat.mean) / (M * |transformed key|)
+// (magic_pig.py:332-403), the collision probability comes from the cosine's bf16
+// table, and the weight is 1 / (p + 1e-6) in bf16 -- or exactly 1 for columns
+// that the unit-weight part of the mask (sink, window) selected.  No per-entry
+// weight array is read or written.
 #pragma once
 
 #ifndef ATM_WARPS
@@ -27,15 +31,8 @@
 #ifndef ATM_STAGES
 #define ATM_STAGES 3
 #endif
-#ifndef ATM_BULK
-#define ATM_BULK 0  // 1: one cp.async.bulk per row + mbarrier; 0: 16-byte cp.async per lane
-#endif
-#ifndef ATM_PF_DIST
-#define ATM_PF_DIST 0  // tiles of L2 prefetch distance beyond the shared-memory ring
-#endif
 #define ATM_THREADS (ATM_WARPS * 32)
 #define ATM_TILE 16
-#define ATM_SPIN_LIMIT (1 << 22)
 
 __device__ __forceinline__ void atm_ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2,
                                                 uint32_t& r3, uint32_t saddr) {
@@ -80,48 +77,8 @@ __device__ __forceinline__ uint32_t atm_pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// ---- mbarrier / bulk copy ----------------------------------------------------
-__device__ __forceinline__ void atm_mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void atm_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ bool atm_mbar_test(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0u;
-}
-// Bounded wait: false when the phase did not complete within the spin limit.
-__device__ __forceinline__ bool atm_mbar_wait(uint32_t bar, uint32_t parity) {
-  for (int i = 0; i < ATM_SPIN_LIMIT; ++i) {
-    if (atm_mbar_test(bar, parity)) return true;
-    if (i > 64) __nanosleep(40);
-  }
-  return false;
-}
-__device__ __forceinline__ void atm_bulk_g2s(uint32_t dst, const void* src, uint32_t bytes,
-                                             uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::
-          "r"(dst),
-      "l"(src), "r"(bytes), "r"(bar)
-      : "memory");
-}
-
 __device__ __forceinline__ void atm_cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
-}
-
-__device__ __forceinline__ void atm_prefetch_l2(const void* p) {
-  asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p));
 }
 
 template <int D>
@@ -136,26 +93,36 @@ struct AtmCfg {
   static constexpr int Q_BYTES = 16 * RSTR;
   static constexpr int RS = D + 8;                          // fp32 row stride of the reduction scratch
   static constexpr int RED_BYTES = 16 * RS * 4 + 16 * 2 * 4;
-  static constexpr int META_BYTES = ATM_WARPS * ATM_STAGES * 16 * 8;
-  static constexpr int BAR_BYTES = ATM_WARPS * ATM_STAGES * 8;
-  static constexpr int SMEM = ATM_WARPS * WARP_BYTES + Q_BYTES + META_BYTES + BAR_BYTES;
+  static constexpr int META_BYTES = ATM_WARPS * ATM_STAGES * 16 * 16;  // (col, memb, 1/(M den), -)
+  static constexpr int SMEM = ATM_WARPS * WARP_BYTES + Q_BYTES + META_BYTES;
 };
 
-template <int D, bool HALF>
+// MagicPig weight of one (row, key) pair from the centred cosine (see the header comment);
+// 0 when the probability is 0 in bfloat16: the reference's dense mask holds a zero there,
+// which means "not selected" (utils/mask.py:19-21).
+__device__ __forceinline__ float atm_lsh_weight(float dot_hat, float qmu, float inv_md,
+                                                const uint16_t* __restrict__ ptable) {
+  float c = __fmul_rn(__fsub_rn(dot_hat, qmu), inv_md);
+  c = __bfloat162float(__float2bfloat16_rn(c));
+  c = fminf(fmaxf(c, -1.0f), 1.0f);
+  const float p = __uint_as_float(((uint32_t)__ldg(ptable + (__float_as_uint(c) >> 16))) << 16);
+  return p == 0.f ? 0.f : sah_inv_weight<__nv_bfloat16>(p);
+}
+
+template <int D, bool HALF, bool LSHW>
 __global__ void __launch_bounds__(ATM_THREADS, 2)
-masked_attention_mma_kernel(AttnArgs a, int* __restrict__ tickets, int* __restrict__ errflag,
-                            const float* __restrict__ sinks, __nv_bfloat16* __restrict__ out,
-                            float* __restrict__ acc_out, float* __restrict__ lse_out) {
+masked_attention_mma_kernel(AttnArgs a, int* __restrict__ tickets, const float* __restrict__ sinks,
+                            __nv_bfloat16* __restrict__ out, float* __restrict__ acc_out,
+                            float* __restrict__ lse_out) {
+  static_assert(!LSHW || HALF, "in-place MagicPig weights use the spare rows of the half tile");
   using C = AtmCfg<D>;
   constexpr int NR = HALF ? 1 : 2;  // row halves a thread owns in the C fragment
   extern __shared__ __align__(128) unsigned char atm_smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   unsigned char* ring = atm_smem + warp * C::WARP_BYTES;
   unsigned char* q_sm = atm_smem + ATM_WARPS * C::WARP_BYTES;
-  int2* meta_sm = reinterpret_cast<int2*>(q_sm + C::Q_BYTES) + warp * ATM_STAGES * 16;  // (col, memb)
-  unsigned char* bar_base = q_sm + C::Q_BYTES + C::META_BYTES + warp * ATM_STAGES * 8;
+  int4* meta_sm = reinterpret_cast<int4*>(q_sm + C::Q_BYTES) + warp * ATM_STAGES * 16;
   const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
-  const uint32_t bar_s = (uint32_t)__cvta_generic_to_shared(bar_base);
   __shared__ int is_last_sm;
 
   const int split = blockIdx.x;
@@ -168,28 +135,55 @@ masked_attention_mma_kernel(AttnArgs a, int* __restrict__ tickets, int* __restri
   const __nv_bfloat16* vbase = reinterpret_cast<const __nv_bfloat16*>(a.v) + b * a.vs_b + kvh * a.vs_h;
   const int32_t* gcols = a.ucols + g * a.S;
   const uint16_t* gmemb = a.umemb + g * a.S;
-  const float* guw = a.uw ? a.uw + g * a.S * a.R : nullptr;
+  const float* guw = (!LSHW && a.uw) ? a.uw + g * a.S * a.R : nullptr;
+  const float* ginv = LSHW ? a.uw + g * a.S : nullptr;  // 1 / (M * |transformed key|) per entry
 
-  if (lane == 0) {
-#pragma unroll
-    for (int s = 0; s < ATM_STAGES; ++s) atm_mbar_init(bar_s + s * 8, 1);
-  }
-  // ---- stage Q (zero padded to 16 rows) ----
+  // ---- this warp's tiles ----
+  const int U = a.ucount[g];
+  const int total_tiles = (U + ATM_TILE - 1) / ATM_TILE;
+  const int lanes_total = a.nsplit * ATM_WARPS;   // warps sharing the group
+  const int my_first = split * ATM_WARPS + warp;  // tile t of this warp = my_first + t * lanes_total
+  const int my_tiles =
+      (total_tiles > my_first) ? (total_tiles - my_first + lanes_total - 1) / lanes_total : 0;
+
+  // Column, membership (and key constant) of the tiles to issue are fetched two tiles early,
+  // so that their latency hides behind the tiles being computed and the first tiles of a
+  // warp do not wait for one list read after the other.
+  struct Meta { int col; unsigned int memb; float inv; };
+  auto load_meta = [&](int t) {
+    Meta m;
+    m.col = -1; m.memb = 0u; m.inv = 0.f;
+    if (t < my_tiles) {
+      const int u = (my_first + t * lanes_total) * ATM_TILE + lane;
+      if (lane < ATM_TILE && u < U) {
+        m.col = gcols[u];
+        m.memb = gmemb[u];
+        if constexpr (LSHW) m.inv = ginv[u];
+      }
+    }
+    return m;
+  };
+  Meta pre0 = load_meta(0), pre1 = load_meta(1);
+
+  // ---- stage Q (zero padded to 16 rows; LSHW: rows 4..7 = centred unit queries) ----
   for (int idx = tid; idx < 16 * (C::ROWB / 16); idx += ATM_THREADS) {
     const int r = idx / (C::ROWB / 16), c = idx - r * (C::ROWB / 16);
     uint4 val = make_uint4(0u, 0u, 0u, 0u);
-    if (r < a.R) {
-      const int gi = r / a.q_block, qo = r - gi * a.q_block;
+    const int rq = (LSHW && r >= 4) ? r - 4 : r;
+    if (rq < a.R && (LSHW || r < a.R) && r < (LSHW ? 8 : 16)) {
+      const int gi = rq / a.q_block, qo = rq - gi * a.q_block;
       const int qi = qb * a.q_block + qo;
       if (qi < a.Sq) {
         const int h = kvh * a.G + gi;
-        val = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.q) +
-                                              b * a.qs_b + (int64_t)h * a.qs_h + qi * a.qs_q + c * 8);
+        if (LSHW && r >= 4)
+          val = *reinterpret_cast<const uint4*>(a.qhat + ((b * a.Hq + h) * a.Sq + qi) * D + c * 8);
+        else
+          val = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.q) +
+                                                b * a.qs_b + (int64_t)h * a.qs_h + qi * a.qs_q + c * 8);
       }
     }
     *reinterpret_cast<uint4*>(q_sm + r * C::RSTR + c * 16) = val;
   }
-  asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   __syncthreads();
 
   // Q fragments.  Full: [ks][0..3] = (rows 0-7, k lo), (rows 8-15, k lo), (rows 0-7, k hi),
@@ -212,14 +206,6 @@ masked_attention_mma_kernel(AttnArgs a, int* __restrict__ tickets, int* __restri
     }
   }
 
-  // ---- this warp's tiles ----
-  const int U = a.ucount[g];
-  const int total_tiles = (U + ATM_TILE - 1) / ATM_TILE;
-  const int lanes_total = a.nsplit * ATM_WARPS;   // warps sharing the group
-  const int my_first = split * ATM_WARPS + warp;  // tile t of this warp = my_first + t * lanes_total
-  const int my_tiles =
-      (total_tiles > my_first) ? (total_tiles - my_first + lanes_total - 1) / lanes_total : 0;
-
   // rows this thread owns in the C fragment, and their bias rows
   const int r0 = lane >> 2, r1 = r0 + 8;
   const __nv_bfloat16* bias_row[2] = {nullptr, nullptr};
@@ -233,6 +219,14 @@ masked_attention_mma_kernel(AttnArgs a, int* __restrict__ tickets, int* __restri
       if (r < a.R && qi < a.Sq) bias_row[rs] = bb + (kvh * a.G + gi) * a.bias_s_h + qi * a.bias_s_q;
     }
   }
+  float qmu0 = 0.f;  // qhat . mean of this thread's row
+  if constexpr (LSHW) {
+    if (r0 < a.R) {
+      const int gi = r0 / a.q_block, qo = r0 - gi * a.q_block;
+      const int qi = qb * a.q_block + qo;
+      if (qi < a.Sq) qmu0 = a.qmu[(b * a.Hq + kvh * a.G + gi) * a.Sq + qi];
+    }
+  }
 
   float o[C::NT][2 * NR];
 #pragma unroll
@@ -243,71 +237,6 @@ masked_attention_mma_kernel(AttnArgs a, int* __restrict__ tickets, int* __restri
 #pragma unroll
   for (int rs = 0; rs < NR; ++rs) { m_run[rs] = -INFINITY; l_run[rs] = 0.f; }
 
-  // Column / membership of the next tile to issue are fetched one tile early so
-  // that their latency hides behind the tile being computed.
-  int pre_col = -1;
-  unsigned int pre_memb = 0u;
-  auto prefetch_meta = [&](int t) {
-    pre_col = -1;
-    pre_memb = 0u;
-    if (t < my_tiles) {
-      const int u = (my_first + t * lanes_total) * ATM_TILE + lane;
-      if (lane < ATM_TILE && u < U) {
-        pre_col = gcols[u];
-        pre_memb = gmemb[u];
-      }
-    }
-  };
-  prefetch_meta(0);
-
-  // The shared-memory ring bounds the bytes a warp can have in flight; rows of
-  // tiles further ahead are pulled into L2 with prefetches (lane l: row l & 15 of
-  // K for l < 16, of V otherwise), so that the ring's copies find them there.
-  const unsigned char* pf_base = reinterpret_cast<const unsigned char*>(lane < 16 ? kbase : vbase);
-  const int64_t pf_stride = (lane < 16 ? a.ks_s : a.vs_s) * 2;
-  auto l2_prefetch_tile = [&](int tt) {
-    if (tt < my_tiles) {
-      const int u = (my_first + tt * lanes_total) * ATM_TILE + (lane & 15);
-      if (u < U) {
-        const unsigned char* p = pf_base + (int64_t)gcols[u] * pf_stride;
-#pragma unroll
-        for (int off = 0; off < C::ROWB; off += 128) atm_prefetch_l2(p + off);
-      }
-    }
-  };
-#pragma unroll 1
-  for (int tt = ATM_STAGES - 1; tt < ATM_STAGES - 1 + ATM_PF_DIST; ++tt) l2_prefetch_tile(tt);
-
-#if ATM_BULK
-  // lane l copies row (l & 15) of K (l < 16) or of V (l >= 16)
-  const int my_row = lane & 15;
-  const uint32_t my_dst = (lane < 16 ? 0u : (uint32_t)C::TILE_BYTES) + my_row * C::RSTR;
-  const __nv_bfloat16* my_base = lane < 16 ? kbase : vbase;
-  const int64_t my_stride = lane < 16 ? a.ks_s : a.vs_s;
-
-  auto issue = [&](int t) {
-    const int st = t % ATM_STAGES;
-    const int col = pre_col;
-    const unsigned int memb = pre_memb;
-    prefetch_meta(t + 1);
-    if (lane < ATM_TILE) meta_sm[st * 16 + lane] = make_int2(col, (int)memb);
-    const int rc = __shfl_sync(0xffffffffu, col, my_row);
-    const uint32_t valid = __ballot_sync(0xffffffffu, rc >= 0);
-    const uint32_t bar = bar_s + st * 8;
-    if (lane == 0) atm_mbar_expect_tx(bar, (uint32_t)__popc(valid) * C::ROWB);
-    const uint32_t dst = ring_s + st * C::STAGE_BYTES + my_dst;
-    if (rc >= 0) {
-      atm_bulk_g2s(dst, my_base + (int64_t)rc * my_stride, C::ROWB, bar);
-    } else {
-      // unused rows must not feed NaNs into the tensor cores
-      unsigned char* p = ring + st * C::STAGE_BYTES + my_dst;
-#pragma unroll
-      for (int c = 0; c < C::ROWB / 16; ++c)
-        *reinterpret_cast<uint4*>(p + c * 16) = make_uint4(0u, 0u, 0u, 0u);
-      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-    }
-  };
-#else
   // 16-byte asynchronous copies: CPR lanes cover one row, so a warp instruction
   // moves 32 / CPR whole rows; destination offsets are compile-time constants
   // plus a per-lane base.
@@ -321,14 +250,15 @@ masked_attention_mma_kernel(AttnArgs a, int* __restrict__ tickets, int* __restri
 
   auto issue = [&](int t) {
     const int st = t % ATM_STAGES;
-    const int col = pre_col;
-    const unsigned int memb = pre_memb;
-    prefetch_meta(t + 1);
-    if (lane < ATM_TILE) meta_sm[st * 16 + lane] = make_int2(col, (int)memb);
+    const Meta cur = pre0;
+    pre0 = pre1;
+    pre1 = load_meta(t + 2);
+    if (lane < ATM_TILE)
+      meta_sm[st * 16 + lane] = make_int4(cur.col, (int)cur.memb, __float_as_int(cur.inv), 0);
     const uint32_t dst0 = ring_s + st * C::STAGE_BYTES + my_dst;
 #pragma unroll
     for (int it = 0; it < ATM_TILE / RPS; ++it) {
-      const int rc = __shfl_sync(0xffffffffu, col, it * RPS + my_sub);
+      const int rc = __shfl_sync(0xffffffffu, cur.col, it * RPS + my_sub);
       const uint32_t dst = dst0 + it * RPS * C::RSTR;
       if (rc >= 0) {
         atm_cp_async16(dst, k_bytes + rc * ks_bytes);
@@ -341,32 +271,19 @@ masked_attention_mma_kernel(AttnArgs a, int* __restrict__ tickets, int* __restri
       }
     }
   };
-#endif
 
 #pragma unroll
   for (int s = 0; s < ATM_STAGES - 1; ++s) {
     if (s < my_tiles) issue(s);
-#if !ATM_BULK
     asm volatile("cp.async.commit_group;\n" ::);
-#endif
   }
 
-  bool alive = true;
-  int t = 0;
-  for (; t < my_tiles; ++t) {
+  for (int t = 0; t < my_tiles; ++t) {
     if (t + ATM_STAGES - 1 < my_tiles) issue(t + ATM_STAGES - 1);
-    l2_prefetch_tile(t + ATM_STAGES - 1 + ATM_PF_DIST);
     const int st = t % ATM_STAGES;
-#if ATM_BULK
-    if (!atm_mbar_wait(bar_s + st * 8, (uint32_t)((t / ATM_STAGES) & 1))) {
-      alive = false;
-      break;
-    }
-#else
     asm volatile("cp.async.commit_group;\n" ::);
     asm volatile("cp.async.wait_group %0;\n" ::"n"(ATM_STAGES - 1));
     __syncwarp();
-#endif
     const uint32_t kst = ring_s + st * C::STAGE_BYTES;
     const uint32_t vst = kst + C::TILE_BYTES;
     const int u0 = (my_first + t * lanes_total) * ATM_TILE;
@@ -393,6 +310,15 @@ masked_attention_mma_kernel(AttnArgs a, int* __restrict__ tickets, int* __restri
         }
       }
     }
+    // LSHW: the products with the centred unit queries sit four rows further down,
+    // i.e. in the lane 16 higher
+    float hat[2][2];
+    if constexpr (LSHW) {
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) hat[nt][e] = __shfl_down_sync(0xffffffffu, s[nt][e], 16);
+    }
 
     // ---- online softmax in the C fragment ----
     // element (nt, e): row half rs = e >> 1, key j = nt * 8 + 2 * (lane & 3) + (e & 1)
@@ -407,12 +333,20 @@ masked_attention_mma_kernel(AttnArgs a, int* __restrict__ tickets, int* __restri
         const int j = nt * 8 + 2 * (lane & 3) + (e & 1);
         const int rs = e >> 1;
         const int r = rs ? r1 : r0;
-        const int2 cm = meta_sm[st * 16 + j];
+        const int4 cm = meta_sm[st * 16 + j];
         float sv = -INFINITY, wv = 0.f;
-        if (cm.x >= 0 && ((cm.y >> r) & 1)) {
+        if (cm.x >= 0 && ((cm.y >> r) & 1) && (!LSHW || r < 4)) {
           sv = s[nt][e] * a.scaling;
           if (bias_row[rs] != nullptr) sv += __bfloat162float(bias_row[rs][cm.x]);
-          wv = guw ? guw[(int64_t)(u0 + j) * a.R + r] : 1.f;
+          if constexpr (LSHW) {
+            wv = ((cm.y >> (8 + r)) & 1)
+                     ? 1.f
+                     : atm_lsh_weight(hat[nt][e & 1], qmu0, __int_as_float(cm.z), a.ptable);
+            if (a.w_dump != nullptr) a.w_dump[((int64_t)g * a.S + u0 + j) * a.R + r] = wv;
+            if (wv == 0.f) sv = -INFINITY;  // probability zero: not part of the mask
+          } else {
+            wv = guw ? guw[(int64_t)(u0 + j) * a.R + r] : 1.f;
+          }
         }
         s[nt][e] = sv;
         wts[nt][e] = wv;
@@ -481,18 +415,12 @@ masked_attention_mma_kernel(AttnArgs a, int* __restrict__ tickets, int* __restri
     }
     __syncwarp();  // all lanes done with this stage before it is refilled
   }
-#if !ATM_BULK
   asm volatile("cp.async.wait_group 0;\n" ::);
-#endif
-  if (!alive) {
-    if (lane == 0) atomicExch(errflag, 1);
-    // give the copies still in flight a bounded chance to land before the ring is reused
-    for (int tt = t; tt < my_tiles && tt < t + ATM_STAGES; ++tt)
-      atm_mbar_wait(bar_s + (tt % ATM_STAGES) * 8, (uint32_t)((tt / ATM_STAGES) & 1));
-  }
   __syncthreads();
 
   // ---- merge the warps of this CTA (ring reused as fp32 scratch) ----
+  // (LSHW: rows 4..7 of the tile carried no softmax state: their maximum is -inf and they
+  // are beyond a.R, so nothing below reads them)
   constexpr int RS = C::RS;
   float* red_o = reinterpret_cast<float*>(ring);  // [16][RS]
   float* red_ml = red_o + 16 * RS;                // [16][2]
@@ -608,29 +536,49 @@ masked_attention_mma_kernel(AttnArgs a, int* __restrict__ tickets, int* __restri
   }
 }
 
+// The kernels ask for more dynamic shared memory than the default limit; the attribute is
+// set once per device and instantiation.
+template <typename Kernel>
+static cudaError_t atm_allow_smem(Kernel kernel, int smem, bool* done_by_device) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev >= 0 && dev < 64 && done_by_device[dev]) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e == cudaSuccess && dev >= 0 && dev < 64) done_by_device[dev] = true;
+  return e;
+}
+
 template <int D>
-static int launch_attention_mma(const AttnArgs& a, int groups, int* tickets, int* errflag,
-                                const float* sinks, void* out, float* acc_out, float* lse_out,
+static int launch_attention_mma(const AttnArgs& a, int groups, int* tickets, const float* sinks,
+                                void* out, float* acc_out, float* lse_out, bool lsh,
                                 cudaStream_t st) {
   using C = AtmCfg<D>;
   static_assert(C::RED_BYTES <= C::WARP_BYTES, "reduction scratch must fit the ring");
+  static bool allowed[3][64] = {};
   const int smem = C::SMEM;
   if ((size_t)16 * a.nsplit * 4 + 128 > (size_t)ATM_WARPS * C::WARP_BYTES)
     return sah_fail(SAH_ERR_UNSUPPORTED, "attention: %d splits do not fit the merge scratch", a.nsplit);
   dim3 grid((unsigned)a.nsplit, (unsigned)groups);
   cudaError_t e;
-  if (a.R <= 8) {
-    e = cudaFuncSetAttribute(masked_attention_mma_kernel<D, true>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (lsh) {
+    if (a.R > 4)
+      return sah_fail(SAH_ERR_UNSUPPORTED, "attention: in-place MagicPig weights need <= 4 mask rows "
+                      "per KV group, got %d", a.R);
+    e = atm_allow_smem(masked_attention_mma_kernel<D, true, true>, smem, allowed[2]);
     if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "attention attr: %s", cudaGetErrorString(e));
-    masked_attention_mma_kernel<D, true><<<grid, ATM_THREADS, smem, st>>>(
-        a, tickets, errflag, sinks, (__nv_bfloat16*)out, acc_out, lse_out);
+    masked_attention_mma_kernel<D, true, true><<<grid, ATM_THREADS, smem, st>>>(
+        a, tickets, sinks, (__nv_bfloat16*)out, acc_out, lse_out);
+  } else if (a.R <= 8) {
+    e = atm_allow_smem(masked_attention_mma_kernel<D, true, false>, smem, allowed[0]);
+    if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "attention attr: %s", cudaGetErrorString(e));
+    masked_attention_mma_kernel<D, true, false><<<grid, ATM_THREADS, smem, st>>>(
+        a, tickets, sinks, (__nv_bfloat16*)out, acc_out, lse_out);
   } else {
-    e = cudaFuncSetAttribute(masked_attention_mma_kernel<D, false>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    e = atm_allow_smem(masked_attention_mma_kernel<D, false, false>, smem, allowed[1]);
     if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "attention attr: %s", cudaGetErrorString(e));
-    masked_attention_mma_kernel<D, false><<<grid, ATM_THREADS, smem, st>>>(
-        a, tickets, errflag, sinks, (__nv_bfloat16*)out, acc_out, lse_out);
+    masked_attention_mma_kernel<D, false, false><<<grid, ATM_THREADS, smem, st>>>(
+        a, tickets, sinks, (__nv_bfloat16*)out, acc_out, lse_out);
   }
   return SAH_OK;
 }

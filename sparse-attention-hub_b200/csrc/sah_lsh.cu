@@ -273,7 +273,8 @@ template <typename T, typename CodeT>
 __global__ void __launch_bounds__(256)
 lsh_query_kernel(const T* __restrict__ q, int64_t qs_b, int64_t qs_h, int64_t qs_q, int Hq, int Sq,
                  int G, int D, const T* __restrict__ mean, const T* __restrict__ proj, int L, int K,
-                 CodeT* __restrict__ qcodes, float* __restrict__ qunit) {
+                 CodeT* __restrict__ qcodes, float* __restrict__ qunit, T* __restrict__ qhat,
+                 float* __restrict__ qmu) {
   extern __shared__ __align__(16) unsigned char lsh_smem[];
   float* qn = reinterpret_cast<float*>(lsh_smem);                 // [D] normalised query
   unsigned char* sb = lsh_smem + (size_t)D * sizeof(float);       // [L*K]
@@ -310,9 +311,18 @@ lsh_query_kernel(const T* __restrict__ q, int64_t qs_b, int64_t qs_h, int64_t qs
     // unit vector of the transformed query (its extra column is zero): qn / (|qn| + 1e-8)
     const float n2 = sah_round_to<T>(sqrtf(lsh_warp_sum(acc)));
     const float den2 = sah_round_to<T>(__fadd_rn(n2, 1e-8f));
+    float mu = 0.f;
 #pragma unroll
     for (int t = 0; t < LSH_MAX_PER_LANE; ++t)
-      if (t < per) qunit[row * D + lane * per + t] = sah_round_to<T>(__fdiv_rn(c[t], den2));
+      if (t < per) {
+        const float u = sah_round_to<T>(__fdiv_rn(c[t], den2));
+        qunit[row * D + lane * per + t] = u;
+        if (qhat != nullptr) qhat[row * D + lane * per + t] = sah_from_float<T>(u);  // exact
+        if (mean) mu = __fmaf_rn(u, m[t], mu);
+      }
+    // unit query . key mean, the query-side constant of the centred cosine
+    mu = lsh_warp_sum(mu);
+    if (qmu != nullptr && lane == 0) qmu[row] = mu;
   }
   __syncthreads();
   for (int o = threadIdx.x; o < nbits; o += 256) {
@@ -333,7 +343,7 @@ lsh_query_kernel(const T* __restrict__ q, int64_t qs_b, int64_t qs_h, int64_t qs
 extern "C" int sah_lsh_query(const void* q, int dtype, int64_t qs_b, int64_t qs_h, int64_t qs_q,
                              int B, int Hq, int Sq, int G, int D, const void* mean,
                              const void* proj, int L, int K, void* qcodes, float* qunit,
-                             void* stream) {
+                             void* qhat, float* qmu, void* stream) {
   SAH_REQUIRE(q && proj && qcodes && qunit, "lsh_query: null pointer");
   SAH_REQUIRE(D % 32 == 0 && D <= 32 * LSH_MAX_PER_LANE, "lsh_query: head_dim must be a multiple of 32, <= 256");
   SAH_REQUIRE(G > 0 && Hq % G == 0 && L > 0 && K > 0, "lsh_query: bad shape");
@@ -348,12 +358,12 @@ extern "C" int sah_lsh_query(const void* q, int dtype, int64_t qs_b, int64_t qs_
       lsh_query_kernel<T, uint8_t><<<(unsigned)rows, 256, smem, st>>>(
           reinterpret_cast<const T*>(q), qs_b, qs_h, qs_q, Hq, Sq, G, D,
           reinterpret_cast<const T*>(mean), reinterpret_cast<const T*>(proj), L, K,
-          reinterpret_cast<uint8_t*>(qcodes), qunit);
+          reinterpret_cast<uint8_t*>(qcodes), qunit, reinterpret_cast<T*>(qhat), qmu);
     else
       lsh_query_kernel<T, uint16_t><<<(unsigned)rows, 256, smem, st>>>(
           reinterpret_cast<const T*>(q), qs_b, qs_h, qs_q, Hq, Sq, G, D,
           reinterpret_cast<const T*>(mean), reinterpret_cast<const T*>(proj), L, K,
-          reinterpret_cast<uint16_t*>(qcodes), qunit);
+          reinterpret_cast<uint16_t*>(qcodes), qunit, reinterpret_cast<T*>(qhat), qmu);
   });
   SAH_LAUNCH_CHECK("lsh_query");
   return SAH_OK;
@@ -374,11 +384,30 @@ __device__ __forceinline__ unsigned int lsh_flags2(unsigned int w) {
 }
 
 // Each thread owns 32 consecutive keys of one (batch, KV head): one bitmap word per mask row.
+// The table planes are taken UNR at a time: their 16-byte loads are all requested before the
+// first compare, so a thread keeps UNR * 32 code bytes in flight.
+template <typename CodeT>
+__device__ __forceinline__ void lsh_match_accumulate(const uint4& v, unsigned int qc, unsigned int* acc) {
+  if (sizeof(CodeT) == 1) {
+    const unsigned int rep = qc * 0x01010101u;
+    acc[0] |= __vcmpeq4(v.x, rep);
+    acc[1] |= __vcmpeq4(v.y, rep);
+    acc[2] |= __vcmpeq4(v.z, rep);
+    acc[3] |= __vcmpeq4(v.w, rep);
+  } else {
+    const unsigned int rep = qc * 0x00010001u;
+    acc[0] |= __vcmpeq2(v.x, rep);
+    acc[1] |= __vcmpeq2(v.y, rep);
+    acc[2] |= __vcmpeq2(v.z, rep);
+    acc[3] |= __vcmpeq2(v.w, rep);
+  }
+}
+
 template <typename CodeT>
 __global__ void __launch_bounds__(256)
 lsh_match_kernel(const CodeT* __restrict__ planes, int64_t cap, const CodeT* __restrict__ qcodes,
                  int Hq, int Sq, int G, int L, int64_t S, int64_t W,
-                 uint32_t* __restrict__ out_bits) {
+                 const uint32_t* __restrict__ prev_bits, uint32_t* __restrict__ out_bits) {
   extern __shared__ __align__(16) unsigned char lsh_smem[];
   CodeT* qs = reinterpret_cast<CodeT*>(lsh_smem);  // [R][L]
   const int R = G * Sq;
@@ -395,6 +424,7 @@ lsh_match_kernel(const CodeT* __restrict__ planes, int64_t cap, const CodeT* __r
   if (word * 32 >= S) return;
   constexpr int PER16 = 16 / (int)sizeof(CodeT);  // codes per 16-byte load
   constexpr int NV = 32 / PER16;                  // 16-byte loads per 32 keys
+  constexpr int UNR = sizeof(CodeT) == 1 ? 4 : 2; // table planes in flight
   const CodeT* pbase = planes + bh * (int64_t)L * cap + word * 32;
   for (int r0 = 0; r0 < R; r0 += LSH_MR) {
     unsigned int acc[LSH_MR][NV * 4];
@@ -402,35 +432,35 @@ lsh_match_kernel(const CodeT* __restrict__ planes, int64_t cap, const CodeT* __r
     for (int r = 0; r < LSH_MR; ++r)
 #pragma unroll
       for (int i = 0; i < NV * 4; ++i) acc[r][i] = 0u;
-    for (int l = 0; l < L; ++l) {
+    int l = 0;
+    for (; l + UNR <= L; l += UNR) {
+      uint4 v[UNR][NV];
+#pragma unroll
+      for (int u = 0; u < UNR; ++u)
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+          v[u][i] = __ldg(reinterpret_cast<const uint4*>(pbase + (int64_t)(l + u) * cap) + i);
+#pragma unroll
+      for (int u = 0; u < UNR; ++u)
+#pragma unroll
+        for (int r = 0; r < LSH_MR; ++r)
+          if (r0 + r < R) {
+            const unsigned int qc = (unsigned int)qs[(r0 + r) * L + l + u];
+#pragma unroll
+            for (int i = 0; i < NV; ++i) lsh_match_accumulate<CodeT>(v[u][i], qc, &acc[r][i * 4]);
+          }
+    }
+    for (; l < L; ++l) {
       uint4 v[NV];
 #pragma unroll
       for (int i = 0; i < NV; ++i) v[i] = __ldg(reinterpret_cast<const uint4*>(pbase + (int64_t)l * cap) + i);
 #pragma unroll
-      for (int r = 0; r < LSH_MR; ++r) {
+      for (int r = 0; r < LSH_MR; ++r)
         if (r0 + r < R) {
           const unsigned int qc = (unsigned int)qs[(r0 + r) * L + l];
-          if (sizeof(CodeT) == 1) {
-            const unsigned int rep = qc * 0x01010101u;
 #pragma unroll
-            for (int i = 0; i < NV; ++i) {
-              acc[r][i * 4 + 0] |= __vcmpeq4(v[i].x, rep);
-              acc[r][i * 4 + 1] |= __vcmpeq4(v[i].y, rep);
-              acc[r][i * 4 + 2] |= __vcmpeq4(v[i].z, rep);
-              acc[r][i * 4 + 3] |= __vcmpeq4(v[i].w, rep);
-            }
-          } else {
-            const unsigned int rep = qc * 0x00010001u;
-#pragma unroll
-            for (int i = 0; i < NV; ++i) {
-              acc[r][i * 4 + 0] |= __vcmpeq2(v[i].x, rep);
-              acc[r][i * 4 + 1] |= __vcmpeq2(v[i].y, rep);
-              acc[r][i * 4 + 2] |= __vcmpeq2(v[i].z, rep);
-              acc[r][i * 4 + 3] |= __vcmpeq2(v[i].w, rep);
-            }
-          }
+          for (int i = 0; i < NV; ++i) lsh_match_accumulate<CodeT>(v[i], qc, &acc[r][i * 4]);
         }
-      }
     }
     const int64_t left = S - word * 32;
     const unsigned int valid = left >= 32 ? 0xffffffffu : ((1u << left) - 1u);
@@ -447,14 +477,17 @@ lsh_match_kernel(const CodeT* __restrict__ planes, int64_t cap, const CodeT* __r
         }
         const int g = (r0 + r) / Sq, qi = (r0 + r) % Sq;
         const int64_t row = ((b * Hq) + hkv * G + g) * Sq + qi;
-        out_bits[row * W + word] = bits & valid;
+        bits &= valid;
+        if (prev_bits != nullptr) bits |= prev_bits[row * W + word];
+        out_bits[row * W + word] = bits;
       }
     }
   }
 }
 
 extern "C" int sah_lsh_match(const void* planes, int64_t cap, const void* qcodes, int B, int Hq,
-                             int Sq, int G, int L, int K, int64_t S, int64_t W, uint32_t* out_bits,
+                             int Sq, int G, int L, int K, int64_t S, int64_t W,
+                             const uint32_t* prev_bits, uint32_t* out_bits, int sm_count,
                              void* stream) {
   SAH_REQUIRE(planes && qcodes && out_bits, "lsh_match: null pointer");
   SAH_REQUIRE(G > 0 && Hq % G == 0 && L > 0 && K > 0 && S > 0 && W * 32 >= S, "lsh_match: bad shape");
@@ -464,17 +497,22 @@ extern "C" int sah_lsh_match(const void* planes, int64_t cap, const void* qcodes
   const size_t smem = (size_t)G * Sq * L * csz;
   if (smem > 48 * 1024) return sah_fail(SAH_ERR_UNSUPPORTED, "lsh_match: too many query rows per group");
   const int64_t words = (S + 31) / 32;
-  dim3 grid((unsigned)((words + 255) / 256), (unsigned)(B * (Hq / G)));
+  if (sm_count <= 0) sm_count = 148;
+  // a short key range (one rank's share of a sharded sequence) still gets a few CTAs per SM
+  int threads = 256;
+  const int64_t bh = (int64_t)B * (Hq / G);
+  while (threads > 64 && sah_ceil_div(words, threads) * bh < 4ll * sm_count) threads >>= 1;
+  dim3 grid((unsigned)sah_ceil_div(words, threads), (unsigned)bh);
   cudaStream_t st = (cudaStream_t)stream;
   sah_prof_begin(SAH_PROF_LSH_MATCH, st);
   if (csz == 1)
-    lsh_match_kernel<uint8_t><<<grid, 256, smem, st>>>(reinterpret_cast<const uint8_t*>(planes), cap,
-                                                       reinterpret_cast<const uint8_t*>(qcodes), Hq, Sq,
-                                                       G, L, S, W, out_bits);
+    lsh_match_kernel<uint8_t><<<grid, threads, smem, st>>>(reinterpret_cast<const uint8_t*>(planes), cap,
+                                                           reinterpret_cast<const uint8_t*>(qcodes), Hq, Sq,
+                                                           G, L, S, W, prev_bits, out_bits);
   else
-    lsh_match_kernel<uint16_t><<<grid, 256, smem, st>>>(reinterpret_cast<const uint16_t*>(planes), cap,
-                                                        reinterpret_cast<const uint16_t*>(qcodes), Hq,
-                                                        Sq, G, L, S, W, out_bits);
+    lsh_match_kernel<uint16_t><<<grid, threads, smem, st>>>(reinterpret_cast<const uint16_t*>(planes), cap,
+                                                            reinterpret_cast<const uint16_t*>(qcodes), Hq,
+                                                            Sq, G, L, S, W, prev_bits, out_bits);
   SAH_LAUNCH_CHECK("lsh_match");
   sah_prof_end(SAH_PROF_LSH_MATCH, st);
   return SAH_OK;

@@ -448,6 +448,44 @@ extern "C" int sah_mask_sample_data(const uint32_t* prev_bits, const uint32_t* o
   return SAH_OK;
 }
 
+// ---- weight 1 for the entries of a sub-set ------------------------------------------------------
+// data[entry] = 1 for every entry of `bits` whose column is also set in `unit_bits`: the
+// clamp(prev + p, 0, 1) of a dense merge when `prev` has unit weights and p <= 1.
+template <typename T>
+__global__ void mask_unit_data_kernel(const uint32_t* __restrict__ bits,
+                                      const uint32_t* __restrict__ unit_bits,
+                                      const int32_t* __restrict__ wpre,
+                                      const int64_t* __restrict__ ptr, int64_t rows, int64_t W,
+                                      T* __restrict__ data) {
+  int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= rows * W) return;
+  const uint32_t m = bits[t];
+  uint32_t u = unit_bits[t] & m;
+  if (!u) return;
+  const int64_t row = t / W;
+  const int64_t o = ptr[row] + wpre[t];
+  while (u) {
+    const int b = __ffs(u) - 1;
+    u &= u - 1;
+    data[o + __popc(m & ((1u << b) - 1u))] = sah_from_float<T>(1.f);
+  }
+}
+
+extern "C" int sah_mask_unit_data(const uint32_t* bits, const uint32_t* unit_bits,
+                                  const int32_t* wpre, const int64_t* ptr, int dtype, int64_t rows,
+                                  int64_t W, void* data, void* stream) {
+  SAH_REQUIRE(bits && unit_bits && wpre && ptr, "unit_data: null pointer");
+  if (rows == 0) return SAH_OK;
+  SAH_REQUIRE(data != nullptr, "unit_data: data is null");
+  const int64_t total = rows * W;
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    mask_unit_data_kernel<T><<<(unsigned)sah_ceil_div(total, 256), 256, 0, (cudaStream_t)stream>>>(
+        bits, unit_bits, wpre, ptr, rows, W, (T*)data);
+  });
+  SAH_LAUNCH_CHECK("mask_unit_data");
+  return SAH_OK;
+}
+
 // ---- ragged sample list -> bitmap ----------------------------------------------------------
 __global__ void mask_scatter_samples_kernel(const int64_t* __restrict__ cols,
                                             const int64_t* __restrict__ sptr, int64_t rows,

@@ -90,6 +90,12 @@ _SIGNATURES = {
                              _L, _I, c_float, _P, _L, _L, _L, _P, POINTER(AttnSizes), _P, _P, _P,
                              _P, _P, _P, _P, _P, _P],
     "sah_attn_merge_parts": [_P, _P, _I, _I, _I, _I, _I, _P, _I, _P, _P],
+    "sah_attn_plan_lsh": [_P, _P, _P, _L, _P, _I, _I, _I, _I, _L, _L, POINTER(AttnSizes), _P, _P, _P,
+                          _P, _P],
+    "sah_masked_attention_lsh": [_P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _I, _I, _I, _L,
+                                 _I, c_float, _P, _L, _L, _L, _P, POINTER(AttnSizes), _P, _P, _P, _P,
+                                 _P, _P, _P, _P, _P, _P, _P, _P, _P],
+    "sah_mask_unit_data": [_P, _P, _P, _P, _I, _L, _L, _P, _P],
     "sah_adaptive_budget": [_P, _I, c_float, _P, _L, _L, _L, _P, _P, _P, _P, _I, _I, _I, _L, _L, _L,
                             _L, _L, ctypes.c_uint64, _P, _P, c_float, c_float, _P, _P, _P, _P],
     "sah_topp_select": [_P, _I, c_float, _P, _L, _L, _L, _I, _I, _I, _L, _L, _P, c_float, _P, _I, _P, _P],
@@ -108,8 +114,8 @@ _SIGNATURES = {
     "sah_lsh_key_sums": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _I, _P, _P],
     "sah_lsh_key_stats": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _I, _P, _L, _P, _P, _I, _P],
     "sah_lsh_key_sign": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _I, _P, _P, _P, _P, _I, _I, _L, _P, _P],
-    "sah_lsh_query": [_P, _I, _L, _L, _L, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P, _P, _P],
-    "sah_lsh_match": [_P, _L, _P, _I, _I, _I, _I, _I, _I, _L, _L, _P, _P],
+    "sah_lsh_query": [_P, _I, _L, _L, _L, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P, _P, _P, _P, _P],
+    "sah_lsh_match": [_P, _L, _P, _I, _I, _I, _I, _I, _I, _L, _L, _P, _P, _I, _P],
     "sah_lsh_key_den": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _I, _P, _P, _L, _P, _P, _P, _I, _P],
     "sah_lsh_prob": [_P, _I, _L, _L, _L, _I, _I, _I, _I, _I, _P, _P, _P, _L, _P, _P, _P, _P, _P, _L,
                      _I, _I, _P, _P, _I, _P],

@@ -17,6 +17,14 @@ every key.  Here the signatures of a layer live in a `PackedLSHSignatures`
 (one code per table and key, table-major, once per KV head), a match kernel streams
 them, and probabilities are evaluated for matched keys only.
 
+In bfloat16 decode (at most four mask rows per KV group, previous mask empty or with unit
+weights) the mask is returned with a `DeferredLSHWeights` payload: the matched set and what
+the attention kernel needs to turn the K row it gathers anyway into the key's weight
+(`sah_masked_attention_lsh`).  Nothing then reads the matched K rows a second time and no
+weight array is written.  Whoever asks the mask for its indices, weights or dense form gets
+them from the probability kernel, which rounds every step as the reference does
+(`MagicPig.fused_weights = False` makes that the only path).
+
 `sparse_meta_data` keys are the reference's: `"projections"[layer]` (`[D+1, L*K]`,
 used as is when pre-populated), `"key_mean"[layer]` (`[B, Hq, 1, D]`, used as is when
 pre-populated) and `"key_signature"[layer]` (the packed handle; a reference-layout
@@ -134,9 +142,41 @@ class PackedLSHSignatures:
         return new
 
 
+class DeferredLSHWeights:
+    """What `sah_attn_plan_lsh` + `sah_masked_attention_lsh` need of one MagicPig call, and the
+    way back to an ordinary bitmap + weight array (`materialise`)."""
+
+    def __init__(self, masker: "MagicPig", previous_mask: Mask, match_bits: torch.Tensor,
+                 unit_bits: Optional[torch.Tensor], qhat: torch.Tensor, qmu: torch.Tensor,
+                 qunit: torch.Tensor, sig: PackedLSHSignatures, table: torch.Tensor,
+                 keys: torch.Tensor, mean: Optional[torch.Tensor], shape: Tuple[int, int, int, int],
+                 G: int) -> None:
+        self.masker, self.previous_mask = masker, previous_mask
+        self.match_bits, self.unit_bits = match_bits, unit_bits
+        self.qhat, self.qmu, self.qunit = qhat, qmu, qunit
+        self.sig, self.table, self.keys, self.mean = sig, table, keys, mean
+        self.shape, self.G = shape, G
+        self.device = match_bits.device
+
+    def materialise(self) -> NativeBits:
+        """`previous.merge_mask(matches with their collision probabilities)`, every operation of
+        the probability rounded as the reference rounds it (magic_pig.py:374-403, :581-593)."""
+        B, Hq, Sq, S = self.shape
+        rows = B * Hq * Sq
+        this = NativeBits(self.match_bits, rows, S)
+        self.masker._probabilities(this, self.keys, self.qunit, self.sig, self.mean, self.table,
+                                   self.shape, self.G, self.previous_mask.dtype)
+        merged = self.previous_mask.merge_mask(
+            Mask._from_native(self.shape, self.previous_mask.dtype, this), inplace=False)
+        return merged.native_bits()
+
+
 @MaskerRegistry.register(MagicPigConfig)
 class MagicPig(SamplingMasker):
     """LSH-sampled keys weighted by their collision probability."""
+
+    #: bfloat16 decode: leave the weights to the attention kernel (see the module docstring)
+    fused_weights: bool = True
 
     def __init__(self, config: MagicPigConfig) -> None:
         super().__init__(config)
@@ -280,30 +320,62 @@ class MagicPig(SamplingMasker):
 
         rows = B * Hq * Sq
         W = words_per_row(S)
+        # the attention kernel can evaluate the weights itself for bfloat16 decode shapes when
+        # everything selected so far has weight 1
+        prev_nb = None
+        fused = self.fused_weights and dtype == torch.bfloat16 and D in (64, 128) and G <= 4
+        if fused and not previous_mask.is_empty:
+            prev_nb = _native_ops.unit_weight_bits(previous_mask)
+            fused = prev_nb is not None
         qcodes = torch.empty((rows, self.lsh_l), dtype=sig.planes.dtype, device=dev)
         qunit = torch.empty((rows, D), dtype=torch.float32, device=dev)
+        qhat = torch.empty((rows, D), dtype=dtype, device=dev) if fused else None
+        qmu = torch.empty(rows, dtype=torch.float32, device=dev) if fused else None
         _native.check(
             lib.sah_lsh_query(q.data_ptr(), code, q.stride(0), q.stride(1), q.stride(2), B, Hq, Sq, G, D,
                               _native.ptr(mean), proj.data_ptr(), self.lsh_l, self.lsh_k,
-                              qcodes.data_ptr(), qunit.data_ptr(), st), "sah_lsh_query")
-        bits = torch.zeros((rows, W), dtype=torch.int32, device=dev)
+                              qcodes.data_ptr(), qunit.data_ptr(), _native.ptr(qhat), _native.ptr(qmu),
+                              st), "sah_lsh_query")
+        bits = torch.empty((rows, W), dtype=torch.int32, device=dev)
         _native.check(
             lib.sah_lsh_match(sig.planes.data_ptr(), sig.capacity, qcodes.data_ptr(), B, Hq, Sq, G,
-                              self.lsh_l, self.lsh_k, S, W, bits.data_ptr(), st), "sah_lsh_match")
-        nb = NativeBits(bits, rows, S)
-        nb.ensure_scan()
-        data = torch.empty(rows * S, dtype=dtype, device=dev)  # worst case; nothing is read back
+                              self.lsh_l, self.lsh_k, S, W, None, bits.data_ptr(),
+                              _native.sm_count(dev), st), "sah_lsh_match")
+        if W * 32 > (S + 31) // 32 * 32:
+            bits[:, (S + 31) // 32:].zero_()  # padding words of the row stride
         table = _native_ops.lsh_prob_table(dev, self.lsh_k, self.lsh_l) if dtype == torch.bfloat16 else None
+        shape = (B, Hq, Sq, S)
+        if fused:
+            payload = DeferredLSHWeights(self, previous_mask, bits,
+                                         None if prev_nb is None else prev_nb.bits, qhat, qmu, qunit,
+                                         sig, table, k, mean, shape, G)
+            return Mask._from_native(shape, previous_mask.dtype,
+                                     NativeBits(None, rows, S, deferred=payload))
+        nb = NativeBits(bits, rows, S)
+        self._probabilities(nb, k, qunit, sig, mean, table, shape, G, dtype)
+        this_mask = Mask._from_native(shape, previous_mask.dtype, nb)
+        return previous_mask.merge_mask(this_mask, inplace=False)
+
+    def _probabilities(self, nb: NativeBits, k: torch.Tensor, qunit: torch.Tensor,
+                       sig: PackedLSHSignatures, mean: Optional[torch.Tensor],
+                       table: Optional[torch.Tensor], shape: Tuple[int, int, int, int], G: int,
+                       dtype: torch.dtype) -> None:
+        """Fill `nb.data` with the collision probability of every entry of `nb` (:374-403)."""
+        B, Hq, Sq, S = shape
+        lib = _native.load()
+        dev = k.device
+        st = _native.stream_of(dev)
+        nb.ensure_scan()
+        data = torch.empty(nb.rows * S, dtype=dtype, device=dev)  # worst case; nothing is read back
         _native.check(
-            lib.sah_lsh_prob(k.data_ptr(), code, k.stride(0), k.stride(1), k.stride(2), B, Hq, Sq, G, D,
-                             _native.ptr(mean), sig.norms.data_ptr(), sig.dens.data_ptr(), sig.capacity,
-                             sig.max_norm.data_ptr(), qunit.data_ptr(), bits.data_ptr(),
-                             nb.wpre.data_ptr(), nb.ptr.data_ptr(), W, self.lsh_k, self.lsh_l,
+            lib.sah_lsh_prob(k.data_ptr(), _native.dtype_code(dtype), k.stride(0), k.stride(1),
+                             k.stride(2), B, Hq, Sq, G, k.shape[-1], _native.ptr(mean),
+                             sig.norms.data_ptr(), sig.dens.data_ptr(), sig.capacity,
+                             sig.max_norm.data_ptr(), qunit.data_ptr(), nb.bits.data_ptr(),
+                             nb.wpre.data_ptr(), nb.ptr.data_ptr(), nb.words, self.lsh_k, self.lsh_l,
                              _native.ptr(table), data.data_ptr(), _native.sm_count(dev), st),
             "sah_lsh_prob")
         nb.data = data
-        this_mask = Mask._from_native((B, Hq, Sq, S), previous_mask.dtype, nb)
-        return previous_mask.merge_mask(this_mask, inplace=False)
 
     @classmethod
     def create_from_config(cls, config: MaskerConfig) -> "MagicPig":

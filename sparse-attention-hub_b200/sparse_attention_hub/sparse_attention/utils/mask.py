@@ -45,14 +45,23 @@ class NativeBits:
     Band edits (sink, local window: `add_band`) and the clearing of a fresh bitmap are not
     launched one by one: they are noted and applied by a single kernel when the words are first
     needed (`bits`).  Objects made by `share()` see the same storage and the same notes.
+
+    A masker whose per-entry weights the attention kernel can evaluate by itself (MagicPig)
+    hands over a `deferred` payload instead of bits and weights: an object with `device` and
+    `materialise() -> NativeBits`.  The attention step reads the payload directly; anybody who
+    asks for `bits`, `data` or the CSR arrays gets the materialised form, built once.
     """
 
-    __slots__ = ("_bits", "_lazy", "data", "ptr", "wpre", "rows", "n_cols", "words")
+    __slots__ = ("_bits", "_lazy", "_data", "ptr", "wpre", "rows", "n_cols", "words", "deferred",
+                 "_device")
 
     MAX_BANDS = 6
 
-    def __init__(self, bits: torch.Tensor, rows: int, n_cols: int,
-                 data: Optional[torch.Tensor] = None, zero_pending: bool = False) -> None:
+    def __init__(self, bits: Optional[torch.Tensor], rows: int, n_cols: int,
+                 data: Optional[torch.Tensor] = None, zero_pending: bool = False,
+                 deferred=None) -> None:
+        if bits is None and deferred is None:
+            raise ValueError("a bitmap needs its words or a deferred payload")
         self._bits = bits         # int32 tensor holding uint32 words, [rows, W]
         # edits not yet applied to the storage: {"zero": the storage is uninitialised and stands
         # for an empty bitmap, "sq": query rows per (batch, head), "bands": [(lo_base, lo_qstep,
@@ -60,10 +69,29 @@ class NativeBits:
         self._lazy = {"zero": bool(zero_pending), "sq": 1, "bands": []}
         self.rows = rows
         self.n_cols = n_cols
-        self.words = bits.shape[-1]
-        self.data = data          # [nnz] in mask dtype or None (all ones)
+        self.words = bits.shape[-1] if bits is not None else words_per_row(n_cols)
+        self._data = data         # [nnz] in mask dtype or None (all ones)
         self.ptr: Optional[torch.Tensor] = None
         self.wpre: Optional[torch.Tensor] = None
+        self.deferred = deferred
+        self._device = bits.device if bits is not None else torch.device(deferred.device)
+
+    def _materialise(self) -> None:
+        """Swap a deferred payload for its bitmap, weights and CSR arrays."""
+        if self._bits is not None:
+            return
+        other = self.deferred.materialise()
+        self._bits, self._lazy = other.bits, {"zero": False, "sq": 1, "bands": []}
+        self._data, self.ptr, self.wpre = other.data, other.ptr, other.wpre
+
+    @property
+    def data(self) -> Optional[torch.Tensor]:
+        self._materialise()
+        return self._data
+
+    @data.setter
+    def data(self, value: Optional[torch.Tensor]) -> None:
+        self._data = value
 
     @classmethod
     def empty(cls, rows: int, n_cols: int, device: torch.device) -> "NativeBits":
@@ -74,16 +102,18 @@ class NativeBits:
 
     def share(self) -> "NativeBits":
         """Same storage and pending edits, CSR companions dropped."""
+        self._materialise()
         other = NativeBits(self._bits, self.rows, self.n_cols)
         other._lazy = self._lazy
         return other
 
     @property
     def device(self) -> torch.device:
-        return self._bits.device
+        return self._device
 
     @property
     def bits(self) -> torch.Tensor:
+        self._materialise()
         if self._lazy["zero"] or self._lazy["bands"]:
             self.flush()
         return self._bits
@@ -92,10 +122,12 @@ class NativeBits:
     def bits(self, value: torch.Tensor) -> None:
         self._bits = value
         self._lazy = {"zero": False, "sq": 1, "bands": []}
+        self.deferred = None
 
     def add_band(self, seq_len_queries: int, lo_base: int, lo_qstep: int, hi_base: int,
                  hi_qstep: int, value: int) -> None:
         """Note a band edit (meaning of `sah_mask_fill_band`); valid for unit-weight masks."""
+        self._materialise()
         lazy = self._lazy
         if lazy["bands"] and (lazy["sq"] != seq_len_queries or len(lazy["bands"]) >= self.MAX_BANDS):
             self.flush()
@@ -124,6 +156,7 @@ class NativeBits:
 
     def ensure_scan(self) -> None:
         """Fill ptr (int64 [rows+1]) and wpre (int32 [rows, W])."""
+        self._materialise()
         if self.ptr is not None:
             return
         lib = _native.load()

@@ -115,24 +115,26 @@ def native_masked_attention(
         nb = Mask.create_full_mask(mask.shape, dtype, dev).native_bits()
     else:
         nb = mask.native_bits()
-    has_data = nb.data is not None
-    if has_data:
+    # a MagicPig mask may come with what the kernel needs to evaluate its weights in place
+    payload = nb.deferred
+    has_data = 2 if payload is not None else int(nb.data is not None)
+    if has_data == 1:
         nb.ensure_scan()
 
     sizes = _native.AttnSizes()
-    _native.check(lib.sah_attn_query_sizes(B, Hq, Hkv, Sq, S, D, int(has_data),
+    _native.check(lib.sah_attn_query_sizes(B, Hq, Hkv, Sq, S, D, has_data,
                                            _native.sm_count(dev), ctypes.byref(sizes)),
                   "sah_attn_query_sizes")
+    if payload is not None and (sizes.rows_per_group > 4 or dtype != torch.bfloat16):
+        payload, has_data = None, int(nb.data is not None)  # materialises the weights
+        nb.ensure_scan()
+        _native.check(lib.sah_attn_query_sizes(B, Hq, Hkv, Sq, S, D, has_data,
+                                               _native.sm_count(dev), ctypes.byref(sizes)),
+                      "sah_attn_query_sizes")
     # scratch is reused across calls of one shape; calls that could overlap on the device
     # (another stream, another host thread) get their own
-    ws = _workspace(dev, sizes, (dev.index, st, threading.get_ident(), B, Hq, Hkv, Sq, S, D, has_data))
-    _native.check(
-        lib.sah_attn_plan(nb.bits.data_ptr(), _native.ptr(nb.data), _native.ptr(nb.wpre),
-                          _native.ptr(nb.ptr), code, B, Hq, Hkv, Sq, S, nb.words,
-                          ctypes.byref(sizes), ws["ucols"].data_ptr(), ws["umemb"].data_ptr(),
-                          _native.ptr(ws["uw"]) if has_data else None, ws["ucount"].data_ptr(), st),
-        "sah_attn_plan")
-
+    key = (dev.index, st, threading.get_ident(), B, Hq, Hkv, Sq, S, D, has_data)
+    ws = _workspace(dev, sizes, key)
     keep, bias_ptr, bsb, bsh, bsq = _bias_args(attention_mask, dtype, S)
     sink_t = None
     if sinks is not None:
@@ -143,32 +145,81 @@ def native_masked_attention(
     rows = B * Hq * Sq
     acc = torch.empty((rows, D), dtype=torch.float32, device=dev) if return_partials else None
     lse = torch.empty((rows, 2), dtype=torch.float32, device=dev) if return_partials else None
-    _native.check(
-        lib.sah_masked_attention(
-            q.data_ptr(), k.data_ptr(), v.data_ptr(), code,
-            q.stride(0), q.stride(1), q.stride(2),
-            k.stride(0), k.stride(1), k.stride(2),
-            v.stride(0), v.stride(1), v.stride(2),
-            B, Hq, Hkv, Sq, S, D, float(scaling), bias_ptr, bsb, bsh, bsq,
-            _native.ptr(sink_t), ctypes.byref(sizes), ws["ucols"].data_ptr(),
-            ws["umemb"].data_ptr(), _native.ptr(ws["uw"]) if has_data else None,
-            ws["ucount"].data_ptr(), ws["partial"].data_ptr(), out.data_ptr(),
-            _native.ptr(acc), _native.ptr(lse), st),
-        "sah_masked_attention")
+    strides = (q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+               v.stride(0), v.stride(1), v.stride(2))
+    try:
+        if payload is not None:
+            sig = payload.sig
+            _native.check(
+                lib.sah_attn_plan_lsh(payload.match_bits.data_ptr(), _native.ptr(payload.unit_bits),
+                                      sig.dens.data_ptr(), sig.capacity, sig.max_norm.data_ptr(), B, Hq,
+                                      Hkv, Sq, S, payload.match_bits.shape[-1], ctypes.byref(sizes),
+                                      ws["ucols"].data_ptr(), ws["umemb"].data_ptr(),
+                                      ws["uw"].data_ptr(), ws["ucount"].data_ptr(), st),
+                "sah_attn_plan_lsh")
+            dump = _weight_dump.get("request")
+            if dump is not None:
+                dump = torch.zeros(sizes.groups * S * sizes.rows_per_group, dtype=torch.float32, device=dev)
+                _weight_dump["weights"] = dump
+            _native.check(
+                lib.sah_masked_attention_lsh(
+                    q.data_ptr(), k.data_ptr(), v.data_ptr(), *strides, B, Hq, Hkv, Sq, S, D,
+                    float(scaling), bias_ptr, bsb, bsh, bsq, _native.ptr(sink_t), ctypes.byref(sizes),
+                    ws["ucols"].data_ptr(), ws["umemb"].data_ptr(), ws["uw"].data_ptr(),
+                    ws["ucount"].data_ptr(), ws["partial"].data_ptr(), payload.qhat.data_ptr(),
+                    payload.qmu.data_ptr(), payload.table.data_ptr(), out.data_ptr(),
+                    _native.ptr(acc), _native.ptr(lse), _native.ptr(dump), st),
+                "sah_masked_attention_lsh")
+        else:
+            _native.check(
+                lib.sah_attn_plan(nb.bits.data_ptr(), _native.ptr(nb.data), _native.ptr(nb.wpre),
+                                  _native.ptr(nb.ptr), code, B, Hq, Hkv, Sq, S, nb.words,
+                                  ctypes.byref(sizes), ws["ucols"].data_ptr(), ws["umemb"].data_ptr(),
+                                  _native.ptr(ws["uw"]) if has_data else None, ws["ucount"].data_ptr(), st),
+                "sah_attn_plan")
+            _native.check(
+                lib.sah_masked_attention(
+                    q.data_ptr(), k.data_ptr(), v.data_ptr(), code, *strides,
+                    B, Hq, Hkv, Sq, S, D, float(scaling), bias_ptr, bsb, bsh, bsq,
+                    _native.ptr(sink_t), ctypes.byref(sizes), ws["ucols"].data_ptr(),
+                    ws["umemb"].data_ptr(), _native.ptr(ws["uw"]) if has_data else None,
+                    ws["ucount"].data_ptr(), ws["partial"].data_ptr(), out.data_ptr(),
+                    _native.ptr(acc), _native.ptr(lse), st),
+                "sah_masked_attention")
+    except Exception:
+        # a refused launch may leave the merge tickets of this scratch non-zero
+        _workspace_cache.pop(key, None)
+        raise
     del keep
     _last_plan["ucount"] = ws["ucount"][: sizes.groups]
+    _last_plan["ws"] = ws
+    _last_plan["sizes"] = (sizes.groups, sizes.rows_per_group, S)
     if return_partials:
         return out, acc, lse
     return out
 
 
-_last_plan: Dict[str, Optional[torch.Tensor]] = {"ucount": None}
+# Test hook: set _weight_dump["request"] to anything but None and the next attention call over a
+# MagicPig mask with in-kernel weights leaves the weights it used in _weight_dump["weights"]
+# (float32 [groups * S * rows_per_group], union-list order; see last_union_list()).
+_weight_dump: Dict[str, Any] = {"request": None, "weights": None}
+
+_last_plan: Dict[str, Any] = {"ucount": None, "ws": None, "sizes": None}
 
 
 def last_union_counts() -> Optional[torch.Tensor]:
     """int32 [groups]: distinct K/V rows the most recent attention call gathered per KV group
     (valid once the launching stream has run; used for bandwidth accounting)."""
     return _last_plan["ucount"]
+
+
+def last_union_list():
+    """(ucols int32 [groups, S], umemb int16 [groups, S], ucount int32 [groups], rows per group)
+    of the most recent attention call: the ascending union of the columns each KV group
+    gathered, and which of the group's rows selected each."""
+    ws, (groups, R, S) = _last_plan["ws"], _last_plan["sizes"]
+    return (ws["ucols"][: groups * S].view(groups, S), ws["umemb"][: groups * S].view(groups, S),
+            ws["ucount"][:groups], R)
 
 
 def merge_attention_partials(acc: torch.Tensor, lse: torch.Tensor, batch: int, heads: int,

@@ -13,7 +13,7 @@ from sparse_attention_hub.sparse_attention import (
     ResearchAttentionConfig,
     SinkMaskerConfig,
 )
-from sparse_attention_hub import workloads
+import workloads
 
 
 def _tiny_llama(dtype):

@@ -42,7 +42,7 @@ def test_bad_arguments_return_a_status_and_a_message():
     assert lib.sah_mask_fill_band(None, 1, 1, 32, 1, 0, 0, 1, 0, 1, None) == 1
     assert b"null" in lib.sah_last_error()
     assert lib.sah_hash_topk(None, 0, None, 32, None, 1, 0, 0, 0, 1, 1, 1, 32, 1, None, 1, None, None) == 1
-    assert lib.sah_lsh_match(None, 32, None, 1, 4, 1, 4, 5, 4, 32, 1, None, None) == 1
+    assert lib.sah_lsh_match(None, 32, None, 1, 4, 1, 4, 5, 4, 32, 1, None, None, 148, None) == 1
     with pytest.raises(_native.NativeLibraryError):
         _native.check(1, "sah_lsh_match")
     with pytest.raises(NotImplementedError):
@@ -56,3 +56,30 @@ def test_workspace_size_queries():
     sizes = _native.AttnSizes()
     assert lib.sah_attn_query_sizes(8, 32, 8, 1, 32768, 128, 0, 148, ctypes.byref(sizes)) == 0
     assert sizes.groups == 64 and sizes.ucols_bytes > 0
+
+
+def test_plan_refuses_sizes_of_another_key_count():
+    """The counter block is laid out by the key count: a plan call whose `sizes` came from a
+    query for fewer keys (too few chunk counters) is refused before anything is launched, and
+    a bitmap row stride W padded beyond ceil(S/32) does not change the layout."""
+    lib = _native.load()
+    small, big = _native.AttnSizes(), _native.AttnSizes()
+    assert lib.sah_attn_query_sizes(1, 8, 2, 1, 40000, 128, 0, 148, ctypes.byref(small)) == 0
+    assert lib.sah_attn_query_sizes(1, 8, 2, 1, 80000, 128, 0, 148, ctypes.byref(big)) == 0
+    assert big.ucount_bytes > small.ucount_bytes
+    one = ctypes.c_void_p(16)  # never dereferenced: the call is refused first
+    status = lib.sah_attn_plan(one, None, None, None, _native.SAH_BF16, 1, 8, 2, 1, 80000, 2500,
+                               ctypes.byref(small), one, one, None, one, None)
+    assert status == 1 and b"key count" in lib.sah_last_error()
+    # W too small for S is refused as before
+    assert lib.sah_attn_plan(one, None, None, None, _native.SAH_BF16, 1, 8, 2, 1, 80000, 100,
+                             ctypes.byref(big), one, one, None, one, None) == 1
+    # the in-kernel MagicPig weights need their own size query (has_data = 2) ...
+    assert lib.sah_attn_plan_lsh(one, None, one, 80000, one, 1, 8, 2, 1, 80000, 2500,
+                                 ctypes.byref(big), one, one, one, one, None) == 1
+    assert b"MagicPig" in lib.sah_last_error()
+    # ... and at most four mask rows per KV group
+    wide = _native.AttnSizes()
+    assert lib.sah_attn_query_sizes(1, 16, 2, 1, 4096, 128, 2, 148, ctypes.byref(wide)) == 0
+    assert lib.sah_attn_plan_lsh(one, None, one, 4096, one, 1, 16, 2, 1, 4096, 128,
+                                 ctypes.byref(wide), one, one, one, one, None) == 2

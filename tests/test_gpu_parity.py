@@ -13,7 +13,7 @@ import torch
 from oracle import attention as o_attention
 from oracle import hashattention as o_hash
 from oracle import mask_ops, qk as o_qk, stacks
-from sparse_attention_hub import workloads
+import workloads
 from sparse_attention_hub.sparse_attention import Mask
 from sparse_attention_hub.sparse_attention import _native_ops
 from sparse_attention_hub.sparse_attention.utils.mask_attention_utils import (

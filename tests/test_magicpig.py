@@ -14,7 +14,7 @@ import numpy as np
 import pytest
 
 from oracle import magicpig, mask_ops, stacks
-from sparse_attention_hub import workloads
+import workloads
 
 from conftest import load_golden
 

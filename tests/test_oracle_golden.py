@@ -14,7 +14,7 @@ import pytest
 
 import oracle
 from oracle import attention, hashattention, mask_ops, qk, stacks, topk
-from sparse_attention_hub import workloads
+import workloads
 
 from conftest import load_golden
 

@@ -12,7 +12,7 @@ import numpy as np
 import pytest
 
 from oracle import mask_ops, pq, stacks
-from sparse_attention_hub import workloads
+import workloads
 
 from conftest import load_golden
 

@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 
 from oracle import mask_ops, quest, stacks
-from sparse_attention_hub import workloads
+import workloads
 
 from conftest import load_golden
 

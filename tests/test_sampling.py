@@ -13,7 +13,7 @@ import numpy as np
 import pytest
 
 from oracle import mask_ops, sampling, stacks
-from sparse_attention_hub import workloads
+import workloads
 
 from conftest import load_golden
 

@@ -17,7 +17,7 @@ import numpy as np
 import pytest
 
 from oracle import mask_ops, sharded as o_sharded, stacks
-from sparse_attention_hub import workloads
+import workloads
 from sparse_attention_hub.sparse_attention.research_attention.sharded import (
     ThreadComm,
     plan_shards,

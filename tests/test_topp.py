@@ -11,7 +11,7 @@ import numpy as np
 import pytest
 
 from oracle import mask_ops, stacks, topp
-from sparse_attention_hub import workloads
+import workloads
 
 from conftest import load_golden
 

@@ -17,7 +17,8 @@ import numpy as np
 import pytest
 import torch
 
-from sparse_attention_hub import _native, workloads
+import workloads
+from sparse_attention_hub import _native
 from sparse_attention_hub.sparse_attention import Mask
 from sparse_attention_hub.sparse_attention.utils.mask_attention_utils import native_masked_attention
 

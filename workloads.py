@@ -266,8 +266,10 @@ def to_torch(x: np.ndarray, dtype: str, device):
 
 
 def masker_configs(stack: List[Tuple[str, Dict[str, Any]]], dtype: str, device="cpu") -> list:
-    """Config dataclasses of `sparse_attention_hub` for a stack description."""
-    from .sparse_attention.research_attention.maskers import fixed
+    """Config dataclasses of `sparse_attention_hub` for a stack description.  The package is
+    whichever one `sparse_attention_hub` resolves to on sys.path: the B200 package, or the
+    reference itself (same import paths, class names and fields) when a caller times that."""
+    from sparse_attention_hub.sparse_attention.research_attention.maskers import fixed
 
     out = []
     for kind, prm in stack:
@@ -295,15 +297,15 @@ def masker_configs(stack: List[Tuple[str, Dict[str, Any]]], dtype: str, device="
                 pq_bits=prm["pq_bits"], kmeans_iter=prm["kmeans_iter"],
                 init_offset=prm["init_offset"], metric=prm["metric"]))
         elif kind == "adaptive_sampling":
-            from .sparse_attention.research_attention.maskers import sampling
+            from sparse_attention_hub.sparse_attention.research_attention.maskers import sampling
             out.append(sampling.AdaptiveSamplingMaskerConfig(
                 base_rate_sampling=prm["base_rate_sampling"], epsilon=prm["epsilon"],
                 delta=prm["delta"], init_offset=prm["init_offset"], local_offset=prm["local_offset"]))
         elif kind == "random_sampling":
-            from .sparse_attention.research_attention.maskers import sampling
+            from sparse_attention_hub.sparse_attention.research_attention.maskers import sampling
             out.append(sampling.RandomSamplingMaskerConfig(sampling_rate=prm["sampling_rate"]))
         elif kind == "magicpig":
-            from .sparse_attention.research_attention.maskers import sampling
+            from sparse_attention_hub.sparse_attention.research_attention.maskers import sampling
             out.append(sampling.MagicPigConfig(lsh_l=prm["lsh_l"], lsh_k=prm["lsh_k"],
                                                center=prm.get("center", True)))
         else:
@@ -312,7 +314,8 @@ def masker_configs(stack: List[Tuple[str, Dict[str, Any]]], dtype: str, device="
 
 
 def research_attention(stack, dtype: str, device="cpu"):
-    from .sparse_attention.research_attention import ResearchAttention, ResearchAttentionConfig
+    from sparse_attention_hub.sparse_attention.research_attention import (ResearchAttention,
+                                                                          ResearchAttentionConfig)
 
     return ResearchAttention.create_from_config(
         ResearchAttentionConfig(masker_configs=masker_configs(stack, dtype, device)))
