@@ -611,6 +611,16 @@ int sah_masked_attention_lsh(const void* q, const void* k, const void* v, int64_
                              const uint16_t* prob_table, void* out, float* acc_out, float* lse_out,
                              float* w_dump, void* stream);
 
+/* Measurement aid (no counterpart in the reference): the K/V row gather of a planned
+ * union list on its own -- the grid, tiling and copy pipeline of the bfloat16
+ * sah_masked_attention without its arithmetic.  Timing it gives the bandwidth that
+ * this access pattern can reach on the device, the ceiling for the attention kernel
+ * on the same list.  `sink` is one device word that is (practically) never written. */
+int sah_attn_gather_probe(const void* k, const void* v, int64_t ks_b, int64_t ks_h, int64_t ks_s,
+                          int64_t vs_b, int64_t vs_h, int64_t vs_s, int B, int Hkv, int Sq,
+                          int64_t S, int D, const sah_attn_sizes* sizes, const int32_t* ucols,
+                          const int32_t* ucount, unsigned int* sink, void* stream);
+
 /* Merge n_parts partial results (unnormalised fp32 accumulators acc
  * [n_parts][rows][D] with lse [n_parts][rows][2]) into out [B][Sq][Hq][D]:
  * the associative combine of sequence-sharded softmax partials. */

@@ -973,6 +973,47 @@ extern "C" int sah_masked_attention_lsh(const void* q, const void* k, const void
                                acc_out, lse_out, &lsh, stream);
 }
 
+extern "C" int sah_attn_gather_probe(const void* k, const void* v, int64_t ks_b, int64_t ks_h,
+                                     int64_t ks_s, int64_t vs_b, int64_t vs_h, int64_t vs_s, int B,
+                                     int Hkv, int Sq, int64_t S, int D, const sah_attn_sizes* sizes,
+                                     const int32_t* ucols, const int32_t* ucount,
+                                     unsigned int* sink, void* stream) {
+  SAH_REQUIRE(k && v && sizes && ucols && ucount && sink, "attn_gather_probe: null pointer");
+  if (D != 64 && D != 128)
+    return sah_fail(SAH_ERR_UNSUPPORTED, "attn_gather_probe: head dim %d (64 or 128 supported)", D);
+  SAH_REQUIRE((ks_s * 2) % 16 == 0 && (vs_s * 2) % 16 == 0 && (uintptr_t)k % 16 == 0 &&
+                  (uintptr_t)v % 16 == 0, "attn_gather_probe: K and V rows must be 16-byte aligned");
+  AttnArgs a = {};
+  a.k = k; a.v = v;
+  a.ks_b = ks_b; a.ks_h = ks_h; a.ks_s = ks_s;
+  a.vs_b = vs_b; a.vs_h = vs_h; a.vs_s = vs_s;
+  a.Hkv = Hkv; a.Sq = Sq;
+  a.q_block = sizes->q_block;
+  a.nqb = (Sq + a.q_block - 1) / a.q_block;
+  a.nsplit = sizes->nsplit;
+  a.S = S;
+  a.ucols = ucols; a.ucount = ucount;
+  SAH_REQUIRE((int64_t)sizes->groups == (int64_t)B * Hkv * a.nqb,
+              "attn_gather_probe: sizes do not match the extents");
+  dim3 grid((unsigned)a.nsplit, (unsigned)sizes->groups);
+  cudaStream_t st = (cudaStream_t)stream;
+  static bool allowed[2][64] = {};
+  cudaError_t e;
+  sah_prof_begin(SAH_PROF_OTHER, st);
+  if (D == 128) {
+    e = atm_allow_smem(attention_gather_probe_kernel<128>, AtmCfg<128>::SMEM, allowed[0]);
+    if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "gather probe attr: %s", cudaGetErrorString(e));
+    attention_gather_probe_kernel<128><<<grid, ATM_THREADS, AtmCfg<128>::SMEM, st>>>(a, sink);
+  } else {
+    e = atm_allow_smem(attention_gather_probe_kernel<64>, AtmCfg<64>::SMEM, allowed[1]);
+    if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "gather probe attr: %s", cudaGetErrorString(e));
+    attention_gather_probe_kernel<64><<<grid, ATM_THREADS, AtmCfg<64>::SMEM, st>>>(a, sink);
+  }
+  SAH_LAUNCH_CHECK("attn_gather_probe");
+  sah_prof_end(SAH_PROF_OTHER, st);
+  return SAH_OK;
+}
+
 // Merge partial results computed on different sequence shards.
 template <typename T>
 __global__ void attn_merge_parts_kernel(const float* __restrict__ acc, const float* __restrict__ lse,

@@ -536,6 +536,82 @@ masked_attention_mma_kernel(AttnArgs a, int* __restrict__ tickets, const float* 
   }
 }
 
+// Row-gather probe: the copy half of the attention kernel alone.  Same grid, same dealing of
+// 16-key tiles to warps, same 16-byte asynchronous copies into the same per-warp ring, no
+// arithmetic: the time of this kernel on a union list is what the K/V row gather of that list
+// costs on this device, i.e. the ceiling the attention kernel can approach.
+template <int D>
+__global__ void __launch_bounds__(ATM_THREADS, 2)
+attention_gather_probe_kernel(AttnArgs a, unsigned int* __restrict__ sink) {
+  using C = AtmCfg<D>;
+  extern __shared__ __align__(128) unsigned char atm_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned char* ring = atm_smem + warp * C::WARP_BYTES;
+  const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
+  const int split = blockIdx.x;
+  const int64_t g = blockIdx.y;
+  const int64_t bk = g / a.nqb;
+  const int kvh = (int)(bk % a.Hkv);
+  const int64_t b = bk / a.Hkv;
+  const __nv_bfloat16* kbase = reinterpret_cast<const __nv_bfloat16*>(a.k) + b * a.ks_b + kvh * a.ks_h;
+  const __nv_bfloat16* vbase = reinterpret_cast<const __nv_bfloat16*>(a.v) + b * a.vs_b + kvh * a.vs_h;
+  const int32_t* gcols = a.ucols + g * a.S;
+  const int U = a.ucount[g];
+  const int total_tiles = (U + ATM_TILE - 1) / ATM_TILE;
+  const int lanes_total = a.nsplit * ATM_WARPS;
+  const int my_first = split * ATM_WARPS + warp;
+  const int my_tiles =
+      (total_tiles > my_first) ? (total_tiles - my_first + lanes_total - 1) / lanes_total : 0;
+  auto load_col = [&](int t) {
+    int col = -1;
+    if (t < my_tiles) {
+      const int u = (my_first + t * lanes_total) * ATM_TILE + lane;
+      if (lane < ATM_TILE && u < U) col = gcols[u];
+    }
+    return col;
+  };
+  int pre0 = load_col(0), pre1 = load_col(1);
+  constexpr int CPR = C::ROWB / 16;
+  constexpr int RPS = 32 / CPR;
+  const int my_chunk = lane % CPR, my_sub = lane / CPR;
+  const uint32_t my_dst = my_sub * C::RSTR + my_chunk * 16;
+  const unsigned char* k_bytes = reinterpret_cast<const unsigned char*>(kbase) + my_chunk * 16;
+  const unsigned char* v_bytes = reinterpret_cast<const unsigned char*>(vbase) + my_chunk * 16;
+  const int64_t ks_bytes = a.ks_s * 2, vs_bytes = a.vs_s * 2;
+  auto issue = [&](int t) {
+    const int st = t % ATM_STAGES;
+    const int col = pre0;
+    pre0 = pre1;
+    pre1 = load_col(t + 2);
+    const uint32_t dst0 = ring_s + st * C::STAGE_BYTES + my_dst;
+#pragma unroll
+    for (int it = 0; it < ATM_TILE / RPS; ++it) {
+      const int rc = __shfl_sync(0xffffffffu, col, it * RPS + my_sub);
+      const uint32_t dst = dst0 + it * RPS * C::RSTR;
+      if (rc >= 0) {
+        atm_cp_async16(dst, k_bytes + rc * ks_bytes);
+        atm_cp_async16(dst + C::TILE_BYTES, v_bytes + rc * vs_bytes);
+      }
+    }
+  };
+#pragma unroll
+  for (int s = 0; s < ATM_STAGES - 1; ++s) {
+    if (s < my_tiles) issue(s);
+    asm volatile("cp.async.commit_group;\n" ::);
+  }
+  unsigned int acc = 0u;
+  for (int t = 0; t < my_tiles; ++t) {
+    if (t + ATM_STAGES - 1 < my_tiles) issue(t + ATM_STAGES - 1);
+    asm volatile("cp.async.commit_group;\n" ::);
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(ATM_STAGES - 1));
+    __syncwarp();
+    acc += *reinterpret_cast<const unsigned int*>(ring + (t % ATM_STAGES) * C::STAGE_BYTES + lane * 16);
+    __syncwarp();
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::);
+  if (acc == 0x9e3779b9u) *sink = acc;  // keeps the reads alive; practically never true
+}
+
 // The kernels ask for more dynamic shared memory than the default limit; the attribute is
 // set once per device and instantiation.
 template <typename Kernel>

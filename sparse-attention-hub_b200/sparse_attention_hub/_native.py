@@ -96,6 +96,8 @@ _SIGNATURES = {
                                  _I, c_float, _P, _L, _L, _L, _P, POINTER(AttnSizes), _P, _P, _P, _P,
                                  _P, _P, _P, _P, _P, _P, _P, _P, _P],
     "sah_mask_unit_data": [_P, _P, _P, _P, _I, _L, _L, _P, _P],
+    "sah_attn_gather_probe": [_P, _P, _L, _L, _L, _L, _L, _L, _I, _I, _I, _L, _I, POINTER(AttnSizes),
+                              _P, _P, _P, _P],
     "sah_adaptive_budget": [_P, _I, c_float, _P, _L, _L, _L, _P, _P, _P, _P, _I, _I, _I, _L, _L, _L,
                             _L, _L, ctypes.c_uint64, _P, _P, c_float, c_float, _P, _P, _P, _P],
     "sah_topp_select": [_P, _I, c_float, _P, _L, _L, _L, _I, _I, _I, _L, _L, _P, c_float, _P, _I, _P, _P],
@@ -132,7 +134,7 @@ _SIGNATURES = {
 }
 
 PROFILE_SLOTS = {"attention": 0, "hash_topk": 1, "hash_encode": 2, "qk_scores": 3,
-                 "topk_select": 4, "attn_plan": 5, "attn_merge": 6, "lsh_match": 8, "lsh_prob": 9,
+                 "topk_select": 4, "attn_plan": 5, "attn_merge": 6, "other": 7, "lsh_match": 8, "lsh_prob": 9,
                  "pq_scores": 10, "adaptive_budget": 11, "topp_select": 12, "quest_scores": 13}
 
 EXPORTED_SYMBOLS = sorted(list(_SIGNATURES) + ["sah_version", "sah_last_error", "sah_launch_count"])

@@ -194,6 +194,7 @@ def native_masked_attention(
     _last_plan["ucount"] = ws["ucount"][: sizes.groups]
     _last_plan["ws"] = ws
     _last_plan["sizes"] = (sizes.groups, sizes.rows_per_group, S)
+    _last_plan["attn_sizes"] = sizes
     if return_partials:
         return out, acc, lse
     return out
@@ -220,6 +221,24 @@ def last_union_list():
     ws, (groups, R, S) = _last_plan["ws"], _last_plan["sizes"]
     return (ws["ucols"][: groups * S].view(groups, S), ws["umemb"][: groups * S].view(groups, S),
             ws["ucount"][:groups], R)
+
+
+def gather_probe(keys: torch.Tensor, values: torch.Tensor, seq_len_queries: int = 1) -> None:
+    """Launch the row-gather probe (`sah_attn_gather_probe`) on the union list of the most recent
+    bfloat16 attention call over these keys and values: the copy pipeline of the attention kernel
+    without its arithmetic.  Timed by the caller (profile slot "other"), it gives the ceiling
+    that the gather of exactly those rows allows."""
+    lib = _native.load()
+    ws, sizes = _last_plan["ws"], _last_plan["attn_sizes"]
+    k, v = _rowmajor(keys), _rowmajor(values)
+    B, Hkv, S, D = k.shape
+    sink = ws.setdefault("probe_sink", torch.zeros(1, dtype=torch.int32, device=k.device))
+    _native.check(
+        lib.sah_attn_gather_probe(k.data_ptr(), v.data_ptr(), k.stride(0), k.stride(1), k.stride(2),
+                                  v.stride(0), v.stride(1), v.stride(2), B, Hkv, seq_len_queries, S, D,
+                                  ctypes.byref(sizes), ws["ucols"].data_ptr(), ws["ucount"].data_ptr(),
+                                  sink.data_ptr(), _native.stream_of(k.device)),
+        "sah_attn_gather_probe")
 
 
 def merge_attention_partials(acc: torch.Tensor, lse: torch.Tensor, batch: int, heads: int,

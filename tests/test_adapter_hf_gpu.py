@@ -1,8 +1,10 @@
 """The HuggingFace hook end to end on a GPU: a small random-weight Llama decodes with the
 registered custom attention function.  With a masker stack that selects every key
 (Sink over the whole sequence -> full mask) the sparse call must reproduce the model's own
-eager attention; with a real sparse stack it must run and produce finite logits."""
+eager attention; with a real sparse stack the attention output of layer 0, for the queries, keys
+and values the hook was given, must be what the CPU restatement of the reference computes."""
 
+import numpy as np
 import pytest
 import torch
 
@@ -57,6 +59,18 @@ def test_gpu_sparse_stack_decodes_through_the_hook():
     adapter = ModelAdapterHF("tiny-llama", cfg, model=model, tokenizer=None)
     ids = torch.randint(0, 128, (1, 300), device="cuda:0")
     meta: dict = {}
+    # record what the hook hands to layer 0 and what it gets back
+    seen = []
+    inner = adapter.sparse_attention.custom_attention
+
+    def recording(module, queries, keys, values, attention_mask, scaling, dropout, **kwargs):
+        result = inner(module, queries, keys, values, attention_mask, scaling, dropout, **kwargs)
+        if kwargs.get("layer_idx") == 0:
+            seen.append(tuple(None if t is None else t.detach().float().cpu().numpy()
+                              for t in (queries, keys, values, attention_mask, result[0])) + (float(scaling),))
+        return result
+
+    adapter.sparse_attention.custom_attention = recording
     with torch.no_grad():
         ctx = model(ids[:, :296], use_cache=True)
         with adapter.enable_sparse_mode():
@@ -66,3 +80,13 @@ def test_gpu_sparse_stack_decodes_through_the_hook():
                 out = model(nxt, past_key_values=out.past_key_values, use_cache=True, sparse_meta_data=meta)
     assert torch.isfinite(out.logits.float()).all()
     assert meta["key"][0].length == 303 and meta["key"][1].length == 303
+    # question tokens (Sq = 4, causal mask) and three decode steps, each against the restatement
+    from oracle import stacks
+
+    assert [s_[0].shape[2] for s_ in seen] == [4, 1, 1, 1]
+    stack = [("sink", {"sink_size": 4}), ("local", {"window_size": 16}),
+             ("hash_topk", {"heavy_size": 0.1, "bits": 32, "hidden": 32, "layers": 2, "activation": "silu",
+                            "weights": {n: [workloads.to_dtype(a, "bf16") for a in arrs] for n, arrs in w.items()}})]
+    for q, k, v, am, got, scaling in seen:
+        _, ref_out, _ = stacks.run_stack(stack, q, k, v, scaling, "bf16", attention_mask=am)
+        np.testing.assert_allclose(got, ref_out, atol=2e-2, rtol=2e-2)

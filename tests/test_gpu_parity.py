@@ -136,6 +136,11 @@ def test_hash_incremental_key_cache():
     fresh = ra.build_mask(q, k, v, None, wl.scaling, 0.0, {}, layer_idx=0)
     a, b = m2.get_index_mask(), fresh.get_index_mask()
     assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+    # and both are what the restatement selects on all 900 keys
+    ref_mask, _, rmeta = stacks.run_stack(wl.stack, wl.q, wl.k, wl.v, wl.scaling, "bf16")
+    _assert_mask_equal(m2, ref_mask)
+    kc = meta["key"][0]
+    np.testing.assert_array_equal(kc.codes[..., : kc.length].cpu().numpy().view(np.uint32), rmeta["hash_kcodes"])
     with pytest.raises(ValueError):
         ra.build_mask(q, k[:, :, :100], v[:, :, :100], None, wl.scaling, 0.0, meta, layer_idx=0)
 

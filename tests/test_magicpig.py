@@ -185,6 +185,42 @@ def test_gpu_merge_of_two_weighted_masks():
             assert torch.equal(merged.get_dense_mask(), want)
 
 
+# ------------------------------------------------------------------ CPU: the restatement's own shortcuts
+def test_fast_projection_signs_equal_the_fixed_order():
+    """BLAS product + recomputation of the sums near zero gives the signs of the fixed order."""
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((3000, 129)).astype(np.float32)
+    p = rng.standard_normal((129, 64)).astype(np.float32)
+    x[:50] = 0.0                                  # exact zeros: "not positive"
+    x[50:200, 64:] = -x[50:200, :65][:, ::-1]     # sums that cancel almost exactly
+    p[:64, :8] = p[64:128, :8][::-1]
+    x[200] = np.nan
+    np.testing.assert_array_equal(magicpig.project_signs_fast(x, p), magicpig.project_signs(x, p))
+
+
+def test_chunked_step_equals_the_whole_sequence():
+    """`chunked_step` (the form that scales to 1M keys) against `run_stack` on a sequence that
+    fits: identical masks chunk by chunk, the same output."""
+    wl = workloads.magicpig(seed=64, dtype="bf16", B=1, Hq=8, Hkv=2, S=1500, D=128, sink=6, window=20,
+                            lsh_l=30, lsh_k=6, n_clusters=8)
+    proj = wl.stack[-1][1]["projection"]
+    ref_mask, ref_out, _ = _oracle(wl, {})
+    masks = {}
+    out, st = magicpig.chunked_step(wl.stack[-1][1], 6, 20, wl.q,
+                                    lambda a, b: (wl.k[:, :, a:b], wl.v[:, :, a:b]), 1500, 400, "bf16",
+                                    proj, wl.scaling, on_chunk=lambda a, b, m, c: masks.__setitem__(a, m))
+    np.testing.assert_array_equal(np.concatenate([masks[a] for a in sorted(masks)], axis=-1), ref_mask)
+    np.testing.assert_allclose(out, ref_out, atol=4e-3, rtol=1e-2)
+    # handing a chunk its matches instead of its signatures changes nothing
+    def _m(a, b):
+        return ref_mask[..., a:b] != 0
+
+    out2, _ = magicpig.chunked_step(wl.stack[-1][1], 6, 20, wl.q,
+                                    lambda a, b: (wl.k[:, :, a:b], wl.v[:, :, a:b]), 1500, 400, "bf16",
+                                    proj, wl.scaling, known_match=lambda a, b: None if a == 400 else _m(a, b))
+    np.testing.assert_array_equal(out2, out)
+
+
 # ------------------------------------------------------------------ CPU: arithmetic shortcuts of the kernels
 def _rn(x, bits):
     """Round a positive Fraction to `bits` significant bits, ties to even (no range limits)."""

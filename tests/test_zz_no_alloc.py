@@ -7,7 +7,7 @@ entry point keeps them in a device array inside the library image.  This test
 calls it through the C ABI, two calls in a row on the same array (different
 queries and a different mask the second time, so that stale contents would
 show), and compares each output with the regular entry points, which take
-caller-provided workspace.  It also checks that a problem beyond the built-in
+caller-provided workspace, and with the CPU restatement of the reference.  It also checks that a problem beyond the built-in
 limits is refused with a clear message instead of being run.
 """
 
@@ -18,6 +18,7 @@ import pytest
 import torch
 
 import workloads
+from oracle import stacks
 from sparse_attention_hub import _native
 from sparse_attention_hub.sparse_attention import Mask
 from sparse_attention_hub.sparse_attention.utils.mask_attention_utils import native_masked_attention
@@ -58,6 +59,10 @@ def test_static_scratch_matches_workspace_path_twice(dtype, tol):
         torch.cuda.synchronize()
         np.testing.assert_allclose(got.float().cpu().numpy(), want.float().cpu().numpy(),
                                    atol=tol, rtol=tol)
+        # and with the CPU restatement of the reference on the same inputs
+        qn, kn, vn = (workloads.to_dtype(a, dtype) for a in (wl.q, wl.k, wl.v))
+        _, ref_out, _ = stacks.run_stack(wl.stack, qn, kn, vn, wl.scaling, dtype)
+        np.testing.assert_allclose(got.float().cpu().numpy(), ref_out, atol=tol, rtol=tol)
 
 
 def test_static_scratch_rejects_oversized_problem():

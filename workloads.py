@@ -282,7 +282,9 @@ def masker_configs(stack: List[Tuple[str, Dict[str, Any]]], dtype: str, device="
         elif kind == "oracle_topp":
             out.append(fixed.OracleTopPMaskerConfig(top_p=prm["top_p"]))
         elif kind == "quest_topk":
-            out.append(fixed.QuestTopKMaskerConfig(heavy_size=prm["heavy_size"], page_size=prm["page_size"],
+            from sparse_attention_hub.sparse_attention.research_attention.maskers.fixed import (
+                implementations as fixed_impl)
+            out.append(fixed_impl.QuestTopKMaskerConfig(heavy_size=prm["heavy_size"], page_size=prm["page_size"],
                                                    label_bits=prm.get("label_bits", 16)))
         elif kind == "hash_topk":
             w = {0: {name: [to_torch(a, dtype, device) for a in arrs]
@@ -297,7 +299,8 @@ def masker_configs(stack: List[Tuple[str, Dict[str, Any]]], dtype: str, device="
                 pq_bits=prm["pq_bits"], kmeans_iter=prm["kmeans_iter"],
                 init_offset=prm["init_offset"], metric=prm["metric"]))
         elif kind == "adaptive_sampling":
-            from sparse_attention_hub.sparse_attention.research_attention.maskers import sampling
+            from sparse_attention_hub.sparse_attention.research_attention.maskers.sampling import (
+                implementations as sampling)
             out.append(sampling.AdaptiveSamplingMaskerConfig(
                 base_rate_sampling=prm["base_rate_sampling"], epsilon=prm["epsilon"],
                 delta=prm["delta"], init_offset=prm["init_offset"], local_offset=prm["local_offset"]))
