@@ -447,7 +447,9 @@ int sah_lsh_query(const void* q, int dtype, int64_t qs_b, int64_t qs_h, int64_t 
  * word of every row is written. */
 int sah_lsh_match(const void* planes, int64_t cap, const void* qcodes, int B, int Hq, int Sq, int G,
                   int L, int K, int64_t S, int64_t W, const uint32_t* prev_bits, uint32_t* out_bits,
-                  int sm_count, void* stream);
+                  int sm_count, int* errflag, void* stream);
+/* ^ errflag (optional): one device word that the kernel sets to 1 when a bounded wait on its
+ * copy pipeline runs out (the result is then incomplete); the caller zeroes and reads it. */
 
 /* data[ptr[row] + i] = collision probability 1 - (1 - (1 - theta/pi)^K)^L of the
  * i-th set bit of the row (:374-403), theta the angle between the transformed

@@ -7,6 +7,8 @@
 //                          fetched once per group and shared by its query heads
 //   sah_attn_merge_parts   associative merge of sequence-sharded partials
 #include <mutex>
+#include <stdlib.h>
+#include <string.h>
 
 #include "sah_common.cuh"
 
@@ -203,17 +205,35 @@ attn_plan_fused_kernel(const uint32_t* __restrict__ bits, const T* __restrict__ 
   if (threadIdx.x == 0 && blockIdx.y == gridDim.y - 1) ucount[g] = base + total;
 }
 
-template <typename T>
-__global__ void attn_plan_emit_kernel(const uint32_t* __restrict__ bits, const T* __restrict__ data,
-                                      const int32_t* __restrict__ wpre,
-                                      const int64_t* __restrict__ ptr, PlanGeom p,
-                                      const int32_t* __restrict__ chunkcnt,
-                                      int32_t* __restrict__ ucols, uint16_t* __restrict__ umemb,
-                                      float* __restrict__ uw, int32_t* __restrict__ ucount) {
-  const int lane = threadIdx.x & 31;
+// Long rows: one warp per (group, chunk of 32 bitmap words).  Lane j owns word j of the chunk
+// (its rows' words, CSR offsets and the count of columns in the words before it go to shared
+// memory); then the warp walks the 32 words and lane i takes column i of each, so that the
+// entries of a word are written side by side: every store of the list is coalesced.
+// LSH: union list for a MagicPig mask whose weights the attention kernel evaluates itself
+// (at most 4 mask rows per group).  `bits` are the LSH matches, `ubits` (may be NULL) the
+// unit-weight part of the mask; the active set is their union.  Per union entry: the column,
+// membership in the low byte and "weight is 1" flags in the high byte of umemb, and in `uw`
+// ([groups][S]) the key's constant of the cosine, 1 / (M * |transformed key|).
+#define PLAN_EMIT_WARPS 4
+
+template <typename T, int RMAX, bool LSH>
+__global__ void __launch_bounds__(PLAN_EMIT_WARPS * 32)
+attn_plan_emit_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restrict__ ubits,
+                      const T* __restrict__ data, const int32_t* __restrict__ wpre,
+                      const int64_t* __restrict__ ptr, const float* __restrict__ dens, int64_t dens_cap,
+                      const unsigned int* __restrict__ max_bits, PlanGeom p,
+                      const int32_t* __restrict__ chunkcnt, int32_t* __restrict__ ucols,
+                      uint16_t* __restrict__ umemb, float* __restrict__ uw,
+                      int32_t* __restrict__ ucount) {
+  __shared__ uint32_t words_sm[PLAN_EMIT_WARPS][RMAX][32];
+  __shared__ uint32_t units_sm[PLAN_EMIT_WARPS][LSH ? RMAX : 1][32];
+  __shared__ int64_t dbase_sm[PLAN_EMIT_WARPS][RMAX][32];
+  __shared__ uint32_t union_sm[PLAN_EMIT_WARPS][32];
+  __shared__ int before_sm[PLAN_EMIT_WARPS][32];
+  const int lane = threadIdx.x & 31, wl = threadIdx.x >> 5;
   const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int64_t g = wid / p.nchunks, c = wid - g * p.nchunks;
-  if (g >= p.groups) return;  // surplus warps of the last block
+  if (g >= p.groups) return;  // surplus warps of the last block (whole warps)
   // columns selected in earlier chunks of this group
   int base = 0;
   for (int64_t cc = lane; cc < c; cc += 32) base += chunkcnt[g * p.nchunks + cc];
@@ -221,23 +241,27 @@ __global__ void attn_plan_emit_kernel(const uint32_t* __restrict__ bits, const T
   for (int o = 16; o > 0; o >>= 1) base += __shfl_xor_sync(0xffffffffu, base, o);
 
   const int64_t w = c * PLAN_CHUNK_WORDS + lane;
-  uint32_t words[AT_MAXR];
-  int64_t rows[AT_MAXR];
-  int64_t dbase[AT_MAXR];  // CSR position of the first entry of this row's word
+  const bool weighted = !LSH && uw != nullptr;
   uint32_t u = 0u;
 #pragma unroll
-  for (int r = 0; r < AT_MAXR; ++r) {
-    words[r] = 0u;
-    rows[r] = -1;
-    dbase[r] = 0;
+  for (int r = 0; r < RMAX; ++r) {
+    uint32_t wd = 0u, un = 0u;
+    int64_t db = 0;
     if (r < p.R && w < p.Wv) {
-      rows[r] = plan_member_row(p, g, r);
-      if (rows[r] >= 0) {
-        words[r] = plan_word(p, bits[rows[r] * p.W + w], w);
-        if (uw != nullptr && words[r]) dbase[r] = ptr[rows[r]] + wpre[rows[r] * p.W + w];
+      const int64_t row = plan_member_row(p, g, r);
+      if (row >= 0) {
+        wd = plan_word(p, bits[row * p.W + w], w);
+        if (LSH && ubits != nullptr) {
+          un = plan_word(p, ubits[row * p.W + w], w);
+          wd |= un;
+        }
+        if (weighted && wd) db = ptr[row] + wpre[row * p.W + w];
       }
     }
-    u |= words[r];
+    words_sm[wl][r][lane] = wd;
+    if (LSH) units_sm[wl][r][lane] = un;
+    if (weighted) dbase_sm[wl][r][lane] = db;
+    u |= wd;
   }
   const int cnt = __popc(u);
   int incl = cnt;
@@ -246,30 +270,47 @@ __global__ void attn_plan_emit_kernel(const uint32_t* __restrict__ bits, const T
     int n = __shfl_up_sync(0xffffffffu, incl, o);
     if (lane >= o) incl += n;
   }
-  int64_t pos = (int64_t)g * p.S + base + incl - cnt;
-  uint32_t m = u;
-  while (m) {
-    const int b = __ffs(m) - 1;
-    m &= m - 1;
+  union_sm[wl][lane] = u;
+  before_sm[wl][lane] = incl - cnt;
+  __syncwarp();
+
+  const int64_t list0 = (int64_t)g * p.S + base;
+  const uint32_t lt = (1u << lane) - 1u;
+  float M = 0.f;
+  const float* gd = nullptr;
+  if constexpr (LSH) {
+    M = __uint_as_float(*max_bits);
+    gd = dens + (g / p.nqb) * dens_cap;  // (batch, KV head) of the group
+  }
+  for (int j = 0; j < 32; ++j) {
+    const uint32_t uj = union_sm[wl][j];
+    if (uj == 0u) continue;  // the same for every lane
+    if (!((uj >> lane) & 1u)) continue;
+    const int64_t pos = list0 + before_sm[wl][j] + __popc(uj & lt);
+    const int64_t col = (c * PLAN_CHUNK_WORDS + j) * 32 + lane;
     unsigned int memb = 0u;
 #pragma unroll
-    for (int r = 0; r < AT_MAXR; ++r) memb |= ((words[r] >> b) & 1u) << r;
-    ucols[pos] = (int32_t)(w * 32 + b);
+    for (int r = 0; r < RMAX; ++r) {
+      memb |= ((words_sm[wl][r][j] >> lane) & 1u) << r;
+      if (LSH) memb |= ((units_sm[wl][r][j] >> lane) & 1u) << (8 + r);
+    }
+    ucols[pos] = (int32_t)col;
     umemb[pos] = (uint16_t)memb;
-    if (uw != nullptr) {
+    if constexpr (LSH) {
+      uw[pos] = __frcp_rn(__fmul_rn(M, gd[col]));
+    } else if (weighted) {
 #pragma unroll
-      for (int r = 0; r < AT_MAXR; ++r) {
+      for (int r = 0; r < RMAX; ++r) {
         if (r < p.R) {
           float wv = 0.f;
           if ((memb >> r) & 1u) {
-            const int64_t dp = dbase[r] + __popc(words[r] & ((1u << b) - 1u));
+            const int64_t dp = dbase_sm[wl][r][j] + __popc(words_sm[wl][r][j] & lt);
             wv = sah_inv_weight<T>(sah_to_float<T>(data[dp]));
           }
           uw[pos * p.R + r] = wv;
         }
       }
     }
-    ++pos;
   }
   if (c == p.nchunks - 1) {
     int total = __shfl_sync(0xffffffffu, incl, 31);
@@ -334,80 +375,20 @@ extern "C" int sah_attn_plan(const uint32_t* bits, const void* data, const int32
   }
   attn_plan_count_kernel<<<(unsigned)blocks, threads, 0, st>>>(bits, nullptr, p, chunkcnt);
   SAH_LAUNCH_CHECK("attn_plan_count");
+  const int64_t eblocks = sah_ceil_div(warps, PLAN_EMIT_WARPS);
   SAH_DISPATCH_DTYPE(dtype, T, {
-    attn_plan_emit_kernel<T><<<(unsigned)blocks, threads, 0, st>>>(
-        bits, (const T*)data, wpre, ptr, p, chunkcnt, ucols, umemb, data ? uw : nullptr, ucount);
+    if (p.R <= 4)
+      attn_plan_emit_kernel<T, 4, false><<<(unsigned)eblocks, PLAN_EMIT_WARPS * 32, 0, st>>>(
+          bits, nullptr, (const T*)data, wpre, ptr, nullptr, 0, nullptr, p, chunkcnt, ucols, umemb,
+          data ? uw : nullptr, ucount);
+    else
+      attn_plan_emit_kernel<T, AT_MAXR, false><<<(unsigned)eblocks, PLAN_EMIT_WARPS * 32, 0, st>>>(
+          bits, nullptr, (const T*)data, wpre, ptr, nullptr, 0, nullptr, p, chunkcnt, ucols, umemb,
+          data ? uw : nullptr, ucount);
   });
   SAH_LAUNCH_CHECK("attn_plan_emit");
   sah_prof_end(SAH_PROF_ATTN_PLAN, (cudaStream_t)stream);
   return SAH_OK;
-}
-
-// Union list for a MagicPig mask whose weights the attention kernel evaluates itself
-// (at most 4 mask rows per group).  `bits` are the LSH matches, `ubits` (may be NULL) the
-// unit-weight part of the mask; the active set is their union.  Per union
-// entry: the column, membership in the low byte and "weight is 1" flags in the high byte
-// of umemb, and the key's constant of the cosine, 1 / (M * |transformed key|).
-__global__ void attn_plan_emit_lsh_kernel(const uint32_t* __restrict__ bits,
-                                          const uint32_t* __restrict__ ubits,
-                                          const float* __restrict__ dens, int64_t dens_cap,
-                                          const unsigned int* __restrict__ max_bits, PlanGeom p,
-                                          const int32_t* __restrict__ chunkcnt,
-                                          int32_t* __restrict__ ucols, uint16_t* __restrict__ umemb,
-                                          float* __restrict__ uinv, int32_t* __restrict__ ucount) {
-  const int lane = threadIdx.x & 31;
-  const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int64_t g = wid / p.nchunks, c = wid - g * p.nchunks;
-  if (g >= p.groups) return;  // surplus warps of the last block
-  int base = 0;
-  for (int64_t cc = lane; cc < c; cc += 32) base += chunkcnt[g * p.nchunks + cc];
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) base += __shfl_xor_sync(0xffffffffu, base, o);
-
-  const int64_t w = c * PLAN_CHUNK_WORDS + lane;
-  uint32_t words[4], units[4];
-  uint32_t u = 0u;
-#pragma unroll
-  for (int r = 0; r < 4; ++r) {
-    words[r] = 0u;
-    units[r] = 0u;
-    if (r < p.R && w < p.Wv) {
-      const int64_t row = plan_member_row(p, g, r);
-      if (row >= 0) {
-        units[r] = ubits ? plan_word(p, ubits[row * p.W + w], w) : 0u;
-        words[r] = plan_word(p, bits[row * p.W + w], w) | units[r];
-      }
-    }
-    u |= words[r];
-  }
-  const int cnt = __popc(u);
-  int incl = cnt;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    int n = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= o) incl += n;
-  }
-  int64_t pos = (int64_t)g * p.S + base + incl - cnt;
-  const float M = __uint_as_float(*max_bits);
-  const float* gd = dens + (g / p.nqb) * dens_cap;  // (batch, KV head) of the group
-  uint32_t m = u;
-  while (m) {
-    const int b = __ffs(m) - 1;
-    m &= m - 1;
-    unsigned int memb = 0u;
-#pragma unroll
-    for (int r = 0; r < 4; ++r)
-      memb |= (((words[r] >> b) & 1u) << r) | (((units[r] >> b) & 1u) << (8 + r));
-    const int64_t col = w * 32 + b;
-    ucols[pos] = (int32_t)col;
-    umemb[pos] = (uint16_t)memb;
-    uinv[pos] = __frcp_rn(__fmul_rn(M, gd[col]));
-    ++pos;
-  }
-  if (c == p.nchunks - 1) {
-    int total = __shfl_sync(0xffffffffu, incl, 31);
-    if (lane == 0) ucount[g] = base + total;
-  }
 }
 
 extern "C" int sah_attn_plan_lsh(const uint32_t* bits, const uint32_t* unit_bits, const float* dens,
@@ -433,8 +414,10 @@ extern "C" int sah_attn_plan_lsh(const uint32_t* bits, const uint32_t* unit_bits
   sah_prof_begin(SAH_PROF_ATTN_PLAN, st);
   attn_plan_count_kernel<<<(unsigned)blocks, threads, 0, st>>>(bits, unit_bits, p, chunkcnt);
   SAH_LAUNCH_CHECK("attn_plan_count");
-  attn_plan_emit_lsh_kernel<<<(unsigned)blocks, threads, 0, st>>>(
-      bits, unit_bits, dens, dens_cap, max_norm_bits, p, chunkcnt, ucols, umemb, uinv, ucount);
+  attn_plan_emit_kernel<float, 4, true><<<(unsigned)sah_ceil_div(warps, PLAN_EMIT_WARPS),
+                                          PLAN_EMIT_WARPS * 32, 0, st>>>(
+      bits, unit_bits, nullptr, nullptr, nullptr, dens, dens_cap, max_norm_bits, p, chunkcnt, ucols,
+      umemb, uinv, ucount);
   SAH_LAUNCH_CHECK("attn_plan_emit_lsh");
   sah_prof_end(SAH_PROF_ATTN_PLAN, st);
   return SAH_OK;
@@ -471,6 +454,9 @@ struct AttnArgs {
   const float* qmu;           // [rows] qhat . key mean
   const uint16_t* ptable;     // [65536] bf16 bits of the cosine -> bits of the probability
   float* w_dump;              // optional [groups][S][R]: the weights used (tests)
+  // TMA copy stage: K and V as 2-D [rows][D] tensors, row = b * rows_b + h * rows_h + key
+  int64_t k_rows_b, k_rows_h, v_rows_b, v_rows_h;
+  int k_rows_total, v_rows_total;
 };
 
 // Shared-memory rows are stored in 16-byte chunks; chunk c of tile row i sits
@@ -901,6 +887,8 @@ static int masked_attention_impl(const void* q, const void* k, const void* v, in
   a.qmu = lsh ? lsh->qmu : nullptr;
   a.ptable = lsh ? lsh->ptable : nullptr;
   a.w_dump = lsh ? lsh->w_dump : nullptr;
+  a.k_rows_b = a.k_rows_h = a.v_rows_b = a.v_rows_h = 0;
+  a.k_rows_total = a.v_rows_total = 0;
   const int groups = sizes->groups;
   SAH_REQUIRE((int64_t)groups == (int64_t)B * Hkv * a.nqb && a.R == a.G * a.q_block &&
                   a.R <= AT_MAXR && a.nsplit >= 1,
@@ -911,9 +899,10 @@ static int masked_attention_impl(const void* q, const void* k, const void* v, in
   if (dtype == SAH_BF16) {
     // tensor-core path; the split merge is fused into the kernel (ticket per group)
     int* tickets = const_cast<int*>(ucount) + groups + (int64_t)groups * plan_chunks(S);
+    int* errflag = tickets + groups;  // set when a bounded wait inside the kernel ran out
     rc = (D == 128)
-             ? launch_attention_mma<128>(a, groups, tickets, sinks, out, acc_out, lse_out, lsh != nullptr, st)
-             : launch_attention_mma<64>(a, groups, tickets, sinks, out, acc_out, lse_out, lsh != nullptr, st);
+             ? launch_attention_mma<128>(a, B, groups, tickets, errflag, sinks, out, acc_out, lse_out, lsh != nullptr, st)
+             : launch_attention_mma<64>(a, B, groups, tickets, errflag, sinks, out, acc_out, lse_out, lsh != nullptr, st);
     if (rc != SAH_OK) return rc;
     SAH_LAUNCH_CHECK("masked_attention_mma");
     sah_prof_end(SAH_PROF_ATTENTION, (cudaStream_t)stream);

@@ -25,6 +25,17 @@
 // weight array is read or written.
 #pragma once
 
+//
+// TMA (optional copy stage, HALF tiles): instead of 16-byte copies issued by every lane, four
+// lanes of the warp issue tensor-map gathers (cp.async.bulk.tensor.2d ... tile::gather4: four
+// indexed rows of a 2-D view of K or V per instruction, 64 columns wide) that land in the ring
+// in the 128-byte swizzled layout; completion is counted on one mbarrier per stage.  No
+// multicast qualifier: every CTA fetches its own rows, and the tensor maps cover this GPU's
+// own K/V allocation only.  Every wait on an mbarrier is bounded; a wait that runs out sets
+// the error word, the warp stops consuming tiles, and the kernel still goes through its
+// merge and ticket protocol so that no other CTA is left waiting.
+#include <cuda.h>
+
 #ifndef ATM_WARPS
 #define ATM_WARPS 4
 #endif
@@ -33,6 +44,48 @@
 #endif
 #define ATM_THREADS (ATM_WARPS * 32)
 #define ATM_TILE 16
+#define ATM_SPIN_LIMIT (1 << 22)
+
+struct AtmMaps {
+  CUtensorMap k, v;
+};
+
+// ---- mbarrier / tensor-map gather ------------------------------------------------
+__device__ __forceinline__ void atm_mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void atm_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool atm_mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0u;
+}
+// Bounded wait: false when the phase did not complete within the spin limit.
+__device__ __forceinline__ bool atm_mbar_wait(uint32_t bar, uint32_t parity) {
+  for (int i = 0; i < ATM_SPIN_LIMIT; ++i) {  // about half a second at most
+    if (atm_mbar_test(bar, parity)) return true;
+    if (i > 64) __nanosleep(64);
+  }
+  return false;
+}
+// Four rows y0..y3 of the 2-D tensor, columns [x, x + box width), to shared memory.
+__device__ __forceinline__ void atm_tma_gather4(uint32_t dst, const CUtensorMap* map, int x, int y0,
+                                                int y1, int y2, int y3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];\n" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3), "r"(bar)
+      : "memory");
+}
 
 __device__ __forceinline__ void atm_ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2,
                                                 uint32_t& r3, uint32_t saddr) {
@@ -81,20 +134,24 @@ __device__ __forceinline__ void atm_cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
 }
 
-template <int D>
+template <int D, bool TMA = false, int NST = ATM_STAGES>
 struct AtmCfg {
   static constexpr int ROWB = D * 2;                        // bytes of one bf16 row
-  static constexpr int RSTR = ROWB + 16;                    // padded row stride in shared memory
+  // cp.async ring: whole rows padded by 16 bytes.  TMA ring: per K (or V) tile D/64 blocks of
+  // [16 rows][128 bytes], each 2 KB and 1 KB aligned, 16-byte chunks swizzled by the row.
+  static constexpr int RSTR = ROWB + 16;                    // padded row stride (cp.async ring, Q tile)
+  static constexpr int HALVES = D / 64;
   static constexpr int KSTEPS = D / 16;                     // k-steps of Q.K^T
   static constexpr int NT = D / 8;                          // n-tiles of the output
-  static constexpr int TILE_BYTES = ATM_TILE * RSTR;        // one K (or V) tile
+  static constexpr int TILE_BYTES = TMA ? HALVES * ATM_TILE * 128 : ATM_TILE * RSTR;  // one K (or V) tile
   static constexpr int STAGE_BYTES = 2 * TILE_BYTES;        // K tile + V tile
-  static constexpr int WARP_BYTES = ATM_STAGES * STAGE_BYTES;
-  static constexpr int Q_BYTES = 16 * RSTR;
+  static constexpr int WARP_BYTES = NST * STAGE_BYTES;
+  static constexpr int Q_BYTES = 16 * RSTR;                 // staged in the first ring before the pipeline starts
   static constexpr int RS = D + 8;                          // fp32 row stride of the reduction scratch
   static constexpr int RED_BYTES = 16 * RS * 4 + 16 * 2 * 4;
-  static constexpr int META_BYTES = ATM_WARPS * ATM_STAGES * 16 * 16;  // (col, memb, 1/(M den), -)
-  static constexpr int SMEM = ATM_WARPS * WARP_BYTES + Q_BYTES + META_BYTES;
+  static constexpr int META_BYTES = ATM_WARPS * NST * 16 * 16;  // (col, memb, 1/(M den), -)
+  static constexpr int BAR_BYTES = ATM_WARPS * NST * 8;
+  static constexpr int SMEM = (TMA ? 1024 : 0) + ATM_WARPS * WARP_BYTES + META_BYTES + BAR_BYTES;
 };
 
 // MagicPig weight of one (row, key) pair from the centred cosine (see the header comment);
@@ -109,21 +166,41 @@ __device__ __forceinline__ float atm_lsh_weight(float dot_hat, float qmu, float 
   return p == 0.f ? 0.f : sah_inv_weight<__nv_bfloat16>(p);
 }
 
-template <int D, bool HALF, bool LSHW>
-__global__ void __launch_bounds__(ATM_THREADS, 2)
-masked_attention_mma_kernel(AttnArgs a, int* __restrict__ tickets, const float* __restrict__ sinks,
+// NST: stages of the per-warp ring.  Three stages fit two CTAs (8 warps) per SM; two stages,
+// with the register count capped accordingly, fit three CTAs (12 warps): fewer tiles in flight
+// per warp, more warps to overlap one warp's arithmetic with the others' copies.
+template <int D, bool HALF, bool LSHW, bool TMA, int NST>
+__global__ void __launch_bounds__(ATM_THREADS, NST == 2 ? 3 : 2)
+masked_attention_mma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, int* __restrict__ tickets,
+                            int* __restrict__ errflag, const float* __restrict__ sinks,
                             __nv_bfloat16* __restrict__ out, float* __restrict__ acc_out,
                             float* __restrict__ lse_out) {
   static_assert(!LSHW || HALF, "in-place MagicPig weights use the spare rows of the half tile");
-  using C = AtmCfg<D>;
+  using C = AtmCfg<D, TMA, NST>;
+  static_assert(C::Q_BYTES <= C::WARP_BYTES, "the Q tile is staged in the first ring");
   constexpr int NR = HALF ? 1 : 2;  // row halves a thread owns in the C fragment
-  extern __shared__ __align__(128) unsigned char atm_smem[];
+  extern __shared__ __align__(128) unsigned char atm_smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // the swizzled blocks of the TMA ring must start on 1 KB boundaries of the shared window
+  unsigned char* atm_smem = atm_smem_raw;
+  if constexpr (TMA) {
+    const uint32_t raw_s = (uint32_t)__cvta_generic_to_shared(atm_smem_raw);
+    atm_smem = atm_smem_raw + (((raw_s + 1023u) & ~1023u) - raw_s);
+  }
   unsigned char* ring = atm_smem + warp * C::WARP_BYTES;
-  unsigned char* q_sm = atm_smem + ATM_WARPS * C::WARP_BYTES;
-  int4* meta_sm = reinterpret_cast<int4*>(q_sm + C::Q_BYTES) + warp * ATM_STAGES * 16;
+  unsigned char* q_sm = atm_smem;  // the first ring, before any copy is issued
+  unsigned char* meta_base = atm_smem + ATM_WARPS * C::WARP_BYTES;
+  int4* meta_sm = reinterpret_cast<int4*>(meta_base) + warp * NST * 16;
   const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
+  const uint32_t bar_s = (uint32_t)__cvta_generic_to_shared(meta_base + C::META_BYTES) + warp * NST * 8;
   __shared__ int is_last_sm;
+  if constexpr (TMA) {
+    if (lane == 0) {
+#pragma unroll
+      for (int s = 0; s < NST; ++s) atm_mbar_init(bar_s + s * 8, 1);
+      asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+  }
 
   const int split = blockIdx.x;
   const int64_t g = blockIdx.y;
@@ -206,6 +283,8 @@ masked_attention_mma_kernel(AttnArgs a, int* __restrict__ tickets, const float* 
     }
   }
 
+  __syncthreads();  // every warp holds its Q fragments: the first ring is free for the pipeline
+
   // rows this thread owns in the C fragment, and their bias rows
   const int r0 = lane >> 2, r1 = r0 + 8;
   const __nv_bfloat16* bias_row[2] = {nullptr, nullptr};
@@ -248,42 +327,80 @@ masked_attention_mma_kernel(AttnArgs a, int* __restrict__ tickets, const float* 
   const unsigned char* v_bytes = reinterpret_cast<const unsigned char*>(vbase) + my_chunk * 16;
   const int64_t ks_bytes = a.ks_s * 2, vs_bytes = a.vs_s * 2;
 
+  // row of (batch b, KV head kvh, key 0) in the 2-D views of K and V that the tensor maps describe
+  const int krow0 = TMA ? (int)(b * a.k_rows_b + kvh * a.k_rows_h) : 0;
+  const int vrow0 = TMA ? (int)(b * a.v_rows_b + kvh * a.v_rows_h) : 0;
+
   auto issue = [&](int t) {
-    const int st = t % ATM_STAGES;
+    const int st = t % NST;
     const Meta cur = pre0;
     pre0 = pre1;
     pre1 = load_meta(t + 2);
     if (lane < ATM_TILE)
       meta_sm[st * 16 + lane] = make_int4(cur.col, (int)cur.memb, __float_as_int(cur.inv), 0);
-    const uint32_t dst0 = ring_s + st * C::STAGE_BYTES + my_dst;
+    if constexpr (TMA) {
+      const uint32_t bar = bar_s + st * 8;
+      if (lane == 0) atm_mbar_expect_tx(bar, (uint32_t)C::STAGE_BYTES);
+      // lanes 0..3 fetch rows 4 * lane .. 4 * lane + 3; a row past the list reads as zeros
+      // (its coordinate lies outside the tensor), and still counts its bytes
+      int y[4];
 #pragma unroll
-    for (int it = 0; it < ATM_TILE / RPS; ++it) {
-      const int rc = __shfl_sync(0xffffffffu, cur.col, it * RPS + my_sub);
-      const uint32_t dst = dst0 + it * RPS * C::RSTR;
-      if (rc >= 0) {
-        atm_cp_async16(dst, k_bytes + rc * ks_bytes);
-        atm_cp_async16(dst + C::TILE_BYTES, v_bytes + rc * vs_bytes);
-      } else {
-        // unused rows must not feed NaNs into the tensor cores
-        unsigned char* p = ring + st * C::STAGE_BYTES + my_dst + it * RPS * C::RSTR;
-        *reinterpret_cast<uint4*>(p) = make_uint4(0u, 0u, 0u, 0u);
-        *reinterpret_cast<uint4*>(p + C::TILE_BYTES) = make_uint4(0u, 0u, 0u, 0u);
+      for (int i = 0; i < 4; ++i) y[i] = __shfl_sync(0xffffffffu, cur.col, (4 * lane + i) & 15);
+      __syncwarp();
+      if (lane < 4) {
+        const uint32_t dst = ring_s + st * C::STAGE_BYTES + lane * 4 * 128;
+        int yk[4], yv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          yk[i] = y[i] >= 0 ? krow0 + y[i] : a.k_rows_total;
+          yv[i] = y[i] >= 0 ? vrow0 + y[i] : a.v_rows_total;
+        }
+#pragma unroll
+        for (int h = 0; h < C::HALVES; ++h) {
+          atm_tma_gather4(dst + h * 2048, &maps.k, h * 64, yk[0], yk[1], yk[2], yk[3], bar);
+          atm_tma_gather4(dst + C::TILE_BYTES + h * 2048, &maps.v, h * 64, yv[0], yv[1], yv[2], yv[3], bar);
+        }
+      }
+    } else {
+      const uint32_t dst0 = ring_s + st * C::STAGE_BYTES + my_dst;
+#pragma unroll
+      for (int it = 0; it < ATM_TILE / RPS; ++it) {
+        const int rc = __shfl_sync(0xffffffffu, cur.col, it * RPS + my_sub);
+        const uint32_t dst = dst0 + it * RPS * C::RSTR;
+        if (rc >= 0) {
+          atm_cp_async16(dst, k_bytes + rc * ks_bytes);
+          atm_cp_async16(dst + C::TILE_BYTES, v_bytes + rc * vs_bytes);
+        } else {
+          // unused rows must not feed NaNs into the tensor cores
+          unsigned char* p = ring + st * C::STAGE_BYTES + my_dst + it * RPS * C::RSTR;
+          *reinterpret_cast<uint4*>(p) = make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4*>(p + C::TILE_BYTES) = make_uint4(0u, 0u, 0u, 0u);
+        }
       }
     }
   };
 
 #pragma unroll
-  for (int s = 0; s < ATM_STAGES - 1; ++s) {
+  for (int s = 0; s < NST - 1; ++s) {
     if (s < my_tiles) issue(s);
-    asm volatile("cp.async.commit_group;\n" ::);
+    if constexpr (!TMA) asm volatile("cp.async.commit_group;\n" ::);
   }
 
-  for (int t = 0; t < my_tiles; ++t) {
-    if (t + ATM_STAGES - 1 < my_tiles) issue(t + ATM_STAGES - 1);
-    const int st = t % ATM_STAGES;
-    asm volatile("cp.async.commit_group;\n" ::);
-    asm volatile("cp.async.wait_group %0;\n" ::"n"(ATM_STAGES - 1));
-    __syncwarp();
+  bool alive = true;
+  int t = 0;
+  for (; t < my_tiles; ++t) {
+    if (t + NST - 1 < my_tiles) issue(t + NST - 1);
+    const int st = t % NST;
+    if constexpr (TMA) {
+      if (!atm_mbar_wait(bar_s + st * 8, (uint32_t)((t / NST) & 1))) {
+        alive = false;
+        break;
+      }
+    } else {
+      asm volatile("cp.async.commit_group;\n" ::);
+      asm volatile("cp.async.wait_group %0;\n" ::"n"(NST - 1));
+      __syncwarp();
+    }
     const uint32_t kst = ring_s + st * C::STAGE_BYTES;
     const uint32_t vst = kst + C::TILE_BYTES;
     const int u0 = (my_first + t * lanes_total) * ATM_TILE;
@@ -296,11 +413,15 @@ masked_attention_mma_kernel(AttnArgs a, int* __restrict__ tickets, const float* 
       for (int e = 0; e < 2 * NR; ++e) s[nt][e] = 0.f;
     {
       const int mi = lane >> 3, rr = lane & 7;
-      const uint32_t kaddr = kst + ((mi >> 1) * 8 + rr) * C::RSTR + (mi & 1) * 16;
+      const uint32_t kaddr = TMA ? kst + ((mi >> 1) * 8 + rr) * 128
+                                 : kst + ((mi >> 1) * 8 + rr) * C::RSTR + (mi & 1) * 16;
 #pragma unroll
       for (int ks = 0; ks < C::KSTEPS; ++ks) {
         uint32_t b0, b1, b2, b3;
-        atm_ldmatrix_x4(b0, b1, b2, b3, kaddr + ks * 32);
+        // TMA ring: 16-byte chunk c of a row sits in block c / 8 at chunk slot (c % 8) ^ (row % 8)
+        const int kc = 2 * ks + (mi & 1);
+        atm_ldmatrix_x4(b0, b1, b2, b3,
+                        TMA ? kaddr + (kc >> 3) * 2048 + (((kc & 7) ^ rr) << 4) : kaddr + ks * 32);
         if constexpr (HALF) {
           atm_mma_half(s[0][0], s[0][1], qf[ks][0], qf[ks][1], b0, b1);
           atm_mma_half(s[1][0], s[1][1], qf[ks][0], qf[ks][1], b2, b3);
@@ -399,11 +520,14 @@ masked_attention_mma_kernel(AttnArgs a, int* __restrict__ tickets, const float* 
     pa[3] = HALF ? 0u : atm_pack_bf16(s[1][2 * NR - 2], s[1][2 * NR - 1]);
     {
       const int mi = lane >> 3, rr = lane & 7;
-      const uint32_t vaddr = vst + ((mi & 1) * 8 + rr) * C::RSTR + (mi >> 1) * 16;
+      const uint32_t vaddr = TMA ? vst + ((mi & 1) * 8 + rr) * 128
+                                 : vst + ((mi & 1) * 8 + rr) * C::RSTR + (mi >> 1) * 16;
 #pragma unroll
       for (int np = 0; np < C::NT / 2; ++np) {
         uint32_t b0, b1, b2, b3;
-        atm_ldmatrix_x4_trans(b0, b1, b2, b3, vaddr + np * 32);
+        const int vc = 2 * np + (mi >> 1);
+        atm_ldmatrix_x4_trans(b0, b1, b2, b3,
+                              TMA ? vaddr + (vc >> 3) * 2048 + (((vc & 7) ^ rr) << 4) : vaddr + np * 32);
         if constexpr (HALF) {
           atm_mma_half(o[2 * np][0], o[2 * np][1], pa[0], pa[2], b0, b1);
           atm_mma_half(o[2 * np + 1][0], o[2 * np + 1][1], pa[0], pa[2], b2, b3);
@@ -415,7 +539,16 @@ masked_attention_mma_kernel(AttnArgs a, int* __restrict__ tickets, const float* 
     }
     __syncwarp();  // all lanes done with this stage before it is refilled
   }
-  asm volatile("cp.async.wait_group 0;\n" ::);
+  if constexpr (TMA) {
+    if (!alive) {
+      if (lane == 0) atomicExch(errflag, 1);
+      // give the copies still in flight a bounded chance to land before the ring is reused
+      for (int tt = t; tt < my_tiles && tt < t + NST; ++tt)
+        atm_mbar_wait(bar_s + (tt % NST) * 8, (uint32_t)((tt / NST) & 1));
+    }
+  } else {
+    asm volatile("cp.async.wait_group 0;\n" ::);
+  }
   __syncthreads();
 
   // ---- merge the warps of this CTA (ring reused as fp32 scratch) ----
@@ -625,36 +758,116 @@ static cudaError_t atm_allow_smem(Kernel kernel, int smem, bool* done_by_device)
   return e;
 }
 
-template <int D>
-static int launch_attention_mma(const AttnArgs& a, int groups, int* tickets, const float* sinks,
-                                void* out, float* acc_out, float* lse_out, bool lsh,
-                                cudaStream_t st) {
-  using C = AtmCfg<D>;
-  static_assert(C::RED_BYTES <= C::WARP_BYTES, "reduction scratch must fit the ring");
-  static bool allowed[3][64] = {};
-  const int smem = C::SMEM;
-  if ((size_t)16 * a.nsplit * 4 + 128 > (size_t)ATM_WARPS * C::WARP_BYTES)
-    return sah_fail(SAH_ERR_UNSUPPORTED, "attention: %d splits do not fit the merge scratch", a.nsplit);
-  dim3 grid((unsigned)a.nsplit, (unsigned)groups);
-  cudaError_t e;
-  if (lsh) {
-    if (a.R > 4)
-      return sah_fail(SAH_ERR_UNSUPPORTED, "attention: in-place MagicPig weights need <= 4 mask rows "
-                      "per KV group, got %d", a.R);
-    e = atm_allow_smem(masked_attention_mma_kernel<D, true, true>, smem, allowed[2]);
-    if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "attention attr: %s", cudaGetErrorString(e));
-    masked_attention_mma_kernel<D, true, true><<<grid, ATM_THREADS, smem, st>>>(
-        a, tickets, sinks, (__nv_bfloat16*)out, acc_out, lse_out);
-  } else if (a.R <= 8) {
-    e = atm_allow_smem(masked_attention_mma_kernel<D, true, false>, smem, allowed[0]);
-    if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "attention attr: %s", cudaGetErrorString(e));
-    masked_attention_mma_kernel<D, true, false><<<grid, ATM_THREADS, smem, st>>>(
-        a, tickets, sinks, (__nv_bfloat16*)out, acc_out, lse_out);
-  } else {
-    e = atm_allow_smem(masked_attention_mma_kernel<D, false, false>, smem, allowed[1]);
-    if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "attention attr: %s", cudaGetErrorString(e));
-    masked_attention_mma_kernel<D, false, false><<<grid, ATM_THREADS, smem, st>>>(
-        a, tickets, sinks, (__nv_bfloat16*)out, acc_out, lse_out);
+// ---- tensor maps of K and V for the TMA copy stage --------------------------------------
+typedef CUresult (*AtmEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+// The driver's encoder, looked up through the runtime (the library does not link libcuda).
+static AtmEncodeTiled atm_encoder() {
+  static AtmEncodeTiled fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
+        qr == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<AtmEncodeTiled>(p);
   }
+  return fn;
+}
+
+// 2-D view [rows][D] of a [B][Hkv][S][D] tensor whose batch and head strides are whole rows:
+// row = b * rows_b + h * rows_h + s.  Box: 64 columns x 1 row (gather4 takes four such rows),
+// 128-byte swizzle, zero fill outside the tensor.  False when the layout is not such a view.
+static bool atm_make_map(CUtensorMap* map, const void* base, int64_t s_b, int64_t s_h, int64_t s_s, int B,
+                         int Hkv, int64_t S, int D, int64_t* rows_b, int64_t* rows_h, int* rows_total) {
+  AtmEncodeTiled enc = atm_encoder();
+  if (enc == nullptr || s_s <= 0 || s_b % s_s != 0 || s_h % s_s != 0 || s_b < 0 || s_h < 0) return false;
+  *rows_b = s_b / s_s;
+  *rows_h = s_h / s_s;
+  const int64_t total = (int64_t)(B - 1) * *rows_b + (int64_t)(Hkv - 1) * *rows_h + S;
+  if (total <= 0 || total >= (1ll << 31) - 8) return false;
+  *rows_total = (int)total;
+  const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)total};
+  const cuuint64_t strides[1] = {(cuuint64_t)s_s * 2};
+  const cuuint32_t box[2] = {64, 1};
+  const cuuint32_t estr[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// SAH_ATTN_TMA=1 in the environment selects the tensor-map gather for the copy stage of the
+// bfloat16 kernel (half tiles); the default is the 16-byte cp.async ring.
+static bool atm_tma_requested() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("SAH_ATTN_TMA");
+    v = (e != nullptr && e[0] == '1') ? 1 : 0;
+  }
+  return v == 1;
+}
+
+// SAH_ATTN_STAGES=2 in the environment selects the two-stage ring (three CTAs per SM) for the
+// half-tile kernels; the default is three stages (two CTAs per SM).
+static int atm_stages_requested() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("SAH_ATTN_STAGES");
+    v = (e != nullptr && e[0] == '2') ? 2 : 3;
+  }
+  return v;
+}
+
+template <int D>
+static int launch_attention_mma(AttnArgs a, int B, int groups, int* tickets, int* errflag,
+                                const float* sinks, void* out, float* acc_out, float* lse_out, bool lsh,
+                                cudaStream_t st) {
+  static bool allowed[9][64] = {};
+  if ((size_t)16 * a.nsplit * 4 + 128 > (size_t)ATM_WARPS * AtmCfg<D, true, 2>::WARP_BYTES)
+    return sah_fail(SAH_ERR_UNSUPPORTED, "attention: %d splits do not fit the merge scratch", a.nsplit);
+  static_assert(AtmCfg<D, false, 2>::RED_BYTES <= AtmCfg<D, false, 2>::WARP_BYTES &&
+                AtmCfg<D, true, 2>::RED_BYTES <= AtmCfg<D, true, 2>::WARP_BYTES,
+                "reduction scratch must fit the ring");
+  if (lsh && a.R > 4)
+    return sah_fail(SAH_ERR_UNSUPPORTED, "attention: in-place MagicPig weights need <= 4 mask rows "
+                    "per KV group, got %d", a.R);
+  dim3 grid((unsigned)a.nsplit, (unsigned)groups);
+  AtmMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  bool tma = false;
+  if (atm_tma_requested() && a.R <= 8) {
+    tma = atm_make_map(&maps.k, a.k, a.ks_b, a.ks_h, a.ks_s, B, a.Hkv, a.S, D, &a.k_rows_b, &a.k_rows_h,
+                       &a.k_rows_total) &&
+          atm_make_map(&maps.v, a.v, a.vs_b, a.vs_h, a.vs_s, B, a.Hkv, a.S, D, &a.v_rows_b, &a.v_rows_h,
+                       &a.v_rows_total);
+  }
+  const bool two = atm_stages_requested() == 2;
+  cudaError_t e = cudaSuccess;
+#define ATM_LAUNCH(HALF, LSHW, TMA, NST, SLOT)                                                      \
+  do {                                                                                              \
+    const int smem = AtmCfg<D, TMA, NST>::SMEM;                                                     \
+    e = atm_allow_smem(masked_attention_mma_kernel<D, HALF, LSHW, TMA, NST>, smem, allowed[SLOT]);  \
+    if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "attention attr: %s", cudaGetErrorString(e)); \
+    masked_attention_mma_kernel<D, HALF, LSHW, TMA, NST><<<grid, ATM_THREADS, smem, st>>>(          \
+        a, maps, tickets, errflag, sinks, (__nv_bfloat16*)out, acc_out, lse_out);                   \
+  } while (0)
+  if (lsh) {
+    if (tma && two) ATM_LAUNCH(true, true, true, 2, 5);
+    else if (tma) ATM_LAUNCH(true, true, true, 3, 3);
+    else if (two) ATM_LAUNCH(true, true, false, 2, 6);
+    else ATM_LAUNCH(true, true, false, 3, 2);
+  } else if (a.R <= 8) {
+    if (tma && two) ATM_LAUNCH(true, false, true, 2, 7);
+    else if (tma) ATM_LAUNCH(true, false, true, 3, 4);
+    else if (two) ATM_LAUNCH(true, false, false, 2, 8);
+    else ATM_LAUNCH(true, false, false, 3, 0);
+  } else {
+    ATM_LAUNCH(false, false, false, 3, 1);
+  }
+#undef ATM_LAUNCH
   return SAH_OK;
 }

@@ -485,10 +485,150 @@ lsh_match_kernel(const CodeT* __restrict__ planes, int64_t cap, const CodeT* __r
   }
 }
 
+// ---- the same with the code planes staged through shared memory by bulk copies ----------
+// One CTA of 128 threads owns 4096 consecutive keys of one (batch, KV head).  An elected thread
+// requests the 4 KB slice of every table plane with one bulk asynchronous copy
+// (cp.async.bulk, global -> shared, completion counted on an mbarrier per group of five
+// planes); three groups circulate in a ring, so two groups (40 KB per CTA, three CTAs per SM)
+// are in flight while the threads compare the third.  Memory parallelism no longer depends on
+// registers, and each plane slice is one contiguous 4 KB read.  Byte codes (lsh_k <= 8) and at
+// most 4 mask rows per group; other shapes take lsh_match_kernel.
+// Every wait on an mbarrier is bounded; a wait that runs out sets *errflag and the CTA
+// finishes without reading further.
+#define LSHM_THREADS 128
+#define LSHM_KEYS (LSHM_THREADS * 32)
+#define LSHM_GROUP 5
+#define LSHM_NGROUPS 3
+#define LSHM_RING (LSHM_NGROUPS * LSHM_GROUP * LSHM_KEYS)
+#define LSHM_SPIN_LIMIT (1 << 22)
+
+__device__ __forceinline__ bool lshm_mbar_wait(uint32_t bar, uint32_t parity) {
+  for (int i = 0; i < LSHM_SPIN_LIMIT; ++i) {  // about half a second at most
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if (i > 64) __nanosleep(64);
+  }
+  return false;
+}
+
+__global__ void __launch_bounds__(LSHM_THREADS)
+lsh_match_staged_kernel(const uint8_t* __restrict__ planes, int64_t cap, const uint8_t* __restrict__ qcodes,
+                        int Hq, int Sq, int G, int L, int64_t S, int64_t W,
+                        const uint32_t* __restrict__ prev_bits, uint32_t* __restrict__ out_bits,
+                        int* __restrict__ errflag) {
+  extern __shared__ __align__(128) unsigned char lsh_smem[];
+  unsigned char* ring = lsh_smem;                               // [NGROUPS][GROUP][4096]
+  uint8_t* qs = lsh_smem + LSHM_RING;                           // [R][L]
+  const int R = G * Sq;                                         // <= 4
+  const uint32_t bar_s = (uint32_t)__cvta_generic_to_shared(lsh_smem + LSHM_RING + 512);
+  const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
+  const int tid = threadIdx.x;
+  const int64_t bh = blockIdx.y;
+  const int Hkv = Hq / G;
+  const int64_t b = bh / Hkv, hkv = bh % Hkv;
+  const int64_t k0 = (int64_t)blockIdx.x * LSHM_KEYS;
+  const uint32_t plane_bytes = (uint32_t)((cap - k0 < LSHM_KEYS) ? (cap - k0) : LSHM_KEYS);  // multiple of 32
+  if (tid == 0) {
+#pragma unroll
+    for (int i = 0; i < LSHM_NGROUPS; ++i)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar_s + i * 8), "r"(1));
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  for (int i = tid; i < R * L; i += LSHM_THREADS) {
+    const int r = i / L, l = i % L;
+    const int g = r / Sq, qi = r % Sq;
+    qs[i] = qcodes[(((b * Hq) + hkv * G + g) * Sq + qi) * L + l];
+  }
+  __syncthreads();
+
+  const int ngroups = (L + LSHM_GROUP - 1) / LSHM_GROUP;
+  const uint8_t* pbase = planes + bh * (int64_t)L * cap + k0;
+  auto issue_group = [&](int gi) {  // elected thread only
+    const int slot = gi % LSHM_NGROUPS;
+    const int l0 = gi * LSHM_GROUP;
+    const int n = (L - l0 < LSHM_GROUP) ? (L - l0) : LSHM_GROUP;
+    const uint32_t bar = bar_s + slot * 8;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar),
+                 "r"((uint32_t)n * plane_bytes)
+                 : "memory");
+    for (int u = 0; u < n; ++u)
+      asm volatile(
+          "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::
+              "r"(ring_s + (uint32_t)(slot * LSHM_GROUP + u) * LSHM_KEYS),
+          "l"(pbase + (int64_t)(l0 + u) * cap), "r"(plane_bytes), "r"(bar)
+          : "memory");
+  };
+  int issued = 0;
+  if (tid == 0)
+    for (; issued < LSHM_NGROUPS && issued < ngroups; ++issued) issue_group(issued);
+
+  const bool active = k0 + (int64_t)tid * 32 < S;  // this thread's 32 keys hold columns < S
+  unsigned int acc[4][8];
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[r][i] = 0u;
+  bool dead = false;
+  for (int gi = 0; gi < ngroups; ++gi) {
+    const int slot = gi % LSHM_NGROUPS;
+    if (!dead && !lshm_mbar_wait(bar_s + slot * 8, (uint32_t)((gi / LSHM_NGROUPS) & 1))) {
+      dead = true;
+      if (errflag != nullptr) atomicExch(errflag, 1);
+    }
+    const int l0 = gi * LSHM_GROUP;
+    const int n = (L - l0 < LSHM_GROUP) ? (L - l0) : LSHM_GROUP;
+    if (active && !dead) {
+      for (int u = 0; u < n; ++u) {
+        const uint4* src = reinterpret_cast<const uint4*>(ring + (slot * LSHM_GROUP + u) * LSHM_KEYS + tid * 32);
+        const uint4 v0 = src[0], v1 = src[1];
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+          if (r < R) {
+            const unsigned int qc = (unsigned int)qs[r * L + l0 + u];
+            lsh_match_accumulate<uint8_t>(v0, qc, &acc[r][0]);
+            lsh_match_accumulate<uint8_t>(v1, qc, &acc[r][4]);
+          }
+      }
+    }
+    __syncthreads();  // every thread has read this slot
+    if (tid == 0 && !dead && issued < ngroups) issue_group(issued++);
+  }
+  if (tid == 0 && dead) {
+    // copies that were requested and never awaited get a bounded chance to land before the
+    // shared memory is handed back
+    for (int gi = 0; gi < issued; ++gi)
+      lshm_mbar_wait(bar_s + (gi % LSHM_NGROUPS) * 8, (uint32_t)((gi / LSHM_NGROUPS) & 1));
+  }
+  if (!active) return;
+  const int64_t word = k0 / 32 + tid;
+  const int64_t left = S - word * 32;
+  const unsigned int valid = left >= 32 ? 0xffffffffu : ((1u << left) - 1u);
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    if (r < R) {
+      unsigned int bits = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) bits |= lsh_flags4(acc[r][i]) << (4 * i);
+      const int g = r / Sq, qi = r % Sq;
+      const int64_t row = ((b * Hq) + hkv * G + g) * Sq + qi;
+      bits &= valid;
+      if (prev_bits != nullptr) bits |= prev_bits[row * W + word];
+      out_bits[row * W + word] = bits;
+    }
+  }
+}
+
 extern "C" int sah_lsh_match(const void* planes, int64_t cap, const void* qcodes, int B, int Hq,
                              int Sq, int G, int L, int K, int64_t S, int64_t W,
                              const uint32_t* prev_bits, uint32_t* out_bits, int sm_count,
-                             void* stream) {
+                             int* errflag, void* stream) {
   SAH_REQUIRE(planes && qcodes && out_bits, "lsh_match: null pointer");
   SAH_REQUIRE(G > 0 && Hq % G == 0 && L > 0 && K > 0 && S > 0 && W * 32 >= S, "lsh_match: bad shape");
   SAH_REQUIRE(cap % 32 == 0 && cap >= S, "lsh_match: plane capacity must be a multiple of 32 keys");
@@ -505,6 +645,24 @@ extern "C" int sah_lsh_match(const void* planes, int64_t cap, const void* qcodes
   dim3 grid((unsigned)sah_ceil_div(words, threads), (unsigned)bh);
   cudaStream_t st = (cudaStream_t)stream;
   sah_prof_begin(SAH_PROF_LSH_MATCH, st);
+  if (csz == 1 && G * Sq <= 4 && L <= 128 && (uintptr_t)planes % 16 == 0) {
+    static bool allowed[64] = {};
+    const int smem_staged = LSHM_RING + 512 + 64;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess && !(dev >= 0 && dev < 64 && allowed[dev])) {
+      e = cudaFuncSetAttribute(lsh_match_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_staged);
+      if (e == cudaSuccess && dev >= 0 && dev < 64) allowed[dev] = true;
+    }
+    if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "lsh_match attr: %s", cudaGetErrorString(e));
+    dim3 sgrid((unsigned)sah_ceil_div(S, LSHM_KEYS), (unsigned)bh);
+    lsh_match_staged_kernel<<<sgrid, LSHM_THREADS, smem_staged, st>>>(
+        reinterpret_cast<const uint8_t*>(planes), cap, reinterpret_cast<const uint8_t*>(qcodes), Hq, Sq, G, L,
+        S, W, prev_bits, out_bits, errflag);
+    SAH_LAUNCH_CHECK("lsh_match_staged");
+    sah_prof_end(SAH_PROF_LSH_MATCH, st);
+    return SAH_OK;
+  }
   if (csz == 1)
     lsh_match_kernel<uint8_t><<<grid, threads, smem, st>>>(reinterpret_cast<const uint8_t*>(planes), cap,
                                                            reinterpret_cast<const uint8_t*>(qcodes), Hq, Sq,

@@ -117,7 +117,7 @@ _SIGNATURES = {
     "sah_lsh_key_stats": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _I, _P, _L, _P, _P, _I, _P],
     "sah_lsh_key_sign": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _I, _P, _P, _P, _P, _I, _I, _L, _P, _P],
     "sah_lsh_query": [_P, _I, _L, _L, _L, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P, _P, _P, _P, _P],
-    "sah_lsh_match": [_P, _L, _P, _I, _I, _I, _I, _I, _I, _L, _L, _P, _P, _I, _P],
+    "sah_lsh_match": [_P, _L, _P, _I, _I, _I, _I, _I, _I, _L, _L, _P, _P, _I, _P, _P],
     "sah_lsh_key_den": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _I, _P, _P, _L, _P, _P, _P, _I, _P],
     "sah_lsh_prob": [_P, _I, _L, _L, _L, _I, _I, _I, _I, _I, _P, _P, _P, _L, _P, _P, _P, _P, _P, _L,
                      _I, _I, _P, _P, _I, _P],

@@ -340,7 +340,8 @@ class MagicPig(SamplingMasker):
         _native.check(
             lib.sah_lsh_match(sig.planes.data_ptr(), sig.capacity, qcodes.data_ptr(), B, Hq, Sq, G,
                               self.lsh_l, self.lsh_k, S, W, None, bits.data_ptr(),
-                              _native.sm_count(dev), st), "sah_lsh_match")
+                              _native.sm_count(dev), _native_ops.wait_flag(dev).data_ptr(), st),
+            "sah_lsh_match")
         if W * 32 > (S + 31) // 32 * 32:
             bits[:, (S + 31) // 32:].zero_()  # padding words of the row stride
         table = _native_ops.lsh_prob_table(dev, self.lsh_k, self.lsh_l) if dtype == torch.bfloat16 else None

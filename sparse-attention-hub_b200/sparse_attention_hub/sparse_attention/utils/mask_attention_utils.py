@@ -135,6 +135,9 @@ def native_masked_attention(
     # (another stream, another host thread) get their own
     key = (dev.index, st, threading.get_ident(), B, Hq, Hkv, Sq, S, D, has_data)
     ws = _workspace(dev, sizes, key)
+    if "groups" not in ws:  # where the kernel's error word sits behind the counters and tickets
+        nchunks = (words_per_row(S) + 31) // 32
+        ws["groups"], ws["err_index"] = sizes.groups, 2 * sizes.groups + sizes.groups * nchunks
     keep, bias_ptr, bsb, bsh, bsq = _bias_args(attention_mask, dtype, S)
     sink_t = None
     if sinks is not None:
@@ -212,6 +215,17 @@ def last_union_counts() -> Optional[torch.Tensor]:
     """int32 [groups]: distinct K/V rows the most recent attention call gathered per KV group
     (valid once the launching stream has run; used for bandwidth accounting)."""
     return _last_plan["ucount"]
+
+
+def attention_wait_errors() -> int:
+    """How many cached attention workspaces carry a set error word (a bounded wait of the
+    tensor-map copy stage ran out in some launch that used them); reads device memory."""
+    n = 0
+    for ws in _workspace_cache.values():
+        groups = ws.get("groups")
+        if groups is not None:
+            n += int(ws["ucount"][ws["err_index"]].item() != 0)
+    return n
 
 
 def last_union_list():
