@@ -404,11 +404,11 @@ int sah_mask_merge_data(const uint32_t* a_bits, const void* a_data, const int32_
 
 /* Signatures are stored once per KV head (the reference hashes keys repeated over
  * the query heads of a group with one projection per layer, magic_pig.py:564-565,
- * :476-491), table-major: planes[(b*Hkv + h)*L + l][cap] holds the code of every
- * key for table l (bit j of a code = sign bit of projection column l*K + j,
- * :120-150); codes are uint8 for lsh_k <= 8 and uint16 for lsh_k <= 16 (larger
- * lsh_k: SAH_ERR_UNSUPPORTED).  cap is a multiple of 32 keys; codes past the
- * last key must be zero.  head_dim must be a multiple of 32, at most 256. */
+ * :476-491), key-major: codes[(b*Hkv + h)*cap + s][LP] holds the L table codes of
+ * key s (bit j of a code = sign bit of projection column l*K + j, :120-150) followed
+ * by zero padding up to the row pitch LP = L rounded up to a whole number of 16-byte
+ * chunks; codes are uint8 for lsh_k <= 8 and uint16 for lsh_k <= 16 (larger lsh_k:
+ * SAH_ERR_UNSUPPORTED).  head_dim must be a multiple of 32, at most 256. */
 
 /* sums[(b*Hkv + h)*D + d] += sum over keys [s0, s1) in float64 (the key mean of
  * _center_KQ, :152-183, is sums / S rounded to the dtype; the caller zeroes sums). */
@@ -429,10 +429,10 @@ int sah_lsh_key_stats(const void* keys, int dtype, int64_t ks_b, int64_t ks_h, i
 int sah_lsh_key_sign(const void* keys, int dtype, int64_t ks_b, int64_t ks_h, int64_t ks_s, int B,
                      int Hkv, int64_t s0, int64_t s1, int D, const void* mean, const float* norms,
                      const unsigned int* max_norm_bits, const void* proj, int L, int K,
-                     int64_t cap, void* planes, void* stream);
+                     int64_t cap, void* codes, void* stream);
 
 /* Per mask row (b, h, q): centred query normalised to unit length, its L codes
- * (qcodes [rows][L], same code type as the planes) and the unit vector of the
+ * (qcodes [rows][L], same code type as the key codes, no padding) and the unit vector of the
  * transformed query (qunit float [rows][D]; the appended column is zero).
  * Optional (NULL to skip): qhat [rows][D], the same unit vector in `dtype` (its values
  * are representable, so nothing is lost), and qmu float [rows] = qunit . mean; both
@@ -445,11 +445,9 @@ int sah_lsh_query(const void* q, int dtype, int64_t qs_b, int64_t qs_h, int64_t 
  * (_compute_matches_int64, :455-463), joined with prev_bits[row][w] when prev_bits is
  * not NULL (the active set of the dense merge with the previous mask, :593).  Every
  * word of every row is written. */
-int sah_lsh_match(const void* planes, int64_t cap, const void* qcodes, int B, int Hq, int Sq, int G,
+int sah_lsh_match(const void* codes, int64_t cap, const void* qcodes, int B, int Hq, int Sq, int G,
                   int L, int K, int64_t S, int64_t W, const uint32_t* prev_bits, uint32_t* out_bits,
-                  int sm_count, int* errflag, void* stream);
-/* ^ errflag (optional): one device word that the kernel sets to 1 when a bounded wait on its
- * copy pipeline runs out (the result is then incomplete); the caller zeroes and reads it. */
+                  void* stream);
 
 /* data[ptr[row] + i] = collision probability 1 - (1 - (1 - theta/pi)^K)^L of the
  * i-th set bit of the row (:374-403), theta the angle between the transformed
@@ -577,8 +575,10 @@ int sah_attn_plan_lsh(const uint32_t* bits, const uint32_t* unit_bits, const flo
  * math, online softmax, every KV row fetched once per group and shared by
  * the group's query heads.  out is [B][Sq][Hq][D] contiguous in `dtype`
  * (utils/mask_attention_utils.py:479-481).  sinks: optional float [Hq]
- * (apply_sink_bias :357-402).  lse_out: optional float [rows][2] = (running
- * max, denominator) of each row, for cross-device merging. */
+ * (apply_sink_bias :357-402).  part_out: optional float [rows][D+2] = the
+ * unnormalised accumulator, the running max and the denominator of each row,
+ * for cross-device merging (one buffer, so that a sequence-sharded caller
+ * gathers it with one collective). */
 int sah_masked_attention(const void* q, const void* k, const void* v, int dtype,
                          int64_t qs_b, int64_t qs_h, int64_t qs_q, int64_t ks_b,
                          int64_t ks_h, int64_t ks_s, int64_t vs_b, int64_t vs_h,
@@ -587,8 +587,7 @@ int sah_masked_attention(const void* q, const void* k, const void* v, int dtype,
                          int64_t bias_s_h, int64_t bias_s_q, const float* sinks,
                          const sah_attn_sizes* sizes, const int32_t* ucols,
                          const uint16_t* umemb, const float* uw, const int32_t* ucount,
-                         float* partial, void* out, float* acc_out, float* lse_out,
-                         void* stream);
+                         float* partial, void* out, float* part_out, void* stream);
 
 /* sah_masked_attention (bfloat16) over a union list made by sah_attn_plan_lsh, with the
  * MagicPig sampling weights computed where the key row already is: the weight of a
@@ -610,8 +609,8 @@ int sah_masked_attention_lsh(const void* q, const void* k, const void* v, int64_
                              const float* sinks, const sah_attn_sizes* sizes, const int32_t* ucols,
                              const uint16_t* umemb, const float* uinv, const int32_t* ucount,
                              float* partial, const void* qhat, const float* qmu,
-                             const uint16_t* prob_table, void* out, float* acc_out, float* lse_out,
-                             float* w_dump, void* stream);
+                             const uint16_t* prob_table, void* out, float* part_out, float* w_dump,
+                             void* stream);
 
 /* Measurement aid (no counterpart in the reference): the K/V row gather of a planned
  * union list on its own -- the grid, tiling and copy pipeline of the bfloat16
@@ -623,12 +622,11 @@ int sah_attn_gather_probe(const void* k, const void* v, int64_t ks_b, int64_t ks
                           int64_t S, int D, const sah_attn_sizes* sizes, const int32_t* ucols,
                           const int32_t* ucount, unsigned int* sink, void* stream);
 
-/* Merge n_parts partial results (unnormalised fp32 accumulators acc
- * [n_parts][rows][D] with lse [n_parts][rows][2]) into out [B][Sq][Hq][D]:
- * the associative combine of sequence-sharded softmax partials. */
-int sah_attn_merge_parts(const float* acc, const float* lse, int n_parts, int B, int Hq,
-                         int Sq, int D, const float* sinks, int dtype, void* out,
-                         void* stream);
+/* Merge n_parts partial results (parts [n_parts][rows][D+2], the part_out of
+ * sah_masked_attention on every shard) into out [B][Sq][Hq][D]: the
+ * associative combine of sequence-sharded softmax partials. */
+int sah_attn_merge_parts(const float* parts, int n_parts, int B, int Hq, int Sq, int D,
+                         const float* sinks, int dtype, void* out, void* stream);
 
 /* Masked attention that brings its own scratch: plan + gather attention for a
  * unit-weight bitmap mask, with the union lists, counters and split partials

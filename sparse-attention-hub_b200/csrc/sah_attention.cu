@@ -276,12 +276,20 @@ attn_plan_emit_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restr
 
   const int64_t list0 = (int64_t)g * p.S + base;
   const uint32_t lt = (1u << lane) - 1u;
+  // LSH: the key constants of this lane's column in each of the 32 words, requested together
+  // (one round trip to memory instead of one per word)
   float M = 0.f;
-  const float* gd = nullptr;
+  float dcol[LSH ? 32 : 1];
   if constexpr (LSH) {
     M = __uint_as_float(*max_bits);
-    gd = dens + (g / p.nqb) * dens_cap;  // (batch, KV head) of the group
+    const float* gd = dens + (g / p.nqb) * dens_cap;  // (batch, KV head) of the group
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int64_t col = (c * PLAN_CHUNK_WORDS + j) * 32 + lane;
+      dcol[j] = col < p.S ? __ldg(gd + col) : 1.f;
+    }
   }
+#pragma unroll
   for (int j = 0; j < 32; ++j) {
     const uint32_t uj = union_sm[wl][j];
     if (uj == 0u) continue;  // the same for every lane
@@ -297,7 +305,7 @@ attn_plan_emit_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restr
     ucols[pos] = (int32_t)col;
     umemb[pos] = (uint16_t)memb;
     if constexpr (LSH) {
-      uw[pos] = __frcp_rn(__fmul_rn(M, gd[col]));
+      uw[pos] = __frcp_rn(__fmul_rn(M, dcol[j]));
     } else if (weighted) {
 #pragma unroll
       for (int r = 0; r < RMAX; ++r) {
@@ -767,8 +775,7 @@ template <typename T>
 __global__ void attn_merge_splits_kernel(const float* __restrict__ partial, int nsplit, int R,
                                          int D, int Hq, int Hkv, int Sq, int G, int q_block,
                                          int nqb, const float* __restrict__ sinks,
-                                         T* __restrict__ out, float* __restrict__ acc_out,
-                                         float* __restrict__ lse_out) {
+                                         T* __restrict__ out, float* __restrict__ part_out) {
   const int64_t g = blockIdx.x / R;
   const int r = (int)(blockIdx.x % R);
   const int qb = (int)(g % nqb);
@@ -803,12 +810,12 @@ __global__ void attn_merge_splits_kernel(const float* __restrict__ partial, int 
       float ms = p0[s * pstride + D];
       if (ms != -INFINITY) accv += p0[s * pstride + d] * expf(ms - M);
     }
-    if (acc_out != nullptr) acc_out[row * D + d] = accv;
+    if (part_out != nullptr) part_out[row * (D + 2) + d] = accv;
     out[((b * Sq + qi) * Hq + h) * D + d] = sah_from_float<T>(accv * resc / den);
   }
-  if (lse_out != nullptr && threadIdx.x == 0) {
-    lse_out[row * 2 + 0] = M;
-    lse_out[row * 2 + 1] = L;
+  if (part_out != nullptr && threadIdx.x == 0) {
+    part_out[row * (D + 2) + D] = M;
+    part_out[row * (D + 2) + D + 1] = L;
   }
 }
 
@@ -857,7 +864,7 @@ static int masked_attention_impl(const void* q, const void* k, const void* v, in
                                  int64_t bias_s_h, int64_t bias_s_q, const float* sinks,
                                  const sah_attn_sizes* sizes, const int32_t* ucols,
                                  const uint16_t* umemb, const float* uw, const int32_t* ucount,
-                                 float* partial, void* out, float* acc_out, float* lse_out,
+                                 float* partial, void* out, float* part_out,
                                  const AttnLsh* lsh, void* stream) {
   SAH_REQUIRE(q && k && v && sizes && ucols && umemb && ucount && partial && out,
               "masked_attention: null pointer");
@@ -901,8 +908,8 @@ static int masked_attention_impl(const void* q, const void* k, const void* v, in
     int* tickets = const_cast<int*>(ucount) + groups + (int64_t)groups * plan_chunks(S);
     int* errflag = tickets + groups;  // set when a bounded wait inside the kernel ran out
     rc = (D == 128)
-             ? launch_attention_mma<128>(a, B, groups, tickets, errflag, sinks, out, acc_out, lse_out, lsh != nullptr, st)
-             : launch_attention_mma<64>(a, B, groups, tickets, errflag, sinks, out, acc_out, lse_out, lsh != nullptr, st);
+             ? launch_attention_mma<128>(a, B, groups, tickets, errflag, sinks, out, part_out, lsh != nullptr, st)
+             : launch_attention_mma<64>(a, B, groups, tickets, errflag, sinks, out, part_out, lsh != nullptr, st);
     if (rc != SAH_OK) return rc;
     SAH_LAUNCH_CHECK("masked_attention_mma");
     sah_prof_end(SAH_PROF_ATTENTION, (cudaStream_t)stream);
@@ -918,8 +925,7 @@ static int masked_attention_impl(const void* q, const void* k, const void* v, in
   sah_prof_end(SAH_PROF_ATTENTION, (cudaStream_t)stream);
   sah_prof_begin(SAH_PROF_ATTN_MERGE, (cudaStream_t)stream);
   attn_merge_splits_kernel<float><<<(unsigned)(groups * a.R), D, 0, st>>>(
-      partial, a.nsplit, a.R, D, Hq, Hkv, Sq, a.G, a.q_block, a.nqb, sinks, (float*)out, acc_out,
-      lse_out);
+      partial, a.nsplit, a.R, D, Hq, Hkv, Sq, a.G, a.q_block, a.nqb, sinks, (float*)out, part_out);
   SAH_LAUNCH_CHECK("attn_merge_splits");
   sah_prof_end(SAH_PROF_ATTN_MERGE, (cudaStream_t)stream);
   return SAH_OK;
@@ -933,12 +939,12 @@ extern "C" int sah_masked_attention(const void* q, const void* k, const void* v,
                                     int64_t bias_s_h, int64_t bias_s_q, const float* sinks,
                                     const sah_attn_sizes* sizes, const int32_t* ucols,
                                     const uint16_t* umemb, const float* uw, const int32_t* ucount,
-                                    float* partial, void* out, float* acc_out, float* lse_out,
+                                    float* partial, void* out, float* part_out,
                                     void* stream) {
   return masked_attention_impl(q, k, v, dtype, qs_b, qs_h, qs_q, ks_b, ks_h, ks_s, vs_b, vs_h, vs_s,
                                B, Hq, Hkv, Sq, S, D, scaling, bias, bias_s_b, bias_s_h, bias_s_q,
-                               sinks, sizes, ucols, umemb, uw, ucount, partial, out, acc_out,
-                               lse_out, nullptr, stream);
+                               sinks, sizes, ucols, umemb, uw, ucount, partial, out, part_out,
+                               nullptr, stream);
 }
 
 extern "C" int sah_masked_attention_lsh(const void* q, const void* k, const void* v, int64_t qs_b,
@@ -951,7 +957,7 @@ extern "C" int sah_masked_attention_lsh(const void* q, const void* k, const void
                                         const uint16_t* umemb, const float* uinv,
                                         const int32_t* ucount, float* partial, const void* qhat,
                                         const float* qmu, const uint16_t* prob_table, void* out,
-                                        float* acc_out, float* lse_out, float* w_dump,
+                                        float* part_out, float* w_dump,
                                         void* stream) {
   SAH_REQUIRE(uinv && qhat && qmu && prob_table, "masked_attention_lsh: null pointer");
   SAH_REQUIRE((uintptr_t)qhat % 16 == 0, "masked_attention_lsh: qhat must be 16-byte aligned");
@@ -959,7 +965,7 @@ extern "C" int sah_masked_attention_lsh(const void* q, const void* k, const void
   return masked_attention_impl(q, k, v, SAH_BF16, qs_b, qs_h, qs_q, ks_b, ks_h, ks_s, vs_b, vs_h,
                                vs_s, B, Hq, Hkv, Sq, S, D, scaling, bias, bias_s_b, bias_s_h,
                                bias_s_q, sinks, sizes, ucols, umemb, uinv, ucount, partial, out,
-                               acc_out, lse_out, &lsh, stream);
+                               part_out, &lsh, stream);
 }
 
 extern "C" int sah_attn_gather_probe(const void* k, const void* v, int64_t ks_b, int64_t ks_h,
@@ -1003,22 +1009,25 @@ extern "C" int sah_attn_gather_probe(const void* k, const void* v, int64_t ks_b,
   return SAH_OK;
 }
 
-// Merge partial results computed on different sequence shards.
+// Merge partial results computed on different sequence shards: parts [n_parts][rows][D+2]
+// holds, per row, the unnormalised accumulator, the running maximum and the denominator.
 template <typename T>
-__global__ void attn_merge_parts_kernel(const float* __restrict__ acc, const float* __restrict__ lse,
-                                        int n_parts, int64_t rows, int Hq, int Sq, int D,
-                                        const float* __restrict__ sinks, T* __restrict__ out) {
+__global__ void attn_merge_parts_kernel(const float* __restrict__ parts, int n_parts, int64_t rows,
+                                        int Hq, int Sq, int D, const float* __restrict__ sinks,
+                                        T* __restrict__ out) {
   const int64_t row = blockIdx.x;
   const int qi = (int)(row % Sq);
   const int64_t bh = row / Sq;
   const int h = (int)(bh % Hq);
   const int64_t b = bh / Hq;
+  const int64_t ld = D + 2, pstride = rows * ld;
+  const float* pr = parts + row * ld;
   float M = -INFINITY;
-  for (int p = 0; p < n_parts; ++p) M = fmaxf(M, lse[((int64_t)p * rows + row) * 2]);
+  for (int p = 0; p < n_parts; ++p) M = fmaxf(M, pr[p * pstride + D]);
   float L = 0.f;
   for (int p = 0; p < n_parts; ++p) {
-    float mp = lse[((int64_t)p * rows + row) * 2];
-    if (mp != -INFINITY) L += lse[((int64_t)p * rows + row) * 2 + 1] * expf(mp - M);
+    const float mp = pr[p * pstride + D];
+    if (mp != -INFINITY) L += pr[p * pstride + D + 1] * expf(mp - M);
   }
   float Mx = M, sink_term = 0.f;
   if (sinks != nullptr) {
@@ -1031,23 +1040,22 @@ __global__ void attn_merge_parts_kernel(const float* __restrict__ acc, const flo
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float a = 0.f;
     for (int p = 0; p < n_parts; ++p) {
-      float mp = lse[((int64_t)p * rows + row) * 2];
-      if (mp != -INFINITY) a += acc[((int64_t)p * rows + row) * D + d] * expf(mp - M);
+      const float mp = pr[p * pstride + D];
+      if (mp != -INFINITY) a += pr[p * pstride + d] * expf(mp - M);
     }
     out[((b * Sq + qi) * Hq + h) * D + d] = sah_from_float<T>(a * resc / den);
   }
 }
 
-extern "C" int sah_attn_merge_parts(const float* acc, const float* lse, int n_parts, int B,
-                                    int Hq, int Sq, int D, const float* sinks, int dtype,
-                                    void* out, void* stream) {
-  SAH_REQUIRE(acc && lse && out, "attn_merge_parts: null pointer");
+extern "C" int sah_attn_merge_parts(const float* parts, int n_parts, int B, int Hq, int Sq, int D,
+                                    const float* sinks, int dtype, void* out, void* stream) {
+  SAH_REQUIRE(parts && out, "attn_merge_parts: null pointer");
   SAH_REQUIRE(n_parts > 0 && B > 0 && Hq > 0 && Sq > 0 && D > 0, "attn_merge_parts: bad extents");
   const int64_t rows = (int64_t)B * Hq * Sq;
   int threads = D < 32 ? 32 : (D > 256 ? 256 : D);
   SAH_DISPATCH_DTYPE(dtype, T, {
     attn_merge_parts_kernel<T><<<(unsigned)rows, threads, 0, (cudaStream_t)stream>>>(
-        acc, lse, n_parts, rows, Hq, Sq, D, sinks, (T*)out);
+        parts, n_parts, rows, Hq, Sq, D, sinks, (T*)out);
   });
   SAH_LAUNCH_CHECK("attn_merge_parts");
   return SAH_OK;
@@ -1143,5 +1151,5 @@ extern "C" int sah_masked_attention_static(
   return sah_masked_attention(q, k, v, dtype, qs_b, qs_h, qs_q, ks_b, ks_h, ks_s, vs_b, vs_h, vs_s,
                               B, Hq, Hkv, Sq, S, D, scaling, bias, bias_s_b, bias_s_h, bias_s_q,
                               sinks, &sizes, ucols, umemb, nullptr, ucount, partial, out, nullptr,
-                              nullptr, stream);
+                              stream);
 }

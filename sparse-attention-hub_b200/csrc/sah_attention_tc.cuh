@@ -44,7 +44,7 @@
 #endif
 #define ATM_THREADS (ATM_WARPS * 32)
 #define ATM_TILE 16
-#define ATM_SPIN_LIMIT (1 << 22)
+#define ATM_SPIN_LIMIT (1 << 19)
 
 struct AtmMaps {
   CUtensorMap k, v;
@@ -58,23 +58,23 @@ __device__ __forceinline__ void atm_mbar_expect_tx(uint32_t bar, uint32_t bytes)
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes)
                : "memory");
 }
-__device__ __forceinline__ bool atm_mbar_test(uint32_t bar, uint32_t parity) {
+// One try of the phase test; the hardware may suspend the thread for up to `hint_ns` while the
+// phase is pending, so a waiting warp does not compete for issue slots.
+__device__ __forceinline__ bool atm_mbar_try(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
   uint32_t ok;
   asm volatile(
       "{\n.reg .pred p;\n"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
       "selp.u32 %0, 1, 0, p;\n}\n"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
       : "memory");
   return ok != 0u;
 }
-// Bounded wait: false when the phase did not complete within the spin limit.
+// Bounded wait: false when the phase did not complete within the limit (about a second).
 __device__ __forceinline__ bool atm_mbar_wait(uint32_t bar, uint32_t parity) {
-  for (int i = 0; i < ATM_SPIN_LIMIT; ++i) {  // about half a second at most
-    if (atm_mbar_test(bar, parity)) return true;
-    if (i > 64) __nanosleep(64);
-  }
+  for (int i = 0; i < ATM_SPIN_LIMIT; ++i)
+    if (atm_mbar_try(bar, parity, 2000u)) return true;
   return false;
 }
 // Four rows y0..y3 of the 2-D tensor, columns [x, x + box width), to shared memory.
@@ -173,8 +173,7 @@ template <int D, bool HALF, bool LSHW, bool TMA, int NST>
 __global__ void __launch_bounds__(ATM_THREADS, NST == 2 ? 3 : 2)
 masked_attention_mma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, int* __restrict__ tickets,
                             int* __restrict__ errflag, const float* __restrict__ sinks,
-                            __nv_bfloat16* __restrict__ out, float* __restrict__ acc_out,
-                            float* __restrict__ lse_out) {
+                            __nv_bfloat16* __restrict__ out, float* __restrict__ part_out) {
   static_assert(!LSHW || HALF, "in-place MagicPig weights use the spare rows of the half tile");
   using C = AtmCfg<D, TMA, NST>;
   static_assert(C::Q_BYTES <= C::WARP_BYTES, "the Q tile is staged in the first ring");
@@ -406,11 +405,12 @@ masked_attention_mma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, in
     const int u0 = (my_first + t * lanes_total) * ATM_TILE;
 
     // ---- S = Q . K^T ----
-    float s[2][2 * NR];
+    // even and odd k-steps accumulate separately: four chains of dependent mma instead of two
+    float s[2][2 * NR], s_odd[2][2 * NR];
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int e = 0; e < 2 * NR; ++e) s[nt][e] = 0.f;
+      for (int e = 0; e < 2 * NR; ++e) s[nt][e] = s_odd[nt][e] = 0.f;
     {
       const int mi = lane >> 3, rr = lane & 7;
       const uint32_t kaddr = TMA ? kst + ((mi >> 1) * 8 + rr) * 128
@@ -422,15 +422,20 @@ masked_attention_mma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, in
         const int kc = 2 * ks + (mi & 1);
         atm_ldmatrix_x4(b0, b1, b2, b3,
                         TMA ? kaddr + (kc >> 3) * 2048 + (((kc & 7) ^ rr) << 4) : kaddr + ks * 32);
+        float(*acc)[2 * NR] = (ks & 1) ? s_odd : s;
         if constexpr (HALF) {
-          atm_mma_half(s[0][0], s[0][1], qf[ks][0], qf[ks][1], b0, b1);
-          atm_mma_half(s[1][0], s[1][1], qf[ks][0], qf[ks][1], b2, b3);
+          atm_mma_half(acc[0][0], acc[0][1], qf[ks][0], qf[ks][1], b0, b1);
+          atm_mma_half(acc[1][0], acc[1][1], qf[ks][0], qf[ks][1], b2, b3);
         } else {
-          atm_mma_full(s[0], qf[ks], b0, b1);
-          atm_mma_full(s[1], qf[ks], b2, b3);
+          atm_mma_full(acc[0], qf[ks], b0, b1);
+          atm_mma_full(acc[1], qf[ks], b2, b3);
         }
       }
     }
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 2 * NR; ++e) s[nt][e] += s_odd[nt][e];
     // LSHW: the products with the centred unit queries sit four rows further down,
     // i.e. in the lane 16 higher
     float hat[2][2];
@@ -660,11 +665,11 @@ masked_attention_mma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, in
     const float resc = (M == -INFINITY) ? 0.f : __expf(M - Mx);
     const float den = L * resc + sink_term;
     const int64_t row = (b * a.Hq + h) * a.Sq + qi;
-    if (acc_out != nullptr) acc_out[row * D + d] = accv;
+    if (part_out != nullptr) part_out[row * (D + 2) + d] = accv;
     out[((b * a.Sq + qi) * a.Hq + h) * D + d] = __float2bfloat16_rn(accv * resc / den);
-    if (lse_out != nullptr && d == 0) {
-      lse_out[row * 2 + 0] = M;
-      lse_out[row * 2 + 1] = L;
+    if (part_out != nullptr && d == 0) {
+      part_out[row * (D + 2) + D] = M;
+      part_out[row * (D + 2) + D + 1] = L;
     }
   }
 }
@@ -824,7 +829,7 @@ static int atm_stages_requested() {
 
 template <int D>
 static int launch_attention_mma(AttnArgs a, int B, int groups, int* tickets, int* errflag,
-                                const float* sinks, void* out, float* acc_out, float* lse_out, bool lsh,
+                                const float* sinks, void* out, float* part_out, bool lsh,
                                 cudaStream_t st) {
   static bool allowed[9][64] = {};
   if ((size_t)16 * a.nsplit * 4 + 128 > (size_t)ATM_WARPS * AtmCfg<D, true, 2>::WARP_BYTES)
@@ -853,7 +858,7 @@ static int launch_attention_mma(AttnArgs a, int B, int groups, int* tickets, int
     e = atm_allow_smem(masked_attention_mma_kernel<D, HALF, LSHW, TMA, NST>, smem, allowed[SLOT]);  \
     if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "attention attr: %s", cudaGetErrorString(e)); \
     masked_attention_mma_kernel<D, HALF, LSHW, TMA, NST><<<grid, ATM_THREADS, smem, st>>>(          \
-        a, maps, tickets, errflag, sinks, (__nv_bfloat16*)out, acc_out, lse_out);                   \
+        a, maps, tickets, errflag, sinks, (__nv_bfloat16*)out, part_out);                           \
   } while (0)
   if (lsh) {
     if (tma && two) ATM_LAUNCH(true, true, true, 2, 5);

@@ -7,11 +7,11 @@
 //   sah_lsh_match         keys that share at least one table code with the query (:455-463)
 //   sah_lsh_prob          collision probability of every matched key (:374-403)
 //
-// Signatures are stored table-major: plane l of (batch, KV head) holds the code of every key
-// for table l, one code per key (uint8 for lsh_k <= 8, uint16 for lsh_k <= 16), so that the
-// match kernel streams each plane with 16-byte loads.  The reference repeats keys over the
-// query heads of a group and uses one projection per layer, so the signatures of a group's
-// heads are identical and are stored once per KV head.
+// Signatures are stored key-major: the L table codes of a key (uint8 for lsh_k <= 8, uint16 for
+// lsh_k <= 16) sit side by side in a row padded to a multiple of 16 bytes, rows in key order,
+// so that the match kernel reads one contiguous stream per (batch, KV head).  The reference
+// repeats keys over the query heads of a group and uses one projection per layer, so the
+// signatures of a group's heads are identical and are stored once per KV head.
 //
 // Reductions over the head dimension use one fixed order ("lane order"): lane t of a warp
 // owns the D/32 consecutive channels starting at t*D/32 and sums them in ascending order,
@@ -20,6 +20,13 @@
 #include "sah_common.cuh"
 
 #define LSH_MAX_PER_LANE 8  // D <= 256
+
+// codes per signature row: L rounded up so that a row is a multiple of 16 bytes
+template <typename CodeT>
+__host__ __device__ __forceinline__ int lsh_row_pitch(int L) {
+  const int per16 = 16 / (int)sizeof(CodeT);
+  return (L + per16 - 1) / per16 * per16;
+}
 
 __device__ __forceinline__ float lsh_warp_sum(float v) {
 #pragma unroll
@@ -164,7 +171,7 @@ lsh_key_sign_kernel(const T* __restrict__ k, int64_t ks_b, int64_t ks_h, int64_t
                     int64_t s0, int64_t s1, int D, const T* __restrict__ mean,
                     const float* __restrict__ norms, const unsigned int* __restrict__ max_bits,
                     const T* __restrict__ proj, int L, int K, int64_t cap,
-                    CodeT* __restrict__ planes) {
+                    CodeT* __restrict__ codes) {
   extern __shared__ __align__(16) unsigned char lsh_smem[];
   const int nbits = L * K;
   const int Dp = D + 1;
@@ -222,14 +229,17 @@ lsh_key_sign_kernel(const T* __restrict__ k, int64_t ks_b, int64_t ks_h, int64_t
     }
   }
   __syncthreads();
-  // pack: bit j of table l is column l*K + j (magic_pig.py:120-150)
-  for (int i = threadIdx.x; i < L * LSH_KT; i += 256) {
-    const int l = i / LSH_KT, kk = i % LSH_KT;
+  // pack: bit j of table l is column l*K + j (magic_pig.py:120-150); the row of a key holds
+  // its L codes and zero padding up to the row pitch
+  const int LP = lsh_row_pitch<CodeT>(L);
+  for (int i = threadIdx.x; i < LP * LSH_KT; i += 256) {
+    const int kk = i / LP, l = i % LP;
     const int64_t s = t0 + kk;
     if (s >= s1) continue;
     unsigned int code = 0;
-    for (int j = 0; j < K; ++j) code |= (unsigned int)sb[kk * nbits + l * K + j] << j;
-    planes[(bh * L + l) * cap + s] = (CodeT)code;
+    if (l < L)
+      for (int j = 0; j < K; ++j) code |= (unsigned int)sb[kk * nbits + l * K + j] << j;
+    codes[(bh * cap + s) * LP + l] = (CodeT)code;
   }
 }
 
@@ -237,8 +247,8 @@ extern "C" int sah_lsh_key_sign(const void* keys, int dtype, int64_t ks_b, int64
                                 int64_t ks_s, int B, int Hkv, int64_t s0, int64_t s1, int D,
                                 const void* mean, const float* norms,
                                 const unsigned int* max_norm_bits, const void* proj, int L, int K,
-                                int64_t cap, void* planes, void* stream) {
-  SAH_REQUIRE(keys && norms && max_norm_bits && proj && planes, "lsh_key_sign: null pointer");
+                                int64_t cap, void* codes, void* stream) {
+  SAH_REQUIRE(keys && norms && max_norm_bits && proj && codes, "lsh_key_sign: null pointer");
   SAH_REQUIRE(D % 32 == 0 && D <= 32 * LSH_MAX_PER_LANE, "lsh_key_sign: head_dim must be a multiple of 32, <= 256");
   SAH_REQUIRE(L > 0 && K > 0, "lsh_key_sign: bad table shape");
   if (K > 16) return sah_fail(SAH_ERR_UNSUPPORTED, "lsh: lsh_k = %d > 16 bits per table is not built", K);
@@ -257,7 +267,7 @@ extern "C" int sah_lsh_key_sign(const void* keys, int dtype, int64_t ks_b, int64
     lsh_key_sign_kernel<T, CodeT><<<grid, 256, smem, st>>>(                                        \
         reinterpret_cast<const T*>(keys), ks_b, ks_h, ks_s, Hkv, s0, s1, D,                        \
         reinterpret_cast<const T*>(mean), norms, max_norm_bits, reinterpret_cast<const T*>(proj),  \
-        L, K, cap, reinterpret_cast<CodeT*>(planes));                                              \
+        L, K, cap, reinterpret_cast<CodeT*>(codes));                                               \
   } while (0)
   SAH_DISPATCH_DTYPE(dtype, T, {
     if (K <= 8) LSH_SIGN_LAUNCH(T, uint8_t); else LSH_SIGN_LAUNCH(T, uint16_t);
@@ -372,305 +382,134 @@ extern "C" int sah_lsh_query(const void* q, int dtype, int64_t qs_b, int64_t qs_
 // ---------------------------------------------------------------------------------------
 // match: any table code equal
 // ---------------------------------------------------------------------------------------
-#define LSH_MR 4  // mask rows (query heads x query positions of a group) per pass
+// One thread per key: it loads the key's signature row (a few 16-byte loads, all requested
+// before the first compare) and compares it byte-wise (or halfword-wise) with the signature
+// rows of the group's queries, which sit in shared memory padded with a value no key row
+// holds in its padding.  A warp covers 32 consecutive keys, so a ballot of "some table code
+// equal" is the bitmap word of those keys; every warp does four such words and writes them
+// side by side.
+#define LSH_MATCH_WARPS 8
+#define LSH_MATCH_WORDS 4
+#define LSH_MAX_CHUNKS 16  // 16-byte chunks per signature row (256 byte codes, 128 halfword codes)
 
-// 4 byte flags (0xFF / 0x00) -> 4 bits, byte i -> bit i
-__device__ __forceinline__ unsigned int lsh_flags4(unsigned int w) {
-  return ((w & 0x01010101u) * 0x01020408u) >> 24;
-}
-// 2 halfword flags (0xFFFF / 0) -> 2 bits
-__device__ __forceinline__ unsigned int lsh_flags2(unsigned int w) {
-  return (w & 1u) | ((w >> 15) & 2u);
-}
-
-// Each thread owns 32 consecutive keys of one (batch, KV head): one bitmap word per mask row.
-// The table planes are taken UNR at a time: their 16-byte loads are all requested before the
-// first compare, so a thread keeps UNR * 32 code bytes in flight.
-template <typename CodeT>
-__device__ __forceinline__ void lsh_match_accumulate(const uint4& v, unsigned int qc, unsigned int* acc) {
-  if (sizeof(CodeT) == 1) {
-    const unsigned int rep = qc * 0x01010101u;
-    acc[0] |= __vcmpeq4(v.x, rep);
-    acc[1] |= __vcmpeq4(v.y, rep);
-    acc[2] |= __vcmpeq4(v.z, rep);
-    acc[3] |= __vcmpeq4(v.w, rep);
-  } else {
-    const unsigned int rep = qc * 0x00010001u;
-    acc[0] |= __vcmpeq2(v.x, rep);
-    acc[1] |= __vcmpeq2(v.y, rep);
-    acc[2] |= __vcmpeq2(v.z, rep);
-    acc[3] |= __vcmpeq2(v.w, rep);
-  }
-}
-
-template <typename CodeT>
-__global__ void __launch_bounds__(256)
-lsh_match_kernel(const CodeT* __restrict__ planes, int64_t cap, const CodeT* __restrict__ qcodes,
+template <typename CodeT, int NC>
+__global__ void __launch_bounds__(LSH_MATCH_WARPS * 32)
+lsh_match_kernel(const CodeT* __restrict__ codes, int64_t cap, const CodeT* __restrict__ qcodes,
                  int Hq, int Sq, int G, int L, int64_t S, int64_t W,
                  const uint32_t* __restrict__ prev_bits, uint32_t* __restrict__ out_bits) {
   extern __shared__ __align__(16) unsigned char lsh_smem[];
-  CodeT* qs = reinterpret_cast<CodeT*>(lsh_smem);  // [R][L]
+  uint4* qs = reinterpret_cast<uint4*>(lsh_smem);  // [R][NC]
   const int R = G * Sq;
+  constexpr int PER16 = 16 / (int)sizeof(CodeT);
+  constexpr int LP = NC * PER16;
   const int64_t bh = blockIdx.y;           // b * Hkv + hkv
   const int Hkv = Hq / G;
   const int64_t b = bh / Hkv, hkv = bh % Hkv;
-  for (int i = threadIdx.x; i < R * L; i += blockDim.x) {
-    const int r = i / L, l = i % L;
-    const int g = r / Sq, qi = r % Sq;
-    qs[i] = qcodes[(((b * Hq) + hkv * G + g) * Sq + qi) * L + l];
-  }
-  __syncthreads();
-  const int64_t word = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (word * 32 >= S) return;
-  constexpr int PER16 = 16 / (int)sizeof(CodeT);  // codes per 16-byte load
-  constexpr int NV = 32 / PER16;                  // 16-byte loads per 32 keys
-  constexpr int UNR = sizeof(CodeT) == 1 ? 4 : 2; // table planes in flight
-  const CodeT* pbase = planes + bh * (int64_t)L * cap + word * 32;
-  for (int r0 = 0; r0 < R; r0 += LSH_MR) {
-    unsigned int acc[LSH_MR][NV * 4];
-#pragma unroll
-    for (int r = 0; r < LSH_MR; ++r)
-#pragma unroll
-      for (int i = 0; i < NV * 4; ++i) acc[r][i] = 0u;
-    int l = 0;
-    for (; l + UNR <= L; l += UNR) {
-      uint4 v[UNR][NV];
-#pragma unroll
-      for (int u = 0; u < UNR; ++u)
-#pragma unroll
-        for (int i = 0; i < NV; ++i)
-          v[u][i] = __ldg(reinterpret_cast<const uint4*>(pbase + (int64_t)(l + u) * cap) + i);
-#pragma unroll
-      for (int u = 0; u < UNR; ++u)
-#pragma unroll
-        for (int r = 0; r < LSH_MR; ++r)
-          if (r0 + r < R) {
-            const unsigned int qc = (unsigned int)qs[(r0 + r) * L + l + u];
-#pragma unroll
-            for (int i = 0; i < NV; ++i) lsh_match_accumulate<CodeT>(v[u][i], qc, &acc[r][i * 4]);
-          }
-    }
-    for (; l < L; ++l) {
-      uint4 v[NV];
-#pragma unroll
-      for (int i = 0; i < NV; ++i) v[i] = __ldg(reinterpret_cast<const uint4*>(pbase + (int64_t)l * cap) + i);
-#pragma unroll
-      for (int r = 0; r < LSH_MR; ++r)
-        if (r0 + r < R) {
-          const unsigned int qc = (unsigned int)qs[(r0 + r) * L + l];
-#pragma unroll
-          for (int i = 0; i < NV; ++i) lsh_match_accumulate<CodeT>(v[i], qc, &acc[r][i * 4]);
-        }
-    }
-    const int64_t left = S - word * 32;
-    const unsigned int valid = left >= 32 ? 0xffffffffu : ((1u << left) - 1u);
-#pragma unroll
-    for (int r = 0; r < LSH_MR; ++r) {
-      if (r0 + r < R) {
-        unsigned int bits = 0;
-        if (sizeof(CodeT) == 1) {
-#pragma unroll
-          for (int i = 0; i < NV * 4; ++i) bits |= lsh_flags4(acc[r][i]) << (4 * i);
-        } else {
-#pragma unroll
-          for (int i = 0; i < NV * 4; ++i) bits |= lsh_flags2(acc[r][i]) << (2 * i);
-        }
-        const int g = (r0 + r) / Sq, qi = (r0 + r) % Sq;
-        const int64_t row = ((b * Hq) + hkv * G + g) * Sq + qi;
-        bits &= valid;
-        if (prev_bits != nullptr) bits |= prev_bits[row * W + word];
-        out_bits[row * W + word] = bits;
-      }
-    }
-  }
-}
-
-// ---- the same with the code planes staged through shared memory by bulk copies ----------
-// One CTA of 128 threads owns 4096 consecutive keys of one (batch, KV head).  An elected thread
-// requests the 4 KB slice of every table plane with one bulk asynchronous copy
-// (cp.async.bulk, global -> shared, completion counted on an mbarrier per group of five
-// planes); three groups circulate in a ring, so two groups (40 KB per CTA, three CTAs per SM)
-// are in flight while the threads compare the third.  Memory parallelism no longer depends on
-// registers, and each plane slice is one contiguous 4 KB read.  Byte codes (lsh_k <= 8) and at
-// most 4 mask rows per group; other shapes take lsh_match_kernel.
-// Every wait on an mbarrier is bounded; a wait that runs out sets *errflag and the CTA
-// finishes without reading further.
-#define LSHM_THREADS 128
-#define LSHM_KEYS (LSHM_THREADS * 32)
-#define LSHM_GROUP 5
-#define LSHM_NGROUPS 3
-#define LSHM_RING (LSHM_NGROUPS * LSHM_GROUP * LSHM_KEYS)
-#define LSHM_SPIN_LIMIT (1 << 22)
-
-__device__ __forceinline__ bool lshm_mbar_wait(uint32_t bar, uint32_t parity) {
-  for (int i = 0; i < LSHM_SPIN_LIMIT; ++i) {  // about half a second at most
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (ok) return true;
-    if (i > 64) __nanosleep(64);
-  }
-  return false;
-}
-
-__global__ void __launch_bounds__(LSHM_THREADS)
-lsh_match_staged_kernel(const uint8_t* __restrict__ planes, int64_t cap, const uint8_t* __restrict__ qcodes,
-                        int Hq, int Sq, int G, int L, int64_t S, int64_t W,
-                        const uint32_t* __restrict__ prev_bits, uint32_t* __restrict__ out_bits,
-                        int* __restrict__ errflag) {
-  extern __shared__ __align__(128) unsigned char lsh_smem[];
-  unsigned char* ring = lsh_smem;                               // [NGROUPS][GROUP][4096]
-  uint8_t* qs = lsh_smem + LSHM_RING;                           // [R][L]
-  const int R = G * Sq;                                         // <= 4
-  const uint32_t bar_s = (uint32_t)__cvta_generic_to_shared(lsh_smem + LSHM_RING + 512);
-  const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
-  const int tid = threadIdx.x;
-  const int64_t bh = blockIdx.y;
-  const int Hkv = Hq / G;
-  const int64_t b = bh / Hkv, hkv = bh % Hkv;
-  const int64_t k0 = (int64_t)blockIdx.x * LSHM_KEYS;
-  const uint32_t plane_bytes = (uint32_t)((cap - k0 < LSHM_KEYS) ? (cap - k0) : LSHM_KEYS);  // multiple of 32
-  if (tid == 0) {
-#pragma unroll
-    for (int i = 0; i < LSHM_NGROUPS; ++i)
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar_s + i * 8), "r"(1));
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-  }
-  for (int i = tid; i < R * L; i += LSHM_THREADS) {
-    const int r = i / L, l = i % L;
-    const int g = r / Sq, qi = r % Sq;
-    qs[i] = qcodes[(((b * Hq) + hkv * G + g) * Sq + qi) * L + l];
-  }
-  __syncthreads();
-
-  const int ngroups = (L + LSHM_GROUP - 1) / LSHM_GROUP;
-  const uint8_t* pbase = planes + bh * (int64_t)L * cap + k0;
-  auto issue_group = [&](int gi) {  // elected thread only
-    const int slot = gi % LSHM_NGROUPS;
-    const int l0 = gi * LSHM_GROUP;
-    const int n = (L - l0 < LSHM_GROUP) ? (L - l0) : LSHM_GROUP;
-    const uint32_t bar = bar_s + slot * 8;
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar),
-                 "r"((uint32_t)n * plane_bytes)
-                 : "memory");
-    for (int u = 0; u < n; ++u)
-      asm volatile(
-          "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::
-              "r"(ring_s + (uint32_t)(slot * LSHM_GROUP + u) * LSHM_KEYS),
-          "l"(pbase + (int64_t)(l0 + u) * cap), "r"(plane_bytes), "r"(bar)
-          : "memory");
-  };
-  int issued = 0;
-  if (tid == 0)
-    for (; issued < LSHM_NGROUPS && issued < ngroups; ++issued) issue_group(issued);
-
-  const bool active = k0 + (int64_t)tid * 32 < S;  // this thread's 32 keys hold columns < S
-  unsigned int acc[4][8];
-#pragma unroll
-  for (int r = 0; r < 4; ++r)
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[r][i] = 0u;
-  bool dead = false;
-  for (int gi = 0; gi < ngroups; ++gi) {
-    const int slot = gi % LSHM_NGROUPS;
-    if (!dead && !lshm_mbar_wait(bar_s + slot * 8, (uint32_t)((gi / LSHM_NGROUPS) & 1))) {
-      dead = true;
-      if (errflag != nullptr) atomicExch(errflag, 1);
-    }
-    const int l0 = gi * LSHM_GROUP;
-    const int n = (L - l0 < LSHM_GROUP) ? (L - l0) : LSHM_GROUP;
-    if (active && !dead) {
-      for (int u = 0; u < n; ++u) {
-        const uint4* src = reinterpret_cast<const uint4*>(ring + (slot * LSHM_GROUP + u) * LSHM_KEYS + tid * 32);
-        const uint4 v0 = src[0], v1 = src[1];
-#pragma unroll
-        for (int r = 0; r < 4; ++r)
-          if (r < R) {
-            const unsigned int qc = (unsigned int)qs[r * L + l0 + u];
-            lsh_match_accumulate<uint8_t>(v0, qc, &acc[r][0]);
-            lsh_match_accumulate<uint8_t>(v1, qc, &acc[r][4]);
-          }
-      }
-    }
-    __syncthreads();  // every thread has read this slot
-    if (tid == 0 && !dead && issued < ngroups) issue_group(issued++);
-  }
-  if (tid == 0 && dead) {
-    // copies that were requested and never awaited get a bounded chance to land before the
-    // shared memory is handed back
-    for (int gi = 0; gi < issued; ++gi)
-      lshm_mbar_wait(bar_s + (gi % LSHM_NGROUPS) * 8, (uint32_t)((gi / LSHM_NGROUPS) & 1));
-  }
-  if (!active) return;
-  const int64_t word = k0 / 32 + tid;
-  const int64_t left = S - word * 32;
-  const unsigned int valid = left >= 32 ? 0xffffffffu : ((1u << left) - 1u);
-#pragma unroll
-  for (int r = 0; r < 4; ++r) {
-    if (r < R) {
-      unsigned int bits = 0;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) bits |= lsh_flags4(acc[r][i]) << (4 * i);
+  {
+    CodeT* qflat = reinterpret_cast<CodeT*>(lsh_smem);
+    for (int i = threadIdx.x; i < R * LP; i += blockDim.x) {
+      const int r = i / LP, l = i % LP;
       const int g = r / Sq, qi = r % Sq;
-      const int64_t row = ((b * Hq) + hkv * G + g) * Sq + qi;
-      bits &= valid;
-      if (prev_bits != nullptr) bits |= prev_bits[row * W + word];
-      out_bits[row * W + word] = bits;
+      // padding: all ones, which the zero padding of a key row never equals
+      qflat[i] = l < L ? qcodes[(((b * Hq) + hkv * G + g) * Sq + qi) * L + l] : (CodeT)~(CodeT)0;
+    }
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t word0 = ((int64_t)blockIdx.x * LSH_MATCH_WARPS + warp) * LSH_MATCH_WORDS;
+  if (word0 * 32 >= S) return;
+  const uint4* base = reinterpret_cast<const uint4*>(codes + bh * cap * LP);
+  for (int r0 = 0; r0 < R; r0 += 4) {
+    uint32_t mine[4] = {0u, 0u, 0u, 0u};  // lane j keeps word j of rows r0 .. r0 + 3
+#pragma unroll
+    for (int j = 0; j < LSH_MATCH_WORDS; ++j) {
+      const int64_t key = (word0 + j) * 32 + lane;
+      unsigned int hit[4] = {0u, 0u, 0u, 0u};
+      if (key < S) {
+        uint4 v[NC];
+#pragma unroll
+        for (int c = 0; c < NC; ++c) v[c] = __ldg(base + key * NC + c);
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            if (r0 + r < R) {
+              const uint4 q = qs[(r0 + r) * NC + c];
+              if (sizeof(CodeT) == 1)
+                hit[r] |= __vcmpeq4(v[c].x, q.x) | __vcmpeq4(v[c].y, q.y) | __vcmpeq4(v[c].z, q.z) |
+                          __vcmpeq4(v[c].w, q.w);
+              else
+                hit[r] |= __vcmpeq2(v[c].x, q.x) | __vcmpeq2(v[c].y, q.y) | __vcmpeq2(v[c].z, q.z) |
+                          __vcmpeq2(v[c].w, q.w);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const uint32_t wbits = __ballot_sync(0xffffffffu, hit[r] != 0u);
+        if (lane == j) mine[r] = wbits;
+      }
+    }
+    if (lane < LSH_MATCH_WORDS && (word0 + lane) * 32 < S) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        if (r0 + r < R) {
+          const int g = (r0 + r) / Sq, qi = (r0 + r) % Sq;
+          const int64_t row = ((b * Hq) + hkv * G + g) * Sq + qi;
+          uint32_t bits = mine[r];  // keys past S never set a bit
+          if (prev_bits != nullptr) bits |= prev_bits[row * W + word0 + lane];
+          out_bits[row * W + word0 + lane] = bits;
+        }
+      }
     }
   }
 }
 
-extern "C" int sah_lsh_match(const void* planes, int64_t cap, const void* qcodes, int B, int Hq,
+template <typename CodeT>
+static int lsh_match_launch(const void* codes, int64_t cap, const void* qcodes, int Hq, int Sq, int G, int L,
+                            int64_t S, int64_t W, const uint32_t* prev_bits, uint32_t* out_bits, dim3 grid,
+                            size_t smem, cudaStream_t st) {
+  const int nc = lsh_row_pitch<CodeT>(L) / (16 / (int)sizeof(CodeT));
+#define LSH_MATCH_CASE(NC)                                                                          \
+  case NC:                                                                                          \
+    lsh_match_kernel<CodeT, NC><<<grid, LSH_MATCH_WARPS * 32, smem, st>>>(                          \
+        reinterpret_cast<const CodeT*>(codes), cap, reinterpret_cast<const CodeT*>(qcodes), Hq, Sq, \
+        G, L, S, W, prev_bits, out_bits);                                                           \
+    break;
+  switch (nc) {
+    LSH_MATCH_CASE(1) LSH_MATCH_CASE(2) LSH_MATCH_CASE(3) LSH_MATCH_CASE(4) LSH_MATCH_CASE(5)
+    LSH_MATCH_CASE(6) LSH_MATCH_CASE(7) LSH_MATCH_CASE(8) LSH_MATCH_CASE(9) LSH_MATCH_CASE(10)
+    LSH_MATCH_CASE(11) LSH_MATCH_CASE(12) LSH_MATCH_CASE(13) LSH_MATCH_CASE(14) LSH_MATCH_CASE(15)
+    LSH_MATCH_CASE(16)
+    default:
+      return sah_fail(SAH_ERR_UNSUPPORTED, "lsh_match: %d tables exceed %d bytes per signature row", L,
+                      LSH_MAX_CHUNKS * 16);
+  }
+#undef LSH_MATCH_CASE
+  return SAH_OK;
+}
+
+extern "C" int sah_lsh_match(const void* codes, int64_t cap, const void* qcodes, int B, int Hq,
                              int Sq, int G, int L, int K, int64_t S, int64_t W,
-                             const uint32_t* prev_bits, uint32_t* out_bits, int sm_count,
-                             int* errflag, void* stream) {
-  SAH_REQUIRE(planes && qcodes && out_bits, "lsh_match: null pointer");
+                             const uint32_t* prev_bits, uint32_t* out_bits, void* stream) {
+  SAH_REQUIRE(codes && qcodes && out_bits, "lsh_match: null pointer");
   SAH_REQUIRE(G > 0 && Hq % G == 0 && L > 0 && K > 0 && S > 0 && W * 32 >= S, "lsh_match: bad shape");
-  SAH_REQUIRE(cap % 32 == 0 && cap >= S, "lsh_match: plane capacity must be a multiple of 32 keys");
+  SAH_REQUIRE(cap >= S && (uintptr_t)codes % 16 == 0, "lsh_match: signature rows must be 16-byte aligned");
   if (K > 16) return sah_fail(SAH_ERR_UNSUPPORTED, "lsh: lsh_k = %d > 16 bits per table is not built", K);
   const int csz = K <= 8 ? 1 : 2;
-  const size_t smem = (size_t)G * Sq * L * csz;
+  const int lp = csz == 1 ? lsh_row_pitch<uint8_t>(L) : lsh_row_pitch<uint16_t>(L);
+  const size_t smem = (size_t)G * Sq * lp * csz;
   if (smem > 48 * 1024) return sah_fail(SAH_ERR_UNSUPPORTED, "lsh_match: too many query rows per group");
   const int64_t words = (S + 31) / 32;
-  if (sm_count <= 0) sm_count = 148;
-  // a short key range (one rank's share of a sharded sequence) still gets a few CTAs per SM
-  int threads = 256;
-  const int64_t bh = (int64_t)B * (Hq / G);
-  while (threads > 64 && sah_ceil_div(words, threads) * bh < 4ll * sm_count) threads >>= 1;
-  dim3 grid((unsigned)sah_ceil_div(words, threads), (unsigned)bh);
+  dim3 grid((unsigned)sah_ceil_div(words, LSH_MATCH_WARPS * LSH_MATCH_WORDS), (unsigned)(B * (Hq / G)));
   cudaStream_t st = (cudaStream_t)stream;
   sah_prof_begin(SAH_PROF_LSH_MATCH, st);
-  if (csz == 1 && G * Sq <= 4 && L <= 128 && (uintptr_t)planes % 16 == 0) {
-    static bool allowed[64] = {};
-    const int smem_staged = LSHM_RING + 512 + 64;
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e == cudaSuccess && !(dev >= 0 && dev < 64 && allowed[dev])) {
-      e = cudaFuncSetAttribute(lsh_match_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_staged);
-      if (e == cudaSuccess && dev >= 0 && dev < 64) allowed[dev] = true;
-    }
-    if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "lsh_match attr: %s", cudaGetErrorString(e));
-    dim3 sgrid((unsigned)sah_ceil_div(S, LSHM_KEYS), (unsigned)bh);
-    lsh_match_staged_kernel<<<sgrid, LSHM_THREADS, smem_staged, st>>>(
-        reinterpret_cast<const uint8_t*>(planes), cap, reinterpret_cast<const uint8_t*>(qcodes), Hq, Sq, G, L,
-        S, W, prev_bits, out_bits, errflag);
-    SAH_LAUNCH_CHECK("lsh_match_staged");
-    sah_prof_end(SAH_PROF_LSH_MATCH, st);
-    return SAH_OK;
-  }
-  if (csz == 1)
-    lsh_match_kernel<uint8_t><<<grid, threads, smem, st>>>(reinterpret_cast<const uint8_t*>(planes), cap,
-                                                           reinterpret_cast<const uint8_t*>(qcodes), Hq, Sq,
-                                                           G, L, S, W, prev_bits, out_bits);
-  else
-    lsh_match_kernel<uint16_t><<<grid, threads, smem, st>>>(reinterpret_cast<const uint16_t*>(planes), cap,
-                                                            reinterpret_cast<const uint16_t*>(qcodes), Hq,
-                                                            Sq, G, L, S, W, prev_bits, out_bits);
+  const int rc = csz == 1 ? lsh_match_launch<uint8_t>(codes, cap, qcodes, Hq, Sq, G, L, S, W, prev_bits,
+                                                      out_bits, grid, smem, st)
+                          : lsh_match_launch<uint16_t>(codes, cap, qcodes, Hq, Sq, G, L, S, W, prev_bits,
+                                                       out_bits, grid, smem, st);
+  if (rc != SAH_OK) return rc;
   SAH_LAUNCH_CHECK("lsh_match");
   sah_prof_end(SAH_PROF_LSH_MATCH, st);
   return SAH_OK;

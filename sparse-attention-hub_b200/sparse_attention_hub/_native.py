@@ -88,13 +88,13 @@ _SIGNATURES = {
                       _P, _P, _P],
     "sah_masked_attention": [_P, _P, _P, _I, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _I, _I, _I,
                              _L, _I, c_float, _P, _L, _L, _L, _P, POINTER(AttnSizes), _P, _P, _P,
-                             _P, _P, _P, _P, _P, _P],
-    "sah_attn_merge_parts": [_P, _P, _I, _I, _I, _I, _I, _P, _I, _P, _P],
+                             _P, _P, _P, _P, _P],
+    "sah_attn_merge_parts": [_P, _I, _I, _I, _I, _I, _P, _I, _P, _P],
     "sah_attn_plan_lsh": [_P, _P, _P, _L, _P, _I, _I, _I, _I, _L, _L, POINTER(AttnSizes), _P, _P, _P,
                           _P, _P],
     "sah_masked_attention_lsh": [_P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _I, _I, _I, _L,
                                  _I, c_float, _P, _L, _L, _L, _P, POINTER(AttnSizes), _P, _P, _P, _P,
-                                 _P, _P, _P, _P, _P, _P, _P, _P, _P],
+                                 _P, _P, _P, _P, _P, _P, _P, _P],
     "sah_mask_unit_data": [_P, _P, _P, _P, _I, _L, _L, _P, _P],
     "sah_attn_gather_probe": [_P, _P, _L, _L, _L, _L, _L, _L, _I, _I, _I, _L, _I, POINTER(AttnSizes),
                               _P, _P, _P, _P],
@@ -117,7 +117,7 @@ _SIGNATURES = {
     "sah_lsh_key_stats": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _I, _P, _L, _P, _P, _I, _P],
     "sah_lsh_key_sign": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _I, _P, _P, _P, _P, _I, _I, _L, _P, _P],
     "sah_lsh_query": [_P, _I, _L, _L, _L, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P, _P, _P, _P, _P],
-    "sah_lsh_match": [_P, _L, _P, _I, _I, _I, _I, _I, _I, _L, _L, _P, _P, _I, _P, _P],
+    "sah_lsh_match": [_P, _L, _P, _I, _I, _I, _I, _I, _I, _L, _L, _P, _P, _P],
     "sah_lsh_key_den": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _I, _P, _P, _L, _P, _P, _P, _I, _P],
     "sah_lsh_prob": [_P, _I, _L, _L, _L, _I, _I, _I, _I, _I, _P, _P, _P, _L, _P, _P, _P, _P, _P, _L,
                      _I, _I, _P, _P, _I, _P],

@@ -447,24 +447,13 @@ def merge_native(a: Mask, b: Mask) -> Mask:
 
 
 # ---- bounded device-side waits ------------------------------------------------------
-_WAIT_FLAGS: dict = {}
-
-
-def wait_flag(device: torch.device) -> torch.Tensor:
-    """int32 [1] on `device`, zero until a kernel of the library gives up a bounded wait on its
-    copy pipeline (it then holds 1 and the result of that launch is incomplete)."""
-    key = str(device)
-    if key not in _WAIT_FLAGS:
-        _WAIT_FLAGS[key] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _WAIT_FLAGS[key]
-
-
 def wait_errors() -> int:
-    """Number of devices on which a bounded wait ran out since the flags were made (reads the
-    flags back: synchronises); also counts the attention kernels' own error words."""
+    """How many attention workspaces carry a set error word: a bounded wait of the tensor-map
+    copy stage ran out in some launch that used them and its result is incomplete (reads
+    device memory: synchronises)."""
     from .utils import mask_attention_utils as mau
 
-    return sum(int(t.item() != 0) for t in _WAIT_FLAGS.values()) + mau.attention_wait_errors()
+    return mau.attention_wait_errors()
 
 
 # ---- MagicPig ---------------------------------------------------------------------

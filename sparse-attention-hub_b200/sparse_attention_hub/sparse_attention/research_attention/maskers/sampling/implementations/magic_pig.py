@@ -14,7 +14,7 @@ the probability of that event, 1 - (1 - (1 - theta/pi)^k)^l, as its weight.
 
 The reference materialises signatures as int64 `[B, Hq, S, L]` and probabilities for
 every key.  Here the signatures of a layer live in a `PackedLSHSignatures`
-(one code per table and key, table-major, once per KV head), a match kernel streams
+(one code per table and key, key-major rows, once per KV head), a match kernel streams
 them, and probabilities are evaluated for matched keys only.
 
 In bfloat16 decode (at most four mask rows per KV group, previous mask empty or with unit
@@ -77,7 +77,8 @@ def _round_up(n: int, m: int) -> int:
 class PackedLSHSignatures:
     """LSH state of one layer's keys.
 
-    planes   uint8 (lsh_k <= 8) or int16 `[B, Hkv, L, capacity]`: code of key s for table l
+    codes    uint8 (lsh_k <= 8) or int16 `[B, Hkv, capacity, pitch]`: the L table codes of key s
+             in row s, zero-padded to `pitch` (L rounded up to a whole number of 16-byte chunks)
     norms    float32 `[B, Hkv, capacity]`: norm of the centred key (rounded to the key dtype)
     max_norm int32 `[1]`: float bits of the largest norm seen so far
     dens     float32 `[B, Hkv, capacity]`: norm of the transformed key + 1e-8 (a per-key constant
@@ -85,9 +86,10 @@ class PackedLSHSignatures:
     length   number of valid keys
     """
 
-    def __init__(self, planes: torch.Tensor, norms: torch.Tensor, max_norm: torch.Tensor,
-                 length: int, lsh_k: int) -> None:
-        self.planes, self.norms, self.max_norm, self.length, self.lsh_k = planes, norms, max_norm, length, lsh_k
+    def __init__(self, codes: torch.Tensor, norms: torch.Tensor, max_norm: torch.Tensor,
+                 length: int, lsh_k: int, lsh_l: int) -> None:
+        self.codes, self.norms, self.max_norm, self.length = codes, norms, max_norm, length
+        self.lsh_k, self.lsh_l = lsh_k, lsh_l
         self.dens = torch.zeros_like(norms)
         self.dens_max = torch.zeros_like(max_norm)
         # sequence-sharded use: total key count at which max_norm was last reduced over the shards
@@ -95,26 +97,31 @@ class PackedLSHSignatures:
 
     @property
     def capacity(self) -> int:
-        return self.planes.shape[-1]
+        return self.codes.shape[2]
 
     @property
     def shape(self) -> Tuple[int, ...]:
-        return (self.planes.shape[0], self.planes.shape[1], self.length, self.planes.shape[2])
+        return (self.codes.shape[0], self.codes.shape[1], self.length, self.lsh_l)
+
+    @staticmethod
+    def pitch(lsh_l: int, lsh_k: int) -> int:
+        per16 = 16 if lsh_k <= 8 else 8
+        return _round_up(lsh_l, per16)
 
     @classmethod
     def allocate(cls, B: int, Hkv: int, L: int, lsh_k: int, n_keys: int, device) -> "PackedLSHSignatures":
         cap = _round_up(n_keys + max(256, n_keys // 8), 32)
         code_dtype = torch.uint8 if lsh_k <= 8 else torch.int16
-        return cls(torch.zeros((B, Hkv, L, cap), dtype=code_dtype, device=device),
+        return cls(torch.zeros((B, Hkv, cap, cls.pitch(L, lsh_k)), dtype=code_dtype, device=device),
                    torch.zeros((B, Hkv, cap), dtype=torch.float32, device=device),
-                   torch.zeros(1, dtype=torch.int32, device=device), 0, lsh_k)
+                   torch.zeros(1, dtype=torch.int32, device=device), 0, lsh_k, L)
 
     def grown(self, n_keys: int) -> "PackedLSHSignatures":
         if n_keys <= self.capacity:
             return self
-        B, Hkv, L, _ = self.planes.shape
-        new = PackedLSHSignatures.allocate(B, Hkv, L, self.lsh_k, n_keys, self.planes.device)
-        new.planes[..., : self.length] = self.planes[..., : self.length]
+        B, Hkv = self.codes.shape[:2]
+        new = PackedLSHSignatures.allocate(B, Hkv, self.lsh_l, self.lsh_k, n_keys, self.codes.device)
+        new.codes[:, :, : self.length] = self.codes[:, :, : self.length]
         new.norms[..., : self.length] = self.norms[..., : self.length]
         new.max_norm.copy_(self.max_norm)
         new.dens[..., : self.length] = self.dens[..., : self.length]
@@ -125,11 +132,11 @@ class PackedLSHSignatures:
 
     def to_reference_layout(self, n_query_heads: int) -> torch.Tensor:
         """int64 `[B, Hq, length, L]`, the tensor the reference caches (magic_pig.py:120-150)."""
-        G = n_query_heads // self.planes.shape[1]
-        codes = self.planes[..., : self.length].to(torch.int64)
-        if self.planes.dtype == torch.int16:
+        G = n_query_heads // self.codes.shape[1]
+        codes = self.codes[:, :, : self.length, : self.lsh_l].to(torch.int64)
+        if self.codes.dtype == torch.int16:
             codes = codes & 0xFFFF
-        return codes.permute(0, 1, 3, 2).repeat_interleave(G, dim=1).contiguous()
+        return codes.repeat_interleave(G, dim=1).contiguous()
 
     @classmethod
     def from_reference_layout(cls, sig: torch.Tensor, n_kv_heads: int, lsh_k: int) -> "PackedLSHSignatures":
@@ -138,7 +145,7 @@ class PackedLSHSignatures:
         B, Hq, S, L = sig.shape
         G = Hq // n_kv_heads
         new = cls.allocate(B, n_kv_heads, L, lsh_k, S, sig.device)
-        new.planes[..., :S] = sig[:, ::G].permute(0, 1, 3, 2).to(new.planes.dtype)
+        new.codes[:, :, :S, :L] = sig[:, ::G].to(new.codes.dtype)
         return new
 
 
@@ -280,7 +287,7 @@ class MagicPig(SamplingMasker):
             _native.check(
                 lib.sah_lsh_key_sign(*kargs, s0, S, D, _native.ptr(mean), handle.norms.data_ptr(),
                                      handle.max_norm.data_ptr(), proj.data_ptr(), self.lsh_l, self.lsh_k,
-                                     handle.capacity, handle.planes.data_ptr(), st), "sah_lsh_key_sign")
+                                     handle.capacity, handle.codes.data_ptr(), st), "sah_lsh_key_sign")
             handle.length = S
         if S > s_new0 or resync or adopted:
             # per-key constants of the probability formula: the new keys, or every key when
@@ -327,7 +334,7 @@ class MagicPig(SamplingMasker):
         if fused and not previous_mask.is_empty:
             prev_nb = _native_ops.unit_weight_bits(previous_mask)
             fused = prev_nb is not None
-        qcodes = torch.empty((rows, self.lsh_l), dtype=sig.planes.dtype, device=dev)
+        qcodes = torch.empty((rows, self.lsh_l), dtype=sig.codes.dtype, device=dev)
         qunit = torch.empty((rows, D), dtype=torch.float32, device=dev)
         qhat = torch.empty((rows, D), dtype=dtype, device=dev) if fused else None
         qmu = torch.empty(rows, dtype=torch.float32, device=dev) if fused else None
@@ -338,9 +345,8 @@ class MagicPig(SamplingMasker):
                               st), "sah_lsh_query")
         bits = torch.empty((rows, W), dtype=torch.int32, device=dev)
         _native.check(
-            lib.sah_lsh_match(sig.planes.data_ptr(), sig.capacity, qcodes.data_ptr(), B, Hq, Sq, G,
-                              self.lsh_l, self.lsh_k, S, W, None, bits.data_ptr(),
-                              _native.sm_count(dev), _native_ops.wait_flag(dev).data_ptr(), st),
+            lib.sah_lsh_match(sig.codes.data_ptr(), sig.capacity, qcodes.data_ptr(), B, Hq, Sq, G,
+                              self.lsh_l, self.lsh_k, S, W, None, bits.data_ptr(), st),
             "sah_lsh_match")
         if W * 32 > (S + 31) // 32 * 32:
             bits[:, (S + 31) // 32:].zero_()  # padding words of the row stride

@@ -172,10 +172,8 @@ class SequenceShardedAttention:
             # every rank takes part in the maskers' reductions, so none may sit a step out
             raise ValueError("a rank of a sequence-sharded call must hold at least one key")
         mask = self.build_mask(queries, keys, values, local_bias, scaling, dropout, meta, **kwargs)
-        _, acc, lse = native_masked_attention(queries, keys, values, local_bias, None, scaling,
-                                              mask, return_partials=True)
-        part = torch.cat([acc, lse], dim=1)
+        _, part = native_masked_attention(queries, keys, values, local_bias, None, scaling,
+                                          mask, return_partials=True)
         gathered = self.comm.all_gather(part)  # [world, rows, D + 2]
-        out = merge_attention_partials(gathered[..., :D], gathered[..., D:], B, Hq, Sq,
-                                       queries.dtype, sinks)
+        out = merge_attention_partials(gathered, B, Hq, Sq, queries.dtype, sinks)
         return out, None

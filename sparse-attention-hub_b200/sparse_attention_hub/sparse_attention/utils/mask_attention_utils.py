@@ -86,9 +86,9 @@ def native_masked_attention(
 ):
     """Run plan + gather attention; returns `out [B, Sq, Hq, D]` in the query dtype.
 
-    With `return_partials=True` also returns the unnormalised fp32 accumulator
-    `[rows, D]` and `(max, denominator)` `[rows, 2]` of every mask row, which is
-    what a sequence-sharded caller all-gathers and merges.
+    With `return_partials=True` also returns a float32 `[rows, D + 2]` tensor: per mask row
+    the unnormalised accumulator, the running maximum and the denominator, which is what a
+    sequence-sharded caller all-gathers (one buffer, one collective) and merges.
     """
     _native.require_cuda(queries, "queries")
     _native.require_cuda(keys, "keys")
@@ -146,8 +146,7 @@ def native_masked_attention(
         sink_t = sinks.to(device=dev, dtype=torch.float32).contiguous()
     out = torch.empty((B, Sq, Hq, D), dtype=dtype, device=dev)
     rows = B * Hq * Sq
-    acc = torch.empty((rows, D), dtype=torch.float32, device=dev) if return_partials else None
-    lse = torch.empty((rows, 2), dtype=torch.float32, device=dev) if return_partials else None
+    part = torch.empty((rows, D + 2), dtype=torch.float32, device=dev) if return_partials else None
     strides = (q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
                v.stride(0), v.stride(1), v.stride(2))
     try:
@@ -171,7 +170,7 @@ def native_masked_attention(
                     ws["ucols"].data_ptr(), ws["umemb"].data_ptr(), ws["uw"].data_ptr(),
                     ws["ucount"].data_ptr(), ws["partial"].data_ptr(), payload.qhat.data_ptr(),
                     payload.qmu.data_ptr(), payload.table.data_ptr(), out.data_ptr(),
-                    _native.ptr(acc), _native.ptr(lse), _native.ptr(dump), st),
+                    _native.ptr(part), _native.ptr(dump), st),
                 "sah_masked_attention_lsh")
         else:
             _native.check(
@@ -187,7 +186,7 @@ def native_masked_attention(
                     _native.ptr(sink_t), ctypes.byref(sizes), ws["ucols"].data_ptr(),
                     ws["umemb"].data_ptr(), _native.ptr(ws["uw"]) if has_data else None,
                     ws["ucount"].data_ptr(), ws["partial"].data_ptr(), out.data_ptr(),
-                    _native.ptr(acc), _native.ptr(lse), st),
+                    _native.ptr(part), st),
                 "sah_masked_attention")
     except Exception:
         # a refused launch may leave the merge tickets of this scratch non-zero
@@ -199,7 +198,7 @@ def native_masked_attention(
     _last_plan["sizes"] = (sizes.groups, sizes.rows_per_group, S)
     _last_plan["attn_sizes"] = sizes
     if return_partials:
-        return out, acc, lse
+        return out, part
     return out
 
 
@@ -255,23 +254,24 @@ def gather_probe(keys: torch.Tensor, values: torch.Tensor, seq_len_queries: int 
         "sah_attn_gather_probe")
 
 
-def merge_attention_partials(acc: torch.Tensor, lse: torch.Tensor, batch: int, heads: int,
-                             seq_len_queries: int, dtype: torch.dtype,
-                             sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Combine `[parts, rows, D]` accumulators and `[parts, rows, 2]` (max, denominator)."""
-    _native.require_cuda(acc, "acc")
+def merge_attention_partials(parts: torch.Tensor, batch: int, heads: int, seq_len_queries: int,
+                             dtype: torch.dtype, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Combine `[n_parts, rows, D + 2]` partials (accumulator, max, denominator per row) of
+    `native_masked_attention(..., return_partials=True)` over disjoint key ranges."""
+    _native.require_cuda(parts, "parts")
     lib = _native.load()
-    parts, rows, D = acc.shape
-    dev = acc.device
+    n_parts, rows, ld = parts.shape
+    D = ld - 2
+    dev = parts.device
     out = torch.empty((batch, seq_len_queries, heads, D), dtype=dtype, device=dev)
     sink_t = None if sinks is None else sinks.to(device=dev, dtype=torch.float32).contiguous()
-    # named, so that the copies outlive the launch (a temporary would be freed, and its memory
+    # named, so that a copy outlives the launch (a temporary would be freed, and its memory
     # handed to the next allocation, as soon as its address had been read)
-    acc_c, lse_c = acc.contiguous(), lse.contiguous()
+    parts_c = parts.contiguous()
     _native.check(
-        lib.sah_attn_merge_parts(acc_c.data_ptr(), lse_c.data_ptr(), parts,
-                                 batch, heads, seq_len_queries, D, _native.ptr(sink_t),
-                                 _native.dtype_code(dtype), out.data_ptr(), _native.stream_of(dev)),
+        lib.sah_attn_merge_parts(parts_c.data_ptr(), n_parts, batch, heads, seq_len_queries, D,
+                                 _native.ptr(sink_t), _native.dtype_code(dtype), out.data_ptr(),
+                                 _native.stream_of(dev)),
         "sah_attn_merge_parts")
     return out
 

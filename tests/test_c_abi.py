@@ -42,7 +42,7 @@ def test_bad_arguments_return_a_status_and_a_message():
     assert lib.sah_mask_fill_band(None, 1, 1, 32, 1, 0, 0, 1, 0, 1, None) == 1
     assert b"null" in lib.sah_last_error()
     assert lib.sah_hash_topk(None, 0, None, 32, None, 1, 0, 0, 0, 1, 1, 1, 32, 1, None, 1, None, None) == 1
-    assert lib.sah_lsh_match(None, 32, None, 1, 4, 1, 4, 5, 4, 32, 1, None, None, 148, None, None) == 1
+    assert lib.sah_lsh_match(None, 32, None, 1, 4, 1, 4, 5, 4, 32, 1, None, None, None) == 1
     with pytest.raises(_native.NativeLibraryError):
         _native.check(1, "sah_lsh_match")
     with pytest.raises(NotImplementedError):

@@ -163,7 +163,7 @@ def _magicpig_against_chunked_oracle(S, sampled, seed, sharded_world=0):
             return
         np.testing.assert_array_equal(dense[..., c0:c1] != 0, ref != 0, err_msg=f"index set, keys {c0}:{c1}")
         np.testing.assert_array_equal(dense[..., c0:c1], ref, err_msg=f"weights, keys {c0}:{c1}")
-        got = meta["key_signature"][0].planes[:, :, :, c0:c1].permute(0, 1, 3, 2).cpu().numpy()
+        got = meta["key_signature"][0].codes[:, :, c0:c1, :75].cpu().numpy()
         np.testing.assert_array_equal(got.astype(np.int64), codes, err_msg=f"key codes, keys {c0}:{c1}")
         checked.append(c0)
 

@@ -271,18 +271,20 @@ def test_partials_merge_equals_single_pass():
     dense = (rng.random((1, 8, 1, 1024)) < 0.1).astype(np.float32)
     full = Mask.create_mask_from_dense_mask(dense.shape, torch.from_numpy(dense).to(DEV), torch.float32)
     want = native_masked_attention(tq, tk, tv, None, None, float(wl.scaling), full)
-    accs, lses = [], []
+    parts = []
     for lo, hi in ((0, 512), (512, 1024)):
         part = Mask.create_mask_from_dense_mask((1, 8, 1, hi - lo),
                                                 torch.from_numpy(dense[..., lo:hi].copy()).to(DEV),
                                                 torch.float32)
-        _, acc, lse = native_masked_attention(tq, tk[:, :, lo:hi].contiguous(),
-                                              tv[:, :, lo:hi].contiguous(), None, None,
-                                              float(wl.scaling), part, return_partials=True)
-        accs.append(acc)
-        lses.append(lse)
-    got = merge_attention_partials(torch.stack(accs), torch.stack(lses), 1, 8, 1, torch.float32)
+        _, p = native_masked_attention(tq, tk[:, :, lo:hi].contiguous(),
+                                       tv[:, :, lo:hi].contiguous(), None, None,
+                                       float(wl.scaling), part, return_partials=True)
+        parts.append(p)
+    got = merge_attention_partials(torch.stack(parts), 1, 8, 1, torch.float32)
     _close(got.cpu().numpy(), want.cpu().numpy(), "f32")
+    # and the restatement's dense computation over all keys
+    ref = o_attention.masked_attention(wl.q, wl.k, wl.v, dense, wl.scaling, "f32")
+    _close(got.cpu().numpy(), ref, "f32")
 
 
 def test_hash_topk_degenerate_score_distributions():
