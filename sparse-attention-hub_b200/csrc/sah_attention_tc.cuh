@@ -44,6 +44,7 @@
 #endif
 #define ATM_THREADS (ATM_WARPS * 32)
 #define ATM_TILE 16
+#define ATM_MIN_TILES 8  // tiles a warp should have before a further CTA joins the group
 #define ATM_SPIN_LIMIT (1 << 19)
 
 struct AtmMaps {
@@ -215,9 +216,15 @@ masked_attention_mma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, in
   const float* ginv = LSHW ? a.uw + g * a.S : nullptr;  // 1 / (M * |transformed key|) per entry
 
   // ---- this warp's tiles ----
+  // The grid holds nsplit CTAs per group, sized for long lists.  A short list is shared by
+  // fewer of them, so that every warp still has a run of tiles to pipeline and the last CTA
+  // merges few partials; the others leave at once (they hold no ticket).
   const int U = a.ucount[g];
   const int total_tiles = (U + ATM_TILE - 1) / ATM_TILE;
-  const int lanes_total = a.nsplit * ATM_WARPS;   // warps sharing the group
+  int active = (total_tiles + ATM_WARPS * ATM_MIN_TILES - 1) / (ATM_WARPS * ATM_MIN_TILES);
+  active = active < 1 ? 1 : (active > a.nsplit ? a.nsplit : active);
+  if (split >= active) return;
+  const int lanes_total = active * ATM_WARPS;     // warps sharing the group
   const int my_first = split * ATM_WARPS + warp;  // tile t of this warp = my_first + t * lanes_total
   const int my_tiles =
       (total_tiles > my_first) ? (total_tiles - my_first + lanes_total - 1) / lanes_total : 0;
@@ -609,7 +616,7 @@ masked_attention_mma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, in
   __syncthreads();
   if (tid == 0) {
     const int old = atomicAdd(&tickets[g], 1);
-    const int last = (old == a.nsplit - 1);
+    const int last = (old == active - 1);
     if (last) tickets[g] = 0;  // ready for the next call
     is_last_sm = last;
   }
@@ -621,18 +628,18 @@ masked_attention_mma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, in
   // phase 1: one warp per row finds the row maximum, the per-split rescale
   // factors and the denominator (ring memory reused as scratch)
   float* sc_sm = reinterpret_cast<float*>(atm_smem);  // [R][nsplit]
-  float* ml_sm = sc_sm + 16 * a.nsplit;               // [R][2]
+  float* ml_sm = sc_sm + 16 * active;                 // [R][2]
   for (int r = warp; r < a.R; r += ATM_WARPS) {
     const float* pr = p0 + (int64_t)r * (D + 2);
     float mloc = -INFINITY;
-    for (int s2 = lane; s2 < a.nsplit; s2 += 32) mloc = fmaxf(mloc, __ldcg(pr + s2 * pstride + D));
+    for (int s2 = lane; s2 < active; s2 += 32) mloc = fmaxf(mloc, __ldcg(pr + s2 * pstride + D));
 #pragma unroll
     for (int of = 16; of > 0; of >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, of));
     float lsum = 0.f;
-    for (int s2 = lane; s2 < a.nsplit; s2 += 32) {
+    for (int s2 = lane; s2 < active; s2 += 32) {
       const float ms = __ldcg(pr + s2 * pstride + D);
       const float sc = (ms == -INFINITY) ? 0.f : __expf(ms - mloc);
-      sc_sm[r * a.nsplit + s2] = sc;
+      sc_sm[r * active + s2] = sc;
       lsum += __ldcg(pr + s2 * pstride + D + 1) * sc;
     }
 #pragma unroll
@@ -651,10 +658,10 @@ masked_attention_mma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, in
     if (qi >= a.Sq) continue;
     const int h = kvh * a.G + gi;
     const float* pr = p0 + (int64_t)r * (D + 2) + d;
-    const float* sc = sc_sm + r * a.nsplit;
+    const float* sc = sc_sm + r * active;
     float accv = 0.f;
 #pragma unroll 8
-    for (int s2 = 0; s2 < a.nsplit; ++s2) accv = fmaf(__ldcg(pr + s2 * pstride), sc[s2], accv);
+    for (int s2 = 0; s2 < active; ++s2) accv = fmaf(__ldcg(pr + s2 * pstride), sc[s2], accv);
     const float M = ml_sm[r * 2], L = ml_sm[r * 2 + 1];
     float Mx = M, sink_term = 0.f;
     if (sinks != nullptr) {
@@ -696,7 +703,10 @@ attention_gather_probe_kernel(AttnArgs a, unsigned int* __restrict__ sink) {
   const int32_t* gcols = a.ucols + g * a.S;
   const int U = a.ucount[g];
   const int total_tiles = (U + ATM_TILE - 1) / ATM_TILE;
-  const int lanes_total = a.nsplit * ATM_WARPS;
+  int active = (total_tiles + ATM_WARPS * ATM_MIN_TILES - 1) / (ATM_WARPS * ATM_MIN_TILES);
+  active = active < 1 ? 1 : (active > a.nsplit ? a.nsplit : active);
+  if (split >= active) return;
+  const int lanes_total = active * ATM_WARPS;
   const int my_first = split * ATM_WARPS + warp;
   const int my_tiles =
       (total_tiles > my_first) ? (total_tiles - my_first + lanes_total - 1) / lanes_total : 0;

@@ -383,11 +383,14 @@ extern "C" int sah_lsh_query(const void* q, int dtype, int64_t qs_b, int64_t qs_
 // match: any table code equal
 // ---------------------------------------------------------------------------------------
 // One thread per key: it loads the key's signature row (a few 16-byte loads, all requested
-// before the first compare) and compares it byte-wise (or halfword-wise) with the signature
-// rows of the group's queries, which sit in shared memory padded with a value no key row
-// holds in its padding.  A warp covers 32 consecutive keys, so a ballot of "some table code
-// equal" is the bitmap word of those keys; every warp does four such words and writes them
-// side by side.
+// before the first compare) and tests it against the signature rows of the group's queries,
+// which sit in shared memory padded with a value no key row holds in its padding.  "Some
+// table code equal" is "some byte (halfword) of key XOR query is zero": with x = key ^ query,
+// (x - 0x01..01) & ~x & 0x80..80 is non-zero exactly when x has a zero byte (a borrow can only
+// start at a zero byte, so the test of the whole word is exact even though single positions
+// above a zero byte are not), three integer instructions per word and query row.  A warp
+// covers 32 consecutive keys, so a ballot of the result is the bitmap word of those keys;
+// every warp does four such words and writes them side by side.
 #define LSH_MATCH_WARPS 8
 #define LSH_MATCH_WORDS 4
 #define LSH_MAX_CHUNKS 16  // 16-byte chunks per signature row (256 byte codes, 128 halfword codes)
@@ -435,12 +438,13 @@ lsh_match_kernel(const CodeT* __restrict__ codes, int64_t cap, const CodeT* __re
           for (int r = 0; r < 4; ++r) {
             if (r0 + r < R) {
               const uint4 q = qs[(r0 + r) * NC + c];
-              if (sizeof(CodeT) == 1)
-                hit[r] |= __vcmpeq4(v[c].x, q.x) | __vcmpeq4(v[c].y, q.y) | __vcmpeq4(v[c].z, q.z) |
-                          __vcmpeq4(v[c].w, q.w);
-              else
-                hit[r] |= __vcmpeq2(v[c].x, q.x) | __vcmpeq2(v[c].y, q.y) | __vcmpeq2(v[c].z, q.z) |
-                          __vcmpeq2(v[c].w, q.w);
+              constexpr uint32_t ONES = sizeof(CodeT) == 1 ? 0x01010101u : 0x00010001u;
+              constexpr uint32_t HIGH = sizeof(CodeT) == 1 ? 0x80808080u : 0x80008000u;
+              const uint32_t x0 = v[c].x ^ q.x, x1 = v[c].y ^ q.y, x2 = v[c].z ^ q.z, x3 = v[c].w ^ q.w;
+              const uint32_t z0 = (x0 - ONES) & ~x0 & HIGH, z1 = (x1 - ONES) & ~x1 & HIGH;
+              const uint32_t z2 = (x2 - ONES) & ~x2 & HIGH, z3 = (x3 - ONES) & ~x3 & HIGH;
+              hit[r] |= z0 | z1;
+              hit[r] |= z2 | z3;
             }
           }
         }
