@@ -145,6 +145,21 @@ int sah_mask_unit_data(const uint32_t* bits, const uint32_t* unit_bits, const in
                        const int64_t* ptr, int dtype, int64_t rows, int64_t W, void* data,
                        void* stream);
 
+/* Mask.create_from_row_wise_idx, dense mode (utils/mask.py:335-395): dense[row][idx[row][j]] =
+ * vals[row][j] for idx int64 [rows][k], vals [rows][k] in `dtype`; every other position 0; of
+ * several j with the same column the last one wins, as the sequential scatter of the CPU
+ * reference does.  claims: device scratch of rows * S * 8 bytes (zeroed by the call). */
+int sah_mask_rowwise_scatter(const int64_t* idx, const void* vals, int dtype, int64_t rows, int64_t k,
+                             int64_t S, void* claims, void* dense, void* stream);
+
+/* Mask.merge_mask_sparse (utils/mask.py:893-1062) in two steps: sah_mask_flat_add adds the
+ * values of an index list (flat int64 indices row * S + col, values in `dtype`, NULL = ones)
+ * into acc, float32 [total] zeroed by the caller -- once per operand -- and
+ * sah_mask_clamp_to_dense rounds every sum to `dtype` and clamps it to [0, 1]. */
+int sah_mask_flat_add(const int64_t* flat_idx, const void* vals, int dtype, int64_t n, int64_t total,
+                      float* acc, void* stream);
+int sah_mask_clamp_to_dense(const float* acc, int dtype, int64_t total, void* dense, void* stream);
+
 /* Scatter a ragged list of sampled columns into a bitmap.  sample j belongs
  * to the row r with sptr[r] <= j < sptr[r+1] (sptr int64 [rows+1], device);
  * cols int64 [n].  Duplicates collapse, as the dense conversion of the
@@ -511,9 +526,9 @@ int sah_pq_update(const void* x, int dtype, int64_t xs_b, int64_t xs_h, int64_t 
  * ascending sub-vector order and rounded once (_compute_pq_scores,
  * pq_top_k.py:406-490).  centroids here are in `dtype`:
  * [B][Hkv][n_sub][n_cent][sub_d].  Columns outside the clustered region are not
- * written.  scores is [rows][S] in `dtype`.  The tables are built once per call in
- * `workspace` (16-byte aligned device memory of sah_pq_scores_ws_bytes(...) bytes;
- * SAH_ERR_WORKSPACE when smaller) and streamed from shared memory. */
+ * written.  scores is [rows][S] in `dtype`.  Every CTA builds the tables of its rows
+ * in shared memory and scores a contiguous key range; `workspace` is not used any more
+ * (NULL is accepted; sah_pq_scores_ws_bytes stays for callers that size one). */
 int64_t sah_pq_scores_ws_bytes(int B, int Hq, int Hkv, int Sq, int n_sub, int n_cent);
 int sah_pq_scores(const void* q, int dtype, int64_t qs_b, int64_t qs_h, int64_t qs_q,
                   const void* centroids, const uint8_t* codes, int64_t cap, int B, int Hq, int Hkv,

@@ -52,3 +52,31 @@ def to_csr(mask: np.ndarray):
     counts = np.count_nonzero(mask.reshape(-1, S), axis=1)
     ptr = np.concatenate([[0], np.cumsum(counts)]).astype(np.int64)
     return idx, ptr, flat[idx].astype(np.float32)
+
+
+def from_row_wise_idx(shape, row_idx: np.ndarray, row_vals: np.ndarray) -> np.ndarray:
+    """Mask.create_from_row_wise_idx, dense mode (utils/mask.py:335-395): each row's values are
+    scattered to its columns; of several entries naming one column the last one stays."""
+    S = shape[-1]
+    idx = np.asarray(row_idx).reshape(-1, row_idx.shape[-1])
+    vals = np.asarray(row_vals, dtype=np.float32).reshape(idx.shape)
+    out = np.zeros((idx.shape[0], S), dtype=np.float32)
+    for r in range(idx.shape[0]):
+        for j in range(idx.shape[1]):
+            out[r, idx[r, j]] = vals[r, j]
+    return out.reshape(shape)
+
+
+def merge_sparse(a: np.ndarray, b: np.ndarray, dtype: str):
+    """Mask.merge_mask_sparse (utils/mask.py:893-1062) for two index-form masks given densely:
+    the entries of both are concatenated, sorted by flat index, duplicates summed in the mask
+    dtype and clamped to [0, 1]; every index either operand stored stays stored.  Returns the
+    CSR triple of the result."""
+    S = a.shape[-1]
+    fa, fb = a.reshape(-1), b.reshape(-1)
+    stored = (fa != 0) | (fb != 0)
+    idx = np.flatnonzero(stored).astype(np.int64)
+    data = np.clip(round_to(fa[idx] + fb[idx], dtype), 0.0, 1.0).astype(np.float32)
+    counts = stored.reshape(-1, S).sum(axis=1)
+    ptr = np.concatenate([[0], np.cumsum(counts)]).astype(np.int64)
+    return idx, ptr, data

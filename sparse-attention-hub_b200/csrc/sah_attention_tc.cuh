@@ -44,7 +44,8 @@
 #endif
 #define ATM_THREADS (ATM_WARPS * 32)
 #define ATM_TILE 16
-#define ATM_MIN_TILES 8  // tiles a warp should have before a further CTA joins the group
+#define ATM_MIN_TILES 8        // tiles a warp should have before a further CTA joins the group
+#define ATM_ONE_WAVE_TILES 48  // below this many tiles per warp, one wave of CTAs instead of two
 #define ATM_SPIN_LIMIT (1 << 19)
 
 struct AtmMaps {
@@ -135,6 +136,19 @@ __device__ __forceinline__ void atm_cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
 }
 
+// CTAs that share one group's union list.  The grid holds nsplit per group, which is two waves
+// of the device for long lists (the second wave evens out groups of different length).  A list
+// that would give a warp fewer than ATM_ONE_WAVE_TILES tiles in that arrangement is worked on
+// by half of them -- one wave, half as many pipeline fills and partials -- and a short list by
+// as few as give every warp ATM_MIN_TILES tiles; the others leave at once (they hold no ticket).
+__device__ __forceinline__ int atm_active_splits(int total_tiles, int nsplit) {
+  int active = nsplit;
+  if (nsplit >= 2 && total_tiles < nsplit * ATM_WARPS * ATM_ONE_WAVE_TILES) active = (nsplit + 1) / 2;
+  const int by_length = (total_tiles + ATM_WARPS * ATM_MIN_TILES - 1) / (ATM_WARPS * ATM_MIN_TILES);
+  if (by_length < active) active = by_length;
+  return active < 1 ? 1 : active;
+}
+
 template <int D, bool TMA = false, int NST = ATM_STAGES>
 struct AtmCfg {
   static constexpr int ROWB = D * 2;                        // bytes of one bf16 row
@@ -216,13 +230,9 @@ masked_attention_mma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, in
   const float* ginv = LSHW ? a.uw + g * a.S : nullptr;  // 1 / (M * |transformed key|) per entry
 
   // ---- this warp's tiles ----
-  // The grid holds nsplit CTAs per group, sized for long lists.  A short list is shared by
-  // fewer of them, so that every warp still has a run of tiles to pipeline and the last CTA
-  // merges few partials; the others leave at once (they hold no ticket).
   const int U = a.ucount[g];
   const int total_tiles = (U + ATM_TILE - 1) / ATM_TILE;
-  int active = (total_tiles + ATM_WARPS * ATM_MIN_TILES - 1) / (ATM_WARPS * ATM_MIN_TILES);
-  active = active < 1 ? 1 : (active > a.nsplit ? a.nsplit : active);
+  const int active = atm_active_splits(total_tiles, a.nsplit);
   if (split >= active) return;
   const int lanes_total = active * ATM_WARPS;     // warps sharing the group
   const int my_first = split * ATM_WARPS + warp;  // tile t of this warp = my_first + t * lanes_total
@@ -703,8 +713,7 @@ attention_gather_probe_kernel(AttnArgs a, unsigned int* __restrict__ sink) {
   const int32_t* gcols = a.ucols + g * a.S;
   const int U = a.ucount[g];
   const int total_tiles = (U + ATM_TILE - 1) / ATM_TILE;
-  int active = (total_tiles + ATM_WARPS * ATM_MIN_TILES - 1) / (ATM_WARPS * ATM_MIN_TILES);
-  active = active < 1 ? 1 : (active > a.nsplit ? a.nsplit : active);
+  const int active = atm_active_splits(total_tiles, a.nsplit);
   if (split >= active) return;
   const int lanes_total = active * ATM_WARPS;
   const int my_first = split * ATM_WARPS + warp;

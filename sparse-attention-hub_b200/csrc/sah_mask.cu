@@ -486,6 +486,116 @@ extern "C" int sah_mask_unit_data(const uint32_t* bits, const uint32_t* unit_bit
   return SAH_OK;
 }
 
+// ---- row-wise column lists -> dense, last duplicate wins -----------------------------------------
+// Mask.create_from_row_wise_idx in dense mode (utils/mask.py:335-395) scatters data[row][j] to
+// dense[row][idx[row][j]]; on the CPU the last duplicate of a column wins.  Here every (row, j)
+// claims its column with an atomic maximum of (j + 1, value bits), so the winner is the same
+// whatever order the threads run in; a second pass turns the claims into the dense tensor.
+template <typename T>
+__device__ __forceinline__ unsigned int mask_value_bits(T v);
+template <>
+__device__ __forceinline__ unsigned int mask_value_bits<float>(float v) { return __float_as_uint(v); }
+template <>
+__device__ __forceinline__ unsigned int mask_value_bits<__nv_bfloat16>(__nv_bfloat16 v) {
+  return (unsigned int)__bfloat16_as_ushort(v);
+}
+template <typename T>
+__device__ __forceinline__ T mask_value_from_bits(unsigned int b);
+template <>
+__device__ __forceinline__ float mask_value_from_bits<float>(unsigned int b) { return __uint_as_float(b); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 mask_value_from_bits<__nv_bfloat16>(unsigned int b) {
+  return __ushort_as_bfloat16((unsigned short)b);
+}
+
+template <typename T>
+__global__ void mask_rowwise_claim_kernel(const int64_t* __restrict__ idx, const T* __restrict__ vals,
+                                          int64_t rows, int64_t k, int64_t S,
+                                          unsigned long long* __restrict__ claims) {
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= rows * k) return;
+  const int64_t row = t / k, j = t - row * k;
+  const int64_t col = idx[t];
+  if (col < 0 || col >= S) return;
+  atomicMax(&claims[row * S + col],
+            ((unsigned long long)(j + 1) << 32) | (unsigned long long)mask_value_bits<T>(vals[t]));
+}
+
+template <typename T>
+__global__ void mask_rowwise_settle_kernel(const unsigned long long* __restrict__ claims, int64_t n,
+                                           T* __restrict__ dense) {
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n) return;
+  const unsigned long long c = claims[t];
+  dense[t] = c ? mask_value_from_bits<T>((unsigned int)(c & 0xffffffffull)) : sah_from_float<T>(0.f);
+}
+
+extern "C" int sah_mask_rowwise_scatter(const int64_t* idx, const void* vals, int dtype, int64_t rows,
+                                        int64_t k, int64_t S, void* claims, void* dense, void* stream) {
+  SAH_REQUIRE(idx && vals && claims && dense, "rowwise_scatter: null pointer");
+  SAH_REQUIRE(rows >= 0 && k > 0 && S > 0 && k < (1ll << 31), "rowwise_scatter: bad extents");
+  if (rows == 0) return SAH_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e = cudaMemsetAsync(claims, 0, (size_t)(rows * S) * sizeof(unsigned long long), st);
+  if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "rowwise_scatter: memset: %s", cudaGetErrorString(e));
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    mask_rowwise_claim_kernel<T><<<(unsigned)sah_ceil_div(rows * k, 256), 256, 0, st>>>(
+        idx, (const T*)vals, rows, k, S, (unsigned long long*)claims);
+    SAH_LAUNCH_CHECK("mask_rowwise_claim");
+    mask_rowwise_settle_kernel<T><<<(unsigned)sah_ceil_div(rows * S, 256), 256, 0, st>>>(
+        (const unsigned long long*)claims, rows * S, (T*)dense);
+  });
+  SAH_LAUNCH_CHECK("mask_rowwise_settle");
+  return SAH_OK;
+}
+
+// ---- index-form merge: sum of duplicates, clamp -------------------------------------------------
+// Mask.merge_mask_sparse (utils/mask.py:893-1062) concatenates the two index lists, sorts them,
+// sums the values of equal indices and clamps to [0, 1].  The sums are taken here in a float32
+// array over all positions (atomic adds: exact for the one or two terms a position normally
+// gets, order-independent up to float32 rounding beyond that), then clamped and rounded once.
+template <typename T>
+__global__ void mask_flat_add_kernel(const int64_t* __restrict__ flat, const T* __restrict__ vals,
+                                     int64_t n, int64_t total, float* __restrict__ acc) {
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n) return;
+  const int64_t i = flat[t];
+  if (i < 0 || i >= total) return;
+  atomicAdd(&acc[i], vals ? sah_to_float<T>(vals[t]) : 1.f);
+}
+
+template <typename T>
+__global__ void mask_clamp_kernel(const float* __restrict__ acc, int64_t total, T* __restrict__ dense) {
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= total) return;
+  const float v = sah_round_to<T>(acc[t]);  // the sum lives in the mask dtype
+  dense[t] = sah_from_float<T>(fminf(fmaxf(v, 0.f), 1.f));
+}
+
+extern "C" int sah_mask_flat_add(const int64_t* flat_idx, const void* vals, int dtype, int64_t n,
+                                 int64_t total, float* acc, void* stream) {
+  SAH_REQUIRE(acc != nullptr && n >= 0 && total > 0, "flat_add: bad argument");
+  if (n == 0) return SAH_OK;
+  SAH_REQUIRE(flat_idx != nullptr, "flat_add: indices are null");
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    mask_flat_add_kernel<T><<<(unsigned)sah_ceil_div(n, 256), 256, 0, (cudaStream_t)stream>>>(
+        flat_idx, (const T*)vals, n, total, acc);
+  });
+  SAH_LAUNCH_CHECK("mask_flat_add");
+  return SAH_OK;
+}
+
+extern "C" int sah_mask_clamp_to_dense(const float* acc, int dtype, int64_t total, void* dense,
+                                       void* stream) {
+  SAH_REQUIRE(acc && dense && total > 0, "clamp_to_dense: bad argument");
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    mask_clamp_kernel<T><<<(unsigned)sah_ceil_div(total, 256), 256, 0, (cudaStream_t)stream>>>(
+        acc, total, (T*)dense);
+  });
+  SAH_LAUNCH_CHECK("mask_clamp");
+  return SAH_OK;
+}
+
 // ---- ragged sample list -> bitmap ----------------------------------------------------------
 __global__ void mask_scatter_samples_kernel(const int64_t* __restrict__ cols,
                                             const int64_t* __restrict__ sptr, int64_t rows,

@@ -221,61 +221,52 @@ extern "C" int sah_pq_update(const void* x, int dtype, int64_t xs_b, int64_t xs_
 // with an fp32 accumulator, pq_top_k.py:481-488).
 // ---------------------------------------------------------------------------
 #define PQ_ROWS 4
-#define PQ_KEYS_PER_THREAD 8
 
-// lut[(bk * rblocks + rblk)][sub][c][rr] = q_sub(row rblk*4 + rr) . centroid(sub, c), fma over
-// ascending dims, rounded to the dtype; rows past R hold 0.  One thread per (sub, c).
-template <typename T>
-__global__ void __launch_bounds__(256)
-pq_lut_kernel(const T* __restrict__ q, int64_t qs_b, int64_t qs_h, int64_t qs_q,
-              const T* __restrict__ centroids, int Hq, int Hkv, int Sq, int n_sub, int sub_d,
-              int n_cent, float* __restrict__ lut) {
-  const int G = Hq / Hkv;
-  const int R = G * Sq;
-  const int64_t bk = blockIdx.z;
-  const int kvh = (int)(bk % Hkv);
-  const int64_t b = bk / Hkv;
-  const int rblk = blockIdx.y, rblocks = gridDim.y;
-  const int idx = blockIdx.x * 256 + threadIdx.x;  // sub * n_cent + c
-  if (idx >= n_sub * n_cent) return;
-  const int sub = idx / n_cent;
-  const T* cp = centroids + (bk * n_sub * (int64_t)n_cent + idx) * sub_d;
-  float out[PQ_ROWS];
-#pragma unroll
-  for (int rr = 0; rr < PQ_ROWS; ++rr) {
-    const int r = rblk * PQ_ROWS + rr;
-    float v = 0.f;
-    if (r < R) {
-      const int g = r / Sq, qi = r - g * Sq;
-      const T* qp = q + b * qs_b + (int64_t)(kvh * G + g) * qs_h + qi * qs_q + sub * sub_d;
-      float acc = 0.f;
-      for (int d = 0; d < sub_d; ++d) acc = fmaf(sah_to_float<T>(qp[d]), sah_to_float<T>(cp[d]), acc);
-      v = sah_round_to<T>(acc);
-    }
-    out[rr] = v;
-  }
-  *reinterpret_cast<float4*>(lut + (((bk * rblocks + rblk) * (int64_t)n_sub * n_cent) + idx) * PQ_ROWS) =
-      make_float4(out[0], out[1], out[2], out[3]);
-}
-
-// One CTA: the table of one (KV group, block of 4 rows) in shared memory, 256 x
-// PQ_KEYS_PER_THREAD keys; a key's n_sub codes index float4 entries (one per row).
+// One CTA: builds the table of one (KV group, block of 4 rows) in shared memory --
+// lut[sub][c][rr] = q_sub(row rblk*4 + rr) . centroid(sub, c), fma over ascending dims, rounded
+// to the dtype; rows past R hold 0 -- then scores a contiguous range of the group's keys: a
+// key's n_sub codes index float4 entries (one per row).  The key range per CTA is sized so that
+// the grid is about two CTAs per SM: the table (64 KB for 16 x 256 centroids) is built a few
+// hundred times per call, not once per 2048 keys.
 template <typename T>
 __global__ void __launch_bounds__(PQ_TILE)
-pq_scores_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ codes, int64_t cap, int Hq,
-                 int Hkv, int Sq, int64_t n_keys, int64_t init_offset, int64_t S, int n_sub, int n_cent,
-                 T* __restrict__ scores) {
+pq_scores_kernel(const T* __restrict__ q, int64_t qs_b, int64_t qs_h, int64_t qs_q,
+                 const T* __restrict__ centroids, const uint8_t* __restrict__ codes, int64_t cap, int Hq,
+                 int Hkv, int Sq, int64_t n_keys, int64_t init_offset, int64_t S, int n_sub, int sub_d,
+                 int n_cent, int64_t keys_per_cta, T* __restrict__ scores) {
   extern __shared__ __align__(16) float pq_lut_sm[];  // [n_sub][n_cent][PQ_ROWS]
   const int G = Hq / Hkv;
   const int R = G * Sq;
   const int64_t bk = blockIdx.z;
   const int kvh = (int)(bk % Hkv);
   const int64_t b = bk / Hkv;
-  const int rblk = blockIdx.y, rblocks = gridDim.y;
+  const int rblk = blockIdx.y;
   const int entries = n_sub * n_cent;
-  const float4* src = reinterpret_cast<const float4*>(lut) + (bk * rblocks + rblk) * (int64_t)entries;
   float4* dst = reinterpret_cast<float4*>(pq_lut_sm);
-  for (int i = threadIdx.x; i < entries; i += PQ_TILE) dst[i] = src[i];
+  const T* qrow[PQ_ROWS];
+#pragma unroll
+  for (int rr = 0; rr < PQ_ROWS; ++rr) {
+    const int r = rblk * PQ_ROWS + rr;
+    const int g = r / Sq, qi = r - g * Sq;
+    qrow[rr] = r < R ? q + b * qs_b + (int64_t)(kvh * G + g) * qs_h + qi * qs_q : nullptr;
+  }
+  for (int idx = threadIdx.x; idx < entries; idx += PQ_TILE) {
+    const int sub = idx / n_cent;
+    const T* cp = centroids + (bk * n_sub * (int64_t)n_cent + idx) * sub_d;
+    float out[PQ_ROWS];
+#pragma unroll
+    for (int rr = 0; rr < PQ_ROWS; ++rr) {
+      float v = 0.f;
+      if (qrow[rr] != nullptr) {
+        const T* qp = qrow[rr] + sub * sub_d;
+        float acc = 0.f;
+        for (int d = 0; d < sub_d; ++d) acc = fmaf(sah_to_float<T>(qp[d]), sah_to_float<T>(cp[d]), acc);
+        v = sah_round_to<T>(acc);
+      }
+      out[rr] = v;
+    }
+    dst[idx] = make_float4(out[0], out[1], out[2], out[3]);
+  }
   __syncthreads();
   const bool vec = (n_sub == 16) && ((reinterpret_cast<uintptr_t>(codes) & 15) == 0);
   int64_t rowoff[PQ_ROWS];
@@ -285,10 +276,9 @@ pq_scores_kernel(const float* __restrict__ lut, const uint8_t* __restrict__ code
     const int g = r / Sq, qi = r - g * Sq;
     rowoff[rr] = r < R ? ((b * Hq + kvh * G + g) * Sq + qi) * S + init_offset : -1;
   }
-  const int64_t j0 = (int64_t)blockIdx.x * PQ_TILE * PQ_KEYS_PER_THREAD;
-  for (int i = 0; i < PQ_KEYS_PER_THREAD; ++i) {
-    const int64_t j = j0 + (int64_t)i * PQ_TILE + threadIdx.x;
-    if (j >= n_keys) break;
+  const int64_t j0 = (int64_t)blockIdx.x * keys_per_cta;
+  const int64_t j1 = j0 + keys_per_cta < n_keys ? j0 + keys_per_cta : n_keys;
+  for (int64_t j = j0 + threadIdx.x; j < j1; j += PQ_TILE) {
     const uint8_t* cj = codes + (bk * cap + j) * n_sub;
     float s[PQ_ROWS] = {0.f, 0.f, 0.f, 0.f};
     if (vec) {
@@ -326,16 +316,12 @@ extern "C" int sah_pq_scores(const void* q, int dtype, int64_t qs_b, int64_t qs_
                              int Hkv, int Sq, int64_t n_keys, int64_t init_offset, int64_t S,
                              int n_sub, int sub_d, int n_cent, void* scores, void* workspace,
                              int64_t workspace_bytes, void* stream) {
-  SAH_REQUIRE(q && centroids && codes && scores && workspace, "pq_scores: null pointer");
+  SAH_REQUIRE(q && centroids && codes && scores, "pq_scores: null pointer");
   SAH_REQUIRE(B > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Sq > 0, "pq_scores: bad heads");
   SAH_REQUIRE(n_keys >= 0 && init_offset >= 0 && init_offset + n_keys <= S && n_keys <= cap,
               "pq_scores: bad key range");
   SAH_REQUIRE(n_cent <= 256, "pq_scores: codes are bytes, at most 256 centroids");
-  SAH_REQUIRE(((uintptr_t)workspace & 15) == 0, "pq_scores: workspace must be 16-byte aligned");
-  if (workspace_bytes < sah_pq_scores_ws_bytes(B, Hq, Hkv, Sq, n_sub, n_cent))
-    return sah_fail(SAH_ERR_WORKSPACE, "pq_scores: workspace of %lld bytes, need %lld",
-                    (long long)workspace_bytes,
-                    (long long)sah_pq_scores_ws_bytes(B, Hq, Hkv, Sq, n_sub, n_cent));
+  (void)workspace_bytes;
   if (n_keys == 0) return SAH_OK;
   const int R = (Hq / Hkv) * Sq;
   const int rblocks = (R + PQ_ROWS - 1) / PQ_ROWS;
@@ -344,23 +330,25 @@ extern "C" int sah_pq_scores(const void* q, int dtype, int64_t qs_b, int64_t qs_
     return sah_fail(SAH_ERR_UNSUPPORTED, "pq_scores: %d x %d lookup table does not fit", n_sub, n_cent);
   SAH_REQUIRE(rblocks <= 65535 && (int64_t)B * Hkv <= 65535, "pq_scores: too many rows per launch");
   cudaStream_t st = (cudaStream_t)stream;
-  float* lut = reinterpret_cast<float*>(workspace);
+  (void)workspace;  // the tables live in shared memory; the argument is kept for callers that pass one
   sah_prof_begin(SAH_PROF_PQ_SCORES, st);
-  dim3 lgrid((unsigned)sah_ceil_div((int64_t)n_sub * n_cent, 256), (unsigned)rblocks, (unsigned)((int64_t)B * Hkv));
-  dim3 grid((unsigned)sah_ceil_div(n_keys, (int64_t)PQ_TILE * PQ_KEYS_PER_THREAD), (unsigned)rblocks,
-            (unsigned)((int64_t)B * Hkv));
+  // about two CTAs per SM, each with a contiguous key range that is a multiple of the CTA width
+  const int64_t groups = (int64_t)B * Hkv * rblocks;
+  int64_t per_group = (2 * 148 + groups - 1) / groups;
+  if (per_group < 1) per_group = 1;
+  int64_t keys_per_cta = sah_ceil_div(sah_ceil_div(n_keys, per_group), PQ_TILE) * PQ_TILE;
+  if (keys_per_cta < 2048) keys_per_cta = 2048;
+  dim3 grid((unsigned)sah_ceil_div(n_keys, keys_per_cta), (unsigned)rblocks, (unsigned)((int64_t)B * Hkv));
   SAH_DISPATCH_DTYPE(dtype, T, {
-    pq_lut_kernel<T><<<lgrid, 256, 0, st>>>((const T*)q, qs_b, qs_h, qs_q, (const T*)centroids, Hq, Hkv,
-                                            Sq, n_sub, sub_d, n_cent, lut);
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(pq_scores_kernel<T>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "pq_scores attr: %s", cudaGetErrorString(e));
     }
-    pq_scores_kernel<T><<<grid, PQ_TILE, smem, st>>>(lut, codes, cap, Hq, Hkv, Sq, n_keys, init_offset, S,
-                                                     n_sub, n_cent, (T*)scores);
+    pq_scores_kernel<T><<<grid, PQ_TILE, smem, st>>>((const T*)q, qs_b, qs_h, qs_q, (const T*)centroids, codes,
+                                                     cap, Hq, Hkv, Sq, n_keys, init_offset, S, n_sub, sub_d,
+                                                     n_cent, keys_per_cta, (T*)scores);
   });
-  sah_count_launch();
   SAH_LAUNCH_CHECK("pq_scores");
   sah_prof_end(SAH_PROF_PQ_SCORES, st);
   return SAH_OK;

@@ -355,6 +355,19 @@ class Mask:
         assert not use_padding, "use_padding is not supported for dense mode; use sparse mode instead"
         if mask_type not in ("dense", "index"):
             raise ValueError(f"type must be 'index' or 'dense', got {mask_type}")
+        if row_wise_idx.is_cuda and dtype in (torch.float32, torch.bfloat16):
+            # deterministic on the device: the last duplicate of a column wins, as on the CPU
+            lib = _native.load()
+            rows, n, k = _n_rows(shape), shape[-1], row_wise_idx.shape[-1]
+            idx = row_wise_idx.to(torch.int64).contiguous()
+            vals = data.to(device=idx.device, dtype=dtype).contiguous()
+            claims = torch.empty(rows * n, dtype=torch.int64, device=idx.device)
+            dense = torch.empty(tuple(shape), dtype=dtype, device=idx.device)
+            _native.check(
+                lib.sah_mask_rowwise_scatter(idx.data_ptr(), vals.data_ptr(), _native.dtype_code(dtype), rows, k,
+                                             n, claims.data_ptr(), dense.data_ptr(),
+                                             _native.stream_of(idx.device)), "sah_mask_rowwise_scatter")
+            return cls.create_mask_from_dense_mask(shape, dense, dtype=dtype)
         dense = torch.zeros(shape, dtype=dtype, device=row_wise_idx.device)
         dense.scatter_(dim=-1, index=row_wise_idx, src=data.to(dtype))
         return cls.create_mask_from_dense_mask(shape, dense, dtype=dtype)
@@ -642,6 +655,22 @@ class Mask:
         elif a_idx.numel() == 0 or b_idx.numel() == 0:
             idx, ptr, val = (b_idx, b_ptr, b_val) if a_idx.numel() == 0 else (a_idx, a_ptr, a_val)
             val = torch.clamp(val, 0.0, 1.0)
+        elif a_idx.is_cuda and self.dtype in (torch.float32, torch.bfloat16):
+            # the sums of equal indices in a float32 array over all positions, clamped and
+            # rounded on the device; the ascending index form comes from the bitmap kernels
+            lib = _native.load()
+            st = _native.stream_of(dev)
+            code = _native.dtype_code(self.dtype)
+            total = rows * n
+            acc = torch.zeros(total, dtype=torch.float32, device=dev)
+            for i_, v_ in ((a_idx, a_val), (b_idx, b_val)):
+                ic, vc = i_.to(torch.int64).contiguous(), v_.to(self.dtype).contiguous()
+                _native.check(lib.sah_mask_flat_add(ic.data_ptr(), vc.data_ptr(), code, ic.numel(), total,
+                                                    acc.data_ptr(), st), "sah_mask_flat_add")
+            dense = torch.empty(tuple(self.shape), dtype=self.dtype, device=dev)
+            _native.check(lib.sah_mask_clamp_to_dense(acc.data_ptr(), code, total, dense.data_ptr(), st),
+                          "sah_mask_clamp_to_dense")
+            idx, ptr, val = Mask.create_mask_from_dense_mask(self.shape, dense, self.dtype).get_index_mask()
         else:
             cat_idx = torch.cat([a_idx, b_idx])
             cat_val = torch.cat([a_val.to(self.dtype), b_val.to(self.dtype)])

@@ -394,3 +394,35 @@ def test_attention_with_sixteen_rows_per_group():
         out = native_masked_attention(tq, tk, tv, None, None, float(wl.scaling), m)
         ref = o_attention.masked_attention(q, k, v, dense, wl.scaling, dtype)
         _close(out.float().cpu().numpy(), ref, dtype)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_gpu_mask_interop_from_rows_and_sparse_merge(dtype):
+    """`Mask.create_from_row_wise_idx(mode="dense")` and `merge_mask(mode="sparse")` on device
+    tensors run the library's scatter / flat-add kernels; both must give the reference's result
+    bit for bit (duplicates inside a row: the last one stays; merged entries: summed in the mask
+    dtype, clamped, every stored index kept)."""
+    g = load_golden(f"mask_interop_{dtype}")
+    td = workloads.torch_dtype(dtype)
+    shape = tuple(g["row_dense"].shape)
+    idx = torch.from_numpy(g["row_idx"]).to(DEV)
+    vals = workloads.to_torch(g["row_vals"], dtype, DEV)
+    m = Mask.create_from_row_wise_idx(shape, idx, vals, mask_type="dense", dtype=td, mode="dense")
+    np.testing.assert_array_equal(m.get_dense_mask().float().cpu().numpy(), g["row_dense"])
+    np.testing.assert_array_equal(m.get_dense_mask().float().cpu().numpy(),
+                                  mask_ops.from_row_wise_idx(shape, g["row_idx"], g["row_vals"]))
+
+    def index_form(dense):
+        d = Mask.create_mask_from_dense_mask(shape, workloads.to_torch(dense, dtype, DEV), td)
+        i, p, v = d.get_index_mask()
+        return Mask.create_mask_from_indices(shape, i, p, v, td)
+
+    merged = index_form(g["a"]).merge_mask(index_form(g["b"]), inplace=False, mode="sparse")
+    mi, mp, md = merged.get_index_mask()
+    np.testing.assert_array_equal(mi.cpu().numpy(), g["merged_idx"])
+    np.testing.assert_array_equal(mp.cpu().numpy(), g["merged_ptr"])
+    np.testing.assert_array_equal(md.float().cpu().numpy(), g["merged_data"])
+    oi, op, od = mask_ops.merge_sparse(g["a"], g["b"], dtype)
+    np.testing.assert_array_equal(mi.cpu().numpy(), oi)
+    np.testing.assert_array_equal(md.float().cpu().numpy(), od)

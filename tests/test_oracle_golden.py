@@ -129,3 +129,16 @@ def test_inverse_weight_rounding():
     assert w32[0] == np.float32(1.0) / (np.float32(1.0) + np.float32(1e-6)) and w32[2] == 0
     wbf = mask_ops.inv_weights(m, "bf16")
     assert wbf[0] == 1.0 and wbf[1] == 2.0 and wbf[2] == 0.0
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_mask_interop_restatements(dtype):
+    """Row-wise construction (last duplicate wins) and the sparse merge (sum, clamp, union of
+    the stored entries) against what the reference's Mask produced."""
+    g = load_golden(f"mask_interop_{dtype}")
+    shape = g["row_dense"].shape
+    np.testing.assert_array_equal(mask_ops.from_row_wise_idx(shape, g["row_idx"], g["row_vals"]), g["row_dense"])
+    idx, ptr, data = mask_ops.merge_sparse(g["a"], g["b"], dtype)
+    np.testing.assert_array_equal(idx, g["merged_idx"])
+    np.testing.assert_array_equal(ptr, g["merged_ptr"])
+    np.testing.assert_array_equal(data, g["merged_data"])
