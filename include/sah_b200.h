@@ -637,6 +637,18 @@ int sah_attn_gather_probe(const void* k, const void* v, int64_t ks_b, int64_t ks
                           int64_t S, int D, const sah_attn_sizes* sizes, const int32_t* ucols,
                           const int32_t* ucount, unsigned int* sink, void* stream);
 
+/* Which bfloat16 attention kernel the library launches (no counterpart in the reference):
+ *   SAH_ATTN_KERNEL_AUTO (-1)  the library decides per call (the start-up value; the environment
+ *                              variable SAH_ATTN_UMMA=0/1 overrides the decision),
+ *   SAH_ATTN_KERNEL_MMA  (0)   per-warp mma.sync pipeline over 16-key tiles,
+ *   SAH_ATTN_KERNEL_UMMA (1)   tcgen05 pipeline over 128-key tiles (head dim 128 only; other
+ *                              problems still take the mma.sync kernel).
+ * Process-wide; returns the previous setting, or -2 for an unknown `which`. */
+#define SAH_ATTN_KERNEL_AUTO (-1)
+#define SAH_ATTN_KERNEL_MMA 0
+#define SAH_ATTN_KERNEL_UMMA 1
+int sah_attn_select_kernel(int which);
+
 /* Merge n_parts partial results (parts [n_parts][rows][D+2], the part_out of
  * sah_masked_attention on every shard) into out [B][Sq][Hq][D]: the
  * associative combine of sequence-sharded softmax partials. */

@@ -484,6 +484,7 @@ struct AttnCfg {
 };
 
 #include "sah_attention_tc.cuh"
+#include "sah_attention_umma.cuh"
 
 template <typename T, int D, int NQUAD>
 __global__ void __launch_bounds__(AT_THREADS)
@@ -907,6 +908,19 @@ static int masked_attention_impl(const void* q, const void* k, const void* v, in
     // tensor-core path; the split merge is fused into the kernel (ticket per group)
     int* tickets = const_cast<int*>(ucount) + groups + (int64_t)groups * plan_chunks(S);
     int* errflag = tickets + groups;  // set when a bounded wait inside the kernel ran out
+    // long lists: keys as the M dimension of tcgen05 tiles; otherwise the mma.sync kernel
+    const int umma = aum_requested();
+    if (D == 128 && (umma == 1 || (umma < 0 && aum_default(lsh != nullptr, S)))) {
+      bool launched = false;
+      rc = launch_attention_umma(a, B, groups, tickets, errflag, sinks, out, part_out, lsh != nullptr, st,
+                                 &launched);
+      if (rc != SAH_OK) return rc;
+      if (launched) {
+        SAH_LAUNCH_CHECK("masked_attention_umma");
+        sah_prof_end(SAH_PROF_ATTENTION, (cudaStream_t)stream);
+        return SAH_OK;
+      }
+    }
     rc = (D == 128)
              ? launch_attention_mma<128>(a, B, groups, tickets, errflag, sinks, out, part_out, lsh != nullptr, st)
              : launch_attention_mma<64>(a, B, groups, tickets, errflag, sinks, out, part_out, lsh != nullptr, st);
@@ -929,6 +943,25 @@ static int masked_attention_impl(const void* q, const void* k, const void* v, in
   SAH_LAUNCH_CHECK("attn_merge_splits");
   sah_prof_end(SAH_PROF_ATTN_MERGE, (cudaStream_t)stream);
   return SAH_OK;
+}
+
+#ifdef AUM_PROF
+extern "C" int sah_debug_umma_prof(long long* host_out, int reset) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(host_out, aum_prof, sizeof(long long) * 32);
+  if (reset) {
+    long long z[32] = {};
+    cudaMemcpyToSymbol(aum_prof, z, sizeof(z));
+  }
+  return 0;
+}
+#endif
+
+extern "C" int sah_attn_select_kernel(int which) {
+  if (which < -1 || which > 1) return -2;
+  const int prev = aum_setting;
+  aum_setting = which;
+  return prev;
 }
 
 extern "C" int sah_masked_attention(const void* q, const void* k, const void* v, int dtype,

@@ -45,7 +45,6 @@
 #define ATM_THREADS (ATM_WARPS * 32)
 #define ATM_TILE 16
 #define ATM_MIN_TILES 8        // tiles a warp should have before a further CTA joins the group
-#define ATM_ONE_WAVE_TILES 48  // below this many tiles per warp, one wave of CTAs instead of two
 #define ATM_SPIN_LIMIT (1 << 19)
 
 struct AtmMaps {
@@ -136,17 +135,13 @@ __device__ __forceinline__ void atm_cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
 }
 
-// CTAs that share one group's union list.  The grid holds nsplit per group, which is two waves
-// of the device for long lists (the second wave evens out groups of different length).  A list
-// that would give a warp fewer than ATM_ONE_WAVE_TILES tiles in that arrangement is worked on
-// by half of them -- one wave, half as many pipeline fills and partials -- and a short list by
-// as few as give every warp ATM_MIN_TILES tiles; the others leave at once (they hold no ticket).
+// CTAs that share one group's union list.  The grid holds nsplit per group, sized for long
+// lists.  A short list is shared by fewer of them, so that every warp still has a run of
+// ATM_MIN_TILES tiles to pipeline and the last CTA merges few partials; the others leave at
+// once (they hold no ticket).
 __device__ __forceinline__ int atm_active_splits(int total_tiles, int nsplit) {
-  int active = nsplit;
-  if (nsplit >= 2 && total_tiles < nsplit * ATM_WARPS * ATM_ONE_WAVE_TILES) active = (nsplit + 1) / 2;
-  const int by_length = (total_tiles + ATM_WARPS * ATM_MIN_TILES - 1) / (ATM_WARPS * ATM_MIN_TILES);
-  if (by_length < active) active = by_length;
-  return active < 1 ? 1 : active;
+  int active = (total_tiles + ATM_WARPS * ATM_MIN_TILES - 1) / (ATM_WARPS * ATM_MIN_TILES);
+  return active < 1 ? 1 : (active > nsplit ? nsplit : active);
 }
 
 template <int D, bool TMA = false, int NST = ATM_STAGES>
@@ -179,6 +174,92 @@ __device__ __forceinline__ float atm_lsh_weight(float dot_hat, float qmu, float 
   c = fminf(fmaxf(c, -1.0f), 1.0f);
   const float p = __uint_as_float(((uint32_t)__ldg(ptable + (__float_as_uint(c) >> 16))) << 16);
   return p == 0.f ? 0.f : sah_inv_weight<__nv_bfloat16>(p);
+}
+
+// The CTA has written its partial (running maximum, denominator and unnormalised output per
+// mask row).  It takes a ticket; the last CTA of the group to arrive merges the `active`
+// partials of the group, applies the sink logits and writes the output rows (and, when
+// `part_out` is given, the group's merged partial for a merge across sequence shards).
+// Called by all NT threads of the CTA; `scratch` is shared memory the CTA no longer needs
+// (16 * active + 32 floats).
+template <int D, int NT>
+__device__ __forceinline__ void atm_finish_group(const AttnArgs& a, int64_t g, int active,
+                                                 unsigned char* scratch, int* is_last_sm,
+                                                 int* __restrict__ tickets, const float* __restrict__ sinks,
+                                                 __nv_bfloat16* __restrict__ out,
+                                                 float* __restrict__ part_out) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int qb = (int)(g % a.nqb);
+  const int64_t bk = g / a.nqb;
+  const int kvh = (int)(bk % a.Hkv);
+  const int64_t b = bk / a.Hkv;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int old = atomicAdd(&tickets[g], 1);
+    const int last = (old == active - 1);
+    if (last) tickets[g] = 0;  // ready for the next call
+    *is_last_sm = last;
+  }
+  __syncthreads();
+  if (!*is_last_sm) return;
+  __threadfence();
+  const float* p0 = a.partial + (int64_t)g * a.nsplit * a.R * (D + 2);
+  const int64_t pstride = (int64_t)a.R * (D + 2);
+  // phase 1: one warp per row finds the row maximum, the per-split rescale
+  // factors and the denominator
+  float* sc_sm = reinterpret_cast<float*>(scratch);  // [R][active]
+  float* ml_sm = sc_sm + 16 * active;                // [R][2]
+  for (int r = warp; r < a.R; r += NT / 32) {
+    const float* pr = p0 + (int64_t)r * (D + 2);
+    float mloc = -INFINITY;
+    for (int s2 = lane; s2 < active; s2 += 32) mloc = fmaxf(mloc, __ldcg(pr + s2 * pstride + D));
+#pragma unroll
+    for (int of = 16; of > 0; of >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, of));
+    float lsum = 0.f;
+    for (int s2 = lane; s2 < active; s2 += 32) {
+      const float ms = __ldcg(pr + s2 * pstride + D);
+      const float sc = (ms == -INFINITY) ? 0.f : __expf(ms - mloc);
+      sc_sm[r * active + s2] = sc;
+      lsum += __ldcg(pr + s2 * pstride + D + 1) * sc;
+    }
+#pragma unroll
+    for (int of = 16; of > 0; of >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, of);
+    if (lane == 0) {
+      ml_sm[r * 2] = mloc;
+      ml_sm[r * 2 + 1] = lsum;
+    }
+  }
+  __syncthreads();
+  // phase 2: every (row, dim) sums its column over the splits; the loads are independent
+  for (int idx = tid; idx < a.R * D; idx += NT) {
+    const int r = idx / D, d = idx - r * D;
+    const int gi = r / a.q_block, qo = r - gi * a.q_block;
+    const int qi = qb * a.q_block + qo;
+    if (qi >= a.Sq) continue;
+    const int h = kvh * a.G + gi;
+    const float* pr = p0 + (int64_t)r * (D + 2) + d;
+    const float* sc = sc_sm + r * active;
+    float accv = 0.f;
+#pragma unroll 8
+    for (int s2 = 0; s2 < active; ++s2) accv = fmaf(__ldcg(pr + s2 * pstride), sc[s2], accv);
+    const float M = ml_sm[r * 2], L = ml_sm[r * 2 + 1];
+    float Mx = M, sink_term = 0.f;
+    if (sinks != nullptr) {
+      const float sk = sinks[h];
+      Mx = fmaxf(M, sk);
+      sink_term = __expf(sk - Mx);
+    }
+    const float resc = (M == -INFINITY) ? 0.f : __expf(M - Mx);
+    const float den = L * resc + sink_term;
+    const int64_t row = (b * a.Hq + h) * a.Sq + qi;
+    if (part_out != nullptr) part_out[row * (D + 2) + d] = accv;
+    out[((b * a.Sq + qi) * a.Hq + h) * D + d] = __float2bfloat16_rn(accv * resc / den);
+    if (part_out != nullptr && d == 0) {
+      part_out[row * (D + 2) + D] = M;
+      part_out[row * (D + 2) + D + 1] = L;
+    }
+  }
 }
 
 // NST: stages of the per-warp ring.  Three stages fit two CTAs (8 warps) per SM; two stages,
@@ -621,74 +702,7 @@ masked_attention_mma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, in
     }
   }
 
-  // ---- last CTA of the group merges the group's partials ----
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const int old = atomicAdd(&tickets[g], 1);
-    const int last = (old == active - 1);
-    if (last) tickets[g] = 0;  // ready for the next call
-    is_last_sm = last;
-  }
-  __syncthreads();
-  if (!is_last_sm) return;
-  __threadfence();
-  const float* p0 = a.partial + (int64_t)g * a.nsplit * a.R * (D + 2);
-  const int64_t pstride = (int64_t)a.R * (D + 2);
-  // phase 1: one warp per row finds the row maximum, the per-split rescale
-  // factors and the denominator (ring memory reused as scratch)
-  float* sc_sm = reinterpret_cast<float*>(atm_smem);  // [R][nsplit]
-  float* ml_sm = sc_sm + 16 * active;                 // [R][2]
-  for (int r = warp; r < a.R; r += ATM_WARPS) {
-    const float* pr = p0 + (int64_t)r * (D + 2);
-    float mloc = -INFINITY;
-    for (int s2 = lane; s2 < active; s2 += 32) mloc = fmaxf(mloc, __ldcg(pr + s2 * pstride + D));
-#pragma unroll
-    for (int of = 16; of > 0; of >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, of));
-    float lsum = 0.f;
-    for (int s2 = lane; s2 < active; s2 += 32) {
-      const float ms = __ldcg(pr + s2 * pstride + D);
-      const float sc = (ms == -INFINITY) ? 0.f : __expf(ms - mloc);
-      sc_sm[r * active + s2] = sc;
-      lsum += __ldcg(pr + s2 * pstride + D + 1) * sc;
-    }
-#pragma unroll
-    for (int of = 16; of > 0; of >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, of);
-    if (lane == 0) {
-      ml_sm[r * 2] = mloc;
-      ml_sm[r * 2 + 1] = lsum;
-    }
-  }
-  __syncthreads();
-  // phase 2: every (row, dim) sums its column over the splits; the loads are independent
-  for (int idx = tid; idx < a.R * D; idx += ATM_THREADS) {
-    const int r = idx / D, d = idx - r * D;
-    const int gi = r / a.q_block, qo = r - gi * a.q_block;
-    const int qi = qb * a.q_block + qo;
-    if (qi >= a.Sq) continue;
-    const int h = kvh * a.G + gi;
-    const float* pr = p0 + (int64_t)r * (D + 2) + d;
-    const float* sc = sc_sm + r * active;
-    float accv = 0.f;
-#pragma unroll 8
-    for (int s2 = 0; s2 < active; ++s2) accv = fmaf(__ldcg(pr + s2 * pstride), sc[s2], accv);
-    const float M = ml_sm[r * 2], L = ml_sm[r * 2 + 1];
-    float Mx = M, sink_term = 0.f;
-    if (sinks != nullptr) {
-      const float sk = sinks[h];
-      Mx = fmaxf(M, sk);
-      sink_term = __expf(sk - Mx);
-    }
-    const float resc = (M == -INFINITY) ? 0.f : __expf(M - Mx);
-    const float den = L * resc + sink_term;
-    const int64_t row = (b * a.Hq + h) * a.Sq + qi;
-    if (part_out != nullptr) part_out[row * (D + 2) + d] = accv;
-    out[((b * a.Sq + qi) * a.Hq + h) * D + d] = __float2bfloat16_rn(accv * resc / den);
-    if (part_out != nullptr && d == 0) {
-      part_out[row * (D + 2) + D] = M;
-      part_out[row * (D + 2) + D + 1] = L;
-    }
-  }
+  atm_finish_group<D, ATM_THREADS>(a, g, active, atm_smem, &is_last_sm, tickets, sinks, out, part_out);
 }
 
 // Row-gather probe: the copy half of the attention kernel alone.  Same grid, same dealing of

@@ -225,16 +225,43 @@ extern "C" int sah_pq_update(const void* x, int dtype, int64_t xs_b, int64_t xs_
 // One CTA: builds the table of one (KV group, block of 4 rows) in shared memory --
 // lut[sub][c][rr] = q_sub(row rblk*4 + rr) . centroid(sub, c), fma over ascending dims, rounded
 // to the dtype; rows past R hold 0 -- then scores a contiguous range of the group's keys: a
-// key's n_sub codes index float4 entries (one per row).  The key range per CTA is sized so that
-// the grid is about two CTAs per SM: the table (64 KB for 16 x 256 centroids) is built a few
-// hundred times per call, not once per 2048 keys.
+// key's n_sub codes index one entry each (the four rows of a centroid side by side: four
+// bfloat16 in 8 bytes, or four floats in 16).  The key range per CTA is sized so that the grid
+// is about two CTAs per SM: the table is built a few hundred times per call.
+// The query rows are staged in shared memory as floats; a centroid is read with 16-byte loads
+// when its sub-vector allows it (VEC: sub_d * sizeof(T) is a multiple of 16).
 template <typename T>
+struct PqEntry;
+template <>
+struct PqEntry<float> {
+  typedef float4 type;
+  static __device__ __forceinline__ float4 pack(const float* v) { return make_float4(v[0], v[1], v[2], v[3]); }
+  static __device__ __forceinline__ void add(float* s, const float4& e) {
+    s[0] = __fadd_rn(s[0], e.x); s[1] = __fadd_rn(s[1], e.y);
+    s[2] = __fadd_rn(s[2], e.z); s[3] = __fadd_rn(s[3], e.w);
+  }
+};
+template <>
+struct PqEntry<__nv_bfloat16> {
+  typedef uint2 type;  // the table values are bfloat16 numbers: two per word
+  static __device__ __forceinline__ uint2 pack(const float* v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+    return make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+  }
+  static __device__ __forceinline__ void add(float* s, const uint2& e) {
+    s[0] = __fadd_rn(s[0], __uint_as_float(e.x << 16)); s[1] = __fadd_rn(s[1], __uint_as_float(e.x & 0xffff0000u));
+    s[2] = __fadd_rn(s[2], __uint_as_float(e.y << 16)); s[3] = __fadd_rn(s[3], __uint_as_float(e.y & 0xffff0000u));
+  }
+};
+
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(PQ_TILE)
 pq_scores_kernel(const T* __restrict__ q, int64_t qs_b, int64_t qs_h, int64_t qs_q,
                  const T* __restrict__ centroids, const uint8_t* __restrict__ codes, int64_t cap, int Hq,
                  int Hkv, int Sq, int64_t n_keys, int64_t init_offset, int64_t S, int n_sub, int sub_d,
                  int n_cent, int64_t keys_per_cta, T* __restrict__ scores) {
-  extern __shared__ __align__(16) float pq_lut_sm[];  // [n_sub][n_cent][PQ_ROWS]
+  typedef typename PqEntry<T>::type Entry;
+  extern __shared__ __align__(16) unsigned char pq_sm_raw[];
   const int G = Hq / Hkv;
   const int R = G * Sq;
   const int64_t bk = blockIdx.z;
@@ -242,30 +269,47 @@ pq_scores_kernel(const T* __restrict__ q, int64_t qs_b, int64_t qs_h, int64_t qs
   const int64_t b = bk / Hkv;
   const int rblk = blockIdx.y;
   const int entries = n_sub * n_cent;
-  float4* dst = reinterpret_cast<float4*>(pq_lut_sm);
-  const T* qrow[PQ_ROWS];
-#pragma unroll
-  for (int rr = 0; rr < PQ_ROWS; ++rr) {
+  const int Dh = n_sub * sub_d;
+  Entry* lut = reinterpret_cast<Entry*>(pq_sm_raw);                  // [n_sub][n_cent]
+  float* q_sm = reinterpret_cast<float*>(lut + entries);             // [PQ_ROWS][Dh]
+  for (int idx = threadIdx.x; idx < PQ_ROWS * Dh; idx += PQ_TILE) {
+    const int rr = idx / Dh, d = idx - rr * Dh;
     const int r = rblk * PQ_ROWS + rr;
-    const int g = r / Sq, qi = r - g * Sq;
-    qrow[rr] = r < R ? q + b * qs_b + (int64_t)(kvh * G + g) * qs_h + qi * qs_q : nullptr;
+    float v = 0.f;
+    if (r < R) {
+      const int g = r / Sq, qi = r - g * Sq;
+      v = sah_to_float<T>(q[b * qs_b + (int64_t)(kvh * G + g) * qs_h + qi * qs_q + d]);
+    }
+    q_sm[idx] = v;
   }
+  __syncthreads();
+  constexpr int PER16 = 16 / (int)sizeof(T);  // elements per 16-byte load
   for (int idx = threadIdx.x; idx < entries; idx += PQ_TILE) {
     const int sub = idx / n_cent;
     const T* cp = centroids + (bk * n_sub * (int64_t)n_cent + idx) * sub_d;
+    float acc[PQ_ROWS] = {0.f, 0.f, 0.f, 0.f};
+    if constexpr (VEC) {
+      for (int d0 = 0; d0 < sub_d; d0 += PER16) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(cp + d0);
+        const T* cv = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int e = 0; e < PER16; ++e) {
+          const float c = sah_to_float<T>(cv[e]);
+#pragma unroll
+          for (int rr = 0; rr < PQ_ROWS; ++rr) acc[rr] = fmaf(q_sm[rr * Dh + sub * sub_d + d0 + e], c, acc[rr]);
+        }
+      }
+    } else {
+      for (int d = 0; d < sub_d; ++d) {
+        const float c = sah_to_float<T>(cp[d]);
+#pragma unroll
+        for (int rr = 0; rr < PQ_ROWS; ++rr) acc[rr] = fmaf(q_sm[rr * Dh + sub * sub_d + d], c, acc[rr]);
+      }
+    }
     float out[PQ_ROWS];
 #pragma unroll
-    for (int rr = 0; rr < PQ_ROWS; ++rr) {
-      float v = 0.f;
-      if (qrow[rr] != nullptr) {
-        const T* qp = qrow[rr] + sub * sub_d;
-        float acc = 0.f;
-        for (int d = 0; d < sub_d; ++d) acc = fmaf(sah_to_float<T>(qp[d]), sah_to_float<T>(cp[d]), acc);
-        v = sah_round_to<T>(acc);
-      }
-      out[rr] = v;
-    }
-    dst[idx] = make_float4(out[0], out[1], out[2], out[3]);
+    for (int rr = 0; rr < PQ_ROWS; ++rr) out[rr] = (rblk * PQ_ROWS + rr < R) ? sah_round_to<T>(acc[rr]) : 0.f;
+    lut[idx] = PqEntry<T>::pack(out);
   }
   __syncthreads();
   const bool vec = (n_sub == 16) && ((reinterpret_cast<uintptr_t>(codes) & 15) == 0);
@@ -287,16 +331,10 @@ pq_scores_kernel(const T* __restrict__ q, int64_t qs_b, int64_t qs_h, int64_t qs
 #pragma unroll
       for (int sub = 0; sub < 16; ++sub) {
         const uint32_t c = (w[sub >> 2] >> ((sub & 3) * 8)) & 255u;
-        const float4 e = dst[sub * n_cent + c];
-        s[0] = __fadd_rn(s[0], e.x); s[1] = __fadd_rn(s[1], e.y);
-        s[2] = __fadd_rn(s[2], e.z); s[3] = __fadd_rn(s[3], e.w);
+        PqEntry<T>::add(s, lut[sub * n_cent + c]);
       }
     } else {
-      for (int sub = 0; sub < n_sub; ++sub) {
-        const float4 e = dst[sub * n_cent + cj[sub]];
-        s[0] = __fadd_rn(s[0], e.x); s[1] = __fadd_rn(s[1], e.y);
-        s[2] = __fadd_rn(s[2], e.z); s[3] = __fadd_rn(s[3], e.w);
-      }
+      for (int sub = 0; sub < n_sub; ++sub) PqEntry<T>::add(s, lut[sub * n_cent + cj[sub]]);
     }
 #pragma unroll
     for (int rr = 0; rr < PQ_ROWS; ++rr)
@@ -325,7 +363,8 @@ extern "C" int sah_pq_scores(const void* q, int dtype, int64_t qs_b, int64_t qs_
   if (n_keys == 0) return SAH_OK;
   const int R = (Hq / Hkv) * Sq;
   const int rblocks = (R + PQ_ROWS - 1) / PQ_ROWS;
-  const size_t smem = (size_t)PQ_ROWS * n_sub * n_cent * sizeof(float);
+  const size_t esz = (dtype == SAH_BF16) ? 8 : 16;  // one table entry: the four rows of a centroid
+  const size_t smem = esz * n_sub * n_cent + (size_t)PQ_ROWS * n_sub * sub_d * sizeof(float);
   if (smem > 200 * 1024)
     return sah_fail(SAH_ERR_UNSUPPORTED, "pq_scores: %d x %d lookup table does not fit", n_sub, n_cent);
   SAH_REQUIRE(rblocks <= 65535 && (int64_t)B * Hkv <= 65535, "pq_scores: too many rows per launch");
@@ -339,16 +378,31 @@ extern "C" int sah_pq_scores(const void* q, int dtype, int64_t qs_b, int64_t qs_
   int64_t keys_per_cta = sah_ceil_div(sah_ceil_div(n_keys, per_group), PQ_TILE) * PQ_TILE;
   if (keys_per_cta < 2048) keys_per_cta = 2048;
   dim3 grid((unsigned)sah_ceil_div(n_keys, keys_per_cta), (unsigned)rblocks, (unsigned)((int64_t)B * Hkv));
-  SAH_DISPATCH_DTYPE(dtype, T, {
-    if (smem > 48 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(pq_scores_kernel<T>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "pq_scores attr: %s", cudaGetErrorString(e));
-    }
-    pq_scores_kernel<T><<<grid, PQ_TILE, smem, st>>>((const T*)q, qs_b, qs_h, qs_q, (const T*)centroids, codes,
-                                                     cap, Hq, Hkv, Sq, n_keys, init_offset, S, n_sub, sub_d,
-                                                     n_cent, keys_per_cta, (T*)scores);
-  });
+  const int64_t tsz = (dtype == SAH_BF16) ? 2 : 4;
+  const bool vecc = (sub_d * tsz) % 16 == 0 && (reinterpret_cast<uintptr_t>(centroids) & 15) == 0;
+  static int smem_allowed[4] = {0, 0, 0, 0};  // largest dynamic shared memory granted per instantiation
+#define PQ_SCORES_LAUNCH(T, VEC, SLOT)                                                                    \
+  do {                                                                                                    \
+    if ((int)smem > 48 * 1024 && (int)smem > smem_allowed[SLOT]) {                                        \
+      cudaError_t e = cudaFuncSetAttribute(pq_scores_kernel<T, VEC>,                                      \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+      if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "pq_scores attr: %s", cudaGetErrorString(e));   \
+      smem_allowed[SLOT] = (int)smem;                                                                     \
+    }                                                                                                     \
+    pq_scores_kernel<T, VEC><<<grid, PQ_TILE, smem, st>>>((const T*)q, qs_b, qs_h, qs_q, (const T*)centroids, \
+                                                          codes, cap, Hq, Hkv, Sq, n_keys, init_offset, S, \
+                                                          n_sub, sub_d, n_cent, keys_per_cta, (T*)scores); \
+  } while (0)
+  if (dtype == SAH_BF16) {
+    if (vecc) PQ_SCORES_LAUNCH(__nv_bfloat16, true, 0);
+    else PQ_SCORES_LAUNCH(__nv_bfloat16, false, 1);
+  } else if (dtype == SAH_F32) {
+    if (vecc) PQ_SCORES_LAUNCH(float, true, 2);
+    else PQ_SCORES_LAUNCH(float, false, 3);
+  } else {
+    return sah_fail(SAH_ERR_INVALID, "pq_scores: unknown dtype %d", dtype);
+  }
+#undef PQ_SCORES_LAUNCH
   SAH_LAUNCH_CHECK("pq_scores");
   sah_prof_end(SAH_PROF_PQ_SCORES, st);
   return SAH_OK;

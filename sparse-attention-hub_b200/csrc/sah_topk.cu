@@ -461,9 +461,169 @@ sel_emit_kernel(const T* __restrict__ scores, int64_t S, int64_t W, int64_t col_
   }
 }
 
+// ---------------------------------------------------------------------------
+// One-rank form of the same selection without state kernels: every CTA derives the threshold
+// found so far from the chunk histograms of the digits already counted (a few hundred loads),
+// so a selection is one launch per digit plus the emit -- 3 launches for bfloat16 keys instead
+// of 6.  A row is cut into at most SELF_MAX_CHUNKS chunks (a multiple of 256 words each); the
+// chunk histograms are plain stores, nothing has to be zeroed between calls.
+// ---------------------------------------------------------------------------
+#define SELF_MAX_CHUNKS 32
+
+struct SelFusedGeom {
+  int64_t chunk_words;
+  int chunks;
+};
+static SelFusedGeom sel_fused_geom(int64_t W) {
+  SelFusedGeom g;
+  int64_t cw = (W + SELF_MAX_CHUNKS - 1) / SELF_MAX_CHUNKS;
+  cw = (cw + SEL_THREADS - 1) / SEL_THREADS * SEL_THREADS;
+  if (cw < SEL_THREADS) cw = SEL_THREADS;
+  g.chunk_words = cw;
+  g.chunks = (int)((W + cw - 1) / cw);
+  return g;
+}
+static size_t sel_fused_ws_bytes(int64_t rows, int64_t W) {
+  return (size_t)4 * rows * sel_fused_geom(W).chunks * 256 * sizeof(unsigned int);
+}
+
+// The selection state after the first `ndig` digits, replayed from their chunk histograms
+// ch[digit][row][chunk][256].  Called by all SEL_THREADS threads; the result is uniform.
+template <int KEYBITS>
+__device__ SelState sel_replay(const unsigned int* __restrict__ ch, int64_t rows, int64_t row, int chunks,
+                               int ndig, long long k, long long* scan, SelState* st_sm) {
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    SelState s0;
+    s0.prefix = 0u; s0.pmask = 0u; s0.need = k; s0.mode = k <= 0 ? 2 : 0; s0.pad = 0;
+    *st_sm = s0;
+  }
+  __syncthreads();
+  for (int d = 0; d < ndig; ++d) {
+    SelState st = *st_sm;
+    __syncthreads();  // everyone holds the state before anyone replaces it
+    if (st.mode != 0) break;
+    const int shift = KEYBITS - 8 * (d + 1);
+    const int bin = 255 - tid;  // the exclusive scan in thread order counts the keys above the bin
+    const unsigned int* hp = ch + (((int64_t)d * rows + row) * chunks) * 256 + bin;
+    long long cnt = 0;
+    for (int c = 0; c < chunks; ++c) cnt += hp[(int64_t)c * 256];
+    long long total;
+    const long long above = sah_block_excl_scan<long long>(cnt, scan, &total);
+    if (total < st.need || (d == 0 && total <= st.need)) {
+      if (tid == 0) st_sm->mode = 1;  // every candidate is selected
+    } else if (above < st.need && above + cnt >= st.need) {
+      st.prefix |= (unsigned int)bin << shift;
+      st.pmask |= 255u << shift;
+      st.need -= above;
+      *st_sm = st;
+    }
+    __syncthreads();
+  }
+  const SelState out = *st_sm;
+  __syncthreads();
+  return out;
+}
+
+template <typename T, int KEYBITS>
+__global__ void __launch_bounds__(SEL_THREADS)
+sel_fused_hist_kernel(const T* __restrict__ scores, int64_t S, int64_t W, int64_t col_begin, int64_t col_end,
+                      const uint32_t* __restrict__ prev_bits, long long k, unsigned int* __restrict__ ch,
+                      int64_t rows, int chunks, int64_t chunk_words, int digit, int vec) {
+  __shared__ unsigned int hs[SEL_THREADS / 32][256];
+  __shared__ long long scan[33];
+  __shared__ SelState st_sm;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int64_t row = blockIdx.y, chunk = blockIdx.x;
+  const SelState st = sel_replay<KEYBITS>(ch, rows, row, chunks, digit, k, scan, &st_sm);
+  unsigned int* outp = ch + (((int64_t)digit * rows + row) * chunks + chunk) * 256;
+  if (st.mode != 0) {  // the whole CTA: nothing left to refine
+    outp[tid] = 0u;
+    return;
+  }
+  for (int i = tid; i < (SEL_THREADS / 32) * 256; i += SEL_THREADS) (&hs[0][0])[i] = 0u;
+  __syncthreads();
+  const int shift = KEYBITS - 8 * (digit + 1);
+  const int64_t w_end = (chunk + 1) * chunk_words < W ? (chunk + 1) * chunk_words : W;
+  for (int64_t w = chunk * chunk_words + tid; w < w_end; w += SEL_THREADS) {
+    const uint32_t valid = sel_valid(prev_bits[row * W + w], w, col_begin, col_end);
+    if (valid) {
+      unsigned int keys[32];
+      sel_load_keys<T, KEYBITS>(scores + row * S, w, S, vec != 0, keys);
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (((valid >> i) & 1u) && (keys[i] & st.pmask) == st.prefix)
+          atomicAdd(&hs[warp][(keys[i] >> shift) & 255u], 1u);
+    }
+  }
+  __syncthreads();
+  unsigned int sum = 0u;
+#pragma unroll
+  for (int i = 0; i < SEL_THREADS / 32; ++i) sum += hs[i][tid];
+  outp[tid] = sum;
+}
+
+template <typename T, int KEYBITS>
+__global__ void __launch_bounds__(SEL_THREADS)
+sel_fused_emit_kernel(const T* __restrict__ scores, int64_t S, int64_t W, int64_t col_begin, int64_t col_end,
+                      const uint32_t* __restrict__ prev_bits, long long k, const unsigned int* __restrict__ ch,
+                      int64_t rows, int chunks, int64_t chunk_words, int vec, uint32_t* __restrict__ out_bits) {
+  __shared__ long long scan[33];
+  __shared__ SelState st_sm;
+  __shared__ long long before_sm;
+  const int tid = threadIdx.x;
+  const int64_t row = blockIdx.y, chunk = blockIdx.x;
+  constexpr int NDIG = KEYBITS / 8;
+  const SelState st = sel_replay<KEYBITS>(ch, rows, row, chunks, NDIG, k, scan, &st_sm);
+  // ties: keys equal to the threshold in the chunks before this one are served first
+  if (tid < 32) {
+    long long e = 0;
+    if (st.mode == 0 && tid < chunk)
+      e = ch[(((int64_t)(NDIG - 1) * rows + row) * chunks + tid) * 256 + (st.prefix & 255u)];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) e += __shfl_xor_sync(0xffffffffu, e, o);
+    if (tid == 0) before_sm = e;
+  }
+  __syncthreads();
+  long long running = before_sm;
+  const int64_t w0 = chunk * chunk_words;
+  const int64_t w_end = w0 + chunk_words < W ? w0 + chunk_words : W;
+  for (int64_t wb = w0; wb < w_end; wb += SEL_THREADS) {
+    const int64_t w = wb + tid;
+    uint32_t pw = 0u, gt = 0u, eq = 0u;
+    if (w < w_end) {
+      pw = prev_bits[row * W + w];
+      const uint32_t valid = sel_valid(pw, w, col_begin, col_end);
+      if (st.mode == 1) {
+        gt = valid;
+      } else if (st.mode == 0 && valid) {
+        unsigned int keys[32];
+        sel_load_keys<T, KEYBITS>(scores + row * S, w, S, vec != 0, keys);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          gt |= (keys[i] > st.prefix ? 1u : 0u) << i;
+          eq |= (keys[i] == st.prefix ? 1u : 0u) << i;
+        }
+        gt &= valid;
+        eq &= valid;
+      }
+    }
+    long long total;
+    const long long before = sah_block_excl_scan<long long>((long long)__popc(eq), scan, &total);
+    if (w < w_end) {
+      const long long quota = st.need - (running + before);
+      const int take = st.mode != 0 ? 0 : (quota > 32 ? 32 : (quota < 0 ? 0 : (int)quota));
+      out_bits[row * W + w] = pw | gt | sah_lowest_bits(eq, take);
+    }
+    running += total;
+  }
+}
+
 extern "C" int64_t sah_topk_select_ws_bytes(int64_t rows, int64_t W) {
   if (rows <= 0 || W <= 0) return 0;
-  return (int64_t)sel_ws_bytes(rows, (W + SEL_CHUNK_WORDS - 1) / SEL_CHUNK_WORDS);
+  const size_t stepwise = sel_ws_bytes(rows, (W + SEL_CHUNK_WORDS - 1) / SEL_CHUNK_WORDS);
+  const size_t fused = sel_fused_ws_bytes(rows, W);
+  return (int64_t)(stepwise > fused ? stepwise : fused);
 }
 
 // ---- the selection step by step (a multi-rank caller reduces the digit histogram between
@@ -570,17 +730,21 @@ extern "C" int sah_topk_sel_emit(const void* scores, int dtype, int64_t rows, in
 template <typename T, int KEYBITS>
 static int sel_run(const T* scores, int64_t rows, int64_t S, int64_t W, int64_t col_begin, int64_t col_end,
                    const uint32_t* prev_bits, int64_t k, uint32_t* out_bits, void* ws, cudaStream_t st) {
-  int rc = sah_topk_sel_begin(rows, W, k, ws, sah_topk_select_ws_bytes(rows, W), st);
-  if (rc != SAH_OK) return rc;
+  const SelFusedGeom g = sel_fused_geom(W);
+  unsigned int* ch = reinterpret_cast<unsigned int*>(ws);
+  const int vec = ((S * (int64_t)sizeof(T)) % 16 == 0 && ((uintptr_t)scores % 16) == 0) ? 1 : 0;
+  dim3 grid((unsigned)g.chunks, (unsigned)rows);
   if (k > 0) {
-    for (int shift = KEYBITS - 8; shift >= 0; shift -= 8) {
-      rc = sel_hist_step<T, KEYBITS>(scores, rows, S, W, col_begin, col_end, prev_bits, ws, shift, st);
-      if (rc != SAH_OK) return rc;
-      rc = sah_topk_sel_pick(rows, W, ws, shift, shift == KEYBITS - 8 ? 1 : 0, nullptr, st);
-      if (rc != SAH_OK) return rc;
+    for (int digit = 0; digit < KEYBITS / 8; ++digit) {
+      sel_fused_hist_kernel<T, KEYBITS><<<grid, SEL_THREADS, 0, st>>>(
+          scores, S, W, col_begin, col_end, prev_bits, (long long)k, ch, rows, g.chunks, g.chunk_words, digit, vec);
+      SAH_LAUNCH_CHECK("topk_select digit histogram");
     }
   }
-  return sel_emit_step<T, KEYBITS>(scores, rows, S, W, col_begin, col_end, prev_bits, ws, nullptr, out_bits, st);
+  sel_fused_emit_kernel<T, KEYBITS><<<grid, SEL_THREADS, 0, st>>>(
+      scores, S, W, col_begin, col_end, prev_bits, (long long)k, ch, rows, g.chunks, g.chunk_words, vec, out_bits);
+  SAH_LAUNCH_CHECK("topk_select emit");
+  return SAH_OK;
 }
 
 extern "C" int sah_topk_select_ws(const void* scores, int dtype, int64_t rows, int64_t S, int64_t W,

@@ -99,6 +99,7 @@ _SIGNATURES = {
     "sah_mask_rowwise_scatter": [_P, _P, _I, _L, _L, _L, _P, _P, _P],
     "sah_mask_flat_add": [_P, _P, _I, _L, _L, _P, _P],
     "sah_mask_clamp_to_dense": [_P, _I, _L, _P, _P],
+    "sah_attn_select_kernel": [_I],
     "sah_attn_gather_probe": [_P, _P, _L, _L, _L, _L, _L, _L, _I, _I, _I, _L, _I, POINTER(AttnSizes),
                               _P, _P, _P, _P],
     "sah_adaptive_budget": [_P, _I, c_float, _P, _L, _L, _L, _P, _P, _P, _P, _I, _I, _I, _L, _L, _L,

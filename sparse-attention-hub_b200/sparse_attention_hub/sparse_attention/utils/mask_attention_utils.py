@@ -236,6 +236,19 @@ def last_union_list():
             ws["ucount"][:groups], R)
 
 
+ATTENTION_KERNELS = {"auto": -1, "mma": 0, "umma": 1}
+
+
+def select_attention_kernel(which: str) -> str:
+    """Choose the bfloat16 attention kernel of this process (`sah_attn_select_kernel`): "mma"
+    (per-warp mma.sync over 16-key tiles), "umma" (tcgen05 over 128-key tiles, head dim 128) or
+    "auto" (the library decides per call).  Returns the previous choice."""
+    if which not in ATTENTION_KERNELS:
+        raise ValueError(f"attention kernel {which!r}: one of {sorted(ATTENTION_KERNELS)}")
+    prev = _native.load().sah_attn_select_kernel(ATTENTION_KERNELS[which])
+    return {v: k for k, v in ATTENTION_KERNELS.items()}[prev]
+
+
 def gather_probe(keys: torch.Tensor, values: torch.Tensor, seq_len_queries: int = 1) -> None:
     """Launch the row-gather probe (`sah_attn_gather_probe`) on the union list of the most recent
     bfloat16 attention call over these keys and values: the copy pipeline of the attention kernel
