@@ -53,7 +53,8 @@ UNIT = "tokens/s/layer"
 MIN_REGION_MS = 100.0
 
 # name: (keys, keys with --small)
-LONG_WORKLOADS = {"magicpig": (1048576, 65536), "hashattention_long": (1048576, 65536)}
+LONG_WORKLOADS = {"magicpig": (1048576, 65536), "hashattention_long": (1048576, 65536),
+                  "pqcache_long": (262144, 65536)}
 DEFAULT_WORKLOAD = "magicpig"
 # keys of the long sequences that the reference is timed on (it is dense in the key count and
 # materialises [B, Hq, S, L] int64 signatures: ~0.4 MB of temporaries per key)
@@ -105,6 +106,10 @@ def long_stack(name: str, seed: int, Hq: int, D: int):
             workloads._rng(seed, 70).standard_normal((D + 1, 75 * 8)).astype(np.float32), "bf16")
         return [("sink", {"sink_size": 64}), ("local", {"window_size": 256}),
                 ("magicpig", {"lsh_l": 75, "lsh_k": 8, "center": True, "projection": proj})]
+    if name == "pqcache_long":
+        return [("sink", {"sink_size": 64}), ("local", {"window_size": 256}),
+                ("pq_topk", {"heavy_size": 2048, "pq_group_factor": 16, "pq_bits": 8, "kmeans_iter": 10,
+                             "init_offset": 64, "metric": "euclidean"})]
     w = {n: [workloads.to_dtype(a, "bf16") for a in arrs]
          for n, arrs in workloads.hat_weights(seed, Hq, D, 128, 32, 3).items()}
     return [("sink", {"sink_size": 128}), ("local", {"window_size": 512}),
@@ -616,6 +621,8 @@ def run_native(args) -> None:
 
     if rank == 0:
         hbm_peak, peak_src = _peaks()
+        from sparse_attention_hub.sparse_attention.utils.mask_attention_utils import last_attention_kernel
+        attention_kernel_name = last_attention_kernel()
         ms_per_pass = total_ms / passes
         tokens = B * world
         attn_ms, attn_n = prof["attention"]
@@ -656,7 +663,7 @@ def run_native(args) -> None:
                 "kernel_us": stage_times,
             }),
             "roofline": {
-                "kernel": "masked_attention kernel (K/V row gather + weighted online softmax)",
+                "kernel": f"{attention_kernel_name} (K/V row gather + weighted online softmax)",
                 "bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                 "frac": achieved / hbm_peak if hbm_peak else None, "peak_source": peak_src,
                 "frac_of_nominal_8TBs": achieved / 8000.0,
@@ -841,6 +848,8 @@ def run_long_native(args) -> None:
     stage_bytes = {"attention": attn_bytes}
     if args.workload == "magicpig":
         stage_bytes["lsh_match"] = B * Hkv * n_local * 75
+    elif args.workload == "pqcache_long":
+        stage_bytes["pq_scores"] = B * Hkv * n_local * 16  # one code byte per sub-vector
     else:
         stage_bytes["hash_topk"] = B * Hq * n_local * 4  # the packed codes, once
     step_bytes = sum(stage_bytes.values())
@@ -857,6 +866,7 @@ def run_long_native(args) -> None:
     host_inputs = [(k[:, :, n_local - 1:, :], kn_host), (v[:, :, n_local - 1:, :], vn_host)] if last else []
     sig = meta.get("key_signature", {}).get(0)
     key_cache = meta.get("key", {}).get(0)
+    pq_codes = meta.get("pq_codebook", {}).get(0)
 
     def mark_appended():
         if sig is not None:       # MagicPig: PackedLSHSignatures
@@ -865,6 +875,8 @@ def run_long_native(args) -> None:
             sig.synced_total = None  # keys arrived somewhere: the maximum norm is agreed on again
         if key_cache is not None and last:  # HashAttention: packed key codes
             key_cache.length = n_local - 1
+        if pq_codes is not None and last:   # PQCache: the appended key is quantised inside the step
+            pq_codes.length -= 1
 
     q_dev = torch.empty_like(q)
     if not args.eager:
@@ -916,11 +928,13 @@ def run_long_native(args) -> None:
         probe_ms, probe_n = prof["other"]
         probe_gbs = (union_rows * row_bytes / (probe_ms / probe_n * 1e-3) / 1e9) if probe_n else None
         # the roofline object describes the kernel that takes the largest share of the pass
-        names = {"attention": "masked_attention_mma_kernel (K/V row gather + weighted online softmax, "
+        from sparse_attention_hub.sparse_attention.utils.mask_attention_utils import last_attention_kernel
+        names = {"attention": f"{last_attention_kernel()} (K/V row gather + weighted online softmax, "
                               "MagicPig weights evaluated in place)" if args.workload == "magicpig"
-                              else "masked_attention_mma_kernel (K/V row gather + online softmax)",
+                              else f"{last_attention_kernel()} (K/V row gather + online softmax)",
                  "lsh_match": "lsh_match_kernel (stream of the packed SimHash signatures)",
-                 "hash_topk": "hash_hist + hash_emit (stream of the packed hash codes)"}
+                 "hash_topk": "hash_hist + hash_emit (stream of the packed hash codes)",
+                 "pq_scores": "pq_scores_kernel (stream of the product-quantisation codes)"}
         dom = max((s for s in stage_bytes if s in stage_times), key=lambda s: stage_times[s])
         dom_us = stage_times[dom]
         achieved = stage_bytes[dom] / (dom_us * 1e-6) / 1e9 if dom_us > 0 else 0.0

@@ -446,6 +446,22 @@ int sah_lsh_key_sign(const void* keys, int dtype, int64_t ks_b, int64_t ks_h, in
                      const unsigned int* max_norm_bits, const void* proj, int L, int K,
                      int64_t cap, void* codes, void* stream);
 
+/* The same signatures for bfloat16 keys of head dim 128 with 8 bits per table, with the
+ * projections computed on the tensor cores (tcgen05) and every sign that the summation order
+ * could have changed redone in the fixed order of sah_lsh_key_sign, so the codes are bit for
+ * bit the same (magic_pig.py:120-150, :332-372).  `workspace` (16-byte aligned,
+ * sah_lsh_key_sign_tc_ws_bytes) starts with two status words that the caller may read after the
+ * stream has finished: [0] the number of 32-column groups that were redone -- a value above
+ * (workspace_bytes - 16) / 16 means the list overflowed and the range must be redone with
+ * sah_lsh_key_sign; [1] non-zero when a bounded wait inside the kernel ran out (the range must
+ * be redone as well). */
+int64_t sah_lsh_key_sign_tc_ws_bytes(int B, int Hkv, int64_t n_keys);
+int sah_lsh_key_sign_tc(const void* keys, int64_t ks_b, int64_t ks_h, int64_t ks_s, int B, int Hkv,
+                        int64_t s0, int64_t s1, int D, const void* mean, const float* norms,
+                        const unsigned int* max_norm_bits, const void* proj, int L, int K,
+                        int64_t cap, void* codes, void* workspace, int64_t workspace_bytes,
+                        int sm_count, void* stream);
+
 /* Per mask row (b, h, q): centred query normalised to unit length, its L codes
  * (qcodes [rows][L], same code type as the key codes, no padding) and the unit vector of the
  * transformed query (qunit float [rows][D]; the appended column is zero).
@@ -648,12 +664,32 @@ int sah_attn_gather_probe(const void* k, const void* v, int64_t ks_b, int64_t ks
 #define SAH_ATTN_KERNEL_MMA 0
 #define SAH_ATTN_KERNEL_UMMA 1
 int sah_attn_select_kernel(int which);
+/* Name of the attention kernel that the most recent sah_masked_attention* call launched. */
+const char* sah_attn_last_kernel(void);
 
 /* Merge n_parts partial results (parts [n_parts][rows][D+2], the part_out of
  * sah_masked_attention on every shard) into out [B][Sq][Hq][D]: the
  * associative combine of sequence-sharded softmax partials. */
 int sah_attn_merge_parts(const float* parts, int n_parts, int B, int Hq, int Sq, int D,
                          const float* sinks, int dtype, void* out, void* stream);
+
+/* Exchange + merge of the sequence shards' partials over peer memory, one launch per rank per
+ * step (replaces an all-gather of part_out followed by sah_attn_merge_parts; the reference has
+ * no sequence sharding, its softmax over the whole row is utils/mask_attention_utils.py:269-340).
+ * Every rank owns a receive buffer of sah_attn_exchange_bytes() bytes and a flag array of
+ * world * rows ints, both zeroed once and mapped by every peer; peer_bufs[p] / peer_flags[p]
+ * (host arrays of `world` device pointers) are rank p's buffer and flags as addressed from
+ * this process.  `steps` ([rows] ints, zeroed once, private to the rank) carries the step
+ * number, so the launch can be replayed by a CUDA graph; all ranks must make the same
+ * sequence of calls.  The kernel stores this rank's partial into every rank's buffer, signals,
+ * waits (bounded: about a second, then *errflag = 2 and the kernel still returns) for the
+ * other ranks' partials and writes out [B][Sq][Hq][D].  The kernels of different ranks wait
+ * on one another: one rank per GPU. */
+int64_t sah_attn_exchange_bytes(int world, int B, int Hq, int Sq, int D);
+int sah_attn_exchange_merge(const float* part, const void* const* peer_bufs,
+                            const void* const* peer_flags, int rank, int world, int B, int Hq, int Sq,
+                            int D, const float* sinks, int dtype, int* steps, int* errflag, void* out,
+                            void* stream);
 
 /* Masked attention that brings its own scratch: plan + gather attention for a
  * unit-weight bitmap mask, with the union lists, counters and split partials

@@ -483,6 +483,8 @@ struct AttnCfg {
   static constexpr int STAGE_BYTES = 2 * TILE * ROWB;    // K tile + V tile
 };
 
+static const char* g_last_attn_kernel = "none";
+
 #include "sah_attention_tc.cuh"
 #include "sah_attention_umma.cuh"
 
@@ -916,6 +918,7 @@ static int masked_attention_impl(const void* q, const void* k, const void* v, in
                                  &launched);
       if (rc != SAH_OK) return rc;
       if (launched) {
+        g_last_attn_kernel = "masked_attention_umma_kernel";
         SAH_LAUNCH_CHECK("masked_attention_umma");
         sah_prof_end(SAH_PROF_ATTENTION, (cudaStream_t)stream);
         return SAH_OK;
@@ -925,6 +928,7 @@ static int masked_attention_impl(const void* q, const void* k, const void* v, in
              ? launch_attention_mma<128>(a, B, groups, tickets, errflag, sinks, out, part_out, lsh != nullptr, st)
              : launch_attention_mma<64>(a, B, groups, tickets, errflag, sinks, out, part_out, lsh != nullptr, st);
     if (rc != SAH_OK) return rc;
+    g_last_attn_kernel = "masked_attention_mma_kernel";
     SAH_LAUNCH_CHECK("masked_attention_mma");
     sah_prof_end(SAH_PROF_ATTENTION, (cudaStream_t)stream);
     return SAH_OK;
@@ -935,6 +939,7 @@ static int masked_attention_impl(const void* q, const void* k, const void* v, in
   rc = (D == 128) ? launch_attention<float, 128>(a, groups, st)
                   : launch_attention<float, 64>(a, groups, st);
   if (rc != SAH_OK) return rc;
+  g_last_attn_kernel = "masked_attention_kernel";
   SAH_LAUNCH_CHECK("masked_attention");
   sah_prof_end(SAH_PROF_ATTENTION, (cudaStream_t)stream);
   sah_prof_begin(SAH_PROF_ATTN_MERGE, (cudaStream_t)stream);
@@ -956,6 +961,8 @@ extern "C" int sah_debug_umma_prof(long long* host_out, int reset) {
   return 0;
 }
 #endif
+
+extern "C" const char* sah_attn_last_kernel(void) { return g_last_attn_kernel; }
 
 extern "C" int sah_attn_select_kernel(int which) {
   if (which < -1 || which > 1) return -2;
@@ -1091,6 +1098,150 @@ extern "C" int sah_attn_merge_parts(const float* parts, int n_parts, int B, int 
         parts, n_parts, rows, Hq, Sq, D, sinks, (T*)out);
   });
   SAH_LAUNCH_CHECK("attn_merge_parts");
+  return SAH_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Exchange + merge of sequence-shard partials over peer memory (NVLink): one kernel per rank
+// per step instead of an all-gather and a merge kernel.
+//
+// Every rank owns a receive buffer [2 parities][world][rows][D+2] floats and a flag array
+// [world][rows] ints in memory that its peers have mapped.  One CTA per row:
+//   1. stores its rank's partial of the row into every rank's receive buffer (its own too),
+//      slot [step parity][my rank][row], with plain stores to the peer addresses,
+//   2. fences at system scope and stores the step number into every rank's flag [my rank][row],
+//   3. waits until the flags [src][row] of its own array have reached the step number -- a
+//      bounded wait (about a second): when it runs out the error word is set and the row is
+//      merged from what is there, so that the kernel always returns,
+//   4. merges the world's partials of the row exactly as attn_merge_parts_kernel does.
+// The step number of a row lives in device memory (`steps[row]`, advanced by the row's CTA),
+// so a CUDA graph can replay the launch.  Two parities make the buffer safe: a rank can be at
+// most one step ahead of a peer (step e + 1 cannot end before the peer has started it, i.e.
+// finished step e), and a slot of parity e & 1 is next written at step e + 2.
+// The kernels of different ranks wait on one another: they must run on different GPUs.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ int sah_ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void sah_st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long sah_globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+  return t;
+}
+
+#define SAH_XCHG_MAX_WORLD 16
+
+struct XchgPeers {
+  float* buf[SAH_XCHG_MAX_WORLD];
+  int* flag[SAH_XCHG_MAX_WORLD];
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+attn_exchange_merge_kernel(const float* __restrict__ part, XchgPeers peers, int rank, int world, int64_t rows,
+                           int Hq, int Sq, int D, const float* __restrict__ sinks, int* __restrict__ steps,
+                           int* __restrict__ errflag, T* __restrict__ out) {
+  __shared__ float scale_sm[SAH_XCHG_MAX_WORLD];
+  __shared__ float ml_sm[2];
+  const int64_t row = blockIdx.x;
+  const int tid = threadIdx.x;
+  const int64_t ld = D + 2;
+  const int step = steps[row] + 1;
+  const int par = step & 1;
+  // 1. this rank's partial of the row to every rank
+  const float* src = part + row * ld;
+  for (int i = tid; i < world * (int)ld; i += blockDim.x) {
+    const int p = i / (int)ld, e = i - p * (int)ld;
+    peers.buf[p][(((int64_t)par * world + rank) * rows + row) * ld + e] = src[e];
+  }
+  // 2. publish
+  __threadfence_system();
+  __syncthreads();
+  if (tid < world) sah_st_release_sys(peers.flag[tid] + (int64_t)rank * rows + row, step);
+  // 3. wait for every rank's partial of this row
+  if (tid < world) {
+    const int* f = peers.flag[rank] + (int64_t)tid * rows + row;
+    const unsigned long long t0 = sah_globaltimer_ns();
+    bool ok = false;
+    for (long long spin = 0; spin < (1ll << 40); ++spin) {
+      if (sah_ld_acquire_sys(f) - step >= 0) { ok = true; break; }
+      if ((spin & 1023) == 1023 && sah_globaltimer_ns() - t0 > 1000000000ull) break;
+    }
+    if (!ok) atomicExch(errflag, 2);
+  }
+  __syncthreads();
+  // 4. merge (reads bypass L1: the lines were written by other GPUs)
+  const float* mine = peers.buf[rank] + ((int64_t)par * world * rows + row) * ld;
+  const int64_t pstride = rows * ld;
+  if (tid == 0) {
+    float M = -INFINITY;
+    for (int p = 0; p < world; ++p) M = fmaxf(M, __ldcv(mine + p * pstride + D));
+    float L = 0.f;
+    for (int p = 0; p < world; ++p) {
+      const float mp = __ldcv(mine + p * pstride + D);
+      const float sc = (mp == -INFINITY) ? 0.f : expf(mp - M);
+      scale_sm[p] = sc;
+      L += __ldcv(mine + p * pstride + D + 1) * sc;
+    }
+    ml_sm[0] = M;
+    ml_sm[1] = L;
+    steps[row] = step;
+  }
+  __syncthreads();
+  const int qi = (int)(row % Sq);
+  const int64_t bh = row / Sq;
+  const int h = (int)(bh % Hq);
+  const int64_t b = bh / Hq;
+  const float M = ml_sm[0], L = ml_sm[1];
+  float Mx = M, sink_term = 0.f;
+  if (sinks != nullptr) {
+    const float sk = sinks[h];
+    Mx = fmaxf(M, sk);
+    sink_term = expf(sk - Mx);
+  }
+  const float resc = (M == -INFINITY) ? 0.f : expf(M - Mx);
+  const float den = L * resc + sink_term;
+  for (int d = tid; d < D; d += blockDim.x) {
+    float acc = 0.f;
+    for (int p = 0; p < world; ++p) {
+      const float sc = scale_sm[p];
+      if (sc != 0.f) acc += __ldcv(mine + p * pstride + d) * sc;
+    }
+    out[((b * Sq + qi) * Hq + h) * D + d] = sah_from_float<T>(acc * resc / den);
+  }
+}
+
+extern "C" int64_t sah_attn_exchange_bytes(int world, int B, int Hq, int Sq, int D) {
+  if (world <= 0 || B <= 0 || Hq <= 0 || Sq <= 0 || D <= 0) return 0;
+  return 2ll * world * B * Hq * Sq * (D + 2) * (int64_t)sizeof(float);
+}
+
+extern "C" int sah_attn_exchange_merge(const float* part, const void* const* peer_bufs,
+                                       const void* const* peer_flags, int rank, int world, int B, int Hq,
+                                       int Sq, int D, const float* sinks, int dtype, int* steps,
+                                       int* errflag, void* out, void* stream) {
+  SAH_REQUIRE(part && peer_bufs && peer_flags && steps && errflag && out, "attn_exchange_merge: null pointer");
+  SAH_REQUIRE(world > 0 && world <= SAH_XCHG_MAX_WORLD && rank >= 0 && rank < world,
+              "attn_exchange_merge: bad rank / world (at most 16 ranks)");
+  SAH_REQUIRE(B > 0 && Hq > 0 && Sq > 0 && D > 0, "attn_exchange_merge: bad extents");
+  XchgPeers peers;
+  for (int p = 0; p < SAH_XCHG_MAX_WORLD; ++p) {
+    peers.buf[p] = p < world ? reinterpret_cast<float*>(const_cast<void*>(peer_bufs[p])) : nullptr;
+    peers.flag[p] = p < world ? reinterpret_cast<int*>(const_cast<void*>(peer_flags[p])) : nullptr;
+    if (p < world) SAH_REQUIRE(peers.buf[p] && peers.flag[p], "attn_exchange_merge: null peer pointer");
+  }
+  const int64_t rows = (int64_t)B * Hq * Sq;
+  int threads = D + 2 < 64 ? 64 : (D + 2 > 256 ? 256 : ((D + 2 + 31) / 32) * 32);
+  SAH_DISPATCH_DTYPE(dtype, T, {
+    attn_exchange_merge_kernel<T><<<(unsigned)rows, threads, 0, (cudaStream_t)stream>>>(
+        part, peers, rank, world, rows, Hq, Sq, D, sinks, steps, errflag, (T*)out);
+  });
+  SAH_LAUNCH_CHECK("attn_exchange_merge");
   return SAH_OK;
 }
 

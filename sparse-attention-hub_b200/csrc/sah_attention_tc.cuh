@@ -35,6 +35,7 @@
 // the error word, the warp stops consuming tiles, and the kernel still goes through its
 // merge and ticket protocol so that no other CTA is left waiting.
 #include <cuda.h>
+#include "sah_tcgen05.cuh"
 
 #ifndef ATM_WARPS
 #define ATM_WARPS 4
@@ -45,39 +46,13 @@
 #define ATM_THREADS (ATM_WARPS * 32)
 #define ATM_TILE 16
 #define ATM_MIN_TILES 8        // tiles a warp should have before a further CTA joins the group
-#define ATM_SPIN_LIMIT (1 << 19)
+#define ATM_ONE_WAVE_TILES 48  // below this many tiles per warp, one wave of CTAs instead of two
+#define ATM_FINE_SPLITS 16     // ... when the grid has at least this many CTAs per group
 
 struct AtmMaps {
   CUtensorMap k, v;
 };
 
-// ---- mbarrier / tensor-map gather ------------------------------------------------
-__device__ __forceinline__ void atm_mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void atm_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-// One try of the phase test; the hardware may suspend the thread for up to `hint_ns` while the
-// phase is pending, so a waiting warp does not compete for issue slots.
-__device__ __forceinline__ bool atm_mbar_try(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
-  uint32_t ok;
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
-      "selp.u32 %0, 1, 0, p;\n}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(hint_ns)
-      : "memory");
-  return ok != 0u;
-}
-// Bounded wait: false when the phase did not complete within the limit (about a second).
-__device__ __forceinline__ bool atm_mbar_wait(uint32_t bar, uint32_t parity) {
-  for (int i = 0; i < ATM_SPIN_LIMIT; ++i)
-    if (atm_mbar_try(bar, parity, 2000u)) return true;
-  return false;
-}
 // Four rows y0..y3 of the 2-D tensor, columns [x, x + box width), to shared memory.
 __device__ __forceinline__ void atm_tma_gather4(uint32_t dst, const CUtensorMap* map, int x, int y0,
                                                 int y1, int y2, int y3, uint32_t bar) {
@@ -131,17 +106,19 @@ __device__ __forceinline__ uint32_t atm_pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__device__ __forceinline__ void atm_cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
-}
 
-// CTAs that share one group's union list.  The grid holds nsplit per group, sized for long
-// lists.  A short list is shared by fewer of them, so that every warp still has a run of
-// ATM_MIN_TILES tiles to pipeline and the last CTA merges few partials; the others leave at
-// once (they hold no ticket).
+// CTAs that share one group's union list.  The grid holds nsplit per group: two waves of the
+// device for long lists (the second wave evens out groups of different length).  When the
+// groups are few (nsplit >= ATM_FINE_SPLITS) and a list would give a warp fewer than
+// ATM_ONE_WAVE_TILES tiles in that arrangement, half of the CTAs work on it: one wave, half as
+// many pipeline fills and partials.  A short list is shared by as few CTAs as give every warp
+// a run of ATM_MIN_TILES tiles; the others leave at once (they hold no ticket).
 __device__ __forceinline__ int atm_active_splits(int total_tiles, int nsplit) {
-  int active = (total_tiles + ATM_WARPS * ATM_MIN_TILES - 1) / (ATM_WARPS * ATM_MIN_TILES);
-  return active < 1 ? 1 : (active > nsplit ? nsplit : active);
+  int active = nsplit;
+  if (nsplit >= ATM_FINE_SPLITS && total_tiles < nsplit * ATM_WARPS * ATM_ONE_WAVE_TILES) active = nsplit / 2;
+  const int by_length = (total_tiles + ATM_WARPS * ATM_MIN_TILES - 1) / (ATM_WARPS * ATM_MIN_TILES);
+  if (by_length < active) active = by_length;
+  return active < 1 ? 1 : active;
 }
 
 template <int D, bool TMA = false, int NST = ATM_STAGES>
@@ -231,18 +208,23 @@ __device__ __forceinline__ void atm_finish_group(const AttnArgs& a, int64_t g, i
     }
   }
   __syncthreads();
-  // phase 2: every (row, dim) sums its column over the splits; the loads are independent
-  for (int idx = tid; idx < a.R * D; idx += NT) {
-    const int r = idx / D, d = idx - r * D;
+  // phase 2: every thread owns (row, pair of dims) items and sums them over the splits with
+  // 8-byte loads, eight in flight
+  for (int idx = tid; idx < a.R * (D / 2); idx += NT) {
+    const int r = idx / (D / 2), d = (idx - r * (D / 2)) * 2;
     const int gi = r / a.q_block, qo = r - gi * a.q_block;
     const int qi = qb * a.q_block + qo;
     if (qi >= a.Sq) continue;
     const int h = kvh * a.G + gi;
     const float* pr = p0 + (int64_t)r * (D + 2) + d;
     const float* sc = sc_sm + r * active;
-    float accv = 0.f;
+    float2 accv = make_float2(0.f, 0.f);
 #pragma unroll 8
-    for (int s2 = 0; s2 < active; ++s2) accv = fmaf(__ldcg(pr + s2 * pstride), sc[s2], accv);
+    for (int s2 = 0; s2 < active; ++s2) {
+      const float2 x = __ldcg(reinterpret_cast<const float2*>(pr + s2 * pstride));
+      accv.x = fmaf(x.x, sc[s2], accv.x);
+      accv.y = fmaf(x.y, sc[s2], accv.y);
+    }
     const float M = ml_sm[r * 2], L = ml_sm[r * 2 + 1];
     float Mx = M, sink_term = 0.f;
     if (sinks != nullptr) {
@@ -253,8 +235,9 @@ __device__ __forceinline__ void atm_finish_group(const AttnArgs& a, int64_t g, i
     const float resc = (M == -INFINITY) ? 0.f : __expf(M - Mx);
     const float den = L * resc + sink_term;
     const int64_t row = (b * a.Hq + h) * a.Sq + qi;
-    if (part_out != nullptr) part_out[row * (D + 2) + d] = accv;
-    out[((b * a.Sq + qi) * a.Hq + h) * D + d] = __float2bfloat16_rn(accv * resc / den);
+    if (part_out != nullptr) *reinterpret_cast<float2*>(part_out + row * (D + 2) + d) = accv;
+    *reinterpret_cast<__nv_bfloat162*>(out + ((b * a.Sq + qi) * a.Hq + h) * D + d) =
+        __floats2bfloat162_rn(accv.x * resc / den, accv.y * resc / den);
     if (part_out != nullptr && d == 0) {
       part_out[row * (D + 2) + D] = M;
       part_out[row * (D + 2) + D + 1] = L;
@@ -865,8 +848,8 @@ static int launch_attention_mma(AttnArgs a, int B, int groups, int* tickets, int
                                 const float* sinks, void* out, float* part_out, bool lsh,
                                 cudaStream_t st) {
   static bool allowed[9][64] = {};
-  if ((size_t)16 * a.nsplit * 4 + 128 > (size_t)ATM_WARPS * AtmCfg<D, true, 2>::WARP_BYTES)
-    return sah_fail(SAH_ERR_UNSUPPORTED, "attention: %d splits do not fit the merge scratch", a.nsplit);
+  // shared memory that the last CTA of a group needs to merge the splits (atm_finish_group)
+  const size_t merge_bytes = (size_t)16 * a.nsplit * 4 + 128;
   static_assert(AtmCfg<D, false, 2>::RED_BYTES <= AtmCfg<D, false, 2>::WARP_BYTES &&
                 AtmCfg<D, true, 2>::RED_BYTES <= AtmCfg<D, true, 2>::WARP_BYTES,
                 "reduction scratch must fit the ring");
@@ -888,6 +871,8 @@ static int launch_attention_mma(AttnArgs a, int B, int groups, int* tickets, int
 #define ATM_LAUNCH(HALF, LSHW, TMA, NST, SLOT)                                                      \
   do {                                                                                              \
     const int smem = AtmCfg<D, TMA, NST>::SMEM;                                                     \
+    if (merge_bytes > (size_t)ATM_WARPS * AtmCfg<D, TMA, NST>::WARP_BYTES)                          \
+      return sah_fail(SAH_ERR_UNSUPPORTED, "attention: %d splits do not fit the merge scratch", a.nsplit); \
     e = atm_allow_smem(masked_attention_mma_kernel<D, HALF, LSHW, TMA, NST>, smem, allowed[SLOT]);  \
     if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "attention attr: %s", cudaGetErrorString(e)); \
     masked_attention_mma_kernel<D, HALF, LSHW, TMA, NST><<<grid, ATM_THREADS, smem, st>>>(          \

@@ -2,19 +2,27 @@
 //
 // Long union lists are bound by the K/V row gather; the mma.sync kernel spends ~48 warp
 // instructions per key on fragment loads, address arithmetic and the softmax in the mma
-// fragment layout, and its warps stall on each other's issue slots.  Here the keys are the
-// M dimension of the tensor-core tile, so one thread owns one key:
+// fragment layout.  Here the keys are the M dimension of the tensor-core tile, so one thread
+// owns one key:
 //
-//   tile = 128 union entries.  A producer warp gathers their K rows and V rows with tensor-map
-//   gathers (cp.async.bulk.tensor.2d ... tile::gather4, four indexed rows per instruction, no
-//   multicast qualifier) into a three-stage ring in the 128-byte swizzled layout.
+//   tile = 128 union entries.  Four producer warps gather their K rows and V rows with 16-byte
+//   asynchronous copies (16 lanes cover one 256-byte row, so every 32-byte sector that is
+//   fetched is used) into a three-stage ring (separate rings for K and V, with K slots freed as
+//   soon as S^T has completed, measured slower), in the 128-byte swizzled layout that the tensor
+//   core's shared-memory descriptors expect: two halves of [128 rows][128 B] per tile, 16-byte
+//   chunk c of row i at chunk slot c ^ (i % 8).  (Tensor-map gathers, tile::gather4, were
+//   measured first: one gather4 -- four 128-byte rows -- every ~64 cycles per SM, 2.2 TB/s over
+//   the device, below what the copies reach.)
 //     S^T[128 keys x 16]  = Ktile[128 x 128] . Qtile[16 x 128]^T    8 tcgen05.mma (K = 16 each),
-//                           accumulator in tensor memory, double buffered
+//                           accumulator in tensor memory
 //     thread-per-key softmax: each of 128 threads reads its key's row of S^T from tensor memory
 //                           (mask rows in columns), applies scaling, bias, weights and the
 //                           running maximum, and writes the key's row of P (bf16) to shared memory
 //     O^T[128 dims x 16] += Vtile^T[128 dims x 128 keys] . P[128 keys x 16]   8 tcgen05.mma,
 //                           accumulator in tensor memory for the whole list
+//   Two softmax groups of four warps take the even and the odd tiles of the CTA, each with its
+//   own S, P and O buffers and its own running maximum and denominator, so that the softmax of
+//   one tile overlaps the next tile's; the groups are merged in shared memory at the end.
 //   One elected thread issues all tcgen05.mma; completion is tracked with tcgen05.commit on
 //   mbarriers.  The running maximum is lazy: the accumulator is rescaled (tensor memory load,
 //   multiply, store) only when a row's maximum grew by more than AUM_RESCALE_T, so that P stays
@@ -24,15 +32,18 @@
 // With LSHW the columns 4..7 of the Q tile hold the centred unit queries and the MagicPig weight
 // of a (row, key) pair is evaluated by the key's thread exactly as in the mma.sync kernel.
 //
-// Every wait on an mbarrier is bounded (about a second) and watches a CTA-wide abort word; a
-// wait that runs out sets the abort word and the caller's error word, every role leaves its
-// loop, the producer gives its copies in flight a bounded chance to land, tensor memory is
-// freed, and the CTA still takes its ticket so that no other CTA waits for it.
+// Every wait on an mbarrier is bounded (about a second of wall time) and watches a CTA-wide
+// abort word; a wait that runs out sets the abort word and the caller's error word, every role
+// leaves its loop, the producers wait for their copies in flight, tensor memory is freed, and
+// the CTA still takes its ticket so that no other CTA waits for it.
 #pragma once
+#include "sah_tcgen05.cuh"
 
 #define AUM_TILE 128
 #define AUM_STAGES 3
-#define AUM_THREADS 192
+#define AUM_SOFT_WARPS 8     // two groups of four
+#define AUM_PROD_WARPS 4
+#define AUM_THREADS ((AUM_SOFT_WARPS + AUM_PROD_WARPS + 1) * 32)
 #define AUM_TMEM_COLS 64
 #define AUM_RESCALE_T 8.0f
 #define AUM_MIN_TILES 2        // tiles a CTA should have before a further CTA joins the group
@@ -46,14 +57,15 @@ struct AumCfg {
   static constexpr int Q_OFF = 2 * AUM_STAGES * KV_TILE;  // two halves of [16 rows][128 B]
   static constexpr int P_OFF = Q_OFF + 4096;              // two buffers of [128 keys][32 B]
   static constexpr int BAR_OFF = P_OFF + 2 * 4096;
-  // barriers: full_k[3] full_v[3] empty_k[3] empty_v[3] s_full[2] s_free[2] p_full[2] p_free[2] max[2]
-  static constexpr int N_BARS = 4 * AUM_STAGES + 10;
+  // barriers: full[3] empty[3] s_full[2] s_free[2] p_full[2] p_free[2] max[2]
+  static constexpr int N_BARS = 2 * AUM_STAGES + 10;
   static constexpr int MISC_OFF = BAR_OFF + ((N_BARS * 8 + 15) & ~15);
-  // misc: tmem slot, abort word, last flag, pad; then wmax [2][4][16], lred [4][16], qmu [16],
-  // bias offsets [16] (int64)
+  // misc: tmem slot, abort word, last flag, pad; then wmax [2][4][16], lred [2][4][16], group
+  // maxima [2][16], qmu [16], bias offsets [16] (int64)
   static constexpr int WMAX_OFF = MISC_OFF + 16;
   static constexpr int LRED_OFF = WMAX_OFF + 2 * 4 * 16 * 4;
-  static constexpr int QMU_OFF = LRED_OFF + 4 * 16 * 4;
+  static constexpr int GMAX_OFF = LRED_OFF + 2 * 4 * 16 * 4;
+  static constexpr int QMU_OFF = GMAX_OFF + 2 * 16 * 4;
   static constexpr int BOFF_OFF = QMU_OFF + 16 * 4;
   static constexpr int END = BOFF_OFF + 16 * 8;
   static constexpr int SMEM = 1024 + END;
@@ -67,71 +79,6 @@ __device__ __forceinline__ int aum_active_splits(int total_tiles, int nsplit) {
   return active < 1 ? 1 : active;
 }
 
-// Shared-memory matrix descriptor of tcgen05.mma: start address, leading-dimension and stride
-// byte offsets (all in units of 16 bytes), the descriptor version of this architecture, and
-// the swizzle mode (0 none, 2 128-byte).
-__device__ __forceinline__ uint64_t aum_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo, uint32_t layout) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)((lbo >> 4) & 0x3FFFu) << 16;
-  d |= (uint64_t)((sbo >> 4) & 0x3FFFu) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)(layout & 7u) << 61;
-  return d;
-}
-// Instruction descriptor, kind::f16: fp32 accumulator, bf16 operands, M = 128, N = 16;
-// bit 15 / 16: A / B are MN-major (0 = K-major).
-__device__ __forceinline__ uint32_t aum_idesc(bool a_mn, bool b_mn) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
-         ((16u >> 3) << 17) | ((128u >> 4) << 24);
-}
-__device__ __forceinline__ void aum_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                        uint32_t accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// The mbarrier gets one arrival when all tcgen05.mma issued so far by this thread are complete.
-__device__ __forceinline__ void aum_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ void aum_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void aum_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-}
-__device__ __forceinline__ void aum_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-}
-// 8 or 16 consecutive columns of this thread's lane of tensor memory
-__device__ __forceinline__ void aum_tmem_ld8(uint32_t taddr, uint32_t* r) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-               : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ void aum_tmem_ld16(uint32_t taddr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ void aum_tmem_st16(uint32_t taddr, const uint32_t* r) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n" ::
-          "r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
-  asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-}
-
 // P tile (B operand of O^T += V^T . P): [128 keys][16 mask rows] bf16, MN-major (the 16 rows of
 // a key are contiguous: 32 bytes), 32-byte swizzle: 16-byte chunk j of key k sits at slot
 // j ^ ((k >> 2) & 1); 8 keys form a 256-byte atom, a k-step of 16 keys is 512 bytes.
@@ -143,51 +90,6 @@ __device__ __forceinline__ void aum_store_p(unsigned char* base, int key, const 
   const int sw = (key >> 2) & 1;
   *reinterpret_cast<uint4*>(base + key * 32 + (sw << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
   *reinterpret_cast<uint4*>(base + key * 32 + ((sw ^ 1) << 4)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-}
-
-// Bounded wait that also gives up when another role of the CTA has given up.  The phase test
-// carries no suspend-time hint: most waits of this kernel are entered before the phase
-// completes and are satisfied a few hundred cycles later, and a hinted test was seen to keep
-// the thread asleep for a good part of the hint.  The bound is wall time (about a second),
-// looked at every 256 tests.
-__device__ __forceinline__ bool aum_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0u;
-}
-__device__ __forceinline__ uint64_t aum_now_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ bool aum_wait(uint32_t bar, uint32_t parity, volatile int* abort_sm,
-                                         int* __restrict__ errflag) {
-  if (aum_try(bar, parity)) return true;
-  const uint64_t t0 = aum_now_ns();
-  for (int round = 0; round < (1 << 24); ++round) {
-#pragma unroll 1
-    for (int i = 0; i < 256; ++i)
-      if (aum_try(bar, parity)) return true;
-    if (*abort_sm) return false;
-    if (aum_now_ns() - t0 > 1000000000ull) break;
-  }
-  *abort_sm = 1;
-  atomicExch(errflag, 1);
-  return false;
-}
-
-// The same for a whole warp: every lane waits, and the warp continues only if all lanes saw the
-// phase complete, so that no lane leaves a loop that the others stay in.
-__device__ __forceinline__ bool aum_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_sm,
-                                              int* __restrict__ errflag) {
-  const bool ok = aum_wait(bar, parity, abort_sm, errflag);
-  return __all_sync(0xffffffffu, ok);
 }
 
 // float -> int whose signed order is the float order (no NaNs here), for redux.sync
@@ -213,12 +115,11 @@ __device__ long long aum_prof[32];
 // RMAX: mask rows a thread handles (4 or 16); LSHW needs RMAX == 4.
 template <bool LSHW, int RMAX>
 __global__ void __launch_bounds__(AUM_THREADS, 1)
-masked_attention_umma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, int* __restrict__ tickets,
-                             int* __restrict__ errflag, const float* __restrict__ sinks,
-                             __nv_bfloat16* __restrict__ out, float* __restrict__ part_out) {
+masked_attention_umma_kernel(AttnArgs a, int* __restrict__ tickets, int* __restrict__ errflag,
+                             const float* __restrict__ sinks, __nv_bfloat16* __restrict__ out,
+                             float* __restrict__ part_out) {
   static_assert(!LSHW || RMAX == 4, "in-place MagicPig weights: at most 4 mask rows");
   constexpr int D = 128;
-  constexpr int NST = AUM_STAGES;
   using C = AumCfg;
   extern __shared__ __align__(1024) unsigned char aum_raw[];
   const uint32_t raw_s = (uint32_t)__cvta_generic_to_shared(aum_raw);
@@ -245,29 +146,37 @@ masked_attention_umma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, i
 
   // barrier addresses
   const uint32_t bar0 = sm_s + C::BAR_OFF;
-  const uint32_t full_k = bar0, full_v = bar0 + NST * 8, empty_k = bar0 + 2 * NST * 8,
-                 empty_v = bar0 + 3 * NST * 8, s_full = bar0 + 4 * NST * 8, s_free = s_full + 16,
+  constexpr int NST = AUM_STAGES;
+  const uint32_t full = bar0, empty = bar0 + NST * 8, s_full = bar0 + 2 * NST * 8, s_free = s_full + 16,
                  p_full = s_full + 32, p_free = s_full + 48, max_bar = s_full + 64;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + C::MISC_OFF);
   volatile int* abort_sm = reinterpret_cast<volatile int*>(sm + C::MISC_OFF + 4);
   int* is_last_sm = reinterpret_cast<int*>(sm + C::MISC_OFF + 8);
   float* wmax_sm = reinterpret_cast<float*>(sm + C::WMAX_OFF);
   float* lred_sm = reinterpret_cast<float*>(sm + C::LRED_OFF);
+  float* gmax_sm = reinterpret_cast<float*>(sm + C::GMAX_OFF);
   float* qmu_sm = reinterpret_cast<float*>(sm + C::QMU_OFF);
   int64_t* boff_sm = reinterpret_cast<int64_t*>(sm + C::BOFF_OFF);
+  constexpr int MMA_WARP = AUM_SOFT_WARPS + AUM_PROD_WARPS;
 
   if (tid == 0) {
 #pragma unroll
-    for (int i = 0; i < 4 * NST; ++i) atm_mbar_init(bar0 + i * 8, 1);
-    atm_mbar_init(s_full, 1);        atm_mbar_init(s_full + 8, 1);
-    atm_mbar_init(s_free, 128);      atm_mbar_init(s_free + 8, 128);
-    atm_mbar_init(p_full, 128);      atm_mbar_init(p_full + 8, 128);
-    atm_mbar_init(p_free, 1);        atm_mbar_init(p_free + 8, 1);
-    atm_mbar_init(max_bar, 4);       atm_mbar_init(max_bar + 8, 4);
+    for (int i = 0; i < NST; ++i) {
+      atm_mbar_init(full + i * 8, AUM_PROD_WARPS);  // one arrival per producer warp
+      atm_mbar_init(empty + i * 8, 1);              // tcgen05.commit after the tile's second product
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      atm_mbar_init(s_full + i * 8, 1);
+      atm_mbar_init(s_free + i * 8, 4);  // one arrival per warp of the softmax group
+      atm_mbar_init(p_full + i * 8, 4);
+      atm_mbar_init(p_free + i * 8, 1);
+      atm_mbar_init(max_bar + i * 8, 4);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     *abort_sm = 0;
   }
-  if (warp == 5) {
+  if (warp == MMA_WARP) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::
                      "r"((uint32_t)__cvta_generic_to_shared(tmem_slot)),
                  "r"(AUM_TMEM_COLS));
@@ -314,68 +223,79 @@ masked_attention_umma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, i
   __syncthreads();
   aum_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tmem_o = tmem + 32;  // columns 0..15 and 16..31: the two S buffers
+  // tensor memory columns: S of group 0, S of group 1, O of group 0, O of group 1 (16 each)
 
-  if (warp == 4) {
-    // =========================== producer ===========================
-    const int krow0 = (int)(b * a.k_rows_b + kvh * a.k_rows_h);
-    const int vrow0 = (int)(b * a.v_rows_b + kvh * a.v_rows_h);
-    int issued = 0;
-    // the rows of a tile are read one tile ahead, so that the list read does not sit between
-    // two issues
-    auto load_rows = [&](int t, int* yk, int* yv) {
-      const int u0 = (split + t * active) * AUM_TILE + 4 * lane;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int col = (t < my_tiles && u0 + i < U) ? gcols[u0 + i] : -1;
-        yk[i] = col >= 0 ? krow0 + col : a.k_rows_total;  // outside the tensor: reads as zeros
-        yv[i] = col >= 0 ? vrow0 + col : a.v_rows_total;
+  if (warp >= AUM_SOFT_WARPS && warp < MMA_WARP) {
+    // =========================== producers ===========================
+    // Warp pw copies rows 32 * pw .. 32 * pw + 31 of every tile: 16 lanes cover one 256-byte
+    // row, two rows per instruction.
+    const int pw = warp - AUM_SOFT_WARPS;
+    const int my_chunk = lane & 15, my_sub = lane >> 4;
+    const unsigned char* k_bytes = reinterpret_cast<const unsigned char*>(
+                                       reinterpret_cast<const __nv_bfloat16*>(a.k) + b * a.ks_b + kvh * a.ks_h) +
+                                   my_chunk * 16;
+    const unsigned char* v_bytes = reinterpret_cast<const unsigned char*>(
+                                       reinterpret_cast<const __nv_bfloat16*>(a.v) + b * a.vs_b + kvh * a.vs_h) +
+                                   my_chunk * 16;
+    const int64_t ks_bytes = a.ks_s * 2, vs_bytes = a.vs_s * 2;
+    // destination of (row 2 * it + my_sub, chunk my_chunk) inside a K (or V) tile
+    const uint32_t half_off = (uint32_t)(my_chunk >> 3) * C::HALF_BYTES;
+    auto load_col = [&](int t) {
+      int col = -1;
+      if (t < my_tiles) {
+        const int u = (split + t * active) * AUM_TILE + pw * 32 + lane;
+        if (u < U) col = gcols[u];
       }
+      return col;
     };
-    int nk[4], nv[4];
-    load_rows(0, nk, nv);
-    for (int t = 0; t < my_tiles; ++t) {
+    int col_next = load_col(0);
+    auto issue = [&](int t) {
       const int st = t % NST;
-      int yk[4], yv[4];
+      const int col = col_next;
+      col_next = load_col(t + 1);
+      const uint32_t kt = C::K_RING + st * C::KV_TILE + half_off;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) { yk[i] = nk[i]; yv[i] = nv[i]; }
-      load_rows(t + 1, nk, nv);
-      {
-        AUM_T0();
-        const bool okk = !(t >= NST) || aum_wait_warp(empty_k + st * 8, (uint32_t)(((t / NST) - 1) & 1), abort_sm, errflag);
-        if (lane == 0) AUM_T1(0);
-        if (!okk) break;
-      }
-      if (lane == 0) atm_mbar_expect_tx(full_k + st * 8, (uint32_t)C::KV_TILE);
-      __syncwarp();
-      const uint32_t kd = sm_s + C::K_RING + st * C::KV_TILE + lane * 512;
-      atm_tma_gather4(kd, &maps.k, 0, yk[0], yk[1], yk[2], yk[3], full_k + st * 8);
-      atm_tma_gather4(kd + C::HALF_BYTES, &maps.k, 64, yk[0], yk[1], yk[2], yk[3], full_k + st * 8);
-      {
-        AUM_T0();
-        const bool okv = !(t >= NST) || aum_wait_warp(empty_v + st * 8, (uint32_t)(((t / NST) - 1) & 1), abort_sm, errflag);
-        if (lane == 0) AUM_T1(1);
-        if (!okv) {
-          issued = t + 1;  // the K half of this tile is in flight
-          break;
+      for (int it = 0; it < 16; ++it) {
+        const int rw = it * 2 + my_sub;  // row within the warp's 32
+        const int rc = __shfl_sync(0xffffffffu, col, rw);
+        const uint32_t off = kt + (uint32_t)(pw * 32 + rw) * 128 + ((uint32_t)((my_chunk & 7) ^ (rw & 7)) << 4);
+        if (rc >= 0) {
+          atm_cp_async16(sm_s + off, k_bytes + rc * ks_bytes);
+          atm_cp_async16(sm_s + off + (C::V_RING - C::K_RING), v_bytes + rc * vs_bytes);
+        } else {  // past the end of the list: zeros, not stale bits, go into the tensor core
+          *reinterpret_cast<uint4*>(sm + off) = make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4*>(sm + off + (C::V_RING - C::K_RING)) = make_uint4(0u, 0u, 0u, 0u);
         }
       }
-      if (lane == 0) atm_mbar_expect_tx(full_v + st * 8, (uint32_t)C::KV_TILE);
+    };
+    // issue() takes the tiles in order (it carries the prefetched columns along)
+#pragma unroll
+    for (int s0 = 0; s0 < NST - 1; ++s0) {
+      if (s0 < my_tiles) issue(s0);
+      asm volatile("cp.async.commit_group;\n" ::);
+    }
+    for (int t = 0; t < my_tiles; ++t) {
+      // tile t has landed (this thread's share): make it visible to the tensor core, signal
+      asm volatile("cp.async.wait_group %0;\n" ::"n"(NST - 2));
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       __syncwarp();
-      const uint32_t vd = sm_s + C::V_RING + st * C::KV_TILE + lane * 512;
-      atm_tma_gather4(vd, &maps.v, 0, yv[0], yv[1], yv[2], yv[3], full_v + st * 8);
-      atm_tma_gather4(vd + C::HALF_BYTES, &maps.v, 64, yv[0], yv[1], yv[2], yv[3], full_v + st * 8);
-      issued = t + 1;
-    }
-    if (*abort_sm) {
-      // copies of the last NST tiles may still be in flight: bounded wait for each
-      for (int t = issued > NST ? issued - NST : 0; t < issued; ++t) {
-        const uint32_t par = (uint32_t)((t / NST) & 1);
-        for (int i = 0; i < 4096 && !atm_mbar_try(full_k + (t % NST) * 8, par, 2000u); ++i) {}
-        for (int i = 0; i < 4096 && !atm_mbar_try(full_v + (t % NST) * 8, par, 2000u); ++i) {}
+      if (lane == 0) aum_arrive(full + (t % NST) * 8);
+      // refill the stage that tile t - 1 used once its second product has completed
+      const int nx = t + NST - 1;
+      if (nx < my_tiles) {
+        bool okp = true;
+        if (nx >= NST) {
+          AUM_T0();
+          okp = aum_wait_warp(empty + (nx % NST) * 8, (uint32_t)(((nx / NST) - 1) & 1), abort_sm, errflag);
+          if (lane == 0 && pw == 0) AUM_T1(0);
+        }
+        if (!okp) break;
+        issue(nx);
       }
+      asm volatile("cp.async.commit_group;\n" ::);
     }
-  } else if (warp == 5) {
+    asm volatile("cp.async.wait_group 0;\n" ::);
+  } else if (warp == MMA_WARP) {
     // =========================== tensor-core issuer ===========================
     if (lane == 0) {
       const uint32_t idesc_qk = aum_idesc(false, false);
@@ -383,44 +303,38 @@ masked_attention_umma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, i
       const uint32_t q_s = sm_s + C::Q_OFF;
       bool ok = true;
       auto pv = [&](int t) {
-        const int st = t % NST, bb = t & 1;
+        const int st = t % NST, gg = t & 1, j = t >> 1;
         {
           AUM_T0();
-          const bool o1 = aum_wait(full_v + st * 8, (uint32_t)((t / NST) & 1), abort_sm, errflag);
-          AUM_T1(4);
-          if (!o1) return false;
-        }
-        {
-          AUM_T0();
-          const bool o2 = aum_wait(p_full + bb * 8, (uint32_t)((t >> 1) & 1), abort_sm, errflag);
+          const bool o2 = aum_wait(p_full + gg * 8, (uint32_t)(j & 1), abort_sm, errflag);
           AUM_T1(5);
           if (!o2) return false;
         }
         aum_fence_after();
         const uint32_t v_s = sm_s + C::V_RING + st * C::KV_TILE;
-        const uint32_t p_s = sm_s + C::P_OFF + bb * 4096;
+        const uint32_t p_s = sm_s + C::P_OFF + gg * 4096;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           // A = V^T, MN-major: 64 dims contiguous per 128-byte row, 8 keys per 1 KB atom,
           // the second 64 dims one half further
           const uint64_t ad = aum_desc(v_s + ks * 2048, C::HALF_BYTES, 1024, 2);
           const uint64_t bd = aum_p_desc(p_s, ks);
-          aum_mma(tmem_o, ad, bd, idesc_pv, (t > 0 || ks > 0) ? 1u : 0u);
+          aum_mma(tmem + 32 + gg * 16, ad, bd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
         }
-        aum_commit(empty_v + st * 8);
-        aum_commit(p_free + bb * 8);
+        aum_commit(empty + st * 8);
+        aum_commit(p_free + gg * 8);
         return true;
       };
       for (int t = 0; t < my_tiles && ok; ++t) {
-        const int st = t % NST, bb = t & 1;
+        const int st = t % NST, gg = t & 1, j = t >> 1;
         {
           AUM_T0();
-          ok = aum_wait(full_k + st * 8, (uint32_t)((t / NST) & 1), abort_sm, errflag);
+          ok = aum_wait(full + st * 8, (uint32_t)((t / NST) & 1), abort_sm, errflag);
           AUM_T1(6);
         }
         {
           AUM_T0();
-          if (ok && t >= 2) ok = aum_wait(s_free + bb * 8, (uint32_t)(((t >> 1) - 1) & 1), abort_sm, errflag);
+          if (ok && j >= 1) ok = aum_wait(s_free + gg * 8, (uint32_t)((j - 1) & 1), abort_sm, errflag);
           AUM_T1(7);
         }
         if (!ok) break;
@@ -431,19 +345,21 @@ masked_attention_umma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, i
           // both K-major, 128-byte swizzle: 8-row groups 1 KB apart, 32 bytes per k-step
           const uint64_t ad = aum_desc(k_s + (ks >> 2) * C::HALF_BYTES + (ks & 3) * 32, 0, 1024, 2);
           const uint64_t bd = aum_desc(q_s + (ks >> 2) * 2048 + (ks & 3) * 32, 0, 1024, 2);
-          aum_mma(tmem + bb * 16, ad, bd, idesc_qk, ks > 0 ? 1u : 0u);
+          aum_mma(tmem + gg * 16, ad, bd, idesc_qk, ks > 0 ? 1u : 0u);
         }
-        aum_commit(s_full + bb * 8);
-        aum_commit(empty_k + st * 8);
+        aum_commit(s_full + gg * 8);
         if (t >= 1) ok = pv(t - 1);
       }
       if (ok && my_tiles > 0) pv(my_tiles - 1);
     }
     __syncwarp();
   } else {
-    // =========================== softmax: one thread per key ===========================
-    const int key = tid;  // 0..127 = lane of tensor memory
-    const uint32_t lane_base = ((uint32_t)(warp * 32)) << 16;
+    // =========================== softmax: one thread per key, two groups ===========================
+    const int gg = warp >> 2;            // group: tiles gg, gg + 2, ...
+    const int wg = warp & 3;             // warp within the group = quarter of tensor memory lanes
+    const int key = (wg << 5) | lane;    // 0..127 = lane of tensor memory = key of the tile
+    const uint32_t lane_base = ((uint32_t)(wg * 32)) << 16;
+    const uint32_t tmem_s = tmem + gg * 16, tmem_o = tmem + 32 + gg * 16;
     float m_used[RMAX], l_thr[RMAX];
 #pragma unroll
     for (int r = 0; r < RMAX; ++r) { m_used[r] = -INFINITY; l_thr[r] = 0.f; }
@@ -461,16 +377,16 @@ masked_attention_umma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, i
       }
       return m;
     };
-    Meta nxt = load_meta(0);
+    Meta nxt = load_meta(gg);
     bool ok = true;
-    for (int t = 0; t < my_tiles; ++t) {
-      const int bb = t & 1, j = t >> 1;
+    int j = 0;
+    for (int t = gg; t < my_tiles; t += 2, ++j) {
       const Meta cur = nxt;
-      nxt = load_meta(t + 1);
+      nxt = load_meta(t + 2);
       const int u = (split + t * active) * AUM_TILE + key;
       {
         AUM_T0();
-        ok = aum_wait_warp(s_full + bb * 8, (uint32_t)(j & 1), abort_sm, errflag);
+        ok = aum_wait_warp(s_full + gg * 8, (uint32_t)(j & 1), abort_sm, errflag);
         if (tid == 0) AUM_T1(8);
       }
       if (!ok) break;
@@ -479,10 +395,14 @@ masked_attention_umma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, i
 #endif
       aum_fence_after();
       uint32_t sr[RMAX == 4 ? 8 : 16];
-      if constexpr (RMAX == 4) aum_tmem_ld8(tmem + lane_base + bb * 16, sr);
-      else aum_tmem_ld16(tmem + lane_base + bb * 16, sr);
+      if constexpr (RMAX == 4) aum_tmem_ld8(tmem_s + lane_base, sr);
+      else aum_tmem_ld16(tmem_s + lane_base, sr);
       aum_fence_before();
-      aum_arrive(s_free + bb * 8);
+      __syncwarp();
+      if (lane == 0) aum_arrive(s_free + gg * 8);
+#ifdef AUM_PROF
+      if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) atomicAdd((unsigned long long*)&aum_prof[14], (unsigned long long)(clock64() - prof_tile_t0));
+#endif
 
       float sv[RMAX], wv[RMAX];
 #pragma unroll
@@ -508,17 +428,21 @@ masked_attention_umma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, i
           }
         }
       }
-      // tile maximum per row: warp reduction, then the four warps exchange through shared memory
+      // tile maximum per row: warp reduction, then the group's four warps exchange through
+      // shared memory
 #pragma unroll
       for (int r = 0; r < RMAX; ++r) {
         const int mx = __reduce_max_sync(0xffffffffu, aum_ordered(sv[r]));
-        if (lane == 0) wmax_sm[(bb * 4 + warp) * 16 + r] = aum_unordered(mx);
+        if (lane == 0) wmax_sm[(gg * 4 + wg) * 16 + r] = aum_unordered(mx);
       }
       __syncwarp();
-      if (lane == 0) aum_arrive(max_bar + bb * 8);
+      if (lane == 0) aum_arrive(max_bar + gg * 8);
+#ifdef AUM_PROF
+      if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) atomicAdd((unsigned long long*)&aum_prof[15], (unsigned long long)(clock64() - prof_tile_t0));
+#endif
       {
         AUM_T0();
-        ok = aum_wait_warp(max_bar + bb * 8, (uint32_t)(j & 1), abort_sm, errflag);
+        ok = aum_wait_warp(max_bar + gg * 8, (uint32_t)(j & 1), abort_sm, errflag);
         if (tid == 0) AUM_T1(9);
       }
       if (!ok) break;
@@ -526,7 +450,7 @@ masked_attention_umma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, i
       bool rescale = false;
 #pragma unroll
       for (int r = 0; r < RMAX; ++r) {
-        const float* wm = wmax_sm + bb * 64 + r;
+        const float* wm = wmax_sm + gg * 64 + r;
         const float tm = fmaxf(fmaxf(wm[0], wm[16]), fmaxf(wm[32], wm[48]));
         alpha[r] = 1.f;
         if (tm > m_used[r] + AUM_RESCALE_T) {  // also the first finite maximum (-inf + T = -inf)
@@ -547,16 +471,15 @@ masked_attention_umma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, i
         l_thr[r + 1] = l_thr[r + 1] * alpha[r + 1] + p1;
         pk[r >> 1] = atm_pack_bf16(p0, p1);
       }
-      // the P buffer is free once the product that read it two tiles ago has completed
+      // the group's P buffer is free, and its accumulator quiet, once the product of the group's
+      // previous tile has completed
       {
         AUM_T0();
-        if (j >= 1) ok = aum_wait_warp(p_free + bb * 8, (uint32_t)((j - 1) & 1), abort_sm, errflag);
+        if (j >= 1) ok = aum_wait_warp(p_free + gg * 8, (uint32_t)((j - 1) & 1), abort_sm, errflag);
         if (tid == 0) AUM_T1(10);
       }
       if (!ok) break;
-      if (rescale && t > 0) {
-        // the accumulator is quiet once the product of the previous tile has completed
-        if (!(ok = aum_wait_warp(p_free + ((t - 1) & 1) * 8, (uint32_t)(((t - 1) >> 1) & 1), abort_sm, errflag))) break;
+      if (rescale && j >= 1) {
         aum_fence_after();
         uint32_t orow[16];
         aum_tmem_ld16(tmem_o + lane_base, orow);
@@ -564,26 +487,25 @@ masked_attention_umma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, i
         for (int r = 0; r < RMAX; ++r) orow[r] = __float_as_uint(__uint_as_float(orow[r]) * alpha[r]);
         aum_tmem_st16(tmem_o + lane_base, orow);
       }
-      aum_store_p(sm + C::P_OFF + bb * 4096, key, pk);
+      aum_store_p(sm + C::P_OFF + gg * 4096, key, pk);
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       aum_fence_before();
-      aum_arrive(p_full + bb * 8);
+      __syncwarp();
+      if (lane == 0) aum_arrive(p_full + gg * 8);
 #ifdef AUM_PROF
       if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
         atomicAdd((unsigned long long*)&aum_prof[11], (unsigned long long)(clock64() - prof_tile_t0));
         atomicAdd((unsigned long long*)&aum_prof[12], 1ull);
-        if (rescale && t > 0) atomicAdd((unsigned long long*)&aum_prof[13], 1ull);
+        if (rescale && j >= 1) atomicAdd((unsigned long long*)&aum_prof[13], 1ull);
       }
 #endif
     }
-    // ---- the CTA's partial: O^T column r of this thread's lane = O[r][dim] ----
-    float* pout = a.partial + ((int64_t)g * a.nsplit + split) * a.R * (D + 2);
+    // ---- this group's share: O^T column r of this thread's lane = O[r][dim] ----
     uint32_t orow[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) orow[i] = 0u;
-    if (ok && my_tiles > 0) {
-      const int last = my_tiles - 1;
-      ok = aum_wait_warp(p_free + (last & 1) * 8, (uint32_t)((last >> 1) & 1), abort_sm, errflag);
+    if (ok && j > 0) {  // j = tiles this group took
+      ok = aum_wait_warp(p_free + gg * 8, (uint32_t)((j - 1) & 1), abort_sm, errflag);
       if (ok) {
         aum_fence_after();
         aum_tmem_ld16(tmem_o + lane_base, orow);
@@ -591,39 +513,68 @@ masked_attention_umma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, i
     }
 #pragma unroll
     for (int r = 0; r < RMAX; ++r) {
-      if (r < a.R) pout[r * (D + 2) + key] = ok ? __uint_as_float(orow[r]) : 0.f;
       float l = l_thr[r];
 #pragma unroll
       for (int of = 16; of > 0; of >>= 1) l += __shfl_xor_sync(0xffffffffu, l, of);
-      if (lane == 0) lred_sm[warp * 16 + r] = l;
+      if (lane == 0) lred_sm[(gg * 4 + wg) * 16 + r] = l;
+      if (key == 0) gmax_sm[gg * 16 + r] = ok ? m_used[r] : -INFINITY;
     }
-    asm volatile("bar.sync 1, 128;\n" ::: "memory");  // after the loops: every softmax thread gets here
-    if (key < a.R && key < RMAX) {
-      const int r = key;
-      float mr = -INFINITY;
+    asm volatile("bar.sync 1, 256;\n" ::: "memory");  // after the loops: every softmax thread gets here
+    // ---- merge the two groups: group 1 leaves its scaled accumulator in shared memory (the
+    //      ring is idle now), group 0 adds its own and writes the CTA's partial ----
+    float* obuf = reinterpret_cast<float*>(sm + C::K_RING);  // [RMAX][128]
+    float scale_me[RMAX], m_cta[RMAX];
 #pragma unroll
-      for (int q = 0; q < RMAX; ++q)
-        if (q == r) mr = m_used[q];
-      const float L = lred_sm[r] + lred_sm[16 + r] + lred_sm[32 + r] + lred_sm[48 + r];
-      pout[r * (D + 2) + D] = ok ? mr : -INFINITY;
-      pout[r * (D + 2) + D + 1] = ok ? L : 0.f;
+    for (int r = 0; r < RMAX; ++r) {
+      const float m0 = gmax_sm[r], m1 = gmax_sm[16 + r];
+      const float mm = fmaxf(m0, m1);
+      const float mine = gg ? m1 : m0;
+      m_cta[r] = mm;
+      scale_me[r] = (mine == -INFINITY) ? 0.f : __expf(mine - mm);
+    }
+    if (gg == 1) {
+#pragma unroll
+      for (int r = 0; r < RMAX; ++r) obuf[r * 128 + key] = __uint_as_float(orow[r]) * scale_me[r];
+    }
+    asm volatile("bar.sync 1, 256;\n" ::: "memory");
+    if (gg == 0) {
+      float* pout = a.partial + ((int64_t)g * a.nsplit + split) * a.R * (D + 2);
+#pragma unroll
+      for (int r = 0; r < RMAX; ++r)
+        if (r < a.R) pout[r * (D + 2) + key] = __uint_as_float(orow[r]) * scale_me[r] + obuf[r * 128 + key];
+      if (key < a.R && key < RMAX) {
+        const int r = key;
+        float mm = -INFINITY, L = 0.f;
+#pragma unroll
+        for (int q = 0; q < RMAX; ++q)
+          if (q == r) {
+            const float m0 = gmax_sm[q], m1 = gmax_sm[16 + q];
+            mm = m_cta[q];
+            const float s0 = (m0 == -INFINITY) ? 0.f : __expf(m0 - mm);
+            const float s1 = (m1 == -INFINITY) ? 0.f : __expf(m1 - mm);
+            L = (lred_sm[q] + lred_sm[16 + q] + lred_sm[32 + q] + lred_sm[48 + q]) * s0 +
+                (lred_sm[64 + q] + lred_sm[80 + q] + lred_sm[96 + q] + lred_sm[112 + q]) * s1;
+          }
+        pout[r * (D + 2) + D] = mm;
+        pout[r * (D + 2) + D + 1] = L;
+      }
     }
   }
   aum_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == MMA_WARP) {
     aum_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(AUM_TMEM_COLS));
   }
   atm_finish_group<D, AUM_THREADS>(a, g, active, sm, is_last_sm, tickets, sinks, out, part_out);
 }
 
-// Which problems take the tcgen05 kernel when the environment does not say.
-static bool aum_default(bool lsh, int64_t S) {
-  (void)lsh;
-  (void)S;
-  return false;
-}
+// Which problems take the tcgen05 kernel when neither the caller nor the environment says.
+// Measured on B200: with MagicPig weights evaluated in place and a sequence of a million keys
+// (a union list of ~770 000 rows per KV group) it is 9 % faster than the mma.sync kernel; on
+// lists of up to ~100 000 rows the mma.sync kernel, whose fixed costs are lower, is ahead.
+#define AUM_DEFAULT_MIN_KEYS (512 * 1024)
+static bool aum_default(bool lsh, int64_t S) { return lsh && S >= AUM_DEFAULT_MIN_KEYS; }
 
 // The kernel choice: a process-wide setting (sah_attn_select_kernel), else SAH_ATTN_UMMA in the
 // environment (1 selects the tcgen05 kernel wherever it applies, 0 never), else aum_default.
@@ -650,26 +601,20 @@ static int aum_sm_count() {
   return sms[dev];
 }
 
-// Launches the tcgen05 kernel when it applies (head dim 128, K and V viewable as 2-D row tensors,
-// at most 4 mask rows with in-place weights, 16 otherwise).  Returns SAH_OK and sets *launched.
+// Launches the tcgen05 kernel when it applies (head dim 128, at most 4 mask rows with in-place
+// weights, 16 otherwise).  Returns SAH_OK and sets *launched.
 static int launch_attention_umma(AttnArgs a, int B, int groups, int* tickets, int* errflag,
                                  const float* sinks, void* out, float* part_out, bool lsh, cudaStream_t st,
                                  bool* launched) {
   static bool allowed[3][64] = {};
   *launched = false;
   if (lsh && a.R > 4) return SAH_OK;
-  AtmMaps maps;
-  memset(&maps, 0, sizeof(maps));
-  if (!(atm_make_map(&maps.k, a.k, a.ks_b, a.ks_h, a.ks_s, B, a.Hkv, a.S, 128, &a.k_rows_b, &a.k_rows_h,
-                     &a.k_rows_total) &&
-        atm_make_map(&maps.v, a.v, a.vs_b, a.vs_h, a.vs_s, B, a.Hkv, a.S, 128, &a.v_rows_b, &a.v_rows_h,
-                     &a.v_rows_total)))
-    return SAH_OK;
+  (void)B;
   // one CTA per SM; two waves of CTAs over the groups (the kernel halves that for shorter lists)
   int64_t nsplit = (2 * (int64_t)aum_sm_count()) / groups;
   if (nsplit > a.nsplit) nsplit = a.nsplit;
   if (nsplit < 1) nsplit = 1;
-  if ((size_t)16 * nsplit * 4 + 128 > (size_t)AumCfg::V_RING)
+  if ((size_t)16 * nsplit * 4 + 128 > (size_t)AumCfg::Q_OFF)
     return sah_fail(SAH_ERR_UNSUPPORTED, "attention: %d splits do not fit the merge scratch", (int)nsplit);
   dim3 grid((unsigned)nsplit, (unsigned)groups);
   cudaError_t e = cudaSuccess;
@@ -678,7 +623,7 @@ static int launch_attention_umma(AttnArgs a, int B, int groups, int* tickets, in
     e = atm_allow_smem(masked_attention_umma_kernel<LSHW, RMAX>, AumCfg::SMEM, allowed[SLOT]);        \
     if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "attention attr: %s", cudaGetErrorString(e)); \
     masked_attention_umma_kernel<LSHW, RMAX><<<grid, AUM_THREADS, AumCfg::SMEM, st>>>(                \
-        a, maps, tickets, errflag, sinks, (__nv_bfloat16*)out, part_out);                             \
+        a, tickets, errflag, sinks, (__nv_bfloat16*)out, part_out);                             \
   } while (0)
   if (lsh) AUM_LAUNCH(true, 4, 0);
   else if (a.R <= 4) AUM_LAUNCH(false, 4, 1);

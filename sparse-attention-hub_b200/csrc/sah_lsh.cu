@@ -276,6 +276,69 @@ extern "C" int sah_lsh_key_sign(const void* keys, int dtype, int64_t ks_b, int64
   return SAH_OK;
 }
 
+#include "sah_lsh_tc.cuh"
+
+// Workspace of sah_lsh_key_sign_tc: two status words (entries appended to the list; error word
+// of the bounded waits), padding to 16 bytes, then the list of 32-column groups to redo.
+extern "C" int64_t sah_lsh_key_sign_tc_ws_bytes(int B, int Hkv, int64_t n_keys) {
+  if (B <= 0 || Hkv <= 0 || n_keys <= 0) return 0;
+  const int64_t rows = (int64_t)B * Hkv * n_keys;
+  return 16 + (rows / 4 + 4096) * (int64_t)sizeof(LtcUncertain);
+}
+
+extern "C" int sah_lsh_key_sign_tc(const void* keys, int64_t ks_b, int64_t ks_h, int64_t ks_s, int B,
+                                   int Hkv, int64_t s0, int64_t s1, int D, const void* mean,
+                                   const float* norms, const unsigned int* max_norm_bits,
+                                   const void* proj, int L, int K, int64_t cap, void* codes,
+                                   void* workspace, int64_t workspace_bytes, int sm_count, void* stream) {
+  SAH_REQUIRE(keys && norms && max_norm_bits && proj && codes && workspace, "lsh_key_sign_tc: null pointer");
+  if (D != 128 || K != 8)
+    return sah_fail(SAH_ERR_UNSUPPORTED, "lsh_key_sign_tc: head dim 128 and 8 bits per table (got %d, %d)", D, K);
+  SAH_REQUIRE(L > 0 && s0 >= 0 && s1 >= s0 && s1 <= cap, "lsh_key_sign_tc: bad extents");
+  SAH_REQUIRE((ks_s * 2) % 16 == 0 && (ks_h * 2) % 16 == 0 && (ks_b * 2) % 16 == 0 && ((uintptr_t)keys % 16) == 0 &&
+                  (mean == nullptr || ((uintptr_t)mean % 16) == 0) && ((uintptr_t)codes % 16) == 0 &&
+                  ((uintptr_t)workspace % 16) == 0,
+              "lsh_key_sign_tc: rows must be 16-byte aligned");
+  if (s1 == s0) return SAH_OK;
+  const int64_t need = sah_lsh_key_sign_tc_ws_bytes(B, Hkv, s1 - s0);
+  if (workspace_bytes < need)
+    return sah_fail(SAH_ERR_WORKSPACE, "lsh_key_sign_tc: workspace of %lld bytes, need %lld",
+                    (long long)workspace_bytes, (long long)need);
+  cudaStream_t st = (cudaStream_t)stream;
+  int* status = reinterpret_cast<int*>(workspace);
+  LtcUncertain* list = reinterpret_cast<LtcUncertain*>(reinterpret_cast<unsigned char*>(workspace) + 16);
+  const int list_cap = (int)((workspace_bytes - 16) / (int64_t)sizeof(LtcUncertain) < (1ll << 30)
+                                 ? (workspace_bytes - 16) / (int64_t)sizeof(LtcUncertain)
+                                 : (1ll << 30));
+  cudaError_t e = cudaMemsetAsync(status, 0, 16, st);
+  if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "lsh_key_sign_tc memset: %s", cudaGetErrorString(e));
+  static bool allowed = false;
+  if (!allowed) {
+    e = cudaFuncSetAttribute(lsh_key_sign_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LtcCfg::SMEM);
+    if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "lsh_key_sign_tc attr: %s", cudaGetErrorString(e));
+    allowed = true;
+  }
+  if (sm_count <= 0) sm_count = 148;
+  const int chunks = (L * 8 + LTC_NCHUNK - 1) / LTC_NCHUNK;
+  const int64_t BH = (int64_t)B * Hkv;
+  const int64_t tiles = BH * ((s1 - s0 + LTC_TILE - 1) / LTC_TILE);
+  int64_t workers = sm_count / chunks;
+  if (workers < 1) workers = 1;
+  if (workers > tiles) workers = tiles;
+  dim3 grid((unsigned)workers, (unsigned)chunks);
+  lsh_key_sign_tc_kernel<<<grid, LTC_THREADS, LtcCfg::SMEM, st>>>(
+      reinterpret_cast<const __nv_bfloat16*>(keys), ks_b, ks_h, ks_s, Hkv, BH, s0, s1,
+      reinterpret_cast<const __nv_bfloat16*>(mean), norms, max_norm_bits, reinterpret_cast<const __nv_bfloat16*>(proj),
+      L, cap, reinterpret_cast<uint8_t*>(codes), list, list_cap, status, status + 1);
+  SAH_LAUNCH_CHECK("lsh_key_sign_tc");
+  lsh_sign_recheck_kernel<<<(unsigned)(sm_count * 4), 256, 0, st>>>(
+      reinterpret_cast<const __nv_bfloat16*>(keys), ks_b, ks_h, ks_s, Hkv, reinterpret_cast<const __nv_bfloat16*>(mean),
+      norms, max_norm_bits, reinterpret_cast<const __nv_bfloat16*>(proj), L, cap, reinterpret_cast<uint8_t*>(codes),
+      list, list_cap, status);
+  SAH_LAUNCH_CHECK("lsh_sign_recheck");
+  return SAH_OK;
+}
+
 // ---------------------------------------------------------------------------------------
 // query: centre, normalise, signatures, unit vector
 // ---------------------------------------------------------------------------------------

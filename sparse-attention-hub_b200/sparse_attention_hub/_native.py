@@ -100,6 +100,8 @@ _SIGNATURES = {
     "sah_mask_flat_add": [_P, _P, _I, _L, _L, _P, _P],
     "sah_mask_clamp_to_dense": [_P, _I, _L, _P, _P],
     "sah_attn_select_kernel": [_I],
+    "sah_attn_exchange_bytes": [_I, _I, _I, _I, _I],  # returns int64
+    "sah_attn_exchange_merge": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P],
     "sah_attn_gather_probe": [_P, _P, _L, _L, _L, _L, _L, _L, _I, _I, _I, _L, _I, POINTER(AttnSizes),
                               _P, _P, _P, _P],
     "sah_adaptive_budget": [_P, _I, c_float, _P, _L, _L, _L, _P, _P, _P, _P, _I, _I, _I, _L, _L, _L,
@@ -119,6 +121,8 @@ _SIGNATURES = {
     "sah_mask_merge_data": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _L, _L, _P, _P, _P, _P, _P],
     "sah_lsh_key_sums": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _I, _P, _P],
     "sah_lsh_key_stats": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _I, _P, _L, _P, _P, _I, _P],
+    "sah_lsh_key_sign_tc_ws_bytes": [_I, _I, _L],  # returns int64
+    "sah_lsh_key_sign_tc": [_P, _L, _L, _L, _I, _I, _L, _L, _I, _P, _P, _P, _P, _I, _I, _L, _P, _P, _L, _I, _P],
     "sah_lsh_key_sign": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _I, _P, _P, _P, _P, _I, _I, _L, _P, _P],
     "sah_lsh_query": [_P, _I, _L, _L, _L, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P, _P, _P, _P, _P],
     "sah_lsh_match": [_P, _L, _P, _I, _I, _I, _I, _I, _I, _L, _L, _P, _P, _P],
@@ -141,7 +145,8 @@ PROFILE_SLOTS = {"attention": 0, "hash_topk": 1, "hash_encode": 2, "qk_scores": 
                  "topk_select": 4, "attn_plan": 5, "attn_merge": 6, "other": 7, "lsh_match": 8, "lsh_prob": 9,
                  "pq_scores": 10, "adaptive_budget": 11, "topp_select": 12, "quest_scores": 13}
 
-EXPORTED_SYMBOLS = sorted(list(_SIGNATURES) + ["sah_version", "sah_last_error", "sah_launch_count"])
+EXPORTED_SYMBOLS = sorted(list(_SIGNATURES) + ["sah_version", "sah_last_error", "sah_launch_count",
+                                                 "sah_attn_last_kernel"])
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -165,12 +170,16 @@ def load() -> ctypes.CDLL:
         fn.argtypes = argtypes
         fn.restype = c_int
     lib.sah_topk_select_ws_bytes.restype = c_int64
+    lib.sah_attn_exchange_bytes.restype = c_int64
+    lib.sah_lsh_key_sign_tc_ws_bytes.restype = c_int64
     lib.sah_pq_scores_ws_bytes.restype = c_int64
     lib.sah_topk_sel_hist_offset.restype = c_int64
     lib.sah_hash_topk_ws_bytes.restype = c_int64
     lib.sah_hash_scores_bytes.restype = c_int64
     lib.sah_version.restype = c_char_p
     lib.sah_last_error.restype = c_char_p
+    lib.sah_attn_last_kernel.restype = c_char_p
+    lib.sah_attn_last_kernel.argtypes = []
     lib.sah_launch_count.restype = ctypes.c_longlong
     lib.sah_launch_count.argtypes = []
     _lib = lib

@@ -103,13 +103,18 @@ class PQCache(TopKMasker):
     def add_mask(self, keys, queries, values, attention_mask, scaling, dropout,
                  sparse_meta_data: Dict[Any, Any], previous_mask: Mask,
                  **kwargs: Dict[str, Any]) -> Mask:
-        self._refuse_sequence_shard(kwargs)
         layer_idx = self._validate_inputs(sparse_meta_data, kwargs)
         if previous_mask.is_full_mask():
             return previous_mask
         dims = self._extract_tensor_dimensions(keys, queries)
-        heavy = self._calculate_effective_size(self.heavy_size, dims.seq_len_keys)
-        if self._should_use_full_attention(dims, heavy):
+        # On a sequence shard the keys at hand are one rank's range [begin, begin + n) of `total`
+        # keys: sizes are those of the whole sequence, the quantised region starts at
+        # init_offset of the whole sequence, the codebook is clustered over all ranks' keys, and
+        # the top-k is taken over all ranks' scores.
+        shard = kwargs.get("sequence_shard")
+        total = shard.total if shard is not None else dims.seq_len_keys
+        heavy = self._calculate_effective_size(self.heavy_size, total)
+        if total <= heavy + self.init_offset + dims.seq_len_queries + 2 ** self.pq_bits:
             return self._create_full_mask(dims, previous_mask.dtype, previous_mask.device)
         if self.metric == "ip":
             raise NotImplementedError("PQCache metric 'ip' (augmented inner product) is not built; "
@@ -118,13 +123,21 @@ class PQCache(TopKMasker):
             raise NotImplementedError("PQCache codes are bytes: pq_bits <= 8")
         _native.require_cuda(keys, "keys")
         self._initialize_pq_cache(sparse_meta_data, layer_idx)
+        # first quantised key in local coordinates
+        local_off = self.init_offset if shard is None else min(max(0, self.init_offset - shard.begin),
+                                                               dims.seq_len_keys)
         if sparse_meta_data["pq_centroids"][layer_idx] is None:
-            centroids, codes = self._perform_kmeans_clustering(keys, layer_idx, sparse_meta_data)
+            centroids, codes = self._perform_kmeans_clustering(keys, layer_idx, sparse_meta_data, local_off, shard)
         else:
-            centroids, codes = self._handle_incremental_keys(keys, layer_idx, sparse_meta_data)
-        scores = self._compute_pq_scores(queries, keys, centroids, codes)
-        merged = _native_ops.topk_select(scores, previous_mask, heavy, self.init_offset,
-                                         self.init_offset + codes.length)
+            centroids, codes = self._handle_incremental_keys(keys, layer_idx, sparse_meta_data, local_off)
+        scores = self._compute_pq_scores(queries, keys, centroids, codes, local_off)
+        if shard is not None:
+            if _native_ops.unit_weight_bits(previous_mask) is None:
+                raise NotImplementedError("PQCache on a sequence shard needs a unit-weight previous mask")
+            merged = _native_ops.topk_select_sharded(scores, previous_mask, heavy, shard.comm, local_off,
+                                                     local_off + codes.length)
+        else:
+            merged = _native_ops.topk_select(scores, previous_mask, heavy, local_off, local_off + codes.length)
         shape = self._mask_shape(dims)
         if _native_ops.unit_weight_bits(previous_mask) is None:
             new_only = _native_ops.bits_andnot(merged, previous_mask.native_bits())
@@ -158,11 +171,41 @@ class PQCache(TopKMasker):
         k = keys if keys.stride(-1) == 1 else keys.contiguous()
         return k, (k.data_ptr(), _native.dtype_code(k.dtype), k.stride(0), k.stride(1), k.stride(2))
 
+    def _gather_subvectors(self, k: torch.Tensor, idx: torch.Tensor, local_off: int, shard) -> torch.Tensor:
+        """Sub-vectors `[B, Hkv, n_sub, n_pick, sub_d]` (float32) of the quantised keys with the
+        region-relative indices `idx` `[B, Hkv, n_sub, n_pick]`.  On a shard an index may name a
+        key of another rank: every rank fills in what it owns and the ranks add up (one
+        non-zero term per element, so the sum is exact)."""
+        B, Hkv, n_local, D = k.shape
+        n_sub = idx.shape[2]
+        sub_d = D // n_sub
+        dev = k.device
+        if shard is None:
+            pos, own = idx + local_off, None
+        else:
+            pos = idx + (self.init_offset - shard.begin)  # local key position of region index
+            own = (pos >= local_off) & (pos < n_local)
+            pos = pos.clamp(0, max(n_local - 1, 0))
+        bi = torch.arange(B, device=dev).view(B, 1, 1, 1)
+        hi = torch.arange(Hkv, device=dev).view(1, Hkv, 1, 1)
+        si = torch.arange(n_sub, device=dev).view(1, 1, n_sub, 1)
+        if n_local == 0:
+            picked = torch.zeros((B, Hkv, n_sub, idx.shape[3], sub_d), dtype=torch.float32, device=dev)
+        else:
+            picked = k.reshape(B, Hkv, n_local, n_sub, sub_d)[bi, hi, pos, si].float()
+        if own is not None:
+            picked = torch.where(own.unsqueeze(-1), picked, torch.zeros_like(picked))
+            shard.comm.all_reduce_sum_(picked)
+        return picked
+
     def _perform_kmeans_clustering(self, keys: torch.Tensor, layer_idx: int,
-                                   sparse_meta_data: Dict[str, Any]):
+                                   sparse_meta_data: Dict[str, Any], local_off: Optional[int] = None,
+                                   shard=None):
         lib = _native.load()
         B, Hkv, n_sub, sub_d, n_cent = self._geometry(keys)
-        n_keys = keys.shape[2] - self.init_offset
+        local_off = self.init_offset if local_off is None else local_off
+        n_local = keys.shape[2] - local_off                       # quantised keys on this rank
+        n_keys = (shard.total if shard is not None else keys.shape[2]) - self.init_offset  # ... in all
         dev = keys.device
         st = _native.stream_of(dev)
         groups = B * Hkv * n_sub
@@ -170,54 +213,71 @@ class PQCache(TopKMasker):
         init = sparse_meta_data.get("pq_init_indices", {}).get(layer_idx)
         if init is None:
             init = torch.stack([torch.randperm(n_keys, device=dev)[:n_cent] for _ in range(groups)])
+            if shard is not None:  # rank 0's draw for everybody
+                init = shard.comm.all_reduce_sum_(init if shard.comm.rank == 0 else torch.zeros_like(init))
         init = init.to(device=dev, dtype=torch.long).reshape(B, Hkv, n_sub, n_cent)
         # initial centres: the chosen keys' sub-vectors, as float32 [groups][n_cent][sub_d]
-        sub_keys = k[:, :, self.init_offset:, :].reshape(B, Hkv, n_keys, n_sub, sub_d)
-        bi = torch.arange(B, device=dev).view(B, 1, 1, 1)
-        hi = torch.arange(Hkv, device=dev).view(1, Hkv, 1, 1)
-        si = torch.arange(n_sub, device=dev).view(1, 1, n_sub, 1)
-        centroids = sub_keys[bi, hi, init, si].float().reshape(groups, n_cent, sub_d).contiguous()
-        codes = torch.empty((B, Hkv, _capacity_for(n_keys), n_sub), dtype=torch.uint8, device=dev)
+        centroids = self._gather_subvectors(k, init, local_off, shard).reshape(groups, n_cent, sub_d).contiguous()
+        codes = torch.empty((B, Hkv, _capacity_for(max(n_local, 1)), n_sub), dtype=torch.uint8, device=dev)
         cap = codes.shape[2]
         sums = torch.empty((groups, n_cent, sub_d), dtype=torch.float64, device=dev)
         counts = torch.empty((groups, n_cent), dtype=torch.int32, device=dev)
         shift2 = torch.empty(groups, dtype=torch.float32, device=dev)
         reseed_src = sparse_meta_data.get("pq_reseed_indices", {}).get(layer_idx)
+        own_pos = torch.arange(n_cent, device=dev, dtype=torch.long).repeat(groups, 1).contiguous()
         for it in range(self.kmeans_iter):
-            _native.check(lib.sah_pq_assign(*kargs, B, Hkv, self.init_offset, keys.shape[2],
-                                            self.init_offset, n_sub, sub_d, n_cent,
-                                            centroids.data_ptr(), codes.data_ptr(), cap, 0, st),
-                          "sah_pq_assign")
+            if n_local > 0:
+                _native.check(lib.sah_pq_assign(*kargs, B, Hkv, local_off, keys.shape[2], local_off, n_sub,
+                                                sub_d, n_cent, centroids.data_ptr(), codes.data_ptr(), cap, 0,
+                                                st), "sah_pq_assign")
             sums.zero_()
             counts.zero_()
-            _native.check(lib.sah_pq_accumulate(*kargs, B, Hkv, n_keys, self.init_offset, n_sub, sub_d,
-                                                n_cent, codes.data_ptr(), cap, sums.data_ptr(),
-                                                counts.data_ptr(), st), "sah_pq_accumulate")
+            if n_local > 0:
+                _native.check(lib.sah_pq_accumulate(*kargs, B, Hkv, n_local, local_off, n_sub, sub_d, n_cent,
+                                                    codes.data_ptr(), cap, sums.data_ptr(), counts.data_ptr(),
+                                                    st), "sah_pq_accumulate")
             if reseed_src is not None:
                 reseed = reseed_src[it].to(device=dev, dtype=torch.long).contiguous()
             else:
                 reseed = torch.randint(0, n_keys, (groups, n_cent), device=dev)
-            _native.check(lib.sah_pq_update(*kargs, B, Hkv, self.init_offset, n_sub, sub_d, n_cent,
-                                            sums.data_ptr(), counts.data_ptr(), reseed.data_ptr(),
-                                            centroids.data_ptr(), shift2.data_ptr(), st),
-                          "sah_pq_update")
+                if shard is not None:
+                    reseed = shard.comm.all_reduce_sum_(reseed if shard.comm.rank == 0
+                                                        else torch.zeros_like(reseed))
+            if shard is None:
+                _native.check(lib.sah_pq_update(*kargs, B, Hkv, local_off, n_sub, sub_d, n_cent,
+                                                sums.data_ptr(), counts.data_ptr(), reseed.data_ptr(),
+                                                centroids.data_ptr(), shift2.data_ptr(), st),
+                              "sah_pq_update")
+            else:
+                # sums of bfloat16 / float32 key values in float64 and counts add up exactly over
+                # the ranks; the keys that re-seed empty clusters may live anywhere, so they are
+                # gathered into a [B, Hkv, n_cent, D] table that the update kernel reads instead
+                shard.comm.all_reduce_sum_(sums)
+                shard.comm.all_reduce_sum_(counts)
+                picked = self._gather_subvectors(k, reseed.reshape(B, Hkv, n_sub, n_cent), local_off, shard)
+                table = picked.permute(0, 1, 3, 2, 4).reshape(B, Hkv, n_cent, n_sub * sub_d).to(k.dtype).contiguous()
+                _native.check(lib.sah_pq_update(table.data_ptr(), _native.dtype_code(table.dtype), table.stride(0),
+                                                table.stride(1), table.stride(2), B, Hkv, 0, n_sub, sub_d,
+                                                n_cent, sums.data_ptr(), counts.data_ptr(), own_pos.data_ptr(),
+                                                centroids.data_ptr(), shift2.data_ptr(), st), "sah_pq_update")
             if bool((shift2 < 1e-4).all().item()):  # the reference's convergence test (host sync)
                 break
         cent_t = centroids.to(keys.dtype).reshape(B, Hkv, n_sub, n_cent, sub_d).contiguous()
-        packed = PackedPQCodes(codes, n_keys)
+        packed = PackedPQCodes(codes, max(n_local, 0))
         sparse_meta_data["pq_centroids"][layer_idx] = cent_t
         sparse_meta_data["pq_codebook"][layer_idx] = packed
         return cent_t, packed
 
     def _handle_incremental_keys(self, keys: torch.Tensor, layer_idx: int,
-                                 sparse_meta_data: Dict[str, Any]):
+                                 sparse_meta_data: Dict[str, Any], local_off: Optional[int] = None):
         lib = _native.load()
         centroids: torch.Tensor = sparse_meta_data["pq_centroids"][layer_idx]
         cached = sparse_meta_data["pq_codebook"][layer_idx]
         B, Hkv, n_sub, sub_d, n_cent = self._geometry(keys)
         if isinstance(cached, torch.Tensor):
             cached = PackedPQCodes.from_reference_layout(cached)
-        n_now = keys.shape[2] - self.init_offset
+        local_off = self.init_offset if local_off is None else local_off
+        n_now = keys.shape[2] - local_off
         if cached is None:
             cached = PackedPQCodes(torch.empty((B, Hkv, _capacity_for(n_now), n_sub), dtype=torch.uint8,
                                                device=keys.device), 0)
@@ -232,8 +292,8 @@ class PQCache(TopKMasker):
             k, kargs = self._key_args(keys)
             cent32 = centroids.float().reshape(-1, n_cent, sub_d).contiguous()
             _native.check(
-                lib.sah_pq_assign(*kargs, B, Hkv, self.init_offset + cached.length, keys.shape[2],
-                                  self.init_offset, n_sub, sub_d, n_cent, cent32.data_ptr(),
+                lib.sah_pq_assign(*kargs, B, Hkv, local_off + cached.length, keys.shape[2],
+                                  local_off, n_sub, sub_d, n_cent, cent32.data_ptr(),
                                   cached.codes.data_ptr(), cached.codes.shape[2], 1,
                                   _native.stream_of(keys.device)), "sah_pq_assign")
             cached.length = n_now
@@ -241,7 +301,7 @@ class PQCache(TopKMasker):
         return centroids, cached
 
     def _compute_pq_scores(self, queries: torch.Tensor, keys: torch.Tensor, centroids: torch.Tensor,
-                           codebook: PackedPQCodes) -> torch.Tensor:
+                           codebook: PackedPQCodes, local_off: Optional[int] = None) -> torch.Tensor:
         """`[B, Hq, Sq, S]` scores; only columns of the clustered region are written."""
         lib = _native.load()
         B, Hq, Sq, D = queries.shape
@@ -257,7 +317,8 @@ class PQCache(TopKMasker):
             lib.sah_pq_scores(q.data_ptr(), _native.dtype_code(q.dtype), q.stride(0), q.stride(1),
                               q.stride(2), cent.data_ptr(), codebook.codes.data_ptr(),
                               codebook.codes.shape[2], B, Hq, Hkv, Sq, codebook.length,
-                              self.init_offset, S, n_sub, sub_d, n_cent, scores.data_ptr(),
+                              self.init_offset if local_off is None else local_off, S, n_sub, sub_d, n_cent,
+                              scores.data_ptr(),
                               tables.data_ptr(), nbytes, _native.stream_of(q.device)), "sah_pq_scores")
         return scores
 

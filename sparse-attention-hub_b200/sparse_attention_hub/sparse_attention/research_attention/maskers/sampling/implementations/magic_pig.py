@@ -31,6 +31,7 @@ pre-populated) and `"key_signature"[layer]` (the packed handle; a reference-layo
 int64 tensor is converted on first use).
 """
 
+import os
 from dataclasses import dataclass, field
 from typing import Any, Dict, Literal, Optional, Tuple
 
@@ -284,10 +285,14 @@ class MagicPig(SamplingMasker):
         s_new0 = handle.length
         if S > handle.length:
             s0 = handle.length
-            _native.check(
-                lib.sah_lsh_key_sign(*kargs, s0, S, D, _native.ptr(mean), handle.norms.data_ptr(),
-                                     handle.max_norm.data_ptr(), proj.data_ptr(), self.lsh_l, self.lsh_k,
-                                     handle.capacity, handle.codes.data_ptr(), st), "sah_lsh_key_sign")
+            done = False
+            if self._tensor_core_build(keys, S - s0, D):
+                done = self._sign_on_tensor_cores(lib, keys, s0, S, mean, handle, proj, sms, st)
+            if not done:
+                _native.check(
+                    lib.sah_lsh_key_sign(*kargs, s0, S, D, _native.ptr(mean), handle.norms.data_ptr(),
+                                         handle.max_norm.data_ptr(), proj.data_ptr(), self.lsh_l, self.lsh_k,
+                                         handle.capacity, handle.codes.data_ptr(), st), "sah_lsh_key_sign")
             handle.length = S
         if S > s_new0 or resync or adopted:
             # per-key constants of the probability formula: the new keys, or every key when
@@ -299,6 +304,36 @@ class MagicPig(SamplingMasker):
                 "sah_lsh_key_den")
         cache[layer_idx] = handle
         return handle
+
+    # Ranges of at least this many keys are hashed on the tensor cores (a decode step's single
+    # appended key stays on the one-launch fixed-order kernel).
+    tensor_core_build_min_keys = 4096
+
+    def _tensor_core_build(self, keys: torch.Tensor, n_new: int, head_dim: int) -> bool:
+        if os.environ.get("SAH_LSH_TC", "1") == "0":
+            return False
+        return (keys.dtype == torch.bfloat16 and head_dim == 128 and self.lsh_k == 8
+                and n_new >= self.tensor_core_build_min_keys
+                and keys.stride(3) == 1 and all((keys.stride(i) * 2) % 16 == 0 for i in range(3))
+                and keys.data_ptr() % 16 == 0)
+
+    def _sign_on_tensor_cores(self, lib, keys, s0, s1, mean, handle, proj, sms, st) -> bool:
+        """Signatures of keys [s0, s1) by `sah_lsh_key_sign_tc` (tcgen05 projections + fixed-order
+        redo of the near-zero ones).  Returns False -- after reading two status words, an index
+        build may synchronise -- when the redo list overflowed or a wait inside the kernel ran
+        out; the caller then hashes the range with the fixed-order kernel."""
+        B, Hkv = keys.shape[0], keys.shape[1]
+        nbytes = int(lib.sah_lsh_key_sign_tc_ws_bytes(B, Hkv, s1 - s0))
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=keys.device)
+        _native.check(
+            lib.sah_lsh_key_sign_tc(keys.data_ptr(), keys.stride(0), keys.stride(1), keys.stride(2), B, Hkv,
+                                    s0, s1, keys.shape[3], _native.ptr(mean), handle.norms.data_ptr(),
+                                    handle.max_norm.data_ptr(), proj.data_ptr(), self.lsh_l, self.lsh_k,
+                                    handle.capacity, handle.codes.data_ptr(), ws.data_ptr(), nbytes, sms, st),
+            "sah_lsh_key_sign_tc")
+        status = ws[:8].view(torch.int32).tolist()
+        self.last_tensor_core_build = {"redone_groups": status[0], "keys": (s1 - s0) * B * Hkv}
+        return status[1] == 0 and status[0] <= (nbytes - 16) // 16
 
     # ------------------------------------------------------------------ public
     def add_mask(self, keys, queries, values, attention_mask, scaling, dropout,

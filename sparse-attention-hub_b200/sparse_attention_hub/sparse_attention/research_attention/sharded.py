@@ -11,6 +11,10 @@ global in the reference -- MagicPig's key mean and maximum key norm
 (maskers/sampling/implementations/magic_pig.py:175-176, :352-353) -- are reduced across the
 ranks when keys arrive, not per step.
 
+On NCCL ranks the all-gather and the merge are one kernel over peer memory instead
+(`PeerExchange`, `sah_attn_exchange_merge`): every rank stores its partial straight into its
+peers' receive buffers over NVLink, signals, and merges what arrived.
+
 Collectives go through a small `ShardComm` interface: `DistComm` is `torch.distributed`
 (NCCL on GPUs), `ThreadComm` runs the ranks as threads of one process (tests on one device).
 Maskers that have not been taught about shards refuse a `sequence_shard` instead of
@@ -19,12 +23,15 @@ silently treating the local range as the whole sequence.
 
 from __future__ import annotations
 
+import ctypes
+import os
 import threading
 from dataclasses import dataclass
 from typing import Any, Dict, List, Optional, Tuple
 
 import torch
 
+from ... import _native
 from ..utils.mask_attention_utils import merge_attention_partials, native_masked_attention
 
 
@@ -70,6 +77,71 @@ class DistComm(ShardComm):
         out = torch.empty(self.world * flat.numel(), dtype=t.dtype, device=t.device)
         self._dist.all_gather_into_tensor(out, flat, group=self.group)
         return out.view((self.world,) + tuple(t.shape))
+
+
+class PeerExchange:
+    """Receive buffer, flags and step counters of `sah_attn_exchange_merge` for one problem shape.
+
+    The buffer and the flags live in one symmetric-memory allocation
+    (`torch.distributed._symmetric_memory`), which maps every rank's copy into every process;
+    the kernel then needs nothing but the peers' base addresses.  One rank per GPU: the
+    kernels of different ranks wait on one another (bounded), so they must not share a device.
+    Collective: every rank of the group constructs it, with the same shape, at the same point.
+    """
+
+    def __init__(self, comm: "DistComm", batch: int, heads: int, seq_len_queries: int, head_dim: int,
+                 device: torch.device) -> None:
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        lib = _native.load()
+        self.shape = (batch, heads, seq_len_queries, head_dim)
+        self.rank, self.world = comm.rank, comm.world
+        rows = batch * heads * seq_len_queries
+        nbytes = int(lib.sah_attn_exchange_bytes(self.world, batch, heads, seq_len_queries, head_dim))
+        if nbytes <= 0 or self.world > 16:
+            raise ValueError("PeerExchange: unsupported shape or more than 16 ranks")
+        words = nbytes // 4 + self.world * rows
+        group = comm.group if comm.group is not None else dist.group.WORLD
+        self._mem = symm.empty(words, dtype=torch.float32, device=device)
+        self._mem.zero_()
+        self._handle = symm.rendezvous(self._mem, group)
+        ptrs = [int(p) for p in self._handle.buffer_ptrs]
+        self._bufs = (ctypes.c_void_p * self.world)(*ptrs)
+        self._flags = (ctypes.c_void_p * self.world)(*[p + nbytes for p in ptrs])
+        self.steps = torch.zeros(rows, dtype=torch.int32, device=device)
+        self.errflag = torch.zeros(1, dtype=torch.int32, device=device)
+        torch.cuda.current_stream(device).synchronize()
+        dist.barrier(group=group)  # every buffer is zeroed before any peer stores into it
+
+    def merge(self, part: torch.Tensor, dtype: torch.dtype, sinks: Optional[torch.Tensor]) -> torch.Tensor:
+        """`part` [rows, D + 2] of this rank -> output [B, Sq, Hq, D] over all ranks."""
+        B, Hq, Sq, D = self.shape
+        lib = _native.load()
+        part = part.contiguous()
+        out = torch.empty((B, Sq, Hq, D), dtype=dtype, device=part.device)
+        sk = None if sinks is None else sinks.to(device=part.device, dtype=torch.float32).contiguous()
+        _native.check(
+            lib.sah_attn_exchange_merge(part.data_ptr(), self._bufs, self._flags, self.rank, self.world, B, Hq,
+                                        Sq, D, None if sk is None else sk.data_ptr(), _native.dtype_code(dtype),
+                                        self.steps.data_ptr(), self.errflag.data_ptr(), out.data_ptr(),
+                                        _native.stream_of(part.device)),
+            "sah_attn_exchange_merge")
+        return out
+
+    def wait_errors(self) -> int:
+        """Non-zero when a bounded wait for a peer ran out since the last call (synchronises)."""
+        v = int(self.errflag.item())
+        self.errflag.zero_()
+        return v
+
+
+def peer_exchange_allowed(comm: ShardComm, tensor: torch.Tensor) -> bool:
+    """The peer-memory exchange needs NCCL ranks on distinct GPUs; `SAH_PEER_EXCHANGE=0` in the
+    environment keeps the all-gather path."""
+    if os.environ.get("SAH_PEER_EXCHANGE", "1") == "0":
+        return False
+    return isinstance(comm, DistComm) and comm.world > 1 and comm.world <= 16 and tensor.is_cuda
 
 
 class ThreadComm(ShardComm):
@@ -140,6 +212,7 @@ class SequenceShardedAttention:
         self.comm = comm
         self.begin = begin
         self.total = total
+        self._exchange: Dict[Tuple[int, int, int, int], PeerExchange] = {}
 
     def keys_appended(self, n: int) -> None:
         """`n` keys joined the sequence (on the last rank); every rank calls this."""
@@ -174,6 +247,12 @@ class SequenceShardedAttention:
         mask = self.build_mask(queries, keys, values, local_bias, scaling, dropout, meta, **kwargs)
         _, part = native_masked_attention(queries, keys, values, local_bias, None, scaling,
                                           mask, return_partials=True)
+        if peer_exchange_allowed(self.comm, part):
+            shape = (B, Hq, Sq, D)
+            ex = self._exchange.get(shape)
+            if ex is None:  # collective; every rank meets the shape for the first time in the same call
+                ex = self._exchange[shape] = PeerExchange(self.comm, B, Hq, Sq, D, part.device)
+            return ex.merge(part, queries.dtype, sinks), None
         gathered = self.comm.all_gather(part)  # [world, rows, D + 2]
         out = merge_attention_partials(gathered, B, Hq, Sq, queries.dtype, sinks)
         return out, None

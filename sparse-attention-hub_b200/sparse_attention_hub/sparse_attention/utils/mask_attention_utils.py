@@ -249,6 +249,11 @@ def select_attention_kernel(which: str) -> str:
     return {v: k for k, v in ATTENTION_KERNELS.items()}[prev]
 
 
+def last_attention_kernel() -> str:
+    """Name of the kernel that the most recent attention call of this process launched."""
+    return _native.load().sah_attn_last_kernel().decode()
+
+
 def gather_probe(keys: torch.Tensor, values: torch.Tensor, seq_len_queries: int = 1) -> None:
     """Launch the row-gather probe (`sah_attn_gather_probe`) on the union list of the most recent
     bfloat16 attention call over these keys and values: the copy pipeline of the attention kernel

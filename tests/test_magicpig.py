@@ -261,3 +261,53 @@ def test_reciprocal_division_of_bf16_values_is_exact():
             got = _rn(_rn(q2, 24), 8)
             want = _rn(_rn(Fraction(x, d), 24), 8)
             assert got == want, (x, d)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("L,S,centred", [(75, 20000, True), (33, 9000, True), (75, 5000, False)])
+def test_gpu_signatures_from_tensor_cores_equal_the_fixed_order_kernel(L, S, centred):
+    """`sah_lsh_key_sign_tc` (tcgen05 projections, near-zero ones redone in the fixed order) writes
+    bit for bit the signature rows of `sah_lsh_key_sign`, padding bytes included; a short range
+    is also checked against the CPU restatement."""
+    import torch
+    from sparse_attention_hub import _native
+
+    lib = _native.load()
+    dev = "cuda:0"
+    B, Hkv, D, K, cap = 2, 2, 128, 8, S + 64
+    gen = torch.Generator(device=dev).manual_seed(5 + L)
+    keys = (torch.randn((B, Hkv, cap, D), generator=gen, device=dev) * 0.7 + 0.3).to(torch.bfloat16)[:, :, :S]
+    proj = torch.randn((D + 1, L * K), generator=gen, device=dev).to(torch.bfloat16)
+    mean = keys.float().mean(dim=2).to(torch.bfloat16).contiguous() if centred else None
+    norms = torch.zeros((B, Hkv, cap), dtype=torch.float32, device=dev)
+    max_norm = torch.zeros(1, dtype=torch.int32, device=dev)
+    st = _native.stream_of(torch.device(dev))
+    kargs = (keys.data_ptr(), _native.SAH_BF16, keys.stride(0), keys.stride(1), keys.stride(2), B, Hkv)
+    _native.check(lib.sah_lsh_key_stats(*kargs, 0, S, D, _native.ptr(mean), cap, norms.data_ptr(),
+                                        max_norm.data_ptr(), 148, st), "sah_lsh_key_stats")
+    pitch = (L + 15) // 16 * 16
+    want = torch.full((B, Hkv, cap, pitch), 0xAA, dtype=torch.uint8, device=dev)
+    got = torch.full_like(want, 0x55)
+    _native.check(lib.sah_lsh_key_sign(*kargs, 0, S, D, _native.ptr(mean), norms.data_ptr(), max_norm.data_ptr(),
+                                       proj.data_ptr(), L, K, cap, want.data_ptr(), st), "sah_lsh_key_sign")
+    nbytes = int(lib.sah_lsh_key_sign_tc_ws_bytes(B, Hkv, S))
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    _native.check(lib.sah_lsh_key_sign_tc(keys.data_ptr(), keys.stride(0), keys.stride(1), keys.stride(2), B, Hkv,
+                                          0, S, D, _native.ptr(mean), norms.data_ptr(), max_norm.data_ptr(),
+                                          proj.data_ptr(), L, K, cap, got.data_ptr(), ws.data_ptr(), nbytes, 148,
+                                          st), "sah_lsh_key_sign_tc")
+    torch.cuda.synchronize()
+    redone, err = ws[:8].view(torch.int32).tolist()
+    assert err == 0 and 0 <= redone <= (nbytes - 16) // 16
+    assert torch.equal(got[:, :, :S], want[:, :, :S])
+    assert bool((got[:, :, S:] == 0x55).all())  # rows past the range are not touched
+    # a few hundred keys against the CPU restatement of the reference's transform and projection
+    n = 300
+    k_np = keys[:, :, :n].float().cpu().numpy()
+    m_np = None if mean is None else mean.float().cpu().numpy()
+    M = np.float32(max_norm.view(torch.float32).item())
+    nk = norms[:, :, :n].cpu().numpy()
+    np.testing.assert_array_equal(nk, magicpig.norms(magicpig.centred(
+        k_np, None if m_np is None else m_np[:, :, None, :], "bf16"), "bf16"))
+    codes = magicpig.key_codes(k_np, m_np, nk, M, proj.float().cpu().numpy(), L, K, "bf16")
+    np.testing.assert_array_equal(got[:, :, :n, :L].cpu().numpy().astype(np.int64), codes)

@@ -41,8 +41,33 @@ def _oracle_wl(dtype="bf16", S=1000, seed=74):
     return wl
 
 
+PQ_CENT, PQ_ITERS = 16, 5
+
+
+def _pq_wl(S=1200, seed=76):
+    wl = workloads.pqcache(seed=seed, dtype="bf16", B=2, Hq=4, Hkv=2, S=S, D=64, sink=40, window=24, heavy=60,
+                           group_factor=8, bits=4, kmeans_iter=PQ_ITERS, n_clusters=8)
+    # a block of duplicated keys: equal scores on both sides of the shard boundaries
+    wl.k[:, :, 500:800] = wl.k[:, :, 100:400]
+    return wl
+
+
+def _pq_draws(wl):
+    """Initial centres and re-seed draws handed to every implementation (the reference draws them
+    with torch.randperm / torch.randint)."""
+    B, Hkv, S = wl.k.shape[0], wl.k.shape[1], wl.k.shape[2]
+    prm = wl.stack[-1][1]
+    groups, n = B * Hkv * prm["pq_group_factor"], S - prm["init_offset"]
+    init = workloads.pq_init_indices(77, groups, n, PQ_CENT)
+    reseed = np.random.default_rng(78).integers(0, n, size=(PQ_ITERS, groups, PQ_CENT)).astype(np.int64)
+    return init, reseed
+
+
 def _oracle_meta(wl):
     last = wl.stack[-1]
+    if last[0] == "pq_topk":
+        init, reseed = _pq_draws(wl)
+        return {"pq_init_indices": init, "pq_reseed_indices": reseed}
     return {"lsh_projection": last[1]["projection"]} if last[0] == "magicpig" else {}
 
 
@@ -178,7 +203,12 @@ def _native_sharded(wl, world, make_meta):
 
 def _proj_meta(wl):
     def make(dev):
+        import torch
+
         last = wl.stack[-1]
+        if last[0] == "pq_topk":
+            init, reseed = _pq_draws(wl)
+            return {"pq_init_indices": {0: torch.from_numpy(init)}, "pq_reseed_indices": {0: torch.from_numpy(reseed)}}
         if last[0] != "magicpig":
             return {}
         return {"projections": {0: workloads.to_torch(last[1]["projection"], wl.dtype, dev)}}
@@ -186,13 +216,14 @@ def _proj_meta(wl):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("case", ["magicpig_bf16", "magicpig_f32_sq2", "hash_bf16", "oracle_bf16", "oracle_f32"])
+@pytest.mark.parametrize("case", ["magicpig_bf16", "magicpig_f32_sq2", "hash_bf16", "oracle_bf16", "oracle_f32",
+                                  "pq_bf16"])
 @pytest.mark.parametrize("world", [2, 4])
 def test_gpu_sharded_equals_unsharded(case, world):
     wl = {"magicpig_bf16": lambda: _magicpig_wl("bf16"),
           "magicpig_f32_sq2": lambda: _magicpig_wl("f32", S=700, Sq=2),
           "hash_bf16": _hash_wl, "oracle_bf16": lambda: _oracle_wl("bf16"),
-          "oracle_f32": lambda: _oracle_wl("f32", S=900)}[case]()
+          "oracle_f32": lambda: _oracle_wl("f32", S=900), "pq_bf16": _pq_wl}[case]()
     dtype = wl.dtype
     full_mask, full_out = _native_unsharded(wl, _proj_meta(wl)("cuda:0"))
     plan, results = _native_sharded(wl, world, _proj_meta(wl))
@@ -214,3 +245,71 @@ def test_gpu_unshardable_masker_refuses_a_shard():
     wl = workloads.oracle_adaptive(seed=73, dtype="bf16", B=1, Hq=4, Hkv=2, S=512, D=64, sink=4, window=8)
     with pytest.raises(NotImplementedError):
         _native_sharded(wl, 2, lambda dev: {})
+
+
+# ------------------------------------------------------------------ GPUs: the peer-memory exchange
+def _nccl_rank(rank: int, world: int, port: int, results) -> None:
+    import torch
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from sparse_attention_hub.sparse_attention.research_attention.sharded import DistComm, PeerExchange
+        from sparse_attention_hub.sparse_attention.utils.mask_attention_utils import merge_attention_partials
+
+        comm = DistComm()
+        B, Hq, Sq, D = 2, 8, 3, 128
+        rows = B * Hq * Sq
+        ex = PeerExchange(comm, B, Hq, Sq, D, torch.device("cuda", rank))
+        sinks = torch.linspace(-1.0, 1.0, Hq, device="cuda")
+        ok = True
+        for step in range(5):  # both parities several times
+            gen = torch.Generator(device="cuda").manual_seed(100 * step + rank)
+            part = torch.randn((rows, D + 2), generator=gen, device="cuda")
+            part[:, D + 1] = part[:, D + 1].abs() + 0.5          # denominators
+            if step == 2 and rank == 0:
+                part[:4, D], part[:4, D + 1], part[:4, :D] = float("-inf"), 0.0, 0.0  # a rank that selected nothing
+            want = merge_attention_partials(comm.all_gather(part), B, Hq, Sq, torch.bfloat16, sinks)
+            got = ex.merge(part, torch.bfloat16, sinks)
+            ok &= bool(torch.equal(got, want))
+        ok &= ex.wait_errors() == 0
+        # replayed by a CUDA graph: the step number advances on the device
+        part = torch.randn((rows, D + 2), device="cuda")
+        part[:, D + 1] = part[:, D + 1].abs() + 0.5
+        want = merge_attention_partials(comm.all_gather(part), B, Hq, Sq, torch.bfloat16, None)
+        torch.cuda.synchronize()
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            ex.merge(part, torch.bfloat16, None)  # warm-up on the capture stream
+            stream.synchronize()
+            dist.barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                out = ex.merge(part, torch.bfloat16, None)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        ok &= bool(torch.equal(out, want)) and ex.wait_errors() == 0
+        results[rank] = ok
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_gpu_peer_exchange_two_nccl_ranks():
+    """`sah_attn_exchange_merge` on two GPUs against all-gather + `sah_attn_merge_parts`, bit for
+    bit, eagerly and replayed by a CUDA graph.  Needs two GPUs (skipped on a one-GPU box)."""
+    import torch
+    import torch.multiprocessing as mp
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world, port = 2, _free_port()
+    with mp.Manager() as mgr:
+        results = mgr.dict()
+        mp.spawn(_nccl_rank, args=(world, port, results), nprocs=world, join=True)
+        assert dict(results) == {0: True, 1: True}
