@@ -61,10 +61,13 @@ DEFAULT_WORKLOAD = "magicpig"
 REFERENCE_LONG_KEYS = 16384
 
 # DRAM traffic per algorithmic byte of one launch (dram__bytes_read.sum + dram__bytes_write.sum
-# over the bytes the kernel has to read), from ncu captures of small cases of the same kernel;
-# traffic grows in proportion to the rows gathered.
+# over the bytes the kernel has to read), from ncu captures of the same kernel: the headline
+# shape for HashAttention; for MagicPig the 65536-key case of the workload (the million-key
+# launch is too large to capture under a profiler; traffic grows in proportion to the rows
+# gathered).
 NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {
-    "hashattention": 225719552.0 / 219225088.0,
+    "hashattention": (221809920.0 + 4204032.0) / 219225088.0,        # masked_attention_mma_kernel
+    "magicpig:attention": (200355072.0 + 3793664.0) / 196420096.0,   # masked_attention_umma_kernel
 }
 
 

@@ -520,6 +520,17 @@ int sah_pq_assign(const void* x, int dtype, int64_t xs_b, int64_t xs_h, int64_t 
                   int sub_d, int n_cent, const float* centroids, uint8_t* codes, int64_t cap,
                   int dtype_math, void* stream);
 
+/* The assignment step of kmeans_batched (utils/pq_utils.py:220-257, :346-358) for bfloat16 keys,
+ * sub-vectors of 8 channels and 16..256 centroids (a multiple of 16), with the distance
+ * contraction on the tensor cores (tcgen05) and the argmin decided by the fixed-order float32
+ * distance among the centroids the product cannot tell apart: the codes equal those of
+ * sah_pq_assign(dtype_math = 0) bit for bit.  *errflag (device) is set when the bounded wait
+ * inside the kernel ran out; the caller then redoes the range with sah_pq_assign. */
+int sah_pq_assign_tc(const void* x, int64_t xs_b, int64_t xs_h, int64_t xs_s, int B, int Hkv,
+                     int64_t key_begin, int64_t key_end, int64_t init_offset, int n_sub, int sub_d,
+                     int n_cent, const float* centroids, uint8_t* codes, int64_t cap, int* errflag,
+                     int sm_count, void* stream);
+
 /* Per-cluster sums (float64 [groups][n_cent][sub_d]) and counts (int32
  * [groups][n_cent]) of the current assignment; both must be zeroed by the caller
  * (pq_utils.py:360-381 computes the same through one-hot masks). */

@@ -101,6 +101,44 @@ extern "C" int sah_pq_assign(const void* x, int dtype, int64_t xs_b, int64_t xs_
   return SAH_OK;
 }
 
+#include "sah_pq_tc.cuh"
+
+// The assignment step on the tensor cores; same codes as sah_pq_assign(dtype_math = 0).
+extern "C" int sah_pq_assign_tc(const void* x, int64_t xs_b, int64_t xs_h, int64_t xs_s, int B, int Hkv,
+                                int64_t key_begin, int64_t key_end, int64_t init_offset, int n_sub,
+                                int sub_d, int n_cent, const float* centroids, uint8_t* codes, int64_t cap,
+                                int* errflag, int sm_count, void* stream) {
+  SAH_REQUIRE(x && centroids && codes && errflag, "pq_assign_tc: null pointer");
+  SAH_REQUIRE(B > 0 && Hkv > 0 && n_sub > 0, "pq_assign_tc: bad extents");
+  SAH_REQUIRE(init_offset <= key_begin && key_begin <= key_end && key_end - init_offset <= cap,
+              "pq_assign_tc: bad key range");
+  if (sub_d != 8 || n_cent < 16 || n_cent > 256 || n_cent % 16 != 0)
+    return sah_fail(SAH_ERR_UNSUPPORTED, "pq_assign_tc: sub-vectors of 8 channels and 16..256 centroids in "
+                    "multiples of 16 (got %d, %d)", sub_d, n_cent);
+  SAH_REQUIRE((xs_s * 2) % 16 == 0 && (xs_h * 2) % 16 == 0 && (xs_b * 2) % 16 == 0 && ((uintptr_t)x % 16) == 0,
+              "pq_assign_tc: key rows must be 16-byte aligned");
+  if (key_begin == key_end) return SAH_OK;
+  static bool allowed = false;
+  if (!allowed) {
+    cudaError_t e = cudaFuncSetAttribute(pq_assign_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PtcCfg::SMEM);
+    if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "pq_assign_tc attr: %s", cudaGetErrorString(e));
+    allowed = true;
+  }
+  if (sm_count <= 0) sm_count = 148;
+  const int64_t groups = (int64_t)B * Hkv * n_sub;
+  const int64_t n_tiles = sah_ceil_div(key_end - key_begin, (int64_t)PTC_TILE);
+  int64_t slices = sah_ceil_div((int64_t)4 * sm_count, groups);  // about two waves of two CTAs per SM
+  if (slices > n_tiles) slices = n_tiles;
+  if (slices < 1) slices = 1;
+  SAH_REQUIRE(groups <= 65535, "pq_assign_tc: too many groups per launch");
+  dim3 grid((unsigned)slices, (unsigned)groups);
+  pq_assign_tc_kernel<<<grid, PTC_THREADS, PtcCfg::SMEM, (cudaStream_t)stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), xs_b, xs_h, xs_s, Hkv, key_begin, key_end, init_offset, n_sub,
+      n_cent, centroids, codes, cap, errflag);
+  SAH_LAUNCH_CHECK("pq_assign_tc");
+  return SAH_OK;
+}
+
 // Cluster sums in fp64 (so that the summation order does not reach the fp32
 // result) and counts; shared-memory accumulation per CTA, then global atomics.
 template <typename T>

@@ -129,6 +129,7 @@ _SIGNATURES = {
     "sah_lsh_key_den": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _I, _P, _P, _L, _P, _P, _P, _I, _P],
     "sah_lsh_prob": [_P, _I, _L, _L, _L, _I, _I, _I, _I, _I, _P, _P, _P, _L, _P, _P, _P, _P, _P, _L,
                      _I, _I, _P, _P, _I, _P],
+    "sah_pq_assign_tc": [_P, _L, _L, _L, _I, _I, _L, _L, _L, _I, _I, _I, _P, _P, _L, _P, _I, _P],
     "sah_pq_assign": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _L, _I, _I, _I, _P, _P, _L, _I, _P],
     "sah_pq_accumulate": [_P, _I, _L, _L, _L, _I, _I, _L, _L, _I, _I, _I, _P, _L, _P, _P, _P],
     "sah_pq_update": [_P, _I, _L, _L, _L, _I, _I, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P],

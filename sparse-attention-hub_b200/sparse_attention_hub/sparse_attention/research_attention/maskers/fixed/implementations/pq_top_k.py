@@ -23,6 +23,7 @@ first `2**bits` entries of a random permutation per group unless
 """
 
 from dataclasses import dataclass
+import os
 from typing import Any, Dict, Optional, Tuple, Union
 
 import torch
@@ -225,11 +226,28 @@ class PQCache(TopKMasker):
         shift2 = torch.empty(groups, dtype=torch.float32, device=dev)
         reseed_src = sparse_meta_data.get("pq_reseed_indices", {}).get(layer_idx)
         own_pos = torch.arange(n_cent, device=dev, dtype=torch.long).repeat(groups, 1).contiguous()
+        # the distance contraction of the assignment runs on the tensor cores when the shapes
+        # allow (bfloat16 keys, 8 channels per sub-vector, 16..256 centroids in multiples of 16)
+        use_tc = (os.environ.get("SAH_PQ_TC", "1") != "0" and k.dtype == torch.bfloat16 and sub_d == 8
+                  and 16 <= n_cent <= 256 and n_cent % 16 == 0 and k.data_ptr() % 16 == 0
+                  and all((k.stride(i) * 2) % 16 == 0 for i in range(3)))
+        tc_err = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.last_build_used_tensor_cores = use_tc
         for it in range(self.kmeans_iter):
             if n_local > 0:
-                _native.check(lib.sah_pq_assign(*kargs, B, Hkv, local_off, keys.shape[2], local_off, n_sub,
-                                                sub_d, n_cent, centroids.data_ptr(), codes.data_ptr(), cap, 0,
-                                                st), "sah_pq_assign")
+                if use_tc:
+                    _native.check(lib.sah_pq_assign_tc(k.data_ptr(), k.stride(0), k.stride(1), k.stride(2), B, Hkv,
+                                                       local_off, keys.shape[2], local_off, n_sub, sub_d, n_cent,
+                                                       centroids.data_ptr(), codes.data_ptr(), cap,
+                                                       tc_err.data_ptr(), _native.sm_count(dev), st),
+                                  "sah_pq_assign_tc")
+                    if int(tc_err.item()) != 0:  # a bounded wait inside the kernel ran out: fixed-order kernel
+                        use_tc = False
+                        tc_err.zero_()
+                if not use_tc:
+                    _native.check(lib.sah_pq_assign(*kargs, B, Hkv, local_off, keys.shape[2], local_off, n_sub,
+                                                    sub_d, n_cent, centroids.data_ptr(), codes.data_ptr(), cap, 0,
+                                                    st), "sah_pq_assign")
             sums.zero_()
             counts.zero_()
             if n_local > 0:

@@ -136,3 +136,46 @@ def test_gpu_decode_and_append_on_reference_codebook():
     np.testing.assert_array_equal(idx, g["append_idx"])
     np.testing.assert_array_equal(ptr, g["append_ptr"])
     np.testing.assert_allclose(out, g["append_out"], atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n_cent,n_keys", [(256, 20000), (16, 3000), (48, 777)])
+def test_gpu_assignment_on_tensor_cores_equals_the_fixed_order_kernel(n_cent, n_keys):
+    """`sah_pq_assign_tc` (tcgen05 distance contraction, fixed-order argmin among the near-minimal
+    centroids) writes the codes of `sah_pq_assign`, including ties (duplicated centroids and keys
+    that sit exactly on centroids) -- and those are the restatement's codes."""
+    import torch
+    from sparse_attention_hub import _native
+
+    lib = _native.load()
+    dev = "cuda:0"
+    B, Hkv, n_sub, sub_d, off = 2, 2, 16, 8, 5
+    D, S = n_sub * sub_d, n_keys + off
+    gen = torch.Generator(device=dev).manual_seed(n_cent)
+    keys = (torch.randn((B, Hkv, S, D), generator=gen, device=dev) * 1.5).to(torch.bfloat16)
+    groups = B * Hkv * n_sub
+    cent = torch.randn((groups, n_cent, sub_d), generator=gen, device=dev) * 1.2
+    cent[:, 3] = cent[:, 1]                       # a duplicated centroid: the lower index must win
+    sub = keys[:, :, off:].reshape(B, Hkv, n_keys, n_sub, sub_d)
+    cent.view(B, Hkv, n_sub, n_cent, sub_d)[:, :, :, 5] = sub[:, :, 7].float()   # a key on a centroid
+    cent = cent.contiguous()
+    cap = n_keys + 11
+    want = torch.full((B, Hkv, cap, n_sub), 255, dtype=torch.uint8, device=dev)
+    got = torch.full_like(want, 254)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    st = _native.stream_of(torch.device(dev))
+    _native.check(lib.sah_pq_assign(keys.data_ptr(), _native.SAH_BF16, keys.stride(0), keys.stride(1), keys.stride(2),
+                                    B, Hkv, off, S, off, n_sub, sub_d, n_cent, cent.data_ptr(), want.data_ptr(), cap,
+                                    0, st), "sah_pq_assign")
+    _native.check(lib.sah_pq_assign_tc(keys.data_ptr(), keys.stride(0), keys.stride(1), keys.stride(2), B, Hkv, off,
+                                       S, off, n_sub, sub_d, n_cent, cent.data_ptr(), got.data_ptr(), cap,
+                                       err.data_ptr(), 148, st), "sah_pq_assign_tc")
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    assert torch.equal(got[:, :, :n_keys], want[:, :, :n_keys])
+    assert bool((got[:, :, n_keys:] == 254).all())
+    # the restatement on a slice
+    n = min(n_keys, 400)
+    X = pq.split_keys(keys[:, :, : off + n].float().cpu().numpy(), off, n_sub)
+    codes = pq.assign(X, cent.cpu().numpy()).reshape(B, Hkv, n_sub, n).transpose(0, 1, 3, 2)
+    np.testing.assert_array_equal(got[:, :, :n].cpu().numpy(), codes)
