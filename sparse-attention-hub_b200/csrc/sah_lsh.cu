@@ -206,8 +206,10 @@ lsh_key_sign_kernel(const T* __restrict__ k, int64_t ks_b, int64_t ks_h, int64_t
 
   // one output column per thread, 8 keys at a time; single accumulator per (key, column),
   // channels ascending (products of dtype values, added in float)
+  // keys of this tile that exist (a decode step appends one key: one pass of eight, not eight)
+  const int kt_used = (int)((s1 - t0 < LSH_KT ? s1 - t0 : LSH_KT) + 7) & ~7;
   for (int o = threadIdx.x; o < nbits; o += 256) {
-    for (int k8 = 0; k8 < LSH_KT; k8 += 8) {
+    for (int k8 = 0; k8 < kt_used; k8 += 8) {
       float acc[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
@@ -232,7 +234,7 @@ lsh_key_sign_kernel(const T* __restrict__ k, int64_t ks_b, int64_t ks_h, int64_t
   // pack: bit j of table l is column l*K + j (magic_pig.py:120-150); the row of a key holds
   // its L codes and zero padding up to the row pitch
   const int LP = lsh_row_pitch<CodeT>(L);
-  for (int i = threadIdx.x; i < LP * LSH_KT; i += 256) {
+  for (int i = threadIdx.x; i < LP * kt_used; i += 256) {
     const int kk = i / LP, l = i % LP;
     const int64_t s = t0 + kk;
     if (s >= s1) continue;
@@ -398,12 +400,33 @@ lsh_query_kernel(const T* __restrict__ q, int64_t qs_b, int64_t qs_h, int64_t qs
     if (qmu != nullptr && lane == 0) qmu[row] = mu;
   }
   __syncthreads();
-  for (int o = threadIdx.x; o < nbits; o += 256) {
-    float acc = 0.f;
-    for (int c = 0; c < D; ++c)
-      acc = __fadd_rn(acc, __fmul_rn(qn[c], sah_to_float<T>(proj[(int64_t)c * nbits + o])));
-    acc = __fadd_rn(acc, __fmul_rn(0.f, sah_to_float<T>(proj[(int64_t)D * nbits + o])));
-    sb[o] = acc > 0.f ? 1 : 0;
+  // A thread owns the columns o, o + 256, ... (four at a time); per column one accumulator and
+  // channels ascending, as everywhere.  The hyperplane values of 16 channels x 4 columns are
+  // requested before the first is used: this kernel sits on the critical path of every decode
+  // step and would otherwise be a chain of 129 dependent (cold) loads per column.
+  for (int o0 = threadIdx.x; o0 < nbits; o0 += 4 * 256) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int c0 = 0; c0 < D; c0 += 16) {
+      T pv[4][16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          pv[j][i] = (o0 + j * 256 < nbits) ? proj[(int64_t)(c0 + i) * nbits + o0 + j * 256] : sah_from_float<T>(0.f);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          acc[j] = __fadd_rn(acc[j], __fmul_rn(qn[c0 + i], sah_to_float<T>(pv[j][i])));
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int o = o0 + j * 256;
+      if (o < nbits) {
+        const float a = __fadd_rn(acc[j], __fmul_rn(0.f, sah_to_float<T>(proj[(int64_t)D * nbits + o])));
+        sb[o] = a > 0.f ? 1 : 0;
+      }
+    }
   }
   __syncthreads();
   for (int l = threadIdx.x; l < L; l += 256) {
