@@ -16,13 +16,15 @@ Prints one JSON line (rank 0).  `value` is whole-job decode tokens per second pe
 everything resident in HBM; `e2e` is the same through the public API with host buffers: the
 query and one appended key/value row come from pinned host memory, the appended key is hashed
 inside the step (with N > 1 that includes the ranks' agreement on the largest key norm), and
-the output is read back to the host.  A "step" of the command line is timed as `repeats`
+the output is read back to the host; it is timed with CUDA events around the copies and the step
+(`e2e.wall_ms_per_step` is the host clock around replay + synchronise of the same step).  A
+"step" of the command line is timed as `repeats`
 passes back to back (L2 flushed before each), so that the timed region is at least 100 ms and
 the clock sampler sees it; all times are per pass.
 
 `--workload hashattention | sink_local | oracle_topk | oracle_adaptive | oracle_topp | quest |
 pqcache` run the batch-sharded configurations (one batch per GPU, no collective, weak scaling);
-`--workload hashattention_long` is the second sequence-sharded one.
+`--workload hashattention_long` and `--workload pqcache_long` are the other sequence-sharded ones.
 
 `--impl reference` times the reference's own `ResearchAttention.custom_attention` (CPU PyTorch,
 from oracle/_ref, which oracle/make_ref.py makes) on the host cores on a bounded sample of the
@@ -601,20 +603,34 @@ def run_native(args) -> None:
             mark_appended()
             o = eager_step(q_dev)
             out_host.copy_(o, non_blocking=True)
-        torch.cuda.synchronize()
 
     for _ in range(3):
         e2e_step()
+        torch.cuda.synchronize()
     barrier()
-    e2e_times = []
+    # Device time of the end-to-end step: events on the launching stream around the replay
+    # (H2D copies, the step, the D2H copy), the L2 flush directly in front of the first event.
+    # The wall clock of the same steps (launch latency and the wake-up of the synchronising
+    # host thread included) is reported beside it.
+    e2e_times, e2e_events = [], []
     for _ in range(passes):
         timer.flush.zero_()
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         e2e_step()
+        torch.cuda.synchronize()
         e2e_times.append(time.perf_counter() - t0)
     barrier()
-    e2e_total = float(sum(e2e_times))
+    for _ in range(passes):
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        timer.flush.zero_()
+        ev0.record()
+        e2e_step()
+        ev1.record()
+        e2e_events.append((ev0, ev1))
+    barrier()
+    e2e_wall_total = float(sum(e2e_times))
+    e2e_total = float(sum(a.elapsed_time(b) for a, b in e2e_events)) * 1e-3
 
     if world > 1:
         import torch.distributed as dist
@@ -682,6 +698,9 @@ def run_native(args) -> None:
                 "h2d_bytes_per_step": int((q_host.numel() + kn_host.numel() + vn_host.numel()) * esz),
                 "d2h_bytes_per_step": int(out_host.numel() * esz),
                 "ms_per_step": e2e_total / passes * 1e3,
+                "wall_ms_per_step": e2e_wall_total / passes * 1e3,
+                "timing": "CUDA events around H2D copies + step + D2H copy; wall_ms_per_step is the host clock "
+                          "around replay + synchronise of the same step",
             },
             "gpu_launches": int(launches_per_pass * passes),
             "clocks": clocks.summary(),
@@ -899,20 +918,34 @@ def run_long_native(args) -> None:
             o = eager_step(q_dev)
             if rank == 0:
                 out_host.copy_(o, non_blocking=True)
-        torch.cuda.synchronize()
 
     for _ in range(3):
         e2e_step()
+        torch.cuda.synchronize()
     barrier()
-    e2e_times = []
+    # Device time of the end-to-end step: events on the launching stream around the replay
+    # (H2D copies, the step, the D2H copy), the L2 flush directly in front of the first event.
+    # The wall clock of the same steps (launch latency and the wake-up of the synchronising
+    # host thread included) is reported beside it.
+    e2e_times, e2e_events = [], []
     for _ in range(passes):
         timer.flush.zero_()
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         e2e_step()
+        torch.cuda.synchronize()
         e2e_times.append(time.perf_counter() - t0)
     barrier()
-    e2e_total = float(sum(e2e_times))
+    for _ in range(passes):
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        timer.flush.zero_()
+        ev0.record()
+        e2e_step()
+        ev1.record()
+        e2e_events.append((ev0, ev1))
+    barrier()
+    e2e_wall_total = float(sum(e2e_times))
+    e2e_total = float(sum(a.elapsed_time(b) for a, b in e2e_events)) * 1e-3
 
     stats = torch.tensor([total_ms, e2e_total, float(union_rows), float(step_bytes)], device=dev,
                          dtype=torch.float64)
@@ -983,7 +1016,10 @@ def run_long_native(args) -> None:
             "e2e": {"value": B / (e2e_total / passes), "unit": UNIT,
                     "h2d_bytes_per_step": int(q_host.numel() * 2 * world + (kn_host.numel() + vn_host.numel()) * 2),
                     "d2h_bytes_per_step": int(out_host.numel() * 2),
-                    "ms_per_step": e2e_total / passes * 1e3},
+                    "ms_per_step": e2e_total / passes * 1e3,
+                    "wall_ms_per_step": e2e_wall_total / passes * 1e3,
+                    "timing": "CUDA events around H2D copies + step + D2H copy (maximum over ranks); "
+                              "wall_ms_per_step is rank 0's host clock around replay + synchronise"},
             "gpu_launches": int(launches_per_pass * passes),
             "clocks": clocks.summary(),
         }

@@ -19,10 +19,12 @@ def apply(kind, prm, st, q, k, v, scaling, attention_mask, meta) -> None:
         n, cent, sd = S - off, 2 ** bits, D // n_sub
         if "pq_centroids" not in meta:
             X = pq.split_keys(k, off, n_sub)
+            if prm.get("metric", "euclidean") == "ip":  # pq_top_k.py:233-237
+                X, meta["pq_ip2l2_phi"] = pq.ip2l2_augment(X, st.dtype)
             init_idx = np.asarray(meta["pq_init_indices"])
             init = X[np.arange(X.shape[0])[:, None], init_idx]
             codes, C = pq.kmeans(X, init, prm["kmeans_iter"], meta.get("pq_reseed_indices"))
-            meta["pq_centroids"] = round_to(C, st.dtype).reshape(B, Hkv, n_sub, cent, sd)
+            meta["pq_centroids"] = round_to(C, st.dtype).reshape(B, Hkv, n_sub, cent, X.shape[2])
             meta["pq_codes"] = codes.reshape(B, Hkv, n_sub, n).transpose(0, 1, 3, 2)
         s = pq.scores(q, meta["pq_centroids"], meta["pq_codes"], st.dtype)
         meta["pq_scores"] = s

@@ -76,14 +76,31 @@ def split_keys(k: np.ndarray, init_offset: int, n_sub: int) -> np.ndarray:
     return np.ascontiguousarray(x).reshape(B * Hkv * n_sub, S - init_offset, sd)
 
 
+def ip2l2_augment(X: np.ndarray, dtype: str):
+    """ip2l2_augment (utils/pq_utils.py:585-612) on dtype values: [g,n,d] -> ([g,n,d+1], phi [g,1,1]).
+    Every tensor operation of the reference is one rounding to the dtype: x**2, the sum over the
+    sub-vector (float32 accumulator, rounded once), phi - |x|^2, the square root."""
+    X = np.asarray(X, np.float32)
+    sq = round_to(X * X, dtype)
+    acc = np.zeros(X.shape[:2], np.float32)
+    for j in range(X.shape[2]):
+        acc = acc + sq[:, :, j]
+    norms_sq = round_to(acc, dtype)[..., None]
+    phi = norms_sq.max(axis=1, keepdims=True)
+    extra = round_to(np.sqrt(round_to(phi - norms_sq, dtype)), dtype)
+    return np.concatenate([X, extra], axis=2).astype(np.float32), phi
+
+
 def scores(q, centroids, codes, dtype: str) -> np.ndarray:
     """_compute_pq_scores (pq_top_k.py:406-490).
-    q [B,Hq,Sq,D]; centroids [B,Hkv,n_sub,cent,sd] (dtype values); codes [B,Hkv,n,n_sub].
+    q [B,Hq,Sq,D]; centroids [B,Hkv,n_sub,cent,sd] (dtype values; with metric "ip" they carry one
+    more column, which scoring leaves out, pq_top_k.py:443-458); codes [B,Hkv,n,n_sub].
     lut = q_sub . centroid (fma over ascending dims, rounded to dtype); score = fp32 sum of
     the table entries over ascending sub-vectors, rounded once.  -> [B,Hq,Sq,n]"""
     q = np.asarray(q, np.float32)
     B, Hq, Sq, D = q.shape
-    _, Hkv, n_sub, cent, sd = centroids.shape
+    _, Hkv, n_sub, cent, _ = centroids.shape
+    sd = D // n_sub
     G = Hq // Hkv
     n = codes.shape[2]
     out = np.empty((B, Hq, Sq, n), np.float32)

@@ -440,6 +440,16 @@ masked_attention_umma_kernel(AttnArgs a, int* __restrict__ tickets, int* __restr
 #ifdef AUM_PROF
       if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) atomicAdd((unsigned long long*)&aum_prof[15], (unsigned long long)(clock64() - prof_tile_t0));
 #endif
+      // Probabilities with the maxima in use so far, before the other warps' maxima are known:
+      // in the common case no row's maximum grows by more than the threshold and these stand, so
+      // the exchange is off the critical path; otherwise they are redone below.
+      float pr[RMAX];
+      auto probabilities = [&]() {
+#pragma unroll
+        for (int r = 0; r < RMAX; ++r)
+          pr[r] = (sv[r] != -INFINITY) ? __expf(sv[r] - m_used[r]) * wv[r] : 0.f;
+      };
+      probabilities();
       {
         AUM_T0();
         ok = aum_wait_warp(max_bar + gg * 8, (uint32_t)(j & 1), abort_sm, errflag);
@@ -447,7 +457,7 @@ masked_attention_umma_kernel(AttnArgs a, int* __restrict__ tickets, int* __restr
       }
       if (!ok) break;
       float alpha[RMAX];
-      bool rescale = false;
+      bool rescale = false, moved = false;
 #pragma unroll
       for (int r = 0; r < RMAX; ++r) {
         const float* wm = wmax_sm + gg * 64 + r;
@@ -457,19 +467,18 @@ masked_attention_umma_kernel(AttnArgs a, int* __restrict__ tickets, int* __restr
           alpha[r] = (m_used[r] == -INFINITY) ? 0.f : __expf(m_used[r] - tm);
           rescale |= (alpha[r] != 0.f);  // an accumulator column scaled by 0 was 0 already
           m_used[r] = tm;
+          moved = true;
         }
       }
+      if (moved) probabilities();  // uniform over the group: every thread sees the same maxima
       uint32_t pk[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) pk[i] = 0u;
 #pragma unroll
       for (int r = 0; r < RMAX; r += 2) {
-        float p0 = 0.f, p1 = 0.f;
-        if (sv[r] != -INFINITY) p0 = __expf(sv[r] - m_used[r]) * wv[r];
-        if (sv[r + 1] != -INFINITY) p1 = __expf(sv[r + 1] - m_used[r + 1]) * wv[r + 1];
-        l_thr[r] = l_thr[r] * alpha[r] + p0;
-        l_thr[r + 1] = l_thr[r + 1] * alpha[r + 1] + p1;
-        pk[r >> 1] = atm_pack_bf16(p0, p1);
+        l_thr[r] = l_thr[r] * alpha[r] + pr[r];
+        l_thr[r + 1] = l_thr[r + 1] * alpha[r + 1] + pr[r + 1];
+        pk[r >> 1] = atm_pack_bf16(pr[r], pr[r + 1]);
       }
       // the group's P buffer is free, and its accumulator quiet, once the product of the group's
       // previous tile has completed

@@ -117,9 +117,8 @@ class PQCache(TopKMasker):
         heavy = self._calculate_effective_size(self.heavy_size, total)
         if total <= heavy + self.init_offset + dims.seq_len_queries + 2 ** self.pq_bits:
             return self._create_full_mask(dims, previous_mask.dtype, previous_mask.device)
-        if self.metric == "ip":
-            raise NotImplementedError("PQCache metric 'ip' (augmented inner product) is not built; "
-                                      "use metric='euclidean'")
+        if self.metric == "ip" and shard is not None:
+            raise NotImplementedError("PQCache metric 'ip' on a sequence shard is not built")
         if self.pq_bits > 8:
             raise NotImplementedError("PQCache codes are bytes: pq_bits <= 8")
         _native.require_cuda(keys, "keys")
@@ -211,6 +210,19 @@ class PQCache(TopKMasker):
         st = _native.stream_of(dev)
         groups = B * Hkv * n_sub
         k, kargs = self._key_args(keys)
+        if self.metric == "ip":
+            # inner product -> L2 (utils/pq_utils.py:585-612): every sub-vector of the clustered keys
+            # gets the column sqrt(phi - |x|^2), phi the largest |x|^2 of its group; the clustering
+            # then runs on sub-vectors of sub_d + 1 channels of a tensor of its own
+            sub = k[:, :, local_off:, :].reshape(B, Hkv, n_local, n_sub, sub_d)
+            norms_sq = (sub ** 2).sum(dim=4, keepdim=True)
+            phi = norms_sq.amax(dim=2, keepdim=True)                       # [B, Hkv, 1, n_sub, 1]
+            k = torch.cat([sub, torch.sqrt(phi - norms_sq)], dim=4).reshape(B, Hkv, n_local, n_sub * (sub_d + 1))
+            k = k.contiguous()
+            kargs = (k.data_ptr(), _native.dtype_code(k.dtype), k.stride(0), k.stride(1), k.stride(2))
+            sparse_meta_data["pq_ip2l2_phi"][layer_idx] = phi.permute(0, 1, 3, 2, 4).reshape(groups, 1, 1)
+            sub_d += 1
+            local_off = 0
         init = sparse_meta_data.get("pq_init_indices", {}).get(layer_idx)
         if init is None:
             init = torch.stack([torch.randperm(n_keys, device=dev)[:n_cent] for _ in range(groups)])
@@ -237,7 +249,7 @@ class PQCache(TopKMasker):
             if n_local > 0:
                 if use_tc:
                     _native.check(lib.sah_pq_assign_tc(k.data_ptr(), k.stride(0), k.stride(1), k.stride(2), B, Hkv,
-                                                       local_off, keys.shape[2], local_off, n_sub, sub_d, n_cent,
+                                                       local_off, k.shape[2], local_off, n_sub, sub_d, n_cent,
                                                        centroids.data_ptr(), codes.data_ptr(), cap,
                                                        tc_err.data_ptr(), _native.sm_count(dev), st),
                                   "sah_pq_assign_tc")
@@ -245,7 +257,7 @@ class PQCache(TopKMasker):
                         use_tc = False
                         tc_err.zero_()
                 if not use_tc:
-                    _native.check(lib.sah_pq_assign(*kargs, B, Hkv, local_off, keys.shape[2], local_off, n_sub,
+                    _native.check(lib.sah_pq_assign(*kargs, B, Hkv, local_off, k.shape[2], local_off, n_sub,
                                                     sub_d, n_cent, centroids.data_ptr(), codes.data_ptr(), cap, 0,
                                                     st), "sah_pq_assign")
             sums.zero_()
@@ -308,12 +320,26 @@ class PQCache(TopKMasker):
                 grown[:, :, : cached.length] = cached.codes[:, :, : cached.length]
                 cached.codes = grown
             k, kargs = self._key_args(keys)
-            cent32 = centroids.float().reshape(-1, n_cent, sub_d).contiguous()
-            _native.check(
-                lib.sah_pq_assign(*kargs, B, Hkv, local_off + cached.length, keys.shape[2],
-                                  local_off, n_sub, sub_d, n_cent, cent32.data_ptr(),
-                                  cached.codes.data_ptr(), cached.codes.shape[2], 1,
-                                  _native.stream_of(keys.device)), "sah_pq_assign")
+            cd = centroids.shape[-1]  # sub_d, or sub_d + 1 when the codebook was clustered with metric "ip"
+            cent32 = centroids.float().reshape(-1, n_cent, cd).contiguous()
+            if cd == sub_d:
+                _native.check(
+                    lib.sah_pq_assign(*kargs, B, Hkv, local_off + cached.length, keys.shape[2],
+                                      local_off, n_sub, sub_d, n_cent, cent32.data_ptr(),
+                                      cached.codes.data_ptr(), cached.codes.shape[2], 1,
+                                      _native.stream_of(keys.device)), "sah_pq_assign")
+            else:
+                # appended keys are augmented with a zero column (pq_top_k.py:371-383); the new rows
+                # go through the same kernel as a tensor of their own, written behind the old codes
+                first = local_off + cached.length
+                new = k[:, :, first:, :].reshape(B, Hkv, n_now - cached.length, n_sub, sub_d)
+                new = torch.cat([new, torch.zeros_like(new[..., :1])], dim=4)
+                new = new.reshape(B, Hkv, n_now - cached.length, n_sub * cd).contiguous()
+                _native.check(
+                    lib.sah_pq_assign(new.data_ptr(), _native.dtype_code(new.dtype), new.stride(0), new.stride(1),
+                                      new.stride(2), B, Hkv, 0, new.shape[2], -cached.length, n_sub, cd, n_cent,
+                                      cent32.data_ptr(), cached.codes.data_ptr(), cached.codes.shape[2], 1,
+                                      _native.stream_of(keys.device)), "sah_pq_assign")
             cached.length = n_now
         sparse_meta_data["pq_codebook"][layer_idx] = cached
         return centroids, cached

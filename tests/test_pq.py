@@ -179,3 +179,54 @@ def test_gpu_assignment_on_tensor_cores_equals_the_fixed_order_kernel(n_cent, n_
     X = pq.split_keys(keys[:, :, : off + n].float().cpu().numpy(), off, n_sub)
     codes = pq.assign(X, cent.cpu().numpy()).reshape(B, Hkv, n_sub, n).transpose(0, 1, 3, 2)
     np.testing.assert_array_equal(got[:, :, :n].cpu().numpy(), codes)
+
+
+# ------------------------------------------------------------------ metric "ip"
+def _ip_workload():
+    wl = workloads.pqcache(seed=45, dtype="bf16", B=1, Hq=8, Hkv=2, S=600, D=128, sink=4, window=16,
+                           heavy=32, group_factor=N_SUB, bits=4, kmeans_iter=5, n_clusters=16)
+    wl.stack[-1][1]["metric"] = "ip"
+    return wl
+
+
+def test_pq_ip_metric_restatement_equals_the_reference():
+    """The inner-product metric (utils/pq_utils.py:585-640): augmented clustering, scores on the
+    first sub_d centroid columns -- phi, centroids, codes, index sets and output of the reference."""
+    g = load_golden("pq_stack_ip_bf16")
+    wl = _ip_workload()
+    meta = {"pq_init_indices": g["init_idx"],
+            "pq_reseed_indices": np.broadcast_to(g["reseed"], (5,) + g["reseed"].shape)}
+    mask, out, meta = stacks.run_stack(wl.stack, wl.q, wl.k[:, :, :592], wl.v[:, :, :592], wl.scaling, "bf16",
+                                       meta=meta)
+    np.testing.assert_array_equal(meta["pq_ip2l2_phi"].reshape(-1), g["phi"].reshape(-1))
+    np.testing.assert_array_equal(meta["pq_centroids"], g["centroids"])
+    np.testing.assert_array_equal(meta["pq_codes"].transpose(0, 2, 1, 3), g["codes_first"])
+    _check_mask(mask, g, "first_")
+    np.testing.assert_allclose(out, g["first_out"], atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.gpu
+def test_gpu_ip_metric_build_decode_and_append_equal_the_reference():
+    import torch
+
+    g = load_golden("pq_stack_ip_bf16")
+    wl = _ip_workload()
+    reseed = np.broadcast_to(g["reseed"], (5,) + g["reseed"].shape).copy()
+    meta = {"pq_init_indices": {0: torch.from_numpy(g["init_idx"])},
+            "pq_reseed_indices": {0: torch.from_numpy(reseed)}}
+    short = workloads.DecodeWorkload(wl.name, wl.dtype, wl.q, wl.k[:, :, :592], wl.v[:, :, :592],
+                                     wl.scaling, wl.stack)
+    (idx, ptr, data), out = _native_stack(short, meta)
+    np.testing.assert_array_equal(meta["pq_ip2l2_phi"][0].float().cpu().numpy().reshape(-1), g["phi"].reshape(-1))
+    np.testing.assert_array_equal(meta["pq_centroids"][0].float().cpu().numpy(), g["centroids"])
+    np.testing.assert_array_equal(meta["pq_codebook"][0].to_reference_layout().cpu().numpy(), g["codes_first"])
+    np.testing.assert_array_equal(idx, g["first_idx"])
+    np.testing.assert_array_equal(ptr, g["first_ptr"])
+    np.testing.assert_allclose(out, g["first_out"], atol=2e-2, rtol=2e-2)
+    # eight appended keys: a zero column instead of the augmentation (pq_top_k.py:371-383)
+    (idx, ptr, data), out = _native_stack(wl, meta)
+    np.testing.assert_array_equal(meta["pq_codebook"][0].to_reference_layout().cpu().numpy(),
+                                  g["codes_after_append"])
+    np.testing.assert_array_equal(idx, g["append_idx"])
+    np.testing.assert_array_equal(ptr, g["append_ptr"])
+    np.testing.assert_allclose(out, g["append_out"], atol=2e-2, rtol=2e-2)
