@@ -634,8 +634,9 @@ int sah_masked_attention(const void* q, const void* k, const void* v, int dtype,
 /* sah_masked_attention (bfloat16) over a union list made by sah_attn_plan_lsh, with the
  * MagicPig sampling weights computed where the key row already is: the weight of a
  * sampled key is 1 / (p + 1e-6) (Mask.apply_inv_mask_dense, utils/mask.py:718-740) with
- * p = 1 - (1 - (1 - acos(c)/pi)^K)^L read from prob_table (uint16 [65536], bf16 bits of
- * the clamped cosine -> bf16 bits of p, the chain of magic_pig.py:389-403) and
+ * p = 1 - (1 - (1 - acos(c)/pi)^K)^L (the chain of magic_pig.py:389-403); the weight is read
+ * from weight_table (uint16 [65536]: bf16 bits of the clamped cosine -> bf16 bits of
+ * bf16(1 / bf16(p + 1e-6)), 0 where p is 0: such an entry is not part of the mask) and
  * c = (qhat . k - qmu) / (M * |transformed key|) evaluated in float32 and rounded once
  * to bfloat16.  The reference rounds every step of that cosine to bfloat16
  * (:332-372), so a weight can differ from the reference's by the effect of one bfloat16
@@ -651,7 +652,7 @@ int sah_masked_attention_lsh(const void* q, const void* k, const void* v, int64_
                              const float* sinks, const sah_attn_sizes* sizes, const int32_t* ucols,
                              const uint16_t* umemb, const float* uinv, const int32_t* ucount,
                              float* partial, const void* qhat, const float* qmu,
-                             const uint16_t* prob_table, void* out, float* part_out, float* w_dump,
+                             const uint16_t* weight_table, void* out, float* part_out, float* w_dump,
                              void* stream);
 
 /* Measurement aid (no counterpart in the reference): the K/V row gather of a planned
@@ -677,6 +678,12 @@ int sah_attn_gather_probe(const void* k, const void* v, int64_t ks_b, int64_t ks
 int sah_attn_select_kernel(int which);
 /* Name of the attention kernel that the most recent sah_masked_attention* call launched. */
 const char* sah_attn_last_kernel(void);
+/* Self-test of the bounded device-side wait used by the tcgen05 kernels (no counterpart in the
+ * reference): one CTA waits on an mbarrier that nothing arrives at, for at most limit_us
+ * (1 .. 100000).  After the stream has finished, *errflag (device int, zeroed by the caller) is
+ * non-zero and *waited_ns (device) holds how long the wait lasted; the kernel has returned
+ * normally and the context is usable.  Nothing faults, traps or hangs. */
+int sah_wait_selftest(int limit_us, int* errflag, unsigned long long* waited_ns, void* stream);
 
 /* Merge n_parts partial results (parts [n_parts][rows][D+2], the part_out of
  * sah_masked_attention on every shard) into out [B][Sq][Hq][D]: the

@@ -460,7 +460,7 @@ struct AttnArgs {
   // MagicPig weights evaluated inside the bf16 kernel (uw then holds one constant per entry)
   const __nv_bfloat16* qhat;  // [rows][D] centred unit queries
   const float* qmu;           // [rows] qhat . key mean
-  const uint16_t* ptable;     // [65536] bf16 bits of the cosine -> bits of the probability
+  const uint16_t* ptable;     // [65536] bf16 bits of the cosine -> bits of the weight 1 / (p + 1e-6)
   float* w_dump;              // optional [groups][S][R]: the weights used (tests)
   // TMA copy stage: K and V as 2-D [rows][D] tensors, row = b * rows_b + h * rows_h + key
   int64_t k_rows_b, k_rows_h, v_rows_b, v_rows_h;
@@ -912,7 +912,7 @@ static int masked_attention_impl(const void* q, const void* k, const void* v, in
     int* errflag = tickets + groups;  // set when a bounded wait inside the kernel ran out
     // long lists: keys as the M dimension of tcgen05 tiles; otherwise the mma.sync kernel
     const int umma = aum_requested();
-    if (D == 128 && (umma == 1 || (umma < 0 && aum_default(lsh != nullptr, S)))) {
+    if (D == 128 && (umma == 1 || (umma < 0 && aum_default(lsh != nullptr, S, groups)))) {
       bool launched = false;
       rc = launch_attention_umma(a, B, groups, tickets, errflag, sinks, out, part_out, lsh != nullptr, st,
                                  &launched);
@@ -964,6 +964,34 @@ extern "C" int sah_debug_umma_prof(long long* host_out, int reset) {
 
 extern "C" const char* sah_attn_last_kernel(void) { return g_last_attn_kernel; }
 
+// Self-test of the bounded wait that every mbarrier wait of the tcgen05 kernels goes through:
+// one CTA waits, for at most `limit_us`, on a barrier that nothing will ever arrive at.  The
+// wait runs out, the error word is set, the kernel returns normally and the context stays
+// usable -- the behaviour the kernels rely on when a producer or a peer does not show up.
+__global__ void wait_selftest_kernel(unsigned long long limit_ns, int* __restrict__ errflag,
+                                     unsigned long long* __restrict__ waited_ns) {
+  __shared__ __align__(8) unsigned long long bar_storage;
+  __shared__ int abort_word;
+  const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&bar_storage);
+  if (threadIdx.x == 0) {
+    atm_mbar_init(bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    abort_word = 0;
+  }
+  __syncthreads();
+  const unsigned long long t0 = aum_now_ns();
+  const bool ok = aum_wait_warp(bar, 0u, &abort_word, errflag, 0u, limit_ns);
+  if (threadIdx.x == 0) *waited_ns = ok ? 0ull : aum_now_ns() - t0;
+}
+
+extern "C" int sah_wait_selftest(int limit_us, int* errflag, unsigned long long* waited_ns, void* stream) {
+  SAH_REQUIRE(errflag && waited_ns, "wait_selftest: null pointer");
+  SAH_REQUIRE(limit_us > 0 && limit_us <= 100000, "wait_selftest: limit of 1 us .. 100 ms");
+  wait_selftest_kernel<<<1, 64, 0, (cudaStream_t)stream>>>((unsigned long long)limit_us * 1000ull, errflag, waited_ns);
+  SAH_LAUNCH_CHECK("wait_selftest");
+  return SAH_OK;
+}
+
 extern "C" int sah_attn_select_kernel(int which) {
   if (which < -1 || which > 1) return -2;
   const int prev = aum_setting;
@@ -996,12 +1024,12 @@ extern "C" int sah_masked_attention_lsh(const void* q, const void* k, const void
                                         const sah_attn_sizes* sizes, const int32_t* ucols,
                                         const uint16_t* umemb, const float* uinv,
                                         const int32_t* ucount, float* partial, const void* qhat,
-                                        const float* qmu, const uint16_t* prob_table, void* out,
+                                        const float* qmu, const uint16_t* weight_table, void* out,
                                         float* part_out, float* w_dump,
                                         void* stream) {
-  SAH_REQUIRE(uinv && qhat && qmu && prob_table, "masked_attention_lsh: null pointer");
+  SAH_REQUIRE(uinv && qhat && qmu && weight_table, "masked_attention_lsh: null pointer");
   SAH_REQUIRE((uintptr_t)qhat % 16 == 0, "masked_attention_lsh: qhat must be 16-byte aligned");
-  AttnLsh lsh = {qhat, qmu, prob_table, w_dump};
+  AttnLsh lsh = {qhat, qmu, weight_table, w_dump};
   return masked_attention_impl(q, k, v, SAH_BF16, qs_b, qs_h, qs_q, ks_b, ks_h, ks_s, vs_b, vs_h,
                                vs_s, B, Hq, Hkv, Sq, S, D, scaling, bias, bias_s_b, bias_s_h,
                                bias_s_q, sinks, sizes, ucols, umemb, uinv, ucount, partial, out,

@@ -141,16 +141,16 @@ struct AtmCfg {
   static constexpr int SMEM = (TMA ? 1024 : 0) + ATM_WARPS * WARP_BYTES + META_BYTES + BAR_BYTES;
 };
 
-// MagicPig weight of one (row, key) pair from the centred cosine (see the header comment);
-// 0 when the probability is 0 in bfloat16: the reference's dense mask holds a zero there,
-// which means "not selected" (utils/mask.py:19-21).
+// MagicPig weight of one (row, key) pair from the centred cosine (see the header comment): the
+// table maps the cosine's bfloat16 bits to the bits of 1 / (p + 1e-6), rounded as the reference
+// rounds it, and to 0 where the probability is 0 in bfloat16: the reference's dense mask holds
+// a zero there, which means "not selected" (utils/mask.py:19-21).
 __device__ __forceinline__ float atm_lsh_weight(float dot_hat, float qmu, float inv_md,
-                                                const uint16_t* __restrict__ ptable) {
+                                                const uint16_t* __restrict__ wtable) {
   float c = __fmul_rn(__fsub_rn(dot_hat, qmu), inv_md);
   c = __bfloat162float(__float2bfloat16_rn(c));
   c = fminf(fmaxf(c, -1.0f), 1.0f);
-  const float p = __uint_as_float(((uint32_t)__ldg(ptable + (__float_as_uint(c) >> 16))) << 16);
-  return p == 0.f ? 0.f : sah_inv_weight<__nv_bfloat16>(p);
+  return __uint_as_float(((uint32_t)__ldg(wtable + (__float_as_uint(c) >> 16))) << 16);
 }
 
 // The CTA has written its partial (running maximum, denominator and unnormalised output per

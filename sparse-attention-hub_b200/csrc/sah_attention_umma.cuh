@@ -579,11 +579,15 @@ masked_attention_umma_kernel(AttnArgs a, int* __restrict__ tickets, int* __restr
 }
 
 // Which problems take the tcgen05 kernel when neither the caller nor the environment says.
-// Measured on B200: with MagicPig weights evaluated in place and a sequence of a million keys
-// (a union list of ~770 000 rows per KV group) it is 9 % faster than the mma.sync kernel; on
-// lists of up to ~100 000 rows the mma.sync kernel, whose fixed costs are lower, is ahead.
+// Measured on B200 (attention kernel, tcgen05 against mma.sync): MagicPig weights in place at a
+// million keys (8 KV groups, ~770 000 rows each) 735 against 831 us; 64 KV groups with lists
+// of a few thousand rows (HashAttention and Quest at B = 8, S = 32768) 64 against 69 us and
+// 56 against 61 us.  In between -- 8 to 32 groups with lists of 10^4..10^5 rows -- the
+// mma.sync kernel, with two CTAs per SM and lower fixed costs, is ahead by 5-40 %.
 #define AUM_DEFAULT_MIN_KEYS (512 * 1024)
-static bool aum_default(bool lsh, int64_t S) { return lsh && S >= AUM_DEFAULT_MIN_KEYS; }
+static bool aum_default(bool lsh, int64_t S, int groups) {
+  return (lsh && S >= AUM_DEFAULT_MIN_KEYS) || (groups >= 64 && S <= 65536);
+}
 
 // The kernel choice: a process-wide setting (sah_attn_select_kernel), else SAH_ATTN_UMMA in the
 // environment (1 selects the tcgen05 kernel wherever it applies, 0 never), else aum_default.

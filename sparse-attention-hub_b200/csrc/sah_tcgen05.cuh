@@ -132,7 +132,8 @@ __device__ __forceinline__ uint64_t aum_now_ns() {
 // phase completes -- a spinning warp takes issue slots and shared-memory bandwidth from the
 // warps that compute); 0: test again at once (waits on the per-tile critical path).
 __device__ __forceinline__ bool aum_wait(uint32_t bar, uint32_t parity, volatile int* abort_sm,
-                                         int* __restrict__ errflag, unsigned backoff_ns = 0) {
+                                         int* __restrict__ errflag, unsigned backoff_ns = 0,
+                                         unsigned long long limit_ns = 1000000000ull) {
   if (aum_try(bar, parity)) return true;
   const uint64_t t0 = aum_now_ns();
   for (int round = 0; round < (1 << 24); ++round) {
@@ -142,7 +143,7 @@ __device__ __forceinline__ bool aum_wait(uint32_t bar, uint32_t parity, volatile
       if (aum_try(bar, parity)) return true;
     }
     if (*abort_sm) return false;
-    if (aum_now_ns() - t0 > 1000000000ull) break;
+    if (aum_now_ns() - t0 > limit_ns) break;
   }
   *abort_sm = 1;
   atomicExch(errflag, 1);
@@ -154,7 +155,8 @@ __device__ __forceinline__ bool aum_wait(uint32_t bar, uint32_t parity, volatile
 // the outcome handed round by a shuffle, and sleeping between polls, both measured slower in
 // the attention kernel: the waits sit on the per-tile critical path.)
 __device__ __forceinline__ bool aum_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_sm,
-                                              int* __restrict__ errflag, unsigned backoff_ns = 0) {
-  const bool ok = aum_wait(bar, parity, abort_sm, errflag, backoff_ns);
+                                              int* __restrict__ errflag, unsigned backoff_ns = 0,
+                                              unsigned long long limit_ns = 1000000000ull) {
+  const bool ok = aum_wait(bar, parity, abort_sm, errflag, backoff_ns, limit_ns);
   return __all_sync(0xffffffffu, ok);
 }

@@ -100,6 +100,7 @@ _SIGNATURES = {
     "sah_mask_flat_add": [_P, _P, _I, _L, _L, _P, _P],
     "sah_mask_clamp_to_dense": [_P, _I, _L, _P, _P],
     "sah_attn_select_kernel": [_I],
+    "sah_wait_selftest": [_I, _P, _P, _P],
     "sah_attn_exchange_bytes": [_I, _I, _I, _I, _I],  # returns int64
     "sah_attn_exchange_merge": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P, _P, _P],
     "sah_attn_gather_probe": [_P, _P, _L, _L, _L, _L, _L, _L, _I, _I, _I, _L, _I, POINTER(AttnSizes),

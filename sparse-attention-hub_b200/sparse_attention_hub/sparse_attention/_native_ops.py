@@ -460,6 +460,23 @@ def wait_errors() -> int:
 _LSH_TABLES: dict = {}
 
 
+def lsh_weight_table(device: torch.device, lsh_k: int, lsh_l: int) -> torch.Tensor:
+    """uint16[65536]: bf16 bits of a cosine -> bf16 bits of the sampling weight 1 / (p + 1e-6) of
+    its collision probability p (`lsh_prob_table`), rounded as Mask.apply_inv_mask_dense rounds it
+    in bfloat16 (utils/mask.py:718-740: the sum to bf16, the reciprocal to bf16); 0 where p is 0
+    (a zero in the reference's dense mask means "not selected")."""
+    key = (str(device), lsh_k, lsh_l, "weight")
+    if key not in _LSH_TABLES:
+        pbits = lsh_prob_table(torch.device("cpu"), lsh_k, lsh_l).numpy().view(np.uint16).astype(np.uint32)
+        p = (pbits << 16).view(np.float32)
+        with np.errstate(invalid="ignore", over="ignore", divide="ignore"):
+            s = _bf16_bits_to_f64(_f64_to_bf16_bits((p + np.float32(1e-6)).astype(np.float64))).astype(np.float32)
+            w = _f64_to_bf16_bits((np.float32(1.0) / s).astype(np.float64))
+        w = np.where(p == 0.0, np.uint16(0), w.astype(np.uint16)).astype(np.uint16)
+        _LSH_TABLES[key] = torch.from_numpy(w.view(np.int16).copy()).to(device)
+    return _LSH_TABLES[key]
+
+
 def lsh_prob_table(device: torch.device, lsh_k: int, lsh_l: int) -> torch.Tensor:
     """uint16[65536]: bf16 bits of a cosine -> bf16 bits of the collision probability
     1 - (1 - (1 - acos(c)/pi)^K)^L with every operation rounded to bf16 as a bf16 tensor

@@ -158,11 +158,12 @@ class DeferredLSHWeights:
                  unit_bits: Optional[torch.Tensor], qhat: torch.Tensor, qmu: torch.Tensor,
                  qunit: torch.Tensor, sig: PackedLSHSignatures, table: torch.Tensor,
                  keys: torch.Tensor, mean: Optional[torch.Tensor], shape: Tuple[int, int, int, int],
-                 G: int) -> None:
+                 G: int, weight_table: Optional[torch.Tensor] = None) -> None:
         self.masker, self.previous_mask = masker, previous_mask
         self.match_bits, self.unit_bits = match_bits, unit_bits
         self.qhat, self.qmu, self.qunit = qhat, qmu, qunit
         self.sig, self.table, self.keys, self.mean = sig, table, keys, mean
+        self.weight_table = weight_table  # cosine -> 1 / (p + 1e-6), what the attention kernel reads
         self.shape, self.G = shape, G
         self.device = match_bits.device
 
@@ -390,7 +391,8 @@ class MagicPig(SamplingMasker):
         if fused:
             payload = DeferredLSHWeights(self, previous_mask, bits,
                                          None if prev_nb is None else prev_nb.bits, qhat, qmu, qunit,
-                                         sig, table, k, mean, shape, G)
+                                         sig, table, k, mean, shape, G,
+                                         _native_ops.lsh_weight_table(dev, self.lsh_k, self.lsh_l))
             return Mask._from_native(shape, previous_mask.dtype,
                                      NativeBits(None, rows, S, deferred=payload))
         nb = NativeBits(bits, rows, S)

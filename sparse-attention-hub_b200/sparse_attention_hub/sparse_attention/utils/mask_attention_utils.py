@@ -169,7 +169,7 @@ def native_masked_attention(
                     float(scaling), bias_ptr, bsb, bsh, bsq, _native.ptr(sink_t), ctypes.byref(sizes),
                     ws["ucols"].data_ptr(), ws["umemb"].data_ptr(), ws["uw"].data_ptr(),
                     ws["ucount"].data_ptr(), ws["partial"].data_ptr(), payload.qhat.data_ptr(),
-                    payload.qmu.data_ptr(), payload.table.data_ptr(), out.data_ptr(),
+                    payload.qmu.data_ptr(), payload.weight_table.data_ptr(), out.data_ptr(),
                     _native.ptr(part), _native.ptr(dump), st),
                 "sah_masked_attention_lsh")
         else:

@@ -100,3 +100,29 @@ def test_magicpig_weights_inside_the_kernel(kernel, S):
     _, ref, _ = stacks.run_stack(wl.stack, wl.q, wl.k, wl.v, wl.scaling, "bf16",
                                  meta={"lsh_projection": wl.stack[-1][1]["projection"]})
     np.testing.assert_allclose(out.float().cpu().numpy(), ref, atol=TOL, rtol=TOL)
+
+
+def test_bounded_wait_runs_out_and_reports_without_hanging():
+    """Every mbarrier wait of the tcgen05 kernels is bounded.  `sah_wait_selftest` waits 2 ms for an
+    arrival that never comes: the error word is set, the measured wait is about the limit, the
+    kernel returns, and the next attention call on the same context works."""
+    from sparse_attention_hub import _native
+
+    lib = _native.load()
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    waited = torch.zeros(1, dtype=torch.int64, device=DEV)
+    _native.check(lib.sah_wait_selftest(2000, err.data_ptr(), waited.data_ptr(),
+                                        _native.stream_of(torch.device(DEV))), "sah_wait_selftest")
+    torch.cuda.synchronize()
+    assert int(err.item()) != 0
+    assert 2_000_000 <= int(waited.item()) < 50_000_000
+    prev = select_attention_kernel("umma")
+    try:
+        wl, q, k, v, dense = _dense_mask_case(77, 1, 8, 2, 2000, 128, 0.3, False)
+        tq, tk, tv = (workloads.to_torch(a, "bf16", DEV) for a in (q, k, v))
+        m = Mask.create_mask_from_dense_mask(dense.shape, workloads.to_torch(dense, "bf16", DEV), torch.bfloat16)
+        out = native_masked_attention(tq, tk, tv, None, None, float(wl.scaling), m)
+        ref = o_attention.masked_attention(q, k, v, dense, wl.scaling, "bf16")
+        np.testing.assert_allclose(out.float().cpu().numpy(), ref, atol=TOL, rtol=TOL)
+    finally:
+        select_attention_kernel(prev)
