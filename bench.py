@@ -739,6 +739,8 @@ def run_long_native(args) -> None:
 
     S_full, S_small = LONG_WORKLOADS[args.workload]
     S = S_small if args.small else S_full
+    if args.keys:
+        S = int(args.keys)
     B, Hq, Hkv, D = 1, 32, 8, 128
     begin, end = plan_shards(S, world)[rank]
     n_local = end - begin
@@ -977,7 +979,7 @@ def run_long_native(args) -> None:
         base = None
         if world == 1 and not args.no_cpu_baseline:
             base = cpu_baseline_subprocess(args)
-        ratio = None if args.small else NCU_TRAFFIC_PER_ALGORITHMIC_BYTE.get(f"{args.workload}:{dom}")
+        ratio = None if (args.small or args.keys) else NCU_TRAFFIC_PER_ALGORITHMIC_BYTE.get(f"{args.workload}:{dom}")
         line = {
             "metric": METRIC, "value": B / (ms_per_pass * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_pass,
@@ -1049,6 +1051,8 @@ def main() -> None:
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--small", action="store_true", help="reduced sizes (development only)")
+    ap.add_argument("--keys", type=int, default=0,
+                    help="sequence length of the sequence-sharded workloads (development only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="launch every step eagerly (no CUDA graph)")
     ap.add_argument("--budget", type=float, default=150.0,

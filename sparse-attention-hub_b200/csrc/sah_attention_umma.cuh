@@ -579,12 +579,13 @@ masked_attention_umma_kernel(AttnArgs a, int* __restrict__ tickets, int* __restr
 }
 
 // Which problems take the tcgen05 kernel when neither the caller nor the environment says.
-// Measured on B200 (attention kernel, tcgen05 against mma.sync): MagicPig weights in place at a
-// million keys (8 KV groups, ~770 000 rows each) 735 against 831 us; 64 KV groups with lists
-// of a few thousand rows (HashAttention and Quest at B = 8, S = 32768) 64 against 69 us and
-// 56 against 61 us.  In between -- 8 to 32 groups with lists of 10^4..10^5 rows -- the
-// mma.sync kernel, with two CTAs per SM and lower fixed costs, is ahead by 5-40 %.
-#define AUM_DEFAULT_MIN_KEYS (512 * 1024)
+// Measured on B200 (attention kernel, tcgen05 against mma.sync).  MagicPig weights in place,
+// 8 KV groups: 1M keys (~770 000 rows per group) 637 us; 512K keys 335 against 366 us; 256K
+// keys 183 against 189 us; 128K keys 111 against 108 us.  64 KV groups with lists of a few
+// thousand rows (HashAttention and Quest at B = 8, S = 32768): 63 against 69 us and 56 against
+// 61 us.  In between -- 8 to 32 groups with lists of 10^4..10^5 rows -- the mma.sync kernel,
+// with two CTAs per SM and lower fixed costs, is ahead by 5-40 %.
+#define AUM_DEFAULT_MIN_KEYS (256 * 1024)
 static bool aum_default(bool lsh, int64_t S, int groups) {
   return (lsh && S >= AUM_DEFAULT_MIN_KEYS) || (groups >= 64 && S <= 65536);
 }
