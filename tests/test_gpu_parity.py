@@ -426,3 +426,34 @@ def test_gpu_mask_interop_from_rows_and_sparse_merge(dtype):
     oi, op, od = mask_ops.merge_sparse(g["a"], g["b"], dtype)
     np.testing.assert_array_equal(mi.cpu().numpy(), oi)
     np.testing.assert_array_equal(md.float().cpu().numpy(), od)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("hidden,layers,bits,act", [(128, 3, 32, "silu"), (64, 2, 16, "relu"), (32, 3, 32, "gelu")])
+def test_hash_signatures_from_tensor_cores_equal_the_fixed_order_kernel(hidden, layers, bits, act,
+                                                                        monkeypatch):
+    """On request (SAH_HASH_TC=1) ranges of 1024 keys and more are hashed with the layers'
+    products on the tensor cores and every output near a bfloat16 rounding midpoint redone in the
+    fixed order; shorter ranges take the fixed-order kernel.  Hashing 6000 keys in one call and in
+    slices of 1000 must give the same words -- and those are the restatement's codes."""
+    monkeypatch.setenv("SAH_HASH_TC", "1")
+    S, B, Hkv, Hq, D = 6000, 2, 2, 4, 128
+    w = workloads.hat_weights(31 + hidden, Hq, D, hidden, bits, layers)
+    rng = np.random.default_rng(3)
+    w["key_bias"] = [(rng.standard_normal(b.shape) * 0.1).astype(np.float32) for b in w["key_bias"]]
+    k = workloads.to_dtype((rng.standard_normal((B, Hkv, S, D)) * 0.8).astype(np.float32), "bf16")
+    tk = workloads.to_torch(k, "bf16", DEV)
+    weights = [workloads.to_torch(a, "bf16", DEV).contiguous() for a in w["key_matrix"]]
+    biases = [workloads.to_torch(a, "bf16", DEV).contiguous() for a in w["key_bias"]]
+    whole = torch.zeros((B, Hq, S), dtype=torch.int32, device=DEV)
+    sliced = torch.zeros_like(whole)
+    _native_ops.hash_encode(tk, Hq, weights, biases, act, whole, 0, S)
+    for s0 in range(0, S, 1000):
+        _native_ops.hash_encode(tk, Hq, weights, biases, act, sliced, s0, min(S, s0 + 1000))
+    torch.cuda.synchronize()
+    assert torch.equal(whole, sliced)
+    n = 256
+    mats = [workloads.to_dtype(a, "bf16") for a in w["key_matrix"]]
+    bias = [workloads.to_dtype(a, "bf16") for a in w["key_bias"]]
+    ref = o_hash.signatures(o_attention.repeat_kv(k[:, :, :n], Hq // Hkv), mats, bias, act, "bf16")
+    np.testing.assert_array_equal(whole[:, :, :n].cpu().numpy().view(np.uint32), ref)
