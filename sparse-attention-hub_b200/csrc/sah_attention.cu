@@ -103,6 +103,7 @@ __device__ __forceinline__ int64_t plan_member_row(const PlanGeom& p, int64_t g,
 __global__ void attn_plan_count_kernel(const uint32_t* __restrict__ bits,
                                        const uint32_t* __restrict__ ubits, PlanGeom p,
                                        int32_t* __restrict__ chunkcnt) {
+  sah_pdl_entry_early();
   const int lane = threadIdx.x & 31;
   const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int64_t g = wid / p.nchunks, c = wid - g * p.nchunks;
@@ -137,6 +138,7 @@ attn_plan_fused_kernel(const uint32_t* __restrict__ bits, const T* __restrict__ 
                        const int32_t* __restrict__ wpre, const int64_t* __restrict__ ptr,
                        PlanGeom p, int32_t* __restrict__ ucols, uint16_t* __restrict__ umemb,
                        float* __restrict__ uw, int32_t* __restrict__ ucount) {
+  sah_pdl_entry_early();
   __shared__ int scan[33];
   __shared__ int64_t rows_sm[RMAX];
   const int64_t g = blockIdx.x;
@@ -225,6 +227,7 @@ attn_plan_emit_kernel(const uint32_t* __restrict__ bits, const uint32_t* __restr
                       const int32_t* __restrict__ chunkcnt, int32_t* __restrict__ ucols,
                       uint16_t* __restrict__ umemb, float* __restrict__ uw,
                       int32_t* __restrict__ ucount) {
+  sah_pdl_entry();
   __shared__ uint32_t words_sm[PLAN_EMIT_WARPS][RMAX][32];
   __shared__ uint32_t units_sm[PLAN_EMIT_WARPS][LSH ? RMAX : 1][32];
   __shared__ int64_t dbase_sm[PLAN_EMIT_WARPS][RMAX][32];
@@ -371,27 +374,23 @@ extern "C" int sah_attn_plan(const uint32_t* bits, const void* data, const int32
     const dim3 fgrid((unsigned)groups, (unsigned)sah_ceil_div(p.Wv, PLAN_FUSED_THREADS));
     SAH_DISPATCH_DTYPE(dtype, T, {
       if (p.R <= 4)
-        attn_plan_fused_kernel<T, 4><<<fgrid, PLAN_FUSED_THREADS, 0, st>>>(
-            bits, (const T*)data, wpre, ptr, p, ucols, umemb, data ? uw : nullptr, ucount);
+        sah_launch_chain(attn_plan_fused_kernel<T, 4>, fgrid, PLAN_FUSED_THREADS, 0, st, bits, (const T*)data, wpre, ptr, p, ucols, umemb, data ? uw : nullptr, ucount);
       else
-        attn_plan_fused_kernel<T, AT_MAXR><<<fgrid, PLAN_FUSED_THREADS, 0, st>>>(
-            bits, (const T*)data, wpre, ptr, p, ucols, umemb, data ? uw : nullptr, ucount);
+        sah_launch_chain(attn_plan_fused_kernel<T, AT_MAXR>, fgrid, PLAN_FUSED_THREADS, 0, st, bits, (const T*)data, wpre, ptr, p, ucols, umemb, data ? uw : nullptr, ucount);
     });
     SAH_LAUNCH_CHECK("attn_plan_fused");
     sah_prof_end(SAH_PROF_ATTN_PLAN, (cudaStream_t)stream);
     return SAH_OK;
   }
-  attn_plan_count_kernel<<<(unsigned)blocks, threads, 0, st>>>(bits, nullptr, p, chunkcnt);
+  sah_launch_chain(attn_plan_count_kernel, (unsigned)blocks, threads, 0, st, bits, nullptr, p, chunkcnt);
   SAH_LAUNCH_CHECK("attn_plan_count");
   const int64_t eblocks = sah_ceil_div(warps, PLAN_EMIT_WARPS);
   SAH_DISPATCH_DTYPE(dtype, T, {
     if (p.R <= 4)
-      attn_plan_emit_kernel<T, 4, false><<<(unsigned)eblocks, PLAN_EMIT_WARPS * 32, 0, st>>>(
-          bits, nullptr, (const T*)data, wpre, ptr, nullptr, 0, nullptr, p, chunkcnt, ucols, umemb,
+      sah_launch_chain(attn_plan_emit_kernel<T, 4, false>, (unsigned)eblocks, PLAN_EMIT_WARPS * 32, 0, st, bits, nullptr, (const T*)data, wpre, ptr, nullptr, 0, nullptr, p, chunkcnt, ucols, umemb,
           data ? uw : nullptr, ucount);
     else
-      attn_plan_emit_kernel<T, AT_MAXR, false><<<(unsigned)eblocks, PLAN_EMIT_WARPS * 32, 0, st>>>(
-          bits, nullptr, (const T*)data, wpre, ptr, nullptr, 0, nullptr, p, chunkcnt, ucols, umemb,
+      sah_launch_chain(attn_plan_emit_kernel<T, AT_MAXR, false>, (unsigned)eblocks, PLAN_EMIT_WARPS * 32, 0, st, bits, nullptr, (const T*)data, wpre, ptr, nullptr, 0, nullptr, p, chunkcnt, ucols, umemb,
           data ? uw : nullptr, ucount);
   });
   SAH_LAUNCH_CHECK("attn_plan_emit");
@@ -420,11 +419,10 @@ extern "C" int sah_attn_plan_lsh(const uint32_t* bits, const uint32_t* unit_bits
   const int64_t blocks = sah_ceil_div(warps * 32, threads);
   cudaStream_t st = (cudaStream_t)stream;
   sah_prof_begin(SAH_PROF_ATTN_PLAN, st);
-  attn_plan_count_kernel<<<(unsigned)blocks, threads, 0, st>>>(bits, unit_bits, p, chunkcnt);
+  sah_launch_chain(attn_plan_count_kernel, (unsigned)blocks, threads, 0, st, bits, unit_bits, p, chunkcnt);
   SAH_LAUNCH_CHECK("attn_plan_count");
-  attn_plan_emit_kernel<float, 4, true><<<(unsigned)sah_ceil_div(warps, PLAN_EMIT_WARPS),
-                                          PLAN_EMIT_WARPS * 32, 0, st>>>(
-      bits, unit_bits, nullptr, nullptr, nullptr, dens, dens_cap, max_norm_bits, p, chunkcnt, ucols,
+  sah_launch_chain(attn_plan_emit_kernel<float, 4, true>, (unsigned)sah_ceil_div(warps, PLAN_EMIT_WARPS),
+                                          PLAN_EMIT_WARPS * 32, 0, st, bits, unit_bits, nullptr, nullptr, nullptr, dens, dens_cap, max_norm_bits, p, chunkcnt, ucols,
       umemb, uinv, ucount);
   SAH_LAUNCH_CHECK("attn_plan_emit_lsh");
   sah_prof_end(SAH_PROF_ATTN_PLAN, st);
@@ -465,6 +463,7 @@ struct AttnArgs {
   // TMA copy stage: K and V as 2-D [rows][D] tensors, row = b * rows_b + h * rows_h + key
   int64_t k_rows_b, k_rows_h, v_rows_b, v_rows_h;
   int k_rows_total, v_rows_total;
+  int one_wave_tiles;  // tcgen05 kernel: tiles per CTA below which only half of the grid works
 };
 
 // Shared-memory rows are stored in 16-byte chunks; chunk c of tile row i sits
@@ -491,6 +490,7 @@ static const char* g_last_attn_kernel = "none";
 template <typename T, int D, int NQUAD>
 __global__ void __launch_bounds__(AT_THREADS)
 masked_attention_kernel(AttnArgs a) {
+  sah_pdl_entry();
   using C = AttnCfg<T, D>;
   constexpr int RP = NQUAD * 4;  // padded row count
   extern __shared__ __align__(128) unsigned char at_smem[];
@@ -779,6 +779,7 @@ __global__ void attn_merge_splits_kernel(const float* __restrict__ partial, int 
                                          int D, int Hq, int Hkv, int Sq, int G, int q_block,
                                          int nqb, const float* __restrict__ sinks,
                                          T* __restrict__ out, float* __restrict__ part_out) {
+  sah_pdl_entry_early();
   const int64_t g = blockIdx.x / R;
   const int r = (int)(blockIdx.x % R);
   const int qb = (int)(g % nqb);
@@ -840,7 +841,7 @@ static int launch_attention(const AttnArgs& a, int groups, cudaStream_t st) {
     cudaError_t e = cudaFuncSetAttribute(masked_attention_kernel<T, D, NQ>,                      \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "attention attr: %s", cudaGetErrorString(e)); \
-    masked_attention_kernel<T, D, NQ><<<grid, AT_THREADS, smem, st>>>(a);                         \
+    sah_launch_chain(masked_attention_kernel<T, D, NQ>, grid, AT_THREADS, smem, st, a);                         \
   }
   switch (nquad) {
     case 1: SAH_AT_LAUNCH(1) break;
@@ -899,6 +900,7 @@ static int masked_attention_impl(const void* q, const void* k, const void* v, in
   a.w_dump = lsh ? lsh->w_dump : nullptr;
   a.k_rows_b = a.k_rows_h = a.v_rows_b = a.v_rows_h = 0;
   a.k_rows_total = a.v_rows_total = 0;
+  a.one_wave_tiles = 0;
   const int groups = sizes->groups;
   SAH_REQUIRE((int64_t)groups == (int64_t)B * Hkv * a.nqb && a.R == a.G * a.q_block &&
                   a.R <= AT_MAXR && a.nsplit >= 1,
@@ -943,8 +945,7 @@ static int masked_attention_impl(const void* q, const void* k, const void* v, in
   SAH_LAUNCH_CHECK("masked_attention");
   sah_prof_end(SAH_PROF_ATTENTION, (cudaStream_t)stream);
   sah_prof_begin(SAH_PROF_ATTN_MERGE, (cudaStream_t)stream);
-  attn_merge_splits_kernel<float><<<(unsigned)(groups * a.R), D, 0, st>>>(
-      partial, a.nsplit, a.R, D, Hq, Hkv, Sq, a.G, a.q_block, a.nqb, sinks, (float*)out, part_out);
+  sah_launch_chain(attn_merge_splits_kernel<float>, (unsigned)(groups * a.R), D, 0, st, partial, a.nsplit, a.R, D, Hq, Hkv, Sq, a.G, a.q_block, a.nqb, sinks, (float*)out, part_out);
   SAH_LAUNCH_CHECK("attn_merge_splits");
   sah_prof_end(SAH_PROF_ATTN_MERGE, (cudaStream_t)stream);
   return SAH_OK;
@@ -1083,6 +1084,7 @@ template <typename T>
 __global__ void attn_merge_parts_kernel(const float* __restrict__ parts, int n_parts, int64_t rows,
                                         int Hq, int Sq, int D, const float* __restrict__ sinks,
                                         T* __restrict__ out) {
+  sah_pdl_entry_early();
   const int64_t row = blockIdx.x;
   const int qi = (int)(row % Sq);
   const int64_t bh = row / Sq;
@@ -1122,8 +1124,7 @@ extern "C" int sah_attn_merge_parts(const float* parts, int n_parts, int B, int 
   const int64_t rows = (int64_t)B * Hq * Sq;
   int threads = D < 32 ? 32 : (D > 256 ? 256 : D);
   SAH_DISPATCH_DTYPE(dtype, T, {
-    attn_merge_parts_kernel<T><<<(unsigned)rows, threads, 0, (cudaStream_t)stream>>>(
-        parts, n_parts, rows, Hq, Sq, D, sinks, (T*)out);
+    sah_launch_chain(attn_merge_parts_kernel<T>, (unsigned)rows, threads, 0, (cudaStream_t)stream, parts, n_parts, rows, Hq, Sq, D, sinks, (T*)out);
   });
   SAH_LAUNCH_CHECK("attn_merge_parts");
   return SAH_OK;

@@ -253,6 +253,7 @@ __global__ void __launch_bounds__(ATM_THREADS, NST == 2 ? 3 : 2)
 masked_attention_mma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, int* __restrict__ tickets,
                             int* __restrict__ errflag, const float* __restrict__ sinks,
                             __nv_bfloat16* __restrict__ out, float* __restrict__ part_out) {
+  sah_pdl_entry();
   static_assert(!LSHW || HALF, "in-place MagicPig weights use the spare rows of the half tile");
   using C = AtmCfg<D, TMA, NST>;
   static_assert(C::Q_BYTES <= C::WARP_BYTES, "the Q tile is staged in the first ring");
@@ -875,7 +876,7 @@ static int launch_attention_mma(AttnArgs a, int B, int groups, int* tickets, int
       return sah_fail(SAH_ERR_UNSUPPORTED, "attention: %d splits do not fit the merge scratch", a.nsplit); \
     e = atm_allow_smem(masked_attention_mma_kernel<D, HALF, LSHW, TMA, NST>, smem, allowed[SLOT]);  \
     if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "attention attr: %s", cudaGetErrorString(e)); \
-    masked_attention_mma_kernel<D, HALF, LSHW, TMA, NST><<<grid, ATM_THREADS, smem, st>>>(          \
+    sah_launch_chain(masked_attention_mma_kernel<D, HALF, LSHW, TMA, NST>, grid, ATM_THREADS, smem, st, \
         a, maps, tickets, errflag, sinks, (__nv_bfloat16*)out, part_out);                           \
   } while (0)
   if (lsh) {

@@ -47,7 +47,7 @@
 #define AUM_TMEM_COLS 64
 #define AUM_RESCALE_T 8.0f
 #define AUM_MIN_TILES 2        // tiles a CTA should have before a further CTA joins the group
-#define AUM_ONE_WAVE_TILES 16  // below this many tiles per CTA, one wave of CTAs instead of two
+#define AUM_ONE_WAVE_TILES 128  // below this many tiles per CTA, one wave of CTAs instead of two
 
 struct AumCfg {
   static constexpr int KV_TILE = AUM_TILE * 256;  // one K (or V) tile: two halves of [128 rows][128 B]
@@ -71,9 +71,10 @@ struct AumCfg {
   static constexpr int SMEM = 1024 + END;
 };
 
-__device__ __forceinline__ int aum_active_splits(int total_tiles, int nsplit) {
+__device__ __forceinline__ int aum_active_splits(int total_tiles, int nsplit, int one_wave_tiles) {
   int active = nsplit;
-  if (nsplit >= 2 && total_tiles < nsplit * AUM_ONE_WAVE_TILES) active = (nsplit + 1) / 2;
+  // the grid holds two CTAs per SM; half of it, rounded down, is at most one per SM
+  if (nsplit >= 2 && total_tiles < nsplit * one_wave_tiles) active = nsplit / 2;
   const int by_length = (total_tiles + AUM_MIN_TILES - 1) / AUM_MIN_TILES;
   if (by_length < active) active = by_length;
   return active < 1 ? 1 : active;
@@ -118,6 +119,7 @@ __global__ void __launch_bounds__(AUM_THREADS, 1)
 masked_attention_umma_kernel(AttnArgs a, int* __restrict__ tickets, int* __restrict__ errflag,
                              const float* __restrict__ sinks, __nv_bfloat16* __restrict__ out,
                              float* __restrict__ part_out) {
+  sah_pdl_entry();
   static_assert(!LSHW || RMAX == 4, "in-place MagicPig weights: at most 4 mask rows");
   constexpr int D = 128;
   using C = AumCfg;
@@ -140,7 +142,7 @@ masked_attention_umma_kernel(AttnArgs a, int* __restrict__ tickets, int* __restr
 
   const int U = a.ucount[g];
   const int total_tiles = (U + AUM_TILE - 1) / AUM_TILE;
-  const int active = aum_active_splits(total_tiles, (int)gridDim.x);
+  const int active = aum_active_splits(total_tiles, (int)gridDim.x, a.one_wave_tiles);
   if (split >= active) return;  // before any barrier or tensor memory exists
   const int my_tiles = (total_tiles > split) ? (total_tiles - split + active - 1) / active : 0;
 
@@ -580,12 +582,14 @@ masked_attention_umma_kernel(AttnArgs a, int* __restrict__ tickets, int* __restr
 
 // Which problems take the tcgen05 kernel when neither the caller nor the environment says.
 // Measured on B200 (attention kernel, tcgen05 against mma.sync).  MagicPig weights in place,
-// 8 KV groups: 1M keys (~770 000 rows per group) 637 us; 512K keys 335 against 366 us; 256K
-// keys 183 against 189 us; 128K keys 111 against 108 us.  64 KV groups with lists of a few
+// 8 KV groups: 1M keys (~770 000 rows per group, two waves of CTAs) 639 us; with one wave of
+// CTAs (AUM_ONE_WAVE_TILES) 512K keys 332 against 366 us; 256K keys 177 against 189 us; 128K
+// keys 99 against 108 us; 64K keys 63 against 73 us (two waves from 512K down: 337, 185 and
+// 111 us -- a CTA's prologue, pipeline fill and merge are paid once per SM instead of twice).  64 KV groups with lists of a few
 // thousand rows (HashAttention and Quest at B = 8, S = 32768): 63 against 69 us and 56 against
 // 61 us.  In between -- 8 to 32 groups with lists of 10^4..10^5 rows -- the mma.sync kernel,
-// with two CTAs per SM and lower fixed costs, is ahead by 5-40 %.
-#define AUM_DEFAULT_MIN_KEYS (256 * 1024)
+// with two CTAs per SM and lower fixed costs, was ahead by 5-40 % (measured with two waves).
+#define AUM_DEFAULT_MIN_KEYS (64 * 1024)
 static bool aum_default(bool lsh, int64_t S, int groups) {
   return (lsh && S >= AUM_DEFAULT_MIN_KEYS) || (groups >= 64 && S <= 65536);
 }
@@ -631,12 +635,18 @@ static int launch_attention_umma(AttnArgs a, int B, int groups, int* tickets, in
   if ((size_t)16 * nsplit * 4 + 128 > (size_t)AumCfg::Q_OFF)
     return sah_fail(SAH_ERR_UNSUPPORTED, "attention: %d splits do not fit the merge scratch", (int)nsplit);
   dim3 grid((unsigned)nsplit, (unsigned)groups);
+  static int one_wave = -1;  // SAH_AUM_ONE_WAVE in the environment replaces AUM_ONE_WAVE_TILES
+  if (one_wave < 0) {
+    const char* ow = getenv("SAH_AUM_ONE_WAVE");
+    one_wave = (ow != nullptr && atoi(ow) >= 0) ? atoi(ow) : AUM_ONE_WAVE_TILES;
+  }
+  a.one_wave_tiles = one_wave;
   cudaError_t e = cudaSuccess;
 #define AUM_LAUNCH(LSHW, RMAX, SLOT)                                                                  \
   do {                                                                                                \
     e = atm_allow_smem(masked_attention_umma_kernel<LSHW, RMAX>, AumCfg::SMEM, allowed[SLOT]);        \
     if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "attention attr: %s", cudaGetErrorString(e)); \
-    masked_attention_umma_kernel<LSHW, RMAX><<<grid, AUM_THREADS, AumCfg::SMEM, st>>>(                \
+    sah_launch_chain(masked_attention_umma_kernel<LSHW, RMAX>, grid, AUM_THREADS, AumCfg::SMEM, st, \
         a, tickets, errflag, sinks, (__nv_bfloat16*)out, part_out);                             \
   } while (0)
   if (lsh) AUM_LAUNCH(true, 4, 0);

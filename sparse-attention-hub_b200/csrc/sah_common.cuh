@@ -7,6 +7,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <utility>
+
 #include "sah_b200.h"
 
 int sah_fail(int status, const char* fmt, ...);
@@ -172,3 +174,59 @@ void sah_count_launch();
     if (e__ != cudaSuccess)                                                        \
       return sah_fail(SAH_ERR_CUDA, "%s: %s", name, cudaGetErrorString(e__));      \
   } while (0)
+
+// ---- chained launches (programmatic dependent launch) -----------------------------
+// The kernels of a decode step follow one another in one stream, many of them a few
+// microseconds long, so the time between the end of one grid and the first instruction of the
+// next is part of the step.  A kernel that begins with sah_pdl_entry() or
+// sah_pdl_entry_early() may be launched with sah_launch_chain(): with SAH_PDL=1 in the
+// environment the launch carries the programmatic-stream-serialization attribute, the grid may
+// be scheduled before the kernel in front of it has finished, and its threads wait, in
+// hardware, until the kernels in front have completed and their writes are visible.  Nothing of
+// global memory is touched before that wait, so the results are those of ordinary stream
+// order; what overlaps is the launch itself.
+//   sah_pdl_entry_early(): short kernels.  Also tells the hardware that the kernels behind
+//     this one may be scheduled as soon as all its CTAs have started.
+//   sah_pdl_entry(): long kernels (scans of all keys, attention).  Their successors are
+//     scheduled when they end.
+// Every kernel of a chain has to execute the wait (a grid that skipped it could complete, and
+// release its own successors, before its predecessor has), which is why the attribute is only
+// ever set by sah_launch_chain() and tests/test_c_abi.py checks that every kernel launched
+// through it starts with one of the two.  Without the attribute the instructions do nothing.
+//
+// Measured on B200 (decode step as a CUDA graph, us, chained against plain): Sink+Local 23.1
+// / 24.8, HashAttention 94.1 / 96.0, PQCache 95.5 / 97.6, Quest 96.7 / 95.9, oracle top-k
+// 211.5 / 209.7, MagicPig at 131072 keys 164.1 / 156.8, oracle top-k + adaptive 345.5 / 346
+// (with grids of up to 1024 warps chained; 362 with 4096; and 184 and 373 for the last two
+// when every kernel, long ones included, released its successors at its start).  A grid that
+// sits waiting beside its predecessor costs that kernel more than the hidden launch saves
+// whenever the waiting grid is large or the predecessor long, and the gain where there is one
+// is 2 us.  So chaining is off by default.
+__device__ __forceinline__ void sah_pdl_entry() {
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+}
+__device__ __forceinline__ void sah_pdl_entry_early() {
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+}
+
+// Grids of more warps than this are launched in plain stream order even with SAH_PDL=1
+// (SAH_PDL_MAX_WARPS replaces the 1024); 0 = no chaining at all, the default.
+int sah_pdl_max_warps();
+
+template <typename... KArgs, typename... Args>
+static inline void sah_launch_chain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  const long long warps = (long long)grid.x * grid.y * grid.z * ((block.x * block.y * block.z + 31) / 32);
+  cfg.numAttrs = warps <= (long long)sah_pdl_max_warps() ? 1 : 0;
+  (void)cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);  // the error stays for SAH_LAUNCH_CHECK
+}

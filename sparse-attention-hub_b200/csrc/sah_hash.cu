@@ -177,6 +177,7 @@ __device__ __forceinline__ void he_cp_async16(void* smem_dst, const void* gmem_s
 template <typename T>
 __global__ void __launch_bounds__(HE_MAXD)
 hash_encode_small_kernel(HashEncodeArgs p) {
+  sah_pdl_entry_early();
   extern __shared__ __align__(16) unsigned char hes_smem[];  // every layer's weights of head h
   __shared__ float xa[HE_MAXD];
   __shared__ float xb[HE_MAXD];
@@ -302,7 +303,7 @@ extern "C" int sah_hash_encode(const void* x, int dtype, int64_t xs_b, int64_t x
       }
       for (int l = 0; l < n_layers; ++l)
         SAH_REQUIRE(((uintptr_t)weights[l] % 16) == 0, "hash_encode: weights must be 16-byte aligned");
-      hash_encode_small_kernel<T><<<sgrid, HE_MAXD, wbytes, st>>>(p);
+      sah_launch_chain(hash_encode_small_kernel<T>, sgrid, HE_MAXD, wbytes, st, p);
     });
     SAH_LAUNCH_CHECK("hash_encode_small");
     sah_prof_end(SAH_PROF_HASH_ENCODE, st);
@@ -406,6 +407,7 @@ hash_topk_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
                  int64_t bias_s_q, int Hq, int Sq, int64_t S, int64_t W,
                  const uint32_t* __restrict__ prev_bits, int64_t k,
                  uint32_t* __restrict__ out_bits) {
+  sah_pdl_entry();
   __shared__ SahSelectSmem sm;
   const int64_t row = blockIdx.x;
   const int q = (int)(row % Sq);
@@ -457,6 +459,7 @@ hash_topk_fast_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
                       const uint32_t* __restrict__ qcodes, int nbits, int Sq, int64_t S, int64_t W,
                       const uint32_t* __restrict__ prev_bits, int64_t k,
                       uint32_t* __restrict__ out_bits) {
+  sah_pdl_entry();
   __shared__ unsigned int hist[32][HT_BINS];
   __shared__ long long scan[33];
   __shared__ int thr_sm;
@@ -767,6 +770,7 @@ hash_topk_reg_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
                      const uint32_t* __restrict__ qcodes, int nbits, int Sq, int64_t S, int64_t W,
                      const uint32_t* __restrict__ prev_bits, int64_t k,
                      uint32_t* __restrict__ out_bits) {
+  sah_pdl_entry();
   __shared__ __align__(16) unsigned char cnt[HT2_THREADS / 32][HT_CNT_BYTES];
   __shared__ unsigned int hist[HT_BINS];
   __shared__ int scan[33];
@@ -855,24 +859,22 @@ extern "C" int sah_hash_topk(const uint32_t* kcodes, int64_t kc_stride, const ui
   if (bias == nullptr) {
     const int64_t wpt = sah_ceil_div(W, HT2_THREADS);
     if (wpt <= 1)
-      hash_topk_reg_kernel<1><<<(unsigned)rows, HT2_THREADS, 0, st>>>(kcodes, kc_stride, qcodes, nbits, Sq,
+      sah_launch_chain(hash_topk_reg_kernel<1>, (unsigned)rows, HT2_THREADS, 0, st, kcodes, kc_stride, qcodes, nbits, Sq,
                                                                      S, W, prev_bits, k, out_bits);
     else if (wpt <= 2)
-      hash_topk_reg_kernel<2><<<(unsigned)rows, HT2_THREADS, 0, st>>>(kcodes, kc_stride, qcodes, nbits, Sq,
+      sah_launch_chain(hash_topk_reg_kernel<2>, (unsigned)rows, HT2_THREADS, 0, st, kcodes, kc_stride, qcodes, nbits, Sq,
                                                                      S, W, prev_bits, k, out_bits);
     else if (wpt <= 4)
-      hash_topk_reg_kernel<4><<<(unsigned)rows, HT2_THREADS, 0, st>>>(kcodes, kc_stride, qcodes, nbits, Sq,
+      sah_launch_chain(hash_topk_reg_kernel<4>, (unsigned)rows, HT2_THREADS, 0, st, kcodes, kc_stride, qcodes, nbits, Sq,
                                                                      S, W, prev_bits, k, out_bits);
     else
-      hash_topk_fast_kernel<<<(unsigned)rows, 1024, 0, st>>>(kcodes, kc_stride, qcodes, nbits, Sq, S,
+      sah_launch_chain(hash_topk_fast_kernel, (unsigned)rows, 1024, 0, st, kcodes, kc_stride, qcodes, nbits, Sq, S,
                                                             W, prev_bits, k, out_bits);
   } else if (dtype == SAH_BF16) {
-    hash_topk_kernel<__nv_bfloat16, 16, true><<<(unsigned)rows, SAH_SELECT_THREADS, 0, st>>>(
-        kcodes, kc_stride, qcodes, nbits, (const __nv_bfloat16*)bias, bias_s_b, bias_s_h, bias_s_q, Hq, Sq,
+    sah_launch_chain(hash_topk_kernel<__nv_bfloat16, 16, true>, (unsigned)rows, SAH_SELECT_THREADS, 0, st, kcodes, kc_stride, qcodes, nbits, (const __nv_bfloat16*)bias, bias_s_b, bias_s_h, bias_s_q, Hq, Sq,
         S, W, prev_bits, k, out_bits);
   } else if (dtype == SAH_F32) {
-    hash_topk_kernel<float, 32, true><<<(unsigned)rows, SAH_SELECT_THREADS, 0, st>>>(
-        kcodes, kc_stride, qcodes, nbits, (const float*)bias, bias_s_b, bias_s_h, bias_s_q, Hq, Sq, S, W,
+    sah_launch_chain(hash_topk_kernel<float, 32, true>, (unsigned)rows, SAH_SELECT_THREADS, 0, st, kcodes, kc_stride, qcodes, nbits, (const float*)bias, bias_s_b, bias_s_h, bias_s_q, Hq, Sq, S, W,
         prev_bits, k, out_bits);
   } else {
     return sah_fail(SAH_ERR_INVALID, "hash_topk: unknown dtype %d", dtype);
@@ -916,6 +918,7 @@ hash_hist_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
                  const uint32_t* __restrict__ qcodes, int nbits, int Sq, int64_t S, int64_t W,
                  int64_t chunk_words, const uint32_t* __restrict__ prev_bits, int64_t rows,
                  int32_t* __restrict__ hist_out, uint4* __restrict__ scores_out) {
+  sah_pdl_entry();
   __shared__ __align__(16) unsigned char cnt[HP_THREADS / 32][HT_CNT_BYTES];
   __shared__ unsigned int hist[HT_BINS];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -964,7 +967,7 @@ extern "C" int sah_hash_hist(const uint32_t* kcodes, int64_t kc_stride, const ui
   const int64_t rows = (int64_t)B * Hq * Sq;
   const int64_t chunk_words = hash_chunk_words(W, chunks);
   dim3 grid((unsigned)rows, (unsigned)chunks);
-  hash_hist_kernel<<<grid, HP_THREADS, 0, (cudaStream_t)stream>>>(kcodes, kc_stride, qcodes, nbits, Sq, S, W,
+  sah_launch_chain(hash_hist_kernel, grid, HP_THREADS, 0, (cudaStream_t)stream, kcodes, kc_stride, qcodes, nbits, Sq, S, W,
                                                                 chunk_words, prev_bits, rows, hist,
                                                                 reinterpret_cast<uint4*>(scores));
   SAH_LAUNCH_CHECK("hash_hist");
@@ -1072,6 +1075,7 @@ __device__ __forceinline__ void hash_plan_cta(const int32_t* __restrict__ hist_a
 __global__ void hash_shard_plan_kernel(const int32_t* __restrict__ hist_all, int world, int rank,
                                        int chunks, int64_t rows, int64_t k,
                                        int32_t* __restrict__ thr_out, int64_t* __restrict__ need_out) {
+  sah_pdl_entry_early();
   const int lane = threadIdx.x & 31;
   const int64_t t = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (t >= rows * chunks) return;   // warp-uniform
@@ -1092,8 +1096,7 @@ extern "C" int sah_hash_shard_plan(const int32_t* hist_all, int world, int rank,
   SAH_REQUIRE(hist_all && thr && need, "hash_shard_plan: null pointer");
   SAH_REQUIRE(world > 0 && rank >= 0 && rank < world && rows > 0 && chunks >= 1,
               "hash_shard_plan: bad extents");
-  hash_shard_plan_kernel<<<(unsigned)sah_ceil_div(rows * chunks, 4), 128, 0, (cudaStream_t)stream>>>(
-      hist_all, world, rank, chunks, rows, k, thr, need);
+  sah_launch_chain(hash_shard_plan_kernel, (unsigned)sah_ceil_div(rows * chunks, 4), 128, 0, (cudaStream_t)stream, hist_all, world, rank, chunks, rows, k, thr, need);
   SAH_LAUNCH_CHECK("hash_shard_plan");
   return SAH_OK;
 }
@@ -1112,6 +1115,7 @@ hash_emit_kernel(const uint32_t* __restrict__ kcodes, int64_t kc_stride,
                  const int32_t* __restrict__ thr_in, const int64_t* __restrict__ need_in,
                  const int32_t* __restrict__ hist_all, int chunks, int64_t k,
                  const uint4* __restrict__ scores_in, uint32_t* __restrict__ out_bits) {
+  sah_pdl_entry();
   __shared__ int wsum[2][HP_THREADS / 32];
   __shared__ unsigned long long pl[3][33];
   __shared__ int thr_sm;
@@ -1208,7 +1212,7 @@ extern "C" int sah_hash_emit(const uint32_t* kcodes, int64_t kc_stride, const ui
   const int64_t rows = (int64_t)B * Hq * Sq;
   const int64_t chunk_words = hash_chunk_words(W, chunks);
   dim3 grid((unsigned)rows, (unsigned)chunks);
-  hash_emit_kernel<<<grid, HP_THREADS, 0, (cudaStream_t)stream>>>(kcodes, kc_stride, qcodes, nbits, Sq, S, W,
+  sah_launch_chain(hash_emit_kernel, grid, HP_THREADS, 0, (cudaStream_t)stream, kcodes, kc_stride, qcodes, nbits, Sq, S, W,
                                                                 chunk_words, prev_bits, rows, thr, need,
                                                                 nullptr, chunks, 0,
                                                                 reinterpret_cast<const uint4*>(scores), out_bits);
@@ -1266,8 +1270,7 @@ extern "C" int sah_hash_topk_ws(const uint32_t* kcodes, int64_t kc_stride, const
   {
     // every emit CTA derives its threshold and tie share from the chunk histograms itself
     dim3 grid((unsigned)rows, (unsigned)chunks);
-    hash_emit_kernel<<<grid, HP_THREADS, 0, (cudaStream_t)stream>>>(
-        kcodes, kc_stride, qcodes, nbits, Sq, S, W, hash_chunk_words(W, chunks), prev_bits, rows, nullptr,
+    sah_launch_chain(hash_emit_kernel, grid, HP_THREADS, 0, (cudaStream_t)stream, kcodes, kc_stride, qcodes, nbits, Sq, S, W, hash_chunk_words(W, chunks), prev_bits, rows, nullptr,
         nullptr, hist, chunks, k, reinterpret_cast<const uint4*>(scores), out_bits);
     SAH_LAUNCH_CHECK("hash_topk_ws emit");
   }

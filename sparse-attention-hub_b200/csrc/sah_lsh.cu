@@ -105,6 +105,7 @@ __global__ void lsh_key_stats_kernel(const T* __restrict__ k, int64_t ks_b, int6
                                      int64_t ks_s, int Hkv, int64_t s0, int64_t s1, int D,
                                      const T* __restrict__ mean, int64_t cap,
                                      float* __restrict__ norms, unsigned int* __restrict__ max_bits) {
+  sah_pdl_entry_early();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
   const int64_t bh = blockIdx.y;
   const int64_t b = bh / Hkv, h = bh % Hkv;
@@ -143,8 +144,7 @@ extern "C" int sah_lsh_key_stats(const void* keys, int dtype, int64_t ks_b, int6
   if (gx > cap_x) gx = cap_x;
   dim3 grid((unsigned)gx, (unsigned)(B * Hkv));
   SAH_DISPATCH_DTYPE(dtype, T, {
-    lsh_key_stats_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>(
-        reinterpret_cast<const T*>(keys), ks_b, ks_h, ks_s, Hkv, s0, s1, D,
+    sah_launch_chain(lsh_key_stats_kernel<T>, grid, 256, 0, (cudaStream_t)stream, reinterpret_cast<const T*>(keys), ks_b, ks_h, ks_s, Hkv, s0, s1, D,
         reinterpret_cast<const T*>(mean), cap, norms, max_norm_bits);
   });
   SAH_LAUNCH_CHECK("lsh_key_stats");
@@ -172,6 +172,7 @@ lsh_key_sign_kernel(const T* __restrict__ k, int64_t ks_b, int64_t ks_h, int64_t
                     const float* __restrict__ norms, const unsigned int* __restrict__ max_bits,
                     const T* __restrict__ proj, int L, int K, int64_t cap,
                     CodeT* __restrict__ codes) {
+  sah_pdl_entry_early();
   extern __shared__ __align__(16) unsigned char lsh_smem[];
   const int nbits = L * K;
   const int Dp = D + 1;
@@ -266,7 +267,7 @@ extern "C" int sah_lsh_key_sign(const void* keys, int dtype, int64_t ks_b, int64
     cudaError_t e = cudaFuncSetAttribute(lsh_key_sign_kernel<T, CodeT>,                            \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
     if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "lsh_key_sign attr: %s", cudaGetErrorString(e)); \
-    lsh_key_sign_kernel<T, CodeT><<<grid, 256, smem, st>>>(                                        \
+    sah_launch_chain(lsh_key_sign_kernel<T, CodeT>, grid, 256, smem, st, \
         reinterpret_cast<const T*>(keys), ks_b, ks_h, ks_s, Hkv, s0, s1, D,                        \
         reinterpret_cast<const T*>(mean), norms, max_norm_bits, reinterpret_cast<const T*>(proj),  \
         L, K, cap, reinterpret_cast<CodeT*>(codes));                                               \
@@ -350,6 +351,7 @@ lsh_query_kernel(const T* __restrict__ q, int64_t qs_b, int64_t qs_h, int64_t qs
                  int G, int D, const T* __restrict__ mean, const T* __restrict__ proj, int L, int K,
                  CodeT* __restrict__ qcodes, float* __restrict__ qunit, T* __restrict__ qhat,
                  float* __restrict__ qmu) {
+  sah_pdl_entry_early();
   extern __shared__ __align__(16) unsigned char lsh_smem[];
   float* qn = reinterpret_cast<float*>(lsh_smem);                 // [D] normalised query
   unsigned char* sb = lsh_smem + (size_t)D * sizeof(float);       // [L*K]
@@ -451,13 +453,11 @@ extern "C" int sah_lsh_query(const void* q, int dtype, int64_t qs_b, int64_t qs_
   cudaStream_t st = (cudaStream_t)stream;
   SAH_DISPATCH_DTYPE(dtype, T, {
     if (K <= 8)
-      lsh_query_kernel<T, uint8_t><<<(unsigned)rows, 256, smem, st>>>(
-          reinterpret_cast<const T*>(q), qs_b, qs_h, qs_q, Hq, Sq, G, D,
+      sah_launch_chain(lsh_query_kernel<T, uint8_t>, (unsigned)rows, 256, smem, st, reinterpret_cast<const T*>(q), qs_b, qs_h, qs_q, Hq, Sq, G, D,
           reinterpret_cast<const T*>(mean), reinterpret_cast<const T*>(proj), L, K,
           reinterpret_cast<uint8_t*>(qcodes), qunit, reinterpret_cast<T*>(qhat), qmu);
     else
-      lsh_query_kernel<T, uint16_t><<<(unsigned)rows, 256, smem, st>>>(
-          reinterpret_cast<const T*>(q), qs_b, qs_h, qs_q, Hq, Sq, G, D,
+      sah_launch_chain(lsh_query_kernel<T, uint16_t>, (unsigned)rows, 256, smem, st, reinterpret_cast<const T*>(q), qs_b, qs_h, qs_q, Hq, Sq, G, D,
           reinterpret_cast<const T*>(mean), reinterpret_cast<const T*>(proj), L, K,
           reinterpret_cast<uint16_t*>(qcodes), qunit, reinterpret_cast<T*>(qhat), qmu);
   });
@@ -486,6 +486,7 @@ __global__ void __launch_bounds__(LSH_MATCH_WARPS * 32)
 lsh_match_kernel(const CodeT* __restrict__ codes, int64_t cap, const CodeT* __restrict__ qcodes,
                  int Hq, int Sq, int G, int L, int64_t S, int64_t W,
                  const uint32_t* __restrict__ prev_bits, uint32_t* __restrict__ out_bits) {
+  sah_pdl_entry();
   extern __shared__ __align__(16) unsigned char lsh_smem[];
   uint4* qs = reinterpret_cast<uint4*>(lsh_smem);  // [R][NC]
   const int R = G * Sq;
@@ -556,14 +557,168 @@ lsh_match_kernel(const CodeT* __restrict__ codes, int64_t cap, const CodeT* __re
   }
 }
 
+// Decode shapes (at most four query rows per group, signature rows of up to 96 bytes): the
+// group's query rows stay in registers (4 x NC 16-byte chunks), so that a (word, row) test is
+// three integer instructions with no shared-memory operand, and a warp takes one bitmap word
+// (32 consecutive keys) per round, striding over the row with all warps of the group's CTAs:
+// the grid is two CTAs per SM whatever the key count, every warp gets the same number of words
+// to within one.  The 32 signature rows of a round are contiguous in memory; the warp copies
+// them to shared memory with 16-byte asynchronous copies, lane after lane (every copy
+// instruction covers 512 contiguous bytes, where a lane loading its own row of 80 bytes makes
+// each load instruction touch 20 cache lines), three rounds ahead, and every lane then reads
+// its own row from there.  Lane r writes the word of row r.
+#define LSH_MATCH_REG_MAX_NC 6
+#define LSH_MATCH_REG_STAGES 4
+
+template <typename CodeT, int NC>
+__global__ void __launch_bounds__(LSH_MATCH_WARPS * 32, 2)
+lsh_match_reg_kernel(const CodeT* __restrict__ codes, int64_t cap, const CodeT* __restrict__ qcodes,
+                     int Hq, int Sq, int G, int L, int64_t S, int64_t W,
+                     const uint32_t* __restrict__ prev_bits, uint32_t* __restrict__ out_bits) {
+  sah_pdl_entry();
+  extern __shared__ __align__(16) unsigned char mr_smem[];  // [warps][stages][32 rows of NC chunks]
+  __shared__ __align__(16) CodeT qflat[4 * NC * (16 / (int)sizeof(CodeT))];
+  constexpr int PER16 = 16 / (int)sizeof(CodeT);
+  constexpr int LP = NC * PER16;
+  constexpr int NST = LSH_MATCH_REG_STAGES;
+  constexpr int ROUND_BYTES = 32 * NC * 16;
+  constexpr uint32_t ONES = sizeof(CodeT) == 1 ? 0x01010101u : 0x00010001u;
+  constexpr uint32_t HIGH = sizeof(CodeT) == 1 ? 0x80808080u : 0x80008000u;
+  const int R = G * Sq;  // <= 4
+  const int64_t bh = blockIdx.y;  // b * Hkv + hkv
+  const int Hkv = Hq / G;
+  const int64_t b = bh / Hkv, hkv = bh % Hkv;
+  for (int i = threadIdx.x; i < 4 * LP; i += blockDim.x) {
+    const int r = i / LP, l = i % LP;
+    CodeT c = (CodeT)~(CodeT)0;  // padding: all ones, which the zero padding of a key row never equals
+    if (r < R && l < L) {
+      const int g = r / Sq, qi = r % Sq;
+      c = qcodes[(((b * Hq) + hkv * G + g) * Sq + qi) * L + l];
+    }
+    qflat[i] = c;
+  }
+  __syncthreads();
+  uint4 q[4][NC];
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int c = 0; c < NC; ++c) q[r][c] = reinterpret_cast<const uint4*>(qflat)[r * NC + c];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t words = (S + 31) / 32;
+  const uint4* base = reinterpret_cast<const uint4*>(codes + bh * cap * LP);
+  const int64_t chunks_end = S * NC;  // 16-byte chunks of this (batch, KV head) that hold keys
+  unsigned char* wbuf = mr_smem + (size_t)warp * NST * ROUND_BYTES;
+  const uint32_t wbuf_s = (uint32_t)__cvta_generic_to_shared(wbuf);
+  int64_t my_row = -1;  // lane r < R writes row r
+  if (lane < R) {
+    const int g = lane / Sq, qi = lane % Sq;
+    my_row = ((b * Hq) + hkv * G + g) * Sq + qi;
+  }
+  const int64_t stride = (int64_t)gridDim.x * LSH_MATCH_WARPS;
+  const int64_t w0 = (int64_t)blockIdx.x * LSH_MATCH_WARPS + warp;
+  // copies of round `w` into stage `st`; one commit per call whether or not anything was copied
+  auto issue = [&](int64_t w, int st) {
+    if (w < words) {
+      const int64_t first = w * 32 * NC;
+#pragma unroll
+      for (int it = 0; it < NC; ++it) {
+        const int j = it * 32 + lane;
+        if (first + j < chunks_end)
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(wbuf_s + st * ROUND_BYTES + j * 16),
+                       "l"(base + first + j)
+                       : "memory");
+      }
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+#pragma unroll
+  for (int s0 = 0; s0 < NST - 1; ++s0) issue(w0 + s0 * stride, s0);
+  int i = 0;
+  for (int64_t w = w0; w < words; w += stride, ++i) {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(NST - 2) : "memory");
+    __syncwarp();  // every lane's copies of this round have landed; everyone is done with round i - 1
+    issue(w + (NST - 1) * stride, (i + NST - 1) % NST);
+    const int64_t key = w * 32 + lane;
+    uint32_t hit[4] = {0u, 0u, 0u, 0u};
+    if (key < S) {
+      const uint4* mine_row = reinterpret_cast<const uint4*>(wbuf + (i % NST) * ROUND_BYTES) + lane * NC;
+      uint4 v[NC];
+#pragma unroll
+      for (int c = 0; c < NC; ++c) v[c] = mine_row[c];
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const uint32_t x0 = v[c].x ^ q[r][c].x, x1 = v[c].y ^ q[r][c].y;
+          const uint32_t x2 = v[c].z ^ q[r][c].z, x3 = v[c].w ^ q[r][c].w;
+          const uint32_t z0 = (x0 - ONES) & ~x0 & HIGH, z1 = (x1 - ONES) & ~x1 & HIGH;
+          const uint32_t z2 = (x2 - ONES) & ~x2 & HIGH, z3 = (x3 - ONES) & ~x3 & HIGH;
+          hit[r] |= z0 | z1;
+          hit[r] |= z2 | z3;
+        }
+      }
+    }
+    uint32_t mine = 0u;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const uint32_t wbits = __ballot_sync(0xffffffffu, hit[r] != 0u);
+      if (lane == r) mine = wbits;
+    }
+    if (my_row >= 0) {
+      if (prev_bits != nullptr) mine |= prev_bits[my_row * W + w];
+      out_bits[my_row * W + w] = mine;
+    }
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+}
+
 template <typename CodeT>
 static int lsh_match_launch(const void* codes, int64_t cap, const void* qcodes, int Hq, int Sq, int G, int L,
                             int64_t S, int64_t W, const uint32_t* prev_bits, uint32_t* out_bits, dim3 grid,
                             size_t smem, cudaStream_t st) {
   const int nc = lsh_row_pitch<CodeT>(L) / (16 / (int)sizeof(CodeT));
+  // SAH_LSH_MATCH_REG=0 in the environment keeps the shared-memory form for every shape
+  static int reg_env = -1;
+  if (reg_env < 0) {
+    const char* e = getenv("SAH_LSH_MATCH_REG");
+    reg_env = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  if (reg_env == 1 && G * Sq <= 4 && nc <= LSH_MATCH_REG_MAX_NC) {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) {
+      int n = 0;
+      if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) sms = n;
+    }
+    const int64_t words = (S + 31) / 32;
+    int64_t per_group = sah_ceil_div((int64_t)2 * sms, (int64_t)grid.y);
+    const int64_t most = sah_ceil_div(words, LSH_MATCH_WARPS);
+    if (per_group > most) per_group = most;
+    if (per_group < 1) per_group = 1;
+    const dim3 rgrid((unsigned)per_group, grid.y);
+#define LSH_MATCH_REG_CASE(NC)                                                                      \
+  case NC: {                                                                                        \
+    constexpr int RSMEM = LSH_MATCH_WARPS * LSH_MATCH_REG_STAGES * 32 * NC * 16;                    \
+    static bool allowed[64] = {};                                                                   \
+    if (RSMEM > 48 * 1024 && dev >= 0 && dev < 64 && !allowed[dev]) {                               \
+      cudaError_t e = cudaFuncSetAttribute(lsh_match_reg_kernel<CodeT, NC>,                         \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, RSMEM);     \
+      if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "lsh_match attr: %s", cudaGetErrorString(e)); \
+      allowed[dev] = true;                                                                          \
+    }                                                                                               \
+    sah_launch_chain(lsh_match_reg_kernel<CodeT, NC>, rgrid, LSH_MATCH_WARPS * 32, RSMEM, st,       \
+        reinterpret_cast<const CodeT*>(codes), cap, reinterpret_cast<const CodeT*>(qcodes), Hq, Sq, \
+        G, L, S, W, prev_bits, out_bits);                                                           \
+  } break;
+    switch (nc) {
+      LSH_MATCH_REG_CASE(1) LSH_MATCH_REG_CASE(2) LSH_MATCH_REG_CASE(3) LSH_MATCH_REG_CASE(4)
+      LSH_MATCH_REG_CASE(5) LSH_MATCH_REG_CASE(6)
+    }
+#undef LSH_MATCH_REG_CASE
+    return SAH_OK;
+  }
 #define LSH_MATCH_CASE(NC)                                                                          \
   case NC:                                                                                          \
-    lsh_match_kernel<CodeT, NC><<<grid, LSH_MATCH_WARPS * 32, smem, st>>>(                          \
+    sah_launch_chain(lsh_match_kernel<CodeT, NC>, grid, LSH_MATCH_WARPS * 32, smem, st, \
         reinterpret_cast<const CodeT*>(codes), cap, reinterpret_cast<const CodeT*>(qcodes), Hq, Sq, \
         G, L, S, W, prev_bits, out_bits);                                                           \
     break;
@@ -787,6 +942,7 @@ lsh_key_den_kernel(const T* __restrict__ k, int64_t ks_b, int64_t ks_h, int64_t 
                    const float* __restrict__ norms, int64_t cap,
                    const unsigned int* __restrict__ max_bits,
                    const unsigned int* __restrict__ dens_max_bits, float* __restrict__ dens) {
+  sah_pdl_entry_early();
   __shared__ float tab[128];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
   const int64_t bh = blockIdx.y;
@@ -818,6 +974,7 @@ lsh_key_den_kernel(const T* __restrict__ k, int64_t ks_b, int64_t ks_h, int64_t 
 }
 
 __global__ void lsh_den_commit_kernel(const unsigned int* max_bits, unsigned int* dens_max_bits) {
+  sah_pdl_entry_early();
   *dens_max_bits = *max_bits;
 }
 
@@ -836,12 +993,12 @@ extern "C" int sah_lsh_key_den(const void* keys, int dtype, int64_t ks_b, int64_
   dim3 grid((unsigned)gx, (unsigned)(B * Hkv));
   cudaStream_t st = (cudaStream_t)stream;
   SAH_DISPATCH_DTYPE(dtype, T, {
-    lsh_key_den_kernel<T><<<grid, 256, 0, st>>>(reinterpret_cast<const T*>(keys), ks_b, ks_h, ks_s, Hkv,
+    sah_launch_chain(lsh_key_den_kernel<T>, grid, 256, 0, st, reinterpret_cast<const T*>(keys), ks_b, ks_h, ks_s, Hkv,
                                                 s_new0, s1, D, reinterpret_cast<const T*>(mean), norms,
                                                 cap, max_norm_bits, dens_max_bits, dens);
   });
   SAH_LAUNCH_CHECK("lsh_key_den");
-  lsh_den_commit_kernel<<<1, 1, 0, st>>>(max_norm_bits, dens_max_bits);
+  sah_launch_chain(lsh_den_commit_kernel, 1, 1, 0, st, max_norm_bits, dens_max_bits);
   SAH_LAUNCH_CHECK("lsh_den_commit");
   return SAH_OK;
 }

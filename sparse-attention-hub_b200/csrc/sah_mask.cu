@@ -35,6 +35,18 @@ static thread_local cudaEvent_t g_prof_open[SAH_PROF_SLOTS];
 
 void sah_count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
+// Chained launches are off unless SAH_PDL=1 is in the environment (read once);
+// SAH_PDL_MAX_WARPS then replaces the grid size up to which a launch may be chained.
+int sah_pdl_max_warps() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("SAH_PDL");
+    const char* m = getenv("SAH_PDL_MAX_WARPS");
+    v = (e != nullptr && e[0] == '1') ? (m != nullptr && atoi(m) > 0 ? atoi(m) : 1024) : 0;
+  }
+  return v;
+}
+
 void sah_prof_begin(int slot, cudaStream_t st) {
   if (!g_prof_on.load(std::memory_order_relaxed)) return;
   cudaEvent_t e;
@@ -83,6 +95,7 @@ __global__ void mask_fill_band_kernel(uint32_t* __restrict__ bits, int64_t rows,
                                       int64_t S, int64_t W, int64_t w_begin, int64_t w_count,
                                       int64_t lo_base, int64_t lo_qstep, int64_t hi_base,
                                       int64_t hi_qstep, int value) {
+  sah_pdl_entry_early();
   int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= rows * w_count) return;
   int64_t row = t / w_count;
@@ -119,8 +132,7 @@ extern "C" int sah_mask_fill_band(uint32_t* bits, int64_t rows, int Sq, int64_t 
   int64_t total = rows * w_count;
   int threads = 256;
   int64_t blocks = sah_ceil_div(total, threads);
-  mask_fill_band_kernel<<<(unsigned)blocks, threads, 0, (cudaStream_t)stream>>>(
-      bits, rows, Sq, S, W, w_begin, w_count, lo_base, lo_qstep, hi_base, hi_qstep, value);
+  sah_launch_chain(mask_fill_band_kernel, (unsigned)blocks, threads, 0, (cudaStream_t)stream, bits, rows, Sq, S, W, w_begin, w_count, lo_base, lo_qstep, hi_base, hi_qstep, value);
   SAH_LAUNCH_CHECK("mask_fill_band");
   return SAH_OK;
 }
@@ -137,6 +149,7 @@ struct MaskBands {
 
 __global__ void mask_fill_bands_kernel(uint32_t* __restrict__ bits, int64_t rows, int Sq, int64_t S,
                                        int64_t W, MaskBands bands, int init_zero) {
+  sah_pdl_entry_early();
   const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= rows * W) return;
   const int64_t row = t / W;
@@ -178,8 +191,7 @@ extern "C" int sah_mask_fill_bands(uint32_t* bits, int64_t rows, int Sq, int64_t
     mb.value[i] = on ? (int)bands[5 * i + 4] : 0;
   }
   const int64_t total = rows * W;
-  mask_fill_bands_kernel<<<(unsigned)sah_ceil_div(total, 256), 256, 0, (cudaStream_t)stream>>>(
-      bits, rows, Sq, S, W, mb, init_zero);
+  sah_launch_chain(mask_fill_bands_kernel, (unsigned)sah_ceil_div(total, 256), 256, 0, (cudaStream_t)stream, bits, rows, Sq, S, W, mb, init_zero);
   SAH_LAUNCH_CHECK("mask_fill_bands");
   return SAH_OK;
 }
@@ -188,6 +200,7 @@ extern "C" int sah_mask_fill_bands(uint32_t* bits, int64_t rows, int Sq, int64_t
 // One CTA per row; the running base carries across blockDim-word chunks.
 __global__ void mask_rowscan_kernel(const uint32_t* __restrict__ bits, int64_t W,
                                     int32_t* __restrict__ wpre, int64_t* __restrict__ rowcnt) {
+  sah_pdl_entry_early();
   __shared__ int scratch[33];
   int64_t row = blockIdx.x;
   const uint32_t* b = bits + row * W;
@@ -205,6 +218,7 @@ __global__ void mask_rowscan_kernel(const uint32_t* __restrict__ bits, int64_t W
 
 // Exclusive scan of rowcnt[rows] into ptr[rows+1] (single CTA, looped).
 __global__ void mask_ptrscan_kernel(const int64_t* rowcnt, int64_t rows, int64_t* ptr) {
+  sah_pdl_entry_early();
   __shared__ long long scratch[33];
   long long base = 0;
   for (int64_t r0 = 0; r0 < rows; r0 += blockDim.x) {
@@ -228,13 +242,13 @@ extern "C" int sah_mask_rowscan(const uint32_t* bits, int64_t rows, int64_t W, i
     // Row counts are staged in ptr[1 .. rows]; the scan kernel reads them
     // from there before overwriting (it walks forward, one chunk at a time,
     // and every chunk is read completely before any of it is written).
-    mask_rowscan_kernel<<<(unsigned)rows, 1024, 0, st>>>(bits, W, wpre, ptr + 1);
+    sah_launch_chain(mask_rowscan_kernel, (unsigned)rows, 1024, 0, st, bits, W, wpre, ptr + 1);
     SAH_LAUNCH_CHECK("mask_rowscan");
   }
   // In-place: chunk r0 reads ptr[1 + r] for r in the chunk, then writes ptr[r]
   // for the same r; ptr[1 + last r of chunk] is read by the next chunk, so the
   // write of ptr[r] (r <= last) never clobbers an unread count.
-  mask_ptrscan_kernel<<<1, 1024, 0, st>>>(ptr + 1, rows, ptr);
+  sah_launch_chain(mask_ptrscan_kernel, 1, 1024, 0, st, ptr + 1, rows, ptr);
   SAH_LAUNCH_CHECK("mask_ptrscan");
   return SAH_OK;
 }
@@ -244,6 +258,7 @@ __global__ void mask_bits_to_indices_kernel(const uint32_t* __restrict__ bits,
                                             const int32_t* __restrict__ wpre,
                                             const int64_t* __restrict__ ptr, int64_t rows,
                                             int64_t S, int64_t W, int64_t* __restrict__ idx) {
+  sah_pdl_entry_early();
   int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= rows * W) return;
   int64_t row = t / W, w = t - row * W;
@@ -265,8 +280,8 @@ extern "C" int sah_mask_bits_to_indices(const uint32_t* bits, const int32_t* wpr
   if (rows == 0) return SAH_OK;
   SAH_REQUIRE(indices != nullptr, "bits_to_indices: indices is null");
   int64_t total = rows * W;
-  mask_bits_to_indices_kernel<<<(unsigned)sah_ceil_div(total, 256), 256, 0,
-                                (cudaStream_t)stream>>>(bits, wpre, ptr, rows, S, W, indices);
+  sah_launch_chain(mask_bits_to_indices_kernel, (unsigned)sah_ceil_div(total, 256), 256, 0,
+                                (cudaStream_t)stream, bits, wpre, ptr, rows, S, W, indices);
   SAH_LAUNCH_CHECK("mask_bits_to_indices");
   return SAH_OK;
 }
@@ -278,6 +293,7 @@ __global__ void mask_bits_to_dense_kernel(const uint32_t* __restrict__ bits,
                                           const int32_t* __restrict__ wpre,
                                           const int64_t* __restrict__ ptr, int64_t rows,
                                           int64_t S, int64_t W, T* __restrict__ dense) {
+  sah_pdl_entry_early();
   int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= rows * S) return;
   int64_t row = t / S, j = t - row * S;
@@ -305,8 +321,8 @@ extern "C" int sah_mask_bits_to_dense(const uint32_t* bits, const void* data,
   if (rows == 0) return SAH_OK;
   int64_t total = rows * S;
   SAH_DISPATCH_DTYPE(dtype, T, {
-    mask_bits_to_dense_kernel<T><<<(unsigned)sah_ceil_div(total, 256), 256, 0,
-                                   (cudaStream_t)stream>>>(bits, (const T*)data, wpre, ptr,
+    sah_launch_chain(mask_bits_to_dense_kernel<T>, (unsigned)sah_ceil_div(total, 256), 256, 0,
+                                   (cudaStream_t)stream, bits, (const T*)data, wpre, ptr,
                                                            rows, S, W, (T*)dense);
   });
   SAH_LAUNCH_CHECK("mask_bits_to_dense");
@@ -317,6 +333,7 @@ extern "C" int sah_mask_bits_to_dense(const uint32_t* bits, const void* data,
 template <typename T>
 __global__ void mask_dense_to_bits_kernel(const T* __restrict__ dense, int64_t rows, int64_t S,
                                           int64_t W, uint32_t* __restrict__ bits) {
+  sah_pdl_entry_early();
   int64_t gw = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;  // one warp per word
   int lane = threadIdx.x & 31;
   if (gw >= rows * W) return;
@@ -335,8 +352,8 @@ extern "C" int sah_mask_dense_to_bits(const void* dense, int dtype, int64_t rows
   if (rows == 0) return SAH_OK;
   int64_t threads_total = rows * W * 32;
   SAH_DISPATCH_DTYPE(dtype, T, {
-    mask_dense_to_bits_kernel<T><<<(unsigned)sah_ceil_div(threads_total, 256), 256, 0,
-                                   (cudaStream_t)stream>>>((const T*)dense, rows, S, W, bits);
+    sah_launch_chain(mask_dense_to_bits_kernel<T>, (unsigned)sah_ceil_div(threads_total, 256), 256, 0,
+                                   (cudaStream_t)stream, (const T*)dense, rows, S, W, bits);
   });
   SAH_LAUNCH_CHECK("mask_dense_to_bits");
   return SAH_OK;
@@ -349,6 +366,7 @@ __global__ void mask_dense_gather_data_kernel(const T* __restrict__ dense,
                                               const int32_t* __restrict__ wpre,
                                               const int64_t* __restrict__ ptr, int64_t rows,
                                               int64_t S, int64_t W, T* __restrict__ data) {
+  sah_pdl_entry_early();
   int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= rows * S) return;
   int64_t row = t / S, j = t - row * S;
@@ -369,8 +387,8 @@ extern "C" int sah_mask_dense_gather_data(const void* dense, int dtype, const ui
   if (rows == 0) return SAH_OK;
   int64_t total = rows * S;
   SAH_DISPATCH_DTYPE(dtype, T, {
-    mask_dense_gather_data_kernel<T><<<(unsigned)sah_ceil_div(total, 256), 256, 0,
-                                       (cudaStream_t)stream>>>((const T*)dense, bits, wpre,
+    sah_launch_chain(mask_dense_gather_data_kernel<T>, (unsigned)sah_ceil_div(total, 256), 256, 0,
+                                       (cudaStream_t)stream, (const T*)dense, bits, wpre,
                                                                ptr, rows, S, W, (T*)data);
   });
   SAH_LAUNCH_CHECK("mask_dense_gather_data");
@@ -380,6 +398,7 @@ extern "C" int sah_mask_dense_gather_data(const void* dense, int dtype, const ui
 // ---- bitmap OR ---------------------------------------------------------------------
 __global__ void mask_or_kernel(const uint32_t* __restrict__ a, const uint32_t* __restrict__ b,
                                int64_t words, uint32_t* __restrict__ out) {
+  sah_pdl_entry_early();
   int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (t < words) out[t] = a[t] | b[t];
 }
@@ -388,8 +407,7 @@ extern "C" int sah_mask_or(const uint32_t* a, const uint32_t* b, int64_t words, 
                            void* stream) {
   SAH_REQUIRE(a && b && out, "mask_or: null pointer");
   if (words == 0) return SAH_OK;
-  mask_or_kernel<<<(unsigned)sah_ceil_div(words, 256), 256, 0, (cudaStream_t)stream>>>(
-      a, b, words, out);
+  sah_launch_chain(mask_or_kernel, (unsigned)sah_ceil_div(words, 256), 256, 0, (cudaStream_t)stream, a, b, words, out);
   SAH_LAUNCH_CHECK("mask_or");
   return SAH_OK;
 }
@@ -405,6 +423,7 @@ __global__ void mask_sample_data_kernel(const uint32_t* __restrict__ prev,
                                         const T* __restrict__ row_weight,
                                         const T* __restrict__ dense_weight, int64_t rows,
                                         int64_t S, int64_t W, T* __restrict__ data) {
+  sah_pdl_entry_early();
   int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= rows * W) return;
   int64_t row = t / W, w = t - row * W;
@@ -438,8 +457,8 @@ extern "C" int sah_mask_sample_data(const uint32_t* prev_bits, const uint32_t* o
   SAH_REQUIRE(data != nullptr, "sample_data: data is null");
   int64_t total = rows * W;
   SAH_DISPATCH_DTYPE(dtype, T, {
-    mask_sample_data_kernel<T><<<(unsigned)sah_ceil_div(total, 256), 256, 0,
-                                 (cudaStream_t)stream>>>(prev_bits, out_bits, wpre, ptr,
+    sah_launch_chain(mask_sample_data_kernel<T>, (unsigned)sah_ceil_div(total, 256), 256, 0,
+                                 (cudaStream_t)stream, prev_bits, out_bits, wpre, ptr,
                                                          (const T*)row_weight,
                                                          (const T*)dense_weight, rows, S, W,
                                                          (T*)data);
@@ -457,6 +476,7 @@ __global__ void mask_unit_data_kernel(const uint32_t* __restrict__ bits,
                                       const int32_t* __restrict__ wpre,
                                       const int64_t* __restrict__ ptr, int64_t rows, int64_t W,
                                       T* __restrict__ data) {
+  sah_pdl_entry_early();
   int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= rows * W) return;
   const uint32_t m = bits[t];
@@ -479,8 +499,7 @@ extern "C" int sah_mask_unit_data(const uint32_t* bits, const uint32_t* unit_bit
   SAH_REQUIRE(data != nullptr, "unit_data: data is null");
   const int64_t total = rows * W;
   SAH_DISPATCH_DTYPE(dtype, T, {
-    mask_unit_data_kernel<T><<<(unsigned)sah_ceil_div(total, 256), 256, 0, (cudaStream_t)stream>>>(
-        bits, unit_bits, wpre, ptr, rows, W, (T*)data);
+    sah_launch_chain(mask_unit_data_kernel<T>, (unsigned)sah_ceil_div(total, 256), 256, 0, (cudaStream_t)stream, bits, unit_bits, wpre, ptr, rows, W, (T*)data);
   });
   SAH_LAUNCH_CHECK("mask_unit_data");
   return SAH_OK;
@@ -512,6 +531,7 @@ template <typename T>
 __global__ void mask_rowwise_claim_kernel(const int64_t* __restrict__ idx, const T* __restrict__ vals,
                                           int64_t rows, int64_t k, int64_t S,
                                           unsigned long long* __restrict__ claims) {
+  sah_pdl_entry_early();
   const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= rows * k) return;
   const int64_t row = t / k, j = t - row * k;
@@ -524,6 +544,7 @@ __global__ void mask_rowwise_claim_kernel(const int64_t* __restrict__ idx, const
 template <typename T>
 __global__ void mask_rowwise_settle_kernel(const unsigned long long* __restrict__ claims, int64_t n,
                                            T* __restrict__ dense) {
+  sah_pdl_entry_early();
   const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= n) return;
   const unsigned long long c = claims[t];
@@ -539,11 +560,9 @@ extern "C" int sah_mask_rowwise_scatter(const int64_t* idx, const void* vals, in
   cudaError_t e = cudaMemsetAsync(claims, 0, (size_t)(rows * S) * sizeof(unsigned long long), st);
   if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "rowwise_scatter: memset: %s", cudaGetErrorString(e));
   SAH_DISPATCH_DTYPE(dtype, T, {
-    mask_rowwise_claim_kernel<T><<<(unsigned)sah_ceil_div(rows * k, 256), 256, 0, st>>>(
-        idx, (const T*)vals, rows, k, S, (unsigned long long*)claims);
+    sah_launch_chain(mask_rowwise_claim_kernel<T>, (unsigned)sah_ceil_div(rows * k, 256), 256, 0, st, idx, (const T*)vals, rows, k, S, (unsigned long long*)claims);
     SAH_LAUNCH_CHECK("mask_rowwise_claim");
-    mask_rowwise_settle_kernel<T><<<(unsigned)sah_ceil_div(rows * S, 256), 256, 0, st>>>(
-        (const unsigned long long*)claims, rows * S, (T*)dense);
+    sah_launch_chain(mask_rowwise_settle_kernel<T>, (unsigned)sah_ceil_div(rows * S, 256), 256, 0, st, (const unsigned long long*)claims, rows * S, (T*)dense);
   });
   SAH_LAUNCH_CHECK("mask_rowwise_settle");
   return SAH_OK;
@@ -557,6 +576,7 @@ extern "C" int sah_mask_rowwise_scatter(const int64_t* idx, const void* vals, in
 template <typename T>
 __global__ void mask_flat_add_kernel(const int64_t* __restrict__ flat, const T* __restrict__ vals,
                                      int64_t n, int64_t total, float* __restrict__ acc) {
+  sah_pdl_entry_early();
   const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= n) return;
   const int64_t i = flat[t];
@@ -566,6 +586,7 @@ __global__ void mask_flat_add_kernel(const int64_t* __restrict__ flat, const T* 
 
 template <typename T>
 __global__ void mask_clamp_kernel(const float* __restrict__ acc, int64_t total, T* __restrict__ dense) {
+  sah_pdl_entry_early();
   const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= total) return;
   const float v = sah_round_to<T>(acc[t]);  // the sum lives in the mask dtype
@@ -578,8 +599,7 @@ extern "C" int sah_mask_flat_add(const int64_t* flat_idx, const void* vals, int 
   if (n == 0) return SAH_OK;
   SAH_REQUIRE(flat_idx != nullptr, "flat_add: indices are null");
   SAH_DISPATCH_DTYPE(dtype, T, {
-    mask_flat_add_kernel<T><<<(unsigned)sah_ceil_div(n, 256), 256, 0, (cudaStream_t)stream>>>(
-        flat_idx, (const T*)vals, n, total, acc);
+    sah_launch_chain(mask_flat_add_kernel<T>, (unsigned)sah_ceil_div(n, 256), 256, 0, (cudaStream_t)stream, flat_idx, (const T*)vals, n, total, acc);
   });
   SAH_LAUNCH_CHECK("mask_flat_add");
   return SAH_OK;
@@ -589,8 +609,7 @@ extern "C" int sah_mask_clamp_to_dense(const float* acc, int dtype, int64_t tota
                                        void* stream) {
   SAH_REQUIRE(acc && dense && total > 0, "clamp_to_dense: bad argument");
   SAH_DISPATCH_DTYPE(dtype, T, {
-    mask_clamp_kernel<T><<<(unsigned)sah_ceil_div(total, 256), 256, 0, (cudaStream_t)stream>>>(
-        acc, total, (T*)dense);
+    sah_launch_chain(mask_clamp_kernel<T>, (unsigned)sah_ceil_div(total, 256), 256, 0, (cudaStream_t)stream, acc, total, (T*)dense);
   });
   SAH_LAUNCH_CHECK("mask_clamp");
   return SAH_OK;
@@ -601,6 +620,7 @@ __global__ void mask_scatter_samples_kernel(const int64_t* __restrict__ cols,
                                             const int64_t* __restrict__ sptr, int64_t rows,
                                             int64_t n_max, int64_t S, int64_t W,
                                             uint32_t* __restrict__ bits) {
+  sah_pdl_entry_early();
   int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (j >= n_max || j >= sptr[rows]) return;
   // row = last r with sptr[r] <= j
@@ -619,8 +639,8 @@ extern "C" int sah_mask_scatter_samples(const int64_t* cols, const int64_t* sptr
                                         void* stream) {
   SAH_REQUIRE(cols && sptr && bits, "scatter_samples: null pointer");
   if (rows == 0 || n_max == 0) return SAH_OK;
-  mask_scatter_samples_kernel<<<(unsigned)sah_ceil_div(n_max, 256), 256, 0,
-                                (cudaStream_t)stream>>>(cols, sptr, rows, n_max, S, W, bits);
+  sah_launch_chain(mask_scatter_samples_kernel, (unsigned)sah_ceil_div(n_max, 256), 256, 0,
+                                (cudaStream_t)stream, cols, sptr, rows, n_max, S, W, bits);
   SAH_LAUNCH_CHECK("mask_scatter_samples");
   return SAH_OK;
 }
@@ -655,6 +675,7 @@ __device__ __forceinline__ float merge_weight(float a, float b) {
 template <typename T>
 __global__ void mask_merge_bits_kernel(MergeSide a, MergeSide b, int64_t rows, int64_t W,
                                        uint32_t* __restrict__ out) {
+  sah_pdl_entry_early();
   const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= rows * W) return;
   const uint32_t wa = a.bits[t], wb = b.bits[t];
@@ -677,6 +698,7 @@ __global__ void mask_merge_data_kernel(MergeSide a, MergeSide b, int64_t rows, i
                                        const uint32_t* __restrict__ outb,
                                        const int32_t* __restrict__ out_wpre,
                                        const int64_t* __restrict__ out_ptr, T* __restrict__ data) {
+  sah_pdl_entry_early();
   const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= rows * W) return;
   uint32_t m = outb[t];
@@ -705,8 +727,7 @@ extern "C" int sah_mask_merge_bits(const uint32_t* a_bits, const void* a_data, c
   if (rows == 0 || W == 0) return SAH_OK;
   MergeSide a{a_bits, a_data, a_wpre, a_ptr}, b{b_bits, b_data, b_wpre, b_ptr};
   SAH_DISPATCH_DTYPE(dtype, T, {
-    mask_merge_bits_kernel<T><<<(unsigned)sah_ceil_div(rows * W, 256), 256, 0, (cudaStream_t)stream>>>(
-        a, b, rows, W, out_bits);
+    sah_launch_chain(mask_merge_bits_kernel<T>, (unsigned)sah_ceil_div(rows * W, 256), 256, 0, (cudaStream_t)stream, a, b, rows, W, out_bits);
   });
   SAH_LAUNCH_CHECK("mask_merge_bits");
   return SAH_OK;
@@ -724,8 +745,7 @@ extern "C" int sah_mask_merge_data(const uint32_t* a_bits, const void* a_data, c
   if (rows == 0 || W == 0) return SAH_OK;
   MergeSide a{a_bits, a_data, a_wpre, a_ptr}, b{b_bits, b_data, b_wpre, b_ptr};
   SAH_DISPATCH_DTYPE(dtype, T, {
-    mask_merge_data_kernel<T><<<(unsigned)sah_ceil_div(rows * W, 256), 256, 0, (cudaStream_t)stream>>>(
-        a, b, rows, W, out_bits, out_wpre, out_ptr, reinterpret_cast<T*>(out_data));
+    sah_launch_chain(mask_merge_data_kernel<T>, (unsigned)sah_ceil_div(rows * W, 256), 256, 0, (cudaStream_t)stream, a, b, rows, W, out_bits, out_wpre, out_ptr, reinterpret_cast<T*>(out_data));
   });
   SAH_LAUNCH_CHECK("mask_merge_data");
   return SAH_OK;

@@ -298,6 +298,7 @@ pq_scores_kernel(const T* __restrict__ q, int64_t qs_b, int64_t qs_h, int64_t qs
                  const T* __restrict__ centroids, const uint8_t* __restrict__ codes, int64_t cap, int Hq,
                  int Hkv, int Sq, int64_t n_keys, int64_t init_offset, int64_t S, int n_sub, int sub_d,
                  int n_cent, int64_t keys_per_cta, T* __restrict__ scores) {
+  sah_pdl_entry();
   typedef typename PqEntry<T>::type Entry;
   extern __shared__ __align__(16) unsigned char pq_sm_raw[];
   const int G = Hq / Hkv;
@@ -427,7 +428,7 @@ extern "C" int sah_pq_scores(const void* q, int dtype, int64_t qs_b, int64_t qs_
       if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "pq_scores attr: %s", cudaGetErrorString(e));   \
       smem_allowed[SLOT] = (int)smem;                                                                     \
     }                                                                                                     \
-    pq_scores_kernel<T, VEC><<<grid, PQ_TILE, smem, st>>>((const T*)q, qs_b, qs_h, qs_q, (const T*)centroids, \
+    sah_launch_chain(pq_scores_kernel<T, VEC>, grid, PQ_TILE, smem, st, (const T*)q, qs_b, qs_h, qs_q, (const T*)centroids, \
                                                           codes, cap, Hq, Hkv, Sq, n_keys, init_offset, S, \
                                                           n_sub, sub_d, n_cent, keys_per_cta, (T*)scores); \
   } while (0)

@@ -73,6 +73,7 @@ quest_scores_kernel(const T* __restrict__ q, int64_t qs_b, int64_t qs_h, int64_t
                     const T* __restrict__ pmin, const T* __restrict__ pmax, int64_t P_cap, int Hq,
                     int Hkv, int Sq, int64_t S, int D, int page_size, const T* __restrict__ bias,
                     int64_t bias_s_b, int64_t bias_s_q, T* __restrict__ scores) {
+  sah_pdl_entry();
   __shared__ float q_sm[QS_MAXD];
   const int64_t row = blockIdx.y;
   const int qi = (int)(row % Sq);
@@ -179,8 +180,7 @@ extern "C" int sah_quest_scores(const void* q, int dtype, int64_t qs_b, int64_t 
   dim3 grid((unsigned)sah_ceil_div(P, QS_THREADS), (unsigned)rows);
   sah_prof_begin(SAH_PROF_QUEST, (cudaStream_t)stream);
   SAH_DISPATCH_DTYPE(dtype, T, {
-    quest_scores_kernel<T><<<grid, QS_THREADS, 0, (cudaStream_t)stream>>>(
-        (const T*)q, qs_b, qs_h, qs_q, (const T*)pmin, (const T*)pmax, P_cap, Hq, Hkv, Sq, S, D, page_size,
+    sah_launch_chain(quest_scores_kernel<T>, grid, QS_THREADS, 0, (cudaStream_t)stream, (const T*)q, qs_b, qs_h, qs_q, (const T*)pmin, (const T*)pmax, P_cap, Hq, Hkv, Sq, S, D, page_size,
         (const T*)bias, bias_s_b, bias_s_q, (T*)scores);
   });
   SAH_LAUNCH_CHECK("quest_scores");
@@ -194,6 +194,7 @@ __global__ void quest_expand_kernel(const uint32_t* __restrict__ page_bits, int6
                                     const uint32_t* __restrict__ prev_bits, const T* __restrict__ bias,
                                     int64_t bias_s_b, int64_t bias_s_q, int Hq, int Sq, int64_t S,
                                     int64_t W, int page_size, uint32_t* __restrict__ out_bits) {
+  sah_pdl_entry_early();
   const int64_t row = blockIdx.y;
   const int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (w >= W) return;
@@ -237,8 +238,7 @@ extern "C" int sah_quest_expand(const uint32_t* page_bits, int64_t Wp, const uin
   SAH_REQUIRE(rows <= 65535, "quest_expand: more than 65535 mask rows");
   dim3 grid((unsigned)sah_ceil_div(W, 256), (unsigned)rows);
   SAH_DISPATCH_DTYPE(dtype, T, {
-    quest_expand_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>(
-        page_bits, Wp, prev_bits, (const T*)bias, bias_s_b, bias_s_q, Hq, Sq, S, W, page_size, out_bits);
+    sah_launch_chain(quest_expand_kernel<T>, grid, 256, 0, (cudaStream_t)stream, page_bits, Wp, prev_bits, (const T*)bias, bias_s_b, bias_s_q, Hq, Sq, S, W, page_size, out_bits);
   });
   SAH_LAUNCH_CHECK("quest_expand");
   return SAH_OK;

@@ -96,6 +96,7 @@ struct AdaptiveArgs {
 template <typename T>
 __global__ void __launch_bounds__(1024)
 adaptive_budget_kernel(AdaptiveArgs a) {
+  sah_pdl_entry();
   extern __shared__ uint32_t ad_base_bits[];  // W words: distinct base-sample columns
   __shared__ float scratch[32];
   const int tid = threadIdx.x;
@@ -238,7 +239,7 @@ extern "C" int sah_adaptive_budget(const void* scores, int dtype, float scaling,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "adaptive_budget attr: %s", cudaGetErrorString(e));
     }
-    adaptive_budget_kernel<T><<<(unsigned)rows, 1024, smem, st>>>(a);
+    sah_launch_chain(adaptive_budget_kernel<T>, (unsigned)rows, 1024, smem, st, a);
   });
   SAH_LAUNCH_CHECK("adaptive_budget");
   sah_prof_end(SAH_PROF_ADAPTIVE, st);
@@ -252,6 +253,7 @@ __global__ void sample_scatter_kernel(const int64_t* __restrict__ sptr, int64_t 
                                       const int64_t* __restrict__ pool, uint64_t seed,
                                       int64_t start, int64_t n, int64_t S, int64_t W,
                                       uint32_t* __restrict__ bits) {
+  sah_pdl_entry_early();
   const int64_t total = sptr[rows];
   for (int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < total;
        j += (int64_t)gridDim.x * blockDim.x) {
@@ -272,8 +274,7 @@ extern "C" int sah_sample_scatter(const int64_t* sptr, int64_t rows, const int64
   SAH_REQUIRE(rows >= 0 && n > 0 && n < (1ll << 32) && W * 32 >= S, "sample_scatter: bad extents");
   if (rows == 0) return SAH_OK;
   if (sm_count <= 0) sm_count = 148;
-  sample_scatter_kernel<<<(unsigned)(sm_count * 8), 256, 0, (cudaStream_t)stream>>>(
-      sptr, rows, pool, seed, start, n, S, W, bits);
+  sah_launch_chain(sample_scatter_kernel, (unsigned)(sm_count * 8), 256, 0, (cudaStream_t)stream, sptr, rows, pool, seed, start, n, S, W, bits);
   SAH_LAUNCH_CHECK("sample_scatter");
   return SAH_OK;
 }

@@ -63,6 +63,7 @@ qk_scores_kernel(const T* __restrict__ q, const T* __restrict__ k, int64_t qs_b,
                  int64_t qs_q, int64_t ks_b, int64_t ks_h, int64_t ks_s, int Hq, int Hkv, int Sq,
                  int64_t S, int D_rt, const T* __restrict__ bias, int64_t bias_s_b,
                  int64_t bias_s_h, int64_t bias_s_q, T* __restrict__ scores) {
+  sah_pdl_entry();
   extern __shared__ __align__(16) float q_sm[];  // [R][D] queries, then the K tile
   const int D = DT ? DT : D_rt;
   const int G = Hq / Hkv;
@@ -183,7 +184,7 @@ extern "C" int sah_qk_scores(const void* q, const void* k, int dtype, int64_t qs
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
       if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "qk_scores attr: %s", cudaGetErrorString(e)); \
     }                                                                                               \
-    qk_scores_kernel<T, DT, F4><<<grid, QK_THREADS, smem, st>>>(                                    \
+    sah_launch_chain(qk_scores_kernel<T, DT, F4>, grid, QK_THREADS, smem, st, \
         (const T*)q, (const T*)k, qs_b, qs_h, qs_q, ks_b, ks_h, ks_s, Hq, Hkv, Sq, S, D,            \
         (const T*)bias, bias_s_b, bias_s_h, bias_s_q, (T*)scores);                                  \
   } while (0)
@@ -215,6 +216,7 @@ __global__ void __launch_bounds__(SAH_SELECT_THREADS)
 topk_select_kernel(const T* __restrict__ scores, int64_t S, int64_t W, int64_t col_begin,
                    int64_t col_end, const uint32_t* __restrict__ prev_bits, int64_t k,
                    uint32_t* __restrict__ out_bits) {
+  sah_pdl_entry();
   __shared__ SahSelectSmem sm;
   const int64_t row = blockIdx.x;
   ScoreKey<T, KEYBITS> kf{scores + row * S};
@@ -231,11 +233,9 @@ extern "C" int sah_topk_select(const void* scores, int dtype, int64_t rows, int6
   cudaStream_t st = (cudaStream_t)stream;
   sah_prof_begin(SAH_PROF_TOPK_SELECT, (cudaStream_t)stream);
   if (dtype == SAH_BF16) {
-    topk_select_kernel<__nv_bfloat16, 16><<<(unsigned)rows, SAH_SELECT_THREADS, 0, st>>>(
-        (const __nv_bfloat16*)scores, S, W, col_begin, col_end, prev_bits, k, out_bits);
+    sah_launch_chain(topk_select_kernel<__nv_bfloat16, 16>, (unsigned)rows, SAH_SELECT_THREADS, 0, st, (const __nv_bfloat16*)scores, S, W, col_begin, col_end, prev_bits, k, out_bits);
   } else if (dtype == SAH_F32) {
-    topk_select_kernel<float, 32><<<(unsigned)rows, SAH_SELECT_THREADS, 0, st>>>(
-        (const float*)scores, S, W, col_begin, col_end, prev_bits, k, out_bits);
+    sah_launch_chain(topk_select_kernel<float, 32>, (unsigned)rows, SAH_SELECT_THREADS, 0, st, (const float*)scores, S, W, col_begin, col_end, prev_bits, k, out_bits);
   } else {
     return sah_fail(SAH_ERR_INVALID, "topk_select: unknown dtype %d", dtype);
   }
@@ -291,6 +291,7 @@ static SelWorkspace sel_ws_carve(void* ws, int64_t rows, int64_t chunks) {
 }
 
 __global__ void sel_init_kernel(SelState* state, unsigned int* hist, int64_t rows, long long k) {
+  sah_pdl_entry_early();
   const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (t < rows * 256) hist[t] = 0u;
   if (t < rows) {
@@ -348,6 +349,7 @@ sel_hist_kernel(const T* __restrict__ scores, int64_t S, int64_t W, int64_t col_
                 const uint32_t* __restrict__ prev_bits, const SelState* __restrict__ state,
                 unsigned int* __restrict__ hist, unsigned int* __restrict__ chunk_hist, int64_t chunks,
                 int shift, int vec) {
+  sah_pdl_entry();
   __shared__ unsigned int hs[SEL_THREADS / 32][256];
   const int tid = threadIdx.x, warp = tid >> 5;
   const int64_t row = blockIdx.y, chunk = blockIdx.x;
@@ -379,6 +381,7 @@ __global__ void __launch_bounds__(256)
 sel_pick_kernel(SelState* __restrict__ state, unsigned int* __restrict__ hist, int shift, int first,
                 const unsigned int* __restrict__ chunk_hist, long long* __restrict__ chunk_before,
                 int64_t chunks, long long* __restrict__ eq_total_out) {
+  sah_pdl_entry_early();
   __shared__ long long scan[33];
   __shared__ int bin_sm;
   const int tid = threadIdx.x;
@@ -428,6 +431,7 @@ sel_emit_kernel(const T* __restrict__ scores, int64_t S, int64_t W, int64_t col_
                 const uint32_t* __restrict__ prev_bits, const SelState* __restrict__ state,
                 const long long* __restrict__ chunk_before, int64_t chunks, int vec,
                 const long long* __restrict__ tie_offset, uint32_t* __restrict__ out_bits) {
+  sah_pdl_entry();
   __shared__ long long scan[33];
   const int tid = threadIdx.x;
   const int64_t row = blockIdx.y, chunk = blockIdx.x;
@@ -530,6 +534,7 @@ __global__ void __launch_bounds__(SEL_THREADS)
 sel_fused_hist_kernel(const T* __restrict__ scores, int64_t S, int64_t W, int64_t col_begin, int64_t col_end,
                       const uint32_t* __restrict__ prev_bits, long long k, unsigned int* __restrict__ ch,
                       int64_t rows, int chunks, int64_t chunk_words, int digit, int vec) {
+  sah_pdl_entry_early();
   __shared__ unsigned int hs[SEL_THREADS / 32][256];
   __shared__ long long scan[33];
   __shared__ SelState st_sm;
@@ -568,6 +573,7 @@ __global__ void __launch_bounds__(SEL_THREADS)
 sel_fused_emit_kernel(const T* __restrict__ scores, int64_t S, int64_t W, int64_t col_begin, int64_t col_end,
                       const uint32_t* __restrict__ prev_bits, long long k, const unsigned int* __restrict__ ch,
                       int64_t rows, int chunks, int64_t chunk_words, int vec, uint32_t* __restrict__ out_bits) {
+  sah_pdl_entry_early();
   __shared__ long long scan[33];
   __shared__ SelState st_sm;
   __shared__ long long before_sm;
@@ -643,7 +649,7 @@ extern "C" int sah_topk_sel_begin(int64_t rows, int64_t W, int64_t k, void* work
   const int64_t chunks = (W + SEL_CHUNK_WORDS - 1) / SEL_CHUNK_WORDS;
   SelWorkspace o = sel_ws_carve(workspace, rows, chunks);
   cudaStream_t st = (cudaStream_t)stream;
-  sel_init_kernel<<<(unsigned)sah_ceil_div(rows * 256, 256), 256, 0, st>>>(o.state, o.hist, rows, k);
+  sah_launch_chain(sel_init_kernel, (unsigned)sah_ceil_div(rows * 256, 256), 256, 0, st, o.state, o.hist, rows, k);
   SAH_LAUNCH_CHECK("topk_select init");
   cudaMemsetAsync(o.chunk_before, 0, (size_t)rows * chunks * 8, st);
   return SAH_OK;
@@ -656,7 +662,7 @@ static int sel_hist_step(const T* scores, int64_t rows, int64_t S, int64_t W, in
   SelWorkspace o = sel_ws_carve(ws, rows, chunks);
   const int vec = ((S * (int64_t)sizeof(T)) % 16 == 0 && ((uintptr_t)scores % 16) == 0) ? 1 : 0;
   dim3 grid((unsigned)chunks, (unsigned)rows);
-  sel_hist_kernel<T, KEYBITS><<<grid, SEL_THREADS, 0, st>>>(scores, S, W, col_begin, col_end, prev_bits, o.state,
+  sah_launch_chain(sel_hist_kernel<T, KEYBITS>, grid, SEL_THREADS, 0, st, scores, S, W, col_begin, col_end, prev_bits, o.state,
                                                             o.hist, shift == 0 ? o.chunk_hist : nullptr, chunks,
                                                             shift, vec);
   SAH_LAUNCH_CHECK("topk_select hist");
@@ -688,8 +694,7 @@ extern "C" int sah_topk_sel_pick(int64_t rows, int64_t W, void* workspace, int s
   SAH_REQUIRE(workspace != nullptr && rows > 0, "topk_sel_pick: bad arguments");
   const int64_t chunks = (W + SEL_CHUNK_WORDS - 1) / SEL_CHUNK_WORDS;
   SelWorkspace o = sel_ws_carve(workspace, rows, chunks);
-  sel_pick_kernel<<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>(
-      o.state, o.hist, shift, first, shift == 0 ? o.chunk_hist : nullptr, o.chunk_before, chunks,
+  sah_launch_chain(sel_pick_kernel, (unsigned)rows, 256, 0, (cudaStream_t)stream, o.state, o.hist, shift, first, shift == 0 ? o.chunk_hist : nullptr, o.chunk_before, chunks,
       reinterpret_cast<long long*>(eq_total));
   SAH_LAUNCH_CHECK("topk_select pick");
   return SAH_OK;
@@ -703,7 +708,7 @@ static int sel_emit_step(const T* scores, int64_t rows, int64_t S, int64_t W, in
   SelWorkspace o = sel_ws_carve(ws, rows, chunks);
   const int vec = ((S * (int64_t)sizeof(T)) % 16 == 0 && ((uintptr_t)scores % 16) == 0) ? 1 : 0;
   dim3 grid((unsigned)chunks, (unsigned)rows);
-  sel_emit_kernel<T, KEYBITS><<<grid, SEL_THREADS, 0, st>>>(scores, S, W, col_begin, col_end, prev_bits, o.state,
+  sah_launch_chain(sel_emit_kernel<T, KEYBITS>, grid, SEL_THREADS, 0, st, scores, S, W, col_begin, col_end, prev_bits, o.state,
                                                             o.chunk_before, chunks, vec,
                                                             reinterpret_cast<const long long*>(tie_offset),
                                                             out_bits);
@@ -736,13 +741,11 @@ static int sel_run(const T* scores, int64_t rows, int64_t S, int64_t W, int64_t 
   dim3 grid((unsigned)g.chunks, (unsigned)rows);
   if (k > 0) {
     for (int digit = 0; digit < KEYBITS / 8; ++digit) {
-      sel_fused_hist_kernel<T, KEYBITS><<<grid, SEL_THREADS, 0, st>>>(
-          scores, S, W, col_begin, col_end, prev_bits, (long long)k, ch, rows, g.chunks, g.chunk_words, digit, vec);
+      sah_launch_chain(sel_fused_hist_kernel<T, KEYBITS>, grid, SEL_THREADS, 0, st, scores, S, W, col_begin, col_end, prev_bits, (long long)k, ch, rows, g.chunks, g.chunk_words, digit, vec);
       SAH_LAUNCH_CHECK("topk_select digit histogram");
     }
   }
-  sel_fused_emit_kernel<T, KEYBITS><<<grid, SEL_THREADS, 0, st>>>(
-      scores, S, W, col_begin, col_end, prev_bits, (long long)k, ch, rows, g.chunks, g.chunk_words, vec, out_bits);
+  sah_launch_chain(sel_fused_emit_kernel<T, KEYBITS>, grid, SEL_THREADS, 0, st, scores, S, W, col_begin, col_end, prev_bits, (long long)k, ch, rows, g.chunks, g.chunk_words, vec, out_bits);
   SAH_LAUNCH_CHECK("topk_select emit");
   return SAH_OK;
 }

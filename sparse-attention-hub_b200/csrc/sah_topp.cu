@@ -73,6 +73,7 @@ __device__ __forceinline__ bool tp_add_run(float& acc, float v, unsigned int cou
 
 __global__ void __launch_bounds__(TP_THREADS)
 topp_select_kernel(ToppArgs a) {
+  sah_pdl_entry();
   extern __shared__ unsigned int tp_hist[];   // [TP_BINS] counts, then the run-end sums
   __shared__ unsigned int nz[TP_WORDS];       // non-empty bins
   __shared__ float scratch[32];
@@ -197,7 +198,7 @@ extern "C" int sah_topp_select(const void* scores, int dtype, float scaling, con
   cudaError_t e = cudaFuncSetAttribute(topp_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "topp_select attr: %s", cudaGetErrorString(e));
   sah_prof_begin(SAH_PROF_TOPP, (cudaStream_t)stream);
-  topp_select_kernel<<<(unsigned)rows, TP_THREADS, smem, (cudaStream_t)stream>>>(a);
+  sah_launch_chain(topp_select_kernel, (unsigned)rows, TP_THREADS, smem, (cudaStream_t)stream, a);
   SAH_LAUNCH_CHECK("topp_select");
   sah_prof_end(SAH_PROF_TOPP, (cudaStream_t)stream);
   return SAH_OK;

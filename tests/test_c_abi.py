@@ -83,3 +83,26 @@ def test_plan_refuses_sizes_of_another_key_count():
     assert lib.sah_attn_query_sizes(1, 16, 2, 1, 4096, 128, 2, 148, ctypes.byref(wide)) == 0
     assert lib.sah_attn_plan_lsh(one, None, one, 4096, one, 1, 16, 2, 1, 4096, 128,
                                  ctypes.byref(wide), one, one, one, one, None) == 2
+
+
+def test_every_chained_launch_names_a_kernel_that_waits_for_its_predecessors():
+    """`sah_launch_chain` sets the programmatic-stream-serialization attribute, which lets a grid
+    start before the kernel in front of it has finished; that is only sound when the kernel's
+    first statement is `sah_pdl_entry()` (the hardware wait for the predecessors).  Read from the
+    sources: every kernel that is launched that way begins with it."""
+    csrc = HEADER.parent.parent / "sparse-attention-hub_b200" / "csrc"
+    text = "\n".join(p.read_text() for p in sorted(csrc.glob("*.cu*")))
+    launched = set(re.findall(r"sah_launch_chain\(\s*([A-Za-z0-9_]+)\s*[<,]", text))
+    launched.discard("kernel")  # the helper's own parameter
+    assert len(launched) > 40
+    for name in sorted(launched):
+        m = re.search(r"__global__[^;{]*?\b" + name + r"\s*\(", text)
+        assert m, name
+        depth, i = 1, m.end()
+        while depth:
+            depth += {"(": 1, ")": -1}.get(text[i], 0)
+            i += 1
+        body = text[text.index("{", i) + 1:]
+        assert body.lstrip().startswith(("sah_pdl_entry();", "sah_pdl_entry_early();")), name
+    # and nothing else sets the attribute
+    assert text.count("cudaLaunchAttributeProgrammaticStreamSerialization") == 1
