@@ -489,8 +489,10 @@ static const char* g_last_attn_kernel = "none";
 
 template <typename T, int D, int NQUAD>
 __global__ void __launch_bounds__(AT_THREADS)
-masked_attention_kernel(AttnArgs a) {
+masked_attention_kernel(AttnArgs a, int* __restrict__ tickets, const float* __restrict__ sinks,
+                        T* __restrict__ out, float* __restrict__ part_out) {
   sah_pdl_entry();
+  __shared__ int is_last_sm;
   using C = AttnCfg<T, D>;
   constexpr int RP = NQUAD * 4;  // padded row count
   extern __shared__ __align__(128) unsigned char at_smem[];
@@ -771,60 +773,15 @@ masked_attention_kernel(AttnArgs a) {
     pout[tid * (D + 2) + D] = m_sm[tid];
     pout[tid * (D + 2) + D + 1] = l_sm[tid];
   }
-}
-
-// Merge the nsplit partials of every row; one CTA of D threads per (group, row).
-template <typename T>
-__global__ void attn_merge_splits_kernel(const float* __restrict__ partial, int nsplit, int R,
-                                         int D, int Hq, int Hkv, int Sq, int G, int q_block,
-                                         int nqb, const float* __restrict__ sinks,
-                                         T* __restrict__ out, float* __restrict__ part_out) {
-  sah_pdl_entry_early();
-  const int64_t g = blockIdx.x / R;
-  const int r = (int)(blockIdx.x % R);
-  const int qb = (int)(g % nqb);
-  const int64_t bk = g / nqb;
-  const int kvh = (int)(bk % Hkv);
-  const int64_t b = bk / Hkv;
-  const int gi = r / q_block, qo = r - gi * q_block;
-  const int qi = qb * q_block + qo;
-  if (qi >= Sq) return;
-  const int h = kvh * G + gi;
-  const float* p0 = partial + ((int64_t)g * nsplit) * R * (D + 2) + (int64_t)r * (D + 2);
-  const int64_t pstride = (int64_t)R * (D + 2);
-  float M = -INFINITY;
-  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, p0[s * pstride + D]);
-  float L = 0.f;
-  for (int s = 0; s < nsplit; ++s) {
-    float ms = p0[s * pstride + D];
-    if (ms != -INFINITY) L += p0[s * pstride + D + 1] * expf(ms - M);
-  }
-  const int64_t row = (b * Hq + h) * Sq + qi;
-  float Mx = M, sink_term = 0.f;
-  if (sinks != nullptr) {
-    const float sk = sinks[h];
-    Mx = fmaxf(M, sk);
-    sink_term = expf(sk - Mx);
-  }
-  const float resc = (M == -INFINITY) ? 0.f : expf(M - Mx);
-  const float den = L * resc + sink_term;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float accv = 0.f;
-    for (int s = 0; s < nsplit; ++s) {
-      float ms = p0[s * pstride + D];
-      if (ms != -INFINITY) accv += p0[s * pstride + d] * expf(ms - M);
-    }
-    if (part_out != nullptr) part_out[row * (D + 2) + d] = accv;
-    out[((b * Sq + qi) * Hq + h) * D + d] = sah_from_float<T>(accv * resc / den);
-  }
-  if (part_out != nullptr && threadIdx.x == 0) {
-    part_out[row * (D + 2) + D] = M;
-    part_out[row * (D + 2) + D + 1] = L;
-  }
+  // the last CTA of the group to get here merges the splits and writes the output rows (every
+  // CTA of the grid writes a partial, an empty one included)
+  __syncthreads();  // the reduction buffer is read no more: it becomes the merge scratch
+  atm_finish_group<D, AT_THREADS, T>(a, g, a.nsplit, stage_base, &is_last_sm, tickets, sinks, out, part_out);
 }
 
 template <typename T, int D>
-static int launch_attention(const AttnArgs& a, int groups, cudaStream_t st) {
+static int launch_attention(const AttnArgs& a, int groups, int* tickets, const float* sinks, void* out,
+                            float* part_out, cudaStream_t st) {
   using C = AttnCfg<T, D>;
   const int nquad = (a.R + 3) / 4;
   const int RP = nquad * 4;
@@ -833,7 +790,8 @@ static int launch_attention(const AttnArgs& a, int groups, cudaStream_t st) {
                                  (size_t)C::TILE * RP + 3 * RP) +
                 sizeof(int) * AT_STAGES * C::TILE;
   size_t red = sizeof(float) * 4 * RP * D;
-  if (red > (size_t)AT_STAGES * C::STAGE_BYTES)
+  if (red > (size_t)AT_STAGES * C::STAGE_BYTES ||
+      sizeof(float) * (16 * (size_t)a.nsplit + 32) > (size_t)AT_STAGES * C::STAGE_BYTES)
     return sah_fail(SAH_ERR_UNSUPPORTED, "attention: reduction buffer does not fit");
   dim3 grid((unsigned)a.nsplit, (unsigned)groups);
 #define SAH_AT_LAUNCH(NQ)                                                                        \
@@ -841,7 +799,7 @@ static int launch_attention(const AttnArgs& a, int groups, cudaStream_t st) {
     cudaError_t e = cudaFuncSetAttribute(masked_attention_kernel<T, D, NQ>,                      \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "attention attr: %s", cudaGetErrorString(e)); \
-    sah_launch_chain(masked_attention_kernel<T, D, NQ>, grid, AT_THREADS, smem, st, a);                         \
+    sah_launch_chain(masked_attention_kernel<T, D, NQ>, grid, AT_THREADS, smem, st, a, tickets, sinks, (T*)out, part_out);                         \
   }
   switch (nquad) {
     case 1: SAH_AT_LAUNCH(1) break;
@@ -938,16 +896,14 @@ static int masked_attention_impl(const void* q, const void* k, const void* v, in
   if (dtype != SAH_F32) return sah_fail(SAH_ERR_INVALID, "masked_attention: unknown dtype %d", dtype);
   if (lsh != nullptr)
     return sah_fail(SAH_ERR_UNSUPPORTED, "masked_attention_lsh: bfloat16 only");
-  rc = (D == 128) ? launch_attention<float, 128>(a, groups, st)
-                  : launch_attention<float, 64>(a, groups, st);
+  // the split merge is fused into the kernel here too (ticket per group, as in bfloat16)
+  int* tickets32 = const_cast<int*>(ucount) + groups + (int64_t)groups * plan_chunks(S);
+  rc = (D == 128) ? launch_attention<float, 128>(a, groups, tickets32, sinks, out, part_out, st)
+                  : launch_attention<float, 64>(a, groups, tickets32, sinks, out, part_out, st);
   if (rc != SAH_OK) return rc;
   g_last_attn_kernel = "masked_attention_kernel";
   SAH_LAUNCH_CHECK("masked_attention");
   sah_prof_end(SAH_PROF_ATTENTION, (cudaStream_t)stream);
-  sah_prof_begin(SAH_PROF_ATTN_MERGE, (cudaStream_t)stream);
-  sah_launch_chain(attn_merge_splits_kernel<float>, (unsigned)(groups * a.R), D, 0, st, partial, a.nsplit, a.R, D, Hq, Hkv, Sq, a.G, a.q_block, a.nqb, sinks, (float*)out, part_out);
-  SAH_LAUNCH_CHECK("attn_merge_splits");
-  sah_prof_end(SAH_PROF_ATTN_MERGE, (cudaStream_t)stream);
   return SAH_OK;
 }
 

@@ -159,11 +159,18 @@ __device__ __forceinline__ float atm_lsh_weight(float dot_hat, float qmu, float 
 // `part_out` is given, the group's merged partial for a merge across sequence shards).
 // Called by all NT threads of the CTA; `scratch` is shared memory the CTA no longer needs
 // (16 * active + 32 floats).
-template <int D, int NT>
+__device__ __forceinline__ void atm_store2(__nv_bfloat16* p, float x, float y) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(x, y);
+}
+__device__ __forceinline__ void atm_store2(float* p, float x, float y) {
+  *reinterpret_cast<float2*>(p) = make_float2(x, y);
+}
+
+template <int D, int NT, typename OutT>
 __device__ __forceinline__ void atm_finish_group(const AttnArgs& a, int64_t g, int active,
                                                  unsigned char* scratch, int* is_last_sm,
                                                  int* __restrict__ tickets, const float* __restrict__ sinks,
-                                                 __nv_bfloat16* __restrict__ out,
+                                                 OutT* __restrict__ out,
                                                  float* __restrict__ part_out) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int qb = (int)(g % a.nqb);
@@ -236,8 +243,7 @@ __device__ __forceinline__ void atm_finish_group(const AttnArgs& a, int64_t g, i
     const float den = L * resc + sink_term;
     const int64_t row = (b * a.Hq + h) * a.Sq + qi;
     if (part_out != nullptr) *reinterpret_cast<float2*>(part_out + row * (D + 2) + d) = accv;
-    *reinterpret_cast<__nv_bfloat162*>(out + ((b * a.Sq + qi) * a.Hq + h) * D + d) =
-        __floats2bfloat162_rn(accv.x * resc / den, accv.y * resc / den);
+    atm_store2(out + ((b * a.Sq + qi) * a.Hq + h) * D + d, accv.x * resc / den, accv.y * resc / den);
     if (part_out != nullptr && d == 0) {
       part_out[row * (D + 2) + D] = M;
       part_out[row * (D + 2) + D + 1] = L;
@@ -686,7 +692,7 @@ masked_attention_mma_kernel(AttnArgs a, const __grid_constant__ AtmMaps maps, in
     }
   }
 
-  atm_finish_group<D, ATM_THREADS>(a, g, active, atm_smem, &is_last_sm, tickets, sinks, out, part_out);
+  atm_finish_group<D, ATM_THREADS, __nv_bfloat16>(a, g, active, atm_smem, &is_last_sm, tickets, sinks, out, part_out);
 }
 
 // Row-gather probe: the copy half of the attention kernel alone.  Same grid, same dealing of

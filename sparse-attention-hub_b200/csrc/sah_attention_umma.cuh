@@ -577,7 +577,7 @@ masked_attention_umma_kernel(AttnArgs a, int* __restrict__ tickets, int* __restr
     aum_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(AUM_TMEM_COLS));
   }
-  atm_finish_group<D, AUM_THREADS>(a, g, active, sm, is_last_sm, tickets, sinks, out, part_out);
+  atm_finish_group<D, AUM_THREADS, __nv_bfloat16>(a, g, active, sm, is_last_sm, tickets, sinks, out, part_out);
 }
 
 // Which problems take the tcgen05 kernel when neither the caller nor the environment says.
