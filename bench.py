@@ -69,7 +69,7 @@ REFERENCE_LONG_KEYS = 16384
 # gathered).
 NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {
     "hashattention": (221809920.0 + 4204032.0) / 219225088.0,        # masked_attention_mma_kernel
-    "magicpig:attention": (200355072.0 + 3793664.0) / 196420096.0,   # masked_attention_umma_kernel
+    "magicpig:attention": (200350976.0 + 4377856.0) / 196420096.0,   # masked_attention_umma_kernel
 }
 
 
