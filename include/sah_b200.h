@@ -475,7 +475,8 @@ int sah_lsh_query(const void* q, int dtype, int64_t qs_b, int64_t qs_h, int64_t 
 /* out_bits[row][w]: keys whose code equals the query's in at least one table
  * (_compute_matches_int64, :455-463), joined with prev_bits[row][w] when prev_bits is
  * not NULL (the active set of the dense merge with the previous mask, :593).  Every
- * word of every row is written. */
+ * word that holds keys (w < ceil(S / 32)) of every row is written; padding words of the
+ * row stride W are left as they are. */
 int sah_lsh_match(const void* codes, int64_t cap, const void* qcodes, int B, int Hq, int Sq, int G,
                   int L, int K, int64_t S, int64_t W, const uint32_t* prev_bits, uint32_t* out_bits,
                   void* stream);
