@@ -374,9 +374,11 @@ extern "C" int sah_attn_plan(const uint32_t* bits, const void* data, const int32
     const dim3 fgrid((unsigned)groups, (unsigned)sah_ceil_div(p.Wv, PLAN_FUSED_THREADS));
     SAH_DISPATCH_DTYPE(dtype, T, {
       if (p.R <= 4)
-        sah_launch_chain(attn_plan_fused_kernel<T, 4>, fgrid, PLAN_FUSED_THREADS, 0, st, bits, (const T*)data, wpre, ptr, p, ucols, umemb, data ? uw : nullptr, ucount);
+        sah_launch_chain(attn_plan_fused_kernel<T, 4>, fgrid, PLAN_FUSED_THREADS, 0, st, bits, (const T*)data,
+            wpre, ptr, p, ucols, umemb, data ? uw : nullptr, ucount);
       else
-        sah_launch_chain(attn_plan_fused_kernel<T, AT_MAXR>, fgrid, PLAN_FUSED_THREADS, 0, st, bits, (const T*)data, wpre, ptr, p, ucols, umemb, data ? uw : nullptr, ucount);
+        sah_launch_chain(attn_plan_fused_kernel<T, AT_MAXR>, fgrid, PLAN_FUSED_THREADS, 0, st, bits,
+            (const T*)data, wpre, ptr, p, ucols, umemb, data ? uw : nullptr, ucount);
     });
     SAH_LAUNCH_CHECK("attn_plan_fused");
     sah_prof_end(SAH_PROF_ATTN_PLAN, (cudaStream_t)stream);
@@ -387,10 +389,12 @@ extern "C" int sah_attn_plan(const uint32_t* bits, const void* data, const int32
   const int64_t eblocks = sah_ceil_div(warps, PLAN_EMIT_WARPS);
   SAH_DISPATCH_DTYPE(dtype, T, {
     if (p.R <= 4)
-      sah_launch_chain(attn_plan_emit_kernel<T, 4, false>, (unsigned)eblocks, PLAN_EMIT_WARPS * 32, 0, st, bits, nullptr, (const T*)data, wpre, ptr, nullptr, 0, nullptr, p, chunkcnt, ucols, umemb,
+      sah_launch_chain(attn_plan_emit_kernel<T, 4, false>, (unsigned)eblocks, PLAN_EMIT_WARPS * 32, 0, st,
+          bits, nullptr, (const T*)data, wpre, ptr, nullptr, 0, nullptr, p, chunkcnt, ucols, umemb,
           data ? uw : nullptr, ucount);
     else
-      sah_launch_chain(attn_plan_emit_kernel<T, AT_MAXR, false>, (unsigned)eblocks, PLAN_EMIT_WARPS * 32, 0, st, bits, nullptr, (const T*)data, wpre, ptr, nullptr, 0, nullptr, p, chunkcnt, ucols, umemb,
+      sah_launch_chain(attn_plan_emit_kernel<T, AT_MAXR, false>, (unsigned)eblocks, PLAN_EMIT_WARPS * 32, 0,
+          st, bits, nullptr, (const T*)data, wpre, ptr, nullptr, 0, nullptr, p, chunkcnt, ucols, umemb,
           data ? uw : nullptr, ucount);
   });
   SAH_LAUNCH_CHECK("attn_plan_emit");
@@ -422,8 +426,8 @@ extern "C" int sah_attn_plan_lsh(const uint32_t* bits, const uint32_t* unit_bits
   sah_launch_chain(attn_plan_count_kernel, (unsigned)blocks, threads, 0, st, bits, unit_bits, p, chunkcnt);
   SAH_LAUNCH_CHECK("attn_plan_count");
   sah_launch_chain(attn_plan_emit_kernel<float, 4, true>, (unsigned)sah_ceil_div(warps, PLAN_EMIT_WARPS),
-                                          PLAN_EMIT_WARPS * 32, 0, st, bits, unit_bits, nullptr, nullptr, nullptr, dens, dens_cap, max_norm_bits, p, chunkcnt, ucols,
-      umemb, uinv, ucount);
+                   PLAN_EMIT_WARPS * 32, 0, st, bits, unit_bits, nullptr, nullptr, nullptr, dens, dens_cap,
+                   max_norm_bits, p, chunkcnt, ucols, umemb, uinv, ucount);
   SAH_LAUNCH_CHECK("attn_plan_emit_lsh");
   sah_prof_end(SAH_PROF_ATTN_PLAN, st);
   return SAH_OK;
@@ -799,7 +803,8 @@ static int launch_attention(const AttnArgs& a, int groups, int* tickets, const f
     cudaError_t e = cudaFuncSetAttribute(masked_attention_kernel<T, D, NQ>,                      \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "attention attr: %s", cudaGetErrorString(e)); \
-    sah_launch_chain(masked_attention_kernel<T, D, NQ>, grid, AT_THREADS, smem, st, a, tickets, sinks, (T*)out, part_out);                         \
+    sah_launch_chain(masked_attention_kernel<T, D, NQ>, grid, AT_THREADS, smem, st, a, tickets, sinks, \
+        (T*)out, part_out); \
   }
   switch (nquad) {
     case 1: SAH_AT_LAUNCH(1) break;
@@ -1080,7 +1085,8 @@ extern "C" int sah_attn_merge_parts(const float* parts, int n_parts, int B, int 
   const int64_t rows = (int64_t)B * Hq * Sq;
   int threads = D < 32 ? 32 : (D > 256 ? 256 : D);
   SAH_DISPATCH_DTYPE(dtype, T, {
-    sah_launch_chain(attn_merge_parts_kernel<T>, (unsigned)rows, threads, 0, (cudaStream_t)stream, parts, n_parts, rows, Hq, Sq, D, sinks, (T*)out);
+    sah_launch_chain(attn_merge_parts_kernel<T>, (unsigned)rows, threads, 0, (cudaStream_t)stream, parts,
+        n_parts, rows, Hq, Sq, D, sinks, (T*)out);
   });
   SAH_LAUNCH_CHECK("attn_merge_parts");
   return SAH_OK;

@@ -871,10 +871,12 @@ extern "C" int sah_hash_topk(const uint32_t* kcodes, int64_t kc_stride, const ui
       sah_launch_chain(hash_topk_fast_kernel, (unsigned)rows, 1024, 0, st, kcodes, kc_stride, qcodes, nbits, Sq, S,
                                                             W, prev_bits, k, out_bits);
   } else if (dtype == SAH_BF16) {
-    sah_launch_chain(hash_topk_kernel<__nv_bfloat16, 16, true>, (unsigned)rows, SAH_SELECT_THREADS, 0, st, kcodes, kc_stride, qcodes, nbits, (const __nv_bfloat16*)bias, bias_s_b, bias_s_h, bias_s_q, Hq, Sq,
+    sah_launch_chain(hash_topk_kernel<__nv_bfloat16, 16, true>, (unsigned)rows, SAH_SELECT_THREADS, 0, st,
+        kcodes, kc_stride, qcodes, nbits, (const __nv_bfloat16*)bias, bias_s_b, bias_s_h, bias_s_q, Hq, Sq,
         S, W, prev_bits, k, out_bits);
   } else if (dtype == SAH_F32) {
-    sah_launch_chain(hash_topk_kernel<float, 32, true>, (unsigned)rows, SAH_SELECT_THREADS, 0, st, kcodes, kc_stride, qcodes, nbits, (const float*)bias, bias_s_b, bias_s_h, bias_s_q, Hq, Sq, S, W,
+    sah_launch_chain(hash_topk_kernel<float, 32, true>, (unsigned)rows, SAH_SELECT_THREADS, 0, st, kcodes,
+        kc_stride, qcodes, nbits, (const float*)bias, bias_s_b, bias_s_h, bias_s_q, Hq, Sq, S, W,
         prev_bits, k, out_bits);
   } else {
     return sah_fail(SAH_ERR_INVALID, "hash_topk: unknown dtype %d", dtype);
@@ -1096,7 +1098,8 @@ extern "C" int sah_hash_shard_plan(const int32_t* hist_all, int world, int rank,
   SAH_REQUIRE(hist_all && thr && need, "hash_shard_plan: null pointer");
   SAH_REQUIRE(world > 0 && rank >= 0 && rank < world && rows > 0 && chunks >= 1,
               "hash_shard_plan: bad extents");
-  sah_launch_chain(hash_shard_plan_kernel, (unsigned)sah_ceil_div(rows * chunks, 4), 128, 0, (cudaStream_t)stream, hist_all, world, rank, chunks, rows, k, thr, need);
+  sah_launch_chain(hash_shard_plan_kernel, (unsigned)sah_ceil_div(rows * chunks, 4), 128, 0,
+      (cudaStream_t)stream, hist_all, world, rank, chunks, rows, k, thr, need);
   SAH_LAUNCH_CHECK("hash_shard_plan");
   return SAH_OK;
 }
@@ -1270,7 +1273,8 @@ extern "C" int sah_hash_topk_ws(const uint32_t* kcodes, int64_t kc_stride, const
   {
     // every emit CTA derives its threshold and tie share from the chunk histograms itself
     dim3 grid((unsigned)rows, (unsigned)chunks);
-    sah_launch_chain(hash_emit_kernel, grid, HP_THREADS, 0, (cudaStream_t)stream, kcodes, kc_stride, qcodes, nbits, Sq, S, W, hash_chunk_words(W, chunks), prev_bits, rows, nullptr,
+    sah_launch_chain(hash_emit_kernel, grid, HP_THREADS, 0, (cudaStream_t)stream, kcodes, kc_stride, qcodes,
+        nbits, Sq, S, W, hash_chunk_words(W, chunks), prev_bits, rows, nullptr,
         nullptr, hist, chunks, k, reinterpret_cast<const uint4*>(scores), out_bits);
     SAH_LAUNCH_CHECK("hash_topk_ws emit");
   }

@@ -144,7 +144,8 @@ extern "C" int sah_lsh_key_stats(const void* keys, int dtype, int64_t ks_b, int6
   if (gx > cap_x) gx = cap_x;
   dim3 grid((unsigned)gx, (unsigned)(B * Hkv));
   SAH_DISPATCH_DTYPE(dtype, T, {
-    sah_launch_chain(lsh_key_stats_kernel<T>, grid, 256, 0, (cudaStream_t)stream, reinterpret_cast<const T*>(keys), ks_b, ks_h, ks_s, Hkv, s0, s1, D,
+    sah_launch_chain(lsh_key_stats_kernel<T>, grid, 256, 0, (cudaStream_t)stream,
+        reinterpret_cast<const T*>(keys), ks_b, ks_h, ks_s, Hkv, s0, s1, D,
         reinterpret_cast<const T*>(mean), cap, norms, max_norm_bits);
   });
   SAH_LAUNCH_CHECK("lsh_key_stats");
@@ -496,11 +497,13 @@ extern "C" int sah_lsh_query(const void* q, int dtype, int64_t qs_b, int64_t qs_
   cudaStream_t st = (cudaStream_t)stream;
   SAH_DISPATCH_DTYPE(dtype, T, {
     if (K <= 8)
-      sah_launch_chain(lsh_query_kernel<T, uint8_t>, (unsigned)rows, 256, smem, st, reinterpret_cast<const T*>(q), qs_b, qs_h, qs_q, Hq, Sq, G, D,
+      sah_launch_chain(lsh_query_kernel<T, uint8_t>, (unsigned)rows, 256, smem, st,
+          reinterpret_cast<const T*>(q), qs_b, qs_h, qs_q, Hq, Sq, G, D,
           reinterpret_cast<const T*>(mean), reinterpret_cast<const T*>(proj), L, K,
           reinterpret_cast<uint8_t*>(qcodes), qunit, reinterpret_cast<T*>(qhat), qmu);
     else
-      sah_launch_chain(lsh_query_kernel<T, uint16_t>, (unsigned)rows, 256, smem, st, reinterpret_cast<const T*>(q), qs_b, qs_h, qs_q, Hq, Sq, G, D,
+      sah_launch_chain(lsh_query_kernel<T, uint16_t>, (unsigned)rows, 256, smem, st,
+          reinterpret_cast<const T*>(q), qs_b, qs_h, qs_q, Hq, Sq, G, D,
           reinterpret_cast<const T*>(mean), reinterpret_cast<const T*>(proj), L, K,
           reinterpret_cast<uint16_t*>(qcodes), qunit, reinterpret_cast<T*>(qhat), qmu);
   });

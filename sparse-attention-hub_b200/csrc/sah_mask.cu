@@ -132,7 +132,8 @@ extern "C" int sah_mask_fill_band(uint32_t* bits, int64_t rows, int Sq, int64_t 
   int64_t total = rows * w_count;
   int threads = 256;
   int64_t blocks = sah_ceil_div(total, threads);
-  sah_launch_chain(mask_fill_band_kernel, (unsigned)blocks, threads, 0, (cudaStream_t)stream, bits, rows, Sq, S, W, w_begin, w_count, lo_base, lo_qstep, hi_base, hi_qstep, value);
+  sah_launch_chain(mask_fill_band_kernel, (unsigned)blocks, threads, 0, (cudaStream_t)stream, bits, rows, Sq,
+      S, W, w_begin, w_count, lo_base, lo_qstep, hi_base, hi_qstep, value);
   SAH_LAUNCH_CHECK("mask_fill_band");
   return SAH_OK;
 }
@@ -191,7 +192,8 @@ extern "C" int sah_mask_fill_bands(uint32_t* bits, int64_t rows, int Sq, int64_t
     mb.value[i] = on ? (int)bands[5 * i + 4] : 0;
   }
   const int64_t total = rows * W;
-  sah_launch_chain(mask_fill_bands_kernel, (unsigned)sah_ceil_div(total, 256), 256, 0, (cudaStream_t)stream, bits, rows, Sq, S, W, mb, init_zero);
+  sah_launch_chain(mask_fill_bands_kernel, (unsigned)sah_ceil_div(total, 256), 256, 0, (cudaStream_t)stream,
+      bits, rows, Sq, S, W, mb, init_zero);
   SAH_LAUNCH_CHECK("mask_fill_bands");
   return SAH_OK;
 }
@@ -499,7 +501,8 @@ extern "C" int sah_mask_unit_data(const uint32_t* bits, const uint32_t* unit_bit
   SAH_REQUIRE(data != nullptr, "unit_data: data is null");
   const int64_t total = rows * W;
   SAH_DISPATCH_DTYPE(dtype, T, {
-    sah_launch_chain(mask_unit_data_kernel<T>, (unsigned)sah_ceil_div(total, 256), 256, 0, (cudaStream_t)stream, bits, unit_bits, wpre, ptr, rows, W, (T*)data);
+    sah_launch_chain(mask_unit_data_kernel<T>, (unsigned)sah_ceil_div(total, 256), 256, 0,
+        (cudaStream_t)stream, bits, unit_bits, wpre, ptr, rows, W, (T*)data);
   });
   SAH_LAUNCH_CHECK("mask_unit_data");
   return SAH_OK;
@@ -560,9 +563,11 @@ extern "C" int sah_mask_rowwise_scatter(const int64_t* idx, const void* vals, in
   cudaError_t e = cudaMemsetAsync(claims, 0, (size_t)(rows * S) * sizeof(unsigned long long), st);
   if (e != cudaSuccess) return sah_fail(SAH_ERR_CUDA, "rowwise_scatter: memset: %s", cudaGetErrorString(e));
   SAH_DISPATCH_DTYPE(dtype, T, {
-    sah_launch_chain(mask_rowwise_claim_kernel<T>, (unsigned)sah_ceil_div(rows * k, 256), 256, 0, st, idx, (const T*)vals, rows, k, S, (unsigned long long*)claims);
+    sah_launch_chain(mask_rowwise_claim_kernel<T>, (unsigned)sah_ceil_div(rows * k, 256), 256, 0, st, idx,
+        (const T*)vals, rows, k, S, (unsigned long long*)claims);
     SAH_LAUNCH_CHECK("mask_rowwise_claim");
-    sah_launch_chain(mask_rowwise_settle_kernel<T>, (unsigned)sah_ceil_div(rows * S, 256), 256, 0, st, (const unsigned long long*)claims, rows * S, (T*)dense);
+    sah_launch_chain(mask_rowwise_settle_kernel<T>, (unsigned)sah_ceil_div(rows * S, 256), 256, 0, st,
+        (const unsigned long long*)claims, rows * S, (T*)dense);
   });
   SAH_LAUNCH_CHECK("mask_rowwise_settle");
   return SAH_OK;
@@ -599,7 +604,8 @@ extern "C" int sah_mask_flat_add(const int64_t* flat_idx, const void* vals, int 
   if (n == 0) return SAH_OK;
   SAH_REQUIRE(flat_idx != nullptr, "flat_add: indices are null");
   SAH_DISPATCH_DTYPE(dtype, T, {
-    sah_launch_chain(mask_flat_add_kernel<T>, (unsigned)sah_ceil_div(n, 256), 256, 0, (cudaStream_t)stream, flat_idx, (const T*)vals, n, total, acc);
+    sah_launch_chain(mask_flat_add_kernel<T>, (unsigned)sah_ceil_div(n, 256), 256, 0, (cudaStream_t)stream,
+        flat_idx, (const T*)vals, n, total, acc);
   });
   SAH_LAUNCH_CHECK("mask_flat_add");
   return SAH_OK;
@@ -609,7 +615,8 @@ extern "C" int sah_mask_clamp_to_dense(const float* acc, int dtype, int64_t tota
                                        void* stream) {
   SAH_REQUIRE(acc && dense && total > 0, "clamp_to_dense: bad argument");
   SAH_DISPATCH_DTYPE(dtype, T, {
-    sah_launch_chain(mask_clamp_kernel<T>, (unsigned)sah_ceil_div(total, 256), 256, 0, (cudaStream_t)stream, acc, total, (T*)dense);
+    sah_launch_chain(mask_clamp_kernel<T>, (unsigned)sah_ceil_div(total, 256), 256, 0, (cudaStream_t)stream,
+        acc, total, (T*)dense);
   });
   SAH_LAUNCH_CHECK("mask_clamp");
   return SAH_OK;
@@ -727,7 +734,8 @@ extern "C" int sah_mask_merge_bits(const uint32_t* a_bits, const void* a_data, c
   if (rows == 0 || W == 0) return SAH_OK;
   MergeSide a{a_bits, a_data, a_wpre, a_ptr}, b{b_bits, b_data, b_wpre, b_ptr};
   SAH_DISPATCH_DTYPE(dtype, T, {
-    sah_launch_chain(mask_merge_bits_kernel<T>, (unsigned)sah_ceil_div(rows * W, 256), 256, 0, (cudaStream_t)stream, a, b, rows, W, out_bits);
+    sah_launch_chain(mask_merge_bits_kernel<T>, (unsigned)sah_ceil_div(rows * W, 256), 256, 0,
+        (cudaStream_t)stream, a, b, rows, W, out_bits);
   });
   SAH_LAUNCH_CHECK("mask_merge_bits");
   return SAH_OK;
@@ -745,7 +753,8 @@ extern "C" int sah_mask_merge_data(const uint32_t* a_bits, const void* a_data, c
   if (rows == 0 || W == 0) return SAH_OK;
   MergeSide a{a_bits, a_data, a_wpre, a_ptr}, b{b_bits, b_data, b_wpre, b_ptr};
   SAH_DISPATCH_DTYPE(dtype, T, {
-    sah_launch_chain(mask_merge_data_kernel<T>, (unsigned)sah_ceil_div(rows * W, 256), 256, 0, (cudaStream_t)stream, a, b, rows, W, out_bits, out_wpre, out_ptr, reinterpret_cast<T*>(out_data));
+    sah_launch_chain(mask_merge_data_kernel<T>, (unsigned)sah_ceil_div(rows * W, 256), 256, 0,
+        (cudaStream_t)stream, a, b, rows, W, out_bits, out_wpre, out_ptr, reinterpret_cast<T*>(out_data));
   });
   SAH_LAUNCH_CHECK("mask_merge_data");
   return SAH_OK;

@@ -180,7 +180,8 @@ extern "C" int sah_quest_scores(const void* q, int dtype, int64_t qs_b, int64_t 
   dim3 grid((unsigned)sah_ceil_div(P, QS_THREADS), (unsigned)rows);
   sah_prof_begin(SAH_PROF_QUEST, (cudaStream_t)stream);
   SAH_DISPATCH_DTYPE(dtype, T, {
-    sah_launch_chain(quest_scores_kernel<T>, grid, QS_THREADS, 0, (cudaStream_t)stream, (const T*)q, qs_b, qs_h, qs_q, (const T*)pmin, (const T*)pmax, P_cap, Hq, Hkv, Sq, S, D, page_size,
+    sah_launch_chain(quest_scores_kernel<T>, grid, QS_THREADS, 0, (cudaStream_t)stream, (const T*)q, qs_b,
+        qs_h, qs_q, (const T*)pmin, (const T*)pmax, P_cap, Hq, Hkv, Sq, S, D, page_size,
         (const T*)bias, bias_s_b, bias_s_q, (T*)scores);
   });
   SAH_LAUNCH_CHECK("quest_scores");
@@ -238,7 +239,8 @@ extern "C" int sah_quest_expand(const uint32_t* page_bits, int64_t Wp, const uin
   SAH_REQUIRE(rows <= 65535, "quest_expand: more than 65535 mask rows");
   dim3 grid((unsigned)sah_ceil_div(W, 256), (unsigned)rows);
   SAH_DISPATCH_DTYPE(dtype, T, {
-    sah_launch_chain(quest_expand_kernel<T>, grid, 256, 0, (cudaStream_t)stream, page_bits, Wp, prev_bits, (const T*)bias, bias_s_b, bias_s_q, Hq, Sq, S, W, page_size, out_bits);
+    sah_launch_chain(quest_expand_kernel<T>, grid, 256, 0, (cudaStream_t)stream, page_bits, Wp, prev_bits,
+        (const T*)bias, bias_s_b, bias_s_q, Hq, Sq, S, W, page_size, out_bits);
   });
   SAH_LAUNCH_CHECK("quest_expand");
   return SAH_OK;

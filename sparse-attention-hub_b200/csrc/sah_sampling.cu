@@ -274,7 +274,8 @@ extern "C" int sah_sample_scatter(const int64_t* sptr, int64_t rows, const int64
   SAH_REQUIRE(rows >= 0 && n > 0 && n < (1ll << 32) && W * 32 >= S, "sample_scatter: bad extents");
   if (rows == 0) return SAH_OK;
   if (sm_count <= 0) sm_count = 148;
-  sah_launch_chain(sample_scatter_kernel, (unsigned)(sm_count * 8), 256, 0, (cudaStream_t)stream, sptr, rows, pool, seed, start, n, S, W, bits);
+  sah_launch_chain(sample_scatter_kernel, (unsigned)(sm_count * 8), 256, 0, (cudaStream_t)stream, sptr, rows,
+      pool, seed, start, n, S, W, bits);
   SAH_LAUNCH_CHECK("sample_scatter");
   return SAH_OK;
 }

@@ -233,9 +233,11 @@ extern "C" int sah_topk_select(const void* scores, int dtype, int64_t rows, int6
   cudaStream_t st = (cudaStream_t)stream;
   sah_prof_begin(SAH_PROF_TOPK_SELECT, (cudaStream_t)stream);
   if (dtype == SAH_BF16) {
-    sah_launch_chain(topk_select_kernel<__nv_bfloat16, 16>, (unsigned)rows, SAH_SELECT_THREADS, 0, st, (const __nv_bfloat16*)scores, S, W, col_begin, col_end, prev_bits, k, out_bits);
+    sah_launch_chain(topk_select_kernel<__nv_bfloat16, 16>, (unsigned)rows, SAH_SELECT_THREADS, 0, st,
+        (const __nv_bfloat16*)scores, S, W, col_begin, col_end, prev_bits, k, out_bits);
   } else if (dtype == SAH_F32) {
-    sah_launch_chain(topk_select_kernel<float, 32>, (unsigned)rows, SAH_SELECT_THREADS, 0, st, (const float*)scores, S, W, col_begin, col_end, prev_bits, k, out_bits);
+    sah_launch_chain(topk_select_kernel<float, 32>, (unsigned)rows, SAH_SELECT_THREADS, 0, st,
+        (const float*)scores, S, W, col_begin, col_end, prev_bits, k, out_bits);
   } else {
     return sah_fail(SAH_ERR_INVALID, "topk_select: unknown dtype %d", dtype);
   }
@@ -662,7 +664,8 @@ static int sel_hist_step(const T* scores, int64_t rows, int64_t S, int64_t W, in
   SelWorkspace o = sel_ws_carve(ws, rows, chunks);
   const int vec = ((S * (int64_t)sizeof(T)) % 16 == 0 && ((uintptr_t)scores % 16) == 0) ? 1 : 0;
   dim3 grid((unsigned)chunks, (unsigned)rows);
-  sah_launch_chain(sel_hist_kernel<T, KEYBITS>, grid, SEL_THREADS, 0, st, scores, S, W, col_begin, col_end, prev_bits, o.state,
+  sah_launch_chain(sel_hist_kernel<T, KEYBITS>, grid, SEL_THREADS, 0, st, scores, S, W, col_begin, col_end,
+      prev_bits, o.state,
                                                             o.hist, shift == 0 ? o.chunk_hist : nullptr, chunks,
                                                             shift, vec);
   SAH_LAUNCH_CHECK("topk_select hist");
@@ -694,7 +697,8 @@ extern "C" int sah_topk_sel_pick(int64_t rows, int64_t W, void* workspace, int s
   SAH_REQUIRE(workspace != nullptr && rows > 0, "topk_sel_pick: bad arguments");
   const int64_t chunks = (W + SEL_CHUNK_WORDS - 1) / SEL_CHUNK_WORDS;
   SelWorkspace o = sel_ws_carve(workspace, rows, chunks);
-  sah_launch_chain(sel_pick_kernel, (unsigned)rows, 256, 0, (cudaStream_t)stream, o.state, o.hist, shift, first, shift == 0 ? o.chunk_hist : nullptr, o.chunk_before, chunks,
+  sah_launch_chain(sel_pick_kernel, (unsigned)rows, 256, 0, (cudaStream_t)stream, o.state, o.hist, shift,
+      first, shift == 0 ? o.chunk_hist : nullptr, o.chunk_before, chunks,
       reinterpret_cast<long long*>(eq_total));
   SAH_LAUNCH_CHECK("topk_select pick");
   return SAH_OK;
@@ -708,7 +712,8 @@ static int sel_emit_step(const T* scores, int64_t rows, int64_t S, int64_t W, in
   SelWorkspace o = sel_ws_carve(ws, rows, chunks);
   const int vec = ((S * (int64_t)sizeof(T)) % 16 == 0 && ((uintptr_t)scores % 16) == 0) ? 1 : 0;
   dim3 grid((unsigned)chunks, (unsigned)rows);
-  sah_launch_chain(sel_emit_kernel<T, KEYBITS>, grid, SEL_THREADS, 0, st, scores, S, W, col_begin, col_end, prev_bits, o.state,
+  sah_launch_chain(sel_emit_kernel<T, KEYBITS>, grid, SEL_THREADS, 0, st, scores, S, W, col_begin, col_end,
+      prev_bits, o.state,
                                                             o.chunk_before, chunks, vec,
                                                             reinterpret_cast<const long long*>(tie_offset),
                                                             out_bits);
@@ -741,11 +746,13 @@ static int sel_run(const T* scores, int64_t rows, int64_t S, int64_t W, int64_t 
   dim3 grid((unsigned)g.chunks, (unsigned)rows);
   if (k > 0) {
     for (int digit = 0; digit < KEYBITS / 8; ++digit) {
-      sah_launch_chain(sel_fused_hist_kernel<T, KEYBITS>, grid, SEL_THREADS, 0, st, scores, S, W, col_begin, col_end, prev_bits, (long long)k, ch, rows, g.chunks, g.chunk_words, digit, vec);
+      sah_launch_chain(sel_fused_hist_kernel<T, KEYBITS>, grid, SEL_THREADS, 0, st, scores, S, W, col_begin,
+          col_end, prev_bits, (long long)k, ch, rows, g.chunks, g.chunk_words, digit, vec);
       SAH_LAUNCH_CHECK("topk_select digit histogram");
     }
   }
-  sah_launch_chain(sel_fused_emit_kernel<T, KEYBITS>, grid, SEL_THREADS, 0, st, scores, S, W, col_begin, col_end, prev_bits, (long long)k, ch, rows, g.chunks, g.chunk_words, vec, out_bits);
+  sah_launch_chain(sel_fused_emit_kernel<T, KEYBITS>, grid, SEL_THREADS, 0, st, scores, S, W, col_begin,
+      col_end, prev_bits, (long long)k, ch, rows, g.chunks, g.chunk_words, vec, out_bits);
   SAH_LAUNCH_CHECK("topk_select emit");
   return SAH_OK;
 }
