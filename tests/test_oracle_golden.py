@@ -142,3 +142,28 @@ def test_mask_interop_restatements(dtype):
     np.testing.assert_array_equal(idx, g["merged_idx"])
     np.testing.assert_array_equal(ptr, g["merged_ptr"])
     np.testing.assert_array_equal(data, g["merged_data"])
+
+
+@pytest.mark.parametrize("act,seed", [("relu", 22), ("gelu", 23), ("tanh", 24)])
+def test_hash_other_activations_against_the_reference(act, seed):
+    """The other activations of the reference's map, two-layer MLPs: sign bits agree with the
+    reference's except where the pre-sign output is within accumulation-order noise of zero (relu
+    leaves exact zeros, which the reference's sign() maps to 0 and the packing to a cleared bit,
+    as here); selection and output are exact given the reference's codes."""
+    g = load_golden(f"hash_bf16_{act}")
+    wl = workloads.hashattention_bf16(seed=seed, B=1, Hq=4, Hkv=2, S=777, D=128, sink=4, window=9,
+                                      heavy=40, bits=32, hidden=64, layers=2, activation=act)
+    w = wl.stack[2][1]["weights"]
+    y = hashattention.mlp_outputs(attention.repeat_kv(wl.k, 2), w["key_matrix"], w["key_bias"], act, "bf16")
+    codes = hashattention.pack_signs(y)
+    diff = codes ^ g["kcodes"]
+    n_bad = int(np.bitwise_count(diff).sum())
+    assert n_bad <= 2e-3 * codes.size * 32, n_bad
+    bad_bits = ((diff[..., None] >> np.arange(32, dtype=np.uint32)) & 1).astype(bool)
+    assert np.all(np.abs(y[bad_bits]) <= 0.05 * np.median(np.abs(y)))
+    yq = hashattention.mlp_outputs(wl.q, w["query_matrix"], w["query_bias"], act, "bf16")
+    assert int(np.bitwise_count(hashattention.pack_signs(yq) ^ g["qcodes"]).sum()) <= 2
+    meta = {"hash_kcodes": g["kcodes"], "hash_qcodes_in": g["qcodes"]}
+    mask, out, _ = stacks.run_stack(wl.stack, wl.q, wl.k, wl.v, wl.scaling, "bf16", meta=meta)
+    _check_mask(mask, g)
+    _check_out(out, g, "bf16")
