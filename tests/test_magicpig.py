@@ -75,6 +75,27 @@ def test_mask_exact_on_reference_codes(name):
     np.testing.assert_allclose(out, g["out"], atol=2e-2 if dtype == "bf16" else 1e-4, rtol=2e-2)
 
 
+def test_two_query_positions_two_batches_against_reference():
+    """The restatement on a reference fixture with B = 2, Sq = 2 and groups of two heads (the
+    local window of a query position ends at its own key): codes close to the reference's,
+    and index sets, weights and output from the reference's codes as the reference has them."""
+    g = load_golden("magicpig_bf16_sq2")
+    wl = workloads.magicpig(seed=64, dtype="bf16", B=2, Hq=4, Hkv=2, S=512, D=128, sink=4, window=8,
+                            lsh_l=20, lsh_k=8, n_clusters=8, Sq=2)
+    _, _, meta = _oracle(wl, {"lsh_key_mean": g["key_mean"]})
+    assert np.mean(meta["lsh_key_codes"] != g["key_sig"]) < 2e-3
+    assert np.mean(meta["lsh_query_codes"] != g["query_sig"]) < 2e-2
+    state = {"codes": g["key_sig"].astype(np.int64), "norms": np.zeros((2, 2, 0), np.float32),
+             "M": np.float32(0)}
+    mask, out, _ = _oracle(wl, {"lsh_key_mean": g["key_mean"], "lsh_state": state,
+                                "lsh_query_codes_in": g["query_sig"]})
+    idx, ptr, data = mask_ops.to_csr(mask)
+    np.testing.assert_array_equal(ptr, g["ptr"])
+    np.testing.assert_array_equal(idx, g["idx"])
+    np.testing.assert_allclose(data, g["data"], rtol=1.6e-2, atol=1.6e-4)
+    np.testing.assert_allclose(out, g["out"], atol=2e-2, rtol=2e-2)
+
+
 # ------------------------------------------------------------------ GPU: kernels vs restatement / reference
 def _native_stack(wl, meta, k=None, v=None):
     import torch

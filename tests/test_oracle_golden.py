@@ -167,3 +167,35 @@ def test_hash_other_activations_against_the_reference(act, seed):
     mask, out, _ = stacks.run_stack(wl.stack, wl.q, wl.k, wl.v, wl.scaling, "bf16", meta=meta)
     _check_mask(mask, g)
     _check_out(out, g, "bf16")
+
+
+@pytest.mark.parametrize("dtype,seed", [("bf16", 33), ("f32", 34)])
+def test_oracle_topk_three_query_positions_under_a_causal_mask(dtype, seed):
+    """The additive attention mask joins the scores before the selection
+    (oracle_top_k.py:70-76): from the reference's own score tensor the restatement reproduces
+    the reference's mask and output for three query positions under an HF causal mask."""
+    g = load_golden(f"oracle_topk_{dtype}_sq3_causal")
+    wl = workloads.oracle_topk(seed=seed, dtype=dtype, B=2, Hq=4, Hkv=2, S=320, D=64, sink=8, window=24,
+                               heavy=0.05, Sq=3)
+    meta = {"oracle_scores_in": g["scores"]}
+    mask, out, _ = stacks.run_stack(wl.stack, wl.q, wl.k, wl.v, wl.scaling, dtype, meta=meta,
+                                    attention_mask=g["attention_mask"])
+    _check_mask(mask, g)
+    _check_out(out, g, dtype)
+
+
+def test_hash_three_query_positions_under_a_causal_mask():
+    """The additive attention mask joins the Hamming scores before the top-k
+    (hashattention_top_k.py:343-371): from the reference's codes the restatement reproduces the
+    reference's mask and output for three query positions under an HF causal mask."""
+    g = load_golden("hash_bf16_sq3_causal")
+    wl = workloads.hashattention_bf16(seed=25, B=2, Hq=4, Hkv=2, S=320, D=64, sink=8, window=24,
+                                      heavy=0.1, bits=32, hidden=64, layers=3, activation="silu", Sq=3)
+    w = wl.stack[2][1]["weights"]
+    y = hashattention.mlp_outputs(attention.repeat_kv(wl.k, 2), w["key_matrix"], w["key_bias"], "silu", "bf16")
+    assert int(np.bitwise_count(hashattention.pack_signs(y) ^ g["kcodes"]).sum()) <= 2e-3 * y.size
+    meta = {"hash_kcodes": g["kcodes"], "hash_qcodes_in": g["qcodes"]}
+    mask, out, _ = stacks.run_stack(wl.stack, wl.q, wl.k, wl.v, wl.scaling, "bf16", meta=meta,
+                                    attention_mask=g["attention_mask"])
+    _check_mask(mask, g)
+    _check_out(out, g, "bf16")
