@@ -689,8 +689,9 @@ def run_native(args) -> None:
                 "algorithmic_bytes_per_launch": attn_bytes,
                 "avg_launch_us": attn_avg_ms * 1e3, "launches_timed": attn_n,
                 "traffic": attn_bytes * ratio if ratio else None,
-                "traffic_source": ("ncu capture of one launch of this workload (read + write), scaled "
-                                   "by the algorithmic bytes of the timed launch") if ratio else None,
+                "traffic_source": ("ncu capture of one launch of the mma.sync attention kernel on this "
+                                   "workload's union list (read + write), scaled by the algorithmic "
+                                   "bytes of the timed launch") if ratio else None,
                 "gather_only_gbs": probe_gbs,
             },
             "e2e": {
