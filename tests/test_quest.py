@@ -41,6 +41,25 @@ def test_restatement_against_reference(name, dtype, seed, S, D, page, heavy, mas
     np.testing.assert_allclose(out, g["out"], atol=1e-4 if dtype == "f32" else 2e-2, rtol=2e-2)
 
 
+def test_restatement_three_query_positions_under_a_causal_mask():
+    """Reference fixture with three query positions under an HF causal mask: page scores, index
+    sets, weights and output of the restatement are the reference's."""
+    g = load_golden("quest_bf16_sq3_causal")
+    wl = workloads.oracle_topk(seed=84, dtype="bf16", B=2, Hq=8, Hkv=2, S=640, D=128, sink=16, window=32, Sq=3)
+    stack = [("sink", {"sink_size": 16}), ("local", {"window_size": 32}),
+             ("quest_topk", {"heavy_size": 0.1, "page_size": 16})]
+    mask, out, meta = stacks.run_stack(stack, wl.q, wl.k, wl.v, wl.scaling, "bf16",
+                                       attention_mask=g["attention_mask"])
+    sc = meta["quest_page_scores"]
+    gated = sc < -1e30
+    np.testing.assert_array_equal(np.where(gated, g["page_scores"], sc), g["page_scores"])
+    idx, ptr, data = mask_ops.to_csr(mask)
+    np.testing.assert_array_equal(idx, g["idx"])
+    np.testing.assert_array_equal(ptr, g["ptr"])
+    np.testing.assert_array_equal(data, g["data"])
+    np.testing.assert_allclose(out, g["out"], atol=2e-2, rtol=2e-2)
+
+
 def test_row_sum_order_against_torch():
     """The restated reduction order is torch's on this machine, for both dtypes and odd lengths."""
     import torch

@@ -181,3 +181,18 @@ def test_gpu_weighted_previous_mask_merges_like_the_reference():
     ri, rp, rd = mask_ops.to_csr(ref_mask)
     np.testing.assert_array_equal(idx.cpu().numpy(), ri)
     np.testing.assert_array_equal(data.float().cpu().numpy(), rd)
+
+
+def test_restatement_three_query_positions_under_a_causal_mask():
+    """Reference fixture with three query positions under an HF causal mask (the additive mask
+    joins the scores before the softmax weights are ranked): same index sets, weights, output."""
+    g = load_golden("oracle_topp_bf16_sq3_causal")
+    wl = workloads.oracle_topk(seed=72, dtype="bf16", B=2, Hq=4, Hkv=2, S=640, D=64, sink=8, window=24, Sq=3)
+    stack = [("sink", {"sink_size": 8}), ("local", {"window_size": 24}), ("oracle_topp", {"top_p": 0.8})]
+    mask, out, _ = stacks.run_stack(stack, wl.q, wl.k, wl.v, wl.scaling, "bf16",
+                                    attention_mask=g["attention_mask"], meta={"oracle_scores_in": g["scores"]})
+    idx, ptr, data = mask_ops.to_csr(mask)
+    np.testing.assert_array_equal(idx, g["idx"])
+    np.testing.assert_array_equal(ptr, g["ptr"])
+    np.testing.assert_array_equal(data, g["data"])
+    np.testing.assert_allclose(out, g["out"], atol=2e-2, rtol=2e-2)
