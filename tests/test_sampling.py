@@ -64,6 +64,29 @@ def test_adaptive_against_reference(dtype):
         np.testing.assert_allclose(out, g["out"], atol=1e-4 if dtype == "f32" else 2e-2, rtol=2e-2)
 
 
+def test_adaptive_two_query_positions_against_reference():
+    """Reference fixture with two query positions (draws per (batch, head, query)): statistics
+    and budgets as close to the reference's as its own summation order allows, and, where the
+    budgets are equal, the same sampled sets, weights and output."""
+    g = load_golden("adaptive_f32_sq2")
+    wl = workloads.oracle_adaptive(seed=56, dtype="f32", B=2, Hq=4, Hkv=2, S=640, D=64, sink=16, window=32,
+                                   heavy=0.02, base_rate=0.05, epsilon=float(g["epsilon"]), delta=0.05, Sq=2)
+    meta = {"oracle_scores_in": g["scores"], "oracle_scores_unbiased": g["scores"],
+            "adaptive_base_draws": g["base"], "adaptive_pool": g["pool"]}
+    mask, out, meta = stacks.run_stack(wl.stack, wl.q, wl.k, wl.v, wl.scaling, "f32", meta=meta)
+    stats = meta["adaptive_stats"]
+    np.testing.assert_allclose(stats[:, 1], g["std"], rtol=1e-4)
+    np.testing.assert_allclose(stats[:, 2], g["est_den"], rtol=1e-4)
+    rel = np.abs(meta["adaptive_budget"] - g["budget"]) / g["budget"]
+    assert rel.max() <= 2e-3, rel
+    assert np.array_equal(meta["adaptive_budget"], g["budget"])
+    idx, ptr, data = mask_ops.to_csr(mask)
+    np.testing.assert_array_equal(idx, g["idx"])
+    np.testing.assert_array_equal(ptr, g["ptr"])
+    np.testing.assert_array_equal(data, g["data"])
+    np.testing.assert_allclose(out, g["out"], atol=1e-4, rtol=2e-2)
+
+
 def test_adaptive_mask_exact_on_reference_budget():
     """With the reference's budgets the sampled set and its weights are the reference's."""
     for dtype in ("f32", "bf16"):
