@@ -205,6 +205,21 @@ def test_pq_ip_metric_restatement_equals_the_reference():
     np.testing.assert_allclose(out, g["first_out"], atol=2e-2, rtol=2e-2)
 
 
+def test_pq_two_batches_two_query_positions_against_the_reference():
+    """Reference fixture with B = 2 and Sq = 2 (euclidean): centroids, codes, index sets and output
+    of the restatement are the reference's."""
+    g = load_golden("pq_stack_bf16_sq2")
+    wl = workloads.pqcache(seed=47, dtype="bf16", B=2, Hq=4, Hkv=2, S=400, D=128, sink=4, window=16,
+                           heavy=24, group_factor=N_SUB, bits=4, kmeans_iter=5, n_clusters=16, Sq=2)
+    meta = {"pq_init_indices": g["init_idx"],
+            "pq_reseed_indices": np.broadcast_to(g["reseed"], (5,) + g["reseed"].shape)}
+    mask, out, meta = stacks.run_stack(wl.stack, wl.q, wl.k, wl.v, wl.scaling, "bf16", meta=meta)
+    np.testing.assert_array_equal(meta["pq_centroids"], g["centroids"])
+    np.testing.assert_array_equal(meta["pq_codes"].transpose(0, 2, 1, 3), g["codes_first"])
+    _check_mask(mask, g, "first_")
+    np.testing.assert_allclose(out, g["first_out"], atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.gpu
 def test_gpu_ip_metric_build_decode_and_append_equal_the_reference():
     import torch
